@@ -1,0 +1,241 @@
+// Memory-bound glue kernels: embedding fan-out into hyper-connection streams, RMSNorm
+// (single and the fused q/kv pair), per-token-group FP8 quantisation (optionally fused
+// behind a norm), SwiGLU with clamp, MoE combine.
+//
+// Replaces the reference's RMSNorm / fused_q_kv_rmsnorm (overlay/attention.py:779-785),
+// per_token_group_quant "armada" and SiluAndMulWithClamp (MEASUREMENTS.md:544-546).
+#include "common.cuh"
+
+namespace stk {
+
+// out[t, j, :] = embed[ids[t], :] for j < hc.  Ids outside [0, vocab) write zeros and flag status.
+__global__ void embed_hc_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict__ embed,
+                                __nv_bfloat16* __restrict__ out, int H, int hc, int vocab, int vocab_start,
+                                int vocab_end, int* status) {
+  const int t = blockIdx.x;
+  const long long id = ids[t];
+  const bool in_vocab = id >= 0 && id < vocab;
+  if (!in_vocab && threadIdx.x == 0) set_status(status, kBadIndex, t);
+  const bool mine = in_vocab && id >= vocab_start && id < vocab_end;
+  const uint4* src = reinterpret_cast<const uint4*>(embed + (mine ? (id - vocab_start) : 0) * static_cast<long long>(H));
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<long long>(t) * hc * H);
+  const int n16 = H / 8;
+  for (int i = threadIdx.x; i < n16; i += blockDim.x) {
+    uint4 v = mine ? src[i] : make_uint4(0, 0, 0, 0);
+    for (int j = 0; j < hc; ++j) dst[j * n16 + i] = v;
+  }
+}
+
+// One CTA per row; grid.y selects one of up to two independent (x, w, out) problems.
+struct NormJob {
+  const __nv_bfloat16* x; long long ldx;
+  const __nv_bfloat16* w;            // may be null (weightless)
+  __nv_bfloat16* out; long long ldo;
+  int H;
+  uint8_t* q_out; long long ldq;     // optional fp8 copy of the normed row
+  float* q_scale; int q_scale_ld;    // [H/128, q_scale_ld] token-contiguous
+};
+
+__global__ void rmsnorm_kernel(NormJob j0, NormJob j1, float eps) {
+  extern __shared__ float sbuf[];     // H floats + 32
+  const NormJob& j = blockIdx.y == 0 ? j0 : j1;
+  const int t = blockIdx.x;
+  float* row = sbuf;
+  float* red = sbuf + j.H;
+  const __nv_bfloat16* x = j.x + t * j.ldx;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < j.H; i += blockDim.x) {
+    const float v = bf16_to_f(x[i]);
+    row[i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float r = rsqrtf(ss / j.H + eps);
+  for (int i = threadIdx.x; i < j.H; i += blockDim.x) {
+    float v = row[i] * r;
+    if (j.w) v *= bf16_to_f(j.w[i]);
+    const __nv_bfloat16 b = __float2bfloat16(v);
+    if (j.out) j.out[t * j.ldo + i] = b;
+    row[i] = bf16_to_f(b);
+  }
+  if (j.q_out) {
+    __syncthreads();
+    // one warp per 128-wide group
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int g = warp; g * 128 < j.H; g += nw) {
+      float v[4];
+      float amax = 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int i = g * 128 + lane * 4 + k;
+        v[k] = i < j.H ? row[i] : 0.f;
+        amax = fmaxf(amax, fabsf(v[k]));
+      }
+      amax = warp_max(amax);
+      const float scale = fmaxf(amax, 1e-10f) * (1.f / 448.f);
+      const float inv = 1.f / scale;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int i = g * 128 + lane * 4 + k;
+        if (i < j.H) j.q_out[t * j.ldq + i] = f_to_fp8(v[k] * inv);
+      }
+      if (lane == 0) j.q_scale[static_cast<long long>(g) * j.q_scale_ld + t] = scale;
+    }
+  }
+}
+
+// x bf16 [T, K] -> fp8 [T, K] + scales [K/128, ld] (scale = amax/448); one warp per group.
+__global__ void quant_fp8_group_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ q,
+                                       long long ldq, float* __restrict__ scales, int scale_ld, int T, int K) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int groups = (K + 127) / 128;
+  if (warp >= T * groups) return;
+  const int t = warp / groups, g = warp % groups;
+  float v[4];
+  float amax = 0.f;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int i = g * 128 + lane * 4 + k;
+    v[k] = i < K ? bf16_to_f(x[t * ldx + i]) : 0.f;
+    amax = fmaxf(amax, fabsf(v[k]));
+  }
+  amax = warp_max(amax);
+  const float scale = fmaxf(amax, 1e-10f) * (1.f / 448.f);
+  const float inv = 1.f / scale;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int i = g * 128 + lane * 4 + k;
+    if (i < K) q[t * ldq + i] = f_to_fp8(v[k] * inv);
+  }
+  if (lane == 0) scales[static_cast<long long>(g) * scale_ld + t] = scale;
+}
+
+// gu [T, 2I] (gate | up) -> act [T, I] = silu(min(g, lim)) * clamp(u, -lim, lim); optional fp8 copy.
+__global__ void swiglu_clamp_kernel(const __nv_bfloat16* __restrict__ gu, long long ldg, __nv_bfloat16* __restrict__ act,
+                                    long long lda, int I, float limit, uint8_t* q_out, long long ldq, float* q_scale,
+                                    int q_scale_ld) {
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int g = warp; g * 128 < I; g += nw) {
+    float v[4];
+    float amax = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int i = g * 128 + lane * 4 + k;
+      float r = 0.f;
+      if (i < I) {
+        float a = bf16_to_f(gu[t * ldg + i]);
+        float u = bf16_to_f(gu[t * ldg + I + i]);
+        if (limit > 0.f) {
+          a = fminf(a, limit);
+          u = fminf(fmaxf(u, -limit), limit);
+        }
+        r = a / (1.f + __expf(-a)) * u;
+        const __nv_bfloat16 b = __float2bfloat16(r);
+        if (act) act[t * lda + i] = b;
+        r = bf16_to_f(b);
+      }
+      v[k] = r;
+      amax = fmaxf(amax, fabsf(r));
+    }
+    if (q_out) {
+      amax = warp_max(amax);
+      const float scale = fmaxf(amax, 1e-10f) * (1.f / 448.f);
+      const float inv = 1.f / scale;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int i = g * 128 + lane * 4 + k;
+        if (i < I) q_out[t * ldq + i] = f_to_fp8(v[k] * inv);
+      }
+      if (lane == 0) q_scale[static_cast<long long>(g) * q_scale_ld + t] = scale;
+    }
+  }
+}
+
+// out[t, :] = sum_j w[t, j] * y[pair(t, j), :] (+ shared[t, :]); fixed j order => deterministic.
+__global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ w,
+                                   const int* __restrict__ pair_row, const __nv_bfloat16* __restrict__ shared,
+                                   __nv_bfloat16* __restrict__ out, int H, int topk) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
+    float a0 = 0.f, a1 = 0.f;
+    for (int j = 0; j < topk; ++j) {
+      const int r = pair_row ? pair_row[t * topk + j] : t * topk + j;
+      if (r < 0) continue;
+      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(y + static_cast<long long>(r) * H + i);
+      const float wt = w[t * topk + j];
+      a0 = fmaf(wt, __low2float(v), a0);
+      a1 = fmaf(wt, __high2float(v), a1);
+    }
+    if (shared) {
+      const __nv_bfloat162 s = *reinterpret_cast<const __nv_bfloat162*>(shared + static_cast<long long>(t) * H + i);
+      a0 += __low2float(s);
+      a1 += __high2float(s);
+    }
+    *reinterpret_cast<__nv_bfloat162*>(out + static_cast<long long>(t) * H + i) = __floats2bfloat162_rn(a0, a1);
+  }
+}
+
+}  // namespace stk
+
+using namespace stk;
+
+STK_API int stk_embed_hc(const int64_t* ids, const void* embed, void* out, int T, int H, int hc, int vocab,
+                         int vocab_start, int vocab_end, int* status, void* stream) {
+  if (T <= 0) return 0;
+  if (H % 8) return -1;
+  embed_hc_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(ids, (const __nv_bfloat16*)embed, (__nv_bfloat16*)out, H, hc,
+                                                       vocab, vocab_start, vocab_end, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Up to two independent RMSNorm problems in one launch (the q / kv pair).  Pass H1 = 0 for one.
+STK_API int stk_rmsnorm(const void* x0, long long ldx0, const void* w0, void* out0, long long ldo0, int H0,
+                        void* q0, long long ldq0, float* qs0, int qs_ld0,
+                        const void* x1, long long ldx1, const void* w1, void* out1, long long ldo1, int H1,
+                        int T, float eps, void* stream) {
+  if (T <= 0) return 0;
+  NormJob a{(const __nv_bfloat16*)x0, ldx0, (const __nv_bfloat16*)w0, (__nv_bfloat16*)out0, ldo0, H0,
+            (uint8_t*)q0, ldq0, qs0, qs_ld0};
+  NormJob b{(const __nv_bfloat16*)x1, ldx1, (const __nv_bfloat16*)w1, (__nv_bfloat16*)out1, ldo1, H1,
+            nullptr, 0, nullptr, 0};
+  const int hmax = H0 > H1 ? H0 : H1;
+  const size_t smem = (hmax + 32) * sizeof(float);
+  if (smem > 200 * 1024) return -2;
+  static bool configured = false;
+  if (!configured && smem > 48 * 1024) {
+    cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    configured = true;
+  }
+  dim3 grid(T, H1 > 0 ? 2 : 1);
+  rmsnorm_kernel<<<grid, 256, smem, (cudaStream_t)stream>>>(a, b, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+STK_API int stk_quant_fp8_group128(const void* x, long long ldx, void* q, long long ldq, float* scales, int scale_ld,
+                                   int T, int K, void* stream) {
+  if (T <= 0) return 0;
+  const long long warps = static_cast<long long>(T) * ((K + 127) / 128);
+  const int blocks = static_cast<int>((warps + 7) / 8);
+  quant_fp8_group_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq,
+                                                                   scales, scale_ld, T, K);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+STK_API int stk_swiglu_clamp(const void* gu, long long ldg, void* act, long long lda, int T, int I, float limit,
+                             void* q_out, long long ldq, float* q_scale, int q_scale_ld, void* stream) {
+  if (T <= 0) return 0;
+  swiglu_clamp_kernel<<<T, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)gu, ldg, (__nv_bfloat16*)act, lda, I,
+                                                           limit, (uint8_t*)q_out, ldq, q_scale, q_scale_ld);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+STK_API int stk_moe_combine(const void* y, const float* w, const int* pair_row, const void* shared, void* out, int T,
+                            int H, int topk, void* stream) {
+  if (T <= 0) return 0;
+  if (H % 2) return -1;
+  moe_combine_kernel<<<T, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)y, w, pair_row,
+                                                          (const __nv_bfloat16*)shared, (__nv_bfloat16*)out, H, topk);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

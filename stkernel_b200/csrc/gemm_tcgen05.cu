@@ -1,0 +1,445 @@
+// Dense linear layer on the 5th-generation tensor cores:  out[T, N] = X[T, K] * W[N, K]^T
+//
+// * Operands arrive by TMA (128-byte swizzle) into a multi-stage shared-memory ring.
+// * One elected thread issues tcgen05.mma; the accumulator lives in TMEM (double buffered).
+// * The weight tile is the 128-row "M" operand and the token tile is the "N" operand
+//   (16..256 tokens), so decode-sized batches still use full-height MMAs and each epilogue
+//   thread owns one output feature, which makes the global stores contiguous across a warp.
+// * bf16 operands: one accumulation over all of K, epilogue once per tile.
+// * fp8 e4m3 operands with 128x128 weight scales and 1x128 activation scales: one TMEM
+//   accumulation per 128-wide K block; the epilogue warps fold `w_scale * x_scale` into
+//   fp32 register accumulators while the next block's MMAs run (two-level accumulation).
+// * Split-K for skinny problems: partial tiles go to an fp32 workspace, the last CTA to
+//   finish a tile sums the partials in split order (deterministic) and writes the output.
+// * Persistent grid: one CTA per SM walks the (split, token-tile, feature-tile) list.
+//
+// Covers the reference's DeepGEMM fp8_gemm_nt call sites (overlay/dspark_v2.py:92-107,
+// probes/oproj_prof.py:65-71) and its bf16 cuBLAS projections.
+#include "common.cuh"
+#include "stk_c_api.h"
+
+namespace stk {
+
+struct GemmArgs {
+  int T, N;
+  int k_blocks;          // K extent in 128-byte blocks
+  int splits;            // split-K factor (>= 1)
+  int tiles_n, tiles_t;
+  void* out;             // [T, ldo]
+  long long ldo;
+  int out_fp32;
+  const float* w_scale;  // fp8 only: [ceil(N/128), w_scale_ld]
+  int w_scale_ld;
+  const float* x_scale;  // fp8 only: [k_blocks, x_scale_ld]  (token index contiguous)
+  int x_scale_ld;
+  float* workspace;      // split-K partials [splits, T, N]
+  int* counters;         // one per output tile; zero on entry, zero again on exit
+  int* status;
+};
+
+template <int BT>
+struct GemmCfg {
+  static constexpr int kStageBytes = 128 * 128 + BT * 128;
+  static constexpr int kStagesRaw = (196 * 1024) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kTmemCols = (2 * BT <= 32) ? 32 : (2 * BT <= 64) ? 64 : (2 * BT <= 128) ? 128 : (2 * BT <= 256) ? 256 : 512;
+  static constexpr int kChunk = BT >= 32 ? 32 : 16;
+};
+
+struct alignas(8) GemmBarriers {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int last_flag;
+};
+
+template <int CW>
+__device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, uint32_t (&r)[32]) {
+  if constexpr (CW == 32) {
+    tmem_ld_32x32(taddr, r);
+  } else {
+    uint32_t t[16];
+    tmem_ld_32x16(taddr, t);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) r[i] = t[i];
+  }
+}
+
+__device__ __forceinline__ void epi_bar_sync(int nthreads) {
+  asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
+}
+
+template <int BT, bool kFp8>
+__global__ void __launch_bounds__(kFp8 ? 320 : 192, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmArgs a) {
+  using Cfg = GemmCfg<BT>;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int CW = Cfg::kChunk;
+  // epilogue warps: fp8 with wide tiles splits the columns over two warps per lane quarter
+  constexpr int kEpiWarps = (kFp8 && BT >= 64) ? 8 : 4;
+  constexpr int kColsPerWarp = (kEpiWarps == 8) ? BT / 2 : BT;
+  constexpr int kChunksPerWarp = kColsPerWarp / CW;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem_a = smem;                                  // kStages x 16 KB
+  uint8_t* smem_b = smem + kStages * 128 * 128;            // kStages x BT*128
+  GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(smem_b + kStages * BT * 128);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->tmem_full[i], 1);
+      mbar_init(&bars->tmem_empty[i], kEpiWarps);
+    }
+    bars->last_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  const int units = a.splits * a.tiles_t * a.tiles_n;
+  const int kb_per_split = (a.k_blocks + a.splits - 1) / a.splits;
+  constexpr uint32_t kIdesc = umma_idesc(kFp8 ? 0u : 1u, kFp8 ? 0u : 1u, 128, BT);
+  constexpr uint32_t kTxBytes = 128 * 128 + BT * 128;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int issued = 0;
+      for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+        const int tn = u % a.tiles_n;
+        const int tt = (u / a.tiles_n) % a.tiles_t;
+        const int sp = u / (a.tiles_n * a.tiles_t);
+        const int kb0 = sp * kb_per_split;
+        const int kb1 = min(a.k_blocks, kb0 + kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&bars->empty[stage], phase ^ 1, a.status, 100 + stage)) { ok = false; break; }
+          mbar_expect_tx(&bars->full[stage], kTxBytes);
+          const int kx = kb * (kFp8 ? 128 : 64);
+          tma_load_2d(smem_a + stage * 128 * 128, &tmW, &bars->full[stage], kx, tn * 128);
+          tma_load_2d(smem_b + stage * BT * 128, &tmX, &bars->full[stage], kx, tt * BT);
+          ++issued;
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // Drain: wait (bounded) until every load issued to the ring has landed.
+        const int pending = issued < kStages ? issued : kStages;
+        int s = stage;
+        uint32_t ph = phase;
+        for (int i = 0; i < pending; ++i) {
+          if (--s < 0) { s = kStages - 1; ph ^= 1; }
+          mbar_wait(&bars->full[s], ph, nullptr, 0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int ab = 0;
+      uint32_t aphase = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+        const int sp = u / (a.tiles_n * a.tiles_t);
+        const int kb0 = sp * kb_per_split;
+        const int kb1 = min(a.k_blocks, kb0 + kb_per_split);
+        if constexpr (!kFp8) {
+          if (!mbar_wait(&bars->tmem_empty[ab], aphase ^ 1, a.status, 200 + ab)) { ok = false; break; }
+          tc_fence_after();
+        }
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if constexpr (kFp8) {
+            if (!mbar_wait(&bars->tmem_empty[ab], aphase ^ 1, a.status, 200 + ab)) { ok = false; break; }
+          }
+          if (!mbar_wait(&bars->full[stage], phase, a.status, 300 + stage)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d = tmem_base + ab * BT;
+          const uint64_t adesc = umma_desc_sw128(smem_u32(smem_a + stage * 128 * 128));
+          const uint64_t bdesc = umma_desc_sw128(smem_u32(smem_b + stage * BT * 128));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            // advance 32 bytes along K inside the swizzled 128-byte row (encoded >> 4)
+            const uint32_t acc = kFp8 ? (k > 0) : (kb > kb0 || k > 0);
+            if constexpr (kFp8) umma_f8(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+            else umma_f16(d, adesc + 2 * k, bdesc + 2 * k, kIdesc, acc);
+          }
+          umma_commit(&bars->empty[stage]);
+          if constexpr (kFp8) {
+            umma_commit(&bars->tmem_full[ab]);
+            if (++ab == 2) { ab = 0; aphase ^= 1; }
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if constexpr (!kFp8) {
+          if (ok) {
+            umma_commit(&bars->tmem_full[ab]);
+            if (++ab == 2) { ab = 0; aphase ^= 1; }
+          }
+        }
+      }
+    }
+  } else if (warp - 2 < kEpiWarps) {
+    // ------------------------------ epilogue -----------------------------------
+    const int e = warp - 2;
+    const int q = warp & 3;                         // TMEM lane quarter this warp may read
+    const int col_base = (kEpiWarps == 8) ? (e >> 2) * kColsPerWarp : 0;
+    const int row = q * 32 + lane;
+    int ab = 0;
+    uint32_t aphase = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+      const int tn = u % a.tiles_n;
+      const int tt = (u / a.tiles_n) % a.tiles_t;
+      const int sp = u / (a.tiles_n * a.tiles_t);
+      const int kb0 = sp * kb_per_split;
+      const int kb1 = min(a.k_blocks, kb0 + kb_per_split);
+      const int n = tn * 128 + row;
+      const int t0 = tt * BT + col_base;
+      const bool n_ok = n < a.N;
+
+      auto store = [&](int t, float v) {
+        if (n_ok && t < a.T) {
+          if (a.splits > 1) {
+            a.workspace[(static_cast<long long>(sp) * a.T + t) * a.N + n] = v;
+          } else if (a.out_fp32) {
+            reinterpret_cast<float*>(a.out)[t * a.ldo + n] = v;
+          } else {
+            reinterpret_cast<__nv_bfloat16*>(a.out)[t * a.ldo + n] = __float2bfloat16(v);
+          }
+        }
+      };
+
+      if constexpr (kFp8) {
+        float acc[kColsPerWarp];
+#pragma unroll
+        for (int j = 0; j < kColsPerWarp; ++j) acc[j] = 0.f;
+        for (int kb = kb0; kb < kb1 && ok; ++kb) {
+          const float sw = a.w_scale[tn * a.w_scale_ld + kb];
+          const float* xs = a.x_scale + static_cast<long long>(kb) * a.x_scale_ld;
+          if (!mbar_wait(&bars->tmem_full[ab], aphase, a.status, 400 + ab)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < kChunksPerWarp; ++c) {
+            uint32_t r[32];
+            tmem_ld_chunk<CW>(tmem_base + ab * BT + col_base + c * CW + (static_cast<uint32_t>(q * 32) << 16), r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < CW; j += 4) {
+              const int t = t0 + c * CW + j;
+              float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (t + 4 <= a.x_scale_ld) s4 = __ldg(reinterpret_cast<const float4*>(xs + t));
+              acc[c * CW + j + 0] = fmaf(__uint_as_float(r[j + 0]), sw * s4.x, acc[c * CW + j + 0]);
+              acc[c * CW + j + 1] = fmaf(__uint_as_float(r[j + 1]), sw * s4.y, acc[c * CW + j + 1]);
+              acc[c * CW + j + 2] = fmaf(__uint_as_float(r[j + 2]), sw * s4.z, acc[c * CW + j + 2]);
+              acc[c * CW + j + 3] = fmaf(__uint_as_float(r[j + 3]), sw * s4.w, acc[c * CW + j + 3]);
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->tmem_empty[ab]);
+          if (++ab == 2) { ab = 0; aphase ^= 1; }
+        }
+        if (ok) {
+#pragma unroll
+          for (int j = 0; j < kColsPerWarp; ++j) store(t0 + j, acc[j]);
+        }
+      } else {
+        if (!mbar_wait(&bars->tmem_full[ab], aphase, a.status, 400 + ab)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < kChunksPerWarp; ++c) {
+          uint32_t r[32];
+          tmem_ld_chunk<CW>(tmem_base + ab * BT + col_base + c * CW + (static_cast<uint32_t>(q * 32) << 16), r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < CW; ++j) store(t0 + c * CW + j, __uint_as_float(r[j]));
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->tmem_empty[ab]);
+        if (++ab == 2) { ab = 0; aphase ^= 1; }
+      }
+
+      if (a.splits > 1 && ok) {
+        // Publish this split's partial; the CTA that completes the tile reduces it.
+        __threadfence();
+        epi_bar_sync(kEpiWarps * 32);
+        if (threadIdx.x == 64) {
+          const int prev = atomicAdd(&a.counters[tt * a.tiles_n + tn], 1);
+          bars->last_flag = (prev == a.splits - 1);
+          if (prev == a.splits - 1) a.counters[tt * a.tiles_n + tn] = 0;
+        }
+        epi_bar_sync(kEpiWarps * 32);
+        const bool last = bars->last_flag != 0;
+        epi_bar_sync(kEpiWarps * 32);
+        if (last) {
+          __threadfence();
+          if (n_ok) {
+            for (int j = 0; j < kColsPerWarp; ++j) {
+              const int t = t0 + j;
+              if (t >= a.T) break;
+              float s = 0.f;
+              for (int p = 0; p < a.splits; ++p)
+                s += __ldcg(&a.workspace[(static_cast<long long>(p) * a.T + t) * a.N + n]);
+              if (a.out_fp32) reinterpret_cast<float*>(a.out)[t * a.ldo + n] = s;
+              else reinterpret_cast<__nv_bfloat16*>(a.out)[t * a.ldo + n] = __float2bfloat16(s);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  }
+  return fn;
+}
+
+// 2-D row-major [rows, cols] tensor with `ld` elements between rows; box = [box_rows, 128 bytes].
+int make_tmap_2d(CUtensorMap* tm, const void* base, int elem_bytes, long long rows, long long cols, long long ld,
+                 int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return -1;
+  CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                         : elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * elem_bytes};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elem_bytes), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
+template <int BT, bool kFp8>
+static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmArgs& a, int grid, cudaStream_t st) {
+  using Cfg = GemmCfg<BT>;
+  const int smem = Cfg::kStages * Cfg::kStageBytes + static_cast<int>(sizeof(GemmBarriers)) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_kernel<BT, kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return -3;
+    configured = true;
+  }
+  gemm_kernel<BT, kFp8><<<grid, kFp8 ? 320 : 192, smem, st>>>(tw, tx, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+}  // namespace stk
+
+using namespace stk;
+
+STK_API int stk_gemm_pick_bt(int T, int is_fp8) {
+  const int cap = is_fp8 ? 128 : 256;
+  int bt = 16;
+  while (bt < T && bt < cap) bt *= 2;
+  return bt;
+}
+
+// Suggested split-K factor so that a skinny problem still fills the SMs.
+STK_API int stk_gemm_pick_splits(int T, int N, int K, int is_fp8, int sm_count) {
+  const int bt = stk_gemm_pick_bt(T, is_fp8);
+  const int tiles = ((N + 127) / 128) * ((T + bt - 1) / bt);
+  const int kb = (K * (is_fp8 ? 1 : 2) + 127) / 128;
+  if (tiles >= sm_count || T > 256) return 1;
+  int s = sm_count / tiles;
+  if (s > kb / 2) s = kb / 2;      // keep at least two K blocks per split
+  if (s > 16) s = 16;
+  return s < 1 ? 1 : s;
+}
+
+STK_API long long stk_gemm_workspace_bytes(int T, int N, int splits) {
+  return splits > 1 ? static_cast<long long>(splits) * T * N * 4 : 0;
+}
+
+STK_API int stk_gemm(const void* W, long long ldw, const void* X, long long ldx, void* out, long long ldo, int T, int N,
+                     int K, int is_fp8, int out_fp32, const float* w_scale, int w_scale_ld, const float* x_scale,
+                     int x_scale_ld, int splits, float* workspace, int* counters, int* status, int sm_count,
+                     void* stream) {
+  if (T <= 0 || N <= 0 || K <= 0) return 0;
+  const int es = is_fp8 ? 1 : 2;
+  if ((ldw * es) % 16 || (ldx * es) % 16 || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(X) & 15))
+    return -10;
+  if (is_fp8 && (w_scale == nullptr || x_scale == nullptr || (x_scale_ld & 3))) return -11;
+  if (splits > 1 && (workspace == nullptr || counters == nullptr)) return -12;
+  const int bt = stk_gemm_pick_bt(T, is_fp8);
+  CUtensorMap tw, tx;
+  if (make_tmap_2d(&tw, W, es, N, K, ldw, 128) != 0) return -13;
+  if (make_tmap_2d(&tx, X, es, T, K, ldx, bt) != 0) return -14;
+  GemmArgs a;
+  a.T = T; a.N = N;
+  a.k_blocks = (K * es + 127) / 128;
+  a.splits = splits < 1 ? 1 : splits;
+  if (a.splits > a.k_blocks) a.splits = a.k_blocks;
+  {  // no split may own an empty K range: its accumulator would never be written
+    const int per = (a.k_blocks + a.splits - 1) / a.splits;
+    a.splits = (a.k_blocks + per - 1) / per;
+  }
+  a.tiles_n = (N + 127) / 128;
+  a.tiles_t = (T + bt - 1) / bt;
+  a.out = out; a.ldo = ldo; a.out_fp32 = out_fp32;
+  a.w_scale = w_scale; a.w_scale_ld = w_scale_ld;
+  a.x_scale = x_scale; a.x_scale_ld = x_scale_ld;
+  a.workspace = workspace; a.counters = counters; a.status = status;
+  const int units = a.splits * a.tiles_n * a.tiles_t;
+  const int grid = units < sm_count ? units : sm_count;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#define STK_LAUNCH(BT_) (is_fp8 ? launch_gemm<BT_, true>(tw, tx, a, grid, st) : launch_gemm<BT_, false>(tw, tx, a, grid, st))
+  switch (bt) {
+    case 16: return STK_LAUNCH(16);
+    case 32: return STK_LAUNCH(32);
+    case 64: return STK_LAUNCH(64);
+    case 128: return STK_LAUNCH(128);
+    case 256: return is_fp8 ? -15 : launch_gemm<256, false>(tw, tx, a, grid, st);
+  }
+#undef STK_LAUNCH
+  return -16;
+}

@@ -1,0 +1,331 @@
+// Manifold hyper-connection kernels (4 residual streams):
+//   mhc_dots      partial products  x_flat[t, :] . fn[j, :]  and  sum x^2   (split over hc*H)
+//   mhc_finalize  rms, sigmoid pre/post mixes, Sinkhorn-normalised hc x hc combine matrix,
+//                 weighted stream sum, fused RMSNorm -> layer input
+//   mhc_post      out[j] = post[j]*x + sum_k comb[j,k]*res[k]
+//   hc_head       collapse the streams with sigmoid weights
+//
+// Same math as the reference's prenorm GEMM + "big fuse" (overlay/mhc_tilelang.py:206-325)
+// and its post mix (overlay/nvidia_model.py:1779-1785).  For large token counts the dot
+// products can instead come from the tcgen05 GEMM (fn kept as a bf16 copy); `mhc_finalize`
+// then takes them as a single pre-reduced split.
+#include "common.cuh"
+
+namespace stk {
+
+constexpr int kMaxMix = 24;
+constexpr int kTokBlock = 4;      // tokens sharing one pass over an fn slice
+
+// grid (ceil(T/4), n_splits); partial [n_splits, T, n_mix + 1] (last entry = sum of squares)
+template <int NMIX>
+__global__ void __launch_bounds__(256)
+mhc_dots_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ fn, float* __restrict__ partial, int T,
+                int HC, int slice) {
+  __shared__ float red[8][kTokBlock][NMIX + 1];
+  const int t0 = blockIdx.x * kTokBlock;
+  const int sp = blockIdx.y;
+  const int k0 = sp * slice;
+  const int k1 = min(HC, k0 + slice);
+  float acc[kTokBlock][NMIX];
+  float ss[kTokBlock];
+#pragma unroll
+  for (int i = 0; i < kTokBlock; ++i) {
+    ss[i] = 0.f;
+#pragma unroll
+    for (int j = 0; j < NMIX; ++j) acc[i][j] = 0.f;
+  }
+  for (int k = k0 + threadIdx.x * 2; k < k1; k += blockDim.x * 2) {
+    float xa[kTokBlock], xb[kTokBlock];
+#pragma unroll
+    for (int i = 0; i < kTokBlock; ++i) {
+      if (t0 + i < T) {
+        const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(x + static_cast<long long>(t0 + i) * HC + k);
+        xa[i] = __low2float(v);
+        xb[i] = __high2float(v);
+      } else {
+        xa[i] = xb[i] = 0.f;
+      }
+      ss[i] = fmaf(xa[i], xa[i], fmaf(xb[i], xb[i], ss[i]));
+    }
+#pragma unroll
+    for (int j = 0; j < NMIX; ++j) {
+      const float2 f = *reinterpret_cast<const float2*>(fn + static_cast<long long>(j) * HC + k);
+#pragma unroll
+      for (int i = 0; i < kTokBlock; ++i) acc[i][j] = fmaf(xa[i], f.x, fmaf(xb[i], f.y, acc[i][j]));
+    }
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int i = 0; i < kTokBlock; ++i) {
+#pragma unroll
+    for (int j = 0; j < NMIX; ++j) {
+      const float v = warp_sum(acc[i][j]);
+      if (lane == 0) red[warp][i][j] = v;
+    }
+    const float v = warp_sum(ss[i]);
+    if (lane == 0) red[warp][i][NMIX] = v;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < kTokBlock * (NMIX + 1); idx += blockDim.x) {
+    const int i = idx / (NMIX + 1), j = idx % (NMIX + 1);
+    if (t0 + i >= T) continue;
+    float s = 0.f;
+    for (int w = 0; w < 8; ++w) s += red[w][i][j];
+    partial[(static_cast<long long>(sp) * T + (t0 + i)) * (NMIX + 1) + j] = s;
+  }
+}
+
+// One CTA (256 threads) per token.  partial: [n_splits, T, n_mix+1] fp32 when sumsq_in_partial,
+// else dots only [n_splits, T, n_mix] and the kernel computes sum x^2 itself.
+// mode 0: mHC pre (writes post [T,hc], comb [T,hc*hc], y [T,H] normed by norm_w)
+// mode 1: hc_head (writes y [T,H] = sum_j w_j x_j, no norm)
+__global__ void __launch_bounds__(256)
+mhc_finalize_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ partial, int n_splits,
+                    int partial_ld, int sumsq_in_partial, const float* __restrict__ base,
+                    const float* __restrict__ scale, const __nv_bfloat16* __restrict__ norm_w, float* __restrict__ post,
+                    float* __restrict__ comb, __nv_bfloat16* __restrict__ y, int T, int H, int hc, float rms_eps,
+                    float hc_eps, int sinkhorn_iters, float post_mult, int mode, uint8_t* q_out, float* q_scale,
+                    int q_scale_ld) {
+  extern __shared__ float sm[];          // H floats (stream sum) + 64
+  float* ybuf = sm;
+  float* mixes = sm + H;                 // kMaxMix
+  float* pre = mixes + kMaxMix;          // up to 8
+  float* red = pre + 8;                  // 32
+  const int t = blockIdx.x;
+  const int n_mix = mode == 0 ? (2 + hc) * hc : hc;
+  const long long HC = static_cast<long long>(hc) * H;
+  const __nv_bfloat16* xt = x + t * HC;
+
+  float ssq = 0.f;
+  if (!sumsq_in_partial) {
+    for (int k = threadIdx.x * 2; k < HC; k += blockDim.x * 2) {
+      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(xt + k);
+      ssq = fmaf(__low2float(v), __low2float(v), fmaf(__high2float(v), __high2float(v), ssq));
+    }
+    ssq = block_sum(ssq, red);
+  }
+  if (threadIdx.x < 32) {
+    if (threadIdx.x < n_mix) {
+      float m = 0.f;
+      for (int s = 0; s < n_splits; ++s) m += partial[(static_cast<long long>(s) * T + t) * partial_ld + threadIdx.x];
+      mixes[threadIdx.x] = m;
+    }
+    if (sumsq_in_partial && threadIdx.x == 31) {
+      float q = 0.f;
+      for (int s = 0; s < n_splits; ++s) q += partial[(static_cast<long long>(s) * T + t) * partial_ld + n_mix];
+      red[0] = q;
+    }
+  }
+  __syncthreads();
+  if (sumsq_in_partial) ssq = red[0];
+  const float rms = rsqrtf(ssq / static_cast<float>(HC) + rms_eps);
+  __syncthreads();
+
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    if (mode == 0) {
+      if (lane < hc) {
+        pre[lane] = 1.f / (1.f + __expf(-(mixes[lane] * rms * scale[0] + base[lane]))) + hc_eps;
+        post[t * hc + lane] = post_mult / (1.f + __expf(-(mixes[hc + lane] * rms * scale[1] + base[hc + lane])));
+      }
+      // Sinkhorn on an hc x hc matrix: lane = j*hc + k (hc <= 5 fits one warp)
+      const int j = lane / hc, k = lane % hc;
+      const bool act = lane < hc * hc;
+      float c = act ? mixes[2 * hc + lane] * rms * scale[2] + base[2 * hc + lane] : -INFINITY;
+      // row softmax
+      float rmax = c;
+      for (int o = 1; o < hc; ++o) {
+        const float other = __shfl_sync(0xffffffffu, c, j * hc + ((k + o) % hc));
+        if (act) rmax = fmaxf(rmax, other);
+      }
+      float e = act ? __expf(c - rmax) : 0.f;
+      float rs = e;
+      for (int o = 1; o < hc; ++o) {
+        const float other = __shfl_sync(0xffffffffu, e, j * hc + ((k + o) % hc));
+        if (act) rs += other;
+      }
+      c = act ? e / rs + hc_eps : 0.f;
+      auto col_norm = [&]() {
+        float cs = c;
+        for (int o = 1; o < hc; ++o) {
+          const float other = __shfl_sync(0xffffffffu, c, ((j + o) % hc) * hc + k);
+          if (act) cs += other;
+        }
+        if (act) c = c / (cs + hc_eps);
+      };
+      auto row_norm = [&]() {
+        float s = c;
+        for (int o = 1; o < hc; ++o) {
+          const float other = __shfl_sync(0xffffffffu, c, j * hc + ((k + o) % hc));
+          if (act) s += other;
+        }
+        if (act) c = c / (s + hc_eps);
+      };
+      col_norm();
+      for (int it = 0; it < sinkhorn_iters - 1; ++it) {
+        row_norm();
+        col_norm();
+      }
+      if (act) comb[t * hc * hc + lane] = c;
+    } else {
+      if (lane < hc) pre[lane] = 1.f / (1.f + __expf(-(mixes[lane] * rms * scale[0] + base[lane]))) + hc_eps;
+    }
+  }
+  __syncthreads();
+
+  // weighted stream sum (rounded to bf16 like the layer input the norm sees)
+  float ss = 0.f;
+  for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
+    float a0 = 0.f, a1 = 0.f;
+    for (int j = 0; j < hc; ++j) {
+      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(xt + static_cast<long long>(j) * H + i);
+      a0 = fmaf(pre[j], __low2float(v), a0);
+      a1 = fmaf(pre[j], __high2float(v), a1);
+    }
+    if (mode == 0) {
+      a0 = bf16_to_f(__float2bfloat16(a0));
+      a1 = bf16_to_f(__float2bfloat16(a1));
+    }
+    ybuf[i] = a0;
+    ybuf[i + 1] = a1;
+    ss = fmaf(a0, a0, fmaf(a1, a1, ss));
+  }
+  float r = 1.f;
+  if (mode == 0 && norm_w != nullptr) {
+    ss = block_sum(ss, red);
+    r = rsqrtf(ss / H + rms_eps);
+  }
+  for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
+    float a0 = ybuf[i] * r, a1 = ybuf[i + 1] * r;
+    if (mode == 0 && norm_w != nullptr) {
+      a0 *= bf16_to_f(norm_w[i]);
+      a1 *= bf16_to_f(norm_w[i + 1]);
+    }
+    const __nv_bfloat162 o = __floats2bfloat162_rn(a0, a1);
+    *reinterpret_cast<__nv_bfloat162*>(y + static_cast<long long>(t) * H + i) = o;
+    ybuf[i] = __low2float(o);
+    ybuf[i + 1] = __high2float(o);
+  }
+  if (q_out != nullptr) {
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int g = warp; g * 128 < H; g += 8) {
+      float v[4];
+      float amax = 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int i = g * 128 + lane * 4 + k;
+        v[k] = i < H ? ybuf[i] : 0.f;
+        amax = fmaxf(amax, fabsf(v[k]));
+      }
+      amax = warp_max(amax);
+      const float sc = fmaxf(amax, 1e-10f) * (1.f / 448.f);
+      const float inv = 1.f / sc;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int i = g * 128 + lane * 4 + k;
+        if (i < H) q_out[static_cast<long long>(t) * H + i] = f_to_fp8(v[k] * inv);
+      }
+      if (lane == 0) q_scale[static_cast<long long>(g) * q_scale_ld + t] = sc;
+    }
+  }
+}
+
+// out[t, j, :] = post[t, j] * x[t, :] + sum_k comb[t, j, k] * res[t, k, :]   (in place on res allowed
+// only when out != res; the engine ping-pongs two residual buffers).
+template <int HCM>
+__global__ void __launch_bounds__(256)
+mhc_post_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                const float* __restrict__ post, const float* __restrict__ comb, __nv_bfloat16* __restrict__ out, int H) {
+  const int t = blockIdx.x;
+  __shared__ float sp[HCM], sc[HCM * HCM];
+  if (threadIdx.x < HCM) sp[threadIdx.x] = post[t * HCM + threadIdx.x];
+  if (threadIdx.x < HCM * HCM) sc[threadIdx.x] = comb[t * HCM * HCM + threadIdx.x];
+  __syncthreads();
+  const long long base = static_cast<long long>(t) * HCM * H;
+  for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 2; i < H; i += gridDim.y * blockDim.x * 2) {
+    const __nv_bfloat162 xv = *reinterpret_cast<const __nv_bfloat162*>(x + static_cast<long long>(t) * H + i);
+    const float x0 = __low2float(xv), x1 = __high2float(xv);
+    float r0[HCM], r1[HCM];
+#pragma unroll
+    for (int k = 0; k < HCM; ++k) {
+      const __nv_bfloat162 rv = *reinterpret_cast<const __nv_bfloat162*>(res + base + static_cast<long long>(k) * H + i);
+      r0[k] = __low2float(rv);
+      r1[k] = __high2float(rv);
+    }
+#pragma unroll
+    for (int j = 0; j < HCM; ++j) {
+      float a0 = sp[j] * x0, a1 = sp[j] * x1;
+#pragma unroll
+      for (int k = 0; k < HCM; ++k) {
+        a0 = fmaf(sc[j * HCM + k], r0[k], a0);
+        a1 = fmaf(sc[j * HCM + k], r1[k], a1);
+      }
+      *reinterpret_cast<__nv_bfloat162*>(out + base + static_cast<long long>(j) * H + i) = __floats2bfloat162_rn(a0, a1);
+    }
+  }
+}
+
+}  // namespace stk
+
+using namespace stk;
+
+STK_API int stk_mhc_pick_splits(int T, int HC) {
+  // enough CTAs to fill the machine at decode sizes, one slice >= 1024 elements
+  int s = 1;
+  const int tok_blocks = (T + kTokBlock - 1) / kTokBlock;
+  while (tok_blocks * s < 148 && HC / (s * 2) >= 1024) s *= 2;
+  return s;
+}
+
+// partial must hold n_splits * T * (n_mix + 1) floats.
+STK_API int stk_mhc_dots(const void* x, const float* fn, float* partial, int T, int H, int hc, int n_mix,
+                         int n_splits, void* stream) {
+  if (T <= 0) return 0;
+  const int HC = H * hc;
+  if (HC % 2) return -1;
+  int slice = (HC + n_splits - 1) / n_splits;
+  slice = (slice + 1) & ~1;
+  dim3 grid((T + kTokBlock - 1) / kTokBlock, n_splits);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (n_mix == 24) mhc_dots_kernel<24><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, fn, partial, T, HC, slice);
+  else if (n_mix == 4) mhc_dots_kernel<4><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, fn, partial, T, HC, slice);
+  else if (n_mix == 8) mhc_dots_kernel<8><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, fn, partial, T, HC, slice);
+  else if (n_mix == 2) mhc_dots_kernel<2><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, fn, partial, T, HC, slice);
+  else return -2;
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+STK_API int stk_mhc_finalize(const void* x, const float* partial, int n_splits, int partial_ld, int sumsq_in_partial,
+                             const float* base, const float* scale, const void* norm_w, float* post, float* comb,
+                             void* y, int T, int H, int hc, float rms_eps, float hc_eps, int sinkhorn_iters,
+                             float post_mult, int mode, void* q_out, float* q_scale, int q_scale_ld, void* stream) {
+  if (T <= 0) return 0;
+  if (hc * hc > 32 || (2 + hc) * hc > kMaxMix || H % 2) return -1;
+  const size_t smem = (H + kMaxMix + 8 + 32) * sizeof(float);
+  if (smem > 200 * 1024) return -2;
+  static bool configured = false;
+  if (!configured && smem > 48 * 1024) {
+    cudaFuncSetAttribute(mhc_finalize_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    configured = true;
+  }
+  mhc_finalize_kernel<<<T, 256, smem, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, partial, n_splits, partial_ld, sumsq_in_partial, base, scale,
+      (const __nv_bfloat16*)norm_w, post, comb, (__nv_bfloat16*)y, T, H, hc, rms_eps, hc_eps, sinkhorn_iters, post_mult,
+      mode, (uint8_t*)q_out, q_scale, q_scale_ld);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+STK_API int stk_mhc_post(const void* x, const void* res, const float* post, const float* comb, void* out, int T, int H,
+                         int hc, void* stream) {
+  if (T <= 0) return 0;
+  if (H % 2 || out == res) return -1;
+  int gy = (H / 2 + 255) / 256;
+  if (gy > 8) gy = 8;
+  dim3 grid(T, gy);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (hc == 4) mhc_post_kernel<4><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, post, comb, (__nv_bfloat16*)out, H);
+  else if (hc == 2) mhc_post_kernel<2><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, post, comb, (__nv_bfloat16*)out, H);
+  else return -2;
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

@@ -1,0 +1,308 @@
+// Mixture-of-experts routing and the weight-streaming (decode-sized) expert path.
+//
+//   router        scores = sigmoid | sqrt(softplus) of fp32 gate logits; selection by score + bias
+//                 (or by a token-id hash table with bounds checks); weights from the unbiased
+//                 score, renormalised and scaled.   (topkGatingSoftplusSqrt / fused_topk_bias and
+//                 the hash-MoE lookup of overlay/nvidia_model.py:806-827)
+//   moe_align     (token, k) pairs sorted by expert, stable in pair order
+//   expert_fc1    act[pair, i] = silu(min(g, lim)) * clamp(u) with g/u = x . W1/W3 rows   (NVFP4)
+//   expert_fc2    y[pair, n]   = act . W2 rows                                              (NVFP4)
+//
+// NVFP4 = e2m1 codes packed two per byte (low nibble first), one e4m3 scale per 16 values and one
+// fp32 scale per expert matrix.  With a handful of tokens per expert the work is bounded by the
+// bytes of the weight rows, so each warp streams whole rows with 16-byte loads and dots them in
+// half2 against activations held in shared memory (fp32 accumulation per 16-value group).
+// Prefill-sized batches use the tcgen05 grouped GEMM instead.
+#include <cuda_fp4.h>
+
+#include "common.cuh"
+
+namespace stk {
+
+// ---- router ------------------------------------------------------------------------
+// One warp per token, E <= 512.
+__global__ void router_kernel(const float* __restrict__ logits, long long ldl, const float* __restrict__ bias,
+                              const int* __restrict__ tid2eid, const int64_t* __restrict__ token_ids, int vocab,
+                              int* __restrict__ ids, float* __restrict__ weights, int T, int E, int topk, int scoring,
+                              int renorm, float scaling, int* status) {
+  const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (t >= T) return;
+  constexpr int kPer = 16;
+  float sc[kPer], sel[kPer];
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    const int e = i * 32 + lane;
+    if (e < E) {
+      const float x = logits[t * ldl + e];
+      float s;
+      if (scoring == 0) s = 1.f / (1.f + __expf(-x));
+      else s = sqrtf(x > 20.f ? x : log1pf(__expf(x)));
+      sc[i] = s;
+      sel[i] = s + (bias ? bias[e] : 0.f);
+    } else {
+      sc[i] = 0.f;
+      sel[i] = -INFINITY;
+    }
+  }
+  float wsum = 0.f;
+  float my_w = 0.f;      // lane j keeps the j-th selected weight
+  int my_id = -1;
+  if (tid2eid != nullptr) {
+    const long long tok = token_ids[t];
+    const bool ok = tok >= 0 && tok < vocab;
+    if (!ok && lane == 0) set_status(status, kBadIndex, t);
+    for (int j = 0; j < topk; ++j) {
+      int e = ok ? tid2eid[tok * topk + j] : 0;
+      if (e < 0 || e >= E) {
+        if (lane == 0) set_status(status, kBadIndex, t);
+        e = 0;
+      }
+      const float s = __shfl_sync(0xffffffffu, sc[e >> 5], e & 31);
+      wsum += s;
+      if (lane == j) { my_w = s; my_id = e; }
+    }
+  } else {
+    for (int j = 0; j < topk; ++j) {
+      float best = -INFINITY;
+      int best_e = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < kPer; ++i) {
+        const int e = i * 32 + lane;
+        if (sel[i] > best) { best = sel[i]; best_e = e; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+        if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+      }
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < kPer; ++i) {
+        if (i * 32 + lane == best_e) { s = sc[i]; sel[i] = -INFINITY; }
+      }
+      s = __shfl_sync(0xffffffffu, s, best_e & 31);
+      wsum += s;
+      if (lane == j) { my_w = s; my_id = best_e; }
+    }
+  }
+  if (lane < topk) {
+    float w = my_w;
+    if (renorm) w = w / fmaxf(wsum, 1e-20f);
+    ids[t * topk + lane] = my_id;
+    weights[t * topk + lane] = w * scaling;
+  }
+}
+
+// ---- pair sort by expert ------------------------------------------------------------
+// Single CTA.  sorted[q] = pair index, pair_row[p] = q (or -1 when the expert is not local),
+// offsets[e] = first row of local expert e, offsets[E_local] = total rows.
+__global__ void __launch_bounds__(1024)
+moe_align_kernel(const int* __restrict__ ids, int n_pairs, int e_start, int e_local, int* __restrict__ sorted,
+                 int* __restrict__ pair_row, int* __restrict__ offsets, int* __restrict__ sorted_expert) {
+  extern __shared__ int sh[];          // counts[e_local + 1]
+  int* counts = sh;
+  for (int i = threadIdx.x; i <= e_local; i += blockDim.x) counts[i] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    const int e = ids[p] - e_start;
+    if (e >= 0 && e < e_local) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < e_local; ++e) {
+      const int c = counts[e];
+      counts[e] = run;
+      offsets[e] = run;
+      run += c;
+    }
+    counts[e_local] = run;
+    offsets[e_local] = run;
+  }
+  __syncthreads();
+  // stable placement: one thread per expert walks the pair list in order
+  for (int e = threadIdx.x; e < e_local; e += blockDim.x) {
+    int pos = counts[e];
+    const int end = (e + 1 <= e_local) ? counts[e + 1] : pos;
+    if (pos == end) continue;
+    for (int p = 0; p < n_pairs && pos < end; ++p) {
+      if (ids[p] - e_start == e) {
+        sorted[pos] = p;
+        sorted_expert[pos] = e;
+        pair_row[p] = pos;
+        ++pos;
+      }
+    }
+  }
+  for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+    const int e = ids[p] - e_start;
+    if (e < 0 || e >= e_local) pair_row[p] = -1;
+  }
+}
+
+// ---- NVFP4 row dot --------------------------------------------------------------------
+// xs: activations as half, permuted so that (iteration k, quarter i, lane) is one uint4:
+//   chunk c = lane + 32*k covers values [32c, 32c+32); uint4 index = (k*4 + i)*32 + lane.
+__device__ __forceinline__ float fp4_row_dot(const uint8_t* __restrict__ wrow, const uint8_t* __restrict__ srow,
+                                             const uint4* __restrict__ xs, int n_chunks, int lane) {
+  float acc = 0.f;
+  for (int k = 0; k * 32 < n_chunks; ++k) {
+    const int c = k * 32 + lane;
+    if (c < n_chunks) {
+      const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wrow) + c);
+      const uint16_t s2 = __ldg(reinterpret_cast<const uint16_t*>(srow) + c);
+      const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
+      float part[2];
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        __half2 hs = __floats2half2_rn(0.f, 0.f);
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const uint4 xv = xs[(k * 4 + g * 2 + q) * 32 + lane];
+          const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+          const uint32_t w = words[g * 2 + q];
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            const __half2_raw hr = __nv_cvt_fp4x2_to_halfraw2(static_cast<__nv_fp4x2_storage_t>((w >> (8 * b)) & 0xff), __NV_E2M1);
+            hs = __hfma2(*reinterpret_cast<const __half2*>(&hr), *reinterpret_cast<const __half2*>(&xw[b]), hs);
+          }
+        }
+        part[g] = __low2float(hs) + __high2float(hs);
+      }
+      acc = fmaf(part[0], fp8_to_f(s2 & 0xff), acc);
+      acc = fmaf(part[1], fp8_to_f(s2 >> 8), acc);
+    }
+  }
+  return warp_sum(acc);
+}
+
+__device__ __forceinline__ float src_to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float src_to_f(__half v) { return __half2float(v); }
+
+// Fill the permuted half activation buffer from a bf16 or half row.  The buffer holds
+// ceil(K / 1024) * 1024 halfs (the permutation leaves holes when K < 1024).
+template <typename SrcT>
+__device__ __forceinline__ void fill_xs(__half* xs_h, const SrcT* x, int K) {
+  for (int e = threadIdx.x; e < K; e += blockDim.x) {
+    const int c = e >> 5, within = e & 31;
+    const int k = c >> 5, lane = c & 31;
+    const int i = within >> 3, b = within & 7;
+    xs_h[((k * 4 + i) * 32 + lane) * 8 + b] = __float2half(src_to_f(x[e]));
+  }
+}
+
+struct ExpertW {
+  const uint8_t* w;       // [E, rows, K/2]
+  const uint8_t* s;       // [E, rows, K/16] e4m3
+  const float* gscale;    // [E]
+};
+
+// grid (ceil(I / 16), n_rows); CTA = 8 warps, 2 outputs per warp.
+__global__ void __launch_bounds__(256)
+expert_fc1_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, ExpertW w13, const int* __restrict__ sorted,
+                  const int* __restrict__ sorted_expert, const int* __restrict__ offsets, int e_local, int topk,
+                  __half* __restrict__ act, int H, int I, float limit) {
+  extern __shared__ uint4 xs[];
+  const int n_rows = offsets[e_local];
+  const int row = blockIdx.y;
+  if (row >= n_rows) return;
+  const int pair = sorted[row];
+  const int e = sorted_expert[row];
+  const int t = pair / topk;
+  fill_xs(reinterpret_cast<__half*>(xs), x + t * ldx, H);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_chunks = H / 32;
+  const float gs = w13.gscale[e];
+  const long long wstride = static_cast<long long>(H) / 2, sstride = static_cast<long long>(H) / 16;
+  const uint8_t* wbase = w13.w + static_cast<long long>(e) * 2 * I * wstride;
+  const uint8_t* sbase = w13.s + static_cast<long long>(e) * 2 * I * sstride;
+  for (int j = 0; j < 2; ++j) {
+    const int i = blockIdx.x * 16 + warp * 2 + j;
+    if (i >= I) break;
+    float g = fp4_row_dot(wbase + i * wstride, sbase + i * sstride, xs, n_chunks, lane) * gs;
+    float u = fp4_row_dot(wbase + (I + i) * wstride, sbase + (I + i) * sstride, xs, n_chunks, lane) * gs;
+    if (lane == 0) {
+      if (limit > 0.f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+      }
+      act[static_cast<long long>(row) * I + i] = __float2half(g / (1.f + __expf(-g)) * u);
+    }
+  }
+}
+
+// grid (ceil(H / 32), n_rows); 4 outputs per warp.
+__global__ void __launch_bounds__(256)
+expert_fc2_kernel(const __half* __restrict__ act, ExpertW w2, const int* __restrict__ sorted_expert,
+                  const int* __restrict__ offsets, int e_local, __nv_bfloat16* __restrict__ y, int H, int I) {
+  extern __shared__ uint4 xs[];
+  const int n_rows = offsets[e_local];
+  const int row = blockIdx.y;
+  if (row >= n_rows) return;
+  const int e = sorted_expert[row];
+  fill_xs(reinterpret_cast<__half*>(xs), act + static_cast<long long>(row) * I, I);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_chunks = I / 32;
+  const float gs = w2.gscale[e];
+  const long long wstride = static_cast<long long>(I) / 2, sstride = static_cast<long long>(I) / 16;
+  const uint8_t* wbase = w2.w + static_cast<long long>(e) * H * wstride;
+  const uint8_t* sbase = w2.s + static_cast<long long>(e) * H * sstride;
+  for (int j = 0; j < 4; ++j) {
+    const int n = blockIdx.x * 32 + warp * 4 + j;
+    if (n >= H) break;
+    const float v = fp4_row_dot(wbase + n * wstride, sbase + n * sstride, xs, n_chunks, lane) * gs;
+    if (lane == 0) y[static_cast<long long>(row) * H + n] = __float2bfloat16(v);
+  }
+}
+
+}  // namespace stk
+
+using namespace stk;
+
+STK_API int stk_router(const float* logits, long long ldl, const float* bias, const int* tid2eid,
+                       const int64_t* token_ids, int vocab, int* ids, float* weights, int T, int E, int topk,
+                       int scoring, int renorm, float scaling, int* status, void* stream) {
+  if (T <= 0) return 0;
+  if (E > 512 || topk > 32) return -1;
+  router_kernel<<<(T + 7) / 8, 256, 0, (cudaStream_t)stream>>>(logits, ldl, bias, tid2eid, token_ids, vocab, ids,
+                                                               weights, T, E, topk, scoring, renorm, scaling, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+STK_API int stk_moe_align(const int* ids, int n_pairs, int e_start, int e_local, int* sorted, int* pair_row,
+                          int* offsets, int* sorted_expert, void* stream) {
+  if (n_pairs <= 0) return 0;
+  moe_align_kernel<<<1, 1024, (e_local + 1) * sizeof(int), (cudaStream_t)stream>>>(ids, n_pairs, e_start, e_local,
+                                                                                   sorted, pair_row, offsets,
+                                                                                   sorted_expert);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// max_rows bounds the grid (rows beyond offsets[e_local] exit at once).
+STK_API int stk_moe_expert_fc1(const void* x, long long ldx, const void* w13, const void* s13, const float* g13,
+                               const int* sorted, const int* sorted_expert, const int* offsets, int e_local, int topk,
+                               void* act, int max_rows, int H, int I, float limit, void* stream) {
+  if (max_rows <= 0) return 0;
+  if (H % 32 || H > 16384) return -1;
+  ExpertW w{(const uint8_t*)w13, (const uint8_t*)s13, g13};
+  dim3 grid((I + 15) / 16, max_rows);
+  expert_fc1_kernel<<<grid, 256, ((H + 1023) / 1024) * 2048, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, w, sorted, sorted_expert,
+                                                                offsets, e_local, topk, (__half*)act, H, I, limit);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+STK_API int stk_moe_expert_fc2(const void* act, const void* w2, const void* s2, const float* g2,
+                               const int* sorted_expert, const int* offsets, int e_local, void* y, int max_rows, int H,
+                               int I, void* stream) {
+  if (max_rows <= 0) return 0;
+  if (I % 32 || I > 16384) return -1;
+  ExpertW w{(const uint8_t*)w2, (const uint8_t*)s2, g2};
+  dim3 grid((H + 31) / 32, max_rows);
+  expert_fc2_kernel<<<grid, 256, ((I + 1023) / 1024) * 2048, (cudaStream_t)stream>>>((const __half*)act, w, sorted_expert, offsets, e_local,
+                                                                (__nv_bfloat16*)y, H, I);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

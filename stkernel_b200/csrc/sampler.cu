@@ -1,0 +1,256 @@
+// Sampling and speculative-decoding kernels.
+//
+//   gumbel_argmax     token = argmax(logits/T + g(seed, pos, v)); g from a counter-based hash so the
+//                     noise is a pure function of (seed, position, vocab id): the drafter, the
+//                     verifier and every tensor-parallel rank draw identical noise.
+//   coupled_accept    accept draft i iff all earlier drafts were accepted and it equals the
+//                     verifier's token at that offset; the emitted token is always the verifier's
+//                     (overlay/dspark_speculator_v2.py:32-38,282-294).
+//   markov_topk_bias  DSpark first-order Markov head on the base-logit top-k:
+//                     out[idx] = base[idx] + W2[idx] . embed, -inf elsewhere
+//                     (overlay/dspark_v2.py:184-236).
+#include "common.cuh"
+
+namespace stk {
+
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+  x = (x ^ (x >> 16)) * 0x7FEB352Du;
+  x = (x ^ (x >> 15)) * 0x846CA68Bu;
+  x = x ^ (x >> 16);
+  return x;
+}
+
+__device__ __forceinline__ uint32_t gumbel_key(long long seed, long long pos) {
+  uint32_t h = mix32(static_cast<uint32_t>(seed & 0xffffffffLL) ^ 0x9E3779B9u);
+  h = mix32(h ^ mix32(static_cast<uint32_t>((seed >> 32) & 0xffffffffLL) + 0x85EBCA6Bu));
+  h = mix32(h ^ mix32(static_cast<uint32_t>(pos & 0xffffffffLL) + 0xC2B2AE35u));
+  return h;
+}
+
+__device__ __forceinline__ float gumbel_from_key(uint32_t key, uint32_t v) {
+  const uint32_t h = mix32(key ^ mix32(v + 0x27D4EB2Fu));
+  const float u = (static_cast<float>(h >> 8) + 0.5f) * (1.0f / 16777216.0f);
+  return -logf(-logf(u));
+}
+
+template <typename T> __device__ __forceinline__ float ld_logit(const T* p, long long i);
+template <> __device__ __forceinline__ float ld_logit<float>(const float* p, long long i) { return p[i]; }
+template <> __device__ __forceinline__ float ld_logit<__nv_bfloat16>(const __nv_bfloat16* p, long long i) {
+  return __bfloat162float(p[i]);
+}
+
+// grid (rows, chunks).  part_val/part_idx: [rows, chunks].
+template <typename T>
+__global__ void __launch_bounds__(256)
+gumbel_argmax_partial_kernel(const T* __restrict__ logits, long long ld, const float* __restrict__ temperature,
+                             const int64_t* __restrict__ seed, const int64_t* __restrict__ pos,
+                             const int* __restrict__ row_group, int pos_stride, float* __restrict__ part_val,
+                             int* __restrict__ part_idx, float* __restrict__ processed, long long ldp, int V) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  const int row = blockIdx.x;
+  const int g = row_group ? row_group[row] : row;          // request that owns seed/temperature
+  const float temp = temperature[g];
+  const bool greedy = temp <= 0.f;
+  const float inv_t = greedy ? 1.f : 1.f / temp;
+  // position of this row: pos[g] + (row offset inside the group) when pos_stride > 0
+  const long long p = pos[g] + (pos_stride > 0 ? (row % pos_stride) : 0);
+  const uint32_t key = gumbel_key(seed[g], p);
+  const int chunk = (V + gridDim.y - 1) / gridDim.y;
+  const int v0 = blockIdx.y * chunk, v1 = min(V, v0 + chunk);
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+    const float l = ld_logit<T>(logits, row * ld + v) * inv_t;
+    if (processed) processed[row * ldp + v] = l;
+    const float x = greedy ? l : l + gumbel_from_key(key, static_cast<uint32_t>(v));
+    if (x > best || (x == best && v < best_i)) { best = x; best_i = v; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (ob > best || (ob == best && oi < best_i)) { best = ob; best_i = oi; }
+  }
+  if (lane == 0) { sv[warp] = best; si[warp] = best_i; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (sv[w] > best || (sv[w] == best && si[w] < best_i)) { best = sv[w]; best_i = si[w]; }
+    part_val[row * gridDim.y + blockIdx.y] = best;
+    part_idx[row * gridDim.y + blockIdx.y] = best_i;
+  }
+}
+
+__global__ void gumbel_argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
+                                           int chunks, int64_t* __restrict__ out, int rows) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int c = 0; c < chunks; ++c) {
+    const float v = part_val[row * chunks + c];
+    const int i = part_idx[row * chunks + c];
+    if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+  }
+  out[row] = best_i == 0x7fffffff ? 0 : best_i;
+}
+
+// verifier [B, N+1], draft [B, N] -> n_acc [B], emitted [B, N+1] (-1 past the first mismatch)
+__global__ void coupled_accept_kernel(const int64_t* __restrict__ verifier, const int64_t* __restrict__ draft,
+                                      int64_t* __restrict__ n_acc, int64_t* __restrict__ emitted, int B, int N) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  bool ok = true;
+  int acc = 0;
+  for (int i = 0; i <= N; ++i) {
+    const int64_t tok = verifier[b * (N + 1) + i];
+    emitted[b * (N + 1) + i] = ok ? tok : -1;
+    if (i < N) {
+      ok = ok && (tok == draft[b * N + i]);
+      acc += ok ? 1 : 0;
+    }
+  }
+  n_acc[b] = acc;
+}
+
+// ---- Markov head -----------------------------------------------------------------------
+__device__ __forceinline__ uint32_t fkey(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// One CTA (1024 threads) per row: threshold of the k largest logits by radix select, then
+// out[v] = (selected) ? base[v] + W2[v] . embed : -inf.   Ties at the threshold: lowest ids.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+markov_topk_bias_kernel(const T* __restrict__ base, long long ld, const __nv_bfloat16* __restrict__ w2,
+                        const __nv_bfloat16* __restrict__ embed, long long lde, float* __restrict__ out,
+                        long long ldo, int V, int R, int k) {
+  __shared__ int hist[256];
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_remaining;
+  __shared__ int warp_eq[32];
+  __shared__ int base_eq;
+  extern __shared__ float emb[];       // R floats
+  const int row = blockIdx.x;
+  const T* brow = base + row * ld;
+  for (int i = threadIdx.x; i < R; i += blockDim.x) emb[i] = __bfloat162float(embed[row * lde + i]);
+  if (threadIdx.x == 0) { s_prefix = 0; s_remaining = k; base_eq = 0; }
+  const bool dense = k <= 0 || k >= V;
+  uint32_t thr = 0;
+  int need_eq = 0x7fffffff;
+  if (!dense) {
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+      __syncthreads();
+      const uint32_t prefix = s_prefix;
+      const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+      for (int v = threadIdx.x; v < V; v += blockDim.x) {
+        const uint32_t key = fkey(ld_logit<T>(brow, v));
+        if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xff], 1);
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        int rem = s_remaining;
+        int b = 255;
+        for (; b > 0; --b) {
+          if (hist[b] >= rem) break;
+          rem -= hist[b];
+        }
+        s_prefix = prefix | (static_cast<uint32_t>(b) << shift);
+        s_remaining = rem;
+      }
+      __syncthreads();
+    }
+    thr = s_prefix;
+    need_eq = s_remaining;
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int v0 = 0; v0 < V; v0 += blockDim.x) {
+    const int v = v0 + threadIdx.x;
+    const bool in = v < V;
+    float l = 0.f;
+    uint32_t key = 0;
+    if (in) { l = ld_logit<T>(brow, v); key = fkey(l); }
+    const bool gt = dense ? in : (in && key > thr);
+    const bool eq = !dense && in && key == thr;
+    const uint32_t be = __ballot_sync(0xffffffffu, eq);
+    if (lane == 0) warp_eq[warp] = __popc(be);
+    __syncthreads();
+    int oe = base_eq;
+    for (int w = 0; w < warp; ++w) oe += warp_eq[w];
+    oe += __popc(be & ((1u << lane) - 1));
+    const bool take = gt || (eq && oe < need_eq);
+    if (in) {
+      float o = -INFINITY;
+      if (take) {
+        const __nv_bfloat162* wr = reinterpret_cast<const __nv_bfloat162*>(w2 + static_cast<long long>(v) * R);
+        float d0 = 0.f, d1 = 0.f;
+        for (int i = 0; i < R / 2; ++i) {
+          const __nv_bfloat162 wv = wr[i];
+          d0 = fmaf(__low2float(wv), emb[2 * i], d0);
+          d1 = fmaf(__high2float(wv), emb[2 * i + 1], d1);
+        }
+        o = l + d0 + d1;
+      }
+      out[row * ldo + v] = o;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int te = 0;
+      for (int w = 0; w < 32; ++w) te += warp_eq[w];
+      base_eq += te;
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace stk
+
+using namespace stk;
+
+// part_val/part_idx: scratch of rows*chunks entries each.  row_group may be null (row == request).
+STK_API int stk_gumbel_argmax(const void* logits, long long ld, int logits_bf16, const float* temperature,
+                              const int64_t* seed, const int64_t* pos, const int* row_group, int pos_stride,
+                              float* part_val, int* part_idx, int chunks, int64_t* out, float* processed,
+                              long long ldp, int rows, int V, void* stream) {
+  if (rows <= 0) return 0;
+  dim3 grid(rows, chunks);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (logits_bf16)
+    gumbel_argmax_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)logits, ld, temperature,
+                                                                      seed, pos, row_group, pos_stride, part_val,
+                                                                      part_idx, processed, ldp, V);
+  else
+    gumbel_argmax_partial_kernel<float><<<grid, 256, 0, st>>>((const float*)logits, ld, temperature, seed, pos,
+                                                              row_group, pos_stride, part_val, part_idx, processed,
+                                                              ldp, V);
+  gumbel_argmax_final_kernel<<<(rows + 127) / 128, 128, 0, st>>>(part_val, part_idx, chunks, out, rows);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+STK_API int stk_coupled_accept(const int64_t* verifier, const int64_t* draft, int64_t* n_acc, int64_t* emitted, int B,
+                               int N, void* stream) {
+  if (B <= 0) return 0;
+  coupled_accept_kernel<<<(B + 127) / 128, 128, 0, (cudaStream_t)stream>>>(verifier, draft, n_acc, emitted, B, N);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+STK_API int stk_markov_topk_bias(const void* base, long long ld, int base_bf16, const void* w2, const void* embed,
+                                 long long lde, float* out, long long ldo, int rows, int V, int R, int k,
+                                 void* stream) {
+  if (rows <= 0) return 0;
+  if (R % 2) return -1;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (base_bf16)
+    markov_topk_bias_kernel<__nv_bfloat16><<<rows, 1024, R * sizeof(float), st>>>(
+        (const __nv_bfloat16*)base, ld, (const __nv_bfloat16*)w2, (const __nv_bfloat16*)embed, lde, out, ldo, V, R, k);
+  else
+    markov_topk_bias_kernel<float><<<rows, 1024, R * sizeof(float), st>>>(
+        (const float*)base, ld, (const __nv_bfloat16*)w2, (const __nv_bfloat16*)embed, lde, out, ldo, V, R, k);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

@@ -1,0 +1,227 @@
+"""Indexer scoring / top-k, per-step index metadata and sparse MLA attention."""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from . import reference as R
+from .cache import PAGE, PagedCache
+from .scratch import scratch
+
+BF16 = torch.bfloat16
+F32 = torch.float32
+I32 = torch.int32
+
+
+# ---- metadata -------------------------------------------------------------------
+def token_maps(query_start: torch.Tensor, req_rows: torch.Tensor, start_pos: torch.Tensor, n_req: int, t_padded: int):
+    """-> (tok_req i32 [T], positions i64 [T], first_pos i32 [T], last_pos i32 [T]); padding tokens get
+    request -1 / position -1."""
+    dev = query_start.device
+    if dev.type != "cuda":
+        tok_req = torch.full((t_padded,), -1, dtype=I32)
+        positions = torch.full((t_padded,), -1, dtype=torch.int64)
+        first = torch.zeros(t_padded, dtype=I32)
+        last = torch.full((t_padded,), -1, dtype=I32)
+        for i in range(n_req):
+            a, b = int(query_start[i]), int(query_start[i + 1])
+            tok_req[a:b] = int(req_rows[i])
+            positions[a:b] = int(start_pos[i]) + torch.arange(b - a)
+            first[a:b] = int(start_pos[i])
+            last[a:b] = int(start_pos[i]) + (b - a) - 1
+        return tok_req, positions, first, last
+    tok_req = scratch("meta.tok_req", (t_padded,), I32, dev)
+    positions = scratch("meta.positions", (t_padded,), torch.int64, dev)
+    first = scratch("meta.first", (t_padded,), I32, dev)
+    last = scratch("meta.last", (t_padded,), I32, dev)
+    _lib.call("stk_token_maps", query_start, req_rows, start_pos, n_req, tok_req, positions, first, last, t_padded,
+              _lib.stream())
+    return tok_req, positions, first, last
+
+
+def _slots_from_bt(block_table, req, p):
+    page = block_table[req, p // PAGE]
+    return torch.where(page >= 0, page * PAGE + p % PAGE, torch.full_like(page, -1))
+
+
+def swa_indices(positions: torch.Tensor, tok_req: torch.Tensor, block_table: torch.Tensor, window: int,
+                tag: str = "swa") -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per token the SWA-cache slots of positions [pos-W+1, pos] (-1 padded) and their count."""
+    t = positions.shape[0]
+    dev = positions.device
+    if dev.type != "cuda":
+        slots = torch.full((t, window), -1, dtype=I32)
+        lens = torch.zeros(t, dtype=I32)
+        for i in range(t):
+            pos, req = int(positions[i]), int(tok_req[i])
+            if pos < 0 or req < 0:
+                continue
+            lo = max(0, pos - window + 1)
+            p = torch.arange(lo, pos + 1)
+            slots[i, :p.numel()] = _slots_from_bt(block_table, req, p).to(I32)
+            lens[i] = p.numel()
+        return slots, lens
+    slots = scratch(f"{tag}.slots", (t, window), I32, dev)
+    lens = scratch(f"{tag}.lens", (t,), I32, dev)
+    _lib.call("stk_swa_indices", positions, tok_req, block_table, block_table.stride(0), slots, window, lens, t, window,
+              _lib.stream())
+    return slots, lens
+
+
+def swa_indices_noncausal(tok_req: torch.Tensor, prefix_len: torch.Tensor, seq_len: torch.Tensor,
+                          block_table: torch.Tensor, window: int, width: int, tag: str = "swa_nc"):
+    """DSpark draft block: every query of a request sees positions [prefix-W, seq_len)."""
+    t = tok_req.shape[0]
+    dev = tok_req.device
+    if dev.type != "cuda":
+        slots = torch.full((t, width), -1, dtype=I32)
+        lens = torch.zeros(t, dtype=I32)
+        for i in range(t):
+            req = int(tok_req[i])
+            if req < 0:
+                continue
+            lo = max(0, int(prefix_len[req]) - window)
+            n = int(seq_len[req]) - lo
+            if n > width:
+                lo += n - width
+                n = width
+            p = torch.arange(lo, lo + n)
+            slots[i, :n] = _slots_from_bt(block_table, req, p).to(I32)
+            lens[i] = n
+        return slots, lens
+    slots = scratch(f"{tag}.slots", (t, width), I32, dev)
+    lens = scratch(f"{tag}.lens", (t,), I32, dev)
+    _lib.call("stk_swa_indices_noncausal", tok_req, prefix_len, seq_len, block_table, block_table.stride(0), slots,
+              width, lens, t, window, _lib.stream())
+    return slots, lens
+
+
+def compressed_valid(positions: torch.Tensor, ratio: int, tag: str = "nvalid") -> torch.Tensor:
+    t = positions.shape[0]
+    if not positions.is_cuda:
+        return torch.where(positions >= 0, (positions + 1) // ratio, torch.zeros_like(positions)).to(I32)
+    out = scratch(tag, (t,), I32, positions.device)
+    _lib.call("stk_compressed_valid", positions, out, t, ratio, _lib.stream())
+    return out
+
+
+def c128_indices(positions, tok_req, block_table, ratio: int, cap: int, tag: str = "c128"):
+    t = positions.shape[0]
+    dev = positions.device
+    if dev.type != "cuda":
+        slots = torch.full((t, cap), -1, dtype=I32)
+        lens = torch.zeros(t, dtype=I32)
+        for i in range(t):
+            pos, req = int(positions[i]), int(tok_req[i])
+            if pos < 0 or req < 0:
+                continue
+            nv = (pos + 1) // ratio
+            lo = max(0, nv - cap)
+            j = torch.arange(lo, nv)
+            slots[i, :j.numel()] = _slots_from_bt(block_table, req, j).to(I32)
+            lens[i] = j.numel()
+        return slots, lens
+    slots = scratch(f"{tag}.slots", (t, cap), I32, dev)
+    lens = scratch(f"{tag}.lens", (t,), I32, dev)
+    _lib.call("stk_c128_indices", positions, tok_req, block_table, block_table.stride(0), slots, cap, lens, t, ratio,
+              cap, _lib.stream())
+    return slots, lens
+
+
+# ---- indexer -----------------------------------------------------------------------
+def indexer_scores(q: torch.Tensor, w: torch.Tensor, kcache: PagedCache, block_table: torch.Tensor,
+                   tok_req: torch.Tensor, n_valid: torch.Tensor, max_rows: int, tag: str = "idx") -> torch.Tensor:
+    """q [T, ih, d] (fp8 or bf16), w [T, ih] folded weights -> scores fp32 [T, ld] (entries >= n_valid[t] undefined)."""
+    t, ih, d = q.shape
+    ld = max(4, (max_rows + 3) // 4 * 4)
+    if not q.is_cuda:
+        scores = torch.full((t, ld), float("-inf"), dtype=F32)
+        for i in range(t):
+            nv, req = int(n_valid[i]), int(tok_req[i])
+            if nv <= 0 or req < 0:
+                continue
+            s = torch.arange(nv)
+            rows, sc = kcache.read_rows_cpu(_slots_from_bt(block_table, req, s))
+            scores[i, :nv] = R.indexer_scores(q[i:i + 1].to(F32), w[i:i + 1], rows, sc)[0]
+        return scores
+    scores = scratch(f"{tag}.scores", (t, ld), F32, q.device)
+    _lib.call("stk_indexer_scores", q, w, kcache.buf, kcache.page_stride, 1 if kcache.fp8 else 0, block_table,
+              block_table.stride(0), tok_req, n_valid, scores, ld, t, max_rows, ih, d,
+              1 if q.dtype != BF16 else 0, _lib.stream())
+    return scores
+
+
+def topk_rows(scores: torch.Tensor, n_valid: torch.Tensor, k: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Indices of the k largest valid scores per row, -1 padded.  The order inside a row is unspecified."""
+    t = scores.shape[0]
+    if not scores.is_cuda:
+        r = R.topk_rows(scores, n_valid, k)
+        if out is not None:
+            out[:t, :k] = r
+            return out
+        return r
+    if out is None:
+        out = torch.empty(t, k, dtype=I32, device=scores.device)
+    _lib.call("stk_topk_rows", scores, scores.stride(0), n_valid, out, out.stride(0), t, k, _lib.stream())
+    return out
+
+
+def topk_to_slots(topk: torch.Tensor, block_table: torch.Tensor, tok_req: torch.Tensor, max_rows: int,
+                  tag: str = "topk") -> Tuple[torch.Tensor, torch.Tensor]:
+    """Local compressed indices -> physical slots of the compressed cache (+ count of valid entries)."""
+    t, k = topk.shape[0], topk.shape[1]
+    if not topk.is_cuda:
+        slots = torch.full((t, k), -1, dtype=I32)
+        lens = torch.zeros(t, dtype=I32)
+        for i in range(t):
+            req = int(tok_req[i])
+            if req < 0:
+                continue
+            idx = topk[i].long()
+            ok = idx >= 0
+            s = _slots_from_bt(block_table, req, idx.clamp(min=0))
+            slots[i] = torch.where(ok, s, torch.full_like(s, -1)).to(I32)
+            lens[i] = int((slots[i] >= 0).sum())
+        return slots, lens
+    slots = scratch(f"{tag}.slots", (t, k), I32, topk.device)
+    lens = scratch(f"{tag}.lens", (t,), I32, topk.device)
+    _lib.call("stk_topk_to_slots", topk, k, topk.stride(0), block_table, block_table.stride(0), tok_req, slots, k, lens,
+              t, max_rows, _lib.status_buffer(), _lib.stream())
+    return slots, lens
+
+
+# ---- attention ------------------------------------------------------------------------
+def sparse_mla(q: torch.Tensor, swa_cache: PagedCache, swa_slots: torch.Tensor, swa_lens: torch.Tensor,
+               comp_cache: Optional[PagedCache], topk_slots: Optional[torch.Tensor], topk_lens: Optional[torch.Tensor],
+               sink: torch.Tensor, scale: float) -> torch.Tensor:
+    """q [T, nh, D] bf16 -> out [T, nh, D] bf16 attending to the SWA rows then the top-k rows.
+
+    Only the first swa_lens[t] / topk_lens[t] entries of each list are read; -1 entries inside that
+    range are masked."""
+    t, nh, d = q.shape
+    if not q.is_cuda:
+        out = torch.zeros(t, nh, d, dtype=F32)
+        for i in range(t):
+            sl = swa_slots[i, :int(swa_lens[i])].long()
+            rows = [swa_cache.read_rows_cpu(sl)[0]]
+            valid = [sl >= 0]
+            if topk_slots is not None:
+                tl = topk_slots[i, :int(topk_lens[i])].long()
+                rows.append(comp_cache.read_rows_cpu(tl)[0])
+                valid.append(tl >= 0)
+            rr = torch.cat(rows)[None]
+            vv = torch.cat(valid)[None]
+            out[i] = R.sparse_mla(q[i:i + 1], rr, vv, sink, scale)[0]
+        return out.to(BF16)
+    max_rows = swa_slots.shape[1] + (topk_slots.shape[1] if topk_slots is not None else 0)
+    n_splits = _lib.query("stk_sparse_mla_pick_splits", t, max_rows)
+    ws = scratch("mla.partial", (t * n_splits * nh * (d + 2),), F32, q.device)
+    out = torch.empty(t, nh, d, dtype=BF16, device=q.device)
+    cc = comp_cache if comp_cache is not None else swa_cache
+    _lib.call("stk_sparse_mla", q, q.stride(0), swa_cache.buf, swa_cache.page_stride, swa_cache.data_bytes, cc.buf,
+              cc.page_stride, cc.data_bytes, 1 if swa_cache.fp8 else 0, swa_slots, swa_slots.stride(0), swa_lens,
+              topk_slots, topk_slots.stride(0) if topk_slots is not None else 0, topk_lens, sink, out, out.stride(0), ws,
+              n_splits, t, nh, d, swa_cache.rope_dim, max_rows, float(scale), _lib.stream())
+    return out

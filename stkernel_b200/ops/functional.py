@@ -1,0 +1,274 @@
+"""The op layer: every function runs the sm_100a kernel when its tensors live on
+a GPU and the PyTorch reference statement (:mod:`.reference`) on CPU.
+
+On a GPU there is no fallback: a missing library raises (see :mod:`._lib`).
+Scratch buffers come from :mod:`.scratch`, so addresses are stable across steps
+and the whole decode step can be captured in a CUDA graph.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from ..config import FP8_BLOCK
+from . import _lib
+from . import reference as R
+from .scratch import scratch
+
+BF16 = torch.bfloat16
+F32 = torch.float32
+FP8 = torch.float8_e4m3fn
+
+
+# ----------------------------------------------------------------------------
+# dense linear
+# ----------------------------------------------------------------------------
+@dataclass
+class LinearWeight:
+    """[N, K] weight in its storage format: bf16, or e4m3 with 128x128 fp32 block scales."""
+    w: torch.Tensor
+    scale: Optional[torch.Tensor] = None
+
+    @property
+    def is_fp8(self) -> bool:
+        return self.scale is not None
+
+    @property
+    def out_features(self) -> int:
+        return self.w.shape[0]
+
+    @property
+    def in_features(self) -> int:
+        return self.w.shape[1]
+
+    @staticmethod
+    def from_master(w: torch.Tensor, dense_dtype: str, device) -> "LinearWeight":
+        if dense_dtype == "fp8":
+            q, s = R.quant_fp8_block128_weight(w.to(device=device, dtype=F32))
+            return LinearWeight(q.contiguous(), s.contiguous())
+        return LinearWeight(w.to(device=device, dtype=BF16).contiguous())
+
+    def dequant(self) -> torch.Tensor:
+        if self.is_fp8:
+            return R.dequant_fp8_block128_weight(self.w, self.scale)
+        return self.w.to(F32)
+
+
+@dataclass
+class QuantAct:
+    """fp8 activation [T, K] with scales stored token-contiguous: [ceil(K/128), ld], ld % 4 == 0."""
+    q: torch.Tensor
+    scale: torch.Tensor
+
+
+def _scale_ld(t: int) -> int:
+    return max(4, (t + 3) // 4 * 4)
+
+
+def quant_act(x: torch.Tensor, tag: str = "act") -> QuantAct:
+    """Per-token 1x128 group quantisation of a bf16 activation."""
+    t, k = x.shape
+    if not x.is_cuda:
+        q, s = R.quant_fp8_group128_act(x)
+        return QuantAct(q, s.t().contiguous())
+    kb = (k + FP8_BLOCK - 1) // FP8_BLOCK
+    ld = _scale_ld(t)
+    q = scratch(f"{tag}.q", (t, k), torch.uint8, x.device)
+    s = scratch(f"{tag}.s", (kb, ld), F32, x.device)
+    _lib.call("stk_quant_fp8_group128", x, x.stride(0), q, k, s, ld, t, k, _lib.stream())
+    return QuantAct(q.view(FP8), s)
+
+
+def linear(x, lw: LinearWeight, out: Optional[torch.Tensor] = None, out_dtype=BF16, tag: str = "lin",
+           splits: Optional[int] = None) -> torch.Tensor:
+    """out[T, N] = x[T, K] @ W[N, K]^T.  x: bf16 tensor or a QuantAct (required format for fp8 weights
+    is produced on the fly when a bf16 tensor is given)."""
+    if isinstance(x, QuantAct):
+        xa, dev, t = x, x.q.device, x.q.shape[0]
+    else:
+        xa, dev, t = None, x.device, x.shape[0]
+    n, k = lw.w.shape
+    if dev.type != "cuda":
+        if lw.is_fp8:
+            if xa is None:
+                xa = quant_act(x)
+            xf = R.dequant_fp8_group128_act(xa.q, xa.scale.t()[:t])
+        else:
+            xf = (x if xa is None else R.dequant_fp8_group128_act(xa.q, xa.scale.t()[:t])).to(BF16).to(F32)
+        y = xf @ lw.dequant().t()
+        y = y.to(out_dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
+    if lw.is_fp8 and xa is None:
+        xa = quant_act(x, tag + ".xq")
+    if out is None:
+        out = torch.empty(t, n, dtype=out_dtype, device=dev)
+    is_fp8 = 1 if lw.is_fp8 else 0
+    sms = _lib.sm_count()
+    if splits is None:
+        splits = _lib.query("stk_gemm_pick_splits", t, n, k, is_fp8, sms)
+    ws = cnt = None
+    if splits > 1:
+        ws = scratch("gemm.splitk", (splits * t * n,), F32, dev)
+        cnt = scratch("gemm.counters", (4096,), torch.int32, dev, zero=True)
+    xin = xa.q if is_fp8 else x
+    if not is_fp8 and xin.dtype != BF16:
+        xin = xin.to(BF16)
+    _lib.call("stk_gemm", lw.w, lw.w.stride(0), xin, xin.stride(0), out, out.stride(0), t, n, k, is_fp8,
+              1 if out.dtype == F32 else 0, lw.scale, lw.scale.stride(0) if is_fp8 else 0,
+              xa.scale if is_fp8 else None, xa.scale.stride(0) if is_fp8 else 0, splits, ws, cnt,
+              _lib.status_buffer(), sms, _lib.stream())
+    return out
+
+
+# ----------------------------------------------------------------------------
+# norms / elementwise
+# ----------------------------------------------------------------------------
+def rms_norm(x: torch.Tensor, w: Optional[torch.Tensor], eps: float, quant: bool = False, tag: str = "norm"):
+    """bf16 RMSNorm; with quant=True also returns the fp8 QuantAct of the normed row."""
+    t, h = x.shape
+    if not x.is_cuda:
+        y = R.rms_norm(x, w, eps).to(BF16)
+        return (y, quant_act(y)) if quant else y
+    out = torch.empty(t, h, dtype=BF16, device=x.device)
+    q = s = None
+    ld = _scale_ld(t)
+    if quant:
+        q = scratch(f"{tag}.q", (t, h), torch.uint8, x.device)
+        s = scratch(f"{tag}.s", ((h + 127) // 128, ld), F32, x.device)
+    _lib.call("stk_rmsnorm", x, x.stride(0), w, out, h, h, q, h, s, ld,
+              None, 0, None, None, 0, 0, t, eps, _lib.stream())
+    return (out, QuantAct(q.view(FP8), s)) if quant else out
+
+
+def rms_norm_pair(x0, w0, x1, w1, eps: float, quant0: bool = False, tag: str = "norm2"):
+    """Two independent RMSNorms in one launch (q_lora row and kv row)."""
+    t = x0.shape[0]
+    if not x0.is_cuda:
+        y0, y1 = R.rms_norm(x0, w0, eps).to(BF16), R.rms_norm(x1, w1, eps).to(BF16)
+        return (y0, y1, quant_act(y0)) if quant0 else (y0, y1)
+    h0, h1 = x0.shape[1], x1.shape[1]
+    o0 = torch.empty(t, h0, dtype=BF16, device=x0.device)
+    o1 = torch.empty(t, h1, dtype=BF16, device=x0.device)
+    q = s = None
+    ld = _scale_ld(t)
+    if quant0:
+        q = scratch(f"{tag}.q", (t, h0), torch.uint8, x0.device)
+        s = scratch(f"{tag}.s", ((h0 + 127) // 128, ld), F32, x0.device)
+    _lib.call("stk_rmsnorm", x0, x0.stride(0), w0, o0, h0, h0, q, h0, s, ld,
+              x1, x1.stride(0), w1, o1, h1, h1, t, eps, _lib.stream())
+    return (o0, o1, QuantAct(q.view(FP8), s)) if quant0 else (o0, o1)
+
+
+def swiglu_clamp(gu: torch.Tensor, limit: float, quant: bool = False, tag: str = "swiglu"):
+    t, two_i = gu.shape
+    i = two_i // 2
+    if not gu.is_cuda:
+        a = R.swiglu_clamp(gu[:, :i], gu[:, i:], limit).to(BF16)
+        return (a, quant_act(a)) if quant else a
+    act = torch.empty(t, i, dtype=BF16, device=gu.device)
+    q = s = None
+    ld = _scale_ld(t)
+    if quant:
+        q = scratch(f"{tag}.q", (t, i), torch.uint8, gu.device)
+        s = scratch(f"{tag}.s", ((i + 127) // 128, ld), F32, gu.device)
+    _lib.call("stk_swiglu_clamp", gu, gu.stride(0), act, i, t, i, float(limit), q, i, s, ld, _lib.stream())
+    return (act, QuantAct(q.view(FP8), s)) if quant else act
+
+
+def embed_hc(ids: torch.Tensor, embed: torch.Tensor, hc: int, vocab: int, vocab_start: int = 0) -> torch.Tensor:
+    """ids [T] -> [T, hc, H] (each stream a copy of the embedding row; rows outside this rank's
+    vocabulary shard are zero so a sum across ranks completes them)."""
+    t = ids.shape[0]
+    h = embed.shape[1]
+    vend = vocab_start + embed.shape[0]
+    if not ids.is_cuda:
+        local = ids.long() - vocab_start
+        ok = (local >= 0) & (local < embed.shape[0])
+        x = torch.where(ok[:, None], embed[local.clamp(0, embed.shape[0] - 1)], torch.zeros_like(embed[:1]))
+        return x[:, None, :].repeat(1, hc, 1).to(BF16)
+    out = torch.empty(t, hc, h, dtype=BF16, device=ids.device)
+    _lib.call("stk_embed_hc", ids, embed, out, t, h, hc, vocab, vocab_start, vend, _lib.status_buffer(), _lib.stream())
+    return out
+
+
+# ----------------------------------------------------------------------------
+# mHC
+# ----------------------------------------------------------------------------
+def mhc_pre(residual: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale: torch.Tensor,
+            norm_w: Optional[torch.Tensor], rms_eps: float, hc_eps: float, iters: int, quant: bool = False,
+            tag: str = "mhc"):
+    """residual [T, hc, H] bf16 -> (y [T, H] bf16, post [T, hc] f32, comb [T, hc*hc] f32[, QuantAct(y)])."""
+    t, hc, h = residual.shape
+    if not residual.is_cuda:
+        y, post, comb = R.mhc_pre(residual, fn, base, scale, norm_w, rms_eps, hc_eps, iters, round_bf16=True)
+        y = y.to(BF16)
+        res = (y, post, comb.reshape(t, hc * hc))
+        return res + (quant_act(y),) if quant else res
+    dev = residual.device
+    n_mix = (2 + hc) * hc
+    splits = _lib.query("stk_mhc_pick_splits", t, hc * h)
+    partial = scratch("mhc.partial", (splits * t * (n_mix + 1),), F32, dev)
+    _lib.call("stk_mhc_dots", residual, fn, partial, t, h, hc, n_mix, splits, _lib.stream())
+    y = torch.empty(t, h, dtype=BF16, device=dev)
+    post = torch.empty(t, hc, dtype=F32, device=dev)
+    comb = torch.empty(t, hc * hc, dtype=F32, device=dev)
+    q = s = None
+    ld = _scale_ld(t)
+    if quant:
+        q = scratch(f"{tag}.q", (t, h), torch.uint8, dev)
+        s = scratch(f"{tag}.s", ((h + 127) // 128, ld), F32, dev)
+    _lib.call("stk_mhc_finalize", residual, partial, splits, n_mix + 1, 1, base, scale, norm_w, post, comb, y, t, h, hc,
+              rms_eps, hc_eps, iters, 2.0, 0, q, s, ld, _lib.stream())
+    return (y, post, comb, QuantAct(q.view(FP8), s)) if quant else (y, post, comb)
+
+
+def mhc_post(x: torch.Tensor, residual: torch.Tensor, post: torch.Tensor, comb: torch.Tensor) -> torch.Tensor:
+    t, hc, h = residual.shape
+    if not residual.is_cuda:
+        return R.mhc_post(x, residual, post, comb.reshape(t, hc, hc)).to(BF16)
+    out = torch.empty_like(residual)
+    _lib.call("stk_mhc_post", x, residual, post, comb, out, t, h, hc, _lib.stream())
+    return out
+
+
+def hc_head(residual: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale: torch.Tensor, rms_eps: float,
+            hc_eps: float) -> torch.Tensor:
+    t, hc, h = residual.shape
+    if not residual.is_cuda:
+        return R.hc_head(residual, fn, base, scale, rms_eps, hc_eps).to(BF16)
+    dev = residual.device
+    splits = _lib.query("stk_mhc_pick_splits", t, hc * h)
+    partial = scratch("mhc.partial", (splits * t * (hc + 1),), F32, dev)
+    _lib.call("stk_mhc_dots", residual, fn, partial, t, h, hc, hc, splits, _lib.stream())
+    y = torch.empty(t, h, dtype=BF16, device=dev)
+    _lib.call("stk_mhc_finalize", residual, partial, splits, hc + 1, 1, base, scale, None, None, None, y, t, h, hc,
+              rms_eps, hc_eps, 0, 2.0, 1, None, None, 0, _lib.stream())
+    return y
+
+
+# ----------------------------------------------------------------------------
+# rope / KV cache
+# ----------------------------------------------------------------------------
+def inv_freq(rope_dim: int, theta: float, device) -> torch.Tensor:
+    return (1.0 / (theta ** (torch.arange(0, rope_dim, 2, dtype=F32) / rope_dim))).to(device)
+
+
+def q_norm_rope(q: torch.Tensor, positions: torch.Tensor, inv: torch.Tensor, rope_dim: int, eps: float,
+                norm: bool = True, inverse: bool = False) -> torch.Tensor:
+    """q [T, nh, D] bf16 (modified in place on GPU): weightless per-head RMSNorm then RoPE on the last dims."""
+    t, nh, d = q.shape
+    if not q.is_cuda:
+        qf = R.rms_norm(q, None, eps) if norm else q.to(F32)
+        ang = positions.to(F32)[:, None] * inv[None, :]
+        cos, sin = torch.cos(ang), torch.sin(ang)
+        qf = torch.cat([qf[..., :d - rope_dim], R.apply_rope_interleaved(qf[..., d - rope_dim:], cos, sin, inverse)], -1)
+        return qf.to(BF16)
+    assert q.stride(2) == 1 and q.stride(1) == d
+    _lib.call("stk_q_norm_rope", q, q.stride(0), positions, inv, t, nh, d, rope_dim, eps, 1 if norm else 0,
+              1 if inverse else 0, _lib.stream())
+    return q
