@@ -1,0 +1,184 @@
+"""Hybrid paged KV manager.
+
+Several cache *groups* share one page-id space per group kind:
+
+* ``swa``   — every layer's sliding-window latent cache (64-token pages).  Only the
+  pages that still intersect a request's window are kept; older ones are released
+  as the request advances, so SWA memory is O(window), not O(context).
+* ``c4``    — compressed latent cache + indexer-K cache of every ratio-4 layer
+  (one row per 4 tokens).
+* ``c128``  — compressed latent cache of every ratio-128 layer.
+* compressor *state* rows (raw value/gate rows of the open window) live in a
+  dense per-request-row tensor owned by each layer.
+
+Each group has a free list and a per-request block table row
+(``[max_requests, max_pages]`` int32, -1 = no page) that lives on the device at a
+fixed address, so captured CUDA graphs keep working while tables change.
+This is the engine-side counterpart of the KV specs and slot mappings the
+reference builds on (overlay/attention.py:743-759,836-849,
+overlay/sparse_swa_dsv4.py:87-111).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config import ModelConfig
+from ..ops.cache import PAGE, PagedCache
+
+
+class OutOfPages(RuntimeError):
+    pass
+
+
+@dataclass
+class GroupTable:
+    """Free list + device block table of one cache group."""
+    name: str
+    num_pages: int
+    max_requests: int
+    max_pages_per_req: int
+    device: torch.device
+    rows_per_token: float            # 1 for swa, 1/ratio for compressed groups
+    table_host: torch.Tensor = field(init=False)
+    table_dev: torch.Tensor = field(init=False)
+    free: List[int] = field(init=False)
+    dirty: bool = field(default=True, init=False)
+
+    def __post_init__(self) -> None:
+        self.table_host = torch.full((self.max_requests, self.max_pages_per_req), -1, dtype=torch.int32)
+        if self.device.type == "cuda":
+            self.table_host = self.table_host.pin_memory()
+        self.table_dev = torch.full((self.max_requests, self.max_pages_per_req), -1, dtype=torch.int32,
+                                    device=self.device)
+        self.free = list(range(self.num_pages - 1, -1, -1))
+
+    def ensure(self, row: int, first_logical: int, last_logical: int) -> None:
+        """Make logical pages [first, last] of request `row` resident."""
+        if last_logical >= self.max_pages_per_req:
+            raise OutOfPages(f"{self.name}: request needs logical page {last_logical} >= {self.max_pages_per_req}")
+        t = self.table_host[row]
+        for lp in range(max(first_logical, 0), last_logical + 1):
+            if t[lp] < 0:
+                if not self.free:
+                    raise OutOfPages(f"{self.name}: pool of {self.num_pages} pages exhausted")
+                t[lp] = self.free.pop()
+                self.dirty = True
+
+    def release_before(self, row: int, logical: int) -> None:
+        t = self.table_host[row]
+        lo = min(max(logical, 0), self.max_pages_per_req)
+        held = (t[:lo] >= 0).nonzero().flatten().tolist()
+        for lp in held:
+            self.free.append(int(t[lp]))
+            t[lp] = -1
+            self.dirty = True
+
+    def release_all(self, row: int) -> None:
+        self.release_before(row, self.max_pages_per_req)
+
+    def sync(self) -> None:
+        if self.dirty:
+            self.table_dev.copy_(self.table_host, non_blocking=True)
+            self.dirty = False
+
+    @property
+    def pages_in_use(self) -> int:
+        return self.num_pages - len(self.free)
+
+
+class KVManager:
+    """Owns the group tables, the per-layer cache tensors and the request-row allocator."""
+
+    def __init__(self, cfg: ModelConfig, device, max_requests: int, max_model_len: int, swa_pages: int,
+                 c4_pages: int, c128_pages: int = 0, max_chunk: int = 4096, layers: Optional[List[int]] = None,
+                 extra_swa_layers: int = 0):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.max_requests = max_requests
+        fp8 = cfg.kv_cache_dtype == "fp8_ds_mla"
+        D, Rd = cfg.head_dim, cfg.qk_rope_head_dim
+        # the block table spans the whole context; SWA residency is bounded by window + chunk
+        pages_ctx = (max_model_len + PAGE - 1) // PAGE + 1
+        self.swa = GroupTable("swa", swa_pages, max_requests, pages_ctx, self.device, 1.0)
+        self.c4 = GroupTable("c4", max(c4_pages, 1), max_requests, (max_model_len // 4) // PAGE + 2, self.device, 0.25)
+        self.c128 = GroupTable("c128", max(c128_pages, 1), max_requests, (max_model_len // 128) // PAGE + 2,
+                               self.device, 1 / 128)
+        self.layers = layers if layers is not None else list(range(cfg.num_hidden_layers))
+        self.swa_cache: Dict[int, PagedCache] = {}
+        self.comp_cache: Dict[int, PagedCache] = {}
+        self.idx_cache: Dict[int, PagedCache] = {}
+        self.comp_state: Dict[int, torch.Tensor] = {}
+        self.idx_state: Dict[int, torch.Tensor] = {}
+        n_total = cfg.num_hidden_layers + extra_swa_layers
+        for li in list(self.layers) + list(range(cfg.num_hidden_layers, n_total)):
+            self.swa_cache[li] = PagedCache.allocate(swa_pages, D, Rd, fp8, "latent", self.device)
+            kind = cfg.layer_kind(li) if li < cfg.num_hidden_layers else "swa"
+            if kind == "c4a":
+                self.comp_cache[li] = PagedCache.allocate(self.c4.num_pages, D, Rd, fp8, "latent", self.device)
+                self.idx_cache[li] = PagedCache.allocate(self.c4.num_pages, cfg.index_head_dim, Rd, fp8, "indexer",
+                                                         self.device)
+                self.comp_state[li] = torch.zeros(max_requests, 8, 2 * 2 * D, dtype=torch.float32, device=self.device)
+                self.idx_state[li] = torch.zeros(max_requests, 8, 2 * 2 * cfg.index_head_dim, dtype=torch.float32,
+                                                 device=self.device)
+            elif kind == "c128a":
+                self.comp_cache[li] = PagedCache.allocate(self.c128.num_pages, D, Rd, fp8, "latent", self.device)
+                self.comp_state[li] = torch.zeros(max_requests, 128, 2 * D, dtype=torch.float32, device=self.device)
+        self.free_rows = list(range(max_requests - 1, -1, -1))
+
+    # ---- request rows -------------------------------------------------------
+    def alloc_row(self) -> int:
+        if not self.free_rows:
+            raise OutOfPages("no free request row")
+        return self.free_rows.pop()
+
+    def free_row(self, row: int) -> None:
+        for g in (self.swa, self.c4, self.c128):
+            g.release_all(row)
+        self.free_rows.append(row)
+
+    # ---- per-step residency ---------------------------------------------------
+    def prepare(self, row: int, start_pos: int, n_tokens: int, lookback: Optional[int] = None) -> None:
+        """Make resident what a step that appends positions [start, start+n) to request `row` touches,
+        and release SWA pages that have left the window."""
+        cfg = self.cfg
+        W = cfg.sliding_window if lookback is None else lookback
+        end = start_pos + n_tokens                 # exclusive
+        lo = max(0, start_pos - W + 1)
+        self.swa.release_before(row, lo // PAGE)
+        self.swa.ensure(row, lo // PAGE, (end - 1) // PAGE)
+        if any(cfg.layer_kind(l) == "c4a" for l in self.layers):
+            n_rows = end // 4
+            if n_rows > 0:
+                self.c4.ensure(row, 0, (n_rows - 1) // PAGE)
+        if any(cfg.layer_kind(l) == "c128a" for l in self.layers):
+            n_rows = end // 128
+            if n_rows > 0:
+                self.c128.ensure(row, 0, (n_rows - 1) // PAGE)
+
+    def can_admit(self, n_tokens: int, context: int) -> bool:
+        need_swa = (min(n_tokens, context) + self.cfg.sliding_window) // PAGE + 2
+        need_c4 = (context // 4) // PAGE + 1
+        return bool(self.free_rows) and len(self.swa.free) >= need_swa and len(self.c4.free) >= need_c4
+
+    def sync(self) -> None:
+        for g in (self.swa, self.c4, self.c128):
+            g.sync()
+
+    def bytes_allocated(self) -> int:
+        n = 0
+        for d in (self.swa_cache, self.comp_cache, self.idx_cache):
+            n += sum(c.buf.numel() for c in d.values())
+        for d in (self.comp_state, self.idx_state):
+            n += sum(t.numel() * 4 for t in d.values())
+        return n
+
+
+def size_pools(cfg: ModelConfig, max_requests: int, max_context: int, max_chunk: int) -> Dict[str, int]:
+    """Pages needed so that `max_requests` sequences of `max_context` tokens fit (no prefix sharing)."""
+    swa = max_requests * ((cfg.sliding_window + PAGE - 1) // PAGE + 2) + (max_chunk + PAGE - 1) // PAGE + 2
+    c4 = max_requests * ((max_context // 4 + PAGE - 1) // PAGE + 1)
+    c128 = max_requests * ((max_context // 128 + PAGE - 1) // PAGE + 1)
+    return {"swa_pages": swa, "c4_pages": c4, "c128_pages": c128}

@@ -18,7 +18,7 @@ def dev():
 
 
 def rel_err(a, b):
-    a, b = a.float(), b.float()
+    a, b = a.float().cpu(), b.float().cpu()
     return ((a - b).norm() / b.norm().clamp(min=1e-12)).item()
 
 
