@@ -165,7 +165,8 @@ __global__ void kv_gather_dequant_kernel(CacheGeom cache, const int64_t* __restr
 
 // ---- KV compressor ----------------------------------------------------------------
 struct CompressArgs {
-  const float* kvs;            // [T, 2*c*D]: value slots (c*D) then gate slots (c*D)
+  const float* kvs;            // [T, kvs_ld]: value slots (c*D) then gate slots (c*D)
+  long long kvs_ld;
   const float* ape;            // [ratio, c*D]
   const __nv_bfloat16* norm_w; // [D]
   const float* inv_freq;
@@ -185,7 +186,7 @@ struct CompressArgs {
 
 __device__ __forceinline__ const float* compress_src_row(const CompressArgs& a, int t, long long pos_t, long long p) {
   const int first = a.tok_first_pos[t];
-  if (p >= first) return a.kvs + static_cast<long long>(t - (pos_t - p)) * (2LL * a.c * a.D);
+  if (p >= first) return a.kvs + static_cast<long long>(t - (pos_t - p)) * a.kvs_ld;
   return a.state + (static_cast<long long>(a.tok_req[t]) * a.ring + (p % a.ring)) * (2LL * a.c * a.D);
 }
 
@@ -285,14 +286,14 @@ __global__ void compress_save_state_kernel(CompressArgs a, const int* __restrict
   const long long pos = a.positions[t];
   if (pos < 0 || pos + a.ring <= tok_last_pos[t]) return;
   const long long w = 2LL * a.c * a.D;
-  const float* src = a.kvs + static_cast<long long>(t) * w;
+  const float* src = a.kvs + static_cast<long long>(t) * a.kvs_ld;
   float* dst = a.state + (static_cast<long long>(a.tok_req[t]) * a.ring + (pos % a.ring)) * w;
   for (int i = threadIdx.x; i < w; i += blockDim.x) dst[i] = src[i];
 }
 
 // ---- indexer Q ---------------------------------------------------------------------
 // q [T, ih, d] bf16, w [T, ih] fp32 -> q_out (fp8 or bf16), w_out fp32.  One warp per (t, head).
-__global__ void indexer_q_prep_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const float* __restrict__ w,
+__global__ void indexer_q_prep_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const float* __restrict__ w, long long ldw,
                                       const int64_t* __restrict__ positions, const float* __restrict__ inv_freq,
                                       void* __restrict__ q_out, float* __restrict__ w_out, int T, int ih, int d, int R,
                                       int quantize) {
@@ -327,13 +328,13 @@ __global__ void indexer_q_prep_kernel(const __nv_bfloat16* __restrict__ q, long 
     for (int i = lane * 2; i < d; i += 64, ++np)
       *reinterpret_cast<uint16_t*>(dst + i) =
           static_cast<uint16_t>(f_to_fp8(va[np] * inv)) | (static_cast<uint16_t>(f_to_fp8(vb[np] * inv)) << 8);
-    if (lane == 0) w_out[t * ih + h] = w[t * ih + h] * sc * fold;
+    if (lane == 0) w_out[t * ih + h] = w[t * ldw + h] * sc * fold;
   } else {
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(q_out) + (static_cast<long long>(t) * ih + h) * d;
     np = 0;
     for (int i = lane * 2; i < d; i += 64, ++np)
       *reinterpret_cast<__nv_bfloat162*>(dst + i) = __floats2bfloat162_rn(va[np], vb[np]);
-    if (lane == 0) w_out[t * ih + h] = w[t * ih + h] * fold;
+    if (lane == 0) w_out[t * ih + h] = w[t * ldw + h] * fold;
   }
 }
 
@@ -371,7 +372,7 @@ STK_API int stk_kv_gather_dequant(const void* cache, long long page_stride, int 
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-STK_API int stk_compress_windows(const float* kvs, const float* ape, const void* norm_w, const float* inv_freq,
+STK_API int stk_compress_windows(const float* kvs, long long kvs_ld, const float* ape, const void* norm_w, const float* inv_freq,
                                  const int64_t* positions, const int* tok_req, const int* tok_first_pos,
                                  const int* tok_last_pos, float* state, const int* block_table, int bt_stride,
                                  void* cache, long long page_stride, int data_bytes, int fp8, int idx_format,
@@ -380,7 +381,7 @@ STK_API int stk_compress_windows(const float* kvs, const float* ape, const void*
   if (T <= 0) return 0;
   if (D % 2 || c < 1 || c > 2) return -1;
   CompressArgs a;
-  a.kvs = kvs; a.ape = ape; a.norm_w = (const __nv_bfloat16*)norm_w; a.inv_freq = inv_freq; a.positions = positions;
+  a.kvs = kvs; a.kvs_ld = kvs_ld; a.ape = ape; a.norm_w = (const __nv_bfloat16*)norm_w; a.inv_freq = inv_freq; a.positions = positions;
   a.tok_req = tok_req; a.tok_first_pos = tok_first_pos; a.state = state; a.block_table = block_table;
   a.bt_stride = bt_stride; a.cache = CacheGeom{(uint8_t*)cache, page_stride, data_bytes, fp8};
   a.idx_format = idx_format; a.T = T; a.D = D; a.R = R; a.ratio = ratio; a.c = c; a.ring = ring;
@@ -391,13 +392,13 @@ STK_API int stk_compress_windows(const float* kvs, const float* ape, const void*
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
-STK_API int stk_indexer_q_prep(const void* q, long long ldq, const float* w, const int64_t* positions,
+STK_API int stk_indexer_q_prep(const void* q, long long ldq, const float* w, long long ldw, const int64_t* positions,
                                const float* inv_freq, void* q_out, float* w_out, int T, int ih, int d, int R,
                                int quantize, void* stream) {
   if (T <= 0) return 0;
   if (d % 2 || d > 256) return -1;
   const long long warps = static_cast<long long>(T) * ih;
   indexer_q_prep_kernel<<<static_cast<int>((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)q, ldq, w, positions, inv_freq, q_out, w_out, T, ih, d, R, quantize);
+      (const __nv_bfloat16*)q, ldq, w, ldw, positions, inv_freq, q_out, w_out, T, ih, d, R, quantize);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -97,7 +97,8 @@ __global__ void c128_indices_kernel(const int64_t* __restrict__ positions, const
 __global__ void token_maps_kernel(const int* __restrict__ query_start, const int* __restrict__ req_rows,
                                   const int* __restrict__ start_pos, int n_req, int* __restrict__ tok_req,
                                   int64_t* __restrict__ positions, int* __restrict__ first_pos,
-                                  int* __restrict__ last_pos, int T_padded) {
+                                  int* __restrict__ last_pos, const int* __restrict__ block_table, int bt_stride,
+                                  int64_t* __restrict__ slot_mapping, int T_padded) {
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= T_padded) return;
   int r = -1;
@@ -109,12 +110,18 @@ __global__ void token_maps_kernel(const int* __restrict__ query_start, const int
     positions[t] = -1;
     first_pos[t] = 0;
     last_pos[t] = -1;
+    if (slot_mapping) slot_mapping[t] = -1;
     return;
   }
   tok_req[t] = req_rows[r];
   positions[t] = start_pos[r] + (t - query_start[r]);
   first_pos[t] = start_pos[r];
   last_pos[t] = start_pos[r] + (query_start[r + 1] - query_start[r]) - 1;
+  if (slot_mapping) {
+    const long long p = start_pos[r] + (t - query_start[r]);
+    const int page = block_table[static_cast<long long>(req_rows[r]) * bt_stride + (p >> 6)];
+    slot_mapping[t] = page >= 0 ? static_cast<long long>(page) * 64 + (p & 63) : -1;
+  }
 }
 
 }  // namespace stk
@@ -153,10 +160,12 @@ STK_API int stk_c128_indices(const int64_t* positions, const int* tok_req, const
 }
 
 STK_API int stk_token_maps(const int* query_start, const int* req_rows, const int* start_pos, int n_req, int* tok_req,
-                           int64_t* positions, int* first_pos, int* last_pos, int T_padded, void* stream) {
+                           int64_t* positions, int* first_pos, int* last_pos, const int* block_table, int bt_stride,
+                           int64_t* slot_mapping, int T_padded, void* stream) {
   if (T_padded <= 0) return 0;
   token_maps_kernel<<<(T_padded + 127) / 128, 128, 0, (cudaStream_t)stream>>>(query_start, req_rows, start_pos, n_req,
                                                                               tok_req, positions, first_pos, last_pos,
+                                                                              block_table, bt_stride, slot_mapping,
                                                                               T_padded);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -1,0 +1,384 @@
+"""The engine's DeepSeek-V4-style decoder: paged caches, batched ragged steps, tensor/expert
+parallel shards, every hot op a kernel from :mod:`stkernel_b200.ops`.
+
+Layer order and data flow follow overlay/nvidia_model.py:1509-1572,1713-1841 and
+overlay/attention.py:541-670; semantics are pinned by :mod:`.dsv4_oracle`.
+
+Parallel layout (one rank per GPU, `tp` ranks):
+  * replicated: embedding, mHC parameters, fused wq_a|wkv, compressors, indexer, router gate
+  * column-parallel: wq_b (heads), wo_a (o-groups), shared-expert w1|w3, LM head (vocab)
+  * row-parallel + all-reduce: wo_b, shared-expert w2
+  * routed experts: expert-parallel (E/tp experts per rank), summed by the same all-reduce
+"""
+from __future__ import annotations
+
+import hashlib
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Tuple
+
+import torch
+
+from ..config import ModelConfig
+from ..ops import attention as A
+from ..ops import cache as C
+from ..ops import functional as Fn
+from ..ops import moe as M
+from ..ops.functional import LinearWeight
+from .dsv4_oracle import index_cache_computes
+from .weights import compressor_slots
+
+BF16 = torch.bfloat16
+F32 = torch.float32
+
+
+# ----------------------------------------------------------------------------
+# weight sources
+# ----------------------------------------------------------------------------
+class WeightSource:
+    """Hands out fp32 master tensors by checkpoint name."""
+
+    def get(self, name: str, shape: Tuple[int, ...], device) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class DictSource(WeightSource):
+    def __init__(self, tensors: Dict[str, torch.Tensor]):
+        self.t = tensors
+
+    def get(self, name, shape, device):
+        t = self.t[name]
+        assert tuple(t.shape) == tuple(shape), (name, t.shape, shape)
+        return t.to(device)
+
+
+class RandomSource(WeightSource):
+    """Random-init weights: every tensor is a pure function of (seed, name), so replicated
+    tensors agree across ranks without communication."""
+
+    def __init__(self, seed: int = 0, std: float = 0.02):
+        self.seed, self.std = seed, std
+
+    def _gen(self, name: str, device) -> torch.Generator:
+        h = int.from_bytes(hashlib.sha256(f"{self.seed}:{name}".encode()).digest()[:7], "little")
+        g = torch.Generator(device=device)
+        g.manual_seed(h)
+        return g
+
+    def get(self, name, shape, device):
+        dev = torch.device(device)
+        g = self._gen(name, dev)
+        if name.endswith("tid2eid"):
+            return torch.randint(0, 1 << 30, shape, generator=g, device=dev, dtype=torch.int64)
+        if name.endswith("norm.weight") or name.endswith("_scale"):
+            return torch.ones(shape, device=dev)
+        if name.endswith("_base") or name.endswith("attn_sink"):
+            return torch.zeros(shape, device=dev)
+        if name.endswith("gate.bias"):
+            return torch.rand(shape, generator=g, device=dev) * 0.2 - 0.1
+        return torch.randn(shape, generator=g, device=dev) * self.std
+
+
+# ----------------------------------------------------------------------------
+# per-layer weights in storage format
+# ----------------------------------------------------------------------------
+@dataclass
+class LayerWeights:
+    kind: str
+    ratio: int
+    computes_topk: bool
+    hc_attn: Tuple[torch.Tensor, torch.Tensor, torch.Tensor]
+    hc_ffn: Tuple[torch.Tensor, torch.Tensor, torch.Tensor]
+    attn_norm: torch.Tensor
+    ffn_norm: torch.Tensor
+    w_qa_kv: LinearWeight
+    q_norm: torch.Tensor
+    kv_norm: torch.Tensor
+    w_qb: LinearWeight                     # [nh_local*D (+ ih*di on F-layers), q_lora]
+    w_oa: List[LinearWeight]
+    w_ob: LinearWeight
+    sink: torch.Tensor
+    w_side: Optional[LinearWeight] = None  # bf16 [2cD (+ ih + 4di), H]: compressor | weights_proj | indexer compressor
+    ape: Optional[torch.Tensor] = None
+    comp_norm: Optional[torch.Tensor] = None
+    iape: Optional[torch.Tensor] = None
+    inorm: Optional[torch.Tensor] = None
+    w_gate: Optional[LinearWeight] = None
+    gate_bias: Optional[torch.Tensor] = None
+    tid2eid: Optional[torch.Tensor] = None
+    w_sh13: Optional[LinearWeight] = None
+    w_sh2: Optional[LinearWeight] = None
+    experts: Optional[M.ExpertWeights] = None
+
+
+def _get(src: WeightSource, name: str, shape, device) -> torch.Tensor:
+    return src.get(name, tuple(shape), device)
+
+
+def build_layer(cfg: ModelConfig, src: WeightSource, prefix: str, li: int, device, tp_rank: int, tp_size: int,
+                kind: Optional[str] = None) -> LayerWeights:
+    H, D, Rd, nh, hc = cfg.hidden_size, cfg.head_dim, cfg.qk_rope_head_dim, cfg.num_attention_heads, cfg.hc_mult
+    dd = cfg.dense_dtype
+    kind = kind or cfg.layer_kind(li)
+    ratio = {"swa": 0, "c4a": 4, "c128a": 128}[kind]
+    nh_l = nh // tp_size
+    h0 = tp_rank * nh_l
+    a = f"{prefix}.attn"
+    mk = lambda w: LinearWeight.from_master(w, dd, device)
+    mkbf = lambda w: LinearWeight(w.to(device=device, dtype=BF16).contiguous())
+    g = lambda n, s: _get(src, n, s, device)
+
+    hc_attn = (g(f"{prefix}.hc_attn_fn", (cfg.mix_hc, hc * H)).to(F32).contiguous(),
+               g(f"{prefix}.hc_attn_base", (cfg.mix_hc,)).to(F32), g(f"{prefix}.hc_attn_scale", (3,)).to(F32))
+    hc_ffn = (g(f"{prefix}.hc_ffn_fn", (cfg.mix_hc, hc * H)).to(F32).contiguous(),
+              g(f"{prefix}.hc_ffn_base", (cfg.mix_hc,)).to(F32), g(f"{prefix}.hc_ffn_scale", (3,)).to(F32))
+    w_qa_kv = mk(torch.cat([g(f"{a}.wq_a.weight", (cfg.q_lora_rank, H)), g(f"{a}.wkv.weight", (D, H))], 0))
+    wqb = g(f"{a}.wq_b.weight", (nh * D, cfg.q_lora_rank))[h0 * D:(h0 + nh_l) * D]
+    computes = kind == "c4a" and index_cache_computes(cfg, li)
+    if kind == "c4a" and computes:
+        wqb = torch.cat([wqb, g(f"{a}.indexer.wq_b.weight", (cfg.index_n_heads * cfg.index_head_dim, cfg.q_lora_rank))], 0)
+    G = cfg.o_groups
+    hpg = nh // G
+    woa_full = g(f"{a}.wo_a.weight", (G * cfg.o_lora_rank, hpg * D)).view(G, cfg.o_lora_rank, hpg * D)
+    if tp_size <= G:
+        g_l = G // tp_size
+        groups = list(range(tp_rank * g_l, (tp_rank + 1) * g_l))
+        w_oa = [mk(woa_full[gi]) for gi in groups]
+        wob = g(f"{a}.wo_b.weight", (H, G * cfg.o_lora_rank))[:, groups[0] * cfg.o_lora_rank:(groups[-1] + 1) * cfg.o_lora_rank]
+    else:
+        raise NotImplementedError("tp_size > o_groups")
+    lw = LayerWeights(
+        kind=kind, ratio=ratio, computes_topk=computes, hc_attn=hc_attn, hc_ffn=hc_ffn,
+        attn_norm=g(f"{prefix}.attn_norm.weight", (H,)).to(BF16), ffn_norm=g(f"{prefix}.ffn_norm.weight", (H,)).to(BF16),
+        w_qa_kv=w_qa_kv, q_norm=g(f"{a}.q_norm.weight", (cfg.q_lora_rank,)).to(BF16),
+        kv_norm=g(f"{a}.kv_norm.weight", (D,)).to(BF16), w_qb=mk(wqb), w_oa=w_oa, w_ob=mk(wob.contiguous()),
+        sink=g(f"{a}.attn_sink", (nh,)).to(F32)[h0:h0 + nh_l].contiguous())
+    if ratio:
+        c = compressor_slots(ratio)
+        side = [g(f"{a}.compressor.wkv.weight", (c * D, H)), g(f"{a}.compressor.wgate.weight", (c * D, H))]
+        lw.ape = g(f"{a}.compressor.ape", (ratio, c * D)).to(F32).contiguous()
+        lw.comp_norm = g(f"{a}.compressor.norm.weight", (D,)).to(BF16)
+        if computes:
+            di = cfg.index_head_dim
+            side += [g(f"{a}.indexer.weights_proj.weight", (cfg.index_n_heads, H)),
+                     g(f"{a}.indexer.compressor.wkv.weight", (2 * di, H)),
+                     g(f"{a}.indexer.compressor.wgate.weight", (2 * di, H))]
+            lw.iape = g(f"{a}.indexer.compressor.ape", (ratio, 2 * di)).to(F32).contiguous()
+            lw.inorm = g(f"{a}.indexer.compressor.norm.weight", (di,)).to(BF16)
+        lw.w_side = mkbf(torch.cat(side, 0))
+    # ---- MoE ----
+    f = f"{prefix}.ffn"
+    E, I = cfg.n_routed_experts, cfg.moe_intermediate_size
+    lw.w_gate = mkbf(g(f"{f}.gate.weight", (E, H)))
+    if li < cfg.num_hash_layers:
+        lw.tid2eid = (g(f"{f}.gate.tid2eid", (cfg.vocab_size, cfg.num_experts_per_tok)) % E).to(torch.int32).contiguous()
+    else:
+        lw.gate_bias = g(f"{f}.gate.bias", (E,)).to(F32)
+    if cfg.n_shared_experts:
+        Is = I * cfg.n_shared_experts
+        isl = Is // tp_size
+        r0 = tp_rank * isl
+        w1 = g(f"{f}.shared_experts.w1.weight", (Is, H))[r0:r0 + isl]
+        w3 = g(f"{f}.shared_experts.w3.weight", (Is, H))[r0:r0 + isl]
+        lw.w_sh13 = mk(torch.cat([w1, w3], 0))
+        lw.w_sh2 = mk(g(f"{f}.shared_experts.w2.weight", (H, Is))[:, r0:r0 + isl].contiguous())
+    e_l = E // tp_size
+    e0 = tp_rank * e_l
+    w13s, w2s = [], []
+    packs = []
+    for e in range(e0, e0 + e_l):
+        w13 = torch.cat([g(f"{f}.experts.{e}.w1.weight", (I, H)), g(f"{f}.experts.{e}.w3.weight", (I, H))], 0)
+        w2 = g(f"{f}.experts.{e}.w2.weight", (H, I))
+        packs.append(M.ExpertWeights.from_master(w13[None], w2[None], cfg.expert_dtype, device, 0))
+    cat = lambda xs: torch.cat(xs, 0).contiguous() if xs[0] is not None else None
+    lw.experts = M.ExpertWeights(cat([p.w13 for p in packs]), cat([p.w2 for p in packs]), cat([p.s13 for p in packs]),
+                                 cat([p.s2 for p in packs]), cat([p.g13 for p in packs]), cat([p.g2 for p in packs]), e0)
+    return lw
+
+
+@dataclass
+class ModelWeights:
+    embed: torch.Tensor                 # bf16 [V, H] replicated
+    head: LinearWeight                  # [V/tp, H]
+    norm: torch.Tensor
+    hc_head: Tuple[torch.Tensor, torch.Tensor, torch.Tensor]
+    layers: List[LayerWeights]
+    vocab_start: int = 0
+
+
+def build_model_weights(cfg: ModelConfig, src: WeightSource, device, tp_rank: int = 0, tp_size: int = 1,
+                        head_fp8: bool = False) -> ModelWeights:
+    H, V, hc = cfg.hidden_size, cfg.vocab_size, cfg.hc_mult
+    g = lambda n, s: _get(src, n, s, device)
+    vl = (V + tp_size - 1) // tp_size
+    v0 = tp_rank * vl
+    head = g("head.weight", (V, H))[v0:min(V, v0 + vl)]
+    head_w = LinearWeight.from_master(head, "fp8", device) if head_fp8 else LinearWeight(head.to(BF16).contiguous())
+    layers = [build_layer(cfg, src, f"layers.{li}", li, device, tp_rank, tp_size) for li in range(cfg.num_hidden_layers)]
+    return ModelWeights(
+        embed=g("embed.weight", (V, H)).to(BF16).contiguous(), head=head_w, norm=g("norm.weight", (H,)).to(BF16),
+        hc_head=(g("hc_head_fn", (hc, hc * H)).to(F32).contiguous(), g("hc_head_base", (hc,)).to(F32),
+                 g("hc_head_scale", (1,)).to(F32)),
+        layers=layers, vocab_start=v0)
+
+
+# ----------------------------------------------------------------------------
+# step inputs
+# ----------------------------------------------------------------------------
+@dataclass
+class StepMeta:
+    """Device-side description of one ragged step (decode rows and prefill chunks alike)."""
+    token_ids: torch.Tensor        # [T] int64
+    tok_req: torch.Tensor          # [T] int32 request row, -1 padding
+    positions: torch.Tensor        # [T] int64, -1 padding
+    first_pos: torch.Tensor        # [T] int32
+    last_pos: torch.Tensor         # [T] int32
+    swa_slot_mapping: torch.Tensor  # [T] int64 destination slot of each token's latent row
+    swa_slots: torch.Tensor        # [T, W] int32 window rows
+    swa_lens: torch.Tensor         # [T] int32
+    max_comp_rows: int             # upper bound of compressed rows any request holds (c4 group)
+    max_c128_rows: int = 0
+
+
+class DSV4Model:
+    def __init__(self, cfg: ModelConfig, weights: ModelWeights, kv, comm=None, tp_rank: int = 0, tp_size: int = 1):
+        self.cfg = cfg
+        self.w = weights
+        self.kv = kv
+        self.comm = comm
+        self.tp_rank, self.tp_size = tp_rank, tp_size
+        dev = weights.embed.device
+        self.device = dev
+        self.inv = Fn.inv_freq(cfg.qk_rope_head_dim, cfg.rope_theta, dev)
+        self.topk_buffer: Optional[torch.Tensor] = None     # IndexCache: shared by consecutive C4A layers
+        self.aux_layers: Tuple[int, ...] = ()
+        self.aux_out: List[torch.Tensor] = []
+
+    # ---- collectives ----------------------------------------------------------
+    def _all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self.tp_size == 1 or self.comm is None:
+            return x
+        return self.comm.all_reduce(x)
+
+    # ---- attention sub-block ---------------------------------------------------
+    def attention(self, li: int, lw: LayerWeights, y: torch.Tensor, yq, meta: StepMeta, causal_meta=None) -> torch.Tensor:
+        cfg = self.cfg
+        T = y.shape[0]
+        D, Rd = cfg.head_dim, cfg.qk_rope_head_dim
+        nh_l = cfg.num_attention_heads // self.tp_size
+        ql = cfg.q_lora_rank
+        qkv = Fn.linear(yq if yq is not None else y, lw.w_qa_kv, tag="qa_kv")
+        use_q = lw.w_qb.is_fp8
+        res = Fn.rms_norm_pair(qkv[:, :ql], lw.q_norm, qkv[:, ql:], lw.kv_norm, cfg.rms_norm_eps, quant0=use_q, tag="qr")
+        qr, kvn = res[0], res[1]
+        qb = Fn.linear(res[2] if use_q else qr, lw.w_qb, tag="qb")
+        q = Fn.q_norm_rope(qb[:, :nh_l * D].view(T, nh_l, D), meta.positions, self.inv, Rd, cfg.rms_norm_eps)
+        C.kv_rope_quant_insert(kvn, meta.positions, meta.swa_slot_mapping, self.inv, self.kv.swa_cache[li])
+
+        topk_slots = topk_lens = None
+        comp_cache = None
+        if lw.ratio:
+            c = compressor_slots(lw.ratio)
+            side = Fn.linear(y, lw.w_side, out_dtype=F32, tag="side")
+            ncomp = 2 * c * D
+            grp = self.kv.c4 if lw.kind == "c4a" else self.kv.c128
+            comp_cache = self.kv.comp_cache[li]
+            C.compress_windows(side[:, :ncomp], lw.ape, lw.comp_norm,
+                               self.inv, meta.positions, meta.tok_req, meta.first_pos, meta.last_pos,
+                               self.kv.comp_state[li], grp.table_dev, comp_cache, lw.ratio, c, cfg.rms_norm_eps)
+            if lw.kind == "c4a":
+                K = cfg.index_topk
+                if self.topk_buffer is None or self.topk_buffer.shape[0] < T:
+                    self.topk_buffer = torch.full((max(T, 16), K), -1, dtype=torch.int32, device=y.device)
+                if lw.computes_topk:
+                    ih, di = cfg.index_n_heads, cfg.index_head_dim
+                    qi = qb[:, nh_l * D:].view(T, ih, di)
+                    wi = side[:, ncomp:ncomp + ih]
+                    quant = cfg.kv_cache_dtype == "fp8_ds_mla"
+                    qq, wf = C.indexer_q_prep(qi, wi, meta.positions, self.inv, Rd, quant)
+                    C.compress_windows(side[:, ncomp + ih:], lw.iape, lw.inorm, self.inv, meta.positions,
+                                       meta.tok_req, meta.first_pos, meta.last_pos, self.kv.idx_state[li],
+                                       grp.table_dev, self.kv.idx_cache[li], lw.ratio, 2, cfg.rms_norm_eps)
+                    nv = A.compressed_valid(meta.positions, lw.ratio)
+                    scores = A.indexer_scores(qq, wf, self.kv.idx_cache[li], grp.table_dev, meta.tok_req, nv,
+                                              max(meta.max_comp_rows, 1))
+                    A.topk_rows(scores, nv, K, out=self.topk_buffer)
+                topk_slots, topk_lens = A.topk_to_slots(self.topk_buffer[:T], grp.table_dev, meta.tok_req,
+                                                        grp.max_pages_per_req * C.PAGE, tag=f"topk")
+            else:
+                topk_slots, topk_lens = A.c128_indices(meta.positions, meta.tok_req, grp.table_dev, lw.ratio,
+                                                       cfg.index_topk)
+        o = A.sparse_mla(q, self.kv.swa_cache[li], meta.swa_slots, meta.swa_lens, comp_cache, topk_slots, topk_lens,
+                         lw.sink, D ** -0.5)
+        o = Fn.q_norm_rope(o, meta.positions, self.inv, Rd, cfg.rms_norm_eps, norm=False, inverse=True)
+        # grouped low-rank output projection, then the row-parallel wo_b (+ all-reduce)
+        G_l = len(lw.w_oa)
+        hpg = cfg.num_attention_heads // cfg.o_groups
+        og = o.view(T, G_l, hpg * D)
+        z = torch.empty(T, G_l * cfg.o_lora_rank, dtype=o.dtype, device=y.device)
+        for gi, wg in enumerate(lw.w_oa):
+            Fn.linear(og[:, gi], wg, out=z[:, gi * cfg.o_lora_rank:(gi + 1) * cfg.o_lora_rank], tag=f"oa")
+        out = Fn.linear(z, lw.w_ob, tag="ob")
+        return self._all_reduce(out)
+
+    # ---- MoE sub-block ----------------------------------------------------------
+    def moe(self, lw: LayerWeights, y: torch.Tensor, yq, meta: StepMeta) -> torch.Tensor:
+        cfg = self.cfg
+        logits = Fn.linear(y, lw.w_gate, out_dtype=F32, tag="gate")
+        ids, wts = M.router(logits, lw.gate_bias, cfg.num_experts_per_tok, cfg.scoring_func, cfg.norm_topk_prob,
+                            cfg.routed_scaling_factor, lw.tid2eid, meta.token_ids)
+        shared = None
+        if lw.w_sh13 is not None:
+            gu = Fn.linear(yq if (yq is not None and lw.w_sh13.is_fp8) else y, lw.w_sh13, tag="sh13")
+            if lw.w_sh2.is_fp8:
+                _, aq = Fn.swiglu_clamp(gu, cfg.swiglu_limit, quant=True, tag="shact")
+                shared = Fn.linear(aq, lw.w_sh2, tag="sh2")
+            else:
+                shared = Fn.linear(Fn.swiglu_clamp(gu, cfg.swiglu_limit), lw.w_sh2, tag="sh2")
+        out = M.moe_experts(y, ids, wts, lw.experts, cfg.swiglu_limit, shared)
+        return self._all_reduce(out)
+
+    def layer(self, li: int, lw: LayerWeights, X: torch.Tensor, meta: StepMeta) -> torch.Tensor:
+        cfg = self.cfg
+        want_q = lw.w_qa_kv.is_fp8
+        r = Fn.mhc_pre(X, *lw.hc_attn, lw.attn_norm, cfg.rms_norm_eps, cfg.hc_eps, cfg.hc_sinkhorn_iters, quant=want_q,
+                       tag="mhc_a")
+        y, post, comb = r[0], r[1], r[2]
+        a = self.attention(li, lw, y, r[3] if want_q else None, meta)
+        X = Fn.mhc_post(a, X, post, comb)
+        want_q = lw.w_sh13 is not None and lw.w_sh13.is_fp8
+        r = Fn.mhc_pre(X, *lw.hc_ffn, lw.ffn_norm, cfg.rms_norm_eps, cfg.hc_eps, cfg.hc_sinkhorn_iters, quant=want_q,
+                       tag="mhc_f")
+        y, post, comb = r[0], r[1], r[2]
+        f = self.moe(lw, y, r[3] if want_q else None, meta)
+        return Fn.mhc_post(f, X, post, comb)
+
+    # ---- whole model -------------------------------------------------------------
+    def forward_hidden(self, meta: StepMeta) -> torch.Tensor:
+        """-> final residual streams [T, hc, H]."""
+        cfg = self.cfg
+        X = Fn.embed_hc(meta.token_ids, self.w.embed, cfg.hc_mult, cfg.vocab_size)
+        self.aux_out = []
+        for li, lw in enumerate(self.w.layers):
+            X = self.layer(li, lw, X, meta)
+            if li in self.aux_layers:
+                self.aux_out.append(X.float().mean(1).to(X.dtype))
+        return X
+
+    def head_hidden(self, X: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
+        h = Fn.hc_head(X, *self.w.hc_head, cfg.rms_norm_eps, cfg.hc_eps)
+        return Fn.rms_norm(h, self.w.norm, cfg.rms_norm_eps)
+
+    def compute_logits(self, h: torch.Tensor) -> torch.Tensor:
+        """h [n, H] -> logits [n, V] (vocab shards gathered across ranks)."""
+        lg = Fn.linear(h, self.w.head, tag="head")
+        if self.tp_size > 1 and self.comm is not None:
+            lg = self.comm.all_gather_last_dim(lg)[:, :self.cfg.vocab_size]
+        return lg
+
+    def forward(self, meta: StepMeta, logit_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Logits for the selected token rows (all rows when logit_rows is None)."""
+        X = self.forward_hidden(meta)
+        if logit_rows is not None:
+            X = X.index_select(0, logit_rows)
+        return self.compute_logits(self.head_hidden(X))

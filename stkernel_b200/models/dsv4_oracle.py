@@ -191,9 +191,16 @@ class OracleModel:
         key = f"{f}.__stacked"
         if key not in self._deq:
             E = cfg.n_routed_experts
-            w13 = torch.stack([torch.cat([self.expert_w(f"{f}.experts.{e}.w1.weight"),
-                                          self.expert_w(f"{f}.experts.{e}.w3.weight")], 0) for e in range(E)])
-            w2 = torch.stack([self.expert_w(f"{f}.experts.{e}.w2.weight") for e in range(E)])
+            def q(t):
+                if cfg.expert_dtype == "nvfp4":
+                    return R.dequant_nvfp4(*R.quant_nvfp4(t))
+                if cfg.expert_dtype == "mxfp4":
+                    return R.dequant_nvfp4(*R.mxfp4_to_nvfp4(*R.quant_mxfp4(t)))
+                return t.to(torch.bfloat16).to(F32)
+            # gate and up rows are stored as one [2I, H] matrix with one global scale
+            w13 = torch.stack([q(torch.cat([self.w[f"{f}.experts.{e}.w1.weight"].to(F32),
+                                            self.w[f"{f}.experts.{e}.w3.weight"].to(F32)], 0)) for e in range(E)])
+            w2 = torch.stack([q(self.w[f"{f}.experts.{e}.w2.weight"].to(F32)) for e in range(E)])
             self._deq[key] = (w13, w2)
         w13, w2 = self._deq[key]
         out = R.moe_experts(y, ids, wts, w13, w2, cfg.swiglu_limit)
@@ -209,12 +216,12 @@ class OracleModel:
         w = self.w
         y, post, comb = R.mhc_pre(X, w[f"{prefix}.hc_attn_fn"], w[f"{prefix}.hc_attn_base"], w[f"{prefix}.hc_attn_scale"],
                                   self.bf16_w(f"{prefix}.attn_norm.weight"), cfg.rms_norm_eps, cfg.hc_eps,
-                                  cfg.hc_sinkhorn_iters)
+                                  cfg.hc_sinkhorn_iters, round_bf16=True)
         a = self._attention(li, prefix, y, positions, shared_topk, kind, causal)
         X = R.mhc_post(a, X, post, comb)
         y, post, comb = R.mhc_pre(X, w[f"{prefix}.hc_ffn_fn"], w[f"{prefix}.hc_ffn_base"], w[f"{prefix}.hc_ffn_scale"],
                                   self.bf16_w(f"{prefix}.ffn_norm.weight"), cfg.rms_norm_eps, cfg.hc_eps,
-                                  cfg.hc_sinkhorn_iters)
+                                  cfg.hc_sinkhorn_iters, round_bf16=True)
         f = self._moe(prefix, li, y, token_ids)
         return R.mhc_post(f, X, post, comb)
 

@@ -9,6 +9,7 @@ from . import _lib
 from . import reference as R
 from .cache import PAGE, PagedCache
 from .scratch import scratch
+from .functional import cpu_act_dtype
 
 BF16 = torch.bfloat16
 F32 = torch.float32
@@ -16,9 +17,11 @@ I32 = torch.int32
 
 
 # ---- metadata -------------------------------------------------------------------
-def token_maps(query_start: torch.Tensor, req_rows: torch.Tensor, start_pos: torch.Tensor, n_req: int, t_padded: int):
-    """-> (tok_req i32 [T], positions i64 [T], first_pos i32 [T], last_pos i32 [T]); padding tokens get
-    request -1 / position -1."""
+def token_maps(query_start: torch.Tensor, req_rows: torch.Tensor, start_pos: torch.Tensor, n_req: int, t_padded: int,
+               block_table: Optional[torch.Tensor] = None):
+    """-> (tok_req i32 [T], positions i64 [T], first_pos i32 [T], last_pos i32 [T][, slot_mapping i64 [T]]);
+    padding tokens get request -1 / position -1 / slot -1.  With a block table the destination slot of
+    every token's own row is returned as well."""
     dev = query_start.device
     if dev.type != "cuda":
         tok_req = torch.full((t_padded,), -1, dtype=I32)
@@ -31,14 +34,23 @@ def token_maps(query_start: torch.Tensor, req_rows: torch.Tensor, start_pos: tor
             positions[a:b] = int(start_pos[i]) + torch.arange(b - a)
             first[a:b] = int(start_pos[i])
             last[a:b] = int(start_pos[i]) + (b - a) - 1
-        return tok_req, positions, first, last
+        if block_table is None:
+            return tok_req, positions, first, last
+        sm = torch.full((t_padded,), -1, dtype=torch.int64)
+        ok = tok_req >= 0
+        if ok.any():
+            sm[ok] = _slots_from_bt(block_table, tok_req[ok].long(), positions[ok]).to(torch.int64)
+        return tok_req, positions, first, last, sm
     tok_req = scratch("meta.tok_req", (t_padded,), I32, dev)
     positions = scratch("meta.positions", (t_padded,), torch.int64, dev)
     first = scratch("meta.first", (t_padded,), I32, dev)
     last = scratch("meta.last", (t_padded,), I32, dev)
-    _lib.call("stk_token_maps", query_start, req_rows, start_pos, n_req, tok_req, positions, first, last, t_padded,
-              _lib.stream())
-    return tok_req, positions, first, last
+    sm = scratch("meta.slot_mapping", (t_padded,), torch.int64, dev) if block_table is not None else None
+    _lib.call("stk_token_maps", query_start, req_rows, start_pos, n_req, tok_req, positions, first, last, block_table,
+              block_table.stride(0) if block_table is not None else 0, sm, t_padded, _lib.stream())
+    if block_table is None:
+        return tok_req, positions, first, last
+    return tok_req, positions, first, last, sm
 
 
 def _slots_from_bt(block_table, req, p):
@@ -214,7 +226,7 @@ def sparse_mla(q: torch.Tensor, swa_cache: PagedCache, swa_slots: torch.Tensor, 
             rr = torch.cat(rows)[None]
             vv = torch.cat(valid)[None]
             out[i] = R.sparse_mla(q[i:i + 1], rr, vv, sink, scale)[0]
-        return out.to(BF16)
+        return out.to(cpu_act_dtype())
     max_rows = swa_slots.shape[1] + (topk_slots.shape[1] if topk_slots is not None else 0)
     n_splits = _lib.query("stk_sparse_mla_pick_splits", t, max_rows)
     ws = scratch("mla.partial", (t * n_splits * nh * (d + 2),), F32, q.device)

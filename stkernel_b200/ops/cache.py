@@ -21,6 +21,11 @@ from . import _lib
 from . import reference as R
 from .scratch import scratch
 
+
+def Fn_act():
+    from .functional import cpu_act_dtype
+    return cpu_act_dtype()
+
 BF16 = torch.bfloat16
 F32 = torch.float32
 FP8 = torch.float8_e4m3fn
@@ -154,7 +159,7 @@ def kv_gather_dequant(cache: PagedCache, slots: torch.Tensor) -> torch.Tensor:
     """slots [n] int64 -> rows [n, D] bf16 (zeros for slot < 0)."""
     n = slots.numel()
     if not cache.buf.is_cuda:
-        return cache.read_rows_cpu(slots)[0].to(BF16)
+        return cache.read_rows_cpu(slots)[0].to(Fn_act())
     out = torch.empty(n, cache.dim, dtype=BF16, device=cache.buf.device)
     _lib.call("stk_kv_gather_dequant", cache.buf, cache.page_stride, cache.data_bytes, 1 if cache.fp8 else 0, slots, out,
               n, cache.dim, cache.rope_dim, _lib.stream())
@@ -213,7 +218,7 @@ def compress_windows(kvs: torch.Tensor, ape: torch.Tensor, norm_w: torch.Tensor,
                 continue
             state[int(tok_req[i]), pos % ring] = kvs[i]
         return
-    _lib.call("stk_compress_windows", kvs, ape, norm_w, inv, positions, tok_req, tok_first_pos, tok_last_pos, state,
+    _lib.call("stk_compress_windows", kvs, kvs.stride(0), ape, norm_w, inv, positions, tok_req, tok_first_pos, tok_last_pos, state,
               block_table, block_table.stride(0), cache.buf, cache.page_stride, cache.data_bytes,
               1 if cache.fp8 else 0, 1 if cache.kind == "indexer" else 0, cache.num_slots, t, d, cache.rope_dim, ratio, c,
               ring, eps, _lib.status_buffer(), _lib.stream())
@@ -229,6 +234,6 @@ def indexer_q_prep(q: torch.Tensor, w: torch.Tensor, positions: torch.Tensor, in
         return (qq.to(FP8) if quantize else qq.to(BF16)), wf
     qo = torch.empty(t, ih, d, dtype=torch.uint8 if quantize else BF16, device=q.device)
     wo = torch.empty(t, ih, dtype=F32, device=q.device)
-    _lib.call("stk_indexer_q_prep", q, q.stride(0), w, positions, inv, qo, wo, t, ih, d, rope_dim, 1 if quantize else 0,
+    _lib.call("stk_indexer_q_prep", q, q.stride(0), w, w.stride(0), positions, inv, qo, wo, t, ih, d, rope_dim, 1 if quantize else 0,
               _lib.stream())
     return (qo.view(FP8) if quantize else qo), wo

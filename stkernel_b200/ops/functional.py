@@ -21,6 +21,17 @@ BF16 = torch.bfloat16
 F32 = torch.float32
 FP8 = torch.float8_e4m3fn
 
+_CPU_ACT = [torch.bfloat16]
+
+
+def set_cpu_act_dtype(dtype: torch.dtype) -> None:
+    """Activation dtype of the CPU reference path (bf16 mirrors the GPU; fp32 for exact oracle checks)."""
+    _CPU_ACT[0] = dtype
+
+
+def cpu_act_dtype() -> torch.dtype:
+    return _CPU_ACT[0]
+
 
 # ----------------------------------------------------------------------------
 # dense linear
@@ -96,9 +107,9 @@ def linear(x, lw: LinearWeight, out: Optional[torch.Tensor] = None, out_dtype=BF
                 xa = quant_act(x)
             xf = R.dequant_fp8_group128_act(xa.q, xa.scale.t()[:t])
         else:
-            xf = (x if xa is None else R.dequant_fp8_group128_act(xa.q, xa.scale.t()[:t])).to(BF16).to(F32)
+            xf = (x if xa is None else R.dequant_fp8_group128_act(xa.q, xa.scale.t()[:t])).to(cpu_act_dtype()).to(F32)
         y = xf @ lw.dequant().t()
-        y = y.to(out_dtype)
+        y = y.to(out_dtype if out_dtype != BF16 else cpu_act_dtype())
         if out is not None:
             out.copy_(y)
             return out
@@ -132,7 +143,7 @@ def rms_norm(x: torch.Tensor, w: Optional[torch.Tensor], eps: float, quant: bool
     """bf16 RMSNorm; with quant=True also returns the fp8 QuantAct of the normed row."""
     t, h = x.shape
     if not x.is_cuda:
-        y = R.rms_norm(x, w, eps).to(BF16)
+        y = R.rms_norm(x, w, eps).to(cpu_act_dtype())
         return (y, quant_act(y)) if quant else y
     out = torch.empty(t, h, dtype=BF16, device=x.device)
     q = s = None
@@ -149,7 +160,7 @@ def rms_norm_pair(x0, w0, x1, w1, eps: float, quant0: bool = False, tag: str = "
     """Two independent RMSNorms in one launch (q_lora row and kv row)."""
     t = x0.shape[0]
     if not x0.is_cuda:
-        y0, y1 = R.rms_norm(x0, w0, eps).to(BF16), R.rms_norm(x1, w1, eps).to(BF16)
+        y0, y1 = R.rms_norm(x0, w0, eps).to(cpu_act_dtype()), R.rms_norm(x1, w1, eps).to(cpu_act_dtype())
         return (y0, y1, quant_act(y0)) if quant0 else (y0, y1)
     h0, h1 = x0.shape[1], x1.shape[1]
     o0 = torch.empty(t, h0, dtype=BF16, device=x0.device)
@@ -168,7 +179,7 @@ def swiglu_clamp(gu: torch.Tensor, limit: float, quant: bool = False, tag: str =
     t, two_i = gu.shape
     i = two_i // 2
     if not gu.is_cuda:
-        a = R.swiglu_clamp(gu[:, :i], gu[:, i:], limit).to(BF16)
+        a = R.swiglu_clamp(gu[:, :i], gu[:, i:], limit).to(cpu_act_dtype())
         return (a, quant_act(a)) if quant else a
     act = torch.empty(t, i, dtype=BF16, device=gu.device)
     q = s = None
@@ -190,7 +201,7 @@ def embed_hc(ids: torch.Tensor, embed: torch.Tensor, hc: int, vocab: int, vocab_
         local = ids.long() - vocab_start
         ok = (local >= 0) & (local < embed.shape[0])
         x = torch.where(ok[:, None], embed[local.clamp(0, embed.shape[0] - 1)], torch.zeros_like(embed[:1]))
-        return x[:, None, :].repeat(1, hc, 1).to(BF16)
+        return x[:, None, :].repeat(1, hc, 1).to(cpu_act_dtype())
     out = torch.empty(t, hc, h, dtype=BF16, device=ids.device)
     _lib.call("stk_embed_hc", ids, embed, out, t, h, hc, vocab, vocab_start, vend, _lib.status_buffer(), _lib.stream())
     return out
@@ -206,7 +217,7 @@ def mhc_pre(residual: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale:
     t, hc, h = residual.shape
     if not residual.is_cuda:
         y, post, comb = R.mhc_pre(residual, fn, base, scale, norm_w, rms_eps, hc_eps, iters, round_bf16=True)
-        y = y.to(BF16)
+        y = y.to(cpu_act_dtype())
         res = (y, post, comb.reshape(t, hc * hc))
         return res + (quant_act(y),) if quant else res
     dev = residual.device
@@ -230,7 +241,7 @@ def mhc_pre(residual: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale:
 def mhc_post(x: torch.Tensor, residual: torch.Tensor, post: torch.Tensor, comb: torch.Tensor) -> torch.Tensor:
     t, hc, h = residual.shape
     if not residual.is_cuda:
-        return R.mhc_post(x, residual, post, comb.reshape(t, hc, hc)).to(BF16)
+        return R.mhc_post(x, residual, post, comb.reshape(t, hc, hc)).to(cpu_act_dtype())
     out = torch.empty_like(residual)
     _lib.call("stk_mhc_post", x, residual, post, comb, out, t, h, hc, _lib.stream())
     return out
@@ -240,7 +251,7 @@ def hc_head(residual: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale:
             hc_eps: float) -> torch.Tensor:
     t, hc, h = residual.shape
     if not residual.is_cuda:
-        return R.hc_head(residual, fn, base, scale, rms_eps, hc_eps).to(BF16)
+        return R.hc_head(residual, fn, base, scale, rms_eps, hc_eps).to(cpu_act_dtype())
     dev = residual.device
     splits = _lib.query("stk_mhc_pick_splits", t, hc * h)
     partial = scratch("mhc.partial", (splits * t * (hc + 1),), F32, dev)
@@ -267,7 +278,7 @@ def q_norm_rope(q: torch.Tensor, positions: torch.Tensor, inv: torch.Tensor, rop
         ang = positions.to(F32)[:, None] * inv[None, :]
         cos, sin = torch.cos(ang), torch.sin(ang)
         qf = torch.cat([qf[..., :d - rope_dim], R.apply_rope_interleaved(qf[..., d - rope_dim:], cos, sin, inverse)], -1)
-        return qf.to(BF16)
+        return qf.to(cpu_act_dtype())
     assert q.stride(2) == 1 and q.stride(1) == d
     _lib.call("stk_q_norm_rope", q, q.stride(0), positions, inv, t, nh, d, rope_dim, eps, 1 if norm else 0,
               1 if inverse else 0, _lib.stream())

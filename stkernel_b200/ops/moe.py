@@ -9,6 +9,7 @@ import torch
 from . import _lib
 from . import reference as R
 from .scratch import scratch
+from .functional import cpu_act_dtype
 
 BF16 = torch.bfloat16
 F32 = torch.float32
@@ -89,10 +90,10 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, ew: E
     k = ids.shape[1]
     if not x.is_cuda or not ew.is_fp4:
         w13, w2 = ew.dequant()
-        out = R.moe_experts(x.to(BF16), ids, weights, w13, w2, limit, ew.expert_start)
+        out = R.moe_experts(x.to(cpu_act_dtype()), ids, weights, w13, w2, limit, ew.expert_start)
         if shared is not None:
             out = out + shared.to(F32)
-        return out.to(BF16)
+        return out.to(cpu_act_dtype())
     dev = x.device
     n_pairs = t * k
     inter = ew.w2.shape[2] * 2

@@ -1,0 +1,347 @@
+"""The serving engine: continuous batching with chunked prefill over the paged caches.
+
+One `Engine` per rank (one process per GPU).  `step()` schedules decode rows first,
+then prefill chunks up to the token budget (the reference's serving mode:
+4096-token chunks, decode-first ordering, launchers/start-hy4-tp4.sh:370-391), builds
+the per-step metadata on the device, runs the model, samples with seeded Gumbel
+noise keyed by (seed, position) and appends the new tokens.  Pure-decode steps
+replay a CUDA graph per batch-size bucket.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..config import EngineConfig
+from ..models.dsv4 import DSV4Model, ModelWeights, StepMeta
+from ..ops import attention as A
+from ..ops import sampling as S
+from ..ops.cache import PAGE
+from .kv import KVManager, OutOfPages, size_pools
+from .metrics import Metrics
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 0.0
+    seed: int = 0
+    max_tokens: int = 16
+    min_tokens: int = 0
+    ignore_eos: bool = False
+    eos_token_id: Optional[int] = None
+
+
+@dataclass
+class Request:
+    req_id: int
+    prompt: List[int]
+    params: SamplingParams
+    row: int = -1
+    num_computed: int = 0               # tokens whose KV is in the cache
+    output: List[int] = field(default_factory=list)
+    finished: bool = False
+    arrival: float = field(default_factory=time.time)
+    first_token_time: Optional[float] = None
+
+    @property
+    def tokens(self) -> List[int]:
+        return self.prompt + self.output
+
+    @property
+    def total_len(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+    @property
+    def in_prefill(self) -> bool:
+        return self.num_computed < len(self.prompt)
+
+
+@dataclass
+class ScheduledSeq:
+    req: Request
+    start: int          # first position computed this step
+    n: int              # tokens computed this step
+    samples: bool       # the last token of this span produces a new token
+
+
+class Scheduler:
+    """Decode-first continuous batching with chunked prefill and page-aware admission."""
+
+    def __init__(self, cfg: EngineConfig, kv: KVManager):
+        self.cfg = cfg
+        self.kv = kv
+        self.waiting: List[Request] = []
+        self.running: List[Request] = []
+
+    def add(self, req: Request) -> None:
+        self.waiting.append(req)
+
+    def schedule(self) -> List[ScheduledSeq]:
+        sc = self.cfg.sched
+        budget = sc.max_num_batched_tokens
+        out: List[ScheduledSeq] = []
+        # 1) decode rows first
+        for r in self.running:
+            if r.finished or r.in_prefill:
+                continue
+            if budget <= 0:
+                break
+            out.append(ScheduledSeq(r, r.num_computed, 1, True))
+            budget -= 1
+        # 2) running prefills continue, chunked
+        for r in self.running:
+            if r.finished or not r.in_prefill or budget <= 0:
+                continue
+            n = min(budget, len(r.prompt) - r.num_computed)
+            out.append(ScheduledSeq(r, r.num_computed, n, r.num_computed + n == len(r.prompt)))
+            budget -= n
+        # 3) admit waiting requests while rows, pages and budget allow
+        while self.waiting and budget > 0 and len(self.running) < sc.max_num_seqs:
+            r = self.waiting[0]
+            ctx = min(len(r.prompt) + r.params.max_tokens, sc.max_model_len)
+            if not self.kv.can_admit(min(budget, len(r.prompt)), ctx):
+                break
+            self.waiting.pop(0)
+            r.row = self.kv.alloc_row()
+            self.running.append(r)
+            n = min(budget, len(r.prompt))
+            out.append(ScheduledSeq(r, 0, n, n == len(r.prompt)))
+            budget -= n
+        return out
+
+    def retire(self, req: Request) -> None:
+        req.finished = True
+        self.kv.free_row(req.row)
+        self.running.remove(req)
+
+    @property
+    def num_running(self) -> int:
+        return len(self.running)
+
+    @property
+    def num_waiting(self) -> int:
+        return len(self.waiting)
+
+
+class StepBuffers:
+    """Pinned host staging + fixed-address device tensors for the step description."""
+
+    def __init__(self, max_tokens: int, max_reqs: int, device):
+        pin = torch.device(device).type == "cuda"
+        mk = lambda n, dt: torch.zeros(n, dtype=dt, pin_memory=pin)
+        self.h_tokens = mk(max_tokens, torch.int64)
+        self.h_qstart = mk(max_reqs + 1, torch.int32)
+        self.h_rows = mk(max_reqs, torch.int32)
+        self.h_start = mk(max_reqs, torch.int32)
+        self.h_logit_rows = mk(max_reqs, torch.int64)
+        self.h_temp = mk(max_reqs, torch.float32)
+        self.h_seed = mk(max_reqs, torch.int64)
+        self.h_pos = mk(max_reqs, torch.int64)
+        dv = lambda h: torch.zeros_like(h, device=device)
+        self.d_tokens, self.d_qstart, self.d_rows, self.d_start = dv(self.h_tokens), dv(self.h_qstart), dv(self.h_rows), dv(self.h_start)
+        self.d_logit_rows, self.d_temp, self.d_seed, self.d_pos = dv(self.h_logit_rows), dv(self.h_temp), dv(self.h_seed), dv(self.h_pos)
+        self.h_out = mk(max_reqs, torch.int64)
+
+    def h2d_bytes(self, t: int, n: int) -> int:
+        return t * 8 + (n + 1) * 4 + n * 4 * 2 + n * 8 * 3 + n * 4
+
+
+class Engine:
+    def __init__(self, cfg: EngineConfig, weights: ModelWeights, device, comm=None, tp_rank: int = 0,
+                 max_context: Optional[int] = None):
+        cfg.validate()
+        self.cfg = cfg
+        self.device = torch.device(device)
+        sc = cfg.sched
+        ctx = max_context or sc.max_model_len
+        pools = size_pools(cfg.model, sc.max_num_seqs, ctx, sc.max_num_batched_tokens)
+        if cfg.cache.num_pages is not None:
+            pools["swa_pages"] = max(pools["swa_pages"], cfg.cache.num_pages)
+        has_c128 = any(cfg.model.layer_kind(i) == "c128a" for i in range(cfg.model.num_hidden_layers))
+        self.kv = KVManager(cfg.model, self.device, sc.max_num_seqs, ctx + 64, pools["swa_pages"], pools["c4_pages"],
+                            pools["c128_pages"] if has_c128 else 0, sc.max_num_batched_tokens)
+        self.model = DSV4Model(cfg.model, weights, self.kv, comm, tp_rank, cfg.parallel.tp_size)
+        self.sched = Scheduler(cfg, self.kv)
+        self.buf = StepBuffers(sc.max_num_batched_tokens + sc.max_num_seqs, sc.max_num_seqs, self.device)
+        self.metrics = Metrics()
+        self._next_id = 0
+        self.requests: Dict[int, Request] = {}
+        self._graphs: Dict[Tuple[int, int], "DecodeGraph"] = {}
+        self.use_graphs = self.device.type == "cuda" and sc.graph_cap > 0
+        self.h2d_bytes_last = 0
+        self.d2h_bytes_last = 0
+
+    # ---- public API ------------------------------------------------------------
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
+        rid = self._next_id
+        self._next_id += 1
+        req = Request(rid, list(prompt), params or SamplingParams())
+        if len(req.prompt) + req.params.max_tokens > self.cfg.sched.max_model_len + 64:
+            raise ValueError("request exceeds max_model_len")
+        self.requests[rid] = req
+        self.sched.add(req)
+        self.metrics.requests_total += 1
+        return rid
+
+    def has_work(self) -> bool:
+        return bool(self.sched.waiting or self.sched.running)
+
+    def generate(self, prompts: Sequence[Sequence[int]], params: Optional[SamplingParams] = None) -> List[List[int]]:
+        ids = [self.add_request(p, params) for p in prompts]
+        while self.has_work():
+            self.step()
+        return [self.requests[i].output for i in ids]
+
+    # ---- one step -----------------------------------------------------------------
+    def _stage(self, seqs: List[ScheduledSeq]) -> Tuple[int, int, int]:
+        """Fill the pinned staging buffers; returns (T, n_req, n_samples)."""
+        b = self.buf
+        t = 0
+        ns = 0
+        for i, s in enumerate(seqs):
+            r = s.req
+            self.kv.prepare(r.row, s.start, s.n)
+            toks = r.tokens[s.start:s.start + s.n]
+            b.h_tokens[t:t + s.n] = torch.tensor(toks, dtype=torch.int64)
+            b.h_qstart[i] = t
+            b.h_rows[i] = r.row
+            b.h_start[i] = s.start
+            t += s.n
+            if s.samples:
+                b.h_logit_rows[ns] = t - 1
+                b.h_temp[ns] = r.params.temperature
+                b.h_seed[ns] = r.params.seed
+                b.h_pos[ns] = s.start + s.n          # position of the token being sampled
+                ns += 1
+        b.h_qstart[len(seqs)] = t
+        return t, len(seqs), ns
+
+    def _upload(self, t: int, n: int, ns: int) -> None:
+        b = self.buf
+        nb = True
+        b.d_tokens[:t].copy_(b.h_tokens[:t], non_blocking=nb)
+        b.d_qstart[:n + 1].copy_(b.h_qstart[:n + 1], non_blocking=nb)
+        b.d_rows[:n].copy_(b.h_rows[:n], non_blocking=nb)
+        b.d_start[:n].copy_(b.h_start[:n], non_blocking=nb)
+        if ns:
+            b.d_logit_rows[:ns].copy_(b.h_logit_rows[:ns], non_blocking=nb)
+            b.d_temp[:ns].copy_(b.h_temp[:ns], non_blocking=nb)
+            b.d_seed[:ns].copy_(b.h_seed[:ns], non_blocking=nb)
+            b.d_pos[:ns].copy_(b.h_pos[:ns], non_blocking=nb)
+        self.kv.sync()
+        self.h2d_bytes_last = b.h2d_bytes(t, n)
+
+    def _build_meta(self, t_pad: int, n_req: int, max_comp_rows: int) -> StepMeta:
+        b = self.buf
+        cfg = self.cfg.model
+        tok_req, positions, first, last, sm = A.token_maps(b.d_qstart, b.d_rows, b.d_start, n_req, t_pad,
+                                                           self.kv.swa.table_dev)
+        swa_slots, swa_lens = A.swa_indices(positions, tok_req, self.kv.swa.table_dev, cfg.sliding_window)
+        return StepMeta(b.d_tokens[:t_pad], tok_req, positions, first, last, sm, swa_slots, swa_lens, max_comp_rows)
+
+    def _run_model(self, t_pad: int, n_req: int, ns: int, max_comp_rows: int) -> torch.Tensor:
+        """-> sampled tokens [ns] (device)."""
+        b = self.buf
+        meta = self._build_meta(t_pad, n_req, max_comp_rows)
+        logits = self.model.forward(meta, b.d_logit_rows[:ns])
+        toks, _ = S.gumbel_argmax(logits, b.d_temp[:ns], b.d_seed[:ns], b.d_pos[:ns])
+        return toks
+
+    def step(self) -> List[Tuple[int, int]]:
+        """Run one scheduler step.  Returns [(req_id, new_token)] for requests that produced a token."""
+        seqs = self.sched.schedule()
+        if not seqs:
+            return []
+        t, n_req, ns = self._stage(seqs)
+        self._upload(t, n_req, ns)
+        max_end = max(s.start + s.n for s in seqs)
+        max_comp_rows = max(1, max_end // 4)
+        pure_decode = all(s.n == 1 and s.samples for s in seqs)
+        if ns == 0:
+            # prefill chunk that samples nothing: run the body only
+            meta = self._build_meta(t, n_req, max_comp_rows)
+            self.model.forward_hidden(meta)
+            toks_dev = None
+        elif self.use_graphs and pure_decode and n_req <= self.cfg.sched.graph_cap:
+            toks_dev = self._decode_graph(n_req, max_comp_rows).replay()
+        else:
+            toks_dev = self._run_model(t, n_req, ns, max_comp_rows)
+        out: List[Tuple[int, int]] = []
+        new_tokens: List[int] = []
+        if toks_dev is not None:
+            if self.device.type == "cuda":
+                self.buf.h_out[:ns].copy_(toks_dev[:ns], non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                new_tokens = self.buf.h_out[:ns].tolist()
+            else:
+                new_tokens = toks_dev[:ns].tolist()
+            self.d2h_bytes_last = ns * 8
+        k = 0
+        now = time.time()
+        for s in seqs:
+            r = s.req
+            r.num_computed = s.start + s.n
+            if s.start < len(r.prompt):
+                self.metrics.prompt_tokens_total += s.n
+            if s.samples:
+                tok = new_tokens[k]
+                k += 1
+                r.output.append(tok)
+                if r.first_token_time is None:
+                    r.first_token_time = now
+                self.metrics.generation_tokens_total += 1
+                out.append((r.req_id, tok))
+                p = r.params
+                hit_eos = (p.eos_token_id is not None and tok == p.eos_token_id and not p.ignore_eos
+                           and len(r.output) >= p.min_tokens)
+                if len(r.output) >= p.max_tokens or hit_eos or r.total_len >= self.cfg.sched.max_model_len:
+                    self.sched.retire(r)
+                    self.metrics.requests_finished += 1
+        self.metrics.num_requests_running = self.sched.num_running
+        self.metrics.num_requests_waiting = self.sched.num_waiting
+        self.metrics.steps_total += 1
+        return out
+
+    # ---- CUDA graphs -----------------------------------------------------------------
+    def _decode_graph(self, n_req: int, max_comp_rows: int) -> "DecodeGraph":
+        bucket = 1
+        while bucket < n_req:
+            bucket *= 2
+        rows_bucket = 2048
+        while rows_bucket < max_comp_rows:
+            rows_bucket *= 2
+        key = (bucket, rows_bucket)
+        if n_req < bucket:
+            # padding rows: empty query ranges => request -1, nothing is read or written for them
+            self.buf.d_qstart[n_req + 1:bucket + 1].fill_(n_req)
+        g = self._graphs.get(key)
+        if g is None:
+            g = DecodeGraph(self, bucket, rows_bucket)
+            self._graphs[key] = g
+        return g
+
+
+class DecodeGraph:
+    """A captured pure-decode step for `bucket` rows (token i belongs to request i)."""
+
+    def __init__(self, eng: Engine, bucket: int, rows_bucket: int):
+        self.eng = eng
+        self.bucket = bucket
+        # warm-up outside capture (allocates scratch, configures kernels), then capture
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.out = eng._run_model(bucket, bucket, bucket, rows_bucket)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.out = eng._run_model(bucket, bucket, bucket, rows_bucket)
+
+    def replay(self) -> torch.Tensor:
+        self.graph.replay()
+        return self.out

@@ -1,0 +1,101 @@
+"""The paged, batched engine against the naive oracle on the tiny CPU config."""
+import pytest
+import torch
+
+from stkernel_b200.config import CacheConfig, EngineConfig, SchedulerConfig, tiny_config
+from stkernel_b200.models.dsv4 import DictSource, build_model_weights
+from stkernel_b200.models.dsv4_oracle import OracleModel, index_cache_computes
+from stkernel_b200.models.weights import init_random_weights
+from stkernel_b200.ops import functional as Fn
+from stkernel_b200.runtime.engine import Engine, SamplingParams
+
+
+@pytest.fixture(autouse=True)
+def fp32_acts():
+    Fn.set_cpu_act_dtype(torch.float32)
+    yield
+    Fn.set_cpu_act_dtype(torch.bfloat16)
+
+
+def close(got, ref, tol=5e-3, frac=0.9):
+    """The layer input is rounded to bf16 by design, so a 1e-6 difference upstream can move an
+    element by one bf16 ulp and, rarely, flip a router or top-k choice for one token.  Require
+    most positions to agree tightly and the whole tensor to agree in norm."""
+    err = (got.float() - ref).abs().amax(-1)
+    assert (err < tol).float().mean().item() >= frac, err
+    assert ((got.float() - ref).norm() / ref.norm()).item() < 5e-2
+
+
+def make_engine(cfg, w, chunk=4096, seqs=4):
+    ec = EngineConfig(model=cfg, sched=SchedulerConfig(max_model_len=512, max_num_seqs=seqs, max_num_batched_tokens=chunk,
+                                                       graph_cap=0)).validate()
+    weights = build_model_weights(cfg, DictSource(w), "cpu")
+    return Engine(ec, weights, "cpu", max_context=512)
+
+
+def test_index_cache_rule():
+    cfg = tiny_config(num_hidden_layers=8, compress_ratios=(4, 0, 4, 4, 0, 4, 4, 4), index_topk_freq=3)
+    flags = [index_cache_computes(cfg, i) for i in range(8)]
+    assert flags == [True, False, False, False, False, True, False, False]
+    cfg1 = tiny_config(num_hidden_layers=3, compress_ratios=(0, 4, 4), index_topk_freq=7)
+    assert [index_cache_computes(cfg1, i) for i in range(3)] == [False, True, False]   # first C4A always computes
+
+
+@pytest.mark.parametrize("chunk", [4096, 24])
+def test_prefill_and_greedy_decode_match_oracle(chunk):
+    torch.manual_seed(0)
+    cfg = tiny_config()
+    w = init_random_weights(cfg, seed=0)
+    oracle = OracleModel(cfg, w)
+    eng = make_engine(cfg, w, chunk=chunk)
+    prompts = [torch.randint(0, cfg.vocab_size, (64,)).tolist() for _ in range(2)]
+    steps = 32 if chunk == 4096 else 8
+    outs = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=steps))
+    for p, o in zip(prompts, outs):
+        ref_ids, ref_logits = oracle.greedy_decode(torch.tensor(p), steps)
+        assert o == ref_ids.tolist()
+
+
+def test_logits_match_oracle_mixed_batch():
+    torch.manual_seed(1)
+    cfg = tiny_config(num_hidden_layers=3, compress_ratios=(4, 0, 4), index_topk_freq=2)
+    w = init_random_weights(cfg, seed=3)
+    oracle = OracleModel(cfg, w)
+    eng = make_engine(cfg, w)
+    a = torch.randint(0, cfg.vocab_size, (50,))
+    b = torch.randint(0, cfg.vocab_size, (37,))
+    # drive the model directly through two ragged steps to compare full logits
+    from stkernel_b200.runtime.engine import Request, ScheduledSeq
+    ra, rb = Request(0, a.tolist(), SamplingParams()), Request(1, b.tolist(), SamplingParams())
+    ra.row, rb.row = eng.kv.alloc_row(), eng.kv.alloc_row()
+    seqs = [ScheduledSeq(ra, 0, 30, False), ScheduledSeq(rb, 0, 37, True)]
+    t, n, ns = eng._stage(seqs)
+    eng._upload(t, n, ns)
+    meta = eng._build_meta(t, n, 16)
+    lg1 = eng.model.forward(meta)
+    seqs = [ScheduledSeq(ra, 30, 20, True)]
+    t, n, ns = eng._stage(seqs)
+    eng._upload(t, n, ns)
+    meta = eng._build_meta(t, n, 16)
+    lg2 = eng.model.forward(meta)
+    ref_a, ref_b = oracle.logits(a), oracle.logits(b)
+    close(lg1[:30], ref_a[:30])
+    close(lg1[30:], ref_b)
+    close(lg2, ref_a[30:])
+
+
+def test_quantised_storage_matches_quant_aware_oracle():
+    torch.manual_seed(2)
+    cfg = tiny_config(dense_dtype="bf16", kv_cache_dtype="fp8_ds_mla", expert_dtype="nvfp4")
+    w = init_random_weights(cfg, seed=5)
+    oracle = OracleModel(cfg, w)
+    eng = make_engine(cfg, w)
+    p = torch.randint(0, cfg.vocab_size, (48,))
+    from stkernel_b200.runtime.engine import Request, ScheduledSeq
+    r = Request(0, p.tolist(), SamplingParams())
+    r.row = eng.kv.alloc_row()
+    t, n, ns = eng._stage([ScheduledSeq(r, 0, 48, True)])
+    eng._upload(t, n, ns)
+    lg = eng.model.forward(eng._build_meta(t, n, 16))
+    ref = oracle.logits(p)
+    close(lg, ref, tol=1e-2)
