@@ -1,0 +1,138 @@
+#!/usr/bin/env python
+"""Headline benchmark: DeepSeek-V4-Flash-shaped decode (and prefill) on N B200s of one node.
+
+    python bench.py --gpus N --steps K --warmup W            # this engine
+    python bench.py --impl reference ...                     # the reference arm
+
+Metric: decode tokens/s at concurrency 1 over a 32K-token context (BASELINE.json's first
+metric; the reference's published C=1 figure is 70.7 tok/s on 4x GB10).  The model is the
+Flash shape with 6*N layers (48 at N=8), tensor/expert parallel over the N ranks, random-init
+weights and uniform-random token ids.  One step = one full decode step of the whole model
+(all layers, LM head, sampling).  `value` is timed on the device with CUDA events around K
+steps (per-step inputs uploaded from pinned memory, no host read-back); `e2e` times K calls
+of `Engine.step()` — the public API — which add the device->host read of the sampled token
+and feed it back.  `extra` carries decode at C=64 and 32K-context prefill throughput.
+Every step streams > 1.5 GB of weights, far more than the 126 MB L2, so no explicit flush.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BASELINE_DECODE_C1 = 70.7      # tok/s, reference with one-shot all-reduce, 4x GB10
+
+
+def reference_arm(args) -> None:
+    # The reference is an overlay of ~20 files bind-mounted over a vLLM fork that ships only
+    # inside a Docker image; it has no setup.py/pyproject and cannot be installed or run here.
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "reference is not installable (no setup.py/pyproject; it is an overlay on a closed "
+                      "vLLM Docker image whose engine and kernels are not in the source tree)"}))
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self._stop = threading.Event()
+        self._thr = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                parts = [p.strip() for p in out.strip().split(",")]
+                if len(parts) >= 7:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._thr.join(timeout=6)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = sorted(float(s[0]) for s in self.samples)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[3 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(self.samples[0][1]), "reasons": reasons,
+                "samples": len(self.samples), "power_w_max": max(float(s[2]) for s in self.samples)}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--ctx", type=int, default=32768)
+    ap.add_argument("--layers-per-gpu", type=int, default=6)
+    ap.add_argument("--skip-extra", action="store_true")
+    ap.add_argument("--no-fused", action="store_true", help="NCCL-after-GEMM baseline collectives")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    from stkernel_b200.bench.decode_bench import run_bench
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    warm = max(3, args.warmup)
+    with ClockSampler(local) as clocks:
+        res = run_bench(n_gpus=world, rank=rank, local=local, steps=args.steps, warmup=warm, ctx=args.ctx,
+                        layers_per_gpu=args.layers_per_gpu, extra=not args.skip_extra, fused=not args.no_fused)
+    if rank == 0:
+        line = {
+            "metric": "decode_tok_s_c1_ctx32k", "value": res["decode_c1_tok_s"], "unit": "tok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warm, "ms_per_step": res["decode_c1_ms"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": res["decode_c1_tok_s"] / BASELINE_DECODE_C1, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"model": f"DeepSeek-V4-Flash-shaped, {res['layers']} layers (6 per GPU), fp8 dense / nvfp4 "
+                                "experts / fp8_ds_mla KV, random-init", "global_batch": 1, "seq_len": args.ctx,
+                       "parallelism": f"tp{world}+ep{world}", "l2": "inputs (weights streamed per step) exceed L2",
+                       "context_fill": res["context_fill"]},
+            "clocks": clocks.summary(),
+            "e2e": {"value": res["e2e_tok_s"], "unit": "tok/s", "h2d_bytes_per_step": res["h2d_bytes"],
+                    "d2h_bytes_per_step": res["d2h_bytes"], "ms_per_step": res["e2e_ms"]},
+            "gpu_launches": res["gpu_launches"],
+            "extra": res.get("extra", {}),
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -50,6 +50,15 @@ class Request:
     def tokens(self) -> List[int]:
         return self.prompt + self.output
 
+    def token_span(self, start: int, n: int) -> List[int]:
+        """tokens[start:start+n] without concatenating the prompt and the output."""
+        lp = len(self.prompt)
+        if start >= lp:
+            return self.output[start - lp:start - lp + n]
+        if start + n <= lp:
+            return self.prompt[start:start + n]
+        return self.prompt[start:] + self.output[:start + n - lp]
+
     @property
     def total_len(self) -> int:
         return len(self.prompt) + len(self.output)
@@ -144,6 +153,11 @@ class StepBuffers:
         self.d_tokens, self.d_qstart, self.d_rows, self.d_start = dv(self.h_tokens), dv(self.h_qstart), dv(self.h_rows), dv(self.h_start)
         self.d_logit_rows, self.d_temp, self.d_seed, self.d_pos = dv(self.h_logit_rows), dv(self.h_temp), dv(self.h_seed), dv(self.h_pos)
         self.h_out = mk(max_reqs, torch.int64)
+        # numpy views of the pinned staging buffers (cheap element writes from Python)
+        self.n_tokens, self.n_qstart, self.n_rows, self.n_start = (self.h_tokens.numpy(), self.h_qstart.numpy(),
+                                                                   self.h_rows.numpy(), self.h_start.numpy())
+        self.n_logit_rows, self.n_temp, self.n_seed, self.n_pos = (self.h_logit_rows.numpy(), self.h_temp.numpy(),
+                                                                   self.h_seed.numpy(), self.h_pos.numpy())
 
     def h2d_bytes(self, t: int, n: int) -> int:
         return t * 8 + (n + 1) * 4 + n * 4 * 2 + n * 8 * 3 + n * 4
@@ -204,19 +218,18 @@ class Engine:
         for i, s in enumerate(seqs):
             r = s.req
             self.kv.prepare(r.row, s.start, s.n)
-            toks = r.tokens[s.start:s.start + s.n]
-            b.h_tokens[t:t + s.n] = torch.tensor(toks, dtype=torch.int64)
-            b.h_qstart[i] = t
-            b.h_rows[i] = r.row
-            b.h_start[i] = s.start
+            b.n_tokens[t:t + s.n] = r.token_span(s.start, s.n)
+            b.n_qstart[i] = t
+            b.n_rows[i] = r.row
+            b.n_start[i] = s.start
             t += s.n
             if s.samples:
-                b.h_logit_rows[ns] = t - 1
-                b.h_temp[ns] = r.params.temperature
-                b.h_seed[ns] = r.params.seed
-                b.h_pos[ns] = s.start + s.n          # position of the token being sampled
+                b.n_logit_rows[ns] = t - 1
+                b.n_temp[ns] = r.params.temperature
+                b.n_seed[ns] = r.params.seed
+                b.n_pos[ns] = s.start + s.n          # position of the token being sampled
                 ns += 1
-        b.h_qstart[len(seqs)] = t
+        b.n_qstart[len(seqs)] = t
         return t, len(seqs), ns
 
     def _upload(self, t: int, n: int, ns: int) -> None:
@@ -250,8 +263,11 @@ class Engine:
         toks, _ = S.gumbel_argmax(logits, b.d_temp[:ns], b.d_seed[:ns], b.d_pos[:ns])
         return toks
 
-    def step(self) -> List[Tuple[int, int]]:
-        """Run one scheduler step.  Returns [(req_id, new_token)] for requests that produced a token."""
+    def step(self, forced: Optional[Sequence[int]] = None) -> List[Tuple[int, int]]:
+        """Run one scheduler step.  Returns [(req_id, new_token)] for requests that produced a token.
+
+        `forced` (benchmarking / teacher forcing): use these tokens as the sampled ones and skip the
+        device->host read, so consecutive steps queue on the device without a host round trip."""
         seqs = self.sched.schedule()
         if not seqs:
             return []
@@ -271,7 +287,10 @@ class Engine:
             toks_dev = self._run_model(t, n_req, ns, max_comp_rows)
         out: List[Tuple[int, int]] = []
         new_tokens: List[int] = []
-        if toks_dev is not None:
+        if toks_dev is not None and forced is not None:
+            new_tokens = list(forced)[:ns]
+            self.d2h_bytes_last = 0
+        elif toks_dev is not None:
             if self.device.type == "cuda":
                 self.buf.h_out[:ns].copy_(toks_dev[:ns], non_blocking=True)
                 torch.cuda.current_stream().synchronize()
@@ -338,10 +357,15 @@ class DecodeGraph:
                 self.out = eng._run_model(bucket, bucket, bucket, rows_bucket)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        from ..ops import _lib
+        before = _lib.launch_count
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
             self.out = eng._run_model(bucket, bucket, bucket, rows_bucket)
+        self.launches_per_replay = _lib.launch_count - before
 
     def replay(self) -> torch.Tensor:
+        from ..ops import _lib
         self.graph.replay()
+        _lib.launch_count += self.launches_per_replay
         return self.out

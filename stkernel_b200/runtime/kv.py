@@ -51,37 +51,59 @@ class GroupTable:
         self.table_host = torch.full((self.max_requests, self.max_pages_per_req), -1, dtype=torch.int32)
         if self.device.type == "cuda":
             self.table_host = self.table_host.pin_memory()
+        self.table_np = self.table_host.numpy()          # shares memory with the pinned tensor
         self.table_dev = torch.full((self.max_requests, self.max_pages_per_req), -1, dtype=torch.int32,
                                     device=self.device)
         self.free = list(range(self.num_pages - 1, -1, -1))
+        # resident logical pages of each row form one interval [lo, hi)
+        self.lo = [0] * self.max_requests
+        self.hi = [0] * self.max_requests
+        self.dirty_rows = set()
 
     def ensure(self, row: int, first_logical: int, last_logical: int) -> None:
-        """Make logical pages [first, last] of request `row` resident."""
+        """Make logical pages [first, last] of request `row` resident (the resident set stays an interval)."""
         if last_logical >= self.max_pages_per_req:
             raise OutOfPages(f"{self.name}: request needs logical page {last_logical} >= {self.max_pages_per_req}")
-        t = self.table_host[row]
-        for lp in range(max(first_logical, 0), last_logical + 1):
-            if t[lp] < 0:
-                if not self.free:
-                    raise OutOfPages(f"{self.name}: pool of {self.num_pages} pages exhausted")
-                t[lp] = self.free.pop()
-                self.dirty = True
+        first_logical = max(first_logical, 0)
+        if self.hi[row] == self.lo[row]:
+            self.lo[row] = self.hi[row] = first_logical
+        t = self.table_np[row]
+        start = max(self.hi[row], first_logical)
+        if first_logical < self.lo[row]:
+            raise OutOfPages(f"{self.name}: page {first_logical} of row {row} was already released")
+        for lp in range(start, last_logical + 1):
+            if not self.free:
+                raise OutOfPages(f"{self.name}: pool of {self.num_pages} pages exhausted")
+            t[lp] = self.free.pop()
+        if last_logical + 1 > self.hi[row]:
+            self.hi[row] = last_logical + 1
+            self.dirty = True
+            self.dirty_rows.add(row)
 
     def release_before(self, row: int, logical: int) -> None:
-        t = self.table_host[row]
-        lo = min(max(logical, 0), self.max_pages_per_req)
-        held = (t[:lo] >= 0).nonzero().flatten().tolist()
-        for lp in held:
+        t = self.table_np[row]
+        end = min(max(logical, 0), self.hi[row])
+        for lp in range(self.lo[row], end):
             self.free.append(int(t[lp]))
             t[lp] = -1
+        if end > self.lo[row]:
+            self.lo[row] = end
             self.dirty = True
+            self.dirty_rows.add(row)
 
     def release_all(self, row: int) -> None:
         self.release_before(row, self.max_pages_per_req)
+        self.lo[row] = self.hi[row] = 0
 
     def sync(self) -> None:
+        """Upload the rows that changed since the last step."""
         if self.dirty:
-            self.table_dev.copy_(self.table_host, non_blocking=True)
+            if len(self.dirty_rows) * 4 >= self.max_requests:
+                self.table_dev.copy_(self.table_host, non_blocking=True)
+            else:
+                for r in self.dirty_rows:
+                    self.table_dev[r].copy_(self.table_host[r], non_blocking=True)
+            self.dirty_rows.clear()
             self.dirty = False
 
     @property
