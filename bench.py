@@ -128,10 +128,15 @@ def main() -> None:
             "gpu_launches": res["gpu_launches"],
             "extra": res.get("extra", {}),
         }
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
+        # Leave without tearing down NCCL: destroying the communicator while captured CUDA graphs still
+        # hold its kernels can block forever; every rank has finished its work at this barrier.
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -1,0 +1,124 @@
+"""Per-kernel device time of real (not serialised) steps, from the torch profiler (CUPTI).
+
+Prints the kernels of `--steps` steps sorted by total device time, the busy time as the union
+of kernel intervals (overlapping streams are not double counted) and the idle share — the same
+accounting as the reference's trace bucketing (bench/profile-step.py:166-281).
+
+    python -m stkernel_b200.bench.kernel_table --mode decode --conc 1 --graphs 1
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import re
+import tempfile
+from typing import Dict, List, Tuple
+
+import torch
+
+BUCKETS = [
+    ("comms", re.compile(r"nccl|allreduce|all_reduce|oneshot|twoshot|symm", re.I)),
+    ("moe", re.compile(r"expert|moe_|router", re.I)),
+    ("attn/indexer", re.compile(r"sparse_mla|indexer|topk|swa_indices|compress", re.I)),
+    ("gemm", re.compile(r"gemm", re.I)),
+    ("mhc", re.compile(r"mhc", re.I)),
+    ("norm/rope/quant", re.compile(r"rmsnorm|rope|quant|swiglu|embed", re.I)),
+    ("sampler", re.compile(r"gumbel|markov|accept", re.I)),
+    ("memops", re.compile(r"memcpy|memset|copy|fill", re.I)),
+]
+
+
+def bucket_of(name: str) -> str:
+    for b, rx in BUCKETS:
+        if rx.search(name):
+            return b
+    return "other"
+
+
+def interval_union(iv: List[Tuple[float, float]]) -> float:
+    """Total length of the union of [start, end) intervals."""
+    tot, cur_s, cur_e = 0.0, None, None
+    for s, e in sorted(iv):
+        if cur_e is None or s > cur_e:
+            if cur_e is not None:
+                tot += cur_e - cur_s
+            cur_s, cur_e = s, e
+        else:
+            cur_e = max(cur_e, e)
+    if cur_e is not None:
+        tot += cur_e - cur_s
+    return tot
+
+
+def summarise_trace(path: str, steps: int) -> Dict:
+    ev = json.load(open(path))["traceEvents"]
+    ks = [e for e in ev if e.get("cat") in ("kernel", "gpu_memcpy", "gpu_memset") and "dur" in e]
+    per: Dict[str, List[float]] = {}
+    for e in ks:
+        per.setdefault(e["name"], []).append(e["dur"])
+    busy = interval_union([(e["ts"], e["ts"] + e["dur"]) for e in ks])
+    span = (max(e["ts"] + e["dur"] for e in ks) - min(e["ts"] for e in ks)) if ks else 0.0
+    buckets: Dict[str, float] = {}
+    for n, d in per.items():
+        buckets[bucket_of(n)] = buckets.get(bucket_of(n), 0.0) + sum(d)
+    return {"kernels": per, "busy_us": busy, "span_us": span, "buckets": buckets, "steps": steps}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--mode", default="decode")
+    ap.add_argument("--layers", type=int, default=6)
+    ap.add_argument("--conc", type=int, default=1)
+    ap.add_argument("--ctx", type=int, default=32768)
+    ap.add_argument("--chunk", type=int, default=4096)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--graphs", type=int, default=1)
+    ap.add_argument("--top", type=int, default=30)
+    ap.add_argument("--out", default="")
+    a = ap.parse_args()
+    from ..config import EngineConfig, SchedulerConfig, flash_config
+    from ..models.dsv4 import RandomSource, build_model_weights
+    from ..runtime.engine import Engine, SamplingParams
+    from .decode_bench import add_synthetic_requests, fill_caches_synthetic
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(0)
+    cfg = flash_config(num_layers=a.layers)
+    ec = EngineConfig(model=cfg, sched=SchedulerConfig(max_model_len=a.ctx + 8192, max_num_seqs=max(a.conc, 2),
+                                                       max_num_batched_tokens=a.chunk,
+                                                       graph_cap=64 if a.graphs else 0)).validate()
+    eng = Engine(ec, build_model_weights(cfg, RandomSource(0), dev, head_fp8=True), dev, max_context=a.ctx + 8192)
+    fill_caches_synthetic(eng)
+    if a.mode == "decode":
+        add_synthetic_requests(eng, a.conc, a.ctx, a.steps + 8, cfg.vocab_size, 3)
+    else:
+        g = torch.Generator().manual_seed(0)
+        eng.add_request(torch.randint(0, cfg.vocab_size, (a.chunk * (a.steps + 2),), generator=g).tolist(),
+                        SamplingParams(max_tokens=1))
+    for _ in range(2):
+        eng.step()
+    torch.cuda.synchronize()
+    with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CUDA]) as prof:
+        for _ in range(a.steps):
+            eng.step()
+        torch.cuda.synchronize()
+    path = os.path.join(tempfile.gettempdir(), "stk_trace.json")
+    prof.export_chrome_trace(path)
+    s = summarise_trace(path, a.steps)
+    lines = [f"mode={a.mode} conc={a.conc} ctx={a.ctx} layers={a.layers} graphs={a.graphs} steps={a.steps}",
+             f"busy {s['busy_us'] / a.steps:.1f} us/step, span {s['span_us'] / a.steps:.1f} us/step, "
+             f"idle {100 * (1 - s['busy_us'] / max(s['span_us'], 1e-9)):.1f} %"]
+    for b, v in sorted(s["buckets"].items(), key=lambda x: -x[1]):
+        lines.append(f"  bucket {b:16s} {v / a.steps:9.1f} us/step  {100 * v / max(s['busy_us'], 1e-9):5.1f} %")
+    rows = sorted(s["kernels"].items(), key=lambda x: -sum(x[1]))[:a.top]
+    for n, d in rows:
+        lines.append(f"  {sum(d) / a.steps:9.1f} us/step {len(d) // a.steps:4d}x/step avg {sum(d) / len(d):7.1f} us  {n[:70]}")
+    text = "\n".join(lines)
+    print(text)
+    if a.out:
+        open(a.out, "w").write(text + "\n")
+
+
+if __name__ == "__main__":
+    main()

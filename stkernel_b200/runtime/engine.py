@@ -329,9 +329,9 @@ class Engine:
         bucket = 1
         while bucket < n_req:
             bucket *= 2
-        rows_bucket = 2048
-        while rows_bucket < max_comp_rows:
-            rows_bucket *= 2
+        # compressed-row bound baked into the graph: next multiple of 2048 with 64 rows of headroom,
+        # so a sequence crosses into a new graph only every 8192 tokens
+        rows_bucket = ((max_comp_rows + 64) // 2048 + 1) * 2048
         key = (bucket, rows_bucket)
         if n_req < bucket:
             # padding rows: empty query ranges => request -1, nothing is read or written for them
