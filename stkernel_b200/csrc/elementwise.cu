@@ -158,23 +158,38 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const fl
                                    const int* __restrict__ pair_row, const __nv_bfloat16* __restrict__ shared,
                                    __nv_bfloat16* __restrict__ out, int H, int topk) {
   const int t = blockIdx.x;
-  for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
-    float a0 = 0.f, a1 = 0.f;
-    for (int j = 0; j < topk; ++j) {
-      const int r = pair_row ? pair_row[t * topk + j] : t * topk + j;
-      if (r < 0) continue;
-      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(y + static_cast<long long>(r) * H + i);
-      const float wt = w[t * topk + j];
-      a0 = fmaf(wt, __low2float(v), a0);
-      a1 = fmaf(wt, __high2float(v), a1);
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 2;
+  if (i >= H) return;
+  constexpr int kMaxK = 16;
+  int rows[kMaxK];
+  float wt[kMaxK];
+#pragma unroll
+  for (int j = 0; j < kMaxK; ++j) {
+    rows[j] = -1;
+    wt[j] = 0.f;
+    if (j < topk) {
+      rows[j] = pair_row ? pair_row[t * topk + j] : t * topk + j;
+      wt[j] = w[t * topk + j];
     }
-    if (shared) {
-      const __nv_bfloat162 s = *reinterpret_cast<const __nv_bfloat162*>(shared + static_cast<long long>(t) * H + i);
-      a0 += __low2float(s);
-      a1 += __high2float(s);
-    }
-    *reinterpret_cast<__nv_bfloat162*>(out + static_cast<long long>(t) * H + i) = __floats2bfloat162_rn(a0, a1);
   }
+  __nv_bfloat162 v[kMaxK];
+#pragma unroll
+  for (int j = 0; j < kMaxK; ++j) {
+    v[j] = __floats2bfloat162_rn(0.f, 0.f);
+    if (rows[j] >= 0) v[j] = *reinterpret_cast<const __nv_bfloat162*>(y + static_cast<long long>(rows[j]) * H + i);
+  }
+  float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+  for (int j = 0; j < kMaxK; ++j) {
+    a0 = fmaf(wt[j], __low2float(v[j]), a0);
+    a1 = fmaf(wt[j], __high2float(v[j]), a1);
+  }
+  if (shared) {
+    const __nv_bfloat162 s = *reinterpret_cast<const __nv_bfloat162*>(shared + static_cast<long long>(t) * H + i);
+    a0 += __low2float(s);
+    a1 += __high2float(s);
+  }
+  *reinterpret_cast<__nv_bfloat162*>(out + static_cast<long long>(t) * H + i) = __floats2bfloat162_rn(a0, a1);
 }
 
 }  // namespace stk
@@ -234,8 +249,9 @@ STK_API int stk_swiglu_clamp(const void* gu, long long ldg, void* act, long long
 STK_API int stk_moe_combine(const void* y, const float* w, const int* pair_row, const void* shared, void* out, int T,
                             int H, int topk, void* stream) {
   if (T <= 0) return 0;
-  if (H % 2) return -1;
-  moe_combine_kernel<<<T, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)y, w, pair_row,
+  if (H % 2 || topk > 16) return -1;
+  dim3 grid(T, (H / 2 + 127) / 128);
+  moe_combine_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)y, w, pair_row,
                                                           (const __nv_bfloat16*)shared, (__nv_bfloat16*)out, H, topk);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

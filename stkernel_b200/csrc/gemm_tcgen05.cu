@@ -15,8 +15,11 @@
 //
 // Covers the reference's DeepGEMM fp8_gemm_nt call sites (overlay/dspark_v2.py:92-107,
 // probes/oproj_prof.py:65-71) and its bf16 cuBLAS projections.
+#include <string.h>
+
 #include "common.cuh"
 #include "stk_c_api.h"
+#include "symm.cuh"
 
 namespace stk {
 
@@ -35,7 +38,19 @@ struct GemmArgs {
   float* workspace;      // split-K partials [splits, T, N]
   int* counters;         // one per output tile; zero on entry, zero again on exit
   int* status;
+  // Grouped mode (block-diagonal weights, e.g. the per-o-group low-rank projection): feature tile
+  // `tn` belongs to group tn / group_tiles and reads X columns starting at group * group_k_elems.
+  int group_tiles;       // 0 = plain GEMM
+  int group_k_elems;
+  // Fused all-reduce (row-parallel layers): every rank pushes its partial output tile into all
+  // peers' slots as soon as the tile's accumulation ends, then sums the tiles it received in
+  // rank order.  The transfer of tile i overlaps the MMAs of tile i+1 of the same CTA and of
+  // all other CTAs.
+  int ar_enabled;
+  SymmCtx ar;
 };
+
+constexpr int kArKind = 3;
 
 template <int BT>
 struct GemmCfg {
@@ -115,6 +130,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  uint32_t ar_epoch = 0;
+  if (a.ar_enabled) ar_epoch = *epoch_ptr(a.ar, kArKind, 0) + 1;   // bumped only after every CTA has finished
 
   const int units = a.splits * a.tiles_t * a.tiles_n;
   const int kb_per_split = (a.k_blocks + a.splits - 1) / a.splits;
@@ -138,8 +155,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
           if (!mbar_wait(&bars->empty[stage], phase ^ 1, a.status, 100 + stage)) { ok = false; break; }
           mbar_expect_tx(&bars->full[stage], kTxBytes);
           const int kx = kb * (kFp8 ? 128 : 64);
+          const int gx = a.group_tiles ? (tn / a.group_tiles) * a.group_k_elems : 0;
           tma_load_2d(smem_a + stage * 128 * 128, &tmW, &bars->full[stage], kx, tn * 128);
-          tma_load_2d(smem_b + stage * BT * 128, &tmX, &bars->full[stage], kx, tt * BT);
+          tma_load_2d(smem_b + stage * BT * 128, &tmX, &bars->full[stage], gx + kx, tt * BT);
           ++issued;
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
@@ -221,10 +239,53 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
       const int t0 = tt * BT + col_base;
       const bool n_ok = n < a.N;
 
+      const int ar_par = ar_epoch & 1;
+      const long long ar_slot = a.ar.gemm_bytes / 2;      // bf16 elements per (parity, source) slot
+      auto ar_push = [&](int t, float v) {
+        const __nv_bfloat16 bv = __float2bfloat16(v);
+        for (int p = 0; p < a.ar.world; ++p) {
+          const int peer = (a.ar.rank + p) % a.ar.world;
+          reinterpret_cast<__nv_bfloat16*>(a.ar.base[peer] + a.ar.off_gemm)
+              [(static_cast<long long>(ar_par) * a.ar.world + a.ar.rank) * ar_slot + static_cast<long long>(t) * a.N + n] = bv;
+        }
+      };
+      // signal the tile to every rank, wait (bounded) for every rank's tile, sum in rank order
+      auto ar_finish = [&]() -> bool {
+        const int tile = (tt * a.tiles_n + tn) & 4095;
+        __threadfence_system();
+        epi_bar_sync(kEpiWarps * 32);
+        const int et = threadIdx.x - 64;
+        if (et < a.ar.world) st_release_sys(flag_ptr(a.ar, et, kArKind, tile, a.ar.rank), ar_epoch);
+        if (et == 0) bars->last_flag = 1;
+        epi_bar_sync(kEpiWarps * 32);
+        if (et < a.ar.world) {
+          if (!wait_flag(flag_ptr(a.ar, a.ar.rank, kArKind, tile, et), ar_epoch, a.ar.spin_budget, a.status, 500 + et))
+            bars->last_flag = 0;
+        }
+        epi_bar_sync(kEpiWarps * 32);
+        const bool got = bars->last_flag != 0;
+        if (got && n_ok) {
+          const __nv_bfloat16* slots = reinterpret_cast<const __nv_bfloat16*>(a.ar.base[a.ar.rank] + a.ar.off_gemm) +
+                                       static_cast<long long>(ar_par) * a.ar.world * ar_slot;
+          for (int j = 0; j < kColsPerWarp; ++j) {
+            const int t = t0 + j;
+            if (t >= a.T) break;
+            float s = 0.f;
+            for (int r = 0; r < a.ar.world; ++r)
+              s += __bfloat162float(__ldcg(slots + r * ar_slot + static_cast<long long>(t) * a.N + n));
+            if (a.out_fp32) reinterpret_cast<float*>(a.out)[t * a.ldo + n] = s;
+            else reinterpret_cast<__nv_bfloat16*>(a.out)[t * a.ldo + n] = __float2bfloat16(s);
+          }
+        }
+        epi_bar_sync(kEpiWarps * 32);
+        return got;
+      };
       auto store = [&](int t, float v) {
         if (n_ok && t < a.T) {
           if (a.splits > 1) {
             a.workspace[(static_cast<long long>(sp) * a.T + t) * a.N + n] = v;
+          } else if (a.ar_enabled) {
+            ar_push(t, v);
           } else if (a.out_fp32) {
             reinterpret_cast<float*>(a.out)[t * a.ldo + n] = v;
           } else {
@@ -239,7 +300,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
         for (int j = 0; j < kColsPerWarp; ++j) acc[j] = 0.f;
         for (int kb = kb0; kb < kb1 && ok; ++kb) {
           const float sw = a.w_scale[tn * a.w_scale_ld + kb];
-          const float* xs = a.x_scale + static_cast<long long>(kb) * a.x_scale_ld;
+          const int gkb = a.group_tiles ? (tn / a.group_tiles) * a.k_blocks : 0;
+          const float* xs = a.x_scale + static_cast<long long>(gkb + kb) * a.x_scale_ld;
           if (!mbar_wait(&bars->tmem_full[ab], aphase, a.status, 400 + ab)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
@@ -284,6 +346,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
         if (++ab == 2) { ab = 0; aphase ^= 1; }
       }
 
+      if (a.ar_enabled && a.splits == 1 && ok) ok = ar_finish();
       if (a.splits > 1 && ok) {
         // Publish this split's partial; the CTA that completes the tile reduces it.
         __threadfence();
@@ -305,10 +368,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
               float s = 0.f;
               for (int p = 0; p < a.splits; ++p)
                 s += __ldcg(&a.workspace[(static_cast<long long>(p) * a.T + t) * a.N + n]);
-              if (a.out_fp32) reinterpret_cast<float*>(a.out)[t * a.ldo + n] = s;
+              if (a.ar_enabled) ar_push(t, s);
+              else if (a.out_fp32) reinterpret_cast<float*>(a.out)[t * a.ldo + n] = s;
               else reinterpret_cast<__nv_bfloat16*>(a.out)[t * a.ldo + n] = __float2bfloat16(s);
             }
           }
+          if (a.ar_enabled) ok = ar_finish();
         }
       }
     }
@@ -319,6 +384,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+  if (a.ar_enabled && threadIdx.x == 0) {
+    // the last CTA to leave advances the epoch for the next call
+    __threadfence();
+    uint32_t* done = epoch_ptr(a.ar, kArKind, 1);
+    if (atomicAdd(done, 1u) == gridDim.x - 1) {
+      *done = 0;
+      *epoch_ptr(a.ar, kArKind, 0) = ar_epoch;
+      __threadfence();
+    }
   }
 }
 
@@ -403,7 +478,7 @@ STK_API long long stk_gemm_workspace_bytes(int T, int N, int splits) {
 STK_API int stk_gemm(const void* W, long long ldw, const void* X, long long ldx, void* out, long long ldo, int T, int N,
                      int K, int is_fp8, int out_fp32, const float* w_scale, int w_scale_ld, const float* x_scale,
                      int x_scale_ld, int splits, float* workspace, int* counters, int* status, int sm_count,
-                     void* stream) {
+                     int groups, const void* ar_ctx, void* stream) {
   if (T <= 0 || N <= 0 || K <= 0) return 0;
   const int es = is_fp8 ? 1 : 2;
   if ((ldw * es) % 16 || (ldx * es) % 16 || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(X) & 15))
@@ -413,7 +488,9 @@ STK_API int stk_gemm(const void* W, long long ldw, const void* X, long long ldx,
   const int bt = stk_gemm_pick_bt(T, is_fp8);
   CUtensorMap tw, tx;
   if (make_tmap_2d(&tw, W, es, N, K, ldw, 128) != 0) return -13;
-  if (make_tmap_2d(&tx, X, es, T, K, ldx, bt) != 0) return -14;
+  if (groups < 1) groups = 1;
+  if (groups > 1 && ((K * es) % 128 || N % (128 * groups))) return -17;   // groups must split on tile boundaries
+  if (make_tmap_2d(&tx, X, es, T, static_cast<long long>(K) * groups, ldx, bt) != 0) return -14;
   GemmArgs a;
   a.T = T; a.N = N;
   a.k_blocks = (K * es + 127) / 128;
@@ -429,6 +506,15 @@ STK_API int stk_gemm(const void* W, long long ldw, const void* X, long long ldx,
   a.w_scale = w_scale; a.w_scale_ld = w_scale_ld;
   a.x_scale = x_scale; a.x_scale_ld = x_scale_ld;
   a.workspace = workspace; a.counters = counters; a.status = status;
+  a.group_tiles = groups > 1 ? (N / groups) / 128 : 0;
+  a.group_k_elems = K;
+  a.ar_enabled = 0;
+  memset(&a.ar, 0, sizeof(a.ar));
+  if (ar_ctx != nullptr) {
+    memcpy(&a.ar, ar_ctx, sizeof(a.ar));
+    if (static_cast<long long>(T) * N * 2 > a.ar.gemm_bytes || ldo != N) return -18;
+    a.ar_enabled = 1;
+  }
   const int units = a.splits * a.tiles_n * a.tiles_t;
   const int grid = units < sm_count ? units : sm_count;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

@@ -97,6 +97,7 @@ class LayerWeights:
     w_oa: List[LinearWeight]
     w_ob: LinearWeight
     sink: torch.Tensor
+    w_oa_grouped: Optional[LinearWeight] = None   # the same groups stacked [G_l*o_lora, hpg*D] for one launch
     w_side: Optional[LinearWeight] = None  # bf16 [2cD (+ ih + 4di), H]: compressor | weights_proj | indexer compressor
     ape: Optional[torch.Tensor] = None
     comp_norm: Optional[torch.Tensor] = None
@@ -143,6 +144,11 @@ def build_layer(cfg: ModelConfig, src: WeightSource, prefix: str, li: int, devic
         g_l = G // tp_size
         groups = list(range(tp_rank * g_l, (tp_rank + 1) * g_l))
         w_oa = [mk(woa_full[gi]) for gi in groups]
+        w_oa_grouped = None
+        kbytes = hpg * D * (1 if dd == "fp8" else 2)
+        if kbytes % 128 == 0 and cfg.o_lora_rank % 128 == 0:
+            w_oa_grouped = LinearWeight(torch.cat([w.w for w in w_oa], 0).contiguous(),
+                                        torch.cat([w.scale for w in w_oa], 0).contiguous() if dd == "fp8" else None)
         wob = g(f"{a}.wo_b.weight", (H, G * cfg.o_lora_rank))[:, groups[0] * cfg.o_lora_rank:(groups[-1] + 1) * cfg.o_lora_rank]
     else:
         raise NotImplementedError("tp_size > o_groups")
@@ -150,7 +156,7 @@ def build_layer(cfg: ModelConfig, src: WeightSource, prefix: str, li: int, devic
         kind=kind, ratio=ratio, computes_topk=computes, hc_attn=hc_attn, hc_ffn=hc_ffn,
         attn_norm=g(f"{prefix}.attn_norm.weight", (H,)).to(BF16), ffn_norm=g(f"{prefix}.ffn_norm.weight", (H,)).to(BF16),
         w_qa_kv=w_qa_kv, q_norm=g(f"{a}.q_norm.weight", (cfg.q_lora_rank,)).to(BF16),
-        kv_norm=g(f"{a}.kv_norm.weight", (D,)).to(BF16), w_qb=mk(wqb), w_oa=w_oa, w_ob=mk(wob.contiguous()),
+        kv_norm=g(f"{a}.kv_norm.weight", (D,)).to(BF16), w_qb=mk(wqb), w_oa=w_oa, w_oa_grouped=w_oa_grouped, w_ob=mk(wob.contiguous()),
         sink=g(f"{a}.attn_sink", (nh,)).to(F32)[h0:h0 + nh_l].contiguous())
     if ratio:
         c = compressor_slots(ratio)
@@ -259,6 +265,14 @@ class DSV4Model:
             return x
         return self.comm.all_reduce(x)
 
+    def _gemm_ar_ctx(self, t: int, n: int):
+        """Symmetric context when the row-parallel GEMM can all-reduce in its own epilogue."""
+        if self.tp_size == 1 or self.comm is None or getattr(self.comm, "symm", None) is None or not self.device.type == "cuda":
+            return None
+        if not self.comm.fuse_gemm:
+            return None
+        return self.comm.symm.gemm_ctx(t, n)
+
     # ---- attention sub-block ---------------------------------------------------
     def attention(self, li: int, lw: LayerWeights, y: torch.Tensor, yq, meta: StepMeta, causal_meta=None) -> torch.Tensor:
         cfg = self.cfg
@@ -314,11 +328,15 @@ class DSV4Model:
         G_l = len(lw.w_oa)
         hpg = cfg.num_attention_heads // cfg.o_groups
         og = o.view(T, G_l, hpg * D)
-        z = torch.empty(T, G_l * cfg.o_lora_rank, dtype=o.dtype, device=y.device)
-        for gi, wg in enumerate(lw.w_oa):
-            Fn.linear(og[:, gi], wg, out=z[:, gi * cfg.o_lora_rank:(gi + 1) * cfg.o_lora_rank], tag=f"oa")
-        out = Fn.linear(z, lw.w_ob, tag="ob")
-        return self._all_reduce(out)
+        if lw.w_oa_grouped is not None:
+            z = Fn.linear(o.view(T, G_l * hpg * D), lw.w_oa_grouped, tag="oa", groups=G_l)
+        else:
+            z = torch.empty(T, G_l * cfg.o_lora_rank, dtype=o.dtype, device=y.device)
+            for gi, wg in enumerate(lw.w_oa):
+                Fn.linear(og[:, gi], wg, out=z[:, gi * cfg.o_lora_rank:(gi + 1) * cfg.o_lora_rank], tag=f"oa")
+        ar = self._gemm_ar_ctx(T, cfg.hidden_size)
+        out = Fn.linear(z, lw.w_ob, tag="ob", ar_ctx=ar)
+        return out if ar is not None else self._all_reduce(out)
 
     # ---- MoE sub-block ----------------------------------------------------------
     def moe(self, lw: LayerWeights, y: torch.Tensor, yq, meta: StepMeta) -> torch.Tensor:

@@ -7,6 +7,7 @@ and the whole decode step can be captured in a CUDA graph.
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
@@ -93,14 +94,32 @@ def quant_act(x: torch.Tensor, tag: str = "act") -> QuantAct:
 
 
 def linear(x, lw: LinearWeight, out: Optional[torch.Tensor] = None, out_dtype=BF16, tag: str = "lin",
-           splits: Optional[int] = None) -> torch.Tensor:
+           splits: Optional[int] = None, groups: int = 1, ar_ctx=None) -> torch.Tensor:
     """out[T, N] = x[T, K] @ W[N, K]^T.  x: bf16 tensor or a QuantAct (required format for fp8 weights
-    is produced on the fly when a bf16 tensor is given)."""
+    is produced on the fly when a bf16 tensor is given).
+
+    ar_ctx: symmetric-memory context; the kernel then all-reduces the output over the ranks in its
+    epilogue (row-parallel layers).  The output must be contiguous.
+
+    groups > 1: block-diagonal product.  W is [N, K] with N/groups rows per group, x is [T, groups*K];
+    output columns of group g use x[:, g*K:(g+1)*K]."""
     if isinstance(x, QuantAct):
         xa, dev, t = x, x.q.device, x.q.shape[0]
     else:
         xa, dev, t = None, x.device, x.shape[0]
     n, k = lw.w.shape
+    if groups > 1 and dev.type != "cuda":
+        xf = x if xa is None else R.dequant_fp8_group128_act(xa.q, xa.scale.t()[:t])
+        if lw.is_fp8 and xa is None:
+            xf = torch.cat([R.dequant_fp8_group128_act(*R.quant_fp8_group128_act(xf[:, g * k:(g + 1) * k]))
+                            for g in range(groups)], 1)
+        wd = lw.dequant().view(groups, n // groups, k)
+        y = torch.einsum("tgk,gnk->tgn", xf.to(F32).view(t, groups, k), wd).reshape(t, n)
+        y = y.to(out_dtype if out_dtype != BF16 else cpu_act_dtype())
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
     if dev.type != "cuda":
         if lw.is_fp8:
             if xa is None:
@@ -132,7 +151,8 @@ def linear(x, lw: LinearWeight, out: Optional[torch.Tensor] = None, out_dtype=BF
     _lib.call("stk_gemm", lw.w, lw.w.stride(0), xin, xin.stride(0), out, out.stride(0), t, n, k, is_fp8,
               1 if out.dtype == F32 else 0, lw.scale, lw.scale.stride(0) if is_fp8 else 0,
               xa.scale if is_fp8 else None, xa.scale.stride(0) if is_fp8 else 0, splits, ws, cnt,
-              _lib.status_buffer(), sms, _lib.stream())
+              _lib.status_buffer(), sms, groups, ctypes.addressof(ar_ctx) if ar_ctx is not None else None,
+              _lib.stream())
     return out
 
 

@@ -18,7 +18,8 @@ import torch.distributed as dist
 
 class Communicator:
     def __init__(self, group: Optional[dist.ProcessGroup] = None, device=None, use_symm: bool = True,
-                 oneshot_max_bytes: int = 512 * 1024, cpu_group: Optional[dist.ProcessGroup] = None):
+                 oneshot_max_bytes: int = 512 * 1024, cpu_group: Optional[dist.ProcessGroup] = None,
+                 fuse_gemm: bool = True):
         self.group = group if group is not None else dist.group.WORLD
         self.world_size = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
@@ -26,6 +27,7 @@ class Communicator:
         self.oneshot_max_bytes = oneshot_max_bytes
         self.cpu_group = cpu_group
         self.symm = None
+        self.fuse_gemm = fuse_gemm
         self.disabled_reason: Optional[str] = None
         self.calls = {"oneshot": 0, "twoshot": 0, "nccl": 0}
         if use_symm and self.device.type == "cuda" and self.world_size > 1:

@@ -1,0 +1,170 @@
+"""Symmetric peer memory (CUDA IPC over NVLink) and the all-reduce kernels that use it.
+
+Bootstrap mirrors the reference's one-shot shim (overlay/dsv4_oneshot_shim.py:62-122): exchange
+handles with ``all_gather_object``, run a lock-step self-test against the library collective, and
+on any failure fall back to NCCL permanently.  The data path differs: kernels store directly into
+peer HBM and spin (bounded) on epoch flags; a timed-out wait sets a device status word that the
+host reads after the step, upon which this path disables itself.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+
+_MB = 1 << 20
+
+
+def region_layout(world: int, oneshot_bytes: int, twoshot_bytes: int, gemm_bytes: int = 2 * _MB) -> dict:
+    """Byte offsets of the symmetric region (identical on every rank)."""
+    off = 0
+    lay = {}
+    lay["off_flags"] = off
+    off += 1 * _MB
+    lay["off_epochs"] = off
+    off += 256 * 1024
+    lay["off_oneshot"] = off
+    off += 2 * world * oneshot_bytes
+    lay["off_rs"] = off
+    chunk = (twoshot_bytes + world - 1) // world
+    chunk = (chunk + 15) // 16 * 16
+    off += 2 * world * chunk
+    off = (off + 255) // 256 * 256
+    lay["off_ag"] = off
+    off += 2 * twoshot_bytes
+    off = (off + 255) // 256 * 256
+    lay["off_gemm"] = off
+    lay["gemm_bytes"] = gemm_bytes
+    off += 2 * world * gemm_bytes
+    lay["off_user"] = (off + 255) // 256 * 256
+    lay["oneshot_bytes"] = oneshot_bytes
+    lay["twoshot_bytes"] = twoshot_bytes
+    return lay
+
+
+class SymmetricHeap:
+    """One cudaMalloc'd region per rank, mapped into every peer."""
+
+    def __init__(self, comm, nbytes: int):
+        self.comm = comm
+        self.nbytes = nbytes
+        L = _lib.lib()
+        p = ctypes.c_void_p()
+        if L.stk_symm_alloc(ctypes.c_longlong(nbytes), ctypes.byref(p)) != 0:
+            raise RuntimeError("symmetric allocation failed")
+        self.local = p.value
+        h = (ctypes.c_ubyte * 64)()
+        if L.stk_symm_export(ctypes.c_void_p(self.local), h) != 0:
+            raise RuntimeError("cudaIpcGetMemHandle failed")
+        handles = comm.all_gather_object(bytes(h))
+        self.bases: List[int] = []
+        self._opened: List[int] = []
+        for r, hb in enumerate(handles):
+            if r == comm.rank:
+                self.bases.append(self.local)
+                continue
+            q = ctypes.c_void_p()
+            buf = (ctypes.c_ubyte * 64).from_buffer_copy(hb)
+            if L.stk_symm_import(buf, ctypes.byref(q)) != 0:
+                raise RuntimeError(f"cudaIpcOpenMemHandle failed for rank {r}")
+            self.bases.append(q.value)
+            self._opened.append(q.value)
+
+    def close(self) -> None:
+        L = _lib.lib()
+        for q in self._opened:
+            L.stk_symm_close(ctypes.c_void_p(q))
+        self._opened = []
+        if self.local:
+            L.stk_symm_free(ctypes.c_void_p(self.local))
+            self.local = 0
+
+
+class SymmetricAllReduce:
+    ONESHOT_BLOCKS = 8
+    TWOSHOT_BLOCKS = 32
+
+    def __init__(self, comm, max_bytes: int = 64 * _MB, oneshot_bytes: int = 2 * _MB, spin_budget: int = 4_000_000,
+                 user_bytes: int = 0):
+        self.comm = comm
+        self.world = comm.world_size
+        if self.world > 8:
+            raise RuntimeError("symmetric all-reduce supports at most 8 ranks")
+        self.layout = region_layout(self.world, oneshot_bytes, max_bytes)
+        self.heap = SymmetricHeap(comm, self.layout["off_user"] + user_bytes)
+        L = _lib.lib()
+        self.ctx = (ctypes.c_ubyte * L.stk_symm_ctx_size())()
+        bases = (ctypes.c_longlong * self.world)(*self.heap.bases)
+        lay = self.layout
+        rc = L.stk_symm_ctx_fill(self.ctx, bases, comm.rank, self.world, lay["off_flags"], lay["off_epochs"],
+                                 lay["off_oneshot"], lay["oneshot_bytes"], lay["off_rs"], lay["off_ag"],
+                                 lay["twoshot_bytes"], lay["off_gemm"], lay["gemm_bytes"], spin_budget)
+        if rc != 0:
+            raise RuntimeError("symmetric context rejected")
+        self.oneshot_max = min(comm.oneshot_max_bytes, oneshot_bytes)
+        self.twoshot_max = max_bytes
+        self.enabled = True
+        comm.barrier()
+
+    def eligible(self, x: torch.Tensor) -> bool:
+        n = x.numel() * x.element_size()
+        return (self.enabled and x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and n % 16 == 0
+                and x.data_ptr() % 16 == 0 and 0 < n <= self.twoshot_max)
+
+    def all_reduce(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        """In-place sum over ranks; returns None when this path is disabled."""
+        if not self.enabled:
+            return None
+        n = x.numel() * x.element_size()
+        L = _lib.lib()
+        st = _lib.status_buffer()
+        if n <= self.oneshot_max:
+            # the block count is fixed per kernel kind: all blocks then share one epoch sequence
+            rc = L.stk_oneshot_allreduce(self.ctx, x.data_ptr(), x.data_ptr(), n, self.ONESHOT_BLOCKS, st.data_ptr(),
+                                         _lib.stream())
+            self.comm.calls["oneshot"] += 1
+        else:
+            rc = L.stk_twoshot_allreduce(self.ctx, x.data_ptr(), x.data_ptr(), n, self.TWOSHOT_BLOCKS, st.data_ptr(),
+                                         _lib.stream())
+            self.comm.calls["twoshot"] += 1
+        if rc != 0:
+            raise _lib.KernelError(f"symmetric all-reduce launch returned {rc}")
+        _lib.launch_count += 1
+        return x
+
+    def self_test(self) -> None:
+        """Lock-step comparison with the library collective at a few sizes; raises on mismatch."""
+        dev = self.comm.device
+        for numel in (4096 * 6, 4096 * 256, 4096 * 2048):
+            if numel * 2 > self.twoshot_max:
+                continue
+            g = torch.Generator(device=dev).manual_seed(1234 + self.comm.rank)
+            x = torch.randn(numel, device=dev, generator=g).to(torch.bfloat16)
+            ref = x.float()
+            dist.all_reduce(ref, group=self.comm.group)
+            for _ in range(3):          # repeated calls exercise both parities
+                y = x.clone()
+                self.all_reduce(y)
+            torch.cuda.synchronize()
+            _lib.check_status()
+            err = (y.float() - ref).abs().max().item()
+            tol = 0.02 * ref.abs().max().item() + 1e-3
+            ok = torch.tensor([1 if err <= tol else 0], device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.comm.group)
+            if int(ok.item()) != 1:
+                self.enabled = False
+                raise RuntimeError(f"symmetric all-reduce self-test diverged at {numel} elements (err {err})")
+
+    def gemm_ctx(self, t: int, n: int):
+        """Context for the GEMM-fused all-reduce, or None when the output does not fit its slots."""
+        if not self.enabled or t * n * 2 > self.layout["gemm_bytes"]:
+            return None
+        return self.ctx
+
+    def disable(self, reason: str) -> None:
+        self.enabled = False
+        self.comm.disabled_reason = reason

@@ -1,0 +1,103 @@
+"""Run under torchrun on 2+ GPUs: symmetric-memory all-reduce kernels and the GEMM-fused
+all-reduce against the NCCL collective, with device-timed comparisons (max over ranks)."""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+from stkernel_b200.ops import _lib                              # noqa: E402
+from stkernel_b200.ops import functional as Fn                  # noqa: E402
+from stkernel_b200.ops import reference as R                    # noqa: E402
+from stkernel_b200.parallel.communicator import Communicator    # noqa: E402
+
+
+def timed(fn, iters=20, warm=5):
+    for _ in range(warm):
+        fn()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters * 1e3], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device(f"cuda:{local}")
+    dist.init_process_group("nccl", device_id=dev)
+    comm = Communicator(device=dev, use_symm=True)
+    out = {"world": world, "symm": comm.symm is not None, "disabled_reason": comm.disabled_reason, "allreduce": [], "gemm_ar": []}
+    assert comm.symm is not None, comm.disabled_reason
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    for numel in (4096, 6 * 4096, 64 * 4096, 256 * 4096, 4096 * 4096):
+        x = torch.randn(numel, device=dev, generator=g).to(torch.bfloat16)
+        ref = x.float()
+        dist.all_reduce(ref)
+        y = x.clone()
+        comm.all_reduce(y)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        err = (y.float() - ref).abs().max().item() / max(ref.abs().max().item(), 1e-6)
+        assert err < 2e-2, (numel, err)
+        buf = x.clone()
+        ours = timed(lambda: comm.all_reduce(buf))
+        nccl = timed(lambda: dist.all_reduce(buf))
+        out["allreduce"].append({"bytes": numel * 2, "ours_us": ours, "nccl_us": nccl, "rel_err": err})
+    # ---- GEMM fused with the all-reduce (row-parallel layer) ----
+    K_total, N = 8192, 4096
+    k = K_total // world
+    for dtype in ("bf16", "fp8"):
+        for T in (1, 8, 64, 256):
+            gw = torch.Generator(device=dev).manual_seed(7 + rank)
+            x = torch.randn(T, k, device=dev, generator=gw).to(torch.bfloat16)
+            w = torch.randn(N, k, device=dev, generator=gw) * 0.05
+            lw = Fn.LinearWeight.from_master(w, dtype, dev)
+            if dtype == "fp8":
+                xq, xs = R.quant_fp8_group128_act(x)
+                ref = R.dequant_fp8_group128_act(xq, xs) @ lw.dequant().t()
+            else:
+                ref = x.float() @ lw.dequant().t()
+            dist.all_reduce(ref)
+            ctx = comm.symm.gemm_ctx(T, N)
+            assert ctx is not None
+            y = None
+            for _ in range(3):
+                y = Fn.linear(x, lw, ar_ctx=ctx)
+            torch.cuda.synchronize()
+            _lib.check_status()
+            err = ((y.float() - ref).norm() / ref.norm()).item()
+            assert err < 2e-2, (dtype, T, err)
+            fused = timed(lambda: Fn.linear(x, lw, ar_ctx=ctx))
+
+            def base():
+                o = Fn.linear(x, lw)
+                dist.all_reduce(o)
+            def base_symm():
+                o = Fn.linear(x, lw)
+                comm.all_reduce(o)
+            def base_torch():
+                o = x @ lw.w.t() if dtype == "bf16" else Fn.linear(x, lw)
+                dist.all_reduce(o)
+            out["gemm_ar"].append({"dtype": dtype, "T": T, "fused_us": fused, "gemm_then_nccl_us": timed(base),
+                                   "gemm_then_oneshot_us": timed(base_symm),
+                                   "cublas_then_nccl_us": timed(base_torch) if dtype == "bf16" else None, "rel_err": err})
+    if rank == 0:
+        print("SYMM_OK " + json.dumps(out), flush=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    sys.stdout.flush()
+    os._exit(0)
+
+
+if __name__ == "__main__":
+    main()
