@@ -55,6 +55,8 @@ constexpr int kArKind = 3;
 template <int BT>
 struct GemmCfg {
   static constexpr int kStageBytes = 128 * 128 + BT * 128;
+  // bf16 staging tile [BT][128] for the fused all-reduce epilogue (token tiles up to 128)
+  static constexpr int kArTileBytes = BT <= 128 ? BT * 256 : 0;
   static constexpr int kStagesRaw = (196 * 1024) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kTmemCols = (2 * BT <= 32) ? 32 : (2 * BT <= 64) ? 64 : (2 * BT <= 128) ? 128 : (2 * BT <= 256) ? 256 : 512;
@@ -102,6 +104,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
   uint8_t* smem_a = smem;                                  // kStages x 16 KB
   uint8_t* smem_b = smem + kStages * 128 * 128;            // kStages x BT*128
   GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(smem_b + kStages * BT * 128);
+  __nv_bfloat16* ar_tile = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -242,42 +245,71 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
       const int ar_par = ar_epoch & 1;
       const long long ar_slot = a.ar.gemm_bytes / 2;      // bf16 elements per (parity, source) slot
       auto ar_push = [&](int t, float v) {
-        const __nv_bfloat16 bv = __float2bfloat16(v);
-        for (int p = 0; p < a.ar.world; ++p) {
-          const int peer = (a.ar.rank + p) % a.ar.world;
-          reinterpret_cast<__nv_bfloat16*>(a.ar.base[peer] + a.ar.off_gemm)
-              [(static_cast<long long>(ar_par) * a.ar.world + a.ar.rank) * ar_slot + static_cast<long long>(t) * a.N + n] = bv;
-        }
+        if constexpr (Cfg::kArTileBytes > 0) ar_tile[(t - tt * BT) * 128 + row] = __float2bfloat16(v);
       };
-      // signal the tile to every rank, wait (bounded) for every rank's tile, sum in rank order
+      // copy the staged tile to every rank with 16-byte stores, signal it, wait (bounded) for every
+      // rank's tile, and sum the tiles in rank order
       auto ar_finish = [&]() -> bool {
         const int tile = (tt * a.tiles_n + tn) & 4095;
-        __threadfence_system();
-        epi_bar_sync(kEpiWarps * 32);
         const int et = threadIdx.x - 64;
-        if (et < a.ar.world) st_release_sys(flag_ptr(a.ar, et, kArKind, tile, a.ar.rank), ar_epoch);
+        const int nthr = kEpiWarps * 32;
+        const int rows_valid = min(BT, a.T - tt * BT);
+        const int nvec = rows_valid * 16;
+        epi_bar_sync(nthr);
+        for (int p = 0; p < a.ar.world; ++p) {
+          const int peer = (a.ar.rank + p) % a.ar.world;
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.ar.base[peer] + a.ar.off_gemm) +
+                               (static_cast<long long>(ar_par) * a.ar.world + a.ar.rank) * ar_slot;
+          for (int v = et; v < nvec; v += nthr) {
+            const int r = v >> 4, cvec = v & 15;
+            const uint4 val = *reinterpret_cast<const uint4*>(ar_tile + r * 128 + cvec * 8);
+            *reinterpret_cast<uint4*>(dst + static_cast<long long>(tt * BT + r) * a.N + tn * 128 + cvec * 8) = val;
+          }
+        }
+        epi_bar_sync(nthr);
+        if (et < a.ar.world) {
+          __threadfence_system();      // cumulative with the barrier: orders every thread's pushes before the flag
+          st_release_sys(flag_ptr(a.ar, et, kArKind, tile, a.ar.rank), ar_epoch);
+        }
         if (et == 0) bars->last_flag = 1;
-        epi_bar_sync(kEpiWarps * 32);
+        epi_bar_sync(nthr);
         if (et < a.ar.world) {
           if (!wait_flag(flag_ptr(a.ar, a.ar.rank, kArKind, tile, et), ar_epoch, a.ar.spin_budget, a.status, 500 + et))
             bars->last_flag = 0;
         }
-        epi_bar_sync(kEpiWarps * 32);
+        epi_bar_sync(nthr);
         const bool got = bars->last_flag != 0;
-        if (got && n_ok) {
+        if (got) {
           const __nv_bfloat16* slots = reinterpret_cast<const __nv_bfloat16*>(a.ar.base[a.ar.rank] + a.ar.off_gemm) +
                                        static_cast<long long>(ar_par) * a.ar.world * ar_slot;
-          for (int j = 0; j < kColsPerWarp; ++j) {
-            const int t = t0 + j;
-            if (t >= a.T) break;
-            float s = 0.f;
-            for (int r = 0; r < a.ar.world; ++r)
-              s += __bfloat162float(__ldcg(slots + r * ar_slot + static_cast<long long>(t) * a.N + n));
-            if (a.out_fp32) reinterpret_cast<float*>(a.out)[t * a.ldo + n] = s;
-            else reinterpret_cast<__nv_bfloat16*>(a.out)[t * a.ldo + n] = __float2bfloat16(s);
+          for (int v = et; v < nvec; v += nthr) {
+            const int r = v >> 4, cvec = v & 15;
+            const long long off = static_cast<long long>(tt * BT + r) * a.N + tn * 128 + cvec * 8;
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int rk = 0; rk < a.ar.world; ++rk) {
+              const uint4 val = __ldcg(reinterpret_cast<const uint4*>(slots + rk * ar_slot + off));
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&val);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                acc[2 * i] += __low2float(h[i]);
+                acc[2 * i + 1] += __high2float(h[i]);
+              }
+            }
+            if (a.out_fp32) {
+              float* o = reinterpret_cast<float*>(a.out) + static_cast<long long>(tt * BT + r) * a.ldo + tn * 128 + cvec * 8;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) o[i] = acc[i];
+            } else {
+              uint4 ov;
+              __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.out) + static_cast<long long>(tt * BT + r) * a.ldo +
+                                        tn * 128 + cvec * 8) = ov;
+            }
           }
         }
-        epi_bar_sync(kEpiWarps * 32);
+        epi_bar_sync(nthr);
         return got;
       };
       auto store = [&](int t, float v) {
@@ -361,16 +393,52 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
         epi_bar_sync(kEpiWarps * 32);
         if (last) {
           __threadfence();
-          if (n_ok) {
-            for (int j = 0; j < kColsPerWarp; ++j) {
-              const int t = t0 + j;
-              if (t >= a.T) break;
-              float s = 0.f;
-              for (int p = 0; p < a.splits; ++p)
-                s += __ldcg(&a.workspace[(static_cast<long long>(p) * a.T + t) * a.N + n]);
-              if (a.ar_enabled) ar_push(t, s);
-              else if (a.out_fp32) reinterpret_cast<float*>(a.out)[t * a.ldo + n] = s;
-              else reinterpret_cast<__nv_bfloat16*>(a.out)[t * a.ldo + n] = __float2bfloat16(s);
+          // Cooperative reduction: the tile's partials are [split][token][128 features] fp32 rows of
+          // 512 contiguous bytes; every epilogue thread sums float4 vectors (all loads independent).
+          {
+            const int et2 = threadIdx.x - 64;
+            const int nthr2 = kEpiWarps * 32;
+            const int rows_valid = min(BT, a.T - tt * BT);
+            const int cols_valid = min(128, a.N - tn * 128);
+            const bool vec_ok = (cols_valid == 128) && ((a.N & 3) == 0);
+            if (vec_ok) {
+              for (int v = et2; v < rows_valid * 32; v += nthr2) {
+                const int r = v >> 5, c4 = (v & 31) * 4;
+                const int t = tt * BT + r;
+                float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int p = 0; p < a.splits; ++p) {
+                  const float4 x = __ldcg(reinterpret_cast<const float4*>(
+                      &a.workspace[(static_cast<long long>(p) * a.T + t) * a.N + tn * 128 + c4]));
+                  s4.x += x.x; s4.y += x.y; s4.z += x.z; s4.w += x.w;
+                }
+                if (a.ar_enabled) {
+                  if constexpr (Cfg::kArTileBytes > 0) {
+                    __nv_bfloat162* d = reinterpret_cast<__nv_bfloat162*>(ar_tile + r * 128 + c4);
+                    d[0] = __floats2bfloat162_rn(s4.x, s4.y);
+                    d[1] = __floats2bfloat162_rn(s4.z, s4.w);
+                  }
+                } else if (a.out_fp32) {
+                  *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + t * a.ldo + tn * 128 + c4) = s4;
+                } else {
+                  __nv_bfloat162* d = reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(a.out) + t * a.ldo + tn * 128 + c4);
+                  d[0] = __floats2bfloat162_rn(s4.x, s4.y);
+                  d[1] = __floats2bfloat162_rn(s4.z, s4.w);
+                }
+              }
+            } else {
+              for (int v = et2; v < rows_valid * cols_valid; v += nthr2) {
+                const int r = v / cols_valid, cc = v % cols_valid;
+                const int t = tt * BT + r, nn = tn * 128 + cc;
+                float sacc = 0.f;
+                for (int p = 0; p < a.splits; ++p) sacc += __ldcg(&a.workspace[(static_cast<long long>(p) * a.T + t) * a.N + nn]);
+                if (a.ar_enabled) {
+                  if constexpr (Cfg::kArTileBytes > 0) ar_tile[r * 128 + cc] = __float2bfloat16(sacc);
+                } else if (a.out_fp32) {
+                  reinterpret_cast<float*>(a.out)[t * a.ldo + nn] = sacc;
+                } else {
+                  reinterpret_cast<__nv_bfloat16*>(a.out)[t * a.ldo + nn] = __float2bfloat16(sacc);
+                }
+              }
             }
           }
           if (a.ar_enabled) ok = ar_finish();
@@ -437,7 +505,8 @@ int make_tmap_2d(CUtensorMap* tm, const void* base, int elem_bytes, long long ro
 template <int BT, bool kFp8>
 static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmArgs& a, int grid, cudaStream_t st) {
   using Cfg = GemmCfg<BT>;
-  const int smem = Cfg::kStages * Cfg::kStageBytes + static_cast<int>(sizeof(GemmBarriers)) + 1024;
+  const int smem = Cfg::kStages * Cfg::kStageBytes + 256 + Cfg::kArTileBytes + 1024;
+  static_assert(sizeof(GemmBarriers) <= 256, "barrier block");
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(gemm_kernel<BT, kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
@@ -464,9 +533,9 @@ STK_API int stk_gemm_pick_splits(int T, int N, int K, int is_fp8, int sm_count) 
   const int bt = stk_gemm_pick_bt(T, is_fp8);
   const int tiles = ((N + 127) / 128) * ((T + bt - 1) / bt);
   const int kb = (K * (is_fp8 ? 1 : 2) + 127) / 128;
-  if (tiles >= sm_count || T > 256) return 1;
+  if (tiles >= sm_count || T > 128) return 1;
   int s = sm_count / tiles;
-  if (s > kb / 2) s = kb / 2;      // keep at least two K blocks per split
+  if (s > kb / 4) s = kb / 4;      // keep at least four K blocks per split
   if (s > 16) s = 16;
   return s < 1 ? 1 : s;
 }
@@ -512,7 +581,9 @@ STK_API int stk_gemm(const void* W, long long ldw, const void* X, long long ldx,
   memset(&a.ar, 0, sizeof(a.ar));
   if (ar_ctx != nullptr) {
     memcpy(&a.ar, ar_ctx, sizeof(a.ar));
-    if (static_cast<long long>(T) * N * 2 > a.ar.gemm_bytes || ldo != N) return -18;
+    if (static_cast<long long>(T) * N * 2 > a.ar.gemm_bytes || ldo % 8 || N % 128 || bt > 128 ||
+        (reinterpret_cast<uintptr_t>(out) & 15))
+      return -18;
     a.ar_enabled = 1;
   }
   const int units = a.splits * a.tiles_n * a.tiles_t;

@@ -42,9 +42,11 @@ oneshot_ar_kernel(SymmCtx c, const uint4* __restrict__ in, uint4* __restrict__ o
     uint4* dst = reinterpret_cast<uint4*>(c.base[peer] + c.off_oneshot) + (static_cast<long long>(par) * c.world + c.rank) * slot_vecs;
     for (long long i = v0 + threadIdx.x; i < v1; i += blockDim.x) dst[i] = in[i];
   }
-  __threadfence_system();
   __syncthreads();
-  if (threadIdx.x < c.world) st_release_sys(flag_ptr(c, threadIdx.x, kind, b, c.rank), epoch);
+  if (threadIdx.x < c.world) {
+    __threadfence_system();      // cumulative with the barrier: every thread's pushes precede the flag
+    st_release_sys(flag_ptr(c, threadIdx.x, kind, b, c.rank), epoch);
+  }
   if (threadIdx.x == 0) ok_s = 1;
   __syncthreads();
   if (threadIdx.x < c.world) {
@@ -86,9 +88,11 @@ twoshot_ar_kernel(SymmCtx c, const uint4* __restrict__ in, uint4* __restrict__ o
       if (g0 + i < n_vec) dst[i] = in[g0 + i];
     }
   }
-  __threadfence_system();
   __syncthreads();
-  if (threadIdx.x < c.world) st_release_sys(flag_ptr(c, threadIdx.x, kind, b, c.rank), epoch);
+  if (threadIdx.x < c.world) {
+    __threadfence_system();      // cumulative with the barrier: every thread's pushes precede the flag
+    st_release_sys(flag_ptr(c, threadIdx.x, kind, b, c.rank), epoch);
+  }
   if (threadIdx.x == 0) ok_s = 1;
   __syncthreads();
   if (threadIdx.x < c.world) {
@@ -110,9 +114,11 @@ twoshot_ar_kernel(SymmCtx c, const uint4* __restrict__ in, uint4* __restrict__ o
       }
     }
   }
-  __threadfence_system();
   __syncthreads();
-  if (threadIdx.x < c.world) st_release_sys(flag_ptr(c, threadIdx.x, kind + 1, b, c.rank), epoch);
+  if (threadIdx.x < c.world) {
+    __threadfence_system();
+    st_release_sys(flag_ptr(c, threadIdx.x, kind + 1, b, c.rank), epoch);
+  }
   __syncthreads();
   if (threadIdx.x < c.world) {
     if (!wait_flag(flag_ptr(c, c.rank, kind + 1, b, threadIdx.x), epoch, c.spin_budget, status, 200 + threadIdx.x)) ok_s = 0;

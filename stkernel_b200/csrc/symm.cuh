@@ -6,7 +6,7 @@
 namespace stk {
 
 constexpr int kMaxRanks = 8;
-constexpr int kMaxArBlocks = 64;
+constexpr int kMaxArBlocks = 256;
 
 struct SymmCtx {
   uint8_t* base[kMaxRanks];   // each rank's region as mapped in this process (base[rank] = own)

@@ -86,7 +86,7 @@ class SymmetricHeap:
 
 class SymmetricAllReduce:
     ONESHOT_BLOCKS = 8
-    TWOSHOT_BLOCKS = 32
+    TWOSHOT_BLOCKS = 128
 
     def __init__(self, comm, max_bytes: int = 64 * _MB, oneshot_bytes: int = 2 * _MB, spin_budget: int = 4_000_000,
                  user_bytes: int = 0):
@@ -161,7 +161,7 @@ class SymmetricAllReduce:
 
     def gemm_ctx(self, t: int, n: int):
         """Context for the GEMM-fused all-reduce, or None when the output does not fit its slots."""
-        if not self.enabled or t * n * 2 > self.layout["gemm_bytes"]:
+        if not self.enabled or t * n * 2 > self.layout["gemm_bytes"] or t > 128 or n % 128:
             return None
         return self.ctx
 

@@ -371,3 +371,34 @@ def test_swa_indices_and_slots():
     sl, ln = A.topk_to_slots(topk, bt, tok_req[:2].contiguous(), 256)
     rsl, rln = A.topk_to_slots(topk.cpu(), bt.cpu(), tok_req[:2].cpu(), 256)
     assert torch.equal(sl.cpu(), rsl) and torch.equal(ln.cpu(), rln)
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp8"])
+@pytest.mark.parametrize("T", [1, 40, 300])
+def test_gemm_grouped_block_diagonal(dtype, T):
+    torch.manual_seed(2)
+    G, Ng, K = 4, 256, 512
+    x = torch.randn(T, G * K, device=dev()).to(BF16)
+    ws = [torch.randn(Ng, K, device=dev()) * 0.05 for _ in range(G)]
+    lws = [Fn.LinearWeight.from_master(w, dtype, dev()) for w in ws]
+    stacked = Fn.LinearWeight(torch.cat([l.w for l in lws], 0).contiguous(),
+                              torch.cat([l.scale for l in lws], 0).contiguous() if dtype == "fp8" else None)
+    out = Fn.linear(x, stacked, out_dtype=F32, groups=G)
+    for g in range(G):
+        xg = x[:, g * K:(g + 1) * K]
+        if dtype == "fp8":
+            xq, xs = R.quant_fp8_group128_act(xg)
+            ref = R.dequant_fp8_group128_act(xq, xs) @ lws[g].dequant().t()
+        else:
+            ref = xg.float() @ lws[g].dequant().t()
+        assert rel_err(out[:, g * Ng:(g + 1) * Ng], ref) < 3e-3
+
+
+@pytest.mark.parametrize("T,N,K", [(64, 4096, 8192), (100, 384, 1024), (128, 4096, 2048)])
+def test_gemm_splitk_wide_tiles(T, N, K):
+    torch.manual_seed(3)
+    x = torch.randn(T, K, device=dev()).to(BF16)
+    w = torch.randn(N, K, device=dev()).to(BF16)
+    ref = x.float() @ w.float().t()
+    for splits in (2, 4):
+        assert rel_err(Fn.linear(x, Fn.LinearWeight(w), splits=splits), ref) < 1e-2
