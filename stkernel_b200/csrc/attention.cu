@@ -274,3 +274,11 @@ STK_API int stk_sparse_mla(const void* q, long long ldt, const void* swa_cache, 
   sparse_mla_combine_kernel<<<g2, 128, 0, st>>>(workspace, sink, (__nv_bfloat16*)out, ldo, nh, D, n_splits);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+STK_API int stk_sparse_mla_combine(const float* workspace, const float* sink, void* out, long long ldo, int T, int nh,
+                                   int D, int n_splits, void* stream) {
+  if (T <= 0) return 0;
+  dim3 g2(T, nh);
+  sparse_mla_combine_kernel<<<g2, 128, 0, (cudaStream_t)stream>>>(workspace, sink, (__nv_bfloat16*)out, ldo, nh, D, n_splits);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

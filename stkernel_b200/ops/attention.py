@@ -14,6 +14,11 @@ from .functional import cpu_act_dtype
 BF16 = torch.bfloat16
 F32 = torch.float32
 I32 = torch.int32
+# The tcgen05 sparse-MLA kernel serves fp8_ds_mla rows of the production shape; other shapes (and
+# this switch set to False, for A/B checks) use the split-row CUDA-core kernel.
+USE_TENSOR_CORE_MLA = True
+# optional int64[8] device tensor receiving stage timestamps (ns) of CTA (0, 0) of the tcgen05 kernel
+MLA_TRACE = None
 
 
 # ---- metadata -------------------------------------------------------------------
@@ -228,10 +233,21 @@ def sparse_mla(q: torch.Tensor, swa_cache: PagedCache, swa_slots: torch.Tensor, 
             out[i] = R.sparse_mla(q[i:i + 1], rr, vv, sink, scale)[0]
         return out.to(cpu_act_dtype())
     max_rows = swa_slots.shape[1] + (topk_slots.shape[1] if topk_slots is not None else 0)
+    cc = comp_cache if comp_cache is not None else swa_cache
+    if USE_TENSOR_CORE_MLA and swa_cache.fp8 and d == 512 and swa_cache.rope_dim == 64 and nh <= 64 and q.stride(0) % 8 == 0:
+        # tcgen05 kernel: 128-row blocks; enough splits to fill the SMs at decode sizes
+        n_splits = max(1, min((max_rows + 127) // 128, (2 * _lib.sm_count()) // max(t, 1)))
+        ws = scratch("mla.partial", (t * n_splits * nh * (d + 2),), F32, q.device)
+        out = torch.empty(t, nh, d, dtype=BF16, device=q.device)
+        _lib.call("stk_sparse_mla_tc", q, q.stride(0), swa_cache.buf, swa_cache.page_stride, cc.buf, cc.page_stride,
+                  swa_slots, swa_slots.stride(0), swa_lens, topk_slots,
+                  topk_slots.stride(0) if topk_slots is not None else 0, topk_lens, ws, n_splits, t, nh, d,
+                  swa_cache.rope_dim, max_rows, float(scale), _lib.status_buffer(), MLA_TRACE, _lib.stream())
+        _lib.call("stk_sparse_mla_combine", ws, sink, out, out.stride(0), t, nh, d, n_splits, _lib.stream())
+        return out
     n_splits = _lib.query("stk_sparse_mla_pick_splits", t, max_rows)
     ws = scratch("mla.partial", (t * n_splits * nh * (d + 2),), F32, q.device)
     out = torch.empty(t, nh, d, dtype=BF16, device=q.device)
-    cc = comp_cache if comp_cache is not None else swa_cache
     _lib.call("stk_sparse_mla", q, q.stride(0), swa_cache.buf, swa_cache.page_stride, swa_cache.data_bytes, cc.buf,
               cc.page_stride, cc.data_bytes, 1 if swa_cache.fp8 else 0, swa_slots, swa_slots.stride(0), swa_lens,
               topk_slots, topk_slots.stride(0) if topk_slots is not None else 0, topk_lens, sink, out, out.stride(0), ws,
