@@ -135,11 +135,10 @@ class Scheduler:
         return len(self.waiting)
 
 
-class StepBuffers:
-    """Pinned host staging + fixed-address device tensors for the step description."""
+class HostStage:
+    """One set of pinned staging buffers with numpy views (cheap element writes from Python)."""
 
-    def __init__(self, max_tokens: int, max_reqs: int, device):
-        pin = torch.device(device).type == "cuda"
+    def __init__(self, max_tokens: int, max_reqs: int, pin: bool):
         mk = lambda n, dt: torch.zeros(n, dtype=dt, pin_memory=pin)
         self.h_tokens = mk(max_tokens, torch.int64)
         self.h_qstart = mk(max_reqs + 1, torch.int32)
@@ -149,15 +148,35 @@ class StepBuffers:
         self.h_temp = mk(max_reqs, torch.float32)
         self.h_seed = mk(max_reqs, torch.int64)
         self.h_pos = mk(max_reqs, torch.int64)
-        dv = lambda h: torch.zeros_like(h, device=device)
-        self.d_tokens, self.d_qstart, self.d_rows, self.d_start = dv(self.h_tokens), dv(self.h_qstart), dv(self.h_rows), dv(self.h_start)
-        self.d_logit_rows, self.d_temp, self.d_seed, self.d_pos = dv(self.h_logit_rows), dv(self.h_temp), dv(self.h_seed), dv(self.h_pos)
-        self.h_out = mk(max_reqs, torch.int64)
-        # numpy views of the pinned staging buffers (cheap element writes from Python)
         self.n_tokens, self.n_qstart, self.n_rows, self.n_start = (self.h_tokens.numpy(), self.h_qstart.numpy(),
                                                                    self.h_rows.numpy(), self.h_start.numpy())
         self.n_logit_rows, self.n_temp, self.n_seed, self.n_pos = (self.h_logit_rows.numpy(), self.h_temp.numpy(),
                                                                    self.h_seed.numpy(), self.h_pos.numpy())
+        self.event = None           # recorded after the uploads that read this set
+
+
+class StepBuffers:
+    """Two pinned host staging sets (the host may prepare step k+1 while the copies of step k are
+    still queued) + fixed-address device tensors for the step description."""
+
+    def __init__(self, max_tokens: int, max_reqs: int, device):
+        pin = torch.device(device).type == "cuda"
+        self.stages = [HostStage(max_tokens, max_reqs, pin) for _ in range(2)]
+        self.parity = 0
+        h = self.stages[0]
+        dv = lambda x: torch.zeros_like(x, device=device)
+        self.d_tokens, self.d_qstart, self.d_rows, self.d_start = dv(h.h_tokens), dv(h.h_qstart), dv(h.h_rows), dv(h.h_start)
+        self.d_logit_rows, self.d_temp, self.d_seed, self.d_pos = dv(h.h_logit_rows), dv(h.h_temp), dv(h.h_seed), dv(h.h_pos)
+        self.h_out = torch.zeros(max_reqs, dtype=torch.int64, pin_memory=pin)
+        self.cuda = pin
+
+    def next_stage(self) -> HostStage:
+        """The staging set for the next step, once no earlier upload still reads it."""
+        self.parity ^= 1
+        st = self.stages[self.parity]
+        if st.event is not None:
+            st.event.synchronize()
+        return st
 
     def h2d_bytes(self, t: int, n: int) -> int:
         return t * 8 + (n + 1) * 4 + n * 4 * 2 + n * 8 * 3 + n * 4
@@ -212,7 +231,7 @@ class Engine:
     # ---- one step -----------------------------------------------------------------
     def _stage(self, seqs: List[ScheduledSeq]) -> Tuple[int, int, int]:
         """Fill the pinned staging buffers; returns (T, n_req, n_samples)."""
-        b = self.buf
+        b = self.buf.next_stage()
         t = 0
         ns = 0
         for i, s in enumerate(seqs):
@@ -233,19 +252,24 @@ class Engine:
         return t, len(seqs), ns
 
     def _upload(self, t: int, n: int, ns: int) -> None:
-        b = self.buf
+        d = self.buf
+        b = d.stages[d.parity]
         nb = True
-        b.d_tokens[:t].copy_(b.h_tokens[:t], non_blocking=nb)
-        b.d_qstart[:n + 1].copy_(b.h_qstart[:n + 1], non_blocking=nb)
-        b.d_rows[:n].copy_(b.h_rows[:n], non_blocking=nb)
-        b.d_start[:n].copy_(b.h_start[:n], non_blocking=nb)
+        d.d_tokens[:t].copy_(b.h_tokens[:t], non_blocking=nb)
+        d.d_qstart[:n + 1].copy_(b.h_qstart[:n + 1], non_blocking=nb)
+        d.d_rows[:n].copy_(b.h_rows[:n], non_blocking=nb)
+        d.d_start[:n].copy_(b.h_start[:n], non_blocking=nb)
         if ns:
-            b.d_logit_rows[:ns].copy_(b.h_logit_rows[:ns], non_blocking=nb)
-            b.d_temp[:ns].copy_(b.h_temp[:ns], non_blocking=nb)
-            b.d_seed[:ns].copy_(b.h_seed[:ns], non_blocking=nb)
-            b.d_pos[:ns].copy_(b.h_pos[:ns], non_blocking=nb)
-        self.kv.sync()
-        self.h2d_bytes_last = b.h2d_bytes(t, n)
+            d.d_logit_rows[:ns].copy_(b.h_logit_rows[:ns], non_blocking=nb)
+            d.d_temp[:ns].copy_(b.h_temp[:ns], non_blocking=nb)
+            d.d_seed[:ns].copy_(b.h_seed[:ns], non_blocking=nb)
+            d.d_pos[:ns].copy_(b.h_pos[:ns], non_blocking=nb)
+        self.kv.sync(d.parity)
+        if d.cuda:
+            if b.event is None:
+                b.event = torch.cuda.Event()
+            b.event.record()
+        self.h2d_bytes_last = d.h2d_bytes(t, n)
 
     def _build_meta(self, t_pad: int, n_req: int, max_comp_rows: int) -> StepMeta:
         b = self.buf

@@ -51,7 +51,13 @@ class GroupTable:
         self.table_host = torch.full((self.max_requests, self.max_pages_per_req), -1, dtype=torch.int32)
         if self.device.type == "cuda":
             self.table_host = self.table_host.pin_memory()
-        self.table_np = self.table_host.numpy()          # shares memory with the pinned tensor
+        self.table_np = self.table_host.numpy()          # host truth; never read by an async copy
+        # upload snapshots: the DMA of step k may run while the host already edits the table for step
+        # k+1, so rows are copied into one of two pinned snapshots and uploaded from there
+        self.snap = [torch.full_like(self.table_host, -1) for _ in range(2)]
+        if self.device.type == "cuda":
+            self.snap = [t.pin_memory() for t in self.snap]
+        self.snap_np = [t.numpy() for t in self.snap]
         self.table_dev = torch.full((self.max_requests, self.max_pages_per_req), -1, dtype=torch.int32,
                                     device=self.device)
         self.free = list(range(self.num_pages - 1, -1, -1))
@@ -95,14 +101,18 @@ class GroupTable:
         self.release_before(row, self.max_pages_per_req)
         self.lo[row] = self.hi[row] = 0
 
-    def sync(self) -> None:
-        """Upload the rows that changed since the last step."""
+    def sync(self, parity: int = 0) -> None:
+        """Upload the rows that changed since the last step (through pinned snapshot `parity`, which
+        the caller guarantees is no longer being read by an earlier upload)."""
         if self.dirty:
+            snap, snap_np = self.snap[parity], self.snap_np[parity]
             if len(self.dirty_rows) * 4 >= self.max_requests:
-                self.table_dev.copy_(self.table_host, non_blocking=True)
+                snap_np[:] = self.table_np
+                self.table_dev.copy_(snap, non_blocking=True)
             else:
                 for r in self.dirty_rows:
-                    self.table_dev[r].copy_(self.table_host[r], non_blocking=True)
+                    snap_np[r] = self.table_np[r]
+                    self.table_dev[r].copy_(snap[r], non_blocking=True)
             self.dirty_rows.clear()
             self.dirty = False
 
@@ -185,9 +195,9 @@ class KVManager:
         need_c4 = (context // 4) // PAGE + 1
         return bool(self.free_rows) and len(self.swa.free) >= need_swa and len(self.c4.free) >= need_c4
 
-    def sync(self) -> None:
+    def sync(self, parity: int = 0) -> None:
         for g in (self.swa, self.c4, self.c128):
-            g.sync()
+            g.sync(parity)
 
     def bytes_allocated(self) -> int:
         n = 0
