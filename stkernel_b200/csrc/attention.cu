@@ -189,9 +189,12 @@ sparse_mla_split_kernel(MlaArgs a) {
   }
 }
 
-// grid (T, nh); merges splits, adds the sink to the denominator, writes bf16.
+// grid (T, nh); merges splits, adds the sink to the denominator, optionally applies the inverse
+// RoPE on the last R dims (the rotation the output projection expects), writes bf16.
 __global__ void sparse_mla_combine_kernel(const float* __restrict__ partial, const float* __restrict__ sink,
-                                          __nv_bfloat16* __restrict__ out, long long ldo, int nh, int D, int n_splits) {
+                                          __nv_bfloat16* __restrict__ out, long long ldo, int nh, int D, int n_splits,
+                                          const int64_t* __restrict__ positions, const float* __restrict__ inv_freq,
+                                          int R) {
   const int t = blockIdx.x, h = blockIdx.y;
   const float* base = partial + (static_cast<long long>(t) * n_splits * nh + h) * (D + 2);
   const long long sstride = static_cast<long long>(nh) * (D + 2);
@@ -203,13 +206,32 @@ __global__ void sparse_mla_combine_kernel(const float* __restrict__ partial, con
     if (ms != -INFINITY) denom += base[s * sstride + D + 1] * __expf(ms - M);
   }
   const float inv = denom > 0.f ? 1.f / denom : 0.f;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float o = 0.f;
+  const int nope = D - R;
+  const float pos = positions ? static_cast<float>(positions[t]) : 0.f;
+  for (int d = threadIdx.x * 2; d < D; d += blockDim.x * 2) {
+    float o0 = 0.f, o1 = 0.f;
     for (int s = 0; s < n_splits; ++s) {
       const float ms = base[s * sstride + D];
-      if (ms != -INFINITY) o += base[s * sstride + d] * __expf(ms - M);
+      if (ms != -INFINITY) {
+        const float w = __expf(ms - M);
+        o0 = fmaf(base[s * sstride + d], w, o0);
+        o1 = fmaf(base[s * sstride + d + 1], w, o1);
+      }
     }
-    out[t * ldo + static_cast<long long>(h) * D + d] = __float2bfloat16(o * inv);
+    o0 *= inv;
+    o1 *= inv;
+    if (positions != nullptr && d >= nope) {
+      // round to bf16 first: the un-fused path stores the attention output before rotating it
+      o0 = __bfloat162float(__float2bfloat16(o0));
+      o1 = __bfloat162float(__float2bfloat16(o1));
+      float sn, cs;
+      sincosf(pos * inv_freq[(d - nope) >> 1], &sn, &cs);
+      const float x = o0 * cs + o1 * sn;
+      const float y = -o0 * sn + o1 * cs;
+      o0 = x;
+      o1 = y;
+    }
+    *reinterpret_cast<__nv_bfloat162*>(out + t * ldo + static_cast<long long>(h) * D + d) = __floats2bfloat162_rn(o0, o1);
   }
 }
 
@@ -271,14 +293,17 @@ STK_API int stk_sparse_mla(const void* q, long long ldt, const void* swa_cache, 
   }
 #undef STK_MLA
   dim3 g2(T, nh);
-  sparse_mla_combine_kernel<<<g2, 128, 0, st>>>(workspace, sink, (__nv_bfloat16*)out, ldo, nh, D, n_splits);
+  sparse_mla_combine_kernel<<<g2, 128, 0, st>>>(workspace, sink, (__nv_bfloat16*)out, ldo, nh, D, n_splits, nullptr, nullptr, 0);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
 STK_API int stk_sparse_mla_combine(const float* workspace, const float* sink, void* out, long long ldo, int T, int nh,
-                                   int D, int n_splits, void* stream) {
+                                   int D, int n_splits, const int64_t* positions, const float* inv_freq, int R,
+                                   void* stream) {
   if (T <= 0) return 0;
+  if (D % 2) return -1;
   dim3 g2(T, nh);
-  sparse_mla_combine_kernel<<<g2, 128, 0, (cudaStream_t)stream>>>(workspace, sink, (__nv_bfloat16*)out, ldo, nh, D, n_splits);
+  sparse_mla_combine_kernel<<<g2, 128, 0, (cudaStream_t)stream>>>(workspace, sink, (__nv_bfloat16*)out, ldo, nh, D, n_splits,
+                                                                  positions, inv_freq, R);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -32,10 +32,10 @@ __device__ __forceinline__ void rope_pair(float& a, float& b, float pos, float i
 }
 
 // q [T, nh, D] in place.  One warp per (token, head).
-__global__ void q_norm_rope_kernel(__nv_bfloat16* __restrict__ q, long long ldt, const int64_t* __restrict__ positions,
-                                   const float* __restrict__ inv_freq, int T, int nh, int D, int R, float eps,
-                                   int do_norm, int inverse) {
-  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+__device__ __forceinline__ void q_norm_rope_body(int block, __nv_bfloat16* __restrict__ q, long long ldt,
+                                                 const int64_t* __restrict__ positions, const float* __restrict__ inv_freq,
+                                                 int T, int nh, int D, int R, float eps, int do_norm, int inverse) {
+  const int w = (block * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (w >= T * nh) return;
   const int t = w / nh, h = w % nh;
@@ -57,6 +57,12 @@ __global__ void q_norm_rope_kernel(__nv_bfloat16* __restrict__ q, long long ldt,
     if (i >= nope) rope_pair(a, b, pos, inv_freq[(i - nope) >> 1], inverse != 0);
     *reinterpret_cast<__nv_bfloat162*>(row + i) = __floats2bfloat162_rn(a, b);
   }
+}
+
+__global__ void q_norm_rope_kernel(__nv_bfloat16* __restrict__ q, long long ldt, const int64_t* __restrict__ positions,
+                                   const float* __restrict__ inv_freq, int T, int nh, int D, int R, float eps,
+                                   int do_norm, int inverse) {
+  q_norm_rope_body(blockIdx.x, q, ldt, positions, inv_freq, T, nh, D, R, eps, do_norm, inverse);
 }
 
 struct CacheGeom {
@@ -98,13 +104,13 @@ __device__ __forceinline__ void write_latent_row(const CacheGeom& c, long long s
 }
 
 // kv [T, D] bf16 (already normed).  One warp per token; slot -1 = padding (skipped).
-__global__ void kv_rope_quant_insert_kernel(const __nv_bfloat16* __restrict__ kv, long long ldk,
-                                            const int64_t* __restrict__ positions, const int64_t* __restrict__ slots,
-                                            const float* __restrict__ inv_freq, CacheGeom cache, int T, int D, int R,
-                                            long long num_slots, int* status) {
-  extern __shared__ float sm[];
+__device__ __forceinline__ void kv_rope_quant_insert_body(int block, float* sm, const __nv_bfloat16* __restrict__ kv,
+                                                          long long ldk, const int64_t* __restrict__ positions,
+                                                          const int64_t* __restrict__ slots,
+                                                          const float* __restrict__ inv_freq, const CacheGeom& cache,
+                                                          int T, int D, int R, long long num_slots, int* status) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  const int t = block * (blockDim.x >> 5) + warp;
   if (t >= T) return;
   const long long slot = slots[t];
   if (slot < 0) return;
@@ -128,6 +134,31 @@ __global__ void kv_rope_quant_insert_kernel(const __nv_bfloat16* __restrict__ kv
   }
   __syncwarp();
   write_latent_row(cache, slot, vals, D, R, lane);
+}
+
+__global__ void kv_rope_quant_insert_kernel(const __nv_bfloat16* __restrict__ kv, long long ldk,
+                                            const int64_t* __restrict__ positions, const int64_t* __restrict__ slots,
+                                            const float* __restrict__ inv_freq, CacheGeom cache, int T, int D, int R,
+                                            long long num_slots, int* status) {
+  extern __shared__ float sm[];
+  kv_rope_quant_insert_body(blockIdx.x, sm, kv, ldk, positions, slots, inv_freq, cache, T, D, R, num_slots, status);
+}
+
+// One launch for both halves of the step's "write" work: blocks [0, q_blocks) norm + rotate Q in place,
+// the rest rotate, quantise and insert the latent rows.  (The reference's horizontally fused
+// qnorm/rope/kv-insert custom op: overlay/attention.py:704-729.)
+__global__ void __launch_bounds__(256)
+q_rope_kv_insert_kernel(__nv_bfloat16* __restrict__ q, long long ldt, int nh, float eps, int q_blocks,
+                        const __nv_bfloat16* __restrict__ kv, long long ldk, const int64_t* __restrict__ positions,
+                        const int64_t* __restrict__ slots, const float* __restrict__ inv_freq, CacheGeom cache, int T,
+                        int D, int R, long long num_slots, int* status) {
+  extern __shared__ float sm[];
+  if (static_cast<int>(blockIdx.x) < q_blocks) {
+    q_norm_rope_body(blockIdx.x, q, ldt, positions, inv_freq, T, nh, D, R, eps, 1, 0);
+  } else {
+    kv_rope_quant_insert_body(blockIdx.x - q_blocks, sm, kv, ldk, positions, slots, inv_freq, cache, T, D, R, num_slots,
+                              status);
+  }
 }
 
 // rows[i, :] = dequant(cache row slots[i]); slot < 0 -> zeros.  One warp per row.
@@ -361,6 +392,21 @@ STK_API int stk_kv_rope_quant_insert(const void* kv, long long ldk, const int64_
   const int wpb = 4;
   kv_rope_quant_insert_kernel<<<(T + wpb - 1) / wpb, wpb * 32, wpb * D * sizeof(float), (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)kv, ldk, positions, slots, inv_freq, g, T, D, R, num_slots, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+STK_API int stk_q_rope_kv_insert(void* q, long long ldt, int nh, float eps, const void* kv, long long ldk,
+                                 const int64_t* positions, const int64_t* slots, const float* inv_freq, void* cache,
+                                 long long page_stride, int data_bytes, int fp8, long long num_slots, int T, int D, int R,
+                                 int* status, void* stream) {
+  if (T <= 0) return 0;
+  if (D % 2 || R % 2 || (fp8 && ((D - R) % 64 || (D - R) / 64 > 8))) return -1;
+  CacheGeom g{(uint8_t*)cache, page_stride, data_bytes, fp8};
+  const int q_blocks = static_cast<int>((static_cast<long long>(T) * nh + 7) / 8);
+  const int kv_blocks = (T + 7) / 8;
+  q_rope_kv_insert_kernel<<<q_blocks + kv_blocks, 256, 8 * D * sizeof(float), (cudaStream_t)stream>>>(
+      (__nv_bfloat16*)q, ldt, nh, eps, q_blocks, (const __nv_bfloat16*)kv, ldk, positions, slots, inv_freq, g, T, D, R,
+      num_slots, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

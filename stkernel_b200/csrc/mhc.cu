@@ -329,3 +329,231 @@ STK_API int stk_mhc_post(const void* x, const void* res, const float* post, cons
   else return -2;
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Decode-sized batches: the whole mHC pre step (or hc_head) in ONE launch.  A thread-block cluster of
+// 8 CTAs serves one token; the split dot products and both sums of squares are exchanged through
+// distributed shared memory, so there is no partial buffer in global memory and no second kernel.
+// ---------------------------------------------------------------------------------------------
+#include <cooperative_groups.h>
+
+namespace stk {
+namespace cg = cooperative_groups;
+
+constexpr int kClusterSize = 8;
+
+template <int NMIX>
+__global__ void __launch_bounds__(256)
+mhc_cluster_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ fn, const float* __restrict__ base,
+                   const float* __restrict__ scale, const __nv_bfloat16* __restrict__ norm_w, float* __restrict__ post,
+                   float* __restrict__ comb, __nv_bfloat16* __restrict__ y, int H, int hc, float rms_eps, float hc_eps,
+                   int sinkhorn_iters, float post_mult, int mode, uint8_t* q_out, float* q_scale, int q_scale_ld) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const int crank = static_cast<int>(cluster.block_rank());
+  const int t = blockIdx.x / kClusterSize;
+  __shared__ float part[NMIX + 1];          // this CTA's partial dots + sum x^2 (read by the peers)
+  __shared__ float part2[1];                // this CTA's partial sum y^2
+  __shared__ float red[8][NMIX + 1];
+  __shared__ float mixes[NMIX + 1];
+  __shared__ float pre[8];
+  __shared__ float gmax[8];
+  const int HC = H * hc;
+  const __nv_bfloat16* xt = x + static_cast<long long>(t) * HC;
+  const int slice = ((HC / kClusterSize) + 1) & ~1;
+  const int k0 = crank * slice, k1 = min(HC, k0 + slice);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ---- phase 1: partial dot products over this CTA's slice ----
+  float acc[NMIX];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < NMIX; ++j) acc[j] = 0.f;
+  for (int k = k0 + threadIdx.x * 2; k < k1; k += blockDim.x * 2) {
+    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(xt + k);
+    const float xa = __low2float(v), xb = __high2float(v);
+    ss = fmaf(xa, xa, fmaf(xb, xb, ss));
+#pragma unroll
+    for (int j = 0; j < NMIX; ++j) {
+      const float2 f = __ldg(reinterpret_cast<const float2*>(fn + static_cast<long long>(j) * HC + k));
+      acc[j] = fmaf(xa, f.x, fmaf(xb, f.y, acc[j]));
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < NMIX; ++j) {
+    const float v = warp_sum(acc[j]);
+    if (lane == 0) red[warp][j] = v;
+  }
+  {
+    const float v = warp_sum(ss);
+    if (lane == 0) red[warp][NMIX] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x <= NMIX) {
+    float s = 0.f;
+    for (int w = 0; w < 8; ++w) s += red[w][threadIdx.x];
+    part[threadIdx.x] = s;
+  }
+  cluster.sync();
+  if (threadIdx.x <= NMIX) {
+    float s = 0.f;
+    for (int r = 0; r < kClusterSize; ++r) s += cluster.map_shared_rank(part, r)[threadIdx.x];
+    mixes[threadIdx.x] = s;
+  }
+  __syncthreads();
+  const float rms = rsqrtf(mixes[NMIX] / static_cast<float>(HC) + rms_eps);
+
+  // ---- phase 2: mixes -> pre / post / Sinkhorn combine (every CTA computes them; rank 0 stores) ----
+  if (threadIdx.x < 32) {
+    if (mode == 0) {
+      if (lane < hc) {
+        pre[lane] = 1.f / (1.f + __expf(-(mixes[lane] * rms * scale[0] + base[lane]))) + hc_eps;
+        if (crank == 0) post[t * hc + lane] = post_mult / (1.f + __expf(-(mixes[hc + lane] * rms * scale[1] + base[hc + lane])));
+      }
+      const int j = lane / hc, k = lane % hc;
+      const bool act = lane < hc * hc;
+      float c = act ? mixes[2 * hc + lane] * rms * scale[2] + base[2 * hc + lane] : -INFINITY;
+      float rmax = c;
+      for (int o = 1; o < hc; ++o) {
+        const float other = __shfl_sync(0xffffffffu, c, j * hc + ((k + o) % hc));
+        if (act) rmax = fmaxf(rmax, other);
+      }
+      const float e = act ? __expf(c - rmax) : 0.f;
+      float rs = e;
+      for (int o = 1; o < hc; ++o) {
+        const float other = __shfl_sync(0xffffffffu, e, j * hc + ((k + o) % hc));
+        if (act) rs += other;
+      }
+      c = act ? e / rs + hc_eps : 0.f;
+      // neighbour lanes of this matrix entry along its row and its column (fixed for the whole loop)
+      int row_src[4], col_src[4];
+#pragma unroll
+      for (int o = 1; o < 4; ++o) {
+        row_src[o] = j * hc + ((k + o) % hc);
+        col_src[o] = ((j + o) % hc) * hc + k;
+      }
+      for (int it = 0; it < 2 * sinkhorn_iters - 1; ++it) {
+        // even steps normalise columns, odd steps rows
+        const bool col = (it & 1) == 0;
+        float s = c;
+        if (hc == 4) {
+          const float a1 = __shfl_sync(0xffffffffu, c, col ? col_src[1] : row_src[1]);
+          const float a2 = __shfl_sync(0xffffffffu, c, col ? col_src[2] : row_src[2]);
+          const float a3 = __shfl_sync(0xffffffffu, c, col ? col_src[3] : row_src[3]);
+          s = (c + a1) + (a2 + a3);
+        } else {
+          for (int o = 1; o < hc; ++o) {
+            const int src = col ? ((j + o) % hc) * hc + k : j * hc + ((k + o) % hc);
+            const float other = __shfl_sync(0xffffffffu, c, src);
+            s += other;
+          }
+        }
+        if (act) c = __fdividef(c, s + hc_eps);
+      }
+      if (act && crank == 0) comb[t * hc * hc + lane] = c;
+    } else {
+      if (lane < hc) pre[lane] = 1.f / (1.f + __expf(-(mixes[lane] * rms * scale[0] + base[lane]))) + hc_eps;
+    }
+  }
+  __syncthreads();
+
+  // ---- phase 3: weighted stream sum over this CTA's columns, cluster-wide RMSNorm ----
+  const int cols = ((H / kClusterSize) + 1) & ~1;
+  const int c0 = crank * cols, c1 = min(H, c0 + cols);
+  constexpr int kMaxPer = 4;                           // column pairs per thread (H <= 8 * 256 * 2 * 4)
+  float ya[kMaxPer], yb[kMaxPer];
+  float ss2 = 0.f;
+#pragma unroll
+  for (int u = 0; u < kMaxPer; ++u) {
+    const int i = c0 + (u * 256 + threadIdx.x) * 2;
+    ya[u] = yb[u] = 0.f;
+    if (i < c1) {
+      float a0 = 0.f, a1 = 0.f;
+      for (int j = 0; j < hc; ++j) {
+        const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(xt + static_cast<long long>(j) * H + i);
+        a0 = fmaf(pre[j], __low2float(v), a0);
+        a1 = fmaf(pre[j], __high2float(v), a1);
+      }
+      if (mode == 0) {
+        a0 = bf16_to_f(__float2bfloat16(a0));
+        a1 = bf16_to_f(__float2bfloat16(a1));
+      }
+      ya[u] = a0;
+      yb[u] = a1;
+      ss2 = fmaf(a0, a0, fmaf(a1, a1, ss2));
+    }
+  }
+  float r = 1.f;
+  const bool do_norm = mode == 0 && norm_w != nullptr;
+  if (do_norm) {
+    const float v = warp_sum(ss2);
+    if (lane == 0) red[warp][0] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float s = 0.f;
+      for (int w = 0; w < 8; ++w) s += red[w][0];
+      part2[0] = s;
+    }
+    cluster.sync();
+    float tot = 0.f;
+    for (int rr = 0; rr < kClusterSize; ++rr) tot += cluster.map_shared_rank(part2, rr)[0];
+    r = rsqrtf(tot / H + rms_eps);
+  }
+#pragma unroll
+  for (int u = 0; u < kMaxPer; ++u) {
+    const int i = c0 + (u * 256 + threadIdx.x) * 2;
+    if (i < c1) {
+      float a0 = ya[u] * r, a1 = yb[u] * r;
+      if (do_norm) {
+        a0 *= bf16_to_f(norm_w[i]);
+        a1 *= bf16_to_f(norm_w[i + 1]);
+      }
+      const __nv_bfloat162 o = __floats2bfloat162_rn(a0, a1);
+      *reinterpret_cast<__nv_bfloat162*>(y + static_cast<long long>(t) * H + i) = o;
+      ya[u] = __low2float(o);
+      yb[u] = __high2float(o);
+    }
+  }
+  // keep this CTA's shared memory alive until every peer has read it
+  cluster.sync();
+  (void)q_out; (void)q_scale; (void)q_scale_ld; (void)gmax;
+}
+
+}  // namespace stk
+
+STK_API int stk_mhc_cluster(const void* x, const float* fn, const float* base, const float* scale, const void* norm_w,
+                            float* post, float* comb, void* y, int T, int H, int hc, int n_mix, float rms_eps,
+                            float hc_eps, int sinkhorn_iters, float post_mult, int mode, void* stream) {
+  if (T <= 0) return 0;
+  if (hc * hc > 32 || H % 2 || H > kClusterSize * 256 * 2 * 4 || (H * hc) % 2) return -1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(T * kClusterSize);
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kClusterSize;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
+  const __nv_bfloat16* nw = (const __nv_bfloat16*)norm_w;
+  __nv_bfloat16* yp = (__nv_bfloat16*)y;
+  uint8_t* qn = nullptr;
+  float* qs = nullptr;
+  int qld = 0;
+  cudaError_t e;
+  if (n_mix == 24)
+    e = cudaLaunchKernelEx(&cfg, mhc_cluster_kernel<24>, xp, fn, base, scale, nw, post, comb, yp, H, hc, rms_eps, hc_eps,
+                           sinkhorn_iters, post_mult, mode, qn, qs, qld);
+  else if (n_mix == 4)
+    e = cudaLaunchKernelEx(&cfg, mhc_cluster_kernel<4>, xp, fn, base, scale, nw, post, comb, yp, H, hc, rms_eps, hc_eps,
+                           sinkhorn_iters, post_mult, mode, qn, qs, qld);
+  else if (n_mix == 8)
+    e = cudaLaunchKernelEx(&cfg, mhc_cluster_kernel<8>, xp, fn, base, scale, nw, post, comb, yp, H, hc, rms_eps, hc_eps,
+                           sinkhorn_iters, post_mult, mode, qn, qs, qld);
+  else
+    return -2;
+  return e == cudaSuccess ? 0 : -4;
+}

@@ -145,15 +145,36 @@ moe_align_kernel(const int* __restrict__ ids, int n_pairs, int e_start, int e_lo
 // ---- NVFP4 row dot --------------------------------------------------------------------
 // xs: activations as half, permuted so that (iteration k, quarter i, lane) is one uint4:
 //   chunk c = lane + 32*k covers values [32c, 32c+32); uint4 index = (k*4 + i)*32 + lane.
-__device__ __forceinline__ float fp4_row_dot(const uint8_t* __restrict__ wrow, const uint8_t* __restrict__ srow,
-                                             const uint4* __restrict__ xs, int n_chunks, int lane) {
+// A row is read in two steps so that several rows' loads can be in flight before any arithmetic.
+template <int ITERS>
+struct Fp4Row {
+  uint4 w[ITERS];
+  uint32_t s[ITERS];
+};
+
+template <int ITERS>
+__device__ __forceinline__ void fp4_row_load(Fp4Row<ITERS>& r, const uint8_t* __restrict__ wrow,
+                                             const uint8_t* __restrict__ srow, int n_chunks, int lane) {
+#pragma unroll
+  for (int k = 0; k < ITERS; ++k) {
+    const int c = k * 32 + lane;
+    r.w[k] = make_uint4(0, 0, 0, 0);
+    r.s[k] = 0;
+    if (c < n_chunks) {
+      r.w[k] = __ldg(reinterpret_cast<const uint4*>(wrow) + c);
+      r.s[k] = __ldg(reinterpret_cast<const uint16_t*>(srow) + c);
+    }
+  }
+}
+
+template <int ITERS>
+__device__ __forceinline__ float fp4_row_dot(const Fp4Row<ITERS>& r, const uint4* __restrict__ xs, int n_chunks, int lane) {
   float acc = 0.f;
-  for (int k = 0; k * 32 < n_chunks; ++k) {
+#pragma unroll
+  for (int k = 0; k < ITERS; ++k) {
     const int c = k * 32 + lane;
     if (c < n_chunks) {
-      const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wrow) + c);
-      const uint16_t s2 = __ldg(reinterpret_cast<const uint16_t*>(srow) + c);
-      const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
+      const uint32_t words[4] = {r.w[k].x, r.w[k].y, r.w[k].z, r.w[k].w};
       float part[2];
 #pragma unroll
       for (int g = 0; g < 2; ++g) {
@@ -171,8 +192,8 @@ __device__ __forceinline__ float fp4_row_dot(const uint8_t* __restrict__ wrow, c
         }
         part[g] = __low2float(hs) + __high2float(hs);
       }
-      acc = fmaf(part[0], fp8_to_f(s2 & 0xff), acc);
-      acc = fmaf(part[1], fp8_to_f(s2 >> 8), acc);
+      acc = fmaf(part[0], fp8_to_f(r.s[k] & 0xff), acc);
+      acc = fmaf(part[1], fp8_to_f((r.s[k] >> 8) & 0xff), acc);
     }
   }
   return warp_sum(acc);
@@ -182,14 +203,32 @@ __device__ __forceinline__ float src_to_f(__nv_bfloat16 v) { return __bfloat162f
 __device__ __forceinline__ float src_to_f(__half v) { return __half2float(v); }
 
 // Fill the permuted half activation buffer from a bf16 or half row.  The buffer holds
-// ceil(K / 1024) * 1024 halfs (the permutation leaves holes when K < 1024).
+// ceil(K / 1024) * 1024 halfs (the permutation leaves holes when K < 1024).  Eight consecutive
+// values move as one 16-byte load and one 16-byte store.
+__device__ __forceinline__ uint4 to_half8(const uint4& v, const __nv_bfloat16*) {
+  uint4 o;
+  __half2* oh = reinterpret_cast<__half2*>(&o);
+  const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) oh[j] = __float22half2_rn(__bfloat1622float2(b[j]));
+  return o;
+}
+__device__ __forceinline__ uint4 to_half8(const uint4& v, const __half*) { return v; }
+
 template <typename SrcT>
 __device__ __forceinline__ void fill_xs(__half* xs_h, const SrcT* x, int K) {
-  for (int e = threadIdx.x; e < K; e += blockDim.x) {
-    const int c = e >> 5, within = e & 31;
-    const int k = c >> 5, lane = c & 31;
-    const int i = within >> 3, b = within & 7;
-    xs_h[((k * 4 + i) * 32 + lane) * 8 + b] = __float2half(src_to_f(x[e]));
+  uint4* xs4 = reinterpret_cast<uint4*>(xs_h);
+  if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    for (int k8 = threadIdx.x; k8 < (K >> 3); k8 += blockDim.x) {
+      const uint4 v = *reinterpret_cast<const uint4*>(x + k8 * 8);
+      const int c = k8 >> 2;                               // 32-value chunk
+      xs4[((c >> 5) * 4 + (k8 & 3)) * 32 + (c & 31)] = to_half8(v, x);
+    }
+  } else {
+    for (int e = threadIdx.x; e < K; e += blockDim.x) {
+      const int c = e >> 5, within = e & 31;
+      xs_h[(((c >> 5) * 4 + (within >> 3)) * 32 + (c & 31)) * 8 + (within & 7)] = __float2half(src_to_f(x[e]));
+    }
   }
 }
 
@@ -200,16 +239,25 @@ struct ExpertW {
 };
 
 // grid (ceil(I / 16), n_rows); CTA = 8 warps, 2 outputs per warp.
+template <int ITERS>
 __global__ void __launch_bounds__(256)
 expert_fc1_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, ExpertW w13, const int* __restrict__ sorted,
                   const int* __restrict__ sorted_expert, const int* __restrict__ offsets, int e_local, int topk,
-                  __half* __restrict__ act, int H, int I, float limit) {
+                  __half* __restrict__ act, int H, int I, float limit, const int* __restrict__ direct_ids,
+                  int e_start) {
   extern __shared__ uint4 xs[];
-  const int n_rows = offsets[e_local];
   const int row = blockIdx.y;
-  if (row >= n_rows) return;
-  const int pair = sorted[row];
-  const int e = sorted_expert[row];
+  int pair, e;
+  if (direct_ids != nullptr) {
+    // direct mode (a handful of pairs): row = pair index, no sort; non-local experts are skipped
+    pair = row;
+    e = direct_ids[row] - e_start;
+    if (e < 0 || e >= e_local) return;
+  } else {
+    if (row >= offsets[e_local]) return;
+    pair = sorted[row];
+    e = sorted_expert[row];
+  }
   const int t = pair / topk;
   fill_xs(reinterpret_cast<__half*>(xs), x + t * ldx, H);
   __syncthreads();
@@ -219,12 +267,20 @@ expert_fc1_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, ExpertW w1
   const long long wstride = static_cast<long long>(H) / 2, sstride = static_cast<long long>(H) / 16;
   const uint8_t* wbase = w13.w + static_cast<long long>(e) * 2 * I * wstride;
   const uint8_t* sbase = w13.s + static_cast<long long>(e) * 2 * I * sstride;
+  // the four weight rows of this warp (gate and up of two outputs) are all loaded before any arithmetic
+  Fp4Row<ITERS> rg[2], ru[2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int i = min(blockIdx.x * 16 + warp * 2 + j, I - 1);
+    fp4_row_load<ITERS>(rg[j], wbase + i * wstride, sbase + i * sstride, n_chunks, lane);
+    fp4_row_load<ITERS>(ru[j], wbase + (I + i) * wstride, sbase + (I + i) * sstride, n_chunks, lane);
+  }
+#pragma unroll
   for (int j = 0; j < 2; ++j) {
     const int i = blockIdx.x * 16 + warp * 2 + j;
-    if (i >= I) break;
-    float g = fp4_row_dot(wbase + i * wstride, sbase + i * sstride, xs, n_chunks, lane) * gs;
-    float u = fp4_row_dot(wbase + (I + i) * wstride, sbase + (I + i) * sstride, xs, n_chunks, lane) * gs;
-    if (lane == 0) {
+    float g = fp4_row_dot<ITERS>(rg[j], xs, n_chunks, lane) * gs;
+    float u = fp4_row_dot<ITERS>(ru[j], xs, n_chunks, lane) * gs;
+    if (lane == 0 && i < I) {
       if (limit > 0.f) {
         g = fminf(g, limit);
         u = fminf(fmaxf(u, -limit), limit);
@@ -235,14 +291,26 @@ expert_fc1_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, ExpertW w1
 }
 
 // grid (ceil(H / 32), n_rows); 4 outputs per warp.
+template <int ITERS>
 __global__ void __launch_bounds__(256)
 expert_fc2_kernel(const __half* __restrict__ act, ExpertW w2, const int* __restrict__ sorted_expert,
-                  const int* __restrict__ offsets, int e_local, __nv_bfloat16* __restrict__ y, int H, int I) {
+                  const int* __restrict__ offsets, int e_local, __nv_bfloat16* __restrict__ y, int H, int I,
+                  const int* __restrict__ direct_ids, int e_start) {
   extern __shared__ uint4 xs[];
-  const int n_rows = offsets[e_local];
   const int row = blockIdx.y;
-  if (row >= n_rows) return;
-  const int e = sorted_expert[row];
+  int e;
+  if (direct_ids != nullptr) {
+    e = direct_ids[row] - e_start;
+    if (e < 0 || e >= e_local) {
+      // not a local expert: this pair contributes nothing on this rank
+      for (int n = blockIdx.x * 32 + threadIdx.x; n < min(H, blockIdx.x * 32 + 32); n += blockDim.x)
+        y[static_cast<long long>(row) * H + n] = __float2bfloat16(0.f);
+      return;
+    }
+  } else {
+    if (row >= offsets[e_local]) return;
+    e = sorted_expert[row];
+  }
   fill_xs(reinterpret_cast<__half*>(xs), act + static_cast<long long>(row) * I, I);
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -251,11 +319,17 @@ expert_fc2_kernel(const __half* __restrict__ act, ExpertW w2, const int* __restr
   const long long wstride = static_cast<long long>(I) / 2, sstride = static_cast<long long>(I) / 16;
   const uint8_t* wbase = w2.w + static_cast<long long>(e) * H * wstride;
   const uint8_t* sbase = w2.s + static_cast<long long>(e) * H * sstride;
+  Fp4Row<ITERS> rw[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int n = min(blockIdx.x * 32 + warp * 4 + j, H - 1);
+    fp4_row_load<ITERS>(rw[j], wbase + n * wstride, sbase + n * sstride, n_chunks, lane);
+  }
+#pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int n = blockIdx.x * 32 + warp * 4 + j;
-    if (n >= H) break;
-    const float v = fp4_row_dot(wbase + n * wstride, sbase + n * sstride, xs, n_chunks, lane) * gs;
-    if (lane == 0) y[static_cast<long long>(row) * H + n] = __float2bfloat16(v);
+    const float v = fp4_row_dot<ITERS>(rw[j], xs, n_chunks, lane) * gs;
+    if (lane == 0 && n < H) y[static_cast<long long>(row) * H + n] = __float2bfloat16(v);
   }
 }
 
@@ -285,24 +359,33 @@ STK_API int stk_moe_align(const int* ids, int n_pairs, int e_start, int e_local,
 // max_rows bounds the grid (rows beyond offsets[e_local] exit at once).
 STK_API int stk_moe_expert_fc1(const void* x, long long ldx, const void* w13, const void* s13, const float* g13,
                                const int* sorted, const int* sorted_expert, const int* offsets, int e_local, int topk,
-                               void* act, int max_rows, int H, int I, float limit, void* stream) {
+                               void* act, int max_rows, int H, int I, float limit, const int* direct_ids, int e_start,
+                               void* stream) {
   if (max_rows <= 0) return 0;
   if (H % 32 || H > 16384) return -1;
   ExpertW w{(const uint8_t*)w13, (const uint8_t*)s13, g13};
   dim3 grid((I + 15) / 16, max_rows);
-  expert_fc1_kernel<<<grid, 256, ((H + 1023) / 1024) * 2048, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, w, sorted, sorted_expert,
-                                                                offsets, e_local, topk, (__half*)act, H, I, limit);
+  const size_t smem = ((H + 1023) / 1024) * 2048;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int iters = (H / 32 + 31) / 32;
+#define STK_FC1(I_) expert_fc1_kernel<I_><<<grid, 256, smem, st>>>((const __nv_bfloat16*)x, ldx, w, sorted, sorted_expert, offsets, e_local, topk, (__half*)act, H, I, limit, direct_ids, e_start)
+  if (iters <= 1) STK_FC1(1); else if (iters <= 2) STK_FC1(2); else if (iters <= 4) STK_FC1(4); else if (iters <= 8) STK_FC1(8); else STK_FC1(16);
+#undef STK_FC1
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
 STK_API int stk_moe_expert_fc2(const void* act, const void* w2, const void* s2, const float* g2,
                                const int* sorted_expert, const int* offsets, int e_local, void* y, int max_rows, int H,
-                               int I, void* stream) {
+                               int I, const int* direct_ids, int e_start, void* stream) {
   if (max_rows <= 0) return 0;
   if (I % 32 || I > 16384) return -1;
   ExpertW w{(const uint8_t*)w2, (const uint8_t*)s2, g2};
   dim3 grid((H + 31) / 32, max_rows);
-  expert_fc2_kernel<<<grid, 256, ((I + 1023) / 1024) * 2048, (cudaStream_t)stream>>>((const __half*)act, w, sorted_expert, offsets, e_local,
-                                                                (__nv_bfloat16*)y, H, I);
+  const size_t smem = ((I + 1023) / 1024) * 2048;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int iters = (I / 32 + 31) / 32;
+#define STK_FC2(I_) expert_fc2_kernel<I_><<<grid, 256, smem, st>>>((const __half*)act, w, sorted_expert, offsets, e_local, (__nv_bfloat16*)y, H, I, direct_ids, e_start)
+  if (iters <= 1) STK_FC2(1); else if (iters <= 2) STK_FC2(2); else if (iters <= 4) STK_FC2(4); else if (iters <= 8) STK_FC2(8); else STK_FC2(16);
+#undef STK_FC2
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

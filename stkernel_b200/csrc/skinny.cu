@@ -1,0 +1,226 @@
+// Weight-streaming linear layer for one to four tokens (single-request decode):
+//   out[t, n] = sum_k x[t, k] * W[n, k]
+// One warp per output feature streams the weight row with 16-byte loads; the activations sit in
+// shared memory (fp16, laid out so that a warp's reads are conflict free); fp32 accumulation.
+// With so few tokens the layer is bounded by the bytes of W, and this single-pass form has a much
+// shorter dependency chain than a tensor-core tile pipeline with split-K: no workspace, no second
+// reduction pass.  Larger token counts use the tcgen05 GEMM.
+//
+// FP8 weights carry 128x128 block scales (applied per 16-value chunk); activations are used
+// unquantised, which is at least as accurate as the quantised tensor-core path.
+#include "common.cuh"
+
+namespace stk {
+
+constexpr int kSkinnyMaxT = 4;
+
+// x: [T, K] bf16 -> xs: half, permuted: chunk c = lane + 32*k holds values [16c, 16c+16) as two uint4
+// at index ((t * kIters + k) * 2 + i) * 32 + lane.
+template <int T>
+__device__ __forceinline__ void skinny_fill_x(__half* xs, const __nv_bfloat16* x, long long ldx, int K, int iters) {
+  // eight consecutive values = one 16-byte load, one conversion, one 16-byte store
+  uint4* xs4 = reinterpret_cast<uint4*>(xs);
+  const int k8n = K >> 3;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((ldx & 7) == 0);
+#pragma unroll
+  for (int t = 0; t < T; ++t) {
+    for (int k8 = threadIdx.x; k8 < k8n; k8 += blockDim.x) {
+      const __nv_bfloat16* src = x + t * ldx + k8 * 8;
+      __nv_bfloat162 b[4];
+      if (aligned) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
+        b[0] = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
+        b[1] = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
+        b[2] = *reinterpret_cast<const __nv_bfloat162*>(&v.z);
+        b[3] = *reinterpret_cast<const __nv_bfloat162*>(&v.w);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) b[j] = __halves2bfloat162(src[2 * j], src[2 * j + 1]);
+      }
+      uint4 o;
+      __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) oh[j] = __float22half2_rn(__bfloat1622float2(b[j]));
+      const int c = k8 >> 1;
+      xs4[((t * iters + (c >> 5)) * 2 + (k8 & 1)) * 32 + (c & 31)] = o;
+    }
+  }
+}
+
+// ITERS = ceil(chunks per row / 32): every lane issues all of its 16-byte weight loads (and block
+// scales) for a row before the first multiply, so a row costs one memory round trip, not ITERS.
+// kSwiglu: W holds [gate rows (N) | up rows (N)]; the warp streams rows n and N + n and writes
+// silu(min(g, limit)) * clamp(u, -limit, limit) — the shared-expert FC1 with its activation fused.
+template <int T, bool kFp8, int ITERS, bool kSwiglu>
+__global__ void __launch_bounds__(256)
+skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const float* __restrict__ w_scale,
+                     int w_scale_ld, const __nv_bfloat16* __restrict__ x, long long ldx, void* __restrict__ out,
+                     long long ldo, int N, int K, int out_fp32, int rows_per_warp, int group_rows, float limit) {
+  extern __shared__ uint4 xs4[];
+  constexpr int kVals = kFp8 ? 16 : 8;                  // values per 16-byte weight chunk
+  const int n_chunks = K / kVals;
+  const int iters16 = ((K / 16) + 31) / 32;             // x layout is always in 16-value chunks
+  // grouped (block-diagonal) mode: all rows of this CTA belong to one group, whose activations start at g*K
+  const int grp = group_rows > 0 ? (blockIdx.x * 8 * rows_per_warp) / group_rows : 0;
+  skinny_fill_x<T>(reinterpret_cast<__half*>(xs4), x + static_cast<long long>(grp) * K, ldx, K, iters16);
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = (blockIdx.x * 8 + warp) * rows_per_warp;
+  for (int r = 0; r < rows_per_warp; ++r) {
+    const int n = n0 + r;
+    if (n >= N) break;
+    float res[kSwiglu ? 2 : 1][T];
+#pragma unroll
+    for (int pass = 0; pass < (kSwiglu ? 2 : 1); ++pass) {
+      const int wn = n + pass * N;                       // weight row (and scale row) of this pass
+      const uint4* wrow = reinterpret_cast<const uint4*>(W + wn * ldw_bytes);
+      uint4 wv[ITERS];
+      float sc[ITERS];
+#pragma unroll
+      for (int it = 0; it < ITERS; ++it) {
+        const int c = it * 32 + lane;
+        wv[it] = make_uint4(0, 0, 0, 0);
+        sc[it] = 0.f;
+        if (c < n_chunks) {
+          wv[it] = __ldg(wrow + c);
+          if constexpr (kFp8) sc[it] = __ldg(w_scale + (wn >> 7) * w_scale_ld + (c >> 3));
+        }
+      }
+      float acc[T];
+#pragma unroll
+      for (int t = 0; t < T; ++t) acc[t] = 0.f;
+#pragma unroll
+      for (int it = 0; it < ITERS; ++it) {
+        const int c = it * 32 + lane;
+        if (c < n_chunks) {
+          const uint32_t ww[4] = {wv[it].x, wv[it].y, wv[it].z, wv[it].w};
+          float wf[kVals];
+          if constexpr (kFp8) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const __half2_raw h01 = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(ww[j] & 0xffff), __NV_E4M3);
+              const __half2_raw h23 = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(ww[j] >> 16), __NV_E4M3);
+              const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&h01));
+              const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&h23));
+              wf[4 * j] = f01.x * sc[it]; wf[4 * j + 1] = f01.y * sc[it];
+              wf[4 * j + 2] = f23.x * sc[it]; wf[4 * j + 3] = f23.y * sc[it];
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&ww[j]);
+              wf[2 * j] = __low2float(b);
+              wf[2 * j + 1] = __high2float(b);
+            }
+          }
+#pragma unroll
+          for (int t = 0; t < T; ++t) {
+            if constexpr (kFp8) {
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                const uint4 xv = xs4[((t * iters16 + it) * 2 + i) * 32 + lane];
+                const __half2* xh = reinterpret_cast<const __half2*>(&xv);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 xf = __half22float2(xh[j]);
+                  acc[t] = fmaf(wf[8 * i + 2 * j], xf.x, fmaf(wf[8 * i + 2 * j + 1], xf.y, acc[t]));
+                }
+              }
+            } else {
+              // bf16 chunk c covers 8 values = half of 16-value chunk c/2
+              const int c16 = c >> 1, it16 = c16 >> 5, lane16 = c16 & 31;
+              const uint4 xv = xs4[((t * iters16 + it16) * 2 + (c & 1)) * 32 + lane16];
+              const __half2* xh = reinterpret_cast<const __half2*>(&xv);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 xf = __half22float2(xh[j]);
+                acc[t] = fmaf(wf[2 * j], xf.x, fmaf(wf[2 * j + 1], xf.y, acc[t]));
+              }
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < T; ++t) res[pass][t] = warp_sum(acc[t]);
+    }
+#pragma unroll
+    for (int t = 0; t < T; ++t) {
+      float v = res[0][t];
+      if constexpr (kSwiglu) {
+        float g = v, u = res[1][t];
+        if (limit > 0.f) {
+          g = fminf(g, limit);
+          u = fminf(fmaxf(u, -limit), limit);
+        }
+        v = g / (1.f + __expf(-g)) * u;
+      }
+      if (lane == 0) {
+        if (out_fp32) reinterpret_cast<float*>(out)[t * ldo + n] = v;
+        else reinterpret_cast<__nv_bfloat16*>(out)[t * ldo + n] = __float2bfloat16(v);
+      }
+    }
+  }
+}
+
+}  // namespace stk
+
+using namespace stk;
+
+// T <= 4.  K must be a multiple of 16 (fp8) / 8 (bf16); rows 16-byte aligned.
+STK_API int stk_skinny_linear(const void* W, long long ldw, int is_fp8, const float* w_scale, int w_scale_ld,
+                              const void* x, long long ldx, void* out, long long ldo, int T, int N, int K,
+                              int out_fp32, int sm_count, int groups, int swiglu, float limit, void* stream) {
+  if (T <= 0 || N <= 0) return 0;
+  if (T > kSkinnyMaxT || K % 16 || K > 16384) return -1;
+  const long long ldw_bytes = ldw * (is_fp8 ? 1 : 2);
+  if (ldw_bytes % 16 || (reinterpret_cast<uintptr_t>(W) & 15)) return -2;
+  const int iters16 = ((K / 16) + 31) / 32;
+  const size_t smem = static_cast<size_t>(T) * iters16 * 2 * 32 * 16;
+  // about four CTAs per SM; each warp takes `rpw` consecutive rows
+  int rpw = 1;
+  while ((N + 8 * rpw - 1) / (8 * rpw) > sm_count * 3 && rpw < 16) rpw *= 2;
+  int group_rows = 0;
+  if (groups > 1) {
+    group_rows = N / groups;
+    while (rpw > 1 && group_rows % (8 * rpw)) rpw /= 2;
+    if (group_rows % (8 * rpw)) return -3;
+  }
+  const int grid = (N + 8 * rpw - 1) / (8 * rpw);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int n_chunks = K / (is_fp8 ? 16 : 8);
+  const int iters = (n_chunks + 31) / 32;
+#define STK_SK3(T_, F_, I_, S_)                                                                                           \
+  {                                                                                                                    \
+    static bool configured = false;                                                                                    \
+    if (!configured) {                                                                                                 \
+      cudaFuncSetAttribute(skinny_linear_kernel<T_, F_, I_, S_>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); \
+      configured = true;                                                                                               \
+    }                                                                                                                  \
+    skinny_linear_kernel<T_, F_, I_, S_><<<grid, 256, smem, st>>>((const uint8_t*)W, ldw_bytes, w_scale, w_scale_ld,       \
+                                                              (const __nv_bfloat16*)x, ldx, out, ldo, N, K, out_fp32,  \
+                                                              rpw, group_rows, limit);                                 \
+  }
+#define STK_SK2(T_, F_)                                                                                 \
+  {                                                                                                     \
+    if (swiglu) {                                                                                       \
+      if (iters <= 4) STK_SK3(T_, F_, 4, true)                                                          \
+      else if (iters <= 8) STK_SK3(T_, F_, 8, true)                                                     \
+      else if (iters <= 16) STK_SK3(T_, F_, 16, true)                                                   \
+      else return -5;                                                                                   \
+    } else {                                                                                            \
+      if (iters <= 4) STK_SK3(T_, F_, 4, false)                                                         \
+      else if (iters <= 8) STK_SK3(T_, F_, 8, false)                                                    \
+      else if (iters <= 16) STK_SK3(T_, F_, 16, false)                                                  \
+      else if (iters <= 32) STK_SK3(T_, F_, 32, false)                                                  \
+      else return -5;                                                                                   \
+    }                                                                                                   \
+  }
+  if (is_fp8) {
+    switch (T) { case 1: STK_SK2(1, true) break; case 2: STK_SK2(2, true) break; case 3: STK_SK2(3, true) break; default: STK_SK2(4, true) }
+  } else {
+    switch (T) { case 1: STK_SK2(1, false) break; case 2: STK_SK2(2, false) break; case 3: STK_SK2(3, false) break; default: STK_SK2(4, false) }
+  }
+#undef STK_SK2
+#undef STK_SK3
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}

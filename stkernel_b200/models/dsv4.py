@@ -281,12 +281,12 @@ class DSV4Model:
         nh_l = cfg.num_attention_heads // self.tp_size
         ql = cfg.q_lora_rank
         qkv = Fn.linear(yq if yq is not None else y, lw.w_qa_kv, tag="qa_kv")
-        use_q = lw.w_qb.is_fp8
+        use_q = lw.w_qb.is_fp8 and Fn.wants_quant_act(T, y.device)
         res = Fn.rms_norm_pair(qkv[:, :ql], lw.q_norm, qkv[:, ql:], lw.kv_norm, cfg.rms_norm_eps, quant0=use_q, tag="qr")
         qr, kvn = res[0], res[1]
         qb = Fn.linear(res[2] if use_q else qr, lw.w_qb, tag="qb")
-        q = Fn.q_norm_rope(qb[:, :nh_l * D].view(T, nh_l, D), meta.positions, self.inv, Rd, cfg.rms_norm_eps)
-        C.kv_rope_quant_insert(kvn, meta.positions, meta.swa_slot_mapping, self.inv, self.kv.swa_cache[li])
+        q = C.q_rope_kv_insert(qb[:, :nh_l * D].view(T, nh_l, D), kvn, meta.positions, meta.swa_slot_mapping, self.inv,
+                               self.kv.swa_cache[li], cfg.rms_norm_eps)
 
         topk_slots = topk_lens = None
         comp_cache = None
@@ -322,8 +322,7 @@ class DSV4Model:
                 topk_slots, topk_lens = A.c128_indices(meta.positions, meta.tok_req, grp.table_dev, lw.ratio,
                                                        cfg.index_topk)
         o = A.sparse_mla(q, self.kv.swa_cache[li], meta.swa_slots, meta.swa_lens, comp_cache, topk_slots, topk_lens,
-                         lw.sink, D ** -0.5)
-        o = Fn.q_norm_rope(o, meta.positions, self.inv, Rd, cfg.rms_norm_eps, norm=False, inverse=True)
+                         lw.sink, D ** -0.5, inv_rope=(meta.positions, self.inv))
         # grouped low-rank output projection, then the row-parallel wo_b (+ all-reduce)
         G_l = len(lw.w_oa)
         hpg = cfg.num_attention_heads // cfg.o_groups
@@ -346,8 +345,12 @@ class DSV4Model:
                             cfg.routed_scaling_factor, lw.tid2eid, meta.token_ids)
         shared = None
         if lw.w_sh13 is not None:
+            act = Fn.linear_swiglu(y, lw.w_sh13, cfg.swiglu_limit) if yq is None else None
+        if lw.w_sh13 is not None and act is not None:
+            shared = Fn.linear(act, lw.w_sh2, tag="sh2")
+        elif lw.w_sh13 is not None:
             gu = Fn.linear(yq if (yq is not None and lw.w_sh13.is_fp8) else y, lw.w_sh13, tag="sh13")
-            if lw.w_sh2.is_fp8:
+            if lw.w_sh2.is_fp8 and Fn.wants_quant_act(y.shape[0], y.device):
                 _, aq = Fn.swiglu_clamp(gu, cfg.swiglu_limit, quant=True, tag="shact")
                 shared = Fn.linear(aq, lw.w_sh2, tag="sh2")
             else:
@@ -357,13 +360,13 @@ class DSV4Model:
 
     def layer(self, li: int, lw: LayerWeights, X: torch.Tensor, meta: StepMeta) -> torch.Tensor:
         cfg = self.cfg
-        want_q = lw.w_qa_kv.is_fp8
+        want_q = lw.w_qa_kv.is_fp8 and Fn.wants_quant_act(X.shape[0], X.device)
         r = Fn.mhc_pre(X, *lw.hc_attn, lw.attn_norm, cfg.rms_norm_eps, cfg.hc_eps, cfg.hc_sinkhorn_iters, quant=want_q,
                        tag="mhc_a")
         y, post, comb = r[0], r[1], r[2]
         a = self.attention(li, lw, y, r[3] if want_q else None, meta)
         X = Fn.mhc_post(a, X, post, comb)
-        want_q = lw.w_sh13 is not None and lw.w_sh13.is_fp8
+        want_q = lw.w_sh13 is not None and lw.w_sh13.is_fp8 and Fn.wants_quant_act(X.shape[0], X.device)
         r = Fn.mhc_pre(X, *lw.hc_ffn, lw.ffn_norm, cfg.rms_norm_eps, cfg.hc_eps, cfg.hc_sinkhorn_iters, quant=want_q,
                        tag="mhc_f")
         y, post, comb = r[0], r[1], r[2]

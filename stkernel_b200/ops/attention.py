@@ -212,11 +212,13 @@ def topk_to_slots(topk: torch.Tensor, block_table: torch.Tensor, tok_req: torch.
 # ---- attention ------------------------------------------------------------------------
 def sparse_mla(q: torch.Tensor, swa_cache: PagedCache, swa_slots: torch.Tensor, swa_lens: torch.Tensor,
                comp_cache: Optional[PagedCache], topk_slots: Optional[torch.Tensor], topk_lens: Optional[torch.Tensor],
-               sink: torch.Tensor, scale: float) -> torch.Tensor:
+               sink: torch.Tensor, scale: float, inv_rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
+               ) -> torch.Tensor:
     """q [T, nh, D] bf16 -> out [T, nh, D] bf16 attending to the SWA rows then the top-k rows.
 
     Only the first swa_lens[t] / topk_lens[t] entries of each list are read; -1 entries inside that
-    range are masked."""
+    range are masked.  inv_rope = (positions, inv_freq): also apply the inverse RoPE to the output's
+    rope dims (fused into the split-merge kernel on the tensor-core path)."""
     t, nh, d = q.shape
     if not q.is_cuda:
         out = torch.zeros(t, nh, d, dtype=F32)
@@ -231,7 +233,11 @@ def sparse_mla(q: torch.Tensor, swa_cache: PagedCache, swa_slots: torch.Tensor, 
             rr = torch.cat(rows)[None]
             vv = torch.cat(valid)[None]
             out[i] = R.sparse_mla(q[i:i + 1], rr, vv, sink, scale)[0]
-        return out.to(cpu_act_dtype())
+        out = out.to(cpu_act_dtype())
+        if inv_rope is not None:
+            from .functional import q_norm_rope
+            out = q_norm_rope(out, inv_rope[0], inv_rope[1], swa_cache.rope_dim, 0.0, norm=False, inverse=True)
+        return out
     max_rows = swa_slots.shape[1] + (topk_slots.shape[1] if topk_slots is not None else 0)
     cc = comp_cache if comp_cache is not None else swa_cache
     if USE_TENSOR_CORE_MLA and swa_cache.fp8 and d == 512 and swa_cache.rope_dim == 64 and nh <= 64 and q.stride(0) % 8 == 0:
@@ -243,7 +249,9 @@ def sparse_mla(q: torch.Tensor, swa_cache: PagedCache, swa_slots: torch.Tensor, 
                   swa_slots, swa_slots.stride(0), swa_lens, topk_slots,
                   topk_slots.stride(0) if topk_slots is not None else 0, topk_lens, ws, n_splits, t, nh, d,
                   swa_cache.rope_dim, max_rows, float(scale), _lib.status_buffer(), MLA_TRACE, _lib.stream())
-        _lib.call("stk_sparse_mla_combine", ws, sink, out, out.stride(0), t, nh, d, n_splits, _lib.stream())
+        _lib.call("stk_sparse_mla_combine", ws, sink, out, out.stride(0), t, nh, d, n_splits,
+                  inv_rope[0] if inv_rope is not None else None, inv_rope[1] if inv_rope is not None else None,
+                  swa_cache.rope_dim, _lib.stream())
         return out
     n_splits = _lib.query("stk_sparse_mla_pick_splits", t, max_rows)
     ws = scratch("mla.partial", (t * n_splits * nh * (d + 2),), F32, q.device)
@@ -252,4 +260,7 @@ def sparse_mla(q: torch.Tensor, swa_cache: PagedCache, swa_slots: torch.Tensor, 
               cc.page_stride, cc.data_bytes, 1 if swa_cache.fp8 else 0, swa_slots, swa_slots.stride(0), swa_lens,
               topk_slots, topk_slots.stride(0) if topk_slots is not None else 0, topk_lens, sink, out, out.stride(0), ws,
               n_splits, t, nh, d, swa_cache.rope_dim, max_rows, float(scale), _lib.stream())
+    if inv_rope is not None:
+        from .functional import q_norm_rope
+        out = q_norm_rope(out, inv_rope[0], inv_rope[1], swa_cache.rope_dim, 0.0, norm=False, inverse=True)
     return out

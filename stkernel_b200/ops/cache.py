@@ -155,6 +155,21 @@ def kv_rope_quant_insert(kv: torch.Tensor, positions: torch.Tensor, slots: torch
               cache.data_bytes, 1 if cache.fp8 else 0, cache.num_slots, t, d, rd, _lib.status_buffer(), _lib.stream())
 
 
+def q_rope_kv_insert(q: torch.Tensor, kv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, inv: torch.Tensor,
+                     cache: PagedCache, eps: float) -> torch.Tensor:
+    """One launch: per-head weightless RMSNorm + RoPE of q [T, nh, D] (in place) and RoPE + quantise +
+    insert of the latent rows kv [T, D]."""
+    if not q.is_cuda:
+        from .functional import q_norm_rope
+        kv_rope_quant_insert(kv, positions, slots, inv, cache)
+        return q_norm_rope(q, positions, inv, cache.rope_dim, eps)
+    t, nh, d = q.shape
+    _lib.call("stk_q_rope_kv_insert", q, q.stride(0), nh, eps, kv, kv.stride(0), positions, slots, inv, cache.buf,
+              cache.page_stride, cache.data_bytes, 1 if cache.fp8 else 0, cache.num_slots, t, d, cache.rope_dim,
+              _lib.status_buffer(), _lib.stream())
+    return q
+
+
 def kv_gather_dequant(cache: PagedCache, slots: torch.Tensor) -> torch.Tensor:
     """slots [n] int64 -> rows [n, D] bf16 (zeros for slot < 0)."""
     n = slots.numel()

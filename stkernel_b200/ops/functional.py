@@ -75,6 +75,16 @@ class QuantAct:
     scale: torch.Tensor
 
 
+SKINNY_MAX_T = 4
+MHC_CLUSTER_MAX_T = 16
+
+
+def wants_quant_act(t: int, device) -> bool:
+    """Whether fp8 layers should be fed pre-quantised activations for a step of t tokens (the
+    weight-streaming kernel used for t <= 4 on a GPU takes bf16 activations)."""
+    return not (torch.device(device).type == "cuda" and t <= SKINNY_MAX_T)
+
+
 def _scale_ld(t: int) -> int:
     return max(4, (t + 3) // 4 * 4)
 
@@ -133,10 +143,16 @@ def linear(x, lw: LinearWeight, out: Optional[torch.Tensor] = None, out_dtype=BF
             out.copy_(y)
             return out
         return y
-    if lw.is_fp8 and xa is None:
-        xa = quant_act(x, tag + ".xq")
     if out is None:
         out = torch.empty(t, n, dtype=out_dtype, device=dev)
+    if xa is None and t <= SKINNY_MAX_T and ar_ctx is None and x.dtype == BF16 and k % 16 == 0 and k <= 16384:
+        # one to four tokens: weight-streaming kernel, activations unquantised
+        _lib.call("stk_skinny_linear", lw.w, lw.w.stride(0), 1 if lw.is_fp8 else 0, lw.scale,
+                  lw.scale.stride(0) if lw.is_fp8 else 0, x, x.stride(0), out, out.stride(0), t, n, k,
+                  1 if out.dtype == F32 else 0, _lib.sm_count(), groups, 0, 0.0, _lib.stream())
+        return out
+    if lw.is_fp8 and xa is None:
+        xa = quant_act(x, tag + ".xq")
     is_fp8 = 1 if lw.is_fp8 else 0
     sms = _lib.sm_count()
     if splits is None:
@@ -153,6 +169,23 @@ def linear(x, lw: LinearWeight, out: Optional[torch.Tensor] = None, out_dtype=BF
               xa.scale if is_fp8 else None, xa.scale.stride(0) if is_fp8 else 0, splits, ws, cnt,
               _lib.status_buffer(), sms, groups, ctypes.addressof(ar_ctx) if ar_ctx is not None else None,
               _lib.stream())
+    return out
+
+
+def linear_swiglu(x: torch.Tensor, lw13: LinearWeight, limit: float) -> Optional[torch.Tensor]:
+    """act[T, I] = silu(min(x W1^T, lim)) * clamp(x W3^T) with W13 = [W1; W3] in one weight-streaming launch
+    (decode-sized batches on a GPU); returns None when that kernel does not apply."""
+    t, k = x.shape
+    n2 = lw13.w.shape[0]
+    if not x.is_cuda or t > SKINNY_MAX_T or x.dtype != BF16 or k % 16 or k > 8192 or n2 % 2:
+        return None
+    i = n2 // 2
+    if lw13.is_fp8 and i % 128:
+        return None
+    out = torch.empty(t, i, dtype=BF16, device=x.device)
+    _lib.call("stk_skinny_linear", lw13.w, lw13.w.stride(0), 1 if lw13.is_fp8 else 0, lw13.scale,
+              lw13.scale.stride(0) if lw13.is_fp8 else 0, x, x.stride(0), out, out.stride(0), t, i, k, 0, _lib.sm_count(),
+              1, 1, float(limit), _lib.stream())
     return out
 
 
@@ -242,6 +275,14 @@ def mhc_pre(residual: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale:
         return res + (quant_act(y),) if quant else res
     dev = residual.device
     n_mix = (2 + hc) * hc
+    if t <= MHC_CLUSTER_MAX_T and not quant and n_mix in (24, 8) and h <= 16384:
+        # decode-sized batch: one launch, an 8-CTA cluster per token (DSMEM reductions)
+        y = torch.empty(t, h, dtype=BF16, device=dev)
+        post = torch.empty(t, hc, dtype=F32, device=dev)
+        comb = torch.empty(t, hc * hc, dtype=F32, device=dev)
+        _lib.call("stk_mhc_cluster", residual, fn, base, scale, norm_w, post, comb, y, t, h, hc, n_mix, rms_eps, hc_eps,
+                  iters, 2.0, 0, _lib.stream())
+        return y, post, comb
     splits = _lib.query("stk_mhc_pick_splits", t, hc * h)
     partial = scratch("mhc.partial", (splits * t * (n_mix + 1),), F32, dev)
     _lib.call("stk_mhc_dots", residual, fn, partial, t, h, hc, n_mix, splits, _lib.stream())
@@ -273,6 +314,11 @@ def hc_head(residual: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale:
     if not residual.is_cuda:
         return R.hc_head(residual, fn, base, scale, rms_eps, hc_eps).to(cpu_act_dtype())
     dev = residual.device
+    if t <= MHC_CLUSTER_MAX_T and hc in (4, 8) and h <= 16384:
+        y = torch.empty(t, h, dtype=BF16, device=dev)
+        _lib.call("stk_mhc_cluster", residual, fn, base, scale, None, None, None, y, t, h, hc, hc, rms_eps, hc_eps, 0, 2.0,
+                  1, _lib.stream())
+        return y
     splits = _lib.query("stk_mhc_pick_splits", t, hc * h)
     partial = scratch("mhc.partial", (splits * t * (hc + 1),), F32, dev)
     _lib.call("stk_mhc_dots", residual, fn, partial, t, h, hc, hc, splits, _lib.stream())

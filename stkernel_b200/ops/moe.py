@@ -14,6 +14,7 @@ from .functional import cpu_act_dtype
 BF16 = torch.bfloat16
 F32 = torch.float32
 I32 = torch.int32
+DIRECT_MAX_PAIRS = 48
 
 
 @dataclass
@@ -97,17 +98,26 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, ew: E
     dev = x.device
     n_pairs = t * k
     inter = ew.w2.shape[2] * 2
-    sorted_p = scratch("moe.sorted", (n_pairs,), I32, dev)
-    pair_row = scratch("moe.pair_row", (n_pairs,), I32, dev)
-    offsets = scratch("moe.offsets", (ew.num_local + 1,), I32, dev)
-    sorted_e = scratch("moe.sorted_e", (n_pairs,), I32, dev)
     st = _lib.stream()
-    _lib.call("stk_moe_align", ids, n_pairs, ew.expert_start, ew.num_local, sorted_p, pair_row, offsets, sorted_e, st)
     act = scratch("moe.act", (n_pairs, inter), torch.float16, dev)
     y = scratch("moe.y", (n_pairs, h), BF16, dev)
-    _lib.call("stk_moe_expert_fc1", x, x.stride(0), ew.w13, ew.s13, ew.g13, sorted_p, sorted_e, offsets, ew.num_local, k,
-              act, n_pairs, h, inter, float(limit), st)
-    _lib.call("stk_moe_expert_fc2", act, ew.w2, ew.s2, ew.g2, sorted_e, offsets, ew.num_local, y, n_pairs, h, inter, st)
+    if n_pairs <= DIRECT_MAX_PAIRS:
+        # a handful of pairs: skip the sort, row = pair index
+        pair_row = None
+        _lib.call("stk_moe_expert_fc1", x, x.stride(0), ew.w13, ew.s13, ew.g13, None, None, None, ew.num_local, k, act,
+                  n_pairs, h, inter, float(limit), ids, ew.expert_start, st)
+        _lib.call("stk_moe_expert_fc2", act, ew.w2, ew.s2, ew.g2, None, None, ew.num_local, y, n_pairs, h, inter, ids,
+                  ew.expert_start, st)
+    else:
+        sorted_p = scratch("moe.sorted", (n_pairs,), I32, dev)
+        pair_row = scratch("moe.pair_row", (n_pairs,), I32, dev)
+        offsets = scratch("moe.offsets", (ew.num_local + 1,), I32, dev)
+        sorted_e = scratch("moe.sorted_e", (n_pairs,), I32, dev)
+        _lib.call("stk_moe_align", ids, n_pairs, ew.expert_start, ew.num_local, sorted_p, pair_row, offsets, sorted_e, st)
+        _lib.call("stk_moe_expert_fc1", x, x.stride(0), ew.w13, ew.s13, ew.g13, sorted_p, sorted_e, offsets, ew.num_local,
+                  k, act, n_pairs, h, inter, float(limit), None, 0, st)
+        _lib.call("stk_moe_expert_fc2", act, ew.w2, ew.s2, ew.g2, sorted_e, offsets, ew.num_local, y, n_pairs, h, inter,
+                  None, 0, st)
     out = torch.empty(t, h, dtype=BF16, device=dev)
     _lib.call("stk_moe_combine", y, weights, pair_row, shared, out, t, h, k, st)
     return out

@@ -54,6 +54,8 @@ def test_gemm_fp8_block(T, N, K):
     lw = Fn.LinearWeight.from_master(w, "fp8", dev())
     xq, xs = R.quant_fp8_group128_act(x)
     ref = R.dequant_fp8_group128_act(xq, xs) @ lw.dequant().t()
+    if T <= Fn.SKINNY_MAX_T:          # the weight-streaming kernel keeps the activations unquantised
+        ref = x.float() @ lw.dequant().t()
     out = Fn.linear(x, lw, out_dtype=F32)
     assert rel_err(out, ref) < 2e-3
     # and against the unquantised product within fp8 error
@@ -386,7 +388,7 @@ def test_gemm_grouped_block_diagonal(dtype, T):
     out = Fn.linear(x, stacked, out_dtype=F32, groups=G)
     for g in range(G):
         xg = x[:, g * K:(g + 1) * K]
-        if dtype == "fp8":
+        if dtype == "fp8" and T > Fn.SKINNY_MAX_T:
             xq, xs = R.quant_fp8_group128_act(xg)
             ref = R.dequant_fp8_group128_act(xq, xs) @ lws[g].dequant().t()
         else:
@@ -402,3 +404,41 @@ def test_gemm_splitk_wide_tiles(T, N, K):
     ref = x.float() @ w.float().t()
     for splits in (2, 4):
         assert rel_err(Fn.linear(x, Fn.LinearWeight(w), splits=splits), ref) < 1e-2
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp8"])
+@pytest.mark.parametrize("T", [1, 3, 4])
+@pytest.mark.parametrize("N,K", [(2048, 4096), (40960, 1536), (4096, 8192), (176, 256)])
+def test_skinny_linear(dtype, T, N, K):
+    torch.manual_seed(T)
+    x = torch.randn(T, K, device=dev()).to(BF16)
+    w = torch.randn(N, K, device=dev()) * 0.05
+    lw = Fn.LinearWeight.from_master(w, dtype, dev())
+    ref = x.float() @ lw.dequant().t()
+    out = Fn.linear(x, lw, out_dtype=F32)          # T <= 4 routes to the weight-streaming kernel
+    assert rel_err(out, ref) < 2e-3
+    out16 = Fn.linear(x, lw)
+    assert rel_err(out16, ref) < 1e-2
+
+
+def test_skinny_linear_grouped():
+    G, Ng, K, T = 8, 1024, 4096, 2
+    x = torch.randn(T, G * K, device=dev()).to(BF16)
+    w = torch.randn(G * Ng, K, device=dev()) * 0.05
+    lw = Fn.LinearWeight.from_master(w, "fp8", dev())
+    out = Fn.linear(x, lw, out_dtype=F32, groups=G)
+    wd = lw.dequant().view(G, Ng, K)
+    ref = torch.einsum("tgk,gnk->tgn", x.float().view(T, G, K), wd).reshape(T, G * Ng)
+    assert rel_err(out, ref) < 2e-3
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp8"])
+def test_skinny_swiglu(dtype):
+    T, I, K = 2, 2048, 4096
+    x = torch.randn(T, K, device=dev()).to(BF16)
+    w = torch.randn(2 * I, K, device=dev()) * 0.03
+    lw = Fn.LinearWeight.from_master(w, dtype, dev())
+    act = Fn.linear_swiglu(x, lw, 10.0)
+    gu = x.float() @ lw.dequant().t()
+    ref = R.swiglu_clamp(gu[:, :I], gu[:, I:], 10.0)
+    assert rel_err(act, ref) < 1e-2
