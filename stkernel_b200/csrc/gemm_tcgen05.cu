@@ -600,3 +600,45 @@ STK_API int stk_gemm(const void* W, long long ldw, const void* X, long long ldx,
 #undef STK_LAUNCH
   return -16;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free entry point (declared in stk_no_alloc.h).
+// ---------------------------------------------------------------------------------------------
+namespace {
+constexpr long long kNoAllocWorkspaceBytes = 8ll << 20;      // split-K partials: splits * T * N * 4 bytes
+constexpr int kNoAllocCounters = 4096;                        // one per output tile
+constexpr long long kNoAllocBytes = kNoAllocWorkspaceBytes + kNoAllocCounters * 4;
+// Lives in every context that loads the library until the process exits.  Zero-initialised by the
+// loader; the GEMM leaves its tile counters at zero when it finishes.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+constexpr int kMaxDevices = 64;
+static void* g_noalloc_ptr[kMaxDevices] = {};
+}  // namespace
+
+STK_API long long stk_gemm_noalloc_max_workspace_bytes() { return kNoAllocWorkspaceBytes; }
+
+STK_API int stk_gemm_noalloc(const void* W, long long ldw, const void* X, long long ldx, void* out, long long ldo,
+                             int T, int N, int K, int is_fp8, int out_fp32, const float* w_scale, int w_scale_ld,
+                             const float* x_scale, int x_scale_ld, int splits, int* status, int sm_count, void* stream) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -30;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // First call on this device: resolve the device address of the static array.  In host code the
+    // array's name is only a handle for this query, never a pointer a kernel may be given.
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) return -31;
+    g_noalloc_ptr[dev] = p;
+  }
+  if (splits < 1) splits = 1;
+  const int bt = stk_gemm_pick_bt(T, is_fp8);
+  const long long tiles = static_cast<long long>((N + 127) / 128) * ((T + bt - 1) / bt);
+  if (splits > 1) {
+    if (static_cast<long long>(splits) * T * N * 4 > kNoAllocWorkspaceBytes) return -32;   // beyond the built-in scratch
+    if (tiles > kNoAllocCounters) return -33;
+  }
+  unsigned char* base = static_cast<unsigned char*>(g_noalloc_ptr[dev]);
+  float* workspace = reinterpret_cast<float*>(base);
+  int* counters = reinterpret_cast<int*>(base + kNoAllocWorkspaceBytes);
+  return stk_gemm(W, ldw, X, ldx, out, ldo, T, N, K, is_fp8, out_fp32, w_scale, w_scale_ld, x_scale, x_scale_ld, splits,
+                  workspace, counters, status, sm_count, 1, nullptr, stream);
+}
