@@ -355,7 +355,7 @@ class DSV4Model:
                 shared = Fn.linear(aq, lw.w_sh2, tag="sh2")
             else:
                 shared = Fn.linear(Fn.swiglu_clamp(gu, cfg.swiglu_limit), lw.w_sh2, tag="sh2")
-        out = M.moe_experts(y, ids, wts, lw.experts, cfg.swiglu_limit, shared)
+        out = M.moe_experts(y, ids, wts, lw.experts, cfg.swiglu_limit, shared, cfg.n_routed_experts)
         return self._all_reduce(out)
 
     def layer(self, li: int, lw: LayerWeights, X: torch.Tensor, meta: StepMeta) -> torch.Tensor:

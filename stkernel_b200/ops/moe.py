@@ -15,6 +15,8 @@ BF16 = torch.bfloat16
 F32 = torch.float32
 I32 = torch.int32
 DIRECT_MAX_PAIRS = 48
+# tcgen05 grouped GEMM for batches beyond a handful of pairs (False: weight-streaming kernels, for A/B checks)
+USE_GROUPED_GEMM = True
 
 
 @dataclass
@@ -85,7 +87,7 @@ def router(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, scori
 
 
 def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, ew: ExpertWeights, limit: float,
-                shared: Optional[torch.Tensor] = None) -> torch.Tensor:
+                shared: Optional[torch.Tensor] = None, total_experts: int = 0) -> torch.Tensor:
     """x [T, H] bf16 -> sum_k w_k * expert_k(x) (+ shared) as bf16 [T, H]; experts that are not local add nothing."""
     t, h = x.shape
     k = ids.shape[1]
@@ -114,10 +116,22 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, ew: E
         offsets = scratch("moe.offsets", (ew.num_local + 1,), I32, dev)
         sorted_e = scratch("moe.sorted_e", (n_pairs,), I32, dev)
         _lib.call("stk_moe_align", ids, n_pairs, ew.expert_start, ew.num_local, sorted_p, pair_row, offsets, sorted_e, st)
-        _lib.call("stk_moe_expert_fc1", x, x.stride(0), ew.w13, ew.s13, ew.g13, sorted_p, sorted_e, offsets, ew.num_local,
-                  k, act, n_pairs, h, inter, float(limit), None, 0, st)
-        _lib.call("stk_moe_expert_fc2", act, ew.w2, ew.s2, ew.g2, sorted_e, offsets, ew.num_local, y, n_pairs, h, inter,
-                  None, 0, st)
+        if USE_GROUPED_GEMM and h % 64 == 0 and inter % 128 == 0 and h % 128 == 0:
+            # tensor-core path: permute the activations into expert order, then two grouped GEMMs
+            avg = max(1, n_pairs // max(1, total_experts or ew.num_local))
+            bt = 16 if avg <= 8 else 32 if avg <= 24 else 64 if avg <= 48 else 128
+            xs = scratch("moe.xs", (n_pairs + 128, h), torch.float16, dev, zero=True)
+            act_p = scratch("moe.act_p", (n_pairs + 128, inter), torch.float16, dev, zero=True)
+            _lib.call("stk_moe_permute", x, x.stride(0), sorted_p, offsets, ew.num_local, k, xs, n_pairs, h, st)
+            _lib.call("stk_moe_grouped", xs, n_pairs + 128, ew.w13, ew.s13, ew.g13, offsets, ew.num_local, inter, h, act_p, 1,
+                      float(limit), bt, _lib.status_buffer(), _lib.sm_count(), st)
+            _lib.call("stk_moe_grouped", act_p, n_pairs + 128, ew.w2, ew.s2, ew.g2, offsets, ew.num_local, h, inter, y, 0,
+                      0.0, bt, _lib.status_buffer(), _lib.sm_count(), st)
+        else:
+            _lib.call("stk_moe_expert_fc1", x, x.stride(0), ew.w13, ew.s13, ew.g13, sorted_p, sorted_e, offsets,
+                      ew.num_local, k, act, n_pairs, h, inter, float(limit), None, 0, st)
+            _lib.call("stk_moe_expert_fc2", act, ew.w2, ew.s2, ew.g2, sorted_e, offsets, ew.num_local, y, n_pairs, h,
+                      inter, None, 0, st)
     out = torch.empty(t, h, dtype=BF16, device=dev)
     _lib.call("stk_moe_combine", y, weights, pair_row, shared, out, t, h, k, st)
     return out

@@ -442,3 +442,27 @@ def test_skinny_swiglu(dtype):
     gu = x.float() @ lw.dequant().t()
     ref = R.swiglu_clamp(gu[:, :I], gu[:, I:], 10.0)
     assert rel_err(act, ref) < 1e-2
+
+
+@pytest.mark.parametrize("T,E,k", [(64, 16, 6), (700, 16, 6), (300, 32, 2), (2048, 8, 2)])
+def test_moe_grouped_gemm_nvfp4(T, E, k):
+    """Batches beyond a handful of pairs go through the tcgen05 grouped GEMM."""
+    torch.manual_seed(13)
+    H, I = 1024, 512
+    w13 = torch.randn(E, 2 * I, H) * 0.03
+    w2 = torch.randn(E, H, I) * 0.03
+    ew = M.ExpertWeights.from_master(w13, w2, "nvfp4", dev())
+    x = torch.randn(T, H, device=dev()).to(BF16)
+    logits = torch.randn(T, E, device=dev())
+    logits[:, 0] -= 100.0                               # expert 0 never selected: an empty group
+    ids, w = M.router(logits, None, k, "sigmoid", True, 1.0)
+    out = M.moe_experts(x, ids, w, ew, 10.0, None, E)
+    d13, d2 = ew.dequant()
+    ref = R.moe_experts(x, ids, w, d13, d2, 10.0)
+    assert rel_err(out, ref) < 1.5e-2
+    M.USE_GROUPED_GEMM = False
+    try:
+        out2 = M.moe_experts(x, ids, w, ew, 10.0, None, E)
+    finally:
+        M.USE_GROUPED_GEMM = True
+    assert rel_err(out, out2) < 1.5e-2
