@@ -142,6 +142,74 @@ moe_align_kernel(const int* __restrict__ ids, int n_pairs, int e_start, int e_lo
   }
 }
 
+// ---- parallel pair sort for large batches (three small launches) ---------------------------
+constexpr int kAlignChunk = 256;
+
+// counts[c][e] = pairs of chunk c routed to local expert e
+__global__ void moe_align_count_kernel(const int* __restrict__ ids, int n_pairs, int e_start, int e_local,
+                                       int* __restrict__ counts) {
+  extern __shared__ int sh[];
+  for (int i = threadIdx.x; i < e_local; i += blockDim.x) sh[i] = 0;
+  __syncthreads();
+  const int p = blockIdx.x * kAlignChunk + threadIdx.x;
+  if (p < n_pairs) {
+    const int e = ids[p] - e_start;
+    if (e >= 0 && e < e_local) atomicAdd(&sh[e], 1);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < e_local; i += blockDim.x) counts[blockIdx.x * e_local + i] = sh[i];
+}
+
+// per expert: exclusive scan of its counts over the chunks (in place) and the expert offsets
+__global__ void moe_align_scan_kernel(int* __restrict__ counts, int n_chunks, int e_local, int* __restrict__ offsets) {
+  extern __shared__ int tot[];
+  for (int e = threadIdx.x; e < e_local; e += blockDim.x) {
+    int run = 0;
+    for (int c = 0; c < n_chunks; ++c) {
+      const int v = counts[c * e_local + e];
+      counts[c * e_local + e] = run;
+      run += v;
+    }
+    tot[e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < e_local; ++e) {
+      offsets[e] = run;
+      run += tot[e];
+    }
+    offsets[e_local] = run;
+  }
+}
+
+// stable placement: row = offsets[e] + (pairs of e in earlier chunks) + (earlier pairs of e in this chunk)
+__global__ void moe_align_place_kernel(const int* __restrict__ ids, int n_pairs, int e_start, int e_local,
+                                       const int* __restrict__ counts, const int* __restrict__ offsets,
+                                       int* __restrict__ sorted, int* __restrict__ pair_row,
+                                       int* __restrict__ sorted_expert) {
+  __shared__ int se[kAlignChunk];
+  const int p = blockIdx.x * kAlignChunk + threadIdx.x;
+  int e = -1;
+  if (p < n_pairs) {
+    e = ids[p] - e_start;
+    if (e < 0 || e >= e_local) e = -1;
+  }
+  se[threadIdx.x] = e;
+  __syncthreads();
+  if (p >= n_pairs) return;
+  if (e < 0) {
+    pair_row[p] = -1;
+    return;
+  }
+  int rank = 0;
+  for (int j = 0; j < static_cast<int>(threadIdx.x); ++j) rank += (se[j] == e) ? 1 : 0;
+  const int row = offsets[e] + counts[blockIdx.x * e_local + e] + rank;
+  sorted[row] = p;
+  sorted_expert[row] = e;
+  pair_row[p] = row;
+}
+
 // ---- NVFP4 row dot --------------------------------------------------------------------
 // xs: activations as half, permuted so that (iteration k, quarter i, lane) is one uint4:
 //   chunk c = lane + 32*k covers values [32c, 32c+32); uint4 index = (k*4 + i)*32 + lane.
@@ -347,9 +415,20 @@ STK_API int stk_router(const float* logits, long long ldl, const float* bias, co
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
+// counts: scratch of ceil(n_pairs / 256) * e_local ints (only used for large batches; may be null for
+// n_pairs <= 2048).
 STK_API int stk_moe_align(const int* ids, int n_pairs, int e_start, int e_local, int* sorted, int* pair_row,
-                          int* offsets, int* sorted_expert, void* stream) {
+                          int* offsets, int* sorted_expert, int* counts, void* stream) {
   if (n_pairs <= 0) return 0;
+  if (n_pairs > 2048 && counts != nullptr) {
+    const int n_chunks = (n_pairs + kAlignChunk - 1) / kAlignChunk;
+    cudaStream_t st = (cudaStream_t)stream;
+    moe_align_count_kernel<<<n_chunks, kAlignChunk, e_local * sizeof(int), st>>>(ids, n_pairs, e_start, e_local, counts);
+    moe_align_scan_kernel<<<1, 256, e_local * sizeof(int), st>>>(counts, n_chunks, e_local, offsets);
+    moe_align_place_kernel<<<n_chunks, kAlignChunk, 0, st>>>(ids, n_pairs, e_start, e_local, counts, offsets, sorted,
+                                                             pair_row, sorted_expert);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  }
   moe_align_kernel<<<1, 1024, (e_local + 1) * sizeof(int), (cudaStream_t)stream>>>(ids, n_pairs, e_start, e_local,
                                                                                    sorted, pair_row, offsets,
                                                                                    sorted_expert);

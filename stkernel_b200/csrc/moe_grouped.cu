@@ -5,9 +5,9 @@
 // each, the expert's token tiles:
 //
 //   TMA warp         activation tile [BT tokens x 64 k] fp16, 128-byte swizzle
-//   dequant warps    one thread per weight row: 32 bytes of e2m1 codes + 4 e4m3 group scales ->
-//                    64 fp16 values written straight into the swizzled K-major operand tile
-//                    (loads for the next two K blocks are already in flight in registers)
+//   dequant warps    sixteen warps, one thread per half weight row: 16 bytes of e2m1 codes + 2 e4m3
+//                    group scales -> 32 fp16 values written straight into the swizzled K-major
+//                    operand tile (a ring of six K blocks per thread is in flight in registers)
 //   MMA warp         tcgen05.mma kind::f16 into TMEM (double-buffered accumulators)
 //   epilogue warps   FC1: gate and up tiles sit side by side in TMEM, so one thread holds both values
 //                    of an output and applies SwiGLU with clamp before storing fp16;
@@ -58,33 +58,33 @@ struct alignas(8) MoeGBars {
   uint32_t tmem_base;
 };
 
+// Half of a weight row's K block: 32 e2m1 codes (16 bytes) and their two e4m3 group scales.
 struct RawRow {
-  uint4 w0, w1;      // 64 e2m1 codes
-  uint32_t sc;       // 4 e4m3 group scales
+  uint4 w;
+  uint32_t sc;
 };
 
-__device__ __forceinline__ void load_raw(RawRow& r, const uint8_t* wrow, const uint8_t* srow, int kb) {
-  const uint4* p = reinterpret_cast<const uint4*>(wrow + kb * 32);
-  r.w0 = __ldg(p);
-  r.w1 = __ldg(p + 1);
-  r.sc = __ldg(reinterpret_cast<const uint32_t*>(srow + kb * 4));
+__device__ __forceinline__ void load_raw(RawRow& r, const uint8_t* wrow, const uint8_t* srow, int kb, int half) {
+  r.w = __ldg(reinterpret_cast<const uint4*>(wrow + kb * 32 + half * 16));
+  r.sc = __ldg(reinterpret_cast<const uint16_t*>(srow + kb * 4 + half * 2));
 }
 
-// 64 values of one weight row -> 128 bytes of fp16 in the swizzled tile row `row`.
-__device__ __forceinline__ void dequant_store(const RawRow& r, uint8_t* tile, int row) {
+// 32 values of one weight row -> 64 bytes of fp16 (chunks 4*half .. 4*half+3) in the swizzled tile row.
+__device__ __forceinline__ void dequant_store(const RawRow& r, uint8_t* tile, int row, int half) {
   uint8_t* dst = tile + row * 128;
   const int sw = row & 7;
-  const uint32_t words[8] = {r.w0.x, r.w0.y, r.w0.z, r.w0.w, r.w1.x, r.w1.y, r.w1.z, r.w1.w};
+  const uint32_t words[4] = {r.w.x, r.w.y, r.w.z, r.w.w};
 #pragma unroll
-  for (int c = 0; c < 8; ++c) {                     // 16-byte chunk c = values [8c, 8c+8) = one code word
-    const int g = c >> 1;                           // 16-value scale group
+  for (int cc = 0; cc < 4; ++cc) {                  // 16-byte chunk = 8 values = one code word
+    const int c = half * 4 + cc;
+    const int g = cc >> 1;                          // 16-value scale group inside this half
     const __half_raw sraw = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>((r.sc >> (8 * g)) & 0xff), __NV_E4M3);
     const __half2 sc2 = __half2half2(*reinterpret_cast<const __half*>(&sraw));
     uint4 o;
     __half2* oh = reinterpret_cast<__half2*>(&o);
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
-      const __half2_raw hr = __nv_cvt_fp4x2_to_halfraw2(static_cast<__nv_fp4x2_storage_t>((words[c] >> (8 * b)) & 0xff), __NV_E2M1);
+      const __half2_raw hr = __nv_cvt_fp4x2_to_halfraw2(static_cast<__nv_fp4x2_storage_t>((words[cc] >> (8 * b)) & 0xff), __NV_E2M1);
       oh[b] = __hmul2(*reinterpret_cast<const __half2*>(&hr), sc2);
     }
     *reinterpret_cast<uint4*>(dst + ((c ^ sw) << 4)) = o;
@@ -92,7 +92,7 @@ __device__ __forceinline__ void dequant_store(const RawRow& r, uint8_t* tile, in
 }
 
 template <int BT, bool kFc1>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(704, 1)
 moe_grouped_kernel(const __grid_constant__ CUtensorMap tmX, const MoeGArgs a) {
   using Cfg = MoeGCfg<BT, kFc1>;
   constexpr int kStages = Cfg::kStages;
@@ -107,7 +107,7 @@ moe_grouped_kernel(const __grid_constant__ CUtensorMap tmX, const MoeGArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(&bars->full[s], 1 + 4);           // TMA arrive (+tx bytes) and four dequant warps
+      mbar_init(&bars->full[s], 1 + 16);          // TMA arrive (+tx bytes) and sixteen dequant warps
       mbar_init(&bars->empty[s], 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -247,7 +247,13 @@ moe_grouped_kernel(const __grid_constant__ CUtensorMap tmX, const MoeGArgs a) {
     }
   } else {
     // ------------------------------ dequant producers (weights) ------------------------------
-    const int row = threadIdx.x - 192;                    // 0..127: weight row inside the tile
+    // 512 threads: each owns half a row (32 values) of one or two operand tiles.  FC1 (two tiles):
+    // thread -> (tile = pt / 256, row, half); FC2 (one tile): 256 threads per (row, half), the other
+    // 256 take every second K block.
+    const int pt = threadIdx.x - 192;                     // 0..511
+    const int half = pt & 1;
+    const int row = (pt >> 1) & 127;
+    const int sel = pt >> 8;                              // FC1: which tile; FC2: which K-block parity
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -258,39 +264,44 @@ moe_grouped_kernel(const __grid_constant__ CUtensorMap tmX, const MoeGArgs a) {
       if (cnt <= 0) continue;
       const uint8_t* wexp = a.w + static_cast<long long>(e) * a.rows * wstride;
       const uint8_t* sexp = a.s + static_cast<long long>(e) * a.rows * sstride;
-      // FC1: tile at = 0 holds gate rows [tn*128, +128), at = 1 the up rows I + same
-      const uint8_t* wrow[kATiles];
-      const uint8_t* srow[kATiles];
-#pragma unroll
-      for (int at = 0; at < kATiles; ++at) {
-        const long long rr = static_cast<long long>(at) * (a.rows / kATiles) + tn * 128 + row;
-        wrow[at] = wexp + rr * wstride;
-        srow[at] = sexp + rr * sstride;
-      }
+      const int at = kFc1 ? sel : 0;
+      const long long rr = static_cast<long long>(at) * (a.rows / kATiles) + tn * 128 + row;
+      const uint8_t* wrow = wexp + rr * wstride;
+      const uint8_t* srow = sexp + rr * sstride;
+      // K blocks this thread converts: FC1 all of them; FC2 those with kb % 2 == sel
+      const int kb_first = kFc1 ? 0 : sel;
+      const int kb_step = kFc1 ? 1 : 2;
       for (int tt = 0; tt * BT < cnt && ok; ++tt) {
-        // software pipeline: raw loads run two K blocks ahead of the conversion
-        RawRow cur[kATiles], nxt[kATiles], nx2[kATiles];
+        // a ring of kDepth raw K blocks is in flight in registers; a slot is refilled right after use
+        constexpr int kDepth = 6;
+        RawRow ring[kDepth];
 #pragma unroll
-        for (int at = 0; at < kATiles; ++at) {
-          load_raw(cur[at], wrow[at], srow[at], 0);
-          if (k_blocks > 1) load_raw(nxt[at], wrow[at], srow[at], 1);
+        for (int d = 0; d < kDepth; ++d) {
+          const int kb = kb_first + d * kb_step;
+          if (kb < k_blocks) load_raw(ring[d], wrow, srow, kb, half);
         }
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb0 = 0; kb0 < k_blocks && ok; kb0 += kDepth * kb_step) {
 #pragma unroll
-          for (int at = 0; at < kATiles; ++at)
-            if (kb + 2 < k_blocks) load_raw(nx2[at], wrow[at], srow[at], kb + 2);
-          if (!mbar_wait(&bars->empty[stage], phase ^ 1, a.status, 740 + stage)) { ok = false; break; }
+          for (int d = 0; d < kDepth; ++d) {
 #pragma unroll
-          for (int at = 0; at < kATiles; ++at) dequant_store(cur[at], smem_a + (stage * kATiles + at) * 128 * 128, row);
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bars->full[stage]);
-#pragma unroll
-          for (int at = 0; at < kATiles; ++at) {
-            cur[at] = nxt[at];
-            nxt[at] = nx2[at];
+            for (int sub = 0; sub < (kFc1 ? 1 : 2); ++sub) {
+              // every thread visits every K block (to arrive on its barrier); it converts only its own
+              const int kb = kb0 + d * kb_step + sub;
+              if (kb < k_blocks && ok) {
+                const bool mine = kFc1 || ((kb & 1) == sel);
+                if (!mbar_wait(&bars->empty[stage], phase ^ 1, a.status, 740 + stage)) {
+                  ok = false;
+                } else {
+                  if (mine) dequant_store(ring[d], smem_a + (stage * kATiles + at) * 128 * 128, row, half);
+                  fence_proxy_async();
+                  __syncwarp();
+                  if (lane == 0) mbar_arrive(&bars->full[stage]);
+                  if (mine && kb + kDepth * kb_step < k_blocks) load_raw(ring[d], wrow, srow, kb + kDepth * kb_step, half);
+                  if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+              }
+            }
           }
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
     }
@@ -333,7 +344,7 @@ static int launch_moe_grouped(const CUtensorMap& tx, const MoeGArgs& a, int grid
       return -3;
     configured = true;
   }
-  moe_grouped_kernel<BT, kFc1><<<grid, 320, smem, st>>>(tx, a);
+  moe_grouped_kernel<BT, kFc1><<<grid, 704, smem, st>>>(tx, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -115,7 +115,9 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, ew: E
         pair_row = scratch("moe.pair_row", (n_pairs,), I32, dev)
         offsets = scratch("moe.offsets", (ew.num_local + 1,), I32, dev)
         sorted_e = scratch("moe.sorted_e", (n_pairs,), I32, dev)
-        _lib.call("stk_moe_align", ids, n_pairs, ew.expert_start, ew.num_local, sorted_p, pair_row, offsets, sorted_e, st)
+        counts = scratch("moe.counts", (((n_pairs + 255) // 256) * ew.num_local,), I32, dev) if n_pairs > 2048 else None
+        _lib.call("stk_moe_align", ids, n_pairs, ew.expert_start, ew.num_local, sorted_p, pair_row, offsets, sorted_e,
+                  counts, st)
         if USE_GROUPED_GEMM and h % 64 == 0 and inter % 128 == 0 and h % 128 == 0:
             # tensor-core path: permute the activations into expert order, then two grouped GEMMs
             avg = max(1, n_pairs // max(1, total_experts or ew.num_local))
