@@ -45,6 +45,7 @@ class Request:
     finished: bool = False
     arrival: float = field(default_factory=time.time)
     first_token_time: Optional[float] = None
+    finish_reason: Optional[str] = None   # "stop" (EOS), "length" (token or context limit), "abort"
 
     @property
     def tokens(self) -> List[int]:
@@ -123,8 +124,11 @@ class Scheduler:
 
     def retire(self, req: Request) -> None:
         req.finished = True
-        self.kv.free_row(req.row)
-        self.running.remove(req)
+        if req in self.running:
+            self.kv.free_row(req.row)
+            self.running.remove(req)
+        elif req in self.waiting:
+            self.waiting.remove(req)
 
     @property
     def num_running(self) -> int:
@@ -221,6 +225,22 @@ class Engine:
 
     def has_work(self) -> bool:
         return bool(self.sched.waiting or self.sched.running)
+
+    def abort(self, req_id: int) -> bool:
+        """Drop a request between steps (client went away, stop string hit); frees its pages."""
+        r = self.requests.get(req_id)
+        if r is None or r.finished:
+            return False
+        r.finish_reason = "abort"
+        self.sched.retire(r)
+        self.metrics.requests_finished += 1
+        return True
+
+    def release(self, req_id: int) -> None:
+        """Forget a finished request (the server calls this once the response is out)."""
+        r = self.requests.get(req_id)
+        if r is not None and r.finished:
+            del self.requests[req_id]
 
     def generate(self, prompts: Sequence[Sequence[int]], params: Optional[SamplingParams] = None) -> List[List[int]]:
         ids = [self.add_request(p, params) for p in prompts]
@@ -341,6 +361,7 @@ class Engine:
                 hit_eos = (p.eos_token_id is not None and tok == p.eos_token_id and not p.ignore_eos
                            and len(r.output) >= p.min_tokens)
                 if len(r.output) >= p.max_tokens or hit_eos or r.total_len >= self.cfg.sched.max_model_len:
+                    r.finish_reason = "stop" if hit_eos else "length"
                     self.sched.retire(r)
                     self.metrics.requests_finished += 1
         self.metrics.num_requests_running = self.sched.num_running

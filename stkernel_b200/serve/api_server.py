@@ -1,0 +1,621 @@
+"""HTTP front end: OpenAI chat/completions, Anthropic messages, metrics, profiling, cache reset.
+
+The endpoints are the ones the reference's launcher, supervisor and bench clients use
+(launchers/start-hy4-tp4.sh:354-392 serve flags; launchers/dsv4-tp4-supervisor.sh:45-54,117-132
+health probe and prefix-cache reset; bench/bench-dec.py:60-119 `/metrics`; bench/profile-step.py:49-57
+`/start_profile` + `/stop_profile`; bench/bench-ctx.py:28-82 streaming with usage):
+
+    GET  /health, /v1/models, /metrics
+    POST /v1/chat/completions   (stream or not; stream_options.include_usage; tools; thinking kwargs)
+    POST /v1/completions        (raw prompt or token ids)
+    POST /v1/messages           (Anthropic wire: text / thinking / tool_use blocks, SSE events)
+    POST /start_profile, /stop_profile, /reset_prefix_cache
+
+`AsyncEngine` owns the engine on one worker thread (the thread that owns the CUDA context and
+replays the decode graphs); HTTP handlers talk to it through thread-safe queues, so a slow client
+never stalls a step.
+"""
+from __future__ import annotations
+
+import asyncio
+import json
+import queue
+import threading
+import time
+import uuid
+from dataclasses import dataclass, field
+from typing import Any, AsyncIterator, Dict, List, Optional, Sequence, Tuple
+
+from fastapi import FastAPI, Request
+from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
+
+from ..runtime.engine import Engine, SamplingParams
+from .reasoning import ReasoningSplitter, thinking_enabled
+from .tokenizer import ChatTokenizer, IncrementalDetokenizer
+from .tool_parser import ToolCallParser, BLOCK_OPENS
+
+
+# ---------------------------------------------------------------------------------------
+# engine driver
+# ---------------------------------------------------------------------------------------
+@dataclass
+class TokenEvent:
+    tokens: List[int]
+    finished: bool
+    finish_reason: Optional[str] = None
+    error: Optional[str] = None
+
+
+class AsyncEngine:
+    """Runs `engine.step()` on a worker thread; per-request asyncio queues carry the tokens out."""
+
+    def __init__(self, engine: Engine):
+        self.engine = engine
+        self._inbox: "queue.Queue[Tuple[str, Any]]" = queue.Queue()
+        self._streams: Dict[int, Tuple[asyncio.AbstractEventLoop, asyncio.Queue]] = {}
+        self._wake = threading.Event()
+        self._stop = False
+        self._profiler = None
+        self.last_trace: Optional[str] = None
+        self._thread = threading.Thread(target=self._run, name="stk-engine", daemon=True)
+        self._thread.start()
+
+    # -- worker thread --------------------------------------------------------------------
+    def _post(self, rid: int, ev: TokenEvent) -> None:
+        target = self._streams.get(rid)
+        if target is not None:
+            loop, q = target
+            loop.call_soon_threadsafe(q.put_nowait, ev)
+
+    def _drain_inbox(self) -> None:
+        while True:
+            try:
+                kind, payload = self._inbox.get_nowait()
+            except queue.Empty:
+                return
+            if kind == "add":
+                prompt, params, loop, q, fut = payload
+                try:
+                    rid = self.engine.add_request(prompt, params)
+                    self._streams[rid] = (loop, q)
+                    loop.call_soon_threadsafe(fut.set_result, rid)
+                except Exception as e:                       # rejected request (too long, ...)
+                    loop.call_soon_threadsafe(fut.set_exception, e)
+            elif kind == "abort":
+                if self.engine.abort(payload):
+                    self._post(payload, TokenEvent([], True, "abort"))
+                self._streams.pop(payload, None)
+                self.engine.release(payload)
+            elif kind == "call":
+                fn, loop, fut = payload
+                try:
+                    res = fn()
+                    loop.call_soon_threadsafe(fut.set_result, res)
+                except Exception as e:
+                    loop.call_soon_threadsafe(fut.set_exception, e)
+
+    def _run(self) -> None:
+        eng = self.engine
+        while not self._stop:
+            self._drain_inbox()
+            if not eng.has_work():
+                self._wake.wait(timeout=0.05)
+                self._wake.clear()
+                continue
+            try:
+                produced = eng.step()
+            except Exception as e:                           # a failed step fails every open stream
+                for rid in list(self._streams):
+                    self._post(rid, TokenEvent([], True, "error", error=f"{type(e).__name__}: {e}"))
+                    eng.abort(rid)
+                self._streams.clear()
+                continue
+            for rid, tok in produced:
+                r = eng.requests.get(rid)
+                done = r is not None and r.finished
+                self._post(rid, TokenEvent([tok], done, r.finish_reason if done else None))
+                if done:
+                    self._streams.pop(rid, None)
+                    eng.release(rid)
+
+    # -- asyncio side ------------------------------------------------------------------------
+    async def generate(self, prompt: Sequence[int], params: SamplingParams) -> AsyncIterator[TokenEvent]:
+        loop = asyncio.get_running_loop()
+        q: asyncio.Queue = asyncio.Queue()
+        fut = loop.create_future()
+        self._inbox.put(("add", (list(prompt), params, loop, q, fut)))
+        self._wake.set()
+        rid = await fut
+        try:
+            while True:
+                ev = await q.get()
+                yield ev
+                if ev.finished:
+                    return
+        finally:
+            self._inbox.put(("abort", rid))                    # no-op for a finished request
+            self._wake.set()
+
+    async def call(self, fn):
+        """Run `fn()` on the engine thread between steps."""
+        loop = asyncio.get_running_loop()
+        fut = loop.create_future()
+        self._inbox.put(("call", (fn, loop, fut)))
+        self._wake.set()
+        return await fut
+
+    def shutdown(self) -> None:
+        self._stop = True
+        self._wake.set()
+        self._thread.join(timeout=5)
+
+    # -- profiling (engine thread) ---------------------------------------------------------
+    def start_profile(self, out_dir: str) -> str:
+        import torch
+        if self._profiler is not None:
+            return "already running"
+        acts = [torch.profiler.ProfilerActivity.CPU]
+        if self.engine.device.type == "cuda":
+            acts.append(torch.profiler.ProfilerActivity.CUDA)
+        self._profiler = torch.profiler.profile(activities=acts)
+        self._profiler.__enter__()
+        self._profile_dir = out_dir
+        return "started"
+
+    def stop_profile(self) -> Optional[str]:
+        import os
+        if self._profiler is None:
+            return None
+        self._profiler.__exit__(None, None, None)
+        os.makedirs(self._profile_dir, exist_ok=True)
+        path = os.path.join(self._profile_dir, f"trace_{int(time.time())}.json")
+        self._profiler.export_chrome_trace(path)
+        self._profiler = None
+        self.last_trace = path
+        return path
+
+    def reset_prefix_cache(self) -> bool:
+        """Only when idle, as the supervisor's daily reset expects."""
+        if self.engine.has_work():
+            return False
+        reset = getattr(self.engine, "reset_prefix_cache", None)
+        if reset is not None:
+            reset()
+        self.engine.metrics.prefix_cache_resets += 1
+        return True
+
+
+# ---------------------------------------------------------------------------------------
+# response assembly
+# ---------------------------------------------------------------------------------------
+@dataclass
+class Piece:
+    reasoning: str = ""
+    content: str = ""
+    tool_calls: list = field(default_factory=list)      # ToolCallDelta
+
+    def __bool__(self) -> bool:
+        return bool(self.reasoning or self.content or self.tool_calls)
+
+
+class OutputPipeline:
+    """tokens -> text -> (reasoning | content | tool-call deltas), with stop strings."""
+
+    def __init__(self, tok: ChatTokenizer, thinking: bool, tools: Optional[list], stop: Sequence[str] = (),
+                 parse_tools: bool = True):
+        self.detok = IncrementalDetokenizer(tok)
+        self.split = ReasoningSplitter(thinking)
+        self.tools = ToolCallParser(tools) if (tools and parse_tools) else None
+        self.stop = [s for s in stop if s]
+        self.text = ""
+        self.stopped = False
+        self._pending = ""
+
+    def _route(self, text: str, final: bool) -> Piece:
+        r, c = self.split.push(text) if text else ("", "")
+        if final:
+            r2, c2 = self.split.flush()
+            r, c = r + r2, c + c2
+        p = Piece(reasoning=r)
+        if self.tools is None:
+            p.content = c
+        else:
+            d = self.tools.push(c) if c else None
+            if d:
+                p.content, p.tool_calls = d.content, d.tool_calls
+            if final:
+                p.content += self.tools.flush().content
+        return p
+
+    def push(self, token_ids: Sequence[int], final: bool, eos_id: Optional[int] = None) -> Piece:
+        ids = [t for t in token_ids if t != eos_id]
+        text = self._pending + self.detok.push(ids)
+        self._pending = ""
+        if self.stop and text:
+            hit = min((text.find(s) for s in self.stop if s in text), default=-1)
+            if hit >= 0:
+                text, self.stopped, final = text[:hit], True, True
+            elif not final:
+                from .tool_parser import held_back
+                k = held_back(text, self.stop)
+                if k:
+                    text, self._pending = text[:-k], text[-k:]
+        self.text += text
+        return self._route(text, final)
+
+    @property
+    def has_tool_calls(self) -> bool:
+        return self.tools is not None and bool(self.tools.complete_calls)
+
+
+def _usage(n_prompt: int, n_out: int) -> Dict[str, int]:
+    return {"prompt_tokens": n_prompt, "completion_tokens": n_out, "total_tokens": n_prompt + n_out}
+
+
+def sampling_from_request(body: Dict[str, Any], eos_id: Optional[int], max_model_len: int, n_prompt: int,
+                          default_max: int = 512) -> SamplingParams:
+    max_tokens = body.get("max_completion_tokens") or body.get("max_tokens") or default_max
+    max_tokens = max(1, min(int(max_tokens), max_model_len - n_prompt))
+    seed = body.get("seed")
+    return SamplingParams(temperature=float(body.get("temperature", 1.0) or 0.0),
+                          seed=int(seed) if seed is not None else uuid.uuid4().int & 0x7FFFFFFF,
+                          max_tokens=max_tokens, min_tokens=int(body.get("min_tokens", 0) or 0),
+                          ignore_eos=bool(body.get("ignore_eos", False)), eos_token_id=eos_id)
+
+
+def anthropic_to_chat(body: Dict[str, Any]) -> Tuple[List[Dict[str, Any]], Optional[List[Dict[str, Any]]]]:
+    """Anthropic /v1/messages request -> chat messages + OpenAI-format tools."""
+    msgs: List[Dict[str, Any]] = []
+    system = body.get("system")
+    if isinstance(system, list):
+        system = "\n\n".join(b.get("text", "") for b in system if b.get("type") == "text")
+    if system:
+        msgs.append({"role": "system", "content": system})
+    for m in body.get("messages", []):
+        role, content = m.get("role"), m.get("content")
+        if isinstance(content, str):
+            msgs.append({"role": role, "content": content})
+            continue
+        text, reasoning, calls = [], [], []
+        for b in content or []:
+            kind = b.get("type")
+            if kind == "text":
+                text.append(b.get("text", ""))
+            elif kind == "thinking":
+                reasoning.append(b.get("thinking", ""))
+            elif kind == "tool_use":
+                calls.append({"id": b.get("id", ""), "type": "function",
+                              "function": {"name": b.get("name", ""), "arguments": json.dumps(b.get("input", {}), ensure_ascii=False)}})
+            elif kind == "tool_result":
+                if text:
+                    msgs.append({"role": role, "content": "\n\n".join(text)})
+                    text = []
+                c = b.get("content", "")
+                msgs.append({"role": "tool", "tool_call_id": b.get("tool_use_id", ""), "content": c})
+        if role == "assistant":
+            a: Dict[str, Any] = {"role": "assistant", "content": "\n\n".join(text)}
+            if reasoning:
+                a["reasoning"] = "\n\n".join(reasoning)
+            if calls:
+                a["tool_calls"] = calls
+            msgs.append(a)
+        elif text:
+            msgs.append({"role": role, "content": "\n\n".join(text)})
+    tools = None
+    if body.get("tools"):
+        tools = [{"type": "function", "function": {"name": t.get("name"), "description": t.get("description", ""),
+                                                    "parameters": t.get("input_schema", {})}} for t in body["tools"]]
+    return msgs, tools
+
+
+# ---------------------------------------------------------------------------------------
+# the app
+# ---------------------------------------------------------------------------------------
+def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deepseek-v4-flash",
+               default_thinking: bool = False, profile_dir: str = "/tmp/stk_profiles",
+               default_chat_template_kwargs: Optional[Dict[str, Any]] = None):
+    app = FastAPI(title="stkernel_b200")
+    aeng = AsyncEngine(engine)
+    app.state.async_engine = aeng
+    max_len = engine.cfg.sched.max_model_len
+    eos_id = tokenizer.eos_token_id
+    created = int(time.time())
+    base_kwargs = dict(default_chat_template_kwargs or {})
+
+    def err(status: int, msg: str, kind: str = "invalid_request_error"):
+        return JSONResponse({"error": {"message": msg, "type": kind, "code": status}}, status_code=status)
+
+    def sse(obj: Any) -> str:
+        return "data: " + (obj if isinstance(obj, str) else json.dumps(obj, ensure_ascii=False)) + "\n\n"
+
+    app.router.on_shutdown.append(aeng.shutdown)
+
+    @app.get("/health")
+    async def health():
+        return PlainTextResponse("")
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": model_name, "object": "model", "created": created,
+                                            "owned_by": "stkernel_b200", "max_model_len": max_len}]}
+
+    @app.get("/metrics")
+    async def metrics():
+        return PlainTextResponse(engine.metrics.render(model_name))
+
+    @app.post("/start_profile")
+    async def start_profile():
+        return {"status": await aeng.call(lambda: aeng.start_profile(profile_dir))}
+
+    @app.post("/stop_profile")
+    async def stop_profile():
+        return {"trace": await aeng.call(aeng.stop_profile)}
+
+    @app.post("/reset_prefix_cache")
+    async def reset_prefix_cache():
+        ok = await aeng.call(aeng.reset_prefix_cache)
+        return JSONResponse({"reset": ok}, status_code=200 if ok else 409)
+
+    # ---- chat completions ---------------------------------------------------------------
+    def prepare_chat(body: Dict[str, Any]):
+        kwargs = {**base_kwargs, **(body.get("chat_template_kwargs") or {})}
+        if "reasoning_effort" in body and "reasoning_effort" not in kwargs:
+            kwargs["reasoning_effort"] = body["reasoning_effort"]
+        thinking = thinking_enabled(kwargs, default_thinking)
+        if thinking:
+            kwargs.setdefault("thinking", True)
+        tools = body.get("tools") if body.get("tool_choice") != "none" else None
+        ids = tokenizer.apply_chat_template(body["messages"], tools=tools, **kwargs)
+        return ids, thinking, tools
+
+    @app.post("/v1/chat/completions")
+    async def chat(request: Request):
+        try:
+            body = await request.json()
+            ids, thinking, tools = prepare_chat(body)
+        except Exception as e:
+            return err(400, f"{type(e).__name__}: {e}")
+        if len(ids) >= max_len:
+            return err(400, f"prompt has {len(ids)} tokens; the model's context is {max_len}")
+        params = sampling_from_request(body, eos_id, max_len, len(ids))
+        stop = body.get("stop") or []
+        stop = [stop] if isinstance(stop, str) else list(stop)
+        rid = f"chatcmpl-{uuid.uuid4().hex}"
+        pipe = OutputPipeline(tokenizer, thinking, tools, stop)
+        base = {"id": rid, "object": "chat.completion.chunk", "created": int(time.time()), "model": model_name}
+        include_usage = bool((body.get("stream_options") or {}).get("include_usage"))
+
+        def finish(reason: Optional[str]) -> str:
+            if pipe.has_tool_calls:
+                return "tool_calls"
+            return "stop" if (pipe.stopped or reason == "stop") else (reason or "stop")
+
+        if body.get("stream"):
+            async def events():
+                n_out = 0
+                yield sse({**base, "choices": [{"index": 0, "delta": {"role": "assistant", "content": ""}, "finish_reason": None}]})
+                reason = None
+                async for ev in aeng.generate(ids, params):
+                    if ev.error:
+                        yield sse({"error": {"message": ev.error, "type": "internal_error"}})
+                        break
+                    n_out += len(ev.tokens)
+                    piece = pipe.push(ev.tokens, ev.finished, eos_id)
+                    delta: Dict[str, Any] = {}
+                    if piece.reasoning:
+                        delta["reasoning_content"] = piece.reasoning
+                    if piece.content:
+                        delta["content"] = piece.content
+                    if piece.tool_calls:
+                        delta["tool_calls"] = [t.to_openai() for t in piece.tool_calls]
+                    if delta:
+                        yield sse({**base, "choices": [{"index": 0, "delta": delta, "finish_reason": None}]})
+                    reason = ev.finish_reason
+                    if pipe.stopped or ev.finished:
+                        break
+                yield sse({**base, "choices": [{"index": 0, "delta": {}, "finish_reason": finish(reason)}]})
+                if include_usage:
+                    yield sse({**base, "choices": [], "usage": _usage(len(ids), n_out)})
+                yield sse("[DONE]")
+            return StreamingResponse(events(), media_type="text/event-stream")
+
+        reasoning, content, n_out, reason = "", "", 0, None
+        async for ev in aeng.generate(ids, params):
+            if ev.error:
+                return err(500, ev.error, "internal_error")
+            n_out += len(ev.tokens)
+            piece = pipe.push(ev.tokens, ev.finished, eos_id)
+            reasoning += piece.reasoning
+            content += piece.content
+            reason = ev.finish_reason
+            if pipe.stopped or ev.finished:
+                break
+        message: Dict[str, Any] = {"role": "assistant", "content": content or None}
+        if reasoning:
+            message["reasoning_content"] = reasoning
+        if pipe.has_tool_calls:
+            message["tool_calls"] = [{"id": c["id"], "type": "function",
+                                      "function": {"name": c["name"], "arguments": c["arguments"]}}
+                                     for c in pipe.tools.complete_calls]
+        return {"id": rid, "object": "chat.completion", "created": base["created"], "model": model_name,
+                "choices": [{"index": 0, "message": message, "finish_reason": finish(reason)}],
+                "usage": _usage(len(ids), n_out)}
+
+    # ---- raw completions ------------------------------------------------------------------
+    @app.post("/v1/completions")
+    async def completions(request: Request):
+        try:
+            body = await request.json()
+            prompt = body["prompt"]
+            ids = list(prompt) if isinstance(prompt, list) and prompt and isinstance(prompt[0], int) else tokenizer.encode(prompt)
+        except Exception as e:
+            return err(400, f"{type(e).__name__}: {e}")
+        if len(ids) >= max_len:
+            return err(400, f"prompt has {len(ids)} tokens; the model's context is {max_len}")
+        params = sampling_from_request(body, eos_id, max_len, len(ids))
+        rid = f"cmpl-{uuid.uuid4().hex}"
+        pipe = OutputPipeline(tokenizer, False, None, [body["stop"]] if isinstance(body.get("stop"), str) else (body.get("stop") or []))
+        base = {"id": rid, "object": "text_completion", "created": int(time.time()), "model": model_name}
+        if body.get("stream"):
+            async def events():
+                n_out, reason = 0, None
+                async for ev in aeng.generate(ids, params):
+                    n_out += len(ev.tokens)
+                    piece = pipe.push(ev.tokens, ev.finished, eos_id)
+                    if piece.content:
+                        yield sse({**base, "choices": [{"index": 0, "text": piece.content, "finish_reason": None}]})
+                    reason = ev.finish_reason
+                    if pipe.stopped or ev.finished:
+                        break
+                yield sse({**base, "choices": [{"index": 0, "text": "", "finish_reason": "stop" if pipe.stopped else reason}],
+                           "usage": _usage(len(ids), n_out)})
+                yield sse("[DONE]")
+            return StreamingResponse(events(), media_type="text/event-stream")
+        n_out, reason = 0, None
+        async for ev in aeng.generate(ids, params):
+            if ev.error:
+                return err(500, ev.error, "internal_error")
+            n_out += len(ev.tokens)
+            pipe.push(ev.tokens, ev.finished, eos_id)
+            reason = ev.finish_reason
+            if pipe.stopped or ev.finished:
+                break
+        return {**base, "choices": [{"index": 0, "text": pipe.text, "finish_reason": "stop" if pipe.stopped else reason}],
+                "usage": _usage(len(ids), n_out)}
+
+    # ---- Anthropic messages ---------------------------------------------------------------
+    @app.post("/v1/messages")
+    async def messages(request: Request):
+        try:
+            body = await request.json()
+            msgs, tools = anthropic_to_chat(body)
+            th = body.get("thinking") or {}
+            kwargs = dict(base_kwargs)
+            if th.get("type") == "enabled":
+                kwargs["thinking"] = True
+            elif th.get("type") == "disabled":
+                kwargs["thinking"] = False
+            thinking = thinking_enabled(kwargs, default_thinking)
+            if thinking:
+                kwargs.setdefault("thinking", True)
+            ids = tokenizer.apply_chat_template(msgs, tools=tools, **kwargs)
+        except Exception as e:
+            return err(400, f"{type(e).__name__}: {e}")
+        if len(ids) >= max_len:
+            return err(400, f"prompt has {len(ids)} tokens; the model's context is {max_len}")
+        params = sampling_from_request(body, eos_id, max_len, len(ids))
+        pipe = OutputPipeline(tokenizer, thinking, tools, body.get("stop_sequences") or [])
+        mid = f"msg_{uuid.uuid4().hex[:24]}"
+
+        def stop_reason(reason):
+            if pipe.has_tool_calls:
+                return "tool_use"
+            if pipe.stopped:
+                return "stop_sequence"
+            return "end_turn" if reason == "stop" else "max_tokens"
+
+        if body.get("stream"):
+            async def events():
+                def ev_line(kind, payload):
+                    return f"event: {kind}\ndata: {json.dumps({'type': kind, **payload}, ensure_ascii=False)}\n\n"
+                yield ev_line("message_start", {"message": {"id": mid, "type": "message", "role": "assistant", "model": model_name,
+                                                            "content": [], "stop_reason": None,
+                                                            "usage": {"input_tokens": len(ids), "output_tokens": 0}}})
+                block, kind_open, n_out, reason = -1, None, 0, None
+                tool_block: Dict[int, int] = {}
+
+                def open_block(kind, payload):
+                    nonlocal block, kind_open
+                    out = ""
+                    if kind_open is not None:
+                        out += ev_line("content_block_stop", {"index": block})
+                    block += 1
+                    kind_open = kind
+                    return out + ev_line("content_block_start", {"index": block, "content_block": payload})
+
+                async for ev in aeng.generate(ids, params):
+                    n_out += len(ev.tokens)
+                    piece = pipe.push(ev.tokens, ev.finished, eos_id)
+                    if piece.reasoning:
+                        if kind_open != "thinking":
+                            yield open_block("thinking", {"type": "thinking", "thinking": ""})
+                        yield ev_line("content_block_delta", {"index": block, "delta": {"type": "thinking_delta", "thinking": piece.reasoning}})
+                    if piece.content:
+                        if kind_open != "text":
+                            yield open_block("text", {"type": "text", "text": ""})
+                        yield ev_line("content_block_delta", {"index": block, "delta": {"type": "text_delta", "text": piece.content}})
+                    for t in piece.tool_calls:
+                        if t.id is not None:
+                            yield open_block(f"tool{t.index}", {"type": "tool_use", "id": t.id.replace("call_", "toolu_"), "name": t.name, "input": {}})
+                            tool_block[t.index] = block
+                        if t.arguments:
+                            yield ev_line("content_block_delta", {"index": tool_block[t.index],
+                                                                  "delta": {"type": "input_json_delta", "partial_json": t.arguments}})
+                    reason = ev.finish_reason
+                    if pipe.stopped or ev.finished:
+                        break
+                if kind_open is not None:
+                    yield ev_line("content_block_stop", {"index": block})
+                yield ev_line("message_delta", {"delta": {"stop_reason": stop_reason(reason), "stop_sequence": None},
+                                                "usage": {"output_tokens": n_out}})
+                yield ev_line("message_stop", {})
+            return StreamingResponse(events(), media_type="text/event-stream")
+
+        reasoning, content, n_out, reason = "", "", 0, None
+        async for ev in aeng.generate(ids, params):
+            if ev.error:
+                return err(500, ev.error, "api_error")
+            n_out += len(ev.tokens)
+            piece = pipe.push(ev.tokens, ev.finished, eos_id)
+            reasoning += piece.reasoning
+            content += piece.content
+            reason = ev.finish_reason
+            if pipe.stopped or ev.finished:
+                break
+        blocks: List[Dict[str, Any]] = []
+        if reasoning:
+            blocks.append({"type": "thinking", "thinking": reasoning})
+        if content:
+            blocks.append({"type": "text", "text": content})
+        if pipe.has_tool_calls:
+            for c in pipe.tools.complete_calls:
+                blocks.append({"type": "tool_use", "id": c["id"].replace("call_", "toolu_"), "name": c["name"],
+                               "input": json.loads(c["arguments"] or "{}")})
+        return {"id": mid, "type": "message", "role": "assistant", "model": model_name, "content": blocks,
+                "stop_reason": stop_reason(reason), "stop_sequence": None,
+                "usage": {"input_tokens": len(ids), "output_tokens": n_out}}
+
+    return app
+
+
+def main(argv: Optional[Sequence[str]] = None) -> int:
+    """`python -m stkernel_b200.serve.api_server --layers N [--tokenizer DIR] [--port P]`: serve a
+    random-weight model of the flagship architecture (a checkpoint path goes through the launcher)."""
+    import argparse
+    import torch
+    import uvicorn
+    from ..config import flash_config, tiny_config, EngineConfig
+    from ..models.dsv4 import RandomSource, build_model_weights
+    from .tokenizer import ByteTokenizer, HFTokenizer
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=2)
+    ap.add_argument("--tiny", action="store_true", help="CPU-sized architecture (tests, demos)")
+    ap.add_argument("--tokenizer", default=None)
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8000)
+    ap.add_argument("--served-model-name", default="deepseek-v4-flash")
+    ap.add_argument("--default-thinking", action="store_true")
+    a = ap.parse_args(argv)
+    device = torch.device("cuda:0" if torch.cuda.is_available() else "cpu")
+    mcfg = tiny_config() if a.tiny else flash_config(a.layers)
+    cfg = EngineConfig(model=mcfg)
+    weights = build_model_weights(mcfg, RandomSource(mcfg, seed=0), device)
+    eng = Engine(cfg, weights, device)
+    tok = ChatTokenizer(HFTokenizer(a.tokenizer) if a.tokenizer else ByteTokenizer(mcfg.vocab_size))
+    uvicorn.run(create_app(eng, tok, a.served_model_name, a.default_thinking), host=a.host, port=a.port, log_level="info")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,0 +1,295 @@
+"""Serving layer on CPU: chat encoding goldens, tool/reasoning parsers (whole and streamed),
+tokenizer front end, and the HTTP app over a tiny random-weight engine."""
+import json
+import os
+import random
+
+import pytest
+
+from stkernel_b200.serve import encoding as E
+from stkernel_b200.serve.reasoning import ReasoningSplitter, split_reasoning, thinking_enabled
+from stkernel_b200.serve.tokenizer import ByteTokenizer, ChatTokenizer, IncrementalDetokenizer, chat_encode_config, render_chat
+from stkernel_b200.serve.tool_parser import ToolCallParser, coerce, extract_tool_calls, held_back, schema_types
+
+GOLD = json.load(open(os.path.join(os.path.dirname(__file__), "fixtures", "dsv4_encoding_golden.json")))
+D = E.DSML
+TOOLS = [{"type": "function", "function": {"name": "get_weather", "parameters": {"type": "object", "properties": {
+    "city": {"type": "string"}, "days": {"type": "integer"}, "opts": {"type": "object"}, "t": {"type": ["number", "null"]}}}}}]
+
+
+# ---- encoding --------------------------------------------------------------------------
+@pytest.mark.parametrize("i", range(len(GOLD["encode"])))
+def test_encode_golden(i):
+    g = GOLD["encode"][i]
+    if g["prompt"] is None:
+        with pytest.raises(Exception):
+            E.encode_messages(g["messages"], **g["kwargs"])
+    else:
+        assert E.encode_messages(g["messages"], **g["kwargs"]) == g["prompt"]
+
+
+@pytest.mark.parametrize("i", range(len(GOLD["parse"])))
+def test_parse_golden(i):
+    g = GOLD["parse"][i]
+    if g["message"] is None:
+        with pytest.raises(ValueError):
+            E.parse_message_from_completion_text(g["text"], g["thinking_mode"])
+    else:
+        assert E.parse_message_from_completion_text(g["text"], g["thinking_mode"]) == g["message"]
+
+
+def test_encode_basics():
+    p = E.encode_messages([{"role": "user", "content": "hi"}], thinking_mode="chat")
+    assert p == f"{E.BOS}{E.USER}hi{E.ASSISTANT}{E.THINK_CLOSE}"
+    p = E.encode_messages([{"role": "user", "content": "hi"}], thinking_mode="thinking", reasoning_effort="max")
+    assert p.startswith(E.BOS + "Reasoning Effort: Beyond maximum") and p.endswith(E.ASSISTANT + E.THINK_OPEN)
+    with pytest.raises(ValueError):
+        E.encode_messages([{"role": "user", "content": "hi"}], thinking_mode="other")
+
+
+def test_encode_roundtrip_with_parser():
+    calls = [{"id": "a", "type": "function", "function": {"name": "get_weather", "arguments": json.dumps({"city": "서울", "days": 2})}}]
+    body = "plan" + E.THINK_CLOSE + "Checking." + E.dsml_tool_calls(calls) + E.EOS
+    m = E.parse_message_from_completion_text(body, "thinking")
+    assert m["reasoning"] == "plan" and m["content"] == "Checking."
+    assert json.loads(m["tool_calls"][0]["function"]["arguments"]) == {"city": "서울", "days": 2}
+
+
+def test_tool_results_follow_call_order_and_drop_thinking():
+    msgs = [{"role": "user", "content": "q"},
+            {"role": "assistant", "content": "", "reasoning": "r1", "tool_calls": [
+                {"id": "x", "type": "function", "function": {"name": "f", "arguments": "{}"}},
+                {"id": "y", "type": "function", "function": {"name": "g", "arguments": "{}"}}]},
+            {"role": "tool", "tool_call_id": "y", "content": "Y"},
+            {"role": "tool", "tool_call_id": "x", "content": "X"},
+            {"role": "assistant", "content": "done", "reasoning": "r2"},
+            {"role": "user", "content": "next"}]
+    p = E.encode_messages(msgs, thinking_mode="thinking")
+    assert p.index("<tool_result>X") < p.index("<tool_result>Y")
+    assert "r1" not in p and "r2" not in p                      # reasoning before the last user turn is dropped
+    p2 = E.encode_messages(msgs, thinking_mode="thinking", drop_thinking=False)
+    assert "r1" in p2 and "r2" in p2
+
+
+# ---- tokenizer front end ---------------------------------------------------------------
+def test_effort_mapping_and_tools_on_system():
+    assert chat_encode_config({"thinking": True, "reasoning_effort": "none"})["thinking_mode"] == "chat"
+    assert chat_encode_config({"reasoning_effort": "xhigh"})["reasoning_effort"] == "max"
+    assert chat_encode_config({"reasoning_effort": "medium"})["reasoning_effort"] is None
+    assert chat_encode_config({"enable_thinking": True})["thinking_mode"] == "thinking"
+    p = render_chat([{"role": "system", "content": "SYS"}, {"role": "user", "content": "u"}], TOOLS)
+    assert p.startswith(E.BOS + "SYS\n\n## Tools")
+    p = render_chat([{"role": "user", "content": "u"}], TOOLS)
+    assert p.startswith(E.BOS + "\n\n## Tools") and "get_weather" in p
+
+
+def test_byte_tokenizer_and_incremental_detok():
+    bt = ByteTokenizer(512)
+    text = f"{E.BOS}{E.USER}héllo 서울 🙂{E.ASSISTANT}{E.THINK_OPEN}"
+    ids = bt.encode(text)
+    assert bt.decode(ids) == text and ids[0] == bt.bos_token_id
+    d = IncrementalDetokenizer(bt)
+    parts = [d.push([t]) for t in ids]
+    assert "".join(parts) == text
+    assert all("�" not in p for p in parts)
+    ct = ChatTokenizer(bt)
+    assert ct.apply_chat_template([{"role": "user", "content": "x"}], tokenize=False).endswith(E.THINK_CLOSE)
+
+
+# ---- reasoning --------------------------------------------------------------------------
+def test_reasoning_split():
+    assert split_reasoning("a</think>b", True) == ("a", "b")
+    assert split_reasoning("<think>a</think>b", True) == ("a", "b")
+    assert split_reasoning("only thinking", True) == ("only thinking", None)
+    assert split_reasoning("a</think>b", False) == (None, "a</think>b")
+    assert thinking_enabled({"thinking": True, "reasoning_effort": "none"}) is False
+    assert thinking_enabled({}, default=True) is True and thinking_enabled({"enable_thinking": False}, default=True) is False
+    text = f"hmm <｜ not a tag</thin still</think>answer <"
+    for step in (1, 2, 5):
+        s = ReasoningSplitter(True)
+        r = c = ""
+        for i in range(0, len(text), step):
+            a, b = s.push(text[i:i + step])
+            r, c = r + a, c + b
+        a, b = s.flush()
+        assert (r + a, c + b) == ("hmm <｜ not a tag</thin still", "answer <")
+
+
+def test_reasoning_recovers_tool_block_without_close():
+    text = f'thinking...\n\n<{D}tool_calls>\n<{D}invoke name="get_weather">\n</{D}invoke>\n</{D}tool_calls>'
+    r, c = split_reasoning(text, True)
+    assert r == "thinking..." and c.startswith(f"\n\n<{D}tool_calls>")
+
+
+# ---- tool parser --------------------------------------------------------------------------
+def _block(name="tool_calls"):
+    return (f'Sure.\n\n<{D}{name}>\n<{D}invoke name="get_weather">\n'
+            f'<{D}parameter name="city" string="true">서울 "x"\n2</{D}parameter>\n'
+            f'<{D}parameter name="days" string="false">3</{D}parameter>\n'
+            f'<{D}parameter name="opts" string="false">{{"a": [1, 2]}}</{D}parameter>\n'
+            f'<{D}parameter name="t" string="false">null</{D}parameter>\n'
+            f'</{D}invoke>\n<{D}invoke name="get_weather">\n'
+            f'<{D}parameter name="arguments" string="false">{{"city": "x"}}</{D}parameter>\n'
+            f'</{D}invoke>\n<{D}invoke name="noargs">\n</{D}invoke>\n</{D}{name}>')
+
+
+@pytest.mark.parametrize("name", ["tool_calls", "function_calls"])
+def test_extract_tool_calls(name):
+    content, calls = extract_tool_calls(_block(name), TOOLS)
+    assert content == "Sure."
+    assert [c["function"]["name"] for c in calls] == ["get_weather", "get_weather", "noargs"]
+    assert json.loads(calls[0]["function"]["arguments"]) == {"city": '서울 "x"\n2', "days": 3, "opts": {"a": [1, 2]}, "t": None}
+    assert json.loads(calls[1]["function"]["arguments"]) == {"city": "x"}            # wrapper unwrapped
+    assert json.loads(calls[2]["function"]["arguments"]) == {}
+    assert all(c["id"].startswith("call_") and len(c["id"]) == 29 for c in calls)
+
+
+def test_extract_without_calls_returns_text():
+    assert extract_tool_calls("plain text") == ("plain text", [])
+    broken = f"x <{D}tool_calls>\n<{D}invoke name="
+    assert extract_tool_calls(broken) == (broken, [])
+
+
+@pytest.mark.parametrize("step", [1, 2, 3, 7, 11, 64, 10000])
+def test_streaming_matches_whole(step):
+    text = _block()
+    _, whole = extract_tool_calls(text, TOOLS)
+    p = ToolCallParser(TOOLS)
+    content, args, names, ids = "", {}, {}, {}
+    for i in range(0, len(text), step):
+        d = p.push(text[i:i + step])
+        content += d.content
+        for t in d.tool_calls:
+            wire = t.to_openai()
+            assert None not in wire.values() and None not in wire["function"].values()    # no null keys on the wire
+            args[t.index] = args.get(t.index, "") + (t.arguments or "")
+            if t.name is not None:
+                assert t.index not in names and t.id is not None
+                names[t.index], ids[t.index] = t.name, t.id
+    content += p.flush().content
+    assert content == "Sure."
+    assert [names[i] for i in range(3)] == [c["function"]["name"] for c in whole]
+    for i in range(3):
+        assert json.loads(args[i]) == json.loads(whole[i]["function"]["arguments"])
+
+
+def test_streaming_string_param_streams_early_scalars_wait():
+    p = ToolCallParser(TOOLS)
+    p.push(f'<{D}tool_calls>\n<{D}invoke name="get_weather">\n<{D}parameter name="city" string="true">Seo')
+    d = p.push("ul and")
+    assert d.tool_calls and d.tool_calls[0].arguments == "ul and"
+    p.push(f'</{D}parameter>\n<{D}parameter name="days" string="false">1')
+    d = p.push("2")
+    assert not d                                               # integer waits for the closing tag
+    d = p.push(f"</{D}parameter>")
+    assert d.tool_calls[0].arguments == ',"days":12'
+
+
+def test_schema_helpers():
+    assert schema_types({"type": ["integer", "null"]}) == ["integer", "null"]
+    assert schema_types({"anyOf": [{"type": "string"}, {"type": "array"}]}) == ["string", "array"]
+    assert schema_types({}) == ["string"] and schema_types({"enum": [1, 2]}) == ["integer"]
+    assert coerce("5", ["integer"]) == 5 and coerce("5.5", ["number"]) == 5.5 and coerce("true", ["boolean"]) is True
+    assert coerce("abc", ["integer"]) == "abc" and coerce('{"a":1}', ["integer"]) == {"a": 1}
+    assert coerce("[1]", ["array"]) == [1] and coerce("null", ["integer", "null"]) is None
+    assert held_back("abc</thi", ["</think>"]) == 5 and held_back("abc", ["</think>"]) == 0
+
+
+# ---- HTTP app ------------------------------------------------------------------------------
+@pytest.fixture(scope="module")
+def client():
+    import torch
+    from fastapi.testclient import TestClient
+    from stkernel_b200.config import EngineConfig, SchedulerConfig, tiny_config
+    from stkernel_b200.models.dsv4 import DictSource, build_model_weights
+    from stkernel_b200.models.weights import init_random_weights
+    from stkernel_b200.runtime.engine import Engine
+    from stkernel_b200.serve.api_server import create_app
+    torch.manual_seed(0)
+    cfg = tiny_config()
+    ec = EngineConfig(model=cfg, sched=SchedulerConfig(max_model_len=512, max_num_seqs=4, max_num_batched_tokens=256,
+                                                       graph_cap=0)).validate()
+    eng = Engine(ec, build_model_weights(cfg, DictSource(init_random_weights(cfg, seed=0)), "cpu"), "cpu", max_context=512)
+    app = create_app(eng, ChatTokenizer(ByteTokenizer(cfg.vocab_size)), "tiny-dsv4", profile_dir="/tmp/stk_test_profiles")
+    with TestClient(app) as c:
+        yield c
+
+
+def _sse(resp):
+    out = []
+    for line in resp.iter_lines():
+        if line.startswith("data: "):
+            out.append(line[6:])
+    return out
+
+
+def test_models_health_metrics(client):
+    assert client.get("/health").status_code == 200
+    m = client.get("/v1/models").json()
+    assert m["data"][0]["id"] == "tiny-dsv4"
+    text = client.get("/metrics").text
+    assert "vllm:generation_tokens_total" in text and "vllm:num_requests_running" in text
+
+
+def test_chat_completion_and_usage(client):
+    body = {"model": "tiny-dsv4", "messages": [{"role": "user", "content": "hello"}], "max_tokens": 6, "temperature": 0, "ignore_eos": True}
+    r = client.post("/v1/chat/completions", json=body).json()
+    assert r["object"] == "chat.completion" and r["choices"][0]["finish_reason"] == "length"
+    assert r["usage"]["completion_tokens"] == 6 and r["usage"]["prompt_tokens"] > 0
+    r2 = client.post("/v1/chat/completions", json=body).json()
+    assert r2["choices"][0]["message"] == r["choices"][0]["message"]               # greedy is reproducible
+    before = client.get("/metrics").text
+    from stkernel_b200.runtime.metrics import parse_prometheus
+    assert parse_prometheus(before)['vllm:generation_tokens_total{model_name="tiny-dsv4"}'] >= 12
+
+
+def test_chat_stream_matches_nonstream(client):
+    body = {"messages": [{"role": "user", "content": "stream me"}], "max_tokens": 8, "temperature": 0, "ignore_eos": True}
+    whole = client.post("/v1/chat/completions", json=body).json()["choices"][0]["message"]["content"] or ""
+    with client.stream("POST", "/v1/chat/completions", json={**body, "stream": True, "stream_options": {"include_usage": True}}) as resp:
+        lines = _sse(resp)
+    assert lines[-1] == "[DONE]"
+    chunks = [json.loads(x) for x in lines[:-1]]
+    assert chunks[0]["choices"][0]["delta"]["role"] == "assistant"
+    text = "".join(c["choices"][0]["delta"].get("content", "") for c in chunks if c["choices"])
+    assert text == whole
+    assert chunks[-1]["usage"]["completion_tokens"] == 8 and chunks[-1]["choices"] == []
+    assert chunks[-2]["choices"][0]["finish_reason"] == "length"
+
+
+def test_thinking_mode_routes_to_reasoning(client):
+    body = {"messages": [{"role": "user", "content": "think"}], "max_tokens": 5, "temperature": 0, "ignore_eos": True,
+            "chat_template_kwargs": {"thinking": True}}
+    m = client.post("/v1/chat/completions", json=body).json()["choices"][0]["message"]
+    assert m["content"] is None and m.get("reasoning_content")                     # never closed its reasoning
+
+
+def test_concurrent_requests_and_bad_request(client):
+    import concurrent.futures as cf
+    def one(i):
+        return client.post("/v1/completions", json={"prompt": f"p{i}", "max_tokens": 4, "temperature": 0, "ignore_eos": True}).json()
+    with cf.ThreadPoolExecutor(4) as ex:
+        outs = list(ex.map(one, range(6)))
+    assert all(o["usage"]["completion_tokens"] == 4 for o in outs)
+    assert client.post("/v1/chat/completions", json={"messages": [{"role": "alien", "content": "x"}]}).status_code == 400
+    long = {"messages": [{"role": "user", "content": "x" * 600}]}
+    assert client.post("/v1/chat/completions", json=long).status_code == 400
+
+
+def test_anthropic_messages(client):
+    body = {"model": "tiny-dsv4", "max_tokens": 5, "temperature": 0, "system": "S", "ignore_eos": True,
+            "messages": [{"role": "user", "content": [{"type": "text", "text": "hi"}]}]}
+    r = client.post("/v1/messages", json=body).json()
+    assert r["type"] == "message" and r["stop_reason"] == "max_tokens" and r["usage"]["output_tokens"] == 5
+    with client.stream("POST", "/v1/messages", json={**body, "stream": True}) as resp:
+        kinds = [json.loads(x)["type"] for x in _sse(resp)]
+    assert kinds[0] == "message_start" and kinds[-1] == "message_stop" and "message_delta" in kinds
+
+
+def test_profile_and_cache_reset(client):
+    assert client.post("/start_profile").json()["status"] == "started"
+    client.post("/v1/completions", json={"prompt": "x", "max_tokens": 2, "temperature": 0})
+    trace = client.post("/stop_profile").json()["trace"]
+    assert trace and os.path.exists(trace)
+    assert client.post("/reset_prefix_cache").json()["reset"] is True
+    assert "stk:prefix_cache_resets_total" in client.get("/metrics").text
