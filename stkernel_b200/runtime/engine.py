@@ -46,6 +46,7 @@ class Request:
     arrival: float = field(default_factory=time.time)
     first_token_time: Optional[float] = None
     finish_reason: Optional[str] = None   # "stop" (EOS), "length" (token or context limit), "abort"
+    drafts: List[int] = field(default_factory=list)   # proposals awaiting verification (speculative decoding)
 
     @property
     def tokens(self) -> List[int]:
@@ -75,6 +76,7 @@ class ScheduledSeq:
     start: int          # first position computed this step
     n: int              # tokens computed this step
     samples: bool       # the last token of this span produces a new token
+    n_sample: int = 1   # trailing rows that sample (1 + drafts for a verifying decode row)
 
 
 class Scheduler:
@@ -99,8 +101,9 @@ class Scheduler:
                 continue
             if budget <= 0:
                 break
-            out.append(ScheduledSeq(r, r.num_computed, 1, True))
-            budget -= 1
+            k = min(len(r.drafts), budget - 1)
+            out.append(ScheduledSeq(r, r.num_computed, 1 + k, True, 1 + k))
+            budget -= 1 + k
         # 2) running prefills continue, chunked
         for r in self.running:
             if r.finished or not r.in_prefill or budget <= 0:
@@ -142,16 +145,17 @@ class Scheduler:
 class HostStage:
     """One set of pinned staging buffers with numpy views (cheap element writes from Python)."""
 
-    def __init__(self, max_tokens: int, max_reqs: int, pin: bool):
+    def __init__(self, max_tokens: int, max_reqs: int, pin: bool, max_samples: Optional[int] = None):
         mk = lambda n, dt: torch.zeros(n, dtype=dt, pin_memory=pin)
         self.h_tokens = mk(max_tokens, torch.int64)
         self.h_qstart = mk(max_reqs + 1, torch.int32)
         self.h_rows = mk(max_reqs, torch.int32)
         self.h_start = mk(max_reqs, torch.int32)
-        self.h_logit_rows = mk(max_reqs, torch.int64)
-        self.h_temp = mk(max_reqs, torch.float32)
-        self.h_seed = mk(max_reqs, torch.int64)
-        self.h_pos = mk(max_reqs, torch.int64)
+        ms = max_samples or max_reqs
+        self.h_logit_rows = mk(ms, torch.int64)
+        self.h_temp = mk(ms, torch.float32)
+        self.h_seed = mk(ms, torch.int64)
+        self.h_pos = mk(ms, torch.int64)
         self.n_tokens, self.n_qstart, self.n_rows, self.n_start = (self.h_tokens.numpy(), self.h_qstart.numpy(),
                                                                    self.h_rows.numpy(), self.h_start.numpy())
         self.n_logit_rows, self.n_temp, self.n_seed, self.n_pos = (self.h_logit_rows.numpy(), self.h_temp.numpy(),
@@ -163,15 +167,15 @@ class StepBuffers:
     """Two pinned host staging sets (the host may prepare step k+1 while the copies of step k are
     still queued) + fixed-address device tensors for the step description."""
 
-    def __init__(self, max_tokens: int, max_reqs: int, device):
+    def __init__(self, max_tokens: int, max_reqs: int, device, max_samples: Optional[int] = None):
         pin = torch.device(device).type == "cuda"
-        self.stages = [HostStage(max_tokens, max_reqs, pin) for _ in range(2)]
+        self.stages = [HostStage(max_tokens, max_reqs, pin, max_samples) for _ in range(2)]
         self.parity = 0
         h = self.stages[0]
         dv = lambda x: torch.zeros_like(x, device=device)
         self.d_tokens, self.d_qstart, self.d_rows, self.d_start = dv(h.h_tokens), dv(h.h_qstart), dv(h.h_rows), dv(h.h_start)
         self.d_logit_rows, self.d_temp, self.d_seed, self.d_pos = dv(h.h_logit_rows), dv(h.h_temp), dv(h.h_seed), dv(h.h_pos)
-        self.h_out = torch.zeros(max_reqs, dtype=torch.int64, pin_memory=pin)
+        self.h_out = torch.zeros(3 * (max_samples or max_reqs) + max_reqs, dtype=torch.int64, pin_memory=pin)
         self.cuda = pin
 
     def next_stage(self) -> HostStage:
@@ -188,7 +192,7 @@ class StepBuffers:
 
 class Engine:
     def __init__(self, cfg: EngineConfig, weights: ModelWeights, device, comm=None, tp_rank: int = 0,
-                 max_context: Optional[int] = None):
+                 max_context: Optional[int] = None, draft_weights=None, mask_token_id: int = 0):
         cfg.validate()
         self.cfg = cfg
         self.device = torch.device(device)
@@ -198,11 +202,25 @@ class Engine:
         if cfg.cache.num_pages is not None:
             pools["swa_pages"] = max(pools["swa_pages"], cfg.cache.num_pages)
         has_c128 = any(cfg.model.layer_kind(i) == "c128a" for i in range(cfg.model.num_hidden_layers))
-        self.kv = KVManager(cfg.model, self.device, sc.max_num_seqs, ctx + 64, pools["swa_pages"], pools["c4_pages"],
-                            pools["c128_pages"] if has_c128 else 0, sc.max_num_batched_tokens)
+        spec_on = cfg.spec.method == "dspark"
+        n_spec = cfg.spec.num_speculative_tokens if spec_on else 0
+        if spec_on and draft_weights is None:
+            raise ValueError("speculative decoding needs the draft weights")
+        # a verify step touches N positions past the accepted prefix and the draft block N more
+        self.spec_lookahead = 2 * n_spec + 1 if spec_on else 0
+        self.kv = KVManager(cfg.model, self.device, sc.max_num_seqs, ctx + 64, pools["swa_pages"] + (sc.max_num_seqs if spec_on else 0),
+                            pools["c4_pages"], pools["c128_pages"] if has_c128 else 0, sc.max_num_batched_tokens,
+                            extra_swa_layers=cfg.model.n_mtp_layers if spec_on else 0, spec_tokens=n_spec)
         self.model = DSV4Model(cfg.model, weights, self.kv, comm, tp_rank, cfg.parallel.tp_size)
         self.sched = Scheduler(cfg, self.kv)
-        self.buf = StepBuffers(sc.max_num_batched_tokens + sc.max_num_seqs, sc.max_num_seqs, self.device)
+        self.buf = StepBuffers(sc.max_num_batched_tokens + sc.max_num_seqs * (1 + n_spec), sc.max_num_seqs, self.device,
+                               sc.max_num_seqs * (1 + n_spec))
+        self.drafter = None
+        if spec_on:
+            from ..spec.dspark import DSparkDrafter
+            self.model.aux_layers = tuple(cfg.model.dspark_target_layer_ids)
+            self.drafter = DSparkDrafter(cfg.model, cfg.spec, draft_weights, self.kv, comm, tp_rank, cfg.parallel.tp_size,
+                                         mask_token_id)
         self.metrics = Metrics()
         self._next_id = 0
         self.requests: Dict[int, Request] = {}
@@ -256,18 +274,22 @@ class Engine:
         ns = 0
         for i, s in enumerate(seqs):
             r = s.req
-            self.kv.prepare(r.row, s.start, s.n)
-            b.n_tokens[t:t + s.n] = r.token_span(s.start, s.n)
+            self.kv.prepare(r.row, s.start, s.n + self.spec_lookahead)
+            if s.n_sample > 1:
+                b.n_tokens[t:t + s.n] = r.token_span(s.start, 1) + r.drafts[:s.n - 1]
+            else:
+                b.n_tokens[t:t + s.n] = r.token_span(s.start, s.n)
             b.n_qstart[i] = t
             b.n_rows[i] = r.row
             b.n_start[i] = s.start
             t += s.n
             if s.samples:
-                b.n_logit_rows[ns] = t - 1
-                b.n_temp[ns] = r.params.temperature
-                b.n_seed[ns] = r.params.seed
-                b.n_pos[ns] = s.start + s.n          # position of the token being sampled
-                ns += 1
+                for j in range(s.n - s.n_sample, s.n):
+                    b.n_logit_rows[ns] = t - s.n + j
+                    b.n_temp[ns] = r.params.temperature
+                    b.n_seed[ns] = r.params.seed
+                    b.n_pos[ns] = s.start + j + 1    # position of the token being sampled
+                    ns += 1
         b.n_qstart[len(seqs)] = t
         return t, len(seqs), ns
 
@@ -312,6 +334,8 @@ class Engine:
 
         `forced` (benchmarking / teacher forcing): use these tokens as the sampled ones and skip the
         device->host read, so consecutive steps queue on the device without a host round trip."""
+        if self.drafter is not None:
+            return self._step_spec()
         seqs = self.sched.schedule()
         if not seqs:
             return []
@@ -364,6 +388,101 @@ class Engine:
                     r.finish_reason = "stop" if hit_eos else "length"
                     self.sched.retire(r)
                     self.metrics.requests_finished += 1
+        self.metrics.num_requests_running = self.sched.num_running
+        self.metrics.num_requests_waiting = self.sched.num_waiting
+        self.metrics.steps_total += 1
+        return out
+
+    # ---- speculative step ---------------------------------------------------------------
+    def _finish_if_done(self, r: Request, tok: int) -> bool:
+        p = r.params
+        hit_eos = (p.eos_token_id is not None and tok == p.eos_token_id and not p.ignore_eos
+                   and len(r.output) >= p.min_tokens)
+        if len(r.output) >= p.max_tokens or hit_eos or r.total_len >= self.cfg.sched.max_model_len:
+            r.finish_reason = "stop" if hit_eos else "length"
+            self.sched.retire(r)
+            self.metrics.requests_finished += 1
+            return True
+        return False
+
+    def _step_spec(self) -> List[Tuple[int, int]]:
+        """Target step over [last token, drafts...] rows + prefill chunks, coupled verify, context-KV
+        insert for the draft layers, next draft block; one device->host read for all of it."""
+        seqs = self.sched.schedule()
+        if not seqs:
+            return []
+        n_spec = self.drafter.n
+        t, n_req, ns = self._stage(seqs)
+        self._upload(t, n_req, ns)
+        max_end = max(s.start + s.n for s in seqs)
+        meta = self._build_meta(t, n_req, max(1, max_end // 4))
+        X = self.model.forward_hidden(meta)
+        aux = self.model.aux_out[0] if len(self.model.aux_out) == 1 else torch.cat(self.model.aux_out, -1)
+        self.drafter.insert_context(aux, meta.positions, meta.swa_slot_mapping)
+        now = time.time()
+        out: List[Tuple[int, int]] = []
+        samp = [s for s in seqs if s.samples]
+        if samp:
+            b = self.buf
+            dev = self.device
+            logits = self.model.compute_logits(self.model.head_hidden(X.index_select(0, b.d_logit_rows[:ns])))
+            toks, _ = S.gumbel_argmax(logits, b.d_temp[:ns], b.d_seed[:ns], b.d_pos[:ns])
+            nb = len(samp)
+            host = torch.zeros(nb, 5 + n_spec, dtype=torch.int64)
+            temps = torch.zeros(nb, dtype=torch.float32)
+            row0 = 0
+            for i, s in enumerate(samp):
+                k = s.n_sample - 1
+                host[i, 0], host[i, 1], host[i, 2], host[i, 3] = row0, s.start + s.n - s.n_sample, s.req.row, s.req.params.seed
+                host[i, 5:] = -1
+                if k:
+                    host[i, 5:5 + k] = torch.tensor(s.req.drafts[:k], dtype=torch.int64)
+                temps[i] = s.req.params.temperature
+                row0 += s.n_sample
+            hd = host.to(dev, non_blocking=True)
+            td = temps.to(dev, non_blocking=True)
+            idx = (hd[:, 0:1] + torch.arange(n_spec + 1, device=dev)[None, :]).clamp_(max=ns - 1)
+            ver = toks[idx]
+            n_acc, _ = S.coupled_accept(ver, hd[:, 5:].contiguous())
+            anchor = ver.gather(1, n_acc[:, None]).squeeze(1)
+            anchor_pos = hd[:, 1] + n_acc + 1
+            new_drafts, _ = self.drafter.draft(anchor, anchor_pos, hd[:, 2], td, hd[:, 3])
+            packed = torch.cat([n_acc, ver.reshape(-1), new_drafts.reshape(-1)])
+            n_out = packed.numel()
+            if dev.type == "cuda":
+                self.buf.h_out[:n_out].copy_(packed, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                res = self.buf.h_out[:n_out].tolist()
+            else:
+                res = packed.tolist()
+            self.d2h_bytes_last = n_out * 8
+            acc_h = res[:nb]
+            ver_h = res[nb:nb + nb * (n_spec + 1)]
+            dr_h = res[nb + nb * (n_spec + 1):]
+        si = 0
+        for s in seqs:
+            r = s.req
+            if s.start < len(r.prompt):
+                self.metrics.prompt_tokens_total += min(s.n, len(r.prompt) - s.start)
+            if not s.samples:
+                r.num_computed = s.start + s.n
+                continue
+            a = acc_h[si]
+            if s.n_sample > 1:
+                self.metrics.record_spec(s.n_sample - 1, a)
+            base = s.start + s.n - s.n_sample
+            for j in range(a + 1):
+                tok = ver_h[si * (n_spec + 1) + j]
+                r.output.append(tok)
+                if r.first_token_time is None:
+                    r.first_token_time = now
+                self.metrics.generation_tokens_total += 1
+                out.append((r.req_id, tok))
+                if self._finish_if_done(r, tok):
+                    break
+            r.num_computed = base + a + 1
+            r.drafts = dr_h[si * n_spec:(si + 1) * n_spec]
+            si += 1
         self.metrics.num_requests_running = self.sched.num_running
         self.metrics.num_requests_waiting = self.sched.num_waiting
         self.metrics.steps_total += 1

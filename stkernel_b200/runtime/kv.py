@@ -126,7 +126,7 @@ class KVManager:
 
     def __init__(self, cfg: ModelConfig, device, max_requests: int, max_model_len: int, swa_pages: int,
                  c4_pages: int, c128_pages: int = 0, max_chunk: int = 4096, layers: Optional[List[int]] = None,
-                 extra_swa_layers: int = 0):
+                 extra_swa_layers: int = 0, spec_tokens: int = 0):
         self.cfg = cfg
         self.device = torch.device(device)
         self.max_requests = max_requests
@@ -145,6 +145,11 @@ class KVManager:
         self.comp_state: Dict[int, torch.Tensor] = {}
         self.idx_state: Dict[int, torch.Tensor] = {}
         n_total = cfg.num_hidden_layers + extra_swa_layers
+        # Speculative verification writes up to `spec_tokens` raw compressor rows past the accepted
+        # prefix; the rings are widened so that those writes never land on a row that a window
+        # closing after the rollback still needs.
+        ring4 = 8 if spec_tokens == 0 else 32
+        ring128 = 128 if spec_tokens == 0 else 160
         for li in list(self.layers) + list(range(cfg.num_hidden_layers, n_total)):
             self.swa_cache[li] = PagedCache.allocate(swa_pages, D, Rd, fp8, "latent", self.device)
             kind = cfg.layer_kind(li) if li < cfg.num_hidden_layers else "swa"
@@ -152,12 +157,12 @@ class KVManager:
                 self.comp_cache[li] = PagedCache.allocate(self.c4.num_pages, D, Rd, fp8, "latent", self.device)
                 self.idx_cache[li] = PagedCache.allocate(self.c4.num_pages, cfg.index_head_dim, Rd, fp8, "indexer",
                                                          self.device)
-                self.comp_state[li] = torch.zeros(max_requests, 8, 2 * 2 * D, dtype=torch.float32, device=self.device)
-                self.idx_state[li] = torch.zeros(max_requests, 8, 2 * 2 * cfg.index_head_dim, dtype=torch.float32,
+                self.comp_state[li] = torch.zeros(max_requests, ring4, 2 * 2 * D, dtype=torch.float32, device=self.device)
+                self.idx_state[li] = torch.zeros(max_requests, ring4, 2 * 2 * cfg.index_head_dim, dtype=torch.float32,
                                                  device=self.device)
             elif kind == "c128a":
                 self.comp_cache[li] = PagedCache.allocate(self.c128.num_pages, D, Rd, fp8, "latent", self.device)
-                self.comp_state[li] = torch.zeros(max_requests, 128, 2 * D, dtype=torch.float32, device=self.device)
+                self.comp_state[li] = torch.zeros(max_requests, ring128, 2 * D, dtype=torch.float32, device=self.device)
         self.free_rows = list(range(max_requests - 1, -1, -1))
 
     # ---- request rows -------------------------------------------------------
