@@ -124,7 +124,9 @@ def build_layer(cfg: ModelConfig, src: WeightSource, prefix: str, li: int, devic
     nh_l = nh // tp_size
     h0 = tp_rank * nh_l
     a = f"{prefix}.attn"
-    mk = lambda w: LinearWeight.from_master(w, dd, device)
+    # a checkpoint with power-of-two block scales is re-quantised with the same rule, which reproduces its codes
+    ue8m0 = getattr(src, "fp8_scale_rule", "absmax") == "ue8m0"
+    mk = lambda w: LinearWeight.from_master(w, dd, device, ue8m0)
     mkbf = lambda w: LinearWeight(w.to(device=device, dtype=BF16).contiguous())
     g = lambda n, s: _get(src, n, s, device)
 

@@ -56,9 +56,9 @@ class LinearWeight:
         return self.w.shape[1]
 
     @staticmethod
-    def from_master(w: torch.Tensor, dense_dtype: str, device) -> "LinearWeight":
+    def from_master(w: torch.Tensor, dense_dtype: str, device, ue8m0: bool = False) -> "LinearWeight":
         if dense_dtype == "fp8":
-            q, s = R.quant_fp8_block128_weight(w.to(device=device, dtype=F32))
+            q, s = R.quant_fp8_block128_weight(w.to(device=device, dtype=F32), ue8m0=ue8m0)
             return LinearWeight(q.contiguous(), s.contiguous())
         return LinearWeight(w.to(device=device, dtype=BF16).contiguous())
 

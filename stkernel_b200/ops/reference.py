@@ -60,8 +60,9 @@ def ue8m0_scale_from_amax(amax: torch.Tensor, floor: float = 1e-4) -> Tuple[torc
     return torch.exp2(exponent), byte
 
 
-def quant_fp8_block128_weight(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Weight [N, K] -> e4m3 [N, K] + fp32 scales [ceil(N/128), ceil(K/128)] (dequant = q*scale)."""
+def quant_fp8_block128_weight(w: torch.Tensor, ue8m0: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Weight [N, K] -> e4m3 [N, K] + fp32 scales [ceil(N/128), ceil(K/128)] (dequant = q*scale).
+    ue8m0: scales rounded up to a power of two (the checkpoint's exponent-byte scale format)."""
     n, k = w.shape
     nb, kb = -(-n // FP8_BLOCK), -(-k // FP8_BLOCK)
     wp = torch.zeros(nb * FP8_BLOCK, kb * FP8_BLOCK, dtype=F32, device=w.device)
@@ -69,6 +70,8 @@ def quant_fp8_block128_weight(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tens
     blocks = wp.view(nb, FP8_BLOCK, kb, FP8_BLOCK)
     amax = blocks.abs().amax(dim=(1, 3)).clamp(min=1e-12)
     scale = amax / FP8_MAX
+    if ue8m0:
+        scale = torch.exp2(torch.ceil(torch.log2(scale)))
     q = to_fp8_e4m3(blocks / scale[:, None, :, None]).view(nb * FP8_BLOCK, kb * FP8_BLOCK)
     return q[:n, :k].contiguous(), scale.contiguous()
 
