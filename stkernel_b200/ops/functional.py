@@ -22,7 +22,10 @@ BF16 = torch.bfloat16
 F32 = torch.float32
 FP8 = torch.float8_e4m3fn
 
-_CPU_ACT = [torch.bfloat16]
+import os as _os
+
+# STK_CPU_ACT_FP32=1: fp32 activations on the CPU path (exact comparisons across TP degrees)
+_CPU_ACT = [torch.float32 if _os.environ.get("STK_CPU_ACT_FP32") == "1" else torch.bfloat16]
 
 
 def set_cpu_act_dtype(dtype: torch.dtype) -> None:

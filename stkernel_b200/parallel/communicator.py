@@ -55,9 +55,9 @@ class Communicator:
         """[T, n] per rank -> [T, n * world] (rank-major along the last dim)."""
         if self.world_size == 1:
             return x
-        parts = torch.empty(self.world_size, *x.shape, dtype=x.dtype, device=x.device)
+        parts = torch.empty(self.world_size * x.shape[0], x.shape[1], dtype=x.dtype, device=x.device)
         dist.all_gather_into_tensor(parts, x.contiguous(), group=self.group)
-        return parts.permute(1, 0, 2).reshape(x.shape[0], -1)
+        return parts.view(self.world_size, x.shape[0], x.shape[1]).permute(1, 0, 2).reshape(x.shape[0], -1)
 
     def all_gather_dim0(self, x: torch.Tensor) -> torch.Tensor:
         if self.world_size == 1:

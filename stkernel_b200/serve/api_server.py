@@ -78,11 +78,13 @@ class AsyncEngine:
                 try:
                     rid = self.engine.add_request(prompt, params)
                     self._streams[rid] = (loop, q)
+                    self._on_add(rid, prompt, params)
                     loop.call_soon_threadsafe(fut.set_result, rid)
                 except Exception as e:                       # rejected request (too long, ...)
                     loop.call_soon_threadsafe(fut.set_exception, e)
             elif kind == "abort":
                 if self.engine.abort(payload):
+                    self._on_abort(payload)
                     self._post(payload, TokenEvent([], True, "abort"))
                 self._streams.pop(payload, None)
                 self.engine.release(payload)
@@ -93,6 +95,12 @@ class AsyncEngine:
                     loop.call_soon_threadsafe(fut.set_result, res)
                 except Exception as e:
                     loop.call_soon_threadsafe(fut.set_exception, e)
+
+    def _on_add(self, rid: int, prompt: List[int], params: SamplingParams) -> None:
+        """Hook: a request entered the engine (multi-rank leaders mirror it to the followers)."""
+
+    def _on_abort(self, rid: int) -> None:
+        """Hook: a live request was aborted."""
 
     def _run(self) -> None:
         eng = self.engine
@@ -253,11 +261,12 @@ def _usage(n_prompt: int, n_out: int) -> Dict[str, int]:
 
 
 def sampling_from_request(body: Dict[str, Any], eos_id: Optional[int], max_model_len: int, n_prompt: int,
-                          default_max: int = 512) -> SamplingParams:
+                          default_max: int = 512, default_temperature: float = 1.0) -> SamplingParams:
     max_tokens = body.get("max_completion_tokens") or body.get("max_tokens") or default_max
     max_tokens = max(1, min(int(max_tokens), max_model_len - n_prompt))
     seed = body.get("seed")
-    return SamplingParams(temperature=float(body.get("temperature", 1.0) or 0.0),
+    temp = body.get("temperature")
+    return SamplingParams(temperature=float(default_temperature if temp is None else temp),
                           seed=int(seed) if seed is not None else uuid.uuid4().int & 0x7FFFFFFF,
                           max_tokens=max_tokens, min_tokens=int(body.get("min_tokens", 0) or 0),
                           ignore_eos=bool(body.get("ignore_eos", False)), eos_token_id=eos_id)
@@ -313,9 +322,10 @@ def anthropic_to_chat(body: Dict[str, Any]) -> Tuple[List[Dict[str, Any]], Optio
 # ---------------------------------------------------------------------------------------
 def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deepseek-v4-flash",
                default_thinking: bool = False, profile_dir: str = "/tmp/stk_profiles",
-               default_chat_template_kwargs: Optional[Dict[str, Any]] = None):
+               default_chat_template_kwargs: Optional[Dict[str, Any]] = None, async_engine: Optional[AsyncEngine] = None,
+               default_temperature: float = 1.0):
     app = FastAPI(title="stkernel_b200")
-    aeng = AsyncEngine(engine)
+    aeng = async_engine if async_engine is not None else AsyncEngine(engine)
     app.state.async_engine = aeng
     max_len = engine.cfg.sched.max_model_len
     eos_id = tokenizer.eos_token_id
@@ -377,7 +387,7 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
             return err(400, f"{type(e).__name__}: {e}")
         if len(ids) >= max_len:
             return err(400, f"prompt has {len(ids)} tokens; the model's context is {max_len}")
-        params = sampling_from_request(body, eos_id, max_len, len(ids))
+        params = sampling_from_request(body, eos_id, max_len, len(ids), default_temperature=default_temperature)
         stop = body.get("stop") or []
         stop = [stop] if isinstance(stop, str) else list(stop)
         rid = f"chatcmpl-{uuid.uuid4().hex}"
@@ -452,7 +462,7 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
             return err(400, f"{type(e).__name__}: {e}")
         if len(ids) >= max_len:
             return err(400, f"prompt has {len(ids)} tokens; the model's context is {max_len}")
-        params = sampling_from_request(body, eos_id, max_len, len(ids))
+        params = sampling_from_request(body, eos_id, max_len, len(ids), default_temperature=default_temperature)
         rid = f"cmpl-{uuid.uuid4().hex}"
         pipe = OutputPipeline(tokenizer, False, None, [body["stop"]] if isinstance(body.get("stop"), str) else (body.get("stop") or []))
         base = {"id": rid, "object": "text_completion", "created": int(time.time()), "model": model_name}
@@ -503,7 +513,7 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
             return err(400, f"{type(e).__name__}: {e}")
         if len(ids) >= max_len:
             return err(400, f"prompt has {len(ids)} tokens; the model's context is {max_len}")
-        params = sampling_from_request(body, eos_id, max_len, len(ids))
+        params = sampling_from_request(body, eos_id, max_len, len(ids), default_temperature=default_temperature)
         pipe = OutputPipeline(tokenizer, thinking, tools, body.get("stop_sequences") or [])
         mid = f"msg_{uuid.uuid4().hex[:24]}"
 

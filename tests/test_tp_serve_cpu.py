@@ -1,0 +1,118 @@
+"""Multi-rank serving on CPU (gloo): lockstep leader/followers behind the HTTP server, and the follower's
+exit when the leader disappears between steps (host-side failure, no device involved)."""
+import json
+import os
+import signal
+import socket
+import subprocess
+import sys
+import time
+import urllib.request
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _post(port, path, body, timeout=120):
+    req = urllib.request.Request(f"http://127.0.0.1:{port}{path}", data=json.dumps(body).encode(),
+                                 headers={"Content-Type": "application/json"})
+    with urllib.request.urlopen(req, timeout=timeout) as r:
+        return json.loads(r.read())
+
+
+def _wait_up(port, proc, timeout=180):
+    t0 = time.time()
+    while time.time() - t0 < timeout:
+        if proc.poll() is not None:
+            raise RuntimeError(f"server exited early with {proc.returncode}")
+        try:
+            urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=2).read()
+            return
+        except OSError:
+            time.sleep(0.5)
+    raise TimeoutError("server did not come up")
+
+
+def _launch(world, port, extra=()):
+    env = dict(os.environ, PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2", STK_CPU_ACT_FP32="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), "-m", "stkernel_b200.serve.tp_worker", "--tiny", "--port", str(port),
+           "--tensor-parallel-size", str(world), "--max-model-len", "512", "--max-num-seqs", "4",
+           "--max-num-batched-tokens", "128", "--graph-cap", "0", "--heartbeat-timeout", "20", *extra]
+    return subprocess.Popen(cmd, env=env, cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, start_new_session=True)
+
+
+def _stop(proc):
+    if proc.poll() is None:
+        os.killpg(proc.pid, signal.SIGTERM)          # exactly the process group this test started
+        try:
+            proc.wait(timeout=30)
+        except subprocess.TimeoutExpired:
+            os.killpg(proc.pid, signal.SIGKILL)
+
+
+@pytest.mark.timeout(600)
+def test_tp2_lockstep_serving_matches_tp1():
+    body = {"prompt": "lockstep", "max_tokens": 8, "temperature": 0, "ignore_eos": True}
+    outs = {}
+    for world in (1, 2):
+        port = _free_port()
+        proc = _launch(world, port)
+        try:
+            _wait_up(port, proc)
+            r1 = _post(port, "/v1/completions", body)
+            r2 = _post(port, "/v1/completions", body)
+            assert r1["usage"]["completion_tokens"] == 8
+            assert r1["choices"][0]["text"] == r2["choices"][0]["text"]           # followers stayed in step
+            chat = _post(port, "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4,
+                                                        "temperature": 0.7, "seed": 3, "ignore_eos": True})
+            assert chat["usage"]["completion_tokens"] == 4
+            outs[world] = r1["choices"][0]["text"]
+        finally:
+            _stop(proc)
+    # the same weights split over two ranks give the same greedy text (fp32 activations on CPU)
+    assert outs[1] == outs[2]
+
+
+def _follower_main(rank, port, result_path):
+    import datetime
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE="2")
+    dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=10))
+    if rank == 0:
+        # a leader that sends one heartbeat and then dies between steps, without the STOP event
+        dist.broadcast_object_list([[]], src=0)
+        os._exit(0)
+    from stkernel_b200.serve.tp_worker import follower_loop
+
+    class Idle:
+        def has_work(self): return False
+    t0 = time.time()
+    rc = follower_loop(Idle(), dist.group.WORLD, 10.0)
+    open(result_path, "w").write(json.dumps({"rc": rc, "dt": time.time() - t0}))
+    os._exit(0)
+
+
+@pytest.mark.timeout(120)
+def test_follower_exits_when_leader_dies(tmp_path):
+    import torch.multiprocessing as mp
+    port = _free_port()
+    res = str(tmp_path / "res.json")
+    ctx = mp.get_context("spawn")
+    ps = [ctx.Process(target=_follower_main, args=(r, port, res)) for r in range(2)]
+    for p in ps:
+        p.start()
+    for p in ps:
+        p.join(90)
+        assert not p.is_alive()
+    out = json.load(open(res))
+    assert out["rc"] == 3 and out["dt"] < 60
