@@ -1,0 +1,249 @@
+"""Pure-logic tests: chunker budgets, SP coverage, DCP index math, trace/bench tooling, n-gram ceiling,
+Markov refit."""
+import json
+import random
+
+import pytest
+import torch
+
+from stkernel_b200.bench import check_quality, ngram_ceiling, streamgap, trace_tools
+from stkernel_b200.bench.http_client import acceptance, spec_counters, summarize, unique_prompt
+from stkernel_b200.bench.kernel_table import bucket_of, interval_union
+from stkernel_b200.config import tiny_config
+from stkernel_b200.models.dsv4_oracle import index_cache_computes
+from stkernel_b200.runtime import planning as P
+from stkernel_b200.runtime.metrics import Metrics, parse_prometheus
+from stkernel_b200.tools import markov_refit
+
+
+# ---- prefill chunker ---------------------------------------------------------------------------
+def _validate(seq_lens, query_lens, ws, logits_bytes, offset=0):
+    chunks = P.split_indexer_prefill_chunks(list(seq_lens), list(query_lens), ws, logits_bytes, request_offset=offset)
+    max_elems = logits_bytes // 4
+    covered = {i: 0 for i in range(len(seq_lens))}
+    for req_slice, q_slice in chunks:
+        reqs = list(range(req_slice.start - offset, req_slice.stop - offset))
+        n = sum(seq_lens[r] for r in reqs)
+        m = q_slice.stop - q_slice.start
+        assert m >= 1
+        if len(reqs) > 1:
+            assert n <= ws and sum(query_lens[r] for r in reqs) * n <= max_elems
+        elif n <= ws and query_lens[reqs[0]] * n > max_elems:
+            assert m * n <= max_elems or m == 1
+        for r in reqs:
+            covered[r] += m if len(reqs) == 1 else query_lens[r]
+    assert all(covered[r] == q for r, q in enumerate(query_lens))
+    return chunks
+
+
+def test_prefill_chunker_budgets():
+    _validate([100, 200, 300], [10, 20, 30], 10_000, 4 * 10 ** 9)
+    assert len(_validate([500, 500, 500], [50, 50, 50], 600, 4 * 10 ** 9)) == 3          # tight workspace: one each
+    assert len(_validate([100_000], [4_096], 200_000, 4 * 10_000_000)) > 1                # query sub-chunking
+    ch = P.split_indexer_prefill_chunks([10], [5], 100, 4 * 10 ** 9, request_offset=7)
+    assert (ch[0][0].start, ch[0][0].stop) == (7, 8)
+    rng = random.Random(0)
+    for _ in range(200):
+        n = rng.randint(1, 8)
+        seq = [rng.randint(1, 5000) for _ in range(n)]
+        q = [rng.randint(1, s) for s in seq]
+        _validate(seq, q, rng.randint(100, 20000), 4 * rng.randint(1000, 10 ** 7), rng.randint(0, 5))
+
+
+# ---- sequence-parallel indexer ranges --------------------------------------------------------------
+def test_indexer_sp_coverage():
+    tp, ndt = 4, 12
+    chunks = [(12, 140), (140, 4236), (4236, 4801)]
+    per_rank = [P.indexer_sp_ranges(ndt, chunks, tp, r) for r in range(tp)]
+    for rr in per_rank:
+        rows = set()
+        for a, b in rr:
+            assert b > a
+            rows.update(range(a, b))
+        assert set(range(0, ndt)) <= rows and set(range(12, 140)) <= rows            # replicated parts
+    assert per_rank[0] == [(0, 1164), (4236, 4378)]                                  # adjacent spans merged
+    assert len(per_rank[1]) == 3
+    for a, b in chunks[1:]:
+        n = b - a
+        owned = [{x for lo, hi in rr for x in range(lo, hi) if a <= x < b} for rr in per_rank]
+        assert set().union(*owned) == set(range(a, b)) and sum(len(s) for s in owned) == n
+        assert all(len(s) <= -(-n // tp) for s in owned)
+        assert P.sp_gather_sizes((a, b), tp) == [len(s) for s in owned]
+    assert P.indexer_sp_ranges(8, None, tp, 0) is None and P.indexer_sp_ranges(8, [], tp, 0) is None
+    assert P.indexer_sp_ranges(0, [(0, 4096)], 1, 0) is None
+    assert P.merge_ranges([(5, 9), (0, 3), (3, 5), (20, 20)]) == [(0, 9)]
+
+
+# ---- DCP / PP / helpers ---------------------------------------------------------------------------
+def test_dcp_index_math_and_topk_merge():
+    for dcp, il in ((2, 1), (4, 1), (4, 64), (8, 16)):
+        n = 1000
+        counts = [0] * dcp
+        for row in range(n):
+            r = P.dcp_owner(row, dcp, il)
+            assert P.dcp_local_index(row, dcp, il) == counts[r]                      # local rows are dense and in order
+            assert P.dcp_global_row(counts[r], dcp, r, il) == row
+            counts[r] += 1
+        assert [P.dcp_local_rows(n, dcp, r, il) for r in range(dcp)] == counts
+    rng = random.Random(1)
+    scores = [rng.random() for _ in range(500)]
+    per_rank = []
+    for r in range(4):
+        mine = [(scores[i], i) for i in range(500) if P.dcp_owner(i, 4) == r]
+        per_rank.append(sorted(mine, key=lambda c: -c[0])[:32])
+    want = [i for _, i in sorted(((scores[i], i) for i in range(500)), key=lambda c: (-c[0], c[1]))[:32]]
+    assert P.merge_topk_candidates(per_rank, 32) == want
+
+
+def test_pp_ranges_tiles_and_layer_kinds():
+    for n, pp in ((48, 4), (43, 4), (6, 8)):
+        spans = [P.pp_layer_range(n, pp, r) for r in range(pp)]
+        assert spans[0][0] == 0 and spans[-1][1] == n and all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+        assert max(b - a for a, b in spans) - min(b - a for a, b in spans) <= 1
+    assert P.round_up_tile(1, 128) == 128 and P.round_up_tile(128, 128) == 128 and P.round_up_tile(129, 128) == 256
+    assert P.layer_kinds((4, 0, 128, 1), 5) == ["c4a", "swa", "c128a", "swa", "swa"]
+    ratios = (4, 0, 4, 4, 0, 4, 4, 4)
+    pat = P.index_cache_pattern(ratios, 8, 3)
+    assert pat == [True, None, False, False, None, True, False, False]
+    cfg = tiny_config(num_hidden_layers=8, compress_ratios=ratios, index_topk_freq=3)
+    assert [p if p is not None else False for p in pat] == [index_cache_computes(cfg, i) for i in range(8)]
+    for freq in (1, 2, 7, 100):
+        assert P.index_cache_pattern((0, 4, 4), 3, freq)[1] is True                   # first C4A always computes
+
+
+# ---- profiling tools ---------------------------------------------------------------------------
+def _trace():
+    ev = []
+    t = 0.0
+    for i in range(10):
+        ev.append({"cat": "kernel", "name": "stk::gemm_kernel<64>", "ts": t, "dur": 10.0, "args": {"stream": 7}})
+        t += 10.0 + (30.0 if i == 4 else 2.0)
+        ev.append({"cat": "kernel", "name": "stk::sparse_mla_tc_kernel<64>", "ts": t, "dur": 5.0, "args": {"stream": 7}})
+        t += 5.0 + 1.0
+    ev.append({"cat": "kernel", "name": "ncclDevKernel_AllReduce", "ts": 80.0, "dur": 25.0, "args": {"stream": 9}})
+    ev.append({"cat": "cpu_op", "name": "aten::mm", "ts": 0.0, "dur": 999.0})
+    return {"traceEvents": ev}
+
+
+def test_bucket_regex_and_interval_union():
+    assert bucket_of("ncclDevKernel_AllReduce_Sum") == "comms" and bucket_of("stk::oneshot_allreduce_kernel") == "comms"
+    assert bucket_of("stk::expert_fc1_kernel<4>") == "moe" and bucket_of("stk::sparse_mla_tc_kernel<64>") == "attn/indexer"
+    assert bucket_of("stk::gemm_kernel<64, true>") == "gemm" and bucket_of("stk::mhc_cluster_kernel<24>") == "mhc"
+    assert bucket_of("stk::rmsnorm_kernel") == "norm/rope/quant" and bucket_of("Memcpy HtoD") == "memops"
+    assert bucket_of("something_else") == "other"
+    assert interval_union([(0, 10), (5, 15), (20, 30)]) == 25 and interval_union([]) == 0
+    assert interval_union([(0, 10), (2, 3), (10, 12)]) == 12
+
+
+def test_trace_tools_reports():
+    evs = trace_tools.gpu_events(_trace())
+    assert len(evs) == 21
+    tab = trace_tools.bucket_table(evs)
+    assert tab["buckets"]["gemm"] == 100.0 and tab["buckets"]["attn/indexer"] == 50.0 and tab["buckets"]["comms"] == 25.0
+    assert tab["busy_us"] == 173.0                             # the collective overlaps a kernel: not counted twice
+    assert abs(tab["busy_us"] + tab["idle_us"] - tab["span_us"]) < 1e-6
+    g = trace_tools.gap_report(evs)
+    assert g["stream"] == 7 and g["n_kernels"] == 20
+    assert g["largest"][0][0] == 30.0 and "gemm" in g["largest"][0][1] and "sparse_mla" in g["largest"][0][2]
+    assert sum(g["hist"]) == 19
+    st = g["kernel_stats"]["stk::gemm_kernel<64>"]
+    assert st["n"] == 10 and st["min"] == st["max"] == 10.0
+    c = trace_tools.concurrent_report(evs)
+    assert c[0]["gap_us"] == 30.0 and c[0]["other"][0][0].startswith("nccl") and c[0]["covered_us"] == 23.0
+    assert "bucket gemm" in trace_tools.format_table(tab, steps=10)
+    assert trace_tools.percentile([1, 2, 3, 4, 100], 0.5) == 3
+
+
+def test_nccl_fingerprint_ignores_volatile_fields():
+    a = ("host1:123:456 [0] NCCL INFO Channel 00/24 : 0 1 2 3\nhost1:123:456 [0] NCCL INFO Trees [0] 1/-1/-1->0->-1\n"
+         "host1:123:456 [0] NCCL INFO comm 0x55aa rank 0 nranks 4 cudaDev 0 - Init COMPLETE\nhost1:1:2 [0] NCCL INFO Using network Socket\n")
+    b = a.replace("host1:123:456", "host9:9:9").replace("0x55aa", "0x7f00")
+    fa, na = trace_tools.nccl_fingerprint(a)
+    assert na == 3 and (fa, na) == trace_tools.nccl_fingerprint(b)
+    assert trace_tools.nccl_fingerprint(a.replace("0 1 2 3", "0 2 1 3"))[0] != fa
+
+
+def test_prometheus_and_acceptance_formulas():
+    m = Metrics()
+    m.record_spec(5, 3); m.record_spec(5, 0); m.record_spec(5, 5)
+    after = spec_counters(parse_prometheus(m.render("x")))
+    assert after["vllm:spec_decode_num_drafts_total"] == 3 and after["vllm:spec_decode_num_draft_tokens_total"] == 15
+    assert after["vllm:spec_decode_num_accepted_tokens_total"] == 8
+    assert after["vllm:spec_decode_num_accepted_tokens_per_pos_total"] == 8            # labels collapsed: 2+2+2+1+1
+    acc = acceptance({}, after)
+    assert abs(acc["raw"] - 8 / 15) < 1e-9 and abs(acc["accepted_per_step"] - 8 / 3) < 1e-9
+    assert abs(acc["acc"] - (8 + 8) / (3 + 15)) < 1e-9                               # the legacy substring convention
+    assert acceptance({}, {}) == {"acc": 0.0, "raw": 0.0, "accepted_per_step": 0.0}
+    assert summarize([3, 1, 2]) == {"mean": 2.0, "median": 2, "min": 1, "max": 3}
+    assert unique_prompt(1, 5) == unique_prompt(1, 5) != unique_prompt(2, 5)
+
+
+def test_quality_document_and_grading():
+    doc = check_quality.build_document(2000, 3)
+    pos = [doc.index(s) / len(doc) for s, _, _ in check_quality.FACTS]
+    assert all(abs(p - d) < 0.05 for p, d in zip(pos, (0.25, 0.5, 0.75)))
+    assert check_quality.grade("It was Dr. Halvorsen, on 14 March 1997.", ("halvorsen", "14 march 1997"))
+    assert not check_quality.grade("Halvorsen in 1998", ("halvorsen", "14 march 1997"))
+    st = [0.0, 0.1, 0.2, 0.3, 5.0, 5.1, 9.0, 9.1, 9.2]
+    r = streamgap.window_rates(st, 0.0, 0.35, 8.0)
+    assert r["before"] > r["during"] and r["after"] > r["during"]
+    assert streamgap.largest_gaps(st, 0.0, 2)[0][0] == pytest.approx(4.7)
+
+
+# ---- n-gram ceiling ---------------------------------------------------------------------------
+def test_ngram_ceiling_pmf_index_and_no_future_leak():
+    pmf = ngram_ceiling.accept_len_pmf(ngram_ceiling.parse_curve("78.5,56.4,39.6,28.6,21.5"))
+    assert abs(sum(pmf) - 1) < 1e-9 and abs(pmf[0] - 0.215) < 1e-9 and abs(pmf[5] - 0.215) < 1e-9
+    with pytest.raises(ValueError):
+        ngram_ceiling.parse_curve("50,60")
+    with pytest.raises(ValueError):
+        ngram_ceiling.parse_curve("150")
+    toks = [1, 2, 3, 4, 5, 9, 1, 2, 3, 4, 5, 7]
+    idx = ngram_ceiling.GramIndex(toks, 3)
+    idx.advance(9)                                          # suffix ending at 9 is (1,2,3) again
+    assert idx.longest(9, 16) == (3, 3)
+    idx2 = ngram_ceiling.GramIndex(toks, 3)
+    idx2.advance(3)
+    assert idx2.longest(3, 16) == (0, -1)                  # the only other (1,2,3) ends at 9, in the future of t=3
+    rep = list(range(50)) * 6
+    st = ngram_ceiling.simulate(rep[:60], rep[60:], pmf, threshold=4)
+    assert st["steps"]["hybrid"] < st["steps"]["drafter"] and st["steps"]["oracle"] <= st["steps"]["hybrid"]
+    assert st["copy_accepted"] / st["copy_steps"] > 4.0
+    r3 = random.Random(3)
+    rnd = [r3.randrange(10 ** 6) for _ in range(400)]
+    st2 = ngram_ceiling.simulate(rnd[:100], rnd[100:], pmf)
+    assert st2["copy_steps"] == 0 and st2["steps"]["hybrid"] == st2["steps"]["drafter"]
+    assert ngram_ceiling.simulate([1], [2], pmf) is None
+
+
+# ---- Markov refit ---------------------------------------------------------------------------
+def test_markov_refit_recovers_bigram_structure(tmp_path):
+    V = 64
+    rng = random.Random(0)
+    nxt = {i: (i * 7 + 3) % V for i in range(V)}              # a deterministic successor for every token
+    docs = []
+    for _ in range(200):
+        t = rng.randrange(V)
+        seq = [t]
+        for _ in range(30):
+            t = nxt[t] if rng.random() < 0.8 else rng.randrange(V)
+            seq.append(t)
+        docs.append(seq)
+    pairs, uni, total = markov_refit.count_bigrams(docs)
+    out = markov_refit.refit(pairs, uni, total, V, rank=48)
+    bias = out["markov_w1"] @ out["markov_w2"].T
+    hit = sum(int(bias[i].argmax()) == nxt[i] for i in range(V))
+    assert hit >= 0.9 * V and out["meta"]["blend"] == 1.0 and out["meta"]["energy"] > 0.5
+    # blending with a shipped head moves the result between the two
+    base = (torch.randn(V, 8) * 0.1, torch.randn(V, 8) * 0.1)
+    keep = markov_refit.refit(pairs, uni, total, V, rank=8, blend=0.0, base=base)
+    assert torch.allclose(keep["markov_w1"] @ keep["markov_w2"].T, base[0] @ base[1].T, atol=1e-3)
+    with pytest.raises(ValueError):
+        markov_refit.refit(pairs, uni, total, V, rank=8, blend=1.5)
+    with pytest.raises(ValueError):
+        markov_refit.pmi_operator(pairs, uni, total, V, min_count=10 ** 6)
+    # the payload passes the serving loader's sideload contract
+    from stkernel_b200.spec.dspark import MarkovHead
+    p = tmp_path / "m.pt"
+    torch.save({"markov_w1": out["markov_w1"], "markov_w2": out["markov_w2"], "meta": out["meta"]}, p)
+    MarkovHead(torch.zeros(V, 48).bfloat16(), torch.zeros(V, 48).bfloat16()).sideload(str(p), V, 48)
