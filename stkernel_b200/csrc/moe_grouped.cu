@@ -37,6 +37,10 @@ struct MoeGArgs {
   void* out;               // FC1: fp16 [P, I]; FC2: bf16 [P, H]
   float limit;
   int* status;
+  // Expert-parallel mode: rows of expert e are pushed into the activation matrix by peers (and by this
+  // GPU's own dispatch); `arrived[e]` counts the rows that have landed.  nullptr = rows are already there.
+  const uint32_t* arrived;
+  uint32_t spin_budget;
 };
 
 template <int BT, bool kFc1>
@@ -140,6 +144,18 @@ moe_grouped_kernel(const __grid_constant__ CUtensorMap tmX, const MoeGArgs a) {
       for (int v = blockIdx.x; v < pairs && ok; v += gridDim.x) {
         const int e = v / tiles_n;
         const int r0 = a.offsets[e], cnt = a.offsets[e + 1] - r0;
+        if (a.arrived != nullptr && cnt > 0) {
+          // rows of this expert come over NVLink: start as soon as they are all here (bounded wait)
+          bool here = false;
+          for (uint32_t i = 0; i < a.spin_budget; ++i) {
+            uint32_t got;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(got) : "l"(a.arrived + e) : "memory");
+            if (got >= static_cast<uint32_t>(cnt)) { here = true; break; }
+            if (i > 64) __nanosleep(64);
+          }
+          if (!here) { set_status(a.status, kTimeoutPeerFlag, 760); ok = false; break; }
+          asm volatile("fence.proxy.async.global;" ::: "memory");      // peer stores (generic proxy) -> TMA reads
+        }
         for (int tt = 0; tt * BT < cnt && ok; ++tt) {
           for (int kb = 0; kb < k_blocks; ++kb) {
             if (!mbar_wait(&bars->empty[stage], phase ^ 1, a.status, 700 + stage)) { ok = false; break; }
@@ -363,9 +379,9 @@ STK_API int stk_moe_permute(const void* x, long long ldx, const int* sorted, con
 
 // xs: fp16 [xs_rows, K] sorted activations (xs_rows >= total rows + bt, tail readable).
 // fc1 = 1: w rows = 2*n_out (gate rows then up rows), out fp16 [P, n_out] = swiglu;  fc1 = 0: w rows = n_out, out bf16.
-STK_API int stk_moe_grouped(const void* xs, long long xs_rows, const void* w, const void* s, const float* gscale,
-                            const int* offsets, int e_local, int n_out, int K, void* out, int fc1, float limit, int bt,
-                            int* status, int sm_count, void* stream) {
+static int moe_grouped_launch(const void* xs, long long xs_rows, const void* w, const void* s, const float* gscale,
+                              const int* offsets, int e_local, int n_out, int K, void* out, int fc1, float limit, int bt,
+                              int* status, int sm_count, const uint32_t* arrived, uint32_t spin_budget, void* stream) {
   if (e_local <= 0) return 0;
   if (K % 64 || n_out % 128 || (bt != 16 && bt != 32 && bt != 64 && bt != 128)) return -1;
   CUtensorMap tx;
@@ -373,6 +389,7 @@ STK_API int stk_moe_grouped(const void* xs, long long xs_rows, const void* w, co
   MoeGArgs a;
   a.w = (const uint8_t*)w; a.s = (const uint8_t*)s; a.gscale = gscale; a.offsets = offsets; a.e_local = e_local;
   a.rows = fc1 ? 2 * n_out : n_out; a.n_out = n_out; a.K = K; a.out = out; a.limit = limit; a.status = status;
+  a.arrived = arrived; a.spin_budget = spin_budget;
   const int pairs = e_local * (n_out / 128);
   const int grid = pairs < sm_count ? pairs : sm_count;
   cudaStream_t st = (cudaStream_t)stream;
@@ -384,4 +401,20 @@ STK_API int stk_moe_grouped(const void* xs, long long xs_rows, const void* w, co
     default: return STK_MG(128);
   }
 #undef STK_MG
+}
+
+STK_API int stk_moe_grouped(const void* xs, long long xs_rows, const void* w, const void* s, const float* gscale,
+                            const int* offsets, int e_local, int n_out, int K, void* out, int fc1, float limit, int bt,
+                            int* status, int sm_count, void* stream) {
+  return moe_grouped_launch(xs, xs_rows, w, s, gscale, offsets, e_local, n_out, K, out, fc1, limit, bt, status, sm_count,
+                            nullptr, 0u, stream);
+}
+
+// Expert-parallel FC1: the activation rows of local expert e are complete once arrived[e] reaches the expert's row
+// count; the producer warp waits for that per expert, so tiles of early experts run while later rows are in flight.
+STK_API int stk_moe_grouped_ep(const void* xs, long long xs_rows, const void* w, const void* s, const float* gscale,
+                               const int* offsets, int e_local, int n_out, int K, void* out, int fc1, float limit, int bt,
+                               int* status, int sm_count, const void* arrived, int spin_budget, void* stream) {
+  return moe_grouped_launch(xs, xs_rows, w, s, gscale, offsets, e_local, n_out, K, out, fc1, limit, bt, status, sm_count,
+                            (const uint32_t*)arrived, static_cast<uint32_t>(spin_budget), stream);
 }

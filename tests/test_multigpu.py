@@ -22,3 +22,15 @@ def _torchrun(script, nproc, port, timeout=300, extra_env=None):
 def test_symmetric_allreduce_and_fused_gemm():
     r = _torchrun(os.path.join(ROOT, "tests", "multigpu", "symm_check.py"), 2, 29531)
     assert "SYMM_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_moe_over_peer_memory():
+    """Route/dispatch/grouped GEMM/return/combine against the fp32 reference (32 experts so that every rank
+    can hold all dequantised weights), two calls in a row with different routing."""
+    env = dict(os.environ)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29532", os.path.join(ROOT, "tests", "multigpu", "ep_check.py"), "--experts", "32",
+           "--tokens", "1,16", "--check-tokens", "48"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
+    assert "EP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
