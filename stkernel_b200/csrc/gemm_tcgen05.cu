@@ -48,9 +48,15 @@ struct GemmArgs {
   // all other CTAs.
   int ar_enabled;
   SymmCtx ar;
+  // Arrival-gated activations (all-gather -> GEMM): X is the gathered matrix in this rank's symmetric region,
+  // rows [s * gate_rows, (s+1) * gate_rows) are pushed by rank s and are complete once flag (kAgKind, 0, s)
+  // carries the current epoch.  Token tiles are visited starting with this rank's own shard.
+  int gate_enabled;
+  int gate_rows;
 };
 
 constexpr int kArKind = 3;
+constexpr int kGateKind = 4;      // flags written by the all-gather push kernel (symm.cu)
 
 template <int BT>
 struct GemmCfg {
@@ -136,6 +142,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
   uint32_t ar_epoch = 0;
   if (a.ar_enabled) ar_epoch = *epoch_ptr(a.ar, kArKind, 0) + 1;   // bumped only after every CTA has finished
 
+  uint32_t gate_epoch = 0;
+  int tt_rot = 0;
+  if (a.gate_enabled) {
+    gate_epoch = *epoch_ptr(a.ar, kGateKind, 0);                   // the push of this call has already run on this rank
+    tt_rot = (a.ar.rank * a.gate_rows) / BT;
+  }
   const int units = a.splits * a.tiles_t * a.tiles_n;
   const int kb_per_split = (a.k_blocks + a.splits - 1) / a.splits;
   constexpr uint32_t kIdesc = umma_idesc(kFp8 ? 0u : 1u, kFp8 ? 0u : 1u, 128, BT);
@@ -150,10 +162,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
       int issued = 0;
       for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
         const int tn = u % a.tiles_n;
-        const int tt = (u / a.tiles_n) % a.tiles_t;
+        const int tt = ((u / a.tiles_n) % a.tiles_t + tt_rot) % a.tiles_t;
         const int sp = u / (a.tiles_n * a.tiles_t);
         const int kb0 = sp * kb_per_split;
         const int kb1 = min(a.k_blocks, kb0 + kb_per_split);
+        if (a.gate_enabled) {
+          // the rows of this token tile come from one or two source ranks: wait (bounded) for their pushes
+          const int s0 = (tt * BT) / a.gate_rows;
+          const int s1 = min(a.ar.world - 1, (min(a.T, (tt + 1) * BT) - 1) / a.gate_rows);
+          for (int sr = s0; sr <= s1 && ok; ++sr) {
+            if (sr == a.ar.rank) continue;
+            if (!wait_flag(flag_ptr(a.ar, a.ar.rank, kGateKind, 0, sr), gate_epoch, a.ar.spin_budget, a.status, 600 + sr))
+              ok = false;
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async.global;" ::: "memory");    // peer stores (generic proxy) -> TMA reads
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&bars->empty[stage], phase ^ 1, a.status, 100 + stage)) { ok = false; break; }
           mbar_expect_tx(&bars->full[stage], kTxBytes);
@@ -234,7 +258,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
     bool ok = true;
     for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
       const int tn = u % a.tiles_n;
-      const int tt = (u / a.tiles_n) % a.tiles_t;
+      const int tt = ((u / a.tiles_n) % a.tiles_t + tt_rot) % a.tiles_t;
       const int sp = u / (a.tiles_n * a.tiles_t);
       const int kb0 = sp * kb_per_split;
       const int kb1 = min(a.k_blocks, kb0 + kb_per_split);
@@ -544,10 +568,10 @@ STK_API long long stk_gemm_workspace_bytes(int T, int N, int splits) {
   return splits > 1 ? static_cast<long long>(splits) * T * N * 4 : 0;
 }
 
-STK_API int stk_gemm(const void* W, long long ldw, const void* X, long long ldx, void* out, long long ldo, int T, int N,
-                     int K, int is_fp8, int out_fp32, const float* w_scale, int w_scale_ld, const float* x_scale,
-                     int x_scale_ld, int splits, float* workspace, int* counters, int* status, int sm_count,
-                     int groups, const void* ar_ctx, void* stream) {
+static int gemm_launch(const void* W, long long ldw, const void* X, long long ldx, void* out, long long ldo, int T, int N,
+                       int K, int is_fp8, int out_fp32, const float* w_scale, int w_scale_ld, const float* x_scale,
+                       int x_scale_ld, int splits, float* workspace, int* counters, int* status, int sm_count,
+                       int groups, const void* ar_ctx, const void* gate_ctx, int gate_rows, void* stream) {
   if (T <= 0 || N <= 0 || K <= 0) return 0;
   const int es = is_fp8 ? 1 : 2;
   if ((ldw * es) % 16 || (ldx * es) % 16 || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(X) & 15))
@@ -586,6 +610,14 @@ STK_API int stk_gemm(const void* W, long long ldw, const void* X, long long ldx,
       return -18;
     a.ar_enabled = 1;
   }
+  a.gate_enabled = 0;
+  a.gate_rows = 0;
+  if (gate_ctx != nullptr) {
+    if (ar_ctx != nullptr || gate_rows <= 0 || a.splits != 1) return -19;
+    memcpy(&a.ar, gate_ctx, sizeof(a.ar));
+    a.gate_enabled = 1;
+    a.gate_rows = gate_rows;
+  }
   const int units = a.splits * a.tiles_n * a.tiles_t;
   const int grid = units < sm_count ? units : sm_count;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -599,6 +631,24 @@ STK_API int stk_gemm(const void* W, long long ldw, const void* X, long long ldx,
   }
 #undef STK_LAUNCH
   return -16;
+}
+
+STK_API int stk_gemm(const void* W, long long ldw, const void* X, long long ldx, void* out, long long ldo, int T, int N,
+                     int K, int is_fp8, int out_fp32, const float* w_scale, int w_scale_ld, const float* x_scale,
+                     int x_scale_ld, int splits, float* workspace, int* counters, int* status, int sm_count,
+                     int groups, const void* ar_ctx, void* stream) {
+  return gemm_launch(W, ldw, X, ldx, out, ldo, T, N, K, is_fp8, out_fp32, w_scale, w_scale_ld, x_scale, x_scale_ld, splits,
+                     workspace, counters, status, sm_count, groups, ar_ctx, nullptr, 0, stream);
+}
+
+// All-gather -> GEMM: X is the gathered [T, K] matrix inside this rank's symmetric region (filled by
+// stk_symm_ag_push on every rank, `gate_rows` rows per source rank); tiles wait only for the shards they read.
+STK_API int stk_gemm_gated(const void* W, long long ldw, const void* X, long long ldx, void* out, long long ldo, int T,
+                           int N, int K, int is_fp8, int out_fp32, const float* w_scale, int w_scale_ld,
+                           const float* x_scale, int x_scale_ld, int* status, int sm_count, const void* gate_ctx,
+                           int gate_rows, void* stream) {
+  return gemm_launch(W, ldw, X, ldx, out, ldo, T, N, K, is_fp8, out_fp32, w_scale, w_scale_ld, x_scale, x_scale_ld, 1,
+                     nullptr, nullptr, status, sm_count, 1, nullptr, gate_ctx, gate_rows, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -211,6 +211,47 @@ STK_API int stk_twoshot_allreduce(const void* ctx, const void* in, void* out, lo
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
+// ---- all-gather push (feeds the arrival-gated GEMM) ----------------------------------------------
+// Every rank copies its shard into slot `rank` of the gathered matrix at byte offset `dst_off` of EVERY
+// rank's region (its own included) with 16-byte stores; the last CTA to finish raises flag (kAgKind, 0, rank)
+// on every peer with the call's epoch and advances the local epoch.
+constexpr int kAgKind = 4;
+
+__global__ void __launch_bounds__(512)
+ag_push_kernel(SymmCtx c, const uint4* __restrict__ shard, long long shard_vecs, long long dst_off, int* status) {
+  __shared__ uint32_t s_last;
+  const uint32_t epoch = *epoch_ptr(c, kAgKind, 0) + 1;
+  for (int r = 0; r < c.world; ++r) {
+    const int peer = (c.rank + r) % c.world;                       // start with the local copy, then spread over the links
+    uint4* dst = reinterpret_cast<uint4*>(c.base[peer] + dst_off) + static_cast<long long>(c.rank) * shard_vecs;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < shard_vecs;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+      dst[i] = __ldg(shard + i);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t* done = epoch_ptr(c, kAgKind, 1);
+    s_last = atomicAdd(done, 1u) == gridDim.x - 1 ? 1u : 0u;
+    if (s_last) *done = 0;
+  }
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    if (threadIdx.x < c.world) st_release_sys(flag_ptr(c, threadIdx.x, kAgKind, 0, c.rank), epoch);
+    if (threadIdx.x == 0) *epoch_ptr(c, kAgKind, 0) = epoch;
+  }
+  (void)status;
+}
+
+STK_API int stk_symm_ag_push(const void* ctx, const void* shard, long long shard_bytes, long long dst_off, int nblocks,
+                             int* status, void* stream) {
+  const SymmCtx* c = reinterpret_cast<const SymmCtx*>(ctx);
+  if (shard_bytes <= 0 || shard_bytes % 16 || dst_off % 16 || nblocks < 1 || nblocks > kMaxArBlocks) return -1;
+  ag_push_kernel<<<nblocks, 512, 0, (cudaStream_t)stream>>>(*c, (const uint4*)shard, shard_bytes / 16, dst_off, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
 STK_API int stk_flag_timeout_probe(const void* flag, int epoch, int budget, int* status, void* stream) {
   flag_timeout_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((const uint32_t*)flag, (uint32_t)epoch, (uint32_t)budget,
                                                                 status);

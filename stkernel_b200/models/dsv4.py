@@ -23,6 +23,7 @@ from ..ops import attention as A
 from ..ops import cache as C
 from ..ops import functional as Fn
 from ..ops import moe as M
+from ..utils.spans import span
 from ..ops.functional import LinearWeight
 from .dsv4_oracle import index_cache_computes
 from .weights import compressor_slots
@@ -323,8 +324,9 @@ class DSV4Model:
             else:
                 topk_slots, topk_lens = A.c128_indices(meta.positions, meta.tok_req, grp.table_dev, lw.ratio,
                                                        cfg.index_topk)
-        o = A.sparse_mla(q, self.kv.swa_cache[li], meta.swa_slots, meta.swa_lens, comp_cache, topk_slots, topk_lens,
-                         lw.sink, D ** -0.5, inv_rope=(meta.positions, self.inv))
+        with span("sparse_mla", T):
+            o = A.sparse_mla(q, self.kv.swa_cache[li], meta.swa_slots, meta.swa_lens, comp_cache, topk_slots, topk_lens,
+                             lw.sink, D ** -0.5, inv_rope=(meta.positions, self.inv))
         # grouped low-rank output projection, then the row-parallel wo_b (+ all-reduce)
         G_l = len(lw.w_oa)
         hpg = cfg.num_attention_heads // cfg.o_groups
@@ -335,9 +337,10 @@ class DSV4Model:
             z = torch.empty(T, G_l * cfg.o_lora_rank, dtype=o.dtype, device=y.device)
             for gi, wg in enumerate(lw.w_oa):
                 Fn.linear(og[:, gi], wg, out=z[:, gi * cfg.o_lora_rank:(gi + 1) * cfg.o_lora_rank], tag=f"oa")
-        ar = self._gemm_ar_ctx(T, cfg.hidden_size)
-        out = Fn.linear(z, lw.w_ob, tag="ob", ar_ctx=ar)
-        return out if ar is not None else self._all_reduce(out)
+        with span("o_proj_b+allreduce", T):
+            ar = self._gemm_ar_ctx(T, cfg.hidden_size)
+            out = Fn.linear(z, lw.w_ob, tag="ob", ar_ctx=ar)
+            return out if ar is not None else self._all_reduce(out)
 
     # ---- MoE sub-block ----------------------------------------------------------
     def moe(self, lw: LayerWeights, y: torch.Tensor, yq, meta: StepMeta) -> torch.Tensor:
@@ -366,13 +369,15 @@ class DSV4Model:
         r = Fn.mhc_pre(X, *lw.hc_attn, lw.attn_norm, cfg.rms_norm_eps, cfg.hc_eps, cfg.hc_sinkhorn_iters, quant=want_q,
                        tag="mhc_a")
         y, post, comb = r[0], r[1], r[2]
-        a = self.attention(li, lw, y, r[3] if want_q else None, meta)
+        with span("attention", X.shape[0]):
+            a = self.attention(li, lw, y, r[3] if want_q else None, meta)
         X = Fn.mhc_post(a, X, post, comb)
         want_q = lw.w_sh13 is not None and lw.w_sh13.is_fp8 and Fn.wants_quant_act(X.shape[0], X.device)
         r = Fn.mhc_pre(X, *lw.hc_ffn, lw.ffn_norm, cfg.rms_norm_eps, cfg.hc_eps, cfg.hc_sinkhorn_iters, quant=want_q,
                        tag="mhc_f")
         y, post, comb = r[0], r[1], r[2]
-        f = self.moe(lw, y, r[3] if want_q else None, meta)
+        with span("moe", X.shape[0]):
+            f = self.moe(lw, y, r[3] if want_q else None, meta)
         return Fn.mhc_post(f, X, post, comb)
 
     # ---- whole model -------------------------------------------------------------

@@ -19,7 +19,7 @@ import torch.distributed as dist
 class Communicator:
     def __init__(self, group: Optional[dist.ProcessGroup] = None, device=None, use_symm: bool = True,
                  oneshot_max_bytes: int = 512 * 1024, cpu_group: Optional[dist.ProcessGroup] = None,
-                 fuse_gemm: bool = True):
+                 fuse_gemm: bool = True, ag_bytes: int = 0):
         self.group = group if group is not None else dist.group.WORLD
         self.world_size = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
@@ -33,7 +33,7 @@ class Communicator:
         if use_symm and self.device.type == "cuda" and self.world_size > 1:
             try:
                 from .symm import SymmetricAllReduce
-                self.symm = SymmetricAllReduce(self, max_bytes=64 << 20)
+                self.symm = SymmetricAllReduce(self, max_bytes=64 << 20, user_bytes=2 * ag_bytes)
                 self.symm.self_test()
             except Exception as e:  # fail closed onto NCCL, permanently
                 self.symm = None

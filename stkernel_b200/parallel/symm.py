@@ -108,6 +108,8 @@ class SymmetricAllReduce:
         self.oneshot_max = min(comm.oneshot_max_bytes, oneshot_bytes)
         self.twoshot_max = max_bytes
         self.enabled = True
+        self.ag_capacity = (user_bytes // 2) // 256 * 256        # two gathered-activation buffers, used alternately
+        self._ag_calls = 0
         comm.barrier()
 
     def eligible(self, x: torch.Tensor) -> bool:
@@ -164,6 +166,35 @@ class SymmetricAllReduce:
         if not self.enabled or t * n * 2 > self.layout["gemm_bytes"] or t > 128 or n % 128:
             return None
         return self.ctx
+
+    AG_BLOCKS = 32
+
+    def ag_gemm(self, x_shard: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """All-gather of row shards fused with a column-parallel GEMM: every rank holds x_shard [T/world, K]
+        (bf16) and weight [N_local, K] (bf16); returns x_full @ weight.T as [T, N_local].
+
+        The shard is pushed into every rank's gathered matrix over NVLink (each row crosses a link once);
+        the tcgen05 GEMM starts with the tiles of its own shard and waits, tile by tile, only for the shards
+        it is about to read.  Two gathered buffers alternate by call, so a rank may start the next push while
+        a slower peer still reads the previous one."""
+        rows, k = x_shard.shape
+        t = rows * self.world
+        n = weight.shape[0]
+        nbytes = rows * k * 2
+        if not (self.enabled and x_shard.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x_shard.is_contiguous()
+                and weight.is_contiguous() and nbytes % 16 == 0 and t * k * 2 <= self.ag_capacity):
+            raise ValueError("ag_gemm: unsupported operands or gathered matrix larger than the reserved buffers")
+        parity = self._ag_calls & 1
+        self._ag_calls += 1
+        off = self.layout["off_user"] + parity * self.ag_capacity
+        st = _lib.status_buffer()
+        _lib.call("stk_symm_ag_push", self.ctx, x_shard, nbytes, off, self.AG_BLOCKS, st, _lib.stream())
+        if out is None:
+            out = torch.empty(t, n, dtype=torch.bfloat16, device=x_shard.device)
+        import ctypes as _ct
+        _lib.call("stk_gemm_gated", weight, k, _ct.c_void_p(self.heap.local + off), k, out, out.stride(0), t, n, k, 0, 0,
+                  None, 0, None, 0, st, _lib.sm_count(), self.ctx, rows, _lib.stream())
+        return out
 
     def disable(self, reason: str) -> None:
         self.enabled = False

@@ -48,8 +48,9 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device(f"cuda:{local}")
     dist.init_process_group("nccl", device_id=dev)
-    comm = Communicator(device=dev, use_symm=True)
-    out = {"world": world, "symm": comm.symm is not None, "disabled_reason": comm.disabled_reason, "allreduce": [], "gemm_ar": []}
+    comm = Communicator(device=dev, use_symm=True, ag_bytes=4096 * 8192 * 2)
+    out = {"world": world, "symm": comm.symm is not None, "disabled_reason": comm.disabled_reason, "allreduce": [], "gemm_ar": [],
+           "ag_gemm": []}
     assert comm.symm is not None, comm.disabled_reason
     g = torch.Generator(device=dev).manual_seed(100 + rank)
     for numel in (4096, 6 * 4096, 64 * 4096, 256 * 4096, 4096 * 4096):
@@ -104,6 +105,42 @@ def main():
             out["gemm_ar"].append({"dtype": dtype, "T": T, "fused_us": fused, "gemm_then_nccl_us": timed(base),
                                    "gemm_then_oneshot_us": timed(base_symm),
                                    "cublas_then_nccl_us": timed(base_torch) if dtype == "bf16" else None, "rel_err": err})
+    # ---- all-gather fused with the column-parallel GEMM (sequence-sharded activations) ----
+    K, N_total = 8192, 4096
+    n_loc = N_total // world
+    for T in (8, 64, 256, 4096):
+        if T % world:
+            continue
+        rows = T // world
+        gw = torch.Generator(device=dev).manual_seed(31 + rank)
+        xs = torch.randn(rows, K, device=dev, generator=gw).to(torch.bfloat16)
+        w = (torch.randn(n_loc, K, device=dev, generator=gw) * 0.05).to(torch.bfloat16)
+        full = torch.empty(T, K, dtype=torch.bfloat16, device=dev)
+        dist.all_gather_into_tensor(full, xs)
+        ref = full.float() @ w.float().t()
+        y = None
+        for _ in range(3):                       # odd count on purpose: both buffers get used
+            y = comm.symm.ag_gemm(xs, w)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        err = ((y.float() - ref).norm() / ref.norm()).item()
+        assert err < 2e-2, ("ag_gemm", T, err)
+        comm.symm.ag_gemm(xs, w)                 # back to an even call count before graph capture
+        fused = timed(lambda: comm.symm.ag_gemm(xs, w))
+        lw = Fn.LinearWeight(w)
+
+        def base_own():
+            dist.all_gather_into_tensor(full, xs)
+            Fn.linear(full, lw)
+        def base_torch():
+            dist.all_gather_into_tensor(full, xs)
+            torch.matmul(full, w.t())
+        flops = 2.0 * T * n_loc * K
+        nvl = rows * K * 2 * (world - 1)         # bytes this rank receives
+        roof = max(flops / 1613.6e12, nvl / 770e9) * 1e6
+        out["ag_gemm"].append({"T": T, "fused_us": fused, "nccl_ag_then_own_gemm_us": timed(base_own),
+                               "nccl_ag_then_cublas_us": timed(base_torch), "roofline_us": roof, "frac_of_roofline": roof / fused,
+                               "rel_err": err})
     if rank == 0:
         print("SYMM_OK " + json.dumps(out), flush=True)
     torch.cuda.synchronize()

@@ -247,3 +247,21 @@ def test_markov_refit_recovers_bigram_structure(tmp_path):
     p = tmp_path / "m.pt"
     torch.save({"markov_w1": out["markov_w1"], "markov_w2": out["markov_w2"], "meta": out["meta"]}, p)
     MarkovHead(torch.zeros(V, 48).bfloat16(), torch.zeros(V, 48).bfloat16()).sideload(str(p), V, 48)
+
+
+def test_span_recorder_accounting():
+    from stkernel_b200.utils import spans
+    r = spans.SpanRecorder(decode_rows=6)
+    assert r.phase(6) == "decode" and r.phase(7) == "prefill"
+    r.add_ms("decode", "attention", 1.5)
+    r.add_ms("decode", "attention", 0.5)
+    r.add_ms("decode", "moe", 1.0)
+    r.add_ms("prefill", "moe", 10.0)
+    rep = r.report()
+    assert "[decode] 3.00 ms in 3 spans" in rep and "attention" in rep and "[prefill] 10.00 ms" in rep
+    assert rep.index("attention") < rep.index("moe")           # sorted by time within a phase
+    with spans.span("x"):                                       # disabled (STK_PROF unset): a null context
+        pass
+    with r.span("cpu-only", 1):                                 # no CUDA here: passes through without recording
+        pass
+    assert ("decode", "cpu-only") not in r.totals
