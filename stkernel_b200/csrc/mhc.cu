@@ -342,8 +342,11 @@ namespace cg = cooperative_groups;
 
 constexpr int kClusterSize = 8;
 
+constexpr int kClusterThreads = 512;
+constexpr int kClusterWarps = kClusterThreads / 32;
+
 template <int NMIX>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kClusterThreads)
 mhc_cluster_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ fn, const float* __restrict__ base,
                    const float* __restrict__ scale, const __nv_bfloat16* __restrict__ norm_w, float* __restrict__ post,
                    float* __restrict__ comb, __nv_bfloat16* __restrict__ y, int H, int hc, float rms_eps, float hc_eps,
@@ -353,7 +356,7 @@ mhc_cluster_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   const int t = blockIdx.x / kClusterSize;
   __shared__ float part[NMIX + 1];          // this CTA's partial dots + sum x^2 (read by the peers)
   __shared__ float part2[1];                // this CTA's partial sum y^2
-  __shared__ float red[8][NMIX + 1];
+  __shared__ float red[kClusterWarps][NMIX + 1];
   __shared__ float mixes[NMIX + 1];
   __shared__ float pre[8];
   __shared__ float gmax[8];
@@ -368,14 +371,32 @@ mhc_cluster_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   float ss = 0.f;
 #pragma unroll
   for (int j = 0; j < NMIX; ++j) acc[j] = 0.f;
-  for (int k = k0 + threadIdx.x * 2; k < k1; k += blockDim.x * 2) {
-    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(xt + k);
-    const float xa = __low2float(v), xb = __high2float(v);
-    ss = fmaf(xa, xa, fmaf(xb, xb, ss));
+  // Four consecutive elements per thread: with 8 x 512 threads the whole [NMIX, HC] matrix is requested in one
+  // round of 16-byte loads (the step is bounded by the latency of that single round, not by a loop of them).
+  const bool vec4 = ((k0 | k1 | HC) & 3) == 0;
+  if (vec4) {
+    for (int k = k0 + threadIdx.x * 4; k < k1; k += blockDim.x * 4) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(xt + k);
+      const __nv_bfloat162 v0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+      const __nv_bfloat162 v1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+      const float x0 = __low2float(v0), x1 = __high2float(v0), x2 = __low2float(v1), x3 = __high2float(v1);
+      ss = fmaf(x0, x0, fmaf(x1, x1, fmaf(x2, x2, fmaf(x3, x3, ss))));
+      float4 f[NMIX];
 #pragma unroll
-    for (int j = 0; j < NMIX; ++j) {
-      const float2 f = __ldg(reinterpret_cast<const float2*>(fn + static_cast<long long>(j) * HC + k));
-      acc[j] = fmaf(xa, f.x, fmaf(xb, f.y, acc[j]));
+      for (int j = 0; j < NMIX; ++j) f[j] = __ldg(reinterpret_cast<const float4*>(fn + static_cast<long long>(j) * HC + k));
+#pragma unroll
+      for (int j = 0; j < NMIX; ++j) acc[j] = fmaf(x0, f[j].x, fmaf(x1, f[j].y, fmaf(x2, f[j].z, fmaf(x3, f[j].w, acc[j]))));
+    }
+  } else {
+    for (int k = k0 + threadIdx.x * 2; k < k1; k += blockDim.x * 2) {
+      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(xt + k);
+      const float xa = __low2float(v), xb = __high2float(v);
+      ss = fmaf(xa, xa, fmaf(xb, xb, ss));
+#pragma unroll
+      for (int j = 0; j < NMIX; ++j) {
+        const float2 f = __ldg(reinterpret_cast<const float2*>(fn + static_cast<long long>(j) * HC + k));
+        acc[j] = fmaf(xa, f.x, fmaf(xb, f.y, acc[j]));
+      }
     }
   }
 #pragma unroll
@@ -390,7 +411,7 @@ mhc_cluster_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   __syncthreads();
   if (threadIdx.x <= NMIX) {
     float s = 0.f;
-    for (int w = 0; w < 8; ++w) s += red[w][threadIdx.x];
+    for (int w = 0; w < kClusterWarps; ++w) s += red[w][threadIdx.x];
     part[threadIdx.x] = s;
   }
   cluster.sync();
@@ -459,12 +480,12 @@ mhc_cluster_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   // ---- phase 3: weighted stream sum over this CTA's columns, cluster-wide RMSNorm ----
   const int cols = ((H / kClusterSize) + 1) & ~1;
   const int c0 = crank * cols, c1 = min(H, c0 + cols);
-  constexpr int kMaxPer = 4;                           // column pairs per thread (H <= 8 * 256 * 2 * 4)
+  constexpr int kMaxPer = 2;                           // column pairs per thread (H <= 8 * 512 * 2 * 2)
   float ya[kMaxPer], yb[kMaxPer];
   float ss2 = 0.f;
 #pragma unroll
   for (int u = 0; u < kMaxPer; ++u) {
-    const int i = c0 + (u * 256 + threadIdx.x) * 2;
+    const int i = c0 + (u * kClusterThreads + threadIdx.x) * 2;
     ya[u] = yb[u] = 0.f;
     if (i < c1) {
       float a0 = 0.f, a1 = 0.f;
@@ -490,7 +511,7 @@ mhc_cluster_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
     __syncthreads();
     if (threadIdx.x == 0) {
       float s = 0.f;
-      for (int w = 0; w < 8; ++w) s += red[w][0];
+      for (int w = 0; w < kClusterWarps; ++w) s += red[w][0];
       part2[0] = s;
     }
     cluster.sync();
@@ -500,7 +521,7 @@ mhc_cluster_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   }
 #pragma unroll
   for (int u = 0; u < kMaxPer; ++u) {
-    const int i = c0 + (u * 256 + threadIdx.x) * 2;
+    const int i = c0 + (u * kClusterThreads + threadIdx.x) * 2;
     if (i < c1) {
       float a0 = ya[u] * r, a1 = yb[u] * r;
       if (do_norm) {
@@ -524,10 +545,10 @@ STK_API int stk_mhc_cluster(const void* x, const float* fn, const float* base, c
                             float* post, float* comb, void* y, int T, int H, int hc, int n_mix, float rms_eps,
                             float hc_eps, int sinkhorn_iters, float post_mult, int mode, void* stream) {
   if (T <= 0) return 0;
-  if (hc * hc > 32 || H % 2 || H > kClusterSize * 256 * 2 * 4 || (H * hc) % 2) return -1;
+  if (hc * hc > 32 || H % 2 || H > kClusterSize * kClusterThreads * 2 * 2 || (H * hc) % 2) return -1;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(T * kClusterSize);
-  cfg.blockDim = dim3(256);
+  cfg.blockDim = dim3(kClusterThreads);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = (cudaStream_t)stream;
   cudaLaunchAttribute attr[1];
