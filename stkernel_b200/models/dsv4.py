@@ -13,6 +13,7 @@ Parallel layout (one rank per GPU, `tp` ranks):
 from __future__ import annotations
 
 import hashlib
+import os
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Tuple
 
@@ -261,6 +262,12 @@ class DSV4Model:
         self.topk_buffer: Optional[torch.Tensor] = None     # IndexCache: shared by consecutive C4A layers
         self.aux_layers: Tuple[int, ...] = ()
         self.aux_out: List[torch.Tensor] = []
+        # Sequence-parallel indexer: with TP the indexer weights are replicated, so each rank scores only its
+        # share of a large step's rows and the top-k rows are all-gathered (overlay/attention.py
+        # `_indexer_sp_owned_ranges` in the reference; here every row of a step is split evenly, which is exact
+        # because scoring and top-k are independent per row).
+        self.indexer_sp = tp_size > 1 and comm is not None
+        self.indexer_sp_min_rows = int(os.environ.get("STK_INDEXER_SP_MIN_ROWS", "256"))
 
     # ---- collectives ----------------------------------------------------------
     def _all_reduce(self, x: torch.Tensor) -> torch.Tensor:
@@ -316,9 +323,20 @@ class DSV4Model:
                                        meta.tok_req, meta.first_pos, meta.last_pos, self.kv.idx_state[li],
                                        grp.table_dev, self.kv.idx_cache[li], lw.ratio, 2, cfg.rms_norm_eps)
                     nv = A.compressed_valid(meta.positions, lw.ratio)
-                    scores = A.indexer_scores(qq, wf, self.kv.idx_cache[li], grp.table_dev, meta.tok_req, nv,
-                                              max(meta.max_comp_rows, 1))
-                    A.topk_rows(scores, nv, K, out=self.topk_buffer)
+                    if self.indexer_sp and T >= self.indexer_sp_min_rows * self.tp_size:
+                        shard = -(-T // self.tp_size)
+                        a0 = min(T, self.tp_rank * shard)
+                        a1 = min(T, a0 + shard)
+                        part = torch.full((shard, K), -1, dtype=torch.int32, device=y.device)
+                        if a1 > a0:
+                            sc = A.indexer_scores(qq[a0:a1], wf[a0:a1], self.kv.idx_cache[li], grp.table_dev,
+                                                  meta.tok_req[a0:a1], nv[a0:a1], max(meta.max_comp_rows, 1))
+                            A.topk_rows(sc, nv[a0:a1], K, out=part)
+                        self.topk_buffer[:T] = self.comm.all_gather_dim0(part)[:T]
+                    else:
+                        scores = A.indexer_scores(qq, wf, self.kv.idx_cache[li], grp.table_dev, meta.tok_req, nv,
+                                                  max(meta.max_comp_rows, 1))
+                        A.topk_rows(scores, nv, K, out=self.topk_buffer)
                 topk_slots, topk_lens = A.topk_to_slots(self.topk_buffer[:T], grp.table_dev, meta.tok_req,
                                                         grp.max_pages_per_req * C.PAGE, tag=f"topk")
             else:

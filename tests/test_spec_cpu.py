@@ -160,3 +160,25 @@ def test_bf16_head_release_truth_table():
     assert len(f(True, False, True, False, True, False)) == 1
     assert f(True, False, True, False, False, False) == []                     # draft does not share the head
     assert len(f(False, False, True, True, True, True)) == 4
+
+
+def test_rowwise_fp8_draft_head():
+    from stkernel_b200.spec import fp8_draft_head as F8
+    torch.manual_seed(0)
+    w = torch.randn(300, 128) * 0.05
+    w[7] *= 40.0                                     # a row with a very different range keeps its own scale
+    h = torch.randn(5, 128)
+    head = F8.quantize_draft_head(w)
+    assert head.weight_fp8.dtype == torch.float8_e4m3fn and head.row_scale.shape == (1, 300)
+    lg = F8.fp8_draft_head_logits(h, head)
+    ref = h @ w.t()
+    assert ((lg - ref).norm() / ref.norm()).item() < 0.05
+    assert (lg.argmax(-1) == ref.argmax(-1)).all()
+    with pytest.raises(ValueError):
+        F8.quantize_draft_head(torch.zeros(3))
+    with pytest.raises(ValueError):
+        F8.fp8_draft_head_logits(torch.zeros(2, 64), head)
+    assert F8.pick_head_impl(True, False) == "rowwise" and F8.pick_head_impl(False, True) == "block"
+    assert F8.pick_head_impl(False, False) == "bf16"
+    with pytest.raises(ValueError):
+        F8.pick_head_impl(True, True)

@@ -43,7 +43,9 @@ def _wait_up(port, proc, timeout=180):
 
 
 def _launch(world, port, extra=()):
-    env = dict(os.environ, PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2", STK_CPU_ACT_FP32="1")
+    # a tiny threshold so that the prompt's prefill step takes the sequence-parallel indexer path at world 2
+    env = dict(os.environ, PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2", STK_CPU_ACT_FP32="1",
+               STK_INDEXER_SP_MIN_ROWS="4")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(_free_port()), "-m", "stkernel_b200.serve.tp_worker", "--tiny", "--port", str(port),
            "--tensor-parallel-size", str(world), "--max-model-len", "512", "--max-num-seqs", "4",
@@ -62,7 +64,8 @@ def _stop(proc):
 
 @pytest.mark.timeout(600)
 def test_tp2_lockstep_serving_matches_tp1():
-    body = {"prompt": "lockstep", "max_tokens": 8, "temperature": 0, "ignore_eos": True}
+    body = {"prompt": "lockstep serving over two ranks, with a prompt long enough to fill compressed rows", "max_tokens": 8,
+            "temperature": 0, "ignore_eos": True}
     outs = {}
     for world in (1, 2):
         port = _free_port()
