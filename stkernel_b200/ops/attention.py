@@ -241,8 +241,9 @@ def sparse_mla(q: torch.Tensor, swa_cache: PagedCache, swa_slots: torch.Tensor, 
     max_rows = swa_slots.shape[1] + (topk_slots.shape[1] if topk_slots is not None else 0)
     cc = comp_cache if comp_cache is not None else swa_cache
     if USE_TENSOR_CORE_MLA and swa_cache.fp8 and d == 512 and swa_cache.rope_dim == 64 and nh <= 64 and q.stride(0) % 8 == 0:
-        # tcgen05 kernel: 128-row blocks; enough splits to fill the SMs at decode sizes
-        n_splits = max(1, min((max_rows + 127) // 128, (2 * _lib.sm_count()) // max(t, 1)))
+        # tcgen05 kernel: one 64-row key block per CTA while the SMs are not full (a block is a serial chain of
+        # gather -> QK^T -> softmax -> PV, so at decode sizes more, shorter CTAs finish sooner)
+        n_splits = max(1, min((max_rows + 63) // 64, (2 * _lib.sm_count()) // max(t, 1)))
         ws = scratch("mla.partial", (t * n_splits * nh * (d + 2),), F32, q.device)
         out = torch.empty(t, nh, d, dtype=BF16, device=q.device)
         _lib.call("stk_sparse_mla_tc", q, q.stride(0), swa_cache.buf, swa_cache.page_stride, cc.buf, cc.page_stride,
