@@ -87,6 +87,130 @@ __device__ __forceinline__ uint32_t float_key(float f) {
 // One CTA (1024 threads) per row.  out[t, :k]: indices of the k largest scores among the first
 // n_valid[t] entries (all of them, ascending, when n_valid <= k), -1 padded.  Elements above the
 // threshold come first in index order, then threshold ties in index order: deterministic.
+// Register-resident variant for rows of up to PER * 1024 scores: every thread keeps PER consecutive keys, so the row
+// is read once; the four radix passes use per-warp histograms (no cross-warp atomic contention) and a warp-parallel
+// suffix search; the compaction is one block-wide exclusive scan.  Same output order as the generic kernel.
+template <int PER>
+__global__ void __launch_bounds__(1024)
+topk_rows_reg_kernel(const float* __restrict__ scores, long long ld, const int* __restrict__ n_valid,
+                     int* __restrict__ out, int k, int out_ld) {
+  __shared__ int whist[32][256];
+  __shared__ int hist[256];
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_remaining;
+  __shared__ int warp_gt[32], warp_eq[32];
+  const int t = blockIdx.x;
+  const int n = n_valid[t];
+  const float* row = scores + t * ld;
+  int* orow = out + static_cast<long long>(t) * out_ld;
+  if (n <= k) {
+    for (int i = threadIdx.x; i < k; i += blockDim.x) orow[i] = i < n ? i : -1;
+    return;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int i0 = threadIdx.x * PER;
+  uint32_t key[PER];
+#pragma unroll
+  for (int j = 0; j < PER; ++j) key[j] = (i0 + j) < n ? float_key(row[i0 + j]) : 0u;
+  const int mine = max(0, min(PER, n - i0));            // valid keys of this thread
+  if (threadIdx.x == 0) {
+    s_prefix = 0;
+    s_remaining = k;
+  }
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 24 - 8 * pass;
+    for (int i = threadIdx.x; i < 32 * 256; i += blockDim.x) (&whist[0][0])[i] = 0;
+    __syncthreads();
+    const uint32_t prefix = s_prefix;
+    const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+#pragma unroll
+    for (int j = 0; j < PER; ++j)
+      if (j < mine && (key[j] & mask) == prefix) atomicAdd(&whist[warp][(key[j] >> shift) & 0xff], 1);
+    __syncthreads();
+    if (threadIdx.x < 256) {
+      int sum = 0;
+#pragma unroll 8
+      for (int w = 0; w < 32; ++w) sum += whist[w][threadIdx.x];
+      hist[threadIdx.x] = sum;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      // lane l owns bins [8l, 8l+8); suffix sums over lanes locate the lane, a short scan the bin
+      int part = 0;
+#pragma unroll
+      for (int b = 0; b < 8; ++b) part += hist[lane * 8 + b];
+      int suf = part;                                     // inclusive suffix sum (lanes >= this one)
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_down_sync(0xffffffffu, suf, o);
+        if (lane + o < 32) suf += v;
+      }
+      const int rem0 = s_remaining;
+      const int above = suf - part;                       // count in bins above this lane's range
+      const bool here = above < rem0 && suf >= rem0;      // the k-th largest falls into this lane's bins
+      const uint32_t who = __ballot_sync(0xffffffffu, here);
+      const int sel = who ? (31 - __clz(who)) : 0;        // exactly one lane when n > k; highest as a guard
+      if (lane == sel) {
+        int rem = rem0 - above;
+        int b = 7;
+        for (; b > 0; --b) {
+          const int h = hist[lane * 8 + b];
+          if (h >= rem) break;
+          rem -= h;
+        }
+        s_prefix = prefix | (static_cast<uint32_t>(lane * 8 + b) << shift);
+        s_remaining = rem;
+      }
+    }
+    __syncthreads();
+  }
+  const uint32_t thr = s_prefix;
+  const int need_eq = s_remaining;
+  const int count_gt = k - need_eq;
+  int cg = 0, ce = 0;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    if (j < mine) {
+      cg += key[j] > thr;
+      ce += key[j] == thr;
+    }
+  }
+  // block-wide exclusive scan of (cg, ce) in thread order = index order
+  int sg = cg, se = ce;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int vg = __shfl_up_sync(0xffffffffu, sg, o);
+    const int ve = __shfl_up_sync(0xffffffffu, se, o);
+    if (lane >= o) { sg += vg; se += ve; }
+  }
+  if (lane == 31) { warp_gt[warp] = sg; warp_eq[warp] = se; }
+  __syncthreads();
+  if (warp == 0) {
+    int g = warp_gt[lane], e = warp_eq[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int vg = __shfl_up_sync(0xffffffffu, g, o);
+      const int ve = __shfl_up_sync(0xffffffffu, e, o);
+      if (lane >= o) { g += vg; e += ve; }
+    }
+    warp_gt[lane] = g;
+    warp_eq[lane] = e;
+  }
+  __syncthreads();
+  int og = (warp ? warp_gt[warp - 1] : 0) + sg - cg;
+  int oe = (warp ? warp_eq[warp - 1] : 0) + se - ce;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    if (j < mine) {
+      if (key[j] > thr) orow[og++] = i0 + j;
+      else if (key[j] == thr) {
+        if (oe < need_eq) orow[count_gt + oe] = i0 + j;
+        ++oe;
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(1024)
 topk_rows_kernel(const float* __restrict__ scores, long long ld, const int* __restrict__ n_valid,
                  int* __restrict__ out, int k, int out_ld) {
@@ -243,6 +367,15 @@ STK_API int stk_indexer_scores(const void* q, const float* w, const void* kcache
 STK_API int stk_topk_rows(const float* scores, long long ld, const int* n_valid, int* out, int out_ld, int T, int k,
                           void* stream) {
   if (T <= 0) return 0;
+  // ld bounds every row's valid length: rows that fit in registers take the single-read kernel
+  if (ld <= 8 * 1024) {
+    topk_rows_reg_kernel<8><<<T, 1024, 0, (cudaStream_t)stream>>>(scores, ld, n_valid, out, k, out_ld);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  }
+  if (ld <= 16 * 1024) {
+    topk_rows_reg_kernel<16><<<T, 1024, 0, (cudaStream_t)stream>>>(scores, ld, n_valid, out, k, out_ld);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  }
   topk_rows_kernel<<<T, 1024, 0, (cudaStream_t)stream>>>(scores, ld, n_valid, out, k, out_ld);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -16,12 +16,39 @@ constexpr int kSkinnyMaxT = 4;
 
 // x: [T, K] bf16 -> xs: half, permuted: chunk c = lane + 32*k holds values [16c, 16c+16) as two uint4
 // at index ((t * kIters + k) * 2 + i) * 32 + lane.
-template <int T>
-__device__ __forceinline__ void skinny_fill_x(__half* xs, const __nv_bfloat16* x, long long ldx, int K, int iters) {
+// kPrescale: each token's row is multiplied by 2^-e with e chosen so that |x| <= 8 (e >= 0 only); xscale[t] = 2^e is
+// folded back in by the caller.  Raw e4m3 codes reach 448, so a product stays below 3584 and a sum of eight below
+// 28672: the packed fp16 partial sums of the fp8 path cannot overflow.
+template <int T, bool kPrescale>
+__device__ __forceinline__ void skinny_fill_x(__half* xs, const __nv_bfloat16* x, long long ldx, int K, int iters,
+                                              float* xscale, float* red) {
   // eight consecutive values = one 16-byte load, one conversion, one 16-byte store
   uint4* xs4 = reinterpret_cast<uint4*>(xs);
   const int k8n = K >> 3;
   const bool aligned = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((ldx & 7) == 0);
+  float mul[T];
+#pragma unroll
+  for (int t = 0; t < T; ++t) mul[t] = 1.f;
+  if constexpr (kPrescale) {
+#pragma unroll
+    for (int t = 0; t < T; ++t) {
+      float amax = 0.f;
+      if (((reinterpret_cast<uintptr_t>(x) & 3) == 0) && ((ldx & 1) == 0)) {
+        for (int k2 = threadIdx.x; k2 < (K >> 1); k2 += blockDim.x) {
+          const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(x + t * ldx + 2 * k2);
+          amax = fmaxf(amax, fmaxf(fabsf(__low2float(v)), fabsf(__high2float(v))));
+        }
+      } else {
+        for (int k = threadIdx.x; k < K; k += blockDim.x) amax = fmaxf(amax, fabsf(bf16_to_f(x[t * ldx + k])));
+      }
+      amax = block_max(amax, red);
+      int e = 0;
+      if (amax > 8.f) e = static_cast<int>(ceilf(log2f(amax * 0.125f)));
+      if (threadIdx.x == 0) xscale[t] = exp2f(static_cast<float>(e));
+      mul[t] = exp2f(static_cast<float>(-e));
+      __syncthreads();
+    }
+  }
 #pragma unroll
   for (int t = 0; t < T; ++t) {
     for (int k8 = threadIdx.x; k8 < k8n; k8 += blockDim.x) {
@@ -40,7 +67,11 @@ __device__ __forceinline__ void skinny_fill_x(__half* xs, const __nv_bfloat16* x
       uint4 o;
       __half2* oh = reinterpret_cast<__half2*>(&o);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) oh[j] = __float22half2_rn(__bfloat1622float2(b[j]));
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(b[j]);
+        if constexpr (kPrescale) { f.x *= mul[t]; f.y *= mul[t]; }
+        oh[j] = __float22half2_rn(f);
+      }
       const int c = k8 >> 1;
       xs4[((t * iters + (c >> 5)) * 2 + (k8 & 1)) * 32 + (c & 31)] = o;
     }
@@ -62,8 +93,13 @@ skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const f
   const int iters16 = ((K / 16) + 31) / 32;             // x layout is always in 16-value chunks
   // grouped (block-diagonal) mode: all rows of this CTA belong to one group, whose activations start at g*K
   const int grp = group_rows > 0 ? (blockIdx.x * 8 * rows_per_warp) / group_rows : 0;
-  skinny_fill_x<T>(reinterpret_cast<__half*>(xs4), x + static_cast<long long>(grp) * K, ldx, K, iters16);
+  __shared__ float s_xscale[kSkinnyMaxT];
+  __shared__ float s_red[32];
+  skinny_fill_x<T, kFp8>(reinterpret_cast<__half*>(xs4), x + static_cast<long long>(grp) * K, ldx, K, iters16, s_xscale, s_red);
   __syncthreads();
+  float xsc[T];
+#pragma unroll
+  for (int t = 0; t < T; ++t) xsc[t] = kFp8 ? s_xscale[t] : 1.f;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = (blockIdx.x * 8 + warp) * rows_per_warp;
   for (int r = 0; r < rows_per_warp; ++r) {
@@ -94,39 +130,44 @@ skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const f
         const int c = it * 32 + lane;
         if (c < n_chunks) {
           const uint32_t ww[4] = {wv[it].x, wv[it].y, wv[it].z, wv[it].w};
-          float wf[kVals];
           if constexpr (kFp8) {
+            // Sixteen raw e4m3 codes -> eight half2; the eight products per token are summed in packed fp16 (activations
+            // are pre-scaled, see skinny_fill_x), widened once, and the 128x128 block scale is applied to that partial.
+            __half2 w2[8];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const __half2_raw h01 = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(ww[j] & 0xffff), __NV_E4M3);
               const __half2_raw h23 = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(ww[j] >> 16), __NV_E4M3);
-              const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&h01));
-              const float2 f23 = __half22float2(*reinterpret_cast<const __half2*>(&h23));
-              wf[4 * j] = f01.x * sc[it]; wf[4 * j + 1] = f01.y * sc[it];
-              wf[4 * j + 2] = f23.x * sc[it]; wf[4 * j + 3] = f23.y * sc[it];
+              w2[2 * j] = *reinterpret_cast<const __half2*>(&h01);
+              w2[2 * j + 1] = *reinterpret_cast<const __half2*>(&h23);
+            }
+#pragma unroll
+            for (int t = 0; t < T; ++t) {
+              const uint4 xa = xs4[((t * iters16 + it) * 2 + 0) * 32 + lane];
+              const uint4 xb = xs4[((t * iters16 + it) * 2 + 1) * 32 + lane];
+              const __half2* ha = reinterpret_cast<const __half2*>(&xa);
+              const __half2* hb = reinterpret_cast<const __half2*>(&xb);
+              __half2 p = __hmul2(w2[0], ha[0]);
+              p = __hfma2(w2[1], ha[1], p);
+              p = __hfma2(w2[2], ha[2], p);
+              p = __hfma2(w2[3], ha[3], p);
+              __half2 q = __hmul2(w2[4], hb[0]);
+              q = __hfma2(w2[5], hb[1], q);
+              q = __hfma2(w2[6], hb[2], q);
+              q = __hfma2(w2[7], hb[3], q);
+              const float2 pf = __half22float2(p), qf = __half22float2(q);
+              acc[t] = fmaf(sc[it], (pf.x + pf.y) + (qf.x + qf.y), acc[t]);
             }
           } else {
+            float wf[kVals];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&ww[j]);
               wf[2 * j] = __low2float(b);
               wf[2 * j + 1] = __high2float(b);
             }
-          }
 #pragma unroll
-          for (int t = 0; t < T; ++t) {
-            if constexpr (kFp8) {
-#pragma unroll
-              for (int i = 0; i < 2; ++i) {
-                const uint4 xv = xs4[((t * iters16 + it) * 2 + i) * 32 + lane];
-                const __half2* xh = reinterpret_cast<const __half2*>(&xv);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const float2 xf = __half22float2(xh[j]);
-                  acc[t] = fmaf(wf[8 * i + 2 * j], xf.x, fmaf(wf[8 * i + 2 * j + 1], xf.y, acc[t]));
-                }
-              }
-            } else {
+            for (int t = 0; t < T; ++t) {
               // bf16 chunk c covers 8 values = half of 16-value chunk c/2
               const int c16 = c >> 1, it16 = c16 >> 5, lane16 = c16 & 31;
               const uint4 xv = xs4[((t * iters16 + it16) * 2 + (c & 1)) * 32 + lane16];
@@ -141,7 +182,7 @@ skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const f
         }
       }
 #pragma unroll
-      for (int t = 0; t < T; ++t) res[pass][t] = warp_sum(acc[t]);
+      for (int t = 0; t < T; ++t) res[pass][t] = warp_sum(acc[t]) * xsc[t];
     }
 #pragma unroll
     for (int t = 0; t < T; ++t) {

@@ -82,9 +82,10 @@ class ScheduledSeq:
 class Scheduler:
     """Decode-first continuous batching with chunked prefill and page-aware admission."""
 
-    def __init__(self, cfg: EngineConfig, kv: KVManager):
+    def __init__(self, cfg: EngineConfig, kv: KVManager, prefix_cache=None):
         self.cfg = cfg
         self.kv = kv
+        self.prefix_cache = prefix_cache
         self.waiting: List[Request] = []
         self.running: List[Request] = []
 
@@ -116,12 +117,23 @@ class Scheduler:
             r = self.waiting[0]
             ctx = min(len(r.prompt) + r.params.max_tokens, sc.max_model_len)
             if not self.kv.can_admit(min(budget, len(r.prompt)), ctx):
-                break
+                if self.prefix_cache is None or not self.prefix_cache.entries:
+                    break
+                # cached prefixes hold pages too: give them up, oldest first, before refusing a request
+                self.prefix_cache.make_room(*self.kv.admit_needs(min(budget, len(r.prompt)), ctx))
+                if not self.kv.can_admit(min(budget, len(r.prompt)), ctx):
+                    break
             self.waiting.pop(0)
             r.row = self.kv.alloc_row()
             self.running.append(r)
-            n = min(budget, len(r.prompt))
-            out.append(ScheduledSeq(r, 0, n, n == len(r.prompt)))
+            start = 0
+            if self.prefix_cache is not None:
+                start, entry = self.prefix_cache.match(r.prompt)
+                if entry is not None:
+                    self.prefix_cache.adopt(r.row, entry)
+                    r.num_computed = start
+            n = min(budget, len(r.prompt) - start)
+            out.append(ScheduledSeq(r, start, n, start + n == len(r.prompt)))
             budget -= n
         return out
 
@@ -212,7 +224,15 @@ class Engine:
                             pools["c4_pages"], pools["c128_pages"] if has_c128 else 0, sc.max_num_batched_tokens,
                             extra_swa_layers=cfg.model.n_mtp_layers if spec_on else 0, spec_tokens=n_spec)
         self.model = DSV4Model(cfg.model, weights, self.kv, comm, tp_rank, cfg.parallel.tp_size)
-        self.sched = Scheduler(cfg, self.kv)
+        self.prefix_cache = None
+        if cfg.cache.enable_prefix_caching:
+            from .prefix_cache import PrefixCache
+            pc = PrefixCache(self.kv)
+            self.prefix_cache = pc if pc.enabled else None
+            if self.prefix_cache is not None:
+                self.kv.swa.on_pressure = pc.evict_one
+                self.kv.c4.on_pressure = pc.evict_one
+        self.sched = Scheduler(cfg, self.kv, self.prefix_cache)
         self.buf = StepBuffers(sc.max_num_batched_tokens + sc.max_num_seqs * (1 + n_spec), sc.max_num_seqs, self.device,
                                sc.max_num_seqs * (1 + n_spec))
         self.drafter = None
@@ -388,10 +408,24 @@ class Engine:
                     r.finish_reason = "stop" if hit_eos else "length"
                     self.sched.retire(r)
                     self.metrics.requests_finished += 1
+        self._offer_prefixes(seqs)
         self.metrics.num_requests_running = self.sched.num_running
         self.metrics.num_requests_waiting = self.sched.num_waiting
         self.metrics.steps_total += 1
         return out
+
+    def _offer_prefixes(self, seqs: List[ScheduledSeq]) -> None:
+        """After a step: a prefill span that ended on a block boundary leaves its state to the prefix cache."""
+        pc = self.prefix_cache
+        if pc is None:
+            return
+        for s in seqs:
+            end = s.start + s.n
+            if s.start < len(s.req.prompt) and end <= len(s.req.prompt) and end % pc.block == 0 and not s.req.finished:
+                pc.offer(s.req.row, s.req.prompt, end)
+
+    def reset_prefix_cache(self) -> int:
+        return self.prefix_cache.reset() if self.prefix_cache is not None else 0
 
     # ---- speculative step ---------------------------------------------------------------
     def _finish_if_done(self, r: Request, tok: int) -> bool:
@@ -483,6 +517,7 @@ class Engine:
             r.num_computed = base + a + 1
             r.drafts = dr_h[si * n_spec:(si + 1) * n_spec]
             si += 1
+        self._offer_prefixes(seqs)
         self.metrics.num_requests_running = self.sched.num_running
         self.metrics.num_requests_waiting = self.sched.num_waiting
         self.metrics.steps_total += 1

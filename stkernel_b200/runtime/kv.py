@@ -21,7 +21,7 @@ overlay/sparse_swa_dsv4.py:87-111).
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional
+from typing import Callable, Dict, List, Optional, Tuple
 
 import torch
 
@@ -46,6 +46,7 @@ class GroupTable:
     table_dev: torch.Tensor = field(init=False)
     free: List[int] = field(init=False)
     dirty: bool = field(default=True, init=False)
+    on_pressure: Optional[Callable[[], bool]] = field(default=None, init=False)
 
     def __post_init__(self) -> None:
         self.table_host = torch.full((self.max_requests, self.max_pages_per_req), -1, dtype=torch.int32)
@@ -61,6 +62,8 @@ class GroupTable:
         self.table_dev = torch.full((self.max_requests, self.max_pages_per_req), -1, dtype=torch.int32,
                                     device=self.device)
         self.free = list(range(self.num_pages - 1, -1, -1))
+        # owners per physical page: a request row, and any number of prefix-cache entries sharing it
+        self.ref = [0] * self.num_pages
         # resident logical pages of each row form one interval [lo, hi)
         self.lo = [0] * self.max_requests
         self.hi = [0] * self.max_requests
@@ -78,9 +81,12 @@ class GroupTable:
         if first_logical < self.lo[row]:
             raise OutOfPages(f"{self.name}: page {first_logical} of row {row} was already released")
         for lp in range(start, last_logical + 1):
+            while not self.free and self.on_pressure is not None and self.on_pressure():
+                pass                                       # cached prefixes give pages back, oldest first
             if not self.free:
                 raise OutOfPages(f"{self.name}: pool of {self.num_pages} pages exhausted")
             t[lp] = self.free.pop()
+            self.ref[int(t[lp])] = 1
         if last_logical + 1 > self.hi[row]:
             self.hi[row] = last_logical + 1
             self.dirty = True
@@ -90,12 +96,38 @@ class GroupTable:
         t = self.table_np[row]
         end = min(max(logical, 0), self.hi[row])
         for lp in range(self.lo[row], end):
-            self.free.append(int(t[lp]))
+            self.unref(int(t[lp]))
             t[lp] = -1
         if end > self.lo[row]:
             self.lo[row] = end
             self.dirty = True
             self.dirty_rows.add(row)
+
+    def unref(self, page: int) -> None:
+        self.ref[page] -= 1
+        if self.ref[page] == 0:
+            self.free.append(page)
+
+    def share(self, row: int, first_logical: int, last_logical: int) -> List[int]:
+        """Physical pages of logical pages [first, last] of `row`, each with one more owner."""
+        t = self.table_np[row]
+        pages = [int(t[lp]) for lp in range(first_logical, last_logical + 1)]
+        if any(pg < 0 for pg in pages):
+            raise OutOfPages(f"{self.name}: cannot share a page that is not resident")
+        for pg in pages:
+            self.ref[pg] += 1
+        return pages
+
+    def adopt(self, row: int, first_logical: int, pages: List[int]) -> None:
+        """Map shared physical pages as logical pages [first, first + len) of an empty row."""
+        assert self.hi[row] == self.lo[row], "adopt needs a row without resident pages"
+        t = self.table_np[row]
+        for i, pg in enumerate(pages):
+            t[first_logical + i] = pg
+            self.ref[pg] += 1
+        self.lo[row], self.hi[row] = first_logical, first_logical + len(pages)
+        self.dirty = True
+        self.dirty_rows.add(row)
 
     def release_all(self, row: int) -> None:
         self.release_before(row, self.max_pages_per_req)
@@ -195,9 +227,12 @@ class KVManager:
             if n_rows > 0:
                 self.c128.ensure(row, 0, (n_rows - 1) // PAGE)
 
+    def admit_needs(self, n_tokens: int, context: int) -> Tuple[int, int]:
+        """(sliding-window pages, ratio-4 pages) a new request of this size must find free."""
+        return (min(n_tokens, context) + self.cfg.sliding_window) // PAGE + 2, (context // 4) // PAGE + 1
+
     def can_admit(self, n_tokens: int, context: int) -> bool:
-        need_swa = (min(n_tokens, context) + self.cfg.sliding_window) // PAGE + 2
-        need_c4 = (context // 4) // PAGE + 1
+        need_swa, need_c4 = self.admit_needs(n_tokens, context)
         return bool(self.free_rows) and len(self.swa.free) >= need_swa and len(self.c4.free) >= need_c4
 
     def sync(self, parity: int = 0) -> None:

@@ -1,0 +1,147 @@
+"""Automatic prefix caching over the hybrid paged KV.
+
+A prompt is cut into blocks of `block` tokens; a hash chain over the blocks keys the state the engine holds
+after computing them: the compressed pages (ratio-4 latent + indexer-K), the sliding-window pages of the
+last `window` tokens, and a copy of the compressors' ring rows (the raw rows a window that straddles the cut
+still needs).  A new request whose prompt starts with a cached chain adopts those pages (they are
+reference-counted, never copied) and starts its prefill at the cut.  `block` is 256 tokens, so that the cut
+falls on a page boundary of every group (64 sliding-window rows, 64 x 4 compressed rows); models with
+ratio-128 layers are not cached (their compressed rows share pages across cuts).
+
+Entries are dropped least-recently-used when a pool runs low, and all at once by `reset()` — the
+`/reset_prefix_cache` endpoint the reference's supervisor calls daily when idle
+(launchers/dsv4-tp4-supervisor.sh:117-132).  The reference relies on its engine's prefix cache for
+multi-turn chat; this is the equivalent for the hybrid cache layout (overlay/attention.py:743-759 lists the
+same groups).
+"""
+from __future__ import annotations
+
+import hashlib
+import struct
+from collections import OrderedDict
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..ops.cache import PAGE
+from .kv import KVManager
+
+BLOCK = 256
+
+
+@dataclass
+class Entry:
+    pos: int                                  # tokens covered
+    c4_pages: List[int]
+    swa_first: int                            # first logical SWA page held
+    swa_pages: List[int]
+    comp_state: Dict[int, torch.Tensor] = field(default_factory=dict)     # layer -> ring rows
+    idx_state: Dict[int, torch.Tensor] = field(default_factory=dict)
+
+
+def chain_hashes(tokens: Sequence[int], block: int = BLOCK, limit: Optional[int] = None) -> List[bytes]:
+    """Hash of every full block prefix: h[i] covers tokens[0 : (i+1)*block]."""
+    out: List[bytes] = []
+    prev = b""
+    n = (len(tokens) if limit is None else min(limit, len(tokens))) // block
+    for i in range(n):
+        h = hashlib.blake2b(prev, digest_size=16)
+        h.update(struct.pack(f"<{block}q", *tokens[i * block:(i + 1) * block]))
+        prev = h.digest()
+        out.append(prev)
+    return out
+
+
+class PrefixCache:
+    def __init__(self, kv: KVManager, max_entries: int = 512, block: int = BLOCK):
+        self.kv = kv
+        self.block = block
+        self.max_entries = max_entries
+        self.entries: "OrderedDict[bytes, Entry]" = OrderedDict()
+        cfg = kv.cfg
+        self.enabled = not any(cfg.layer_kind(l) == "c128a" for l in kv.layers) and block % (4 * PAGE) == 0
+        self.window_pages = (cfg.sliding_window + PAGE - 1) // PAGE
+        self.hits = 0
+        self.hit_tokens = 0
+        self.queries = 0
+
+    # ---- lookup --------------------------------------------------------------------------------
+    def match(self, prompt: Sequence[int]) -> Tuple[int, Optional[Entry]]:
+        """Longest cached prefix that leaves at least one prompt token to compute."""
+        if not self.enabled or not self.entries:
+            return 0, None
+        self.queries += 1
+        best: Optional[Entry] = None
+        for h in chain_hashes(prompt, self.block, limit=len(prompt) - 1):
+            e = self.entries.get(h)
+            if e is None:
+                break
+            best = e
+            self.entries.move_to_end(h)
+        return (best.pos, best) if best is not None else (0, None)
+
+    def adopt(self, row: int, e: Entry) -> None:
+        """Give request row `row` the cached state (pages shared, ring rows copied)."""
+        kv = self.kv
+        kv.c4.adopt(row, 0, e.c4_pages)
+        kv.swa.adopt(row, e.swa_first, e.swa_pages)
+        for li, st in e.comp_state.items():
+            kv.comp_state[li][row].copy_(st)
+        for li, st in e.idx_state.items():
+            kv.idx_state[li][row].copy_(st)
+        self.hits += 1
+        self.hit_tokens += e.pos
+
+    # ---- registration ----------------------------------------------------------------------------
+    def offer(self, row: int, prompt: Sequence[int], pos: int) -> bool:
+        """Called when request `row` has exactly `pos` prompt tokens computed; keeps the state if `pos` is a
+        block boundary that is not cached yet."""
+        if not self.enabled or pos <= 0 or pos % self.block or pos > len(prompt):
+            return False
+        hashes = chain_hashes(prompt, self.block, limit=pos)
+        key = hashes[-1]
+        if key in self.entries:
+            self.entries.move_to_end(key)
+            return False
+        kv = self.kv
+        n_c4_pages = (pos // 4) // PAGE
+        last_swa = pos // PAGE - 1
+        first_swa = max(0, last_swa - self.window_pages + 1)
+        if first_swa < kv.swa.lo[row] or last_swa >= kv.swa.hi[row] or n_c4_pages > kv.c4.hi[row]:
+            return False                                        # window pages already released: nothing to keep
+        while len(self.entries) >= self.max_entries:
+            self.evict_one()
+        e = Entry(pos, kv.c4.share(row, 0, n_c4_pages - 1) if n_c4_pages else [], first_swa,
+                  kv.swa.share(row, first_swa, last_swa))
+        for li, st in kv.comp_state.items():
+            e.comp_state[li] = st[row].clone()
+        for li, st in kv.idx_state.items():
+            e.idx_state[li] = st[row].clone()
+        self.entries[key] = e
+        return True
+
+    # ---- eviction ------------------------------------------------------------------------------
+    def _drop(self, e: Entry) -> None:
+        for pg in e.c4_pages:
+            self.kv.c4.unref(pg)
+        for pg in e.swa_pages:
+            self.kv.swa.unref(pg)
+
+    def evict_one(self) -> bool:
+        if not self.entries:
+            return False
+        _, e = self.entries.popitem(last=False)
+        self._drop(e)
+        return True
+
+    def make_room(self, need_swa: int, need_c4: int) -> None:
+        """Drop least-recently-used entries until the pools have the requested free pages (or none are left)."""
+        while (len(self.kv.swa.free) < need_swa or len(self.kv.c4.free) < need_c4) and self.evict_one():
+            pass
+
+    def reset(self) -> int:
+        n = len(self.entries)
+        while self.evict_one():
+            pass
+        return n
