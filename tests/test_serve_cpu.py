@@ -293,3 +293,129 @@ def test_profile_and_cache_reset(client):
     assert trace and os.path.exists(trace)
     assert client.post("/reset_prefix_cache").json()["reset"] is True
     assert "stk:prefix_cache_resets_total" in client.get("/metrics").text
+
+
+# ---- scripted engine: the HTTP layer's handling of reasoning + DSML tool calls end to end -------------------
+class ScriptedEngine:
+    """Stands in for the engine: every request emits the token ids of a fixed completion text, one per step."""
+
+    def __init__(self, tok, text):
+        import types
+        from stkernel_b200.runtime.metrics import Metrics
+        self.tok, self.script = tok, tok.encode(text) + [tok.eos_token_id]
+        self.cfg = types.SimpleNamespace(sched=types.SimpleNamespace(max_model_len=4096))
+        self.metrics = Metrics()
+        import torch
+        self.device = torch.device("cpu")
+        self.requests, self._next, self._live = {}, 0, []
+
+    def add_request(self, prompt, params):
+        import types
+        rid = self._next
+        self._next += 1
+        self.requests[rid] = types.SimpleNamespace(req_id=rid, prompt=prompt, params=params, output=[], finished=False, finish_reason=None)
+        self._live.append(rid)
+        return rid
+
+    def has_work(self):
+        return bool(self._live)
+
+    def step(self):
+        out = []
+        for rid in list(self._live):
+            r = self.requests[rid]
+            tokn = self.script[len(r.output)]
+            r.output.append(tokn)
+            out.append((rid, tokn))
+            if tokn == self.tok.eos_token_id or len(r.output) >= r.params.max_tokens:
+                r.finished, r.finish_reason = True, "stop" if tokn == self.tok.eos_token_id else "length"
+                self._live.remove(rid)
+        return out
+
+    def abort(self, rid):
+        r = self.requests.get(rid)
+        if r is None or r.finished:
+            return False
+        r.finished, r.finish_reason = True, "abort"
+        self._live.remove(rid)
+        return True
+
+    def release(self, rid):
+        self.requests.pop(rid, None)
+
+
+TOOL_COMPLETION = ('I should look it up.' + E.THINK_CLOSE + 'Let me check.' +
+                   E.dsml_tool_calls([{"function": {"name": "get_weather", "arguments": json.dumps({"city": "서울", "days": 2})}}]))
+
+
+@pytest.fixture()
+def tool_client():
+    from fastapi.testclient import TestClient
+    from stkernel_b200.serve.api_server import create_app
+    tok = ChatTokenizer(ByteTokenizer(1024))
+    with TestClient(create_app(ScriptedEngine(tok, TOOL_COMPLETION), tok, "scripted")) as c:
+        yield c
+
+
+def test_chat_with_tools_nonstream(tool_client):
+    body = {"messages": [{"role": "user", "content": "weather?"}], "tools": TOOLS, "max_tokens": 2000,
+            "chat_template_kwargs": {"thinking": True}}
+    r = tool_client.post("/v1/chat/completions", json=body).json()
+    ch = r["choices"][0]
+    assert ch["finish_reason"] == "tool_calls"
+    m = ch["message"]
+    assert m["reasoning_content"] == "I should look it up." and m["content"] == "Let me check."
+    call = m["tool_calls"][0]
+    assert call["function"]["name"] == "get_weather" and json.loads(call["function"]["arguments"]) == {"city": "서울", "days": 2}
+    # without thinking the same bytes are content up to the block (the </think> tag stays literal text)
+    r2 = tool_client.post("/v1/chat/completions", json={**body, "chat_template_kwargs": {}}).json()
+    assert "reasoning_content" not in r2["choices"][0]["message"] and r2["choices"][0]["finish_reason"] == "tool_calls"
+
+
+def test_chat_with_tools_stream_deltas(tool_client):
+    body = {"messages": [{"role": "user", "content": "weather?"}], "tools": TOOLS, "max_tokens": 2000, "stream": True,
+            "chat_template_kwargs": {"thinking": True}, "stream_options": {"include_usage": True}}
+    with tool_client.stream("POST", "/v1/chat/completions", json=body) as resp:
+        lines = _sse(resp)
+    chunks = [json.loads(x) for x in lines[:-1]]
+    reasoning = "".join(c["choices"][0]["delta"].get("reasoning_content", "") for c in chunks if c["choices"])
+    content = "".join(c["choices"][0]["delta"].get("content", "") for c in chunks if c["choices"])
+    assert reasoning == "I should look it up." and content == "Let me check."
+    name, args, ids = None, "", set()
+    for c in chunks:
+        for ch in c["choices"]:
+            for t in ch["delta"].get("tool_calls", []):
+                assert t["index"] == 0 and None not in t.values() and None not in t["function"].values()
+                if "id" in t:
+                    ids.add(t["id"])
+                    name = t["function"]["name"]
+                args += t["function"].get("arguments", "")
+    assert name == "get_weather" and len(ids) == 1 and json.loads(args) == {"city": "서울", "days": 2}
+    finals = [c["choices"][0]["finish_reason"] for c in chunks if c["choices"] and c["choices"][0]["finish_reason"]]
+    assert finals == ["tool_calls"] and chunks[-1]["usage"]["completion_tokens"] > 0
+
+
+def test_anthropic_tool_use_blocks(tool_client):
+    body = {"model": "scripted", "max_tokens": 2000, "thinking": {"type": "enabled"},
+            "tools": [{"name": "get_weather", "description": "w", "input_schema": TOOLS[0]["function"]["parameters"]}],
+            "messages": [{"role": "user", "content": "weather?"},
+                         {"role": "assistant", "content": [{"type": "tool_use", "id": "toolu_1", "name": "get_weather", "input": {"city": "x"}}]},
+                         {"role": "user", "content": [{"type": "tool_result", "tool_use_id": "toolu_1", "content": "sunny"},
+                                                      {"type": "text", "text": "and Seoul?"}]}]}
+    r = tool_client.post("/v1/messages", json=body).json()
+    kinds = [b["type"] for b in r["content"]]
+    assert kinds == ["thinking", "text", "tool_use"] and r["stop_reason"] == "tool_use"
+    assert r["content"][2]["input"] == {"city": "서울", "days": 2} and r["content"][2]["id"].startswith("toolu_")
+    with tool_client.stream("POST", "/v1/messages", json={**body, "stream": True}) as resp:
+        events = [json.loads(x) for x in _sse(resp)]
+    starts = [e["content_block"]["type"] for e in events if e["type"] == "content_block_start"]
+    assert starts == ["thinking", "text", "tool_use"]
+    partial = "".join(e["delta"]["partial_json"] for e in events if e["type"] == "content_block_delta" and e["delta"]["type"] == "input_json_delta")
+    assert json.loads(partial) == {"city": "서울", "days": 2}
+    assert [e["delta"]["stop_reason"] for e in events if e["type"] == "message_delta"] == ["tool_use"]
+
+
+def test_stop_string_ends_stream_early(tool_client):
+    body = {"messages": [{"role": "user", "content": "x"}], "max_tokens": 2000, "stop": ["check"], "chat_template_kwargs": {"thinking": True}}
+    r = tool_client.post("/v1/chat/completions", json=body).json()
+    assert r["choices"][0]["message"]["content"] == "Let me " and r["choices"][0]["finish_reason"] == "stop"
