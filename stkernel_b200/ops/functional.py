@@ -148,7 +148,9 @@ def linear(x, lw: LinearWeight, out: Optional[torch.Tensor] = None, out_dtype=BF
         return y
     if out is None:
         out = torch.empty(t, n, dtype=out_dtype, device=dev)
-    if xa is None and t <= SKINNY_MAX_T and ar_ctx is None and x.dtype == BF16 and k % 16 == 0 and k <= 16384:
+    # a lane holds at most 32 16-byte chunks of a weight row: K <= 16384 for fp8, K <= 8192 for bf16
+    if (xa is None and t <= SKINNY_MAX_T and ar_ctx is None and x.dtype == BF16 and k % 16 == 0
+            and k <= (16384 if lw.is_fp8 else 8192)):
         # one to four tokens: weight-streaming kernel, activations unquantised
         _lib.call("stk_skinny_linear", lw.w, lw.w.stride(0), 1 if lw.is_fp8 else 0, lw.scale,
                   lw.scale.stride(0) if lw.is_fp8 else 0, x, x.stride(0), out, out.stride(0), t, n, k,
