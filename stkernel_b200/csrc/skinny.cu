@@ -12,7 +12,7 @@
 
 namespace stk {
 
-constexpr int kSkinnyMaxT = 4;
+constexpr int kSkinnyMaxT = 8;
 
 // x: [T, K] bf16 -> xs: half, permuted: chunk c = lane + 32*k holds values [16c, 16c+16) as two uint4
 // at index ((t * kIters + k) * 2 + i) * 32 + lane.
@@ -21,7 +21,7 @@ constexpr int kSkinnyMaxT = 4;
 // 28672: the packed fp16 partial sums of the fp8 path cannot overflow.
 template <int T, bool kPrescale>
 __device__ __forceinline__ void skinny_fill_x(__half* xs, const __nv_bfloat16* x, long long ldx, int K, int iters,
-                                              float* xscale, float* red) {
+                                              float* xscale, float* red, int t_valid) {
   // eight consecutive values = one 16-byte load, one conversion, one 16-byte store
   uint4* xs4 = reinterpret_cast<uint4*>(xs);
   const int k8n = K >> 3;
@@ -33,7 +33,9 @@ __device__ __forceinline__ void skinny_fill_x(__half* xs, const __nv_bfloat16* x
 #pragma unroll
     for (int t = 0; t < T; ++t) {
       float amax = 0.f;
-      if (((reinterpret_cast<uintptr_t>(x) & 3) == 0) && ((ldx & 1) == 0)) {
+      if (t >= t_valid) {
+        // a template instance may be wider than the batch: the surplus rows are zeros
+      } else if (((reinterpret_cast<uintptr_t>(x) & 3) == 0) && ((ldx & 1) == 0)) {
         for (int k2 = threadIdx.x; k2 < (K >> 1); k2 += blockDim.x) {
           const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(x + t * ldx + 2 * k2);
           amax = fmaxf(amax, fmaxf(fabsf(__low2float(v)), fabsf(__high2float(v))));
@@ -54,7 +56,10 @@ __device__ __forceinline__ void skinny_fill_x(__half* xs, const __nv_bfloat16* x
     for (int k8 = threadIdx.x; k8 < k8n; k8 += blockDim.x) {
       const __nv_bfloat16* src = x + t * ldx + k8 * 8;
       __nv_bfloat162 b[4];
-      if (aligned) {
+      if (t >= t_valid) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) b[j] = __floats2bfloat162_rn(0.f, 0.f);
+      } else if (aligned) {
         const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
         b[0] = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
         b[1] = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
@@ -86,7 +91,7 @@ template <int T, bool kFp8, int ITERS, bool kSwiglu>
 __global__ void __launch_bounds__(256)
 skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const float* __restrict__ w_scale,
                      int w_scale_ld, const __nv_bfloat16* __restrict__ x, long long ldx, void* __restrict__ out,
-                     long long ldo, int N, int K, int out_fp32, int rows_per_warp, int group_rows, float limit) {
+                     long long ldo, int N, int K, int out_fp32, int rows_per_warp, int group_rows, float limit, int t_valid) {
   extern __shared__ uint4 xs4[];
   constexpr int kVals = kFp8 ? 16 : 8;                  // values per 16-byte weight chunk
   const int n_chunks = K / kVals;
@@ -95,7 +100,7 @@ skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const f
   const int grp = group_rows > 0 ? (blockIdx.x * 8 * rows_per_warp) / group_rows : 0;
   __shared__ float s_xscale[kSkinnyMaxT];
   __shared__ float s_red[32];
-  skinny_fill_x<T, kFp8>(reinterpret_cast<__half*>(xs4), x + static_cast<long long>(grp) * K, ldx, K, iters16, s_xscale, s_red);
+  skinny_fill_x<T, kFp8>(reinterpret_cast<__half*>(xs4), x + static_cast<long long>(grp) * K, ldx, K, iters16, s_xscale, s_red, t_valid);
   __syncthreads();
   float xsc[T];
 #pragma unroll
@@ -195,7 +200,7 @@ skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const f
         }
         v = g / (1.f + __expf(-g)) * u;
       }
-      if (lane == 0) {
+      if (lane == 0 && t < t_valid) {
         if (out_fp32) reinterpret_cast<float*>(out)[t * ldo + n] = v;
         else reinterpret_cast<__nv_bfloat16*>(out)[t * ldo + n] = __float2bfloat16(v);
       }
@@ -216,7 +221,9 @@ STK_API int stk_skinny_linear(const void* W, long long ldw, int is_fp8, const fl
   const long long ldw_bytes = ldw * (is_fp8 ? 1 : 2);
   if (ldw_bytes % 16 || (reinterpret_cast<uintptr_t>(W) & 15)) return -2;
   const int iters16 = ((K / 16) + 31) / 32;
-  const size_t smem = static_cast<size_t>(T) * iters16 * 2 * 32 * 16;
+  const int t_inst = T <= 4 ? T : (T <= 6 ? 6 : 8);                // template instance that serves this batch
+  const size_t smem = static_cast<size_t>(t_inst) * iters16 * 2 * 32 * 16;
+  if (smem > 160 * 1024) return -6;
   // about four CTAs per SM; each warp takes `rpw` consecutive rows
   int rpw = 1;
   while ((N + 8 * rpw - 1) / (8 * rpw) > sm_count * 3 && rpw < 16) rpw *= 2;
@@ -239,7 +246,7 @@ STK_API int stk_skinny_linear(const void* W, long long ldw, int is_fp8, const fl
     }                                                                                                                  \
     skinny_linear_kernel<T_, F_, I_, S_><<<grid, 256, smem, st>>>((const uint8_t*)W, ldw_bytes, w_scale, w_scale_ld,       \
                                                               (const __nv_bfloat16*)x, ldx, out, ldo, N, K, out_fp32,  \
-                                                              rpw, group_rows, limit);                                 \
+                                                              rpw, group_rows, limit, T);                              \
   }
 #define STK_SK2(T_, F_)                                                                                 \
   {                                                                                                     \
@@ -257,9 +264,11 @@ STK_API int stk_skinny_linear(const void* W, long long ldw, int is_fp8, const fl
     }                                                                                                   \
   }
   if (is_fp8) {
-    switch (T) { case 1: STK_SK2(1, true) break; case 2: STK_SK2(2, true) break; case 3: STK_SK2(3, true) break; default: STK_SK2(4, true) }
+    switch (T) { case 1: STK_SK2(1, true) break; case 2: STK_SK2(2, true) break; case 3: STK_SK2(3, true) break; case 4: STK_SK2(4, true) break;
+                 case 5: case 6: STK_SK2(6, true) break; default: STK_SK2(8, true) }
   } else {
-    switch (T) { case 1: STK_SK2(1, false) break; case 2: STK_SK2(2, false) break; case 3: STK_SK2(3, false) break; default: STK_SK2(4, false) }
+    switch (T) { case 1: STK_SK2(1, false) break; case 2: STK_SK2(2, false) break; case 3: STK_SK2(3, false) break; case 4: STK_SK2(4, false) break;
+                 case 5: case 6: STK_SK2(6, false) break; default: STK_SK2(8, false) }
   }
 #undef STK_SK2
 #undef STK_SK3

@@ -78,8 +78,13 @@ class QuantAct:
     scale: torch.Tensor
 
 
-SKINNY_MAX_T = 4
+SKINNY_MAX_T = 8
 MHC_CLUSTER_MAX_T = 16
+
+
+def _skinny_rows(t: int) -> int:
+    """Rows of the kernel instance that serves a batch of t tokens (its activation tile lives in shared memory)."""
+    return t if t <= 4 else (6 if t <= 6 else 8)
 
 
 def wants_quant_act(t: int, device) -> bool:
@@ -150,7 +155,7 @@ def linear(x, lw: LinearWeight, out: Optional[torch.Tensor] = None, out_dtype=BF
         out = torch.empty(t, n, dtype=out_dtype, device=dev)
     # a lane holds at most 32 16-byte chunks of a weight row: K <= 16384 for fp8, K <= 8192 for bf16
     if (xa is None and t <= SKINNY_MAX_T and ar_ctx is None and x.dtype == BF16 and k % 16 == 0
-            and k <= (16384 if lw.is_fp8 else 8192)):
+            and k <= (16384 if lw.is_fp8 else 8192) and _skinny_rows(t) * k * 2 <= 160 * 1024):
         # one to four tokens: weight-streaming kernel, activations unquantised
         _lib.call("stk_skinny_linear", lw.w, lw.w.stride(0), 1 if lw.is_fp8 else 0, lw.scale,
                   lw.scale.stride(0) if lw.is_fp8 else 0, x, x.stride(0), out, out.stride(0), t, n, k,
@@ -182,7 +187,7 @@ def linear_swiglu(x: torch.Tensor, lw13: LinearWeight, limit: float) -> Optional
     (decode-sized batches on a GPU); returns None when that kernel does not apply."""
     t, k = x.shape
     n2 = lw13.w.shape[0]
-    if not x.is_cuda or t > SKINNY_MAX_T or x.dtype != BF16 or k % 16 or k > 8192 or n2 % 2:
+    if not x.is_cuda or t > SKINNY_MAX_T or x.dtype != BF16 or k % 16 or k > 8192 or n2 % 2 or _skinny_rows(t) * k * 2 > 160 * 1024:
         return None
     i = n2 // 2
     if lw13.is_fp8 and i % 128:
@@ -280,14 +285,15 @@ def mhc_pre(residual: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale:
         return res + (quant_act(y),) if quant else res
     dev = residual.device
     n_mix = (2 + hc) * hc
-    if t <= MHC_CLUSTER_MAX_T and not quant and n_mix in (24, 8) and h <= 16384:
-        # decode-sized batch: one launch, an 8-CTA cluster per token (DSMEM reductions)
+    if t <= MHC_CLUSTER_MAX_T and n_mix in (24, 8) and h <= 16384:
+        # decode-sized batch: one launch, an 8-CTA cluster per token (DSMEM reductions); a quantised copy of the
+        # few output rows, when the consumer wants one, is a second tiny launch
         y = torch.empty(t, h, dtype=BF16, device=dev)
         post = torch.empty(t, hc, dtype=F32, device=dev)
         comb = torch.empty(t, hc * hc, dtype=F32, device=dev)
         _lib.call("stk_mhc_cluster", residual, fn, base, scale, norm_w, post, comb, y, t, h, hc, n_mix, rms_eps, hc_eps,
                   iters, 2.0, 0, _lib.stream())
-        return y, post, comb
+        return (y, post, comb, quant_act(y, tag + ".q")) if quant else (y, post, comb)
     splits = _lib.query("stk_mhc_pick_splits", t, hc * h)
     partial = scratch("mhc.partial", (splits * t * (n_mix + 1),), F32, dev)
     _lib.call("stk_mhc_dots", residual, fn, partial, t, h, hc, n_mix, splits, _lib.stream())

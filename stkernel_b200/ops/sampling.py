@@ -72,3 +72,63 @@ def markov_topk_bias(base: torch.Tensor, w2: torch.Tensor, embed: torch.Tensor, 
     _lib.call("stk_markov_topk_bias", base, base.stride(0), 1 if base.dtype == BF16 else 0, w2, embed, embed.stride(0),
               out, v, b, v, w2.shape[1], topk, _lib.stream())
     return out
+
+
+def topk_candidates(logits: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """logits [rows, V] -> (vocab ids int32 [rows, k], values fp32 [rows, k]) of the k largest entries per row, in no
+    particular order.  Two levels of the register-resident row top-k: the vocabulary is cut into segments of at most
+    16384 entries, each segment keeps its own top-k, and a second pass picks k among those candidates."""
+    from . import attention as A
+    rows, v = logits.shape
+    lf = logits.float()
+    if not logits.is_cuda:
+        val, idx = torch.topk(lf, k, dim=-1)
+        return idx.to(torch.int32), val
+    segs = max(1, -(-v // 16384))
+    seg = -(-v // segs)
+    seg = (seg + 3) // 4 * 4
+    if seg * segs != v:
+        lf = torch.nn.functional.pad(lf, (0, seg * segs - v), value=float("-inf"))
+    flat = lf.view(rows * segs, seg)
+    n_valid = torch.full((rows * segs,), seg, dtype=torch.int32, device=lf.device)
+    if seg * segs != v:
+        n_valid.view(rows, segs)[:, -1] = v - seg * (segs - 1)
+    kk = min(k, seg)
+    local = A.topk_rows(flat, n_valid, kk)                                   # [rows*segs, kk], -1 padded
+    ok = local >= 0
+    vals = torch.where(ok, flat.gather(1, local.clamp(min=0).long()), torch.full_like(local, float("-inf"), dtype=F32))
+    gidx = torch.where(ok, local + (torch.arange(rows * segs, device=lf.device, dtype=torch.int32) % segs)[:, None] * seg,
+                       torch.full_like(local, -1))
+    if segs == 1:
+        return gidx.contiguous(), vals.contiguous()
+    cand_v = vals.view(rows, segs * kk).contiguous()
+    cand_i = gidx.view(rows, segs * kk)
+    n2 = torch.full((rows,), segs * kk, dtype=torch.int32, device=lf.device)
+    sel = A.topk_rows(cand_v, n2, k).clamp(min=0).long()
+    return cand_i.gather(1, sel).contiguous(), cand_v.gather(1, sel).contiguous()
+
+
+def markov_chain(cand_idx: torch.Tensor, cand_val: torch.Tensor, anchors: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
+                 temperature: torch.Tensor, seed: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+    """Sequential Markov sampling over fixed candidate sets.  cand_idx int32 / cand_val fp32 [B, N, K]; anchors [B] the
+    token before the block; position i is drawn with the noise key (seed, pos + i).  Returns tokens int64 [B, N]."""
+    b, n, k = cand_idx.shape
+    if not cand_idx.is_cuda:
+        out = torch.empty(b, n, dtype=torch.int64)
+        prev = anchors.clone()
+        v = w1.shape[0]
+        for i in range(n):
+            e = w1[prev].float()
+            idx = cand_idx[:, i].long()
+            ok = idx >= 0
+            bias = torch.einsum("bkr,br->bk", w2.float()[idx.clamp(min=0)], e)
+            full = torch.full((b, v), float("-inf"))
+            full.scatter_(1, idx.clamp(min=0), torch.where(ok, cand_val[:, i] + bias, torch.full_like(bias, float("-inf"))))
+            tok, _ = R.gumbel_sample(full, temperature, seed, pos + i)
+            out[:, i] = tok
+            prev = tok
+        return out
+    out = torch.empty(b, n, dtype=torch.int64, device=cand_idx.device)
+    _lib.call("stk_markov_chain", cand_idx.contiguous(), cand_val.contiguous(), anchors.contiguous(), w1, w2, temperature,
+              seed, pos.contiguous(), out, b, n, k, w1.shape[1], w1.shape[0], _lib.stream())
+    return out

@@ -256,6 +256,13 @@ class DSparkDrafter:
         meta = self.block_meta(anchors, anchor_pos, rows)
         X = self.model.forward_hidden(meta)
         base = self.model.compute_logits(self.model.head_hidden(X)).view(b, n, -1)
+        if self.topk > 0 and not want_logits:
+            # the candidate sets (top-k of the base logits) do not depend on the sampled tokens: select them for all
+            # positions at once, then run the dependent part -- W1 row, gathered W2 rows, noisy arg-max -- in one kernel
+            ci, cv = S.topk_candidates(base.reshape(b * n, -1), self.topk)
+            toks = S.markov_chain(ci.view(b, n, -1), cv.view(b, n, -1), anchors, self.w.markov.w1, self.w.markov.w2,
+                                  temperature, seed, anchor_pos.to(torch.int64) + 1)
+            return toks, None
         out = torch.empty(b, n, dtype=torch.int64, device=self.device)
         rec = torch.empty(b, n, base.shape[-1], dtype=F32, device=self.device) if want_logits else None
         prev = anchors

@@ -466,3 +466,33 @@ def test_moe_grouped_gemm_nvfp4(T, E, k):
     finally:
         M.USE_GROUPED_GEMM = True
     assert rel_err(out, out2) < 1.5e-2
+
+
+def test_topk_candidates_and_markov_chain_match_cpu():
+    """The drafter's sampling path: two-level candidate selection over the full vocabulary and the one-launch
+    sequential Markov sampling against their CPU statements."""
+    torch.manual_seed(21)
+    B, N, V, Rk, K = 3, 5, 129280, 256, 512
+    base = (torch.randn(B * N, V, device=dev()) * 3).to(BF16)
+    ci, cv = S.topk_candidates(base, K)
+    ri, rv = S.topk_candidates(base.cpu(), K)
+    assert ci.shape == (B * N, K) and int(ci.min()) >= 0 and int(ci.max()) < V
+    # same value multiset (ties at the threshold may pick different ids of equal value)
+    assert torch.equal(cv.sort(-1).values.cpu(), rv.sort(-1).values)
+    assert torch.equal(base.float().gather(1, ci.long()), cv)
+    w1 = (torch.randn(V, Rk, device=dev()) * 0.3).to(BF16)
+    w2 = (torch.randn(V, Rk, device=dev()) * 0.3).to(BF16)
+    anchors = torch.randint(0, V, (B,), device=dev())
+    temp = torch.tensor([0.6, 0.0, 1.0], device=dev())
+    seed = torch.tensor([11, 2 ** 41 + 5, 3], device=dev(), dtype=torch.int64)
+    pos = torch.tensor([100, 32768, 7], device=dev(), dtype=torch.int64)
+    got = S.markov_chain(ci.view(B, N, K), cv.view(B, N, K), anchors, w1, w2, temp, seed, pos)
+    ref = S.markov_chain(ci.view(B, N, K).cpu(), cv.view(B, N, K).cpu(), anchors.cpu(), w1.cpu(), w2.cpu(), temp.cpu(),
+                         seed.cpu(), pos.cpu())
+    assert got.shape == (B, N)
+    assert torch.equal(got[:, 0].cpu(), ref[:, 0])                       # first position: same inputs on both sides
+    assert (got.cpu() == ref).float().mean().item() >= 0.8              # later ones depend on earlier draws
+    # every drawn token is one of its position's candidates
+    for b in range(B):
+        for i in range(N):
+            assert int(got[b, i]) in set(ci.view(B, N, K)[b, i].tolist())
