@@ -31,7 +31,7 @@ def run(layers: int, ctx: int, conc: int, steps: int, n_spec: int, temperature: 
     n_mtp = 3 if spec else 0
     cfg = flash_config(layers, n_mtp_layers=n_mtp,
                        dspark_target_layer_ids=(layers // 4, layers // 2, layers - 1) if spec else ())
-    sc = SchedulerConfig(max_model_len=ctx + 4096, max_num_seqs=max(conc, 2), max_num_batched_tokens=4096, graph_cap=64)
+    sc = SchedulerConfig(max_model_len=ctx + 4096, max_num_seqs=max(conc, 2), max_num_batched_tokens=4096, graph_cap=256)
     ec = EngineConfig(model=cfg, sched=sc, spec=SpecConfig(method="dspark" if spec else "none", num_speculative_tokens=n_spec,
                                                             markov_topk=512, temperature=temperature)).validate()
     src = RandomSource(0)

@@ -215,19 +215,21 @@ markov_topk_bias_kernel(const T* __restrict__ base, long long ld, const __nv_bfl
 // For i = 0..N-1:  e = W1[prev];  logit_c = cand_val[i, c] + W2[cand_idx[i, c]] . e;
 //                  token_i = argmax_c(logit_c / T + g(seed, pos + i, vocab id))   (T <= 0: greedy; ties -> lowest id)
 //                  prev = token_i.
-// One CTA per request; a warp takes a candidate at a time (coalesced 16-byte reads of its W2 row).  This is the
-// drafter's whole sampling loop: the proposals depend on each other, the candidate sets do not.
-__global__ void __launch_bounds__(256)
+// One CTA of 1024 threads per request; two threads per candidate, each streaming half of its W2 row with eight
+// 16-byte loads in flight, so a position costs about two memory round trips.  This is the drafter's whole sampling loop: the proposals depend on each other, the candidate sets do not.
+__global__ void __launch_bounds__(1024)
 markov_chain_kernel(const int* __restrict__ cand_idx, const float* __restrict__ cand_val, const int64_t* __restrict__ anchors,
                     const __nv_bfloat16* __restrict__ w1, const __nv_bfloat16* __restrict__ w2,
                     const float* __restrict__ temperature, const int64_t* __restrict__ seed, const int64_t* __restrict__ pos,
                     int64_t* __restrict__ out, int N, int K, int R, int V) {
   extern __shared__ float emb[];                 // R floats
-  __shared__ float sv[8];
-  __shared__ int si[8];
+  __shared__ float sv[32];
+  __shared__ int si[32];
   __shared__ int s_prev;
   const int b = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int half = threadIdx.x & 1;              // two threads per candidate, half a W2 row each
+  const int hv = R / 16;                         // 16-byte vectors per half row
   const float temp = temperature[b];
   const bool greedy = temp <= 0.f;
   const float inv_t = greedy ? 1.f : 1.f / temp;
@@ -245,31 +247,51 @@ markov_chain_kernel(const int* __restrict__ cand_idx, const float* __restrict__ 
     const float* cv = cand_val + (static_cast<long long>(b) * N + i) * K;
     float best = -INFINITY;
     int best_i = 0x7fffffff;
-    for (int c = warp; c < K; c += 8) {
-      const int v = ci[c];
-      if (v < 0 || v >= V) continue;             // warp-uniform
-      const uint4* row = reinterpret_cast<const uint4*>(w2 + static_cast<long long>(v) * R);
+    for (int c0 = 0; c0 < K; c0 += 512) {
+      const int c = c0 + (threadIdx.x >> 1);
+      const int v = c < K ? ci[c] : -1;
+      const bool valid = v >= 0 && v < V;
       float d = 0.f;
-      for (int j = lane; j < R / 8; j += 32) {
-        const uint4 q = __ldg(row + j);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+      if (valid) {
+        const uint4* row = reinterpret_cast<const uint4*>(w2 + static_cast<long long>(v) * R) + half * hv;
+        const float* e = emb + half * (R / 2);
+        for (int j0 = 0; j0 < hv; j0 += 8) {
+          uint4 q[8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const float2 f = __bfloat1622float2(h[u]);
-          d = fmaf(f.x, emb[8 * j + 2 * u], fmaf(f.y, emb[8 * j + 2 * u + 1], d));
+          for (int j = 0; j < 8; ++j)
+            if (j0 + j < hv) q[j] = __ldg(row + j0 + j);        // eight loads in flight before the first multiply
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (j0 + j < hv) {
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q[j]);
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const float2 f = __bfloat1622float2(h[u]);
+                d = fmaf(f.x, e[8 * (j0 + j) + 2 * u], fmaf(f.y, e[8 * (j0 + j) + 2 * u + 1], d));
+              }
+            }
+          }
         }
       }
-      d = warp_sum(d);
-      const float l = (cv[c] + d) * inv_t;
-      const float x = greedy ? l : l + gumbel_from_key(key, static_cast<uint32_t>(v));
-      if (x > best || (x == best && v < best_i)) { best = x; best_i = v; }
+      d += __shfl_xor_sync(0xffffffffu, d, 1);
+      if (valid && half == 0) {
+        const float l = (cv[c] + d) * inv_t;
+        const float x = greedy ? l : l + gumbel_from_key(key, static_cast<uint32_t>(v));
+        if (x > best || (x == best && v < best_i)) { best = x; best_i = v; }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (ob > best || (ob == best && oi < best_i)) { best = ob; best_i = oi; }
     }
     if (lane == 0) { sv[warp] = best; si[warp] = best_i; }
     __syncthreads();
     if (threadIdx.x == 0) {
       float bb = sv[0];
       int bi = si[0];
-      for (int w = 1; w < 8; ++w)
+      for (int w = 1; w < 32; ++w)
         if (sv[w] > bb || (sv[w] == bb && si[w] < bi)) { bb = sv[w]; bi = si[w]; }
       if (bi == 0x7fffffff) bi = 0;              // no candidate at all: emit token 0 rather than an invalid id
       s_prev = bi;
@@ -329,8 +351,8 @@ STK_API int stk_markov_chain(const int* cand_idx, const float* cand_val, const i
                              const void* w2, const float* temperature, const int64_t* seed, const int64_t* pos,
                              int64_t* out, int B, int N, int K, int R, int V, void* stream) {
   if (B <= 0 || N <= 0) return 0;
-  if (R % 8 || K <= 0) return -1;
-  markov_chain_kernel<<<B, 256, R * sizeof(float), (cudaStream_t)stream>>>(
+  if (R % 16 || K <= 0) return -1;
+  markov_chain_kernel<<<B, 1024, R * sizeof(float), (cudaStream_t)stream>>>(
       cand_idx, cand_val, anchors, (const __nv_bfloat16*)w1, (const __nv_bfloat16*)w2, temperature, seed, pos, out, N, K, R, V);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -78,7 +78,7 @@ class QuantAct:
     scale: torch.Tensor
 
 
-SKINNY_MAX_T = 8
+SKINNY_MAX_T = 4          # above four tokens the tcgen05 GEMM with split-K is faster (measured at six)
 MHC_CLUSTER_MAX_T = 16
 
 

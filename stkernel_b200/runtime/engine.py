@@ -237,6 +237,12 @@ class Engine:
                                sc.max_num_seqs * (1 + n_spec))
         self.drafter = None
         if spec_on:
+            pin = self.device.type == "cuda"
+            self.h_spec_host = torch.zeros(sc.max_num_seqs, 5 + n_spec, dtype=torch.int64, pin_memory=pin)
+            self.h_spec_temp = torch.zeros(sc.max_num_seqs, dtype=torch.float32, pin_memory=pin)
+            self.d_spec_host = torch.zeros(sc.max_num_seqs, 5 + n_spec, dtype=torch.int64, device=self.device)
+            self.d_spec_temp = torch.zeros(sc.max_num_seqs, dtype=torch.float32, device=self.device)
+            self._spec_cols = torch.arange(n_spec + 1, device=self.device)
             from ..spec.dspark import DSparkDrafter
             self.model.aux_layers = tuple(cfg.model.dspark_target_layer_ids)
             self.drafter = DSparkDrafter(cfg.model, cfg.spec, draft_weights, self.kv, comm, tp_rank, cfg.parallel.tp_size,
@@ -244,7 +250,7 @@ class Engine:
         self.metrics = Metrics()
         self._next_id = 0
         self.requests: Dict[int, Request] = {}
-        self._graphs: Dict[Tuple[int, int], "DecodeGraph"] = {}
+        self._graphs: Dict[tuple, object] = {}
         self.use_graphs = self.device.type == "cuda" and sc.graph_cap > 0
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
@@ -439,6 +445,29 @@ class Engine:
             return True
         return False
 
+    def _spec_device(self, t: int, n_req: int, ns: int, nb: int, max_comp_rows: int) -> Optional[torch.Tensor]:
+        """Device work of a speculative step over the staged inputs: target forward, context-KV insert, coupled
+        verify, next draft block.  Returns [n_acc (nb) | verifier tokens (nb x (1+N)) | new drafts (nb x N)] int64.
+        Reads fixed-address buffers only, so a pure-decode step can be captured into a CUDA graph."""
+        n_spec = self.drafter.n
+        meta = self._build_meta(t, n_req, max_comp_rows)
+        X = self.model.forward_hidden(meta)
+        aux = self.model.aux_out[0] if len(self.model.aux_out) == 1 else torch.cat(self.model.aux_out, -1)
+        self.drafter.insert_context(aux, meta.positions, meta.swa_slot_mapping)
+        if nb == 0:
+            return None
+        b = self.buf
+        logits = self.model.compute_logits(self.model.head_hidden(X.index_select(0, b.d_logit_rows[:ns])))
+        toks, _ = S.gumbel_argmax(logits, b.d_temp[:ns], b.d_seed[:ns], b.d_pos[:ns])
+        hd, td = self.d_spec_host[:nb], self.d_spec_temp[:nb]
+        idx = (hd[:, 0:1] + self._spec_cols[None, :]).clamp_(max=ns - 1)
+        ver = toks[idx]
+        n_acc, _ = S.coupled_accept(ver, hd[:, 5:].contiguous())
+        anchor = ver.gather(1, n_acc[:, None]).squeeze(1)
+        anchor_pos = hd[:, 1] + n_acc + 1
+        new_drafts, _ = self.drafter.draft(anchor, anchor_pos, hd[:, 2], td, hd[:, 3])
+        return torch.cat([n_acc, ver.reshape(-1), new_drafts.reshape(-1)])
+
     def _step_spec(self) -> List[Tuple[int, int]]:
         """Target step over [last token, drafts...] rows + prefill chunks, coupled verify, context-KV
         insert for the draft layers, next draft block; one device->host read for all of it."""
@@ -449,21 +478,13 @@ class Engine:
         t, n_req, ns = self._stage(seqs)
         self._upload(t, n_req, ns)
         max_end = max(s.start + s.n for s in seqs)
-        meta = self._build_meta(t, n_req, max(1, max_end // 4))
-        X = self.model.forward_hidden(meta)
-        aux = self.model.aux_out[0] if len(self.model.aux_out) == 1 else torch.cat(self.model.aux_out, -1)
-        self.drafter.insert_context(aux, meta.positions, meta.swa_slot_mapping)
+        max_comp_rows = max(1, max_end // 4)
         now = time.time()
         out: List[Tuple[int, int]] = []
         samp = [s for s in seqs if s.samples]
-        if samp:
-            b = self.buf
-            dev = self.device
-            logits = self.model.compute_logits(self.model.head_hidden(X.index_select(0, b.d_logit_rows[:ns])))
-            toks, _ = S.gumbel_argmax(logits, b.d_temp[:ns], b.d_seed[:ns], b.d_pos[:ns])
-            nb = len(samp)
-            host = torch.zeros(nb, 5 + n_spec, dtype=torch.int64)
-            temps = torch.zeros(nb, dtype=torch.float32)
+        nb = len(samp)
+        if nb:
+            host, temps = self.h_spec_host, self.h_spec_temp
             row0 = 0
             for i, s in enumerate(samp):
                 k = s.n_sample - 1
@@ -473,17 +494,22 @@ class Engine:
                     host[i, 5:5 + k] = torch.tensor(s.req.drafts[:k], dtype=torch.int64)
                 temps[i] = s.req.params.temperature
                 row0 += s.n_sample
-            hd = host.to(dev, non_blocking=True)
-            td = temps.to(dev, non_blocking=True)
-            idx = (hd[:, 0:1] + torch.arange(n_spec + 1, device=dev)[None, :]).clamp_(max=ns - 1)
-            ver = toks[idx]
-            n_acc, _ = S.coupled_accept(ver, hd[:, 5:].contiguous())
-            anchor = ver.gather(1, n_acc[:, None]).squeeze(1)
-            anchor_pos = hd[:, 1] + n_acc + 1
-            new_drafts, _ = self.drafter.draft(anchor, anchor_pos, hd[:, 2], td, hd[:, 3])
-            packed = torch.cat([n_acc, ver.reshape(-1), new_drafts.reshape(-1)])
+            self.d_spec_host[:nb].copy_(host[:nb], non_blocking=True)
+            self.d_spec_temp[:nb].copy_(temps[:nb], non_blocking=True)
+        full = nb == len(seqs) and all(s.n_sample == 1 + n_spec for s in seqs)
+        if self.use_graphs and full and t <= self.cfg.sched.graph_cap:
+            rows_bucket = ((max_comp_rows + 64) // 2048 + 1) * 2048
+            key = ("spec", n_req, rows_bucket)
+            g = self._graphs.get(key)
+            if g is None:
+                g = SpecGraph(self, t, n_req, ns, nb, rows_bucket)
+                self._graphs[key] = g
+            packed = g.replay()
+        else:
+            packed = self._spec_device(t, n_req, ns, nb, max_comp_rows)
+        if nb:
             n_out = packed.numel()
-            if dev.type == "cuda":
+            if self.device.type == "cuda":
                 self.buf.h_out[:n_out].copy_(packed, non_blocking=True)
                 torch.cuda.current_stream().synchronize()
                 res = self.buf.h_out[:n_out].tolist()
@@ -540,6 +566,31 @@ class Engine:
             g = DecodeGraph(self, bucket, rows_bucket)
             self._graphs[key] = g
         return g
+
+
+class SpecGraph:
+    """A captured speculative pure-decode step: every request verifies 1 + N rows and drafts its next block."""
+
+    def __init__(self, eng: "Engine", t: int, n_req: int, ns: int, nb: int, rows_bucket: int):
+        from ..ops import _lib
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                eng._spec_device(t, n_req, ns, nb, rows_bucket)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        before = _lib.launch_count
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.out = eng._spec_device(t, n_req, ns, nb, rows_bucket)
+        self.launches_per_replay = _lib.launch_count - before
+
+    def replay(self) -> torch.Tensor:
+        from ..ops import _lib
+        self.graph.replay()
+        _lib.launch_count += self.launches_per_replay
+        return self.out
 
 
 class DecodeGraph:

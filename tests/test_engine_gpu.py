@@ -102,3 +102,29 @@ def test_dspark_speculative_engine_runs_and_agrees_with_plain_prefix():
     assert [g[0] for g in got] == [r[0] for r in ref]
     m = spec.metrics
     assert m.spec_num_drafts > 0 and m.spec_num_accepted_tokens <= m.spec_num_draft_tokens
+
+
+def test_dspark_step_graph_replay_matches_eager():
+    """The captured speculative step (verify + context insert + draft block + Markov chain) gives the same text
+    as the eager one: same kernels, same inputs."""
+    from stkernel_b200.config import SpecConfig
+    from stkernel_b200.spec.dspark import build_draft_weights
+    cfg = tiny_config(dense_dtype="bf16", kv_cache_dtype="fp8_ds_mla", expert_dtype="nvfp4", n_mtp_layers=2,
+                      dspark_target_layer_ids=(0, 1), dspark_markov_rank=16)
+    w = init_random_weights(cfg, seed=4)
+    tw = build_model_weights(cfg, DictSource(w), "cuda:0")
+    dw = build_draft_weights(cfg, DictSource(w), tw, "cuda:0")
+    torch.manual_seed(1)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,)).tolist() for n in (30, 70)]
+    sp = SamplingParams(temperature=0.8, seed=9, max_tokens=20)
+    outs = []
+    for cap in (0, 64):
+        sc = SchedulerConfig(max_model_len=512, max_num_seqs=4, max_num_batched_tokens=256, graph_cap=cap)
+        ec = EngineConfig(model=cfg, sched=sc, spec=SpecConfig(method="dspark", num_speculative_tokens=3, markov_topk=8)).validate()
+        eng = Engine(ec, tw, "cuda:0", max_context=512, draft_weights=dw)
+        outs.append(eng.generate(prompts, sp))
+        torch.cuda.synchronize()
+        _lib.check_status()
+        if cap:
+            assert any(isinstance(k, tuple) and k[0] == "spec" for k in eng._graphs)
+    assert outs[0] == outs[1]
