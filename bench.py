@@ -27,7 +27,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-BASELINE_DECODE_C1 = 70.7      # tok/s, reference with one-shot all-reduce, 4x GB10
+BASELINE_DECODE_C1 = 70.7      # tok/s at C=1 published by the reference (4x GB10, TP4, one-shot all-reduce, MEASUREMENTS.md:154)
 
 
 def reference_arm(args) -> None:
