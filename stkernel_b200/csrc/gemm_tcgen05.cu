@@ -53,6 +53,11 @@ struct GemmArgs {
   // carries the current epoch.  Token tiles are visited starting with this rank's own shard.
   int gate_enabled;
   int gate_rows;
+  // Token-major mode (fp8, T >= 128): the operands swap roles -- TMEM lanes are tokens, columns are weight rows -- so
+  // the activation scale of a K block is one value per thread and the weight scale one value per tile: the per-block
+  // rescale is a single multiplier per thread instead of one per accumulator column.  T/N/tiles_* then describe the
+  // swapped problem (a.N = tokens, a.T = weight rows); out is still [tokens, ldo].
+  int token_major;
 };
 
 constexpr int kArKind = 3;
@@ -354,6 +359,51 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
         float acc[kColsPerWarp];
 #pragma unroll
         for (int j = 0; j < kColsPerWarp; ++j) acc[j] = 0.f;
+        if (a.token_major) {
+          // lane = token n, columns = weight rows t0 .. t0 + kColsPerWarp of row block tt (BT == 128)
+          for (int kb = kb0; kb < kb1 && ok; ++kb) {
+            const float s = a.w_scale[tt * a.w_scale_ld + kb] *
+                            (n_ok ? a.x_scale[static_cast<long long>(kb) * a.x_scale_ld + n] : 0.f);
+            if (!mbar_wait(&bars->tmem_full[ab], aphase, a.status, 400 + ab)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < kChunksPerWarp; ++c) {
+              uint32_t r[32];
+              tmem_ld_chunk<CW>(tmem_base + ab * BT + col_base + c * CW + (static_cast<uint32_t>(q * 32) << 16), r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < CW; ++j) acc[c * CW + j] = fmaf(__uint_as_float(r[j]), s, acc[c * CW + j]);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->tmem_empty[ab]);
+            if (++ab == 2) { ab = 0; aphase ^= 1; }
+          }
+          if (ok && n_ok) {
+            // a thread owns kColsPerWarp consecutive outputs of its token row
+            const long long o0 = static_cast<long long>(n) * a.ldo + t0;
+            const bool vec = !a.out_fp32 && (a.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.out) & 15) == 0) &&
+                             t0 + kColsPerWarp <= a.T;
+            if (vec) {
+#pragma unroll
+              for (int j = 0; j < kColsPerWarp; j += 8) {
+                uint4 ov;
+                __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) oh[i] = __floats2bfloat162_rn(acc[j + 2 * i], acc[j + 2 * i + 1]);
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.out) + o0 + j) = ov;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < kColsPerWarp; ++j) {
+                if (t0 + j < a.T) {
+                  if (a.out_fp32) reinterpret_cast<float*>(a.out)[o0 + j] = acc[j];
+                  else reinterpret_cast<__nv_bfloat16*>(a.out)[o0 + j] = __float2bfloat16(acc[j]);
+                }
+              }
+            }
+          }
+        } else {
         for (int kb = kb0; kb < kb1 && ok; ++kb) {
           const float sw = a.w_scale[tn * a.w_scale_ld + kb];
           const int gkb = a.group_tiles ? (tn / a.group_tiles) * a.k_blocks : 0;
@@ -384,6 +434,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
         if (ok) {
 #pragma unroll
           for (int j = 0; j < kColsPerWarp; ++j) store(t0 + j, acc[j]);
+        }
         }
       } else {
         if (!mbar_wait(&bars->tmem_full[ab], aphase, a.status, 400 + ab)) { ok = false; break; }
@@ -578,10 +629,33 @@ static int gemm_launch(const void* W, long long ldw, const void* X, long long ld
     return -10;
   if (is_fp8 && (w_scale == nullptr || x_scale == nullptr || (x_scale_ld & 3))) return -11;
   if (splits > 1 && (workspace == nullptr || counters == nullptr)) return -12;
+  if (groups < 1) groups = 1;
+  // fp8 with at least a full tile of tokens: token-major orientation (see GemmArgs::token_major)
+  const bool token_major = is_fp8 && T >= 128 && groups == 1 && ar_ctx == nullptr && gate_ctx == nullptr && splits <= 1 &&
+                           (reinterpret_cast<uintptr_t>(X) & 15) == 0;
+  if (token_major) {
+    CUtensorMap ta, tb;
+    if (make_tmap_2d(&ta, X, 1, T, K, ldx, 128) != 0) return -13;        // lanes: tokens
+    if (make_tmap_2d(&tb, W, 1, N, K, ldw, 128) != 0) return -14;        // columns: weight rows
+    GemmArgs a;
+    memset(&a, 0, sizeof(a));
+    a.T = N; a.N = T;
+    a.k_blocks = (K + 127) / 128;
+    a.splits = 1;
+    a.tiles_n = (T + 127) / 128;
+    a.tiles_t = (N + 127) / 128;
+    a.out = out; a.ldo = ldo; a.out_fp32 = out_fp32;
+    a.w_scale = w_scale; a.w_scale_ld = w_scale_ld;
+    a.x_scale = x_scale; a.x_scale_ld = x_scale_ld;
+    a.status = status;
+    a.token_major = 1;
+    const int units = a.tiles_n * a.tiles_t;
+    const int grid = units < sm_count ? units : sm_count;
+    return launch_gemm<128, true>(ta, tb, a, grid, reinterpret_cast<cudaStream_t>(stream));
+  }
   const int bt = stk_gemm_pick_bt(T, is_fp8);
   CUtensorMap tw, tx;
   if (make_tmap_2d(&tw, W, es, N, K, ldw, 128) != 0) return -13;
-  if (groups < 1) groups = 1;
   if (groups > 1 && ((K * es) % 128 || N % (128 * groups))) return -17;   // groups must split on tile boundaries
   if (make_tmap_2d(&tx, X, es, T, static_cast<long long>(K) * groups, ldx, bt) != 0) return -14;
   GemmArgs a;
@@ -612,6 +686,7 @@ static int gemm_launch(const void* W, long long ldw, const void* X, long long ld
   }
   a.gate_enabled = 0;
   a.gate_rows = 0;
+  a.token_major = 0;
   if (gate_ctx != nullptr) {
     if (ar_ctx != nullptr || gate_rows <= 0 || a.splits != 1) return -19;
     memcpy(&a.ar, gate_ctx, sizeof(a.ar));
