@@ -228,6 +228,33 @@ STK_API int stk_rmsnorm(const void* x0, long long ldx0, const void* w0, void* ou
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
+// out[t * ldo] = sum_k x[t, k]^2 (fp32); one CTA per row.
+__global__ void __launch_bounds__(256)
+row_sumsq_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, float* __restrict__ out, long long ldo, int K) {
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const uint4* row = reinterpret_cast<const uint4*>(x + t * ldx);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
+    const uint4 v = __ldg(row + i);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(h[j]);
+      ss = fmaf(f.x, f.x, fmaf(f.y, f.y, ss));
+    }
+  }
+  ss = stk::block_sum(ss, red);
+  if (threadIdx.x == 0) out[t * ldo] = ss;
+}
+
+STK_API int stk_row_sumsq(const void* x, long long ldx, float* out, long long ldo, int T, int K, void* stream) {
+  if (T <= 0) return 0;
+  if (K % 8 || ldx % 8 || (reinterpret_cast<uintptr_t>(x) & 15)) return -1;
+  row_sumsq_kernel<<<T, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, out, ldo, K);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
 STK_API int stk_quant_fp8_group128(const void* x, long long ldx, void* q, long long ldq, float* scales, int scale_ld,
                                    int T, int K, void* stream) {
   if (T <= 0) return 0;

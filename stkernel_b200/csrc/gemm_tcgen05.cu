@@ -622,7 +622,7 @@ STK_API long long stk_gemm_workspace_bytes(int T, int N, int splits) {
 static int gemm_launch(const void* W, long long ldw, const void* X, long long ldx, void* out, long long ldo, int T, int N,
                        int K, int is_fp8, int out_fp32, const float* w_scale, int w_scale_ld, const float* x_scale,
                        int x_scale_ld, int splits, float* workspace, int* counters, int* status, int sm_count,
-                       int groups, const void* ar_ctx, const void* gate_ctx, int gate_rows, void* stream) {
+                       int groups, const void* ar_ctx, const void* gate_ctx, int gate_rows, void* stream, int bt_override = 0) {
   if (T <= 0 || N <= 0 || K <= 0) return 0;
   const int es = is_fp8 ? 1 : 2;
   if ((ldw * es) % 16 || (ldx * es) % 16 || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(X) & 15))
@@ -653,7 +653,8 @@ static int gemm_launch(const void* W, long long ldw, const void* X, long long ld
     const int grid = units < sm_count ? units : sm_count;
     return launch_gemm<128, true>(ta, tb, a, grid, reinterpret_cast<cudaStream_t>(stream));
   }
-  const int bt = stk_gemm_pick_bt(T, is_fp8);
+  int bt = stk_gemm_pick_bt(T, is_fp8);
+  if (bt_override == 16 || bt_override == 32 || bt_override == 64 || bt_override == 128) bt = bt_override;
   CUtensorMap tw, tx;
   if (make_tmap_2d(&tw, W, es, N, K, ldw, 128) != 0) return -13;
   if (groups > 1 && ((K * es) % 128 || N % (128 * groups))) return -17;   // groups must split on tile boundaries
@@ -714,6 +715,14 @@ STK_API int stk_gemm(const void* W, long long ldw, const void* X, long long ldx,
                      int groups, const void* ar_ctx, void* stream) {
   return gemm_launch(W, ldw, X, ldx, out, ldo, T, N, K, is_fp8, out_fp32, w_scale, w_scale_ld, x_scale, x_scale_ld, splits,
                      workspace, counters, status, sm_count, groups, ar_ctx, nullptr, 0, stream);
+}
+
+// Plain GEMM with an explicit token-tile width (16/32/64/128): narrow weights with many tokens get their parallelism
+// from token tiles instead of split-K (e.g. the 24-row hyper-connection mix projection over [T, 16384]).
+STK_API int stk_gemm_tile(const void* W, long long ldw, const void* X, long long ldx, void* out, long long ldo, int T, int N,
+                          int K, int out_fp32, int bt, int* status, int sm_count, void* stream) {
+  return gemm_launch(W, ldw, X, ldx, out, ldo, T, N, K, 0, out_fp32, nullptr, 0, nullptr, 0, 1, nullptr, nullptr, status,
+                     sm_count, 1, nullptr, nullptr, 0, stream, bt);
 }
 
 // All-gather -> GEMM: X is the gathered [T, K] matrix inside this rank's symmetric region (filled by

@@ -273,6 +273,25 @@ def embed_hc(ids: torch.Tensor, embed: torch.Tensor, hc: int, vocab: int, vocab_
 # ----------------------------------------------------------------------------
 # mHC
 # ----------------------------------------------------------------------------
+MHC_GEMM_MIN_T = 256
+_MHC_WCAT: dict = {}
+
+
+def _mhc_wcat(fn: torch.Tensor, n_mix: int) -> torch.Tensor:
+    """[128, hc*H] bf16: rows [0, n_mix) the bf16 rounding of fn, rows [32, 32 + n_mix) the bf16 rounding of the
+    remainder, zeros elsewhere (a full 128-row weight tile).  Built once per weight tensor."""
+    key = (fn.data_ptr(), fn.shape)
+    w = _MHC_WCAT.get(key)
+    if w is None:
+        hi = fn.to(BF16)
+        lo = (fn - hi.to(F32)).to(BF16)
+        w = torch.zeros(128, fn.shape[1], dtype=BF16, device=fn.device)
+        w[:n_mix] = hi
+        w[32:32 + n_mix] = lo
+        _MHC_WCAT[key] = w
+    return w
+
+
 def mhc_pre(residual: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale: torch.Tensor,
             norm_w: Optional[torch.Tensor], rms_eps: float, hc_eps: float, iters: int, quant: bool = False,
             tag: str = "mhc"):
@@ -294,9 +313,23 @@ def mhc_pre(residual: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale:
         _lib.call("stk_mhc_cluster", residual, fn, base, scale, norm_w, post, comb, y, t, h, hc, n_mix, rms_eps, hc_eps,
                   iters, 2.0, 0, _lib.stream())
         return (y, post, comb, quant_act(y, tag + ".q")) if quant else (y, post, comb)
-    splits = _lib.query("stk_mhc_pick_splits", t, hc * h)
-    partial = scratch("mhc.partial", (splits * t * (n_mix + 1),), F32, dev)
-    _lib.call("stk_mhc_dots", residual, fn, partial, t, h, hc, n_mix, splits, _lib.stream())
+    if t >= MHC_GEMM_MIN_T and n_mix <= 32 and (hc * h) % 64 == 0:
+        # many tokens: the [n_mix, hc*H] mix projection runs on the tensor cores.  fn (fp32) is split into a bf16 high
+        # part and a bf16 remainder (two weight rows per mix, products accumulate in fp32: ~16 mantissa bits, more
+        # than the tf32 the reference uses); narrow 32-token tiles supply the parallelism, no split-K.
+        wcat = _mhc_wcat(fn, n_mix)
+        x2d = residual.view(t, hc * h)
+        prod = scratch("mhc.gemm", (t, 128), F32, dev)
+        _lib.call("stk_gemm_tile", wcat, wcat.stride(0), x2d, x2d.stride(0), prod, 128, t, 128, hc * h, 1, 32,
+                  _lib.status_buffer(), _lib.sm_count(), _lib.stream())
+        partial = scratch("mhc.partial", (t * (n_mix + 1),), F32, dev).view(t, n_mix + 1)
+        torch.add(prod[:, :n_mix], prod[:, 32:32 + n_mix], out=partial[:, :n_mix])
+        _lib.call("stk_row_sumsq", x2d, x2d.stride(0), partial[:, n_mix:], n_mix + 1, t, hc * h, _lib.stream())
+        splits = 1
+    else:
+        splits = _lib.query("stk_mhc_pick_splits", t, hc * h)
+        partial = scratch("mhc.partial", (splits * t * (n_mix + 1),), F32, dev)
+        _lib.call("stk_mhc_dots", residual, fn, partial, t, h, hc, n_mix, splits, _lib.stream())
     y = torch.empty(t, h, dtype=BF16, device=dev)
     post = torch.empty(t, hc, dtype=F32, device=dev)
     comb = torch.empty(t, hc * hc, dtype=F32, device=dev)

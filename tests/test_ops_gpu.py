@@ -90,7 +90,7 @@ def test_swiglu_clamp():
     assert rel_err(a, R.swiglu_clamp(gu[:, :256], gu[:, 256:], 10.0)) < 5e-3
 
 
-@pytest.mark.parametrize("T,H", [(1, 4096), (7, 4096), (33, 256)])
+@pytest.mark.parametrize("T,H", [(1, 4096), (7, 4096), (33, 256), (300, 4096), (700, 1024)])
 def test_mhc_pre_post_head(T, H):
     torch.manual_seed(0)
     hc = 4
