@@ -5,6 +5,9 @@ of kernel intervals (overlapping streams are not double counted) and the idle sh
 accounting as the reference's trace bucketing (bench/profile-step.py:166-281).
 
     python -m stkernel_b200.bench.kernel_table --mode decode --conc 1 --graphs 1
+
+Under `python -m torch.distributed.run --nproc-per-node N` the model is tensor/expert parallel over the N ranks
+(`--layers` is then the total layer count) and rank 0 prints its own table.
 """
 from __future__ import annotations
 
@@ -82,13 +85,23 @@ def main() -> None:
     from ..runtime.engine import Engine, SamplingParams
     from .decode_bench import add_synthetic_requests, fill_caches_synthetic
 
-    dev = torch.device("cuda:0")
-    torch.cuda.set_device(0)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(local)
+    comm = None
+    if world > 1:
+        import torch.distributed as dist
+        from ..parallel.communicator import Communicator
+        dist.init_process_group("nccl", device_id=dev)
+        comm = Communicator(device=dev, use_symm=True)
     cfg = flash_config(num_layers=a.layers)
     ec = EngineConfig(model=cfg, sched=SchedulerConfig(max_model_len=a.ctx + 8192, max_num_seqs=max(a.conc, 2),
                                                        max_num_batched_tokens=a.chunk,
                                                        graph_cap=64 if a.graphs else 0)).validate()
-    eng = Engine(ec, build_model_weights(cfg, RandomSource(0), dev, head_fp8=True), dev, max_context=a.ctx + 8192)
+    eng = Engine(ec, build_model_weights(cfg, RandomSource(0), dev, rank, world, head_fp8=True), dev, comm, rank,
+                 max_context=a.ctx + 8192)
     fill_caches_synthetic(eng)
     if a.mode == "decode":
         add_synthetic_requests(eng, a.conc, a.ctx, a.steps + 8, cfg.vocab_size, 3)
@@ -103,10 +116,10 @@ def main() -> None:
         for _ in range(a.steps):
             eng.step()
         torch.cuda.synchronize()
-    path = os.path.join(tempfile.gettempdir(), "stk_trace.json")
+    path = os.path.join(tempfile.gettempdir(), f"stk_trace_{rank}.json")
     prof.export_chrome_trace(path)
     s = summarise_trace(path, a.steps)
-    lines = [f"mode={a.mode} conc={a.conc} ctx={a.ctx} layers={a.layers} graphs={a.graphs} steps={a.steps}",
+    lines = [f"mode={a.mode} conc={a.conc} ctx={a.ctx} layers={a.layers} graphs={a.graphs} steps={a.steps} gpus={world}",
              f"busy {s['busy_us'] / a.steps:.1f} us/step, span {s['span_us'] / a.steps:.1f} us/step, "
              f"idle {100 * (1 - s['busy_us'] / max(s['span_us'], 1e-9)):.1f} %"]
     for b, v in sorted(s["buckets"].items(), key=lambda x: -x[1]):
@@ -115,9 +128,14 @@ def main() -> None:
     for n, d in rows:
         lines.append(f"  {sum(d) / a.steps:9.1f} us/step {len(d) // a.steps:4d}x/step avg {sum(d) / len(d):7.1f} us  {n[:70]}")
     text = "\n".join(lines)
-    print(text)
-    if a.out:
-        open(a.out, "w").write(text + "\n")
+    if rank == 0:
+        print(text, flush=True)
+        if a.out:
+            open(a.out, "w").write(text + "\n")
+    if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()
+        os._exit(0)
 
 
 if __name__ == "__main__":

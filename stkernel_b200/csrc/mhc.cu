@@ -345,12 +345,24 @@ constexpr int kClusterSize = 8;
 constexpr int kClusterThreads = 512;
 constexpr int kClusterWarps = kClusterThreads / 32;
 
+// Fused post->pre: the residual streams this step reads are themselves the post-mix of the previous sub-block,
+//   X'[j] = post_old[j] * fa + sum_k comb_old[j, k] * res_old[k]        (rounded to bf16, written to x_out),
+// computed on the fly instead of by a separate launch.  fa == nullptr: the streams are read from `x` as given.
+struct MhcFuse {
+  const __nv_bfloat16* fa;        // [T, H] output of the previous attention / MoE sub-block
+  const __nv_bfloat16* res_old;   // [T, hc, H]
+  const float* post_old;          // [T, hc]
+  const float* comb_old;          // [T, hc*hc]
+  __nv_bfloat16* x_out;           // [T, hc, H]
+};
+
 template <int NMIX>
 __global__ void __launch_bounds__(kClusterThreads)
 mhc_cluster_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ fn, const float* __restrict__ base,
                    const float* __restrict__ scale, const __nv_bfloat16* __restrict__ norm_w, float* __restrict__ post,
                    float* __restrict__ comb, __nv_bfloat16* __restrict__ y, int H, int hc, float rms_eps, float hc_eps,
-                   int sinkhorn_iters, float post_mult, int mode, uint8_t* q_out, float* q_scale, int q_scale_ld) {
+                   int sinkhorn_iters, float post_mult, int mode, uint8_t* q_out, float* q_scale, int q_scale_ld,
+                   const MhcFuse fz) {
   cg::cluster_group cluster = cg::this_cluster();
   const int crank = static_cast<int>(cluster.block_rank());
   const int t = blockIdx.x / kClusterSize;
@@ -360,8 +372,17 @@ mhc_cluster_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   __shared__ float mixes[NMIX + 1];
   __shared__ float pre[8];
   __shared__ float gmax[8];
+  __shared__ float s_po[4], s_co[16];
   const int HC = H * hc;
-  const __nv_bfloat16* xt = x + static_cast<long long>(t) * HC;
+  const bool fused = fz.fa != nullptr;
+  if (fused) {
+    if (threadIdx.x < hc) s_po[threadIdx.x] = fz.post_old[t * hc + threadIdx.x];
+    if (threadIdx.x < hc * hc) s_co[threadIdx.x] = fz.comb_old[t * hc * hc + threadIdx.x];
+    __syncthreads();
+  }
+  const __nv_bfloat16* xt = fused ? nullptr : x + static_cast<long long>(t) * HC;
+  const __nv_bfloat16* fat = fused ? fz.fa + static_cast<long long>(t) * H : nullptr;
+  const __nv_bfloat16* rot = fused ? fz.res_old + static_cast<long long>(t) * HC : nullptr;
   const int slice = ((HC / kClusterSize) + 1) & ~1;
   const int k0 = crank * slice, k1 = min(HC, k0 + slice);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -376,7 +397,29 @@ mhc_cluster_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   const bool vec4 = ((k0 | k1 | HC) & 3) == 0;
   if (vec4) {
     for (int k = k0 + threadIdx.x * 4; k < k1; k += blockDim.x * 4) {
-      const uint2 raw = *reinterpret_cast<const uint2*>(xt + k);
+      uint2 raw;
+      if (fused) {
+        const int j = k / H, h = k - j * H;
+        const uint2 av = *reinterpret_cast<const uint2*>(fat + h);
+        const __nv_bfloat162 a01 = *reinterpret_cast<const __nv_bfloat162*>(&av.x);
+        const __nv_bfloat162 a23 = *reinterpret_cast<const __nv_bfloat162*>(&av.y);
+        float v0 = s_po[j] * __low2float(a01), v1 = s_po[j] * __high2float(a01);
+        float v2 = s_po[j] * __low2float(a23), v3 = s_po[j] * __high2float(a23);
+        for (int kk = 0; kk < hc; ++kk) {
+          const uint2 rv = *reinterpret_cast<const uint2*>(rot + static_cast<long long>(kk) * H + h);
+          const __nv_bfloat162 r01 = *reinterpret_cast<const __nv_bfloat162*>(&rv.x);
+          const __nv_bfloat162 r23 = *reinterpret_cast<const __nv_bfloat162*>(&rv.y);
+          const float c = s_co[j * hc + kk];
+          v0 = fmaf(c, __low2float(r01), v0); v1 = fmaf(c, __high2float(r01), v1);
+          v2 = fmaf(c, __low2float(r23), v2); v3 = fmaf(c, __high2float(r23), v3);
+        }
+        const __nv_bfloat162 o01 = __floats2bfloat162_rn(v0, v1), o23 = __floats2bfloat162_rn(v2, v3);
+        raw.x = *reinterpret_cast<const uint32_t*>(&o01);
+        raw.y = *reinterpret_cast<const uint32_t*>(&o23);
+        *reinterpret_cast<uint2*>(fz.x_out + static_cast<long long>(t) * HC + k) = raw;
+      } else {
+        raw = *reinterpret_cast<const uint2*>(xt + k);
+      }
       const __nv_bfloat162 v0 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
       const __nv_bfloat162 v1 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
       const float x0 = __low2float(v0), x1 = __high2float(v0), x2 = __low2float(v1), x3 = __high2float(v1);
@@ -387,7 +430,7 @@ mhc_cluster_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
 #pragma unroll
       for (int j = 0; j < NMIX; ++j) acc[j] = fmaf(x0, f[j].x, fmaf(x1, f[j].y, fmaf(x2, f[j].z, fmaf(x3, f[j].w, acc[j]))));
     }
-  } else {
+  } else if (!fused) {
     for (int k = k0 + threadIdx.x * 2; k < k1; k += blockDim.x * 2) {
       const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(xt + k);
       const float xa = __low2float(v), xb = __high2float(v);
@@ -489,10 +532,31 @@ mhc_cluster_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
     ya[u] = yb[u] = 0.f;
     if (i < c1) {
       float a0 = 0.f, a1 = 0.f;
+      if (fused) {
+        // recompute the (bf16-rounded) streams of these two columns from the previous sub-block's operands
+        const __nv_bfloat162 av = *reinterpret_cast<const __nv_bfloat162*>(fat + i);
+        float r0[4], r1[4];
+        for (int kk = 0; kk < hc; ++kk) {
+          const __nv_bfloat162 rv = *reinterpret_cast<const __nv_bfloat162*>(rot + static_cast<long long>(kk) * H + i);
+          r0[kk] = __low2float(rv);
+          r1[kk] = __high2float(rv);
+        }
+        for (int j = 0; j < hc; ++j) {
+          float v0 = s_po[j] * __low2float(av), v1 = s_po[j] * __high2float(av);
+          for (int kk = 0; kk < hc; ++kk) {
+            v0 = fmaf(s_co[j * hc + kk], r0[kk], v0);
+            v1 = fmaf(s_co[j * hc + kk], r1[kk], v1);
+          }
+          const __nv_bfloat162 o = __floats2bfloat162_rn(v0, v1);
+          a0 = fmaf(pre[j], __low2float(o), a0);
+          a1 = fmaf(pre[j], __high2float(o), a1);
+        }
+      } else {
       for (int j = 0; j < hc; ++j) {
         const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(xt + static_cast<long long>(j) * H + i);
         a0 = fmaf(pre[j], __low2float(v), a0);
         a1 = fmaf(pre[j], __high2float(v), a1);
+      }
       }
       if (mode == 0) {
         a0 = bf16_to_f(__float2bfloat16(a0));
@@ -541,10 +605,11 @@ mhc_cluster_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
 
 }  // namespace stk
 
-STK_API int stk_mhc_cluster(const void* x, const float* fn, const float* base, const float* scale, const void* norm_w,
-                            float* post, float* comb, void* y, int T, int H, int hc, int n_mix, float rms_eps,
-                            float hc_eps, int sinkhorn_iters, float post_mult, int mode, void* stream) {
+static int mhc_cluster_launch(const void* x, const float* fn, const float* base, const float* scale, const void* norm_w,
+                              float* post, float* comb, void* y, int T, int H, int hc, int n_mix, float rms_eps,
+                              float hc_eps, int sinkhorn_iters, float post_mult, int mode, const MhcFuse& fz, void* stream) {
   if (T <= 0) return 0;
+  if (fz.fa != nullptr && (hc > 4 || H % 4 || ((H * hc / kClusterSize + 1) & ~1) % 4)) return -3;
   if (hc * hc > 32 || H % 2 || H > kClusterSize * kClusterThreads * 2 * 2 || (H * hc) % 2) return -1;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(T * kClusterSize);
@@ -567,14 +632,34 @@ STK_API int stk_mhc_cluster(const void* x, const float* fn, const float* base, c
   cudaError_t e;
   if (n_mix == 24)
     e = cudaLaunchKernelEx(&cfg, mhc_cluster_kernel<24>, xp, fn, base, scale, nw, post, comb, yp, H, hc, rms_eps, hc_eps,
-                           sinkhorn_iters, post_mult, mode, qn, qs, qld);
+                           sinkhorn_iters, post_mult, mode, qn, qs, qld, fz);
   else if (n_mix == 4)
     e = cudaLaunchKernelEx(&cfg, mhc_cluster_kernel<4>, xp, fn, base, scale, nw, post, comb, yp, H, hc, rms_eps, hc_eps,
-                           sinkhorn_iters, post_mult, mode, qn, qs, qld);
+                           sinkhorn_iters, post_mult, mode, qn, qs, qld, fz);
   else if (n_mix == 8)
     e = cudaLaunchKernelEx(&cfg, mhc_cluster_kernel<8>, xp, fn, base, scale, nw, post, comb, yp, H, hc, rms_eps, hc_eps,
-                           sinkhorn_iters, post_mult, mode, qn, qs, qld);
+                           sinkhorn_iters, post_mult, mode, qn, qs, qld, fz);
   else
     return -2;
   return e == cudaSuccess ? 0 : -4;
+}
+
+STK_API int stk_mhc_cluster(const void* x, const float* fn, const float* base, const float* scale, const void* norm_w,
+                            float* post, float* comb, void* y, int T, int H, int hc, int n_mix, float rms_eps,
+                            float hc_eps, int sinkhorn_iters, float post_mult, int mode, void* stream) {
+  MhcFuse fz = {nullptr, nullptr, nullptr, nullptr, nullptr};
+  return mhc_cluster_launch(x, fn, base, scale, norm_w, post, comb, y, T, H, hc, n_mix, rms_eps, hc_eps, sinkhorn_iters,
+                            post_mult, mode, fz, stream);
+}
+
+// Post-mix of the previous sub-block fused into this pre step: reads fa [T, H], res_old [T, hc, H], post_old, comb_old;
+// writes the new residual streams to x_out and the usual pre outputs.
+STK_API int stk_mhc_post_pre(const void* fa, const void* res_old, const float* post_old, const float* comb_old, void* x_out,
+                             const float* fn, const float* base, const float* scale, const void* norm_w, float* post,
+                             float* comb, void* y, int T, int H, int hc, int n_mix, float rms_eps, float hc_eps,
+                             int sinkhorn_iters, float post_mult, int mode, void* stream) {
+  MhcFuse fz = {(const __nv_bfloat16*)fa, (const __nv_bfloat16*)res_old, post_old, comb_old, (__nv_bfloat16*)x_out};
+  if (fa == nullptr || res_old == nullptr || x_out == nullptr || x_out == res_old) return -1;
+  return mhc_cluster_launch(nullptr, fn, base, scale, norm_w, post, comb, y, T, H, hc, n_mix, rms_eps, hc_eps,
+                            sinkhorn_iters, post_mult, mode, fz, stream);
 }

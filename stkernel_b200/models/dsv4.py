@@ -381,21 +381,28 @@ class DSV4Model:
         out = M.moe_experts(y, ids, wts, lw.experts, cfg.swiglu_limit, shared, cfg.n_routed_experts)
         return self._all_reduce(out)
 
-    def layer(self, li: int, lw: LayerWeights, X: torch.Tensor, meta: StepMeta) -> torch.Tensor:
+    def layer(self, li: int, lw: LayerWeights, X: torch.Tensor, meta: StepMeta, pend=None, defer: bool = False):
+        """One decoder layer.  `pend` = (sub-block output, streams, post, comb) left unmixed by the previous layer: its
+        post-mix runs inside this layer's first pre-mix.  With `defer` the layer returns such a tuple instead of the
+        mixed streams."""
         cfg = self.cfg
-        want_q = lw.w_qa_kv.is_fp8 and Fn.wants_quant_act(X.shape[0], X.device)
-        r = Fn.mhc_pre(X, *lw.hc_attn, lw.attn_norm, cfg.rms_norm_eps, cfg.hc_eps, cfg.hc_sinkhorn_iters, quant=want_q,
-                       tag="mhc_a")
+        n = X.shape[0]
+        want_q = lw.w_qa_kv.is_fp8 and Fn.wants_quant_act(n, X.device)
+        hc_args = (cfg.rms_norm_eps, cfg.hc_eps, cfg.hc_sinkhorn_iters)
+        if pend is None:
+            r = Fn.mhc_pre(X, *lw.hc_attn, lw.attn_norm, *hc_args, quant=want_q, tag="mhc_a")
+        else:
+            X, r = Fn.mhc_post_pre(*pend, *lw.hc_attn, lw.attn_norm, *hc_args, quant=want_q, tag="mhc_a")
         y, post, comb = r[0], r[1], r[2]
-        with span("attention", X.shape[0]):
+        with span("attention", n):
             a = self.attention(li, lw, y, r[3] if want_q else None, meta)
-        X = Fn.mhc_post(a, X, post, comb)
-        want_q = lw.w_sh13 is not None and lw.w_sh13.is_fp8 and Fn.wants_quant_act(X.shape[0], X.device)
-        r = Fn.mhc_pre(X, *lw.hc_ffn, lw.ffn_norm, cfg.rms_norm_eps, cfg.hc_eps, cfg.hc_sinkhorn_iters, quant=want_q,
-                       tag="mhc_f")
+        want_q = lw.w_sh13 is not None and lw.w_sh13.is_fp8 and Fn.wants_quant_act(n, X.device)
+        X, r = Fn.mhc_post_pre(a, X, post, comb, *lw.hc_ffn, lw.ffn_norm, *hc_args, quant=want_q, tag="mhc_f")
         y, post, comb = r[0], r[1], r[2]
-        with span("moe", X.shape[0]):
+        with span("moe", n):
             f = self.moe(lw, y, r[3] if want_q else None, meta)
+        if defer:
+            return f, X, post, comb
         return Fn.mhc_post(f, X, post, comb)
 
     # ---- whole model -------------------------------------------------------------
@@ -404,8 +411,15 @@ class DSV4Model:
         cfg = self.cfg
         X = Fn.embed_hc(meta.token_ids, self.w.embed, cfg.hc_mult, cfg.vocab_size)
         self.aux_out = []
+        pend = None
+        last = len(self.w.layers) - 1
         for li, lw in enumerate(self.w.layers):
-            X = self.layer(li, lw, X, meta)
+            defer = li != last and li not in self.aux_layers
+            out = self.layer(li, lw, X, meta, pend, defer)
+            if defer:
+                pend, X = out, out[1]
+            else:
+                pend, X = None, out
             if li in self.aux_layers:
                 self.aux_out.append(X.float().mean(1).to(X.dtype))
         return X

@@ -352,6 +352,28 @@ def mhc_post(x: torch.Tensor, residual: torch.Tensor, post: torch.Tensor, comb: 
     return out
 
 
+def mhc_post_pre(x: torch.Tensor, residual: torch.Tensor, post_old: torch.Tensor, comb_old: torch.Tensor,
+                 fn: torch.Tensor, base: torch.Tensor, scale: torch.Tensor, norm_w: Optional[torch.Tensor], rms_eps: float,
+                 hc_eps: float, iters: int, quant: bool = False, tag: str = "mhc"):
+    """The post-mix of one sub-block followed by the pre-mix of the next: -> (new residual [T, hc, H], mhc_pre outputs).
+    Decode-sized batches run both in one cluster launch (the new streams are formed on the fly from x and the old
+    streams and never re-read); otherwise the two ops run back to back."""
+    t, hc, h = residual.shape
+    n_mix = (2 + hc) * hc
+    if (residual.is_cuda and t <= MHC_CLUSTER_MAX_T and n_mix == 24 and h <= 16384 and h % 32 == 0):
+        dev = residual.device
+        new_res = torch.empty_like(residual)
+        y = torch.empty(t, h, dtype=BF16, device=dev)
+        post = torch.empty(t, hc, dtype=F32, device=dev)
+        comb = torch.empty(t, hc * hc, dtype=F32, device=dev)
+        _lib.call("stk_mhc_post_pre", x, residual, post_old, comb_old, new_res, fn, base, scale, norm_w, post, comb, y, t,
+                  h, hc, n_mix, rms_eps, hc_eps, iters, 2.0, 0, _lib.stream())
+        r = (y, post, comb, quant_act(y, tag + ".q")) if quant else (y, post, comb)
+        return new_res, r
+    new_res = mhc_post(x, residual, post_old, comb_old)
+    return new_res, mhc_pre(new_res, fn, base, scale, norm_w, rms_eps, hc_eps, iters, quant=quant, tag=tag)
+
+
 def hc_head(residual: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale: torch.Tensor, rms_eps: float,
             hc_eps: float) -> torch.Tensor:
     t, hc, h = residual.shape

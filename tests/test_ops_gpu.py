@@ -116,6 +116,29 @@ def test_mhc_pre_post_head(T, H):
     assert rel_err(hh, R.hc_head(res, hfn, hb, hs, 1e-6, 1e-6)) < 5e-3
 
 
+@pytest.mark.parametrize("T,H", [(1, 4096), (5, 4096), (16, 1024), (40, 512)])
+def test_mhc_post_pre_fused(T, H):
+    """Post-mix of one sub-block fused into the next pre-mix (one cluster launch for T <= 16) against the two
+    reference ops run back to back in fp32 (streams rounded to bf16 in between, as the unfused path stores them)."""
+    torch.manual_seed(1)
+    hc = 4
+    res = torch.randn(T, hc, H, device=dev()).to(BF16)
+    x = torch.randn(T, H, device=dev()).to(BF16)
+    post_old = torch.rand(T, hc, device=dev()) * 2
+    comb_old = torch.softmax(torch.randn(T, hc, hc, device=dev()), -1).reshape(T, hc * hc).contiguous()
+    fn = torch.randn(24, hc * H, device=dev()) * 0.02
+    base = torch.randn(24, device=dev()) * 0.1
+    scale = torch.tensor([1.0, 0.7, 1.3], device=dev())
+    nw = (1 + 0.1 * torch.randn(H, device=dev())).to(BF16)
+    new_res, r = Fn.mhc_post_pre(x, res, post_old, comb_old, fn, base, scale, nw, 1e-6, 1e-6, 20)
+    ref_res = R.mhc_post(x, res, post_old, comb_old.view(T, hc, hc)).to(BF16)
+    assert rel_err(new_res, ref_res) < 5e-3
+    yr, pr, cr = R.mhc_pre(ref_res, fn, base, scale, nw, 1e-6, 1e-6, 20, round_bf16=True)
+    assert rel_err(r[0], yr) < 6e-3
+    assert torch.allclose(r[1], pr, atol=2e-3, rtol=2e-3)
+    assert torch.allclose(r[2].view(T, hc, hc), cr, atol=2e-3, rtol=2e-3)
+
+
 def _rope_setup(T, R_):
     pos = torch.randint(0, 100000, (T,), device=dev(), dtype=torch.int64)
     inv = Fn.inv_freq(R_, 10000.0, dev())
