@@ -26,6 +26,7 @@ from ..ops import functional as Fn
 from ..ops import moe as M
 from ..utils.spans import span
 from ..ops.functional import LinearWeight
+from ..ops.scratch import side_branch
 from .dsv4_oracle import index_cache_computes
 from .weights import compressor_slots
 
@@ -268,6 +269,11 @@ class DSV4Model:
         # because scoring and top-k are independent per row).
         self.indexer_sp = tp_size > 1 and comm is not None
         self.indexer_sp_min_rows = int(os.environ.get("STK_INDEXER_SP_MIN_ROWS", "256"))
+        # Decode-sized steps are a chain of launches that each fill a fraction of the GPU: independent branches of a
+        # sub-block (compressor state update and KV insert beside the q / indexer chain, the shared expert beside the
+        # router) run on a second stream, also inside captured graphs, so the chain gets shorter.
+        self.fork_max_t = int(os.environ.get("STK_FORK_MAX_T", "64")) if dev.type == "cuda" else 0
+        self.side_stream = torch.cuda.Stream(dev) if self.fork_max_t > 0 else None
 
     # ---- collectives ----------------------------------------------------------
     def _all_reduce(self, x: torch.Tensor) -> torch.Tensor:
@@ -290,38 +296,77 @@ class DSV4Model:
         D, Rd = cfg.head_dim, cfg.qk_rope_head_dim
         nh_l = cfg.num_attention_heads // self.tp_size
         ql = cfg.q_lora_rank
+        fork = bool(lw.ratio) and self.side_stream is not None and 0 < T <= self.fork_max_t
+        ev_in = torch.cuda.current_stream().record_event() if fork else None
         qkv = Fn.linear(yq if yq is not None else y, lw.w_qa_kv, tag="qa_kv")
         use_q = lw.w_qb.is_fp8 and Fn.wants_quant_act(T, y.device)
         res = Fn.rms_norm_pair(qkv[:, :ql], lw.q_norm, qkv[:, ql:], lw.kv_norm, cfg.rms_norm_eps, quant0=use_q, tag="qr")
         qr, kvn = res[0], res[1]
         qb = Fn.linear(res[2] if use_q else qr, lw.w_qb, tag="qb")
-        q = C.q_rope_kv_insert(qb[:, :nh_l * D].view(T, nh_l, D), kvn, meta.positions, meta.swa_slot_mapping, self.inv,
-                               self.kv.swa_cache[li], cfg.rms_norm_eps)
+
+        def kv_insert():
+            return C.q_rope_kv_insert(qb[:, :nh_l * D].view(T, nh_l, D), kvn, meta.positions, meta.swa_slot_mapping,
+                                      self.inv, self.kv.swa_cache[li], cfg.rms_norm_eps)
 
         topk_slots = topk_lens = None
         comp_cache = None
-        if lw.ratio:
+        if not lw.ratio:
+            q = kv_insert()
+        else:
             c = compressor_slots(lw.ratio)
-            side = Fn.linear(y, lw.w_side, out_dtype=F32, tag="side")
             ncomp = 2 * c * D
             grp = self.kv.c4 if lw.kind == "c4a" else self.kv.c128
             comp_cache = self.kv.comp_cache[li]
-            C.compress_windows(side[:, :ncomp], lw.ape, lw.comp_norm,
-                               self.inv, meta.positions, meta.tok_req, meta.first_pos, meta.last_pos,
-                               self.kv.comp_state[li], grp.table_dev, comp_cache, lw.ratio, c, cfg.rms_norm_eps)
+            computes = lw.kind == "c4a" and lw.computes_topk
+            ih = cfg.index_n_heads
+
+            def compress_main(side):
+                C.compress_windows(side[:, :ncomp], lw.ape, lw.comp_norm,
+                                   self.inv, meta.positions, meta.tok_req, meta.first_pos, meta.last_pos,
+                                   self.kv.comp_state[li], grp.table_dev, comp_cache, lw.ratio, c, cfg.rms_norm_eps)
+
+            def compress_idx(side):
+                C.compress_windows(side[:, ncomp + ih:], lw.iape, lw.inorm, self.inv, meta.positions,
+                                   meta.tok_req, meta.first_pos, meta.last_pos, self.kv.idx_state[li],
+                                   grp.table_dev, self.kv.idx_cache[li], lw.ratio, 2, cfg.rms_norm_eps)
+
+            ev_side = ev_idx = ev_done = None
+            if fork:
+                # side stream: side projection -> indexer-key compressor -> KV compressor -> q rope + SWA insert;
+                # this stream keeps the q / indexer scoring chain and waits where it needs the other's results
+                main, sd = torch.cuda.current_stream(), self.side_stream
+                ev_qb = main.record_event()
+                with side_branch(sd):
+                    sd.wait_event(ev_in)       # y is ready: the branch starts beside the qa/kv projection
+                    side = Fn.linear(y, lw.w_side, out_dtype=F32, tag="side")
+                    ev_side = sd.record_event()
+                    if computes:
+                        compress_idx(side)
+                        ev_idx = sd.record_event()
+                    compress_main(side)
+                    sd.wait_event(ev_qb)
+                    q = kv_insert()
+                    ev_done = sd.record_event()
+            else:
+                q = kv_insert()
+                side = Fn.linear(y, lw.w_side, out_dtype=F32, tag="side")
+                compress_main(side)
             if lw.kind == "c4a":
                 K = cfg.index_topk
                 if self.topk_buffer is None or self.topk_buffer.shape[0] < T:
                     self.topk_buffer = torch.full((max(T, 16), K), -1, dtype=torch.int32, device=y.device)
-                if lw.computes_topk:
-                    ih, di = cfg.index_n_heads, cfg.index_head_dim
+                if computes:
+                    di = cfg.index_head_dim
                     qi = qb[:, nh_l * D:].view(T, ih, di)
+                    if fork:
+                        torch.cuda.current_stream().wait_event(ev_side)
                     wi = side[:, ncomp:ncomp + ih]
                     quant = cfg.kv_cache_dtype == "fp8_ds_mla"
                     qq, wf = C.indexer_q_prep(qi, wi, meta.positions, self.inv, Rd, quant)
-                    C.compress_windows(side[:, ncomp + ih:], lw.iape, lw.inorm, self.inv, meta.positions,
-                                       meta.tok_req, meta.first_pos, meta.last_pos, self.kv.idx_state[li],
-                                       grp.table_dev, self.kv.idx_cache[li], lw.ratio, 2, cfg.rms_norm_eps)
+                    if fork:
+                        torch.cuda.current_stream().wait_event(ev_idx)
+                    else:
+                        compress_idx(side)
                     nv = A.compressed_valid(meta.positions, lw.ratio)
                     if self.indexer_sp and T >= self.indexer_sp_min_rows * self.tp_size:
                         shard = -(-T // self.tp_size)
@@ -342,6 +387,8 @@ class DSV4Model:
             else:
                 topk_slots, topk_lens = A.c128_indices(meta.positions, meta.tok_req, grp.table_dev, lw.ratio,
                                                        cfg.index_topk)
+            if fork:
+                torch.cuda.current_stream().wait_event(ev_done)
         with span("sparse_mla", T):
             o = A.sparse_mla(q, self.kv.swa_cache[li], meta.swa_slots, meta.swa_lens, comp_cache, topk_slots, topk_lens,
                              lw.sink, D ** -0.5, inv_rope=(meta.positions, self.inv))
@@ -363,23 +410,37 @@ class DSV4Model:
     # ---- MoE sub-block ----------------------------------------------------------
     def moe(self, lw: LayerWeights, y: torch.Tensor, yq, meta: StepMeta) -> torch.Tensor:
         cfg = self.cfg
+        T = y.shape[0]
+        fork = self.side_stream is not None and 0 < T <= self.fork_max_t and lw.w_sh13 is not None
+        if fork:
+            # the shared expert (two launches) runs beside the gate projection, the router and the routed experts
+            main, sd = torch.cuda.current_stream(), self.side_stream
+            ev_in = main.record_event()
+            with side_branch(sd):
+                sd.wait_event(ev_in)
+                shared = self._shared_expert(lw, y, yq)
+                ev_sh = sd.record_event()
         logits = Fn.linear(y, lw.w_gate, out_dtype=F32, tag="gate")
         ids, wts = M.router(logits, lw.gate_bias, cfg.num_experts_per_tok, cfg.scoring_func, cfg.norm_topk_prob,
                             cfg.routed_scaling_factor, lw.tid2eid, meta.token_ids)
-        shared = None
-        if lw.w_sh13 is not None:
-            act = Fn.linear_swiglu(y, lw.w_sh13, cfg.swiglu_limit) if yq is None else None
-        if lw.w_sh13 is not None and act is not None:
-            shared = Fn.linear(act, lw.w_sh2, tag="sh2")
-        elif lw.w_sh13 is not None:
-            gu = Fn.linear(yq if (yq is not None and lw.w_sh13.is_fp8) else y, lw.w_sh13, tag="sh13")
-            if lw.w_sh2.is_fp8 and Fn.wants_quant_act(y.shape[0], y.device):
-                _, aq = Fn.swiglu_clamp(gu, cfg.swiglu_limit, quant=True, tag="shact")
-                shared = Fn.linear(aq, lw.w_sh2, tag="sh2")
-            else:
-                shared = Fn.linear(Fn.swiglu_clamp(gu, cfg.swiglu_limit), lw.w_sh2, tag="sh2")
-        out = M.moe_experts(y, ids, wts, lw.experts, cfg.swiglu_limit, shared, cfg.n_routed_experts)
+        if not fork:
+            shared = self._shared_expert(lw, y, yq)
+        out = M.moe_experts(y, ids, wts, lw.experts, cfg.swiglu_limit, shared, cfg.n_routed_experts,
+                            shared_ready=ev_sh if fork else None)
         return self._all_reduce(out)
+
+    def _shared_expert(self, lw: LayerWeights, y: torch.Tensor, yq) -> Optional[torch.Tensor]:
+        cfg = self.cfg
+        if lw.w_sh13 is None:
+            return None
+        act = Fn.linear_swiglu(y, lw.w_sh13, cfg.swiglu_limit) if yq is None else None
+        if act is not None:
+            return Fn.linear(act, lw.w_sh2, tag="sh2")
+        gu = Fn.linear(yq if (yq is not None and lw.w_sh13.is_fp8) else y, lw.w_sh13, tag="sh13")
+        if lw.w_sh2.is_fp8 and Fn.wants_quant_act(y.shape[0], y.device):
+            _, aq = Fn.swiglu_clamp(gu, cfg.swiglu_limit, quant=True, tag="shact")
+            return Fn.linear(aq, lw.w_sh2, tag="sh2")
+        return Fn.linear(Fn.swiglu_clamp(gu, cfg.swiglu_limit), lw.w_sh2, tag="sh2")
 
     def layer(self, li: int, lw: LayerWeights, X: torch.Tensor, meta: StepMeta, pend=None, defer: bool = False):
         """One decoder layer.  `pend` = (sub-block output, streams, post, comb) left unmixed by the previous layer: its
