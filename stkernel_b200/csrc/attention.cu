@@ -64,6 +64,8 @@ __device__ __forceinline__ void load_row_bf16(const MlaCache& c, int slot, __nv_
 template <int NH>
 __global__ void __launch_bounds__(256)
 sparse_mla_split_kernel(MlaArgs a) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ uint8_t smraw[];
   const int D = a.D;
   const int DP = D + 2;                       // padded row (bank-conflict-free column reads)
@@ -195,6 +197,8 @@ __global__ void sparse_mla_combine_kernel(const float* __restrict__ partial, con
                                           __nv_bfloat16* __restrict__ out, long long ldo, int nh, int D, int n_splits,
                                           const int64_t* __restrict__ positions, const float* __restrict__ inv_freq,
                                           int R) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
   const float* base = partial + (static_cast<long long>(t) * n_splits * nh + h) * (D + 2);
   const long long sstride = static_cast<long long>(nh) * (D + 2);
@@ -281,7 +285,7 @@ STK_API int stk_sparse_mla(const void* q, long long ldt, const void* swa_cache, 
       cudaFuncSetAttribute(sparse_mla_split_kernel<NH_>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
       configured = true;                                                                                          \
     }                                                                                                             \
-    sparse_mla_split_kernel<NH_><<<grid, 256, smem, st>>>(a);                                                      \
+    launch_pdl(sparse_mla_split_kernel<NH_>, dim3(grid), dim3(256), smem, st, a);                                                      \
   }
   switch (NH) {
     case 4: STK_MLA(4) break;
@@ -293,7 +297,7 @@ STK_API int stk_sparse_mla(const void* q, long long ldt, const void* swa_cache, 
   }
 #undef STK_MLA
   dim3 g2(T, nh);
-  sparse_mla_combine_kernel<<<g2, 128, 0, st>>>(workspace, sink, (__nv_bfloat16*)out, ldo, nh, D, n_splits, nullptr, nullptr, 0);
+  launch_pdl(sparse_mla_combine_kernel, dim3(g2), dim3(128), 0, st, workspace, sink, (__nv_bfloat16*)out, ldo, nh, D, n_splits, nullptr, nullptr, 0);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -303,7 +307,7 @@ STK_API int stk_sparse_mla_combine(const float* workspace, const float* sink, vo
   if (T <= 0) return 0;
   if (D % 2) return -1;
   dim3 g2(T, nh);
-  sparse_mla_combine_kernel<<<g2, 128, 0, (cudaStream_t)stream>>>(workspace, sink, (__nv_bfloat16*)out, ldo, nh, D, n_splits,
+  launch_pdl(sparse_mla_combine_kernel, dim3(g2), dim3(128), 0, (cudaStream_t)stream, workspace, sink, (__nv_bfloat16*)out, ldo, nh, D, n_splits,
                                                                   positions, inv_freq, R);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -144,6 +144,8 @@ __device__ __forceinline__ void bfly_reduce_store(float (&v)[NH], float* out, in
 template <int NH>
 __global__ void __launch_bounds__(kThreads, 1)
 sparse_mla_tc_kernel(const MlaTcArgs a) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int kTmemCols = (5 * NH <= 128) ? 128 : (5 * NH <= 256) ? 256 : 512;
   constexpr int kQBytes = kPanels * NH * 128;
   constexpr int kPBytes = 2 * NH * 128;
@@ -488,7 +490,7 @@ static int launch_mla_tc(const MlaTcArgs& a, cudaStream_t st) {
     configured = true;
   }
   dim3 grid(a.T, a.n_splits);
-  sparse_mla_tc_kernel<NH><<<grid, kThreads, smem, st>>>(a);
+  launch_pdl(sparse_mla_tc_kernel<NH>, dim3(grid), dim3(kThreads), smem, st, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -34,6 +34,18 @@ __device__ __forceinline__ void set_status(int* status, int code, int detail) {
 
 constexpr uint32_t kSpinBudget = 20u * 1000u * 1000u;   // try_wait polls, ~ a second at most
 
+// ---- programmatic dependent launch -------------------------------------------
+// The decode step is a chain of short kernels.  Each one is launched with the programmatic-serialization attribute:
+// its CTAs may become resident while the previous kernel is still running.  A kernel first calls pdl_trigger() (so
+// that its own successor may do the same), touches only immutable data (weight prefetches into L2), and then calls
+// pdl_wait(), which returns once every earlier kernel of the stream has completed and its writes are visible.
+// Rules: every thread of every such kernel reaches pdl_wait() before its first access to anything another kernel
+// writes, and before any early return; nothing written by another kernel is touched ahead of it.  Launched without
+// the attribute both calls are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 // ---- shared-memory addressing ----------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -254,4 +266,24 @@ __device__ __forceinline__ float block_max(float v, float* red) {
   return t;
 }
 
+}  // namespace stk
+
+// ---- host: kernel launch with the programmatic-serialization attribute ---------
+extern "C" int stk_pdl_enabled();
+
+namespace stk {
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = stk_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 }  // namespace stk

@@ -4,6 +4,8 @@
 //
 // Replaces the reference's RMSNorm / fused_q_kv_rmsnorm (overlay/attention.py:779-785),
 // per_token_group_quant "armada" and SiluAndMulWithClamp (MEASUREMENTS.md:544-546).
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace stk {
@@ -12,6 +14,8 @@ namespace stk {
 __global__ void embed_hc_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict__ embed,
                                 __nv_bfloat16* __restrict__ out, int H, int hc, int vocab, int vocab_start,
                                 int vocab_end, int* status) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const long long id = ids[t];
   const bool in_vocab = id >= 0 && id < vocab;
@@ -37,6 +41,8 @@ struct NormJob {
 };
 
 __global__ void rmsnorm_kernel(NormJob j0, NormJob j1, float eps) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float sbuf[];     // H floats + 32
   const NormJob& j = blockIdx.y == 0 ? j0 : j1;
   const int t = blockIdx.x;
@@ -87,6 +93,8 @@ __global__ void rmsnorm_kernel(NormJob j0, NormJob j1, float eps) {
 // x bf16 [T, K] -> fp8 [T, K] + scales [K/128, ld] (scale = amax/448); one warp per group.
 __global__ void quant_fp8_group_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ q,
                                        long long ldq, float* __restrict__ scales, int scale_ld, int T, int K) {
+  pdl_trigger();
+  pdl_wait();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int groups = (K + 127) / 128;
@@ -115,6 +123,8 @@ __global__ void quant_fp8_group_kernel(const __nv_bfloat16* __restrict__ x, long
 __global__ void swiglu_clamp_kernel(const __nv_bfloat16* __restrict__ gu, long long ldg, __nv_bfloat16* __restrict__ act,
                                     long long lda, int I, float limit, uint8_t* q_out, long long ldq, float* q_scale,
                                     int q_scale_ld) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   for (int g = warp; g * 128 < I; g += nw) {
@@ -157,6 +167,8 @@ __global__ void swiglu_clamp_kernel(const __nv_bfloat16* __restrict__ gu, long l
 __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ w,
                                    const int* __restrict__ pair_row, const __nv_bfloat16* __restrict__ shared,
                                    __nv_bfloat16* __restrict__ out, int H, int topk) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 2;
   if (i >= H) return;
@@ -196,11 +208,27 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const fl
 
 using namespace stk;
 
+// Programmatic dependent launch of the decode-chain kernels: on unless STK_PDL=0 in the environment or switched off by
+// stk_set_pdl(0).
+static int g_pdl = -1;
+STK_API int stk_pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* e = getenv("STK_PDL");
+    g_pdl = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return g_pdl;
+}
+STK_API int stk_set_pdl(int on) {
+  g_pdl = on ? 1 : 0;
+  return 0;
+}
+
+
 STK_API int stk_embed_hc(const int64_t* ids, const void* embed, void* out, int T, int H, int hc, int vocab,
                          int vocab_start, int vocab_end, int* status, void* stream) {
   if (T <= 0) return 0;
   if (H % 8) return -1;
-  embed_hc_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(ids, (const __nv_bfloat16*)embed, (__nv_bfloat16*)out, H, hc,
+  launch_pdl(embed_hc_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, ids, (const __nv_bfloat16*)embed, (__nv_bfloat16*)out, H, hc,
                                                        vocab, vocab_start, vocab_end, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -224,7 +252,7 @@ STK_API int stk_rmsnorm(const void* x0, long long ldx0, const void* w0, void* ou
     configured = true;
   }
   dim3 grid(T, H1 > 0 ? 2 : 1);
-  rmsnorm_kernel<<<grid, 256, smem, (cudaStream_t)stream>>>(a, b, eps);
+  launch_pdl(rmsnorm_kernel, dim3(grid), dim3(256), smem, (cudaStream_t)stream, a, b, eps);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -260,7 +288,7 @@ STK_API int stk_quant_fp8_group128(const void* x, long long ldx, void* q, long l
   if (T <= 0) return 0;
   const long long warps = static_cast<long long>(T) * ((K + 127) / 128);
   const int blocks = static_cast<int>((warps + 7) / 8);
-  quant_fp8_group_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq,
+  launch_pdl(quant_fp8_group_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq,
                                                                    scales, scale_ld, T, K);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -268,7 +296,7 @@ STK_API int stk_quant_fp8_group128(const void* x, long long ldx, void* q, long l
 STK_API int stk_swiglu_clamp(const void* gu, long long ldg, void* act, long long lda, int T, int I, float limit,
                              void* q_out, long long ldq, float* q_scale, int q_scale_ld, void* stream) {
   if (T <= 0) return 0;
-  swiglu_clamp_kernel<<<T, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)gu, ldg, (__nv_bfloat16*)act, lda, I,
+  launch_pdl(swiglu_clamp_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)gu, ldg, (__nv_bfloat16*)act, lda, I,
                                                            limit, (uint8_t*)q_out, ldq, q_scale, q_scale_ld);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -278,7 +306,7 @@ STK_API int stk_moe_combine(const void* y, const float* w, const int* pair_row, 
   if (T <= 0) return 0;
   if (H % 2 || topk > 16) return -1;
   dim3 grid(T, (H / 2 + 127) / 128);
-  moe_combine_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)y, w, pair_row,
+  launch_pdl(moe_combine_kernel, dim3(grid), dim3(128), 0, (cudaStream_t)stream, (const __nv_bfloat16*)y, w, pair_row,
                                                           (const __nv_bfloat16*)shared, (__nv_bfloat16*)out, H, topk);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

@@ -23,6 +23,8 @@ indexer_scores_kernel(const void* __restrict__ q, const float* __restrict__ w, I
                       const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_req,
                       const int* __restrict__ n_valid, float* __restrict__ scores, long long ld_scores, int ih,
                       int q_fp8) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float sm[];     // ih * DI floats + ih weights
   float* qs = sm;
   float* ws = sm + ih * DI;
@@ -94,6 +96,8 @@ template <int PER>
 __global__ void __launch_bounds__(1024)
 topk_rows_reg_kernel(const float* __restrict__ scores, long long ld, const int* __restrict__ n_valid,
                      int* __restrict__ out, int k, int out_ld) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ int whist[32][256];
   __shared__ int hist[256];
   __shared__ uint32_t s_prefix;
@@ -214,6 +218,8 @@ topk_rows_reg_kernel(const float* __restrict__ scores, long long ld, const int* 
 __global__ void __launch_bounds__(1024)
 topk_rows_kernel(const float* __restrict__ scores, long long ld, const int* __restrict__ n_valid,
                  int* __restrict__ out, int k, int out_ld) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ int hist[256];
   __shared__ uint32_t s_prefix;
   __shared__ int s_remaining;
@@ -306,6 +312,8 @@ __global__ void topk_to_slots_kernel(const int* __restrict__ topk, int k, int to
                                      const int* __restrict__ block_table, int bt_stride,
                                      const int* __restrict__ tok_req, int* __restrict__ slots, int slots_ld,
                                      int* __restrict__ lens, int max_rows, int* status) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   __shared__ int cnt;
   if (threadIdx.x == 0) cnt = 0;
@@ -353,7 +361,7 @@ STK_API int stk_indexer_scores(const void* q, const float* w, const void* kcache
       cudaFuncSetAttribute(indexer_scores_kernel<DI_>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024); \
       configured = true;                                                                                      \
     }                                                                                                         \
-    indexer_scores_kernel<DI_><<<grid, 128, smem, st>>>(q, w, kc, block_table, bt_stride, tok_req, n_valid,    \
+    launch_pdl(indexer_scores_kernel<DI_>, dim3(grid), dim3(128), smem, st, q, w, kc, block_table, bt_stride, tok_req, n_valid,    \
                                                         scores, ld_scores, ih, q_fp8);                        \
   }
   if (di == 128) STK_IDX(128)
@@ -369,14 +377,14 @@ STK_API int stk_topk_rows(const float* scores, long long ld, const int* n_valid,
   if (T <= 0) return 0;
   // ld bounds every row's valid length: rows that fit in registers take the single-read kernel
   if (ld <= 8 * 1024) {
-    topk_rows_reg_kernel<8><<<T, 1024, 0, (cudaStream_t)stream>>>(scores, ld, n_valid, out, k, out_ld);
+    launch_pdl(topk_rows_reg_kernel<8>, dim3(T), dim3(1024), 0, (cudaStream_t)stream, scores, ld, n_valid, out, k, out_ld);
     return cudaGetLastError() == cudaSuccess ? 0 : -4;
   }
   if (ld <= 16 * 1024) {
-    topk_rows_reg_kernel<16><<<T, 1024, 0, (cudaStream_t)stream>>>(scores, ld, n_valid, out, k, out_ld);
+    launch_pdl(topk_rows_reg_kernel<16>, dim3(T), dim3(1024), 0, (cudaStream_t)stream, scores, ld, n_valid, out, k, out_ld);
     return cudaGetLastError() == cudaSuccess ? 0 : -4;
   }
-  topk_rows_kernel<<<T, 1024, 0, (cudaStream_t)stream>>>(scores, ld, n_valid, out, k, out_ld);
+  launch_pdl(topk_rows_kernel, dim3(T), dim3(1024), 0, (cudaStream_t)stream, scores, ld, n_valid, out, k, out_ld);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -384,7 +392,7 @@ STK_API int stk_topk_to_slots(const int* topk, int k, int topk_ld, const int* bl
                               const int* tok_req, int* slots, int slots_ld, int* lens, int T, int max_rows,
                               int* status, void* stream) {
   if (T <= 0) return 0;
-  topk_to_slots_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(topk, k, topk_ld, block_table, bt_stride, tok_req, slots,
+  launch_pdl(topk_to_slots_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, topk, k, topk_ld, block_table, bt_stride, tok_req, slots,
                                                             slots_ld, lens, max_rows, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

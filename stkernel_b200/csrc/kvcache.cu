@@ -62,6 +62,8 @@ __device__ __forceinline__ void q_norm_rope_body(int block, __nv_bfloat16* __res
 __global__ void q_norm_rope_kernel(__nv_bfloat16* __restrict__ q, long long ldt, const int64_t* __restrict__ positions,
                                    const float* __restrict__ inv_freq, int T, int nh, int D, int R, float eps,
                                    int do_norm, int inverse) {
+  pdl_trigger();
+  pdl_wait();
   q_norm_rope_body(blockIdx.x, q, ldt, positions, inv_freq, T, nh, D, R, eps, do_norm, inverse);
 }
 
@@ -140,6 +142,8 @@ __global__ void kv_rope_quant_insert_kernel(const __nv_bfloat16* __restrict__ kv
                                             const int64_t* __restrict__ positions, const int64_t* __restrict__ slots,
                                             const float* __restrict__ inv_freq, CacheGeom cache, int T, int D, int R,
                                             long long num_slots, int* status) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float sm[];
   kv_rope_quant_insert_body(blockIdx.x, sm, kv, ldk, positions, slots, inv_freq, cache, T, D, R, num_slots, status);
 }
@@ -152,6 +156,8 @@ q_rope_kv_insert_kernel(__nv_bfloat16* __restrict__ q, long long ldt, int nh, fl
                         const __nv_bfloat16* __restrict__ kv, long long ldk, const int64_t* __restrict__ positions,
                         const int64_t* __restrict__ slots, const float* __restrict__ inv_freq, CacheGeom cache, int T,
                         int D, int R, long long num_slots, int* status) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float sm[];
   if (static_cast<int>(blockIdx.x) < q_blocks) {
     q_norm_rope_body(blockIdx.x, q, ldt, positions, inv_freq, T, nh, D, R, eps, 1, 0);
@@ -224,6 +230,8 @@ __device__ __forceinline__ const float* compress_src_row(const CompressArgs& a, 
 // One CTA per token; only the token that closes a window does work.
 __global__ void __launch_bounds__(128)
 compress_windows_kernel(CompressArgs a) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float sm[];    // D floats + 32
   const int t = blockIdx.x;
   const long long pos = a.positions[t];
@@ -313,6 +321,8 @@ compress_windows_kernel(CompressArgs a) {
 
 // Keep the raw rows of the last `ring` positions of each request (runs after compress_windows).
 __global__ void compress_save_state_kernel(CompressArgs a, const int* __restrict__ tok_last_pos) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const long long pos = a.positions[t];
   if (pos < 0 || pos + a.ring <= tok_last_pos[t]) return;
@@ -328,6 +338,8 @@ __global__ void indexer_q_prep_kernel(const __nv_bfloat16* __restrict__ q, long 
                                       const int64_t* __restrict__ positions, const float* __restrict__ inv_freq,
                                       void* __restrict__ q_out, float* __restrict__ w_out, int T, int ih, int d, int R,
                                       int quantize) {
+  pdl_trigger();
+  pdl_wait();
   const int wp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (wp >= T * ih) return;
@@ -378,7 +390,7 @@ STK_API int stk_q_norm_rope(void* q, long long ldt, const int64_t* positions, co
   if (T <= 0) return 0;
   if (D % 2 || R % 2) return -1;
   const long long warps = static_cast<long long>(T) * nh;
-  q_norm_rope_kernel<<<static_cast<int>((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+  launch_pdl(q_norm_rope_kernel, dim3(static_cast<int>((warps + 7) / 8)), dim3(256), 0, (cudaStream_t)stream, 
       (__nv_bfloat16*)q, ldt, positions, inv_freq, T, nh, D, R, eps, do_norm, inverse);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -390,7 +402,7 @@ STK_API int stk_kv_rope_quant_insert(const void* kv, long long ldk, const int64_
   if (D % 2 || (fp8 && ((D - R) % 64 || (D - R) / 64 > 8))) return -1;
   CacheGeom g{(uint8_t*)cache, page_stride, data_bytes, fp8};
   const int wpb = 4;
-  kv_rope_quant_insert_kernel<<<(T + wpb - 1) / wpb, wpb * 32, wpb * D * sizeof(float), (cudaStream_t)stream>>>(
+  launch_pdl(kv_rope_quant_insert_kernel, dim3((T + wpb - 1) / wpb), dim3(wpb * 32), wpb * D * sizeof(float), (cudaStream_t)stream, 
       (const __nv_bfloat16*)kv, ldk, positions, slots, inv_freq, g, T, D, R, num_slots, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -404,7 +416,7 @@ STK_API int stk_q_rope_kv_insert(void* q, long long ldt, int nh, float eps, cons
   CacheGeom g{(uint8_t*)cache, page_stride, data_bytes, fp8};
   const int q_blocks = static_cast<int>((static_cast<long long>(T) * nh + 7) / 8);
   const int kv_blocks = (T + 7) / 8;
-  q_rope_kv_insert_kernel<<<q_blocks + kv_blocks, 256, 8 * D * sizeof(float), (cudaStream_t)stream>>>(
+  launch_pdl(q_rope_kv_insert_kernel, dim3(q_blocks + kv_blocks), dim3(256), 8 * D * sizeof(float), (cudaStream_t)stream, 
       (__nv_bfloat16*)q, ldt, nh, eps, q_blocks, (const __nv_bfloat16*)kv, ldk, positions, slots, inv_freq, g, T, D, R,
       num_slots, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
@@ -433,8 +445,8 @@ STK_API int stk_compress_windows(const float* kvs, long long kvs_ld, const float
   a.idx_format = idx_format; a.T = T; a.D = D; a.R = R; a.ratio = ratio; a.c = c; a.ring = ring;
   a.num_slots = num_slots; a.eps = eps; a.status = status;
   cudaStream_t st = (cudaStream_t)stream;
-  compress_windows_kernel<<<T, 128, (D + 32) * sizeof(float), st>>>(a);
-  compress_save_state_kernel<<<T, 128, 0, st>>>(a, tok_last_pos);
+  launch_pdl(compress_windows_kernel, dim3(T), dim3(128), (D + 32) * sizeof(float), st, a);
+  launch_pdl(compress_save_state_kernel, dim3(T), dim3(128), 0, st, a, tok_last_pos);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
@@ -444,7 +456,7 @@ STK_API int stk_indexer_q_prep(const void* q, long long ldq, const float* w, lon
   if (T <= 0) return 0;
   if (d % 2 || d > 256) return -1;
   const long long warps = static_cast<long long>(T) * ih;
-  indexer_q_prep_kernel<<<static_cast<int>((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+  launch_pdl(indexer_q_prep_kernel, dim3(static_cast<int>((warps + 7) / 8)), dim3(256), 0, (cudaStream_t)stream, 
       (const __nv_bfloat16*)q, ldq, w, ldw, positions, inv_freq, q_out, w_out, T, ih, d, R, quantize);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

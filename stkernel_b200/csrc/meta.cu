@@ -14,6 +14,8 @@ namespace stk {
 __global__ void swa_indices_kernel(const int64_t* __restrict__ positions, const int* __restrict__ tok_req,
                                    const int* __restrict__ block_table, int bt_stride, int* __restrict__ slots,
                                    int ld, int* __restrict__ lens, int window) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const long long pos = positions[t];
   const int req = tok_req[t];
@@ -41,6 +43,8 @@ __global__ void swa_indices_noncausal_kernel(const int* __restrict__ tok_req, co
                                              const int* __restrict__ seq_len, const int* __restrict__ block_table,
                                              int bt_stride, int* __restrict__ slots, int ld, int* __restrict__ lens,
                                              int window) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int req = tok_req[t];
   int n = 0;
@@ -65,6 +69,8 @@ __global__ void swa_indices_noncausal_kernel(const int* __restrict__ tok_req, co
 
 __global__ void compressed_valid_kernel(const int64_t* __restrict__ positions, int* __restrict__ n_valid, int T,
                                         int ratio) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= T) return;
   const long long pos = positions[t];
@@ -74,6 +80,8 @@ __global__ void compressed_valid_kernel(const int64_t* __restrict__ positions, i
 __global__ void c128_indices_kernel(const int64_t* __restrict__ positions, const int* __restrict__ tok_req,
                                     const int* __restrict__ block_table, int bt_stride, int* __restrict__ slots,
                                     int ld, int* __restrict__ lens, int ratio, int cap) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const long long pos = positions[t];
   const int req = tok_req[t];
@@ -99,6 +107,8 @@ __global__ void token_maps_kernel(const int* __restrict__ query_start, const int
                                   int64_t* __restrict__ positions, int* __restrict__ first_pos,
                                   int* __restrict__ last_pos, const int* __restrict__ block_table, int bt_stride,
                                   int64_t* __restrict__ slot_mapping, int T_padded) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= T_padded) return;
   int r = -1;
@@ -131,7 +141,7 @@ using namespace stk;
 STK_API int stk_swa_indices(const int64_t* positions, const int* tok_req, const int* block_table, int bt_stride,
                             int* slots, int ld, int* lens, int T, int window, void* stream) {
   if (T <= 0) return 0;
-  swa_indices_kernel<<<T, 128, 0, (cudaStream_t)stream>>>(positions, tok_req, block_table, bt_stride, slots, ld, lens,
+  launch_pdl(swa_indices_kernel, dim3(T), dim3(128), 0, (cudaStream_t)stream, positions, tok_req, block_table, bt_stride, slots, ld, lens,
                                                           window);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -140,21 +150,21 @@ STK_API int stk_swa_indices_noncausal(const int* tok_req, const int* prefix_len,
                                       const int* block_table, int bt_stride, int* slots, int ld, int* lens, int T,
                                       int window, void* stream) {
   if (T <= 0) return 0;
-  swa_indices_noncausal_kernel<<<T, 128, 0, (cudaStream_t)stream>>>(tok_req, prefix_len, seq_len, block_table,
+  launch_pdl(swa_indices_noncausal_kernel, dim3(T), dim3(128), 0, (cudaStream_t)stream, tok_req, prefix_len, seq_len, block_table,
                                                                     bt_stride, slots, ld, lens, window);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
 STK_API int stk_compressed_valid(const int64_t* positions, int* n_valid, int T, int ratio, void* stream) {
   if (T <= 0) return 0;
-  compressed_valid_kernel<<<(T + 127) / 128, 128, 0, (cudaStream_t)stream>>>(positions, n_valid, T, ratio);
+  launch_pdl(compressed_valid_kernel, dim3((T + 127) / 128), dim3(128), 0, (cudaStream_t)stream, positions, n_valid, T, ratio);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
 STK_API int stk_c128_indices(const int64_t* positions, const int* tok_req, const int* block_table, int bt_stride,
                              int* slots, int ld, int* lens, int T, int ratio, int cap, void* stream) {
   if (T <= 0) return 0;
-  c128_indices_kernel<<<T, 128, 0, (cudaStream_t)stream>>>(positions, tok_req, block_table, bt_stride, slots, ld, lens,
+  launch_pdl(c128_indices_kernel, dim3(T), dim3(128), 0, (cudaStream_t)stream, positions, tok_req, block_table, bt_stride, slots, ld, lens,
                                                            ratio, cap);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -163,7 +173,7 @@ STK_API int stk_token_maps(const int* query_start, const int* req_rows, const in
                            int64_t* positions, int* first_pos, int* last_pos, const int* block_table, int bt_stride,
                            int64_t* slot_mapping, int T_padded, void* stream) {
   if (T_padded <= 0) return 0;
-  token_maps_kernel<<<(T_padded + 127) / 128, 128, 0, (cudaStream_t)stream>>>(query_start, req_rows, start_pos, n_req,
+  launch_pdl(token_maps_kernel, dim3((T_padded + 127) / 128), dim3(128), 0, (cudaStream_t)stream, query_start, req_rows, start_pos, n_req,
                                                                               tok_req, positions, first_pos, last_pos,
                                                                               block_table, bt_stride, slot_mapping,
                                                                               T_padded);

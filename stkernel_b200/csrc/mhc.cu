@@ -237,6 +237,8 @@ template <int HCM>
 __global__ void __launch_bounds__(256)
 mhc_post_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                 const float* __restrict__ post, const float* __restrict__ comb, __nv_bfloat16* __restrict__ out, int H) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   __shared__ float sp[HCM], sc[HCM * HCM];
   if (threadIdx.x < HCM) sp[threadIdx.x] = post[t * HCM + threadIdx.x];
@@ -324,8 +326,8 @@ STK_API int stk_mhc_post(const void* x, const void* res, const float* post, cons
   if (gy > 8) gy = 8;
   dim3 grid(T, gy);
   cudaStream_t st = (cudaStream_t)stream;
-  if (hc == 4) mhc_post_kernel<4><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, post, comb, (__nv_bfloat16*)out, H);
-  else if (hc == 2) mhc_post_kernel<2><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)res, post, comb, (__nv_bfloat16*)out, H);
+  if (hc == 4) launch_pdl(mhc_post_kernel<4>, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, post, comb, (__nv_bfloat16*)out, H);
+  else if (hc == 2) launch_pdl(mhc_post_kernel<2>, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, post, comb, (__nv_bfloat16*)out, H);
   else return -2;
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -375,6 +377,17 @@ mhc_cluster_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   __shared__ float s_po[4], s_co[16];
   const int HC = H * hc;
   const bool fused = fz.fa != nullptr;
+  // ahead of the previous kernel's completion: this CTA's slice of the (immutable) mix weights goes towards L2
+  pdl_trigger();
+  {
+    const int pslice = ((HC / kClusterSize) + 1) & ~1;
+    const int pk0 = crank * pslice, pk1 = min(HC, pk0 + pslice);
+    for (int idx = threadIdx.x; idx < NMIX * ((pk1 - pk0 + 31) / 32); idx += blockDim.x) {
+      const int j = idx % NMIX, c = idx / NMIX;
+      prefetch_l2(fn + static_cast<long long>(j) * HC + pk0 + c * 32);
+    }
+  }
+  pdl_wait();
   if (fused) {
     if (threadIdx.x < hc) s_po[threadIdx.x] = fz.post_old[t * hc + threadIdx.x];
     if (threadIdx.x < hc * hc) s_co[threadIdx.x] = fz.comb_old[t * hc * hc + threadIdx.x];
@@ -616,13 +629,15 @@ static int mhc_cluster_launch(const void* x, const float* fn, const float* base,
   cfg.blockDim = dim3(kClusterThreads);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = (cudaStream_t)stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = kClusterSize;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = stk_pdl_enabled() ? 2 : 1;
   const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
   const __nv_bfloat16* nw = (const __nv_bfloat16*)norm_w;
   __nv_bfloat16* yp = (__nv_bfloat16*)y;

@@ -25,6 +25,8 @@ __global__ void router_kernel(const float* __restrict__ logits, long long ldl, c
                               const int* __restrict__ tid2eid, const int64_t* __restrict__ token_ids, int vocab,
                               int* __restrict__ ids, float* __restrict__ weights, int T, int E, int topk, int scoring,
                               int renorm, float scaling, int* status) {
+  pdl_trigger();
+  pdl_wait();
   const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (t >= T) return;
@@ -101,6 +103,8 @@ __global__ void router_kernel(const float* __restrict__ logits, long long ldl, c
 __global__ void __launch_bounds__(1024)
 moe_align_kernel(const int* __restrict__ ids, int n_pairs, int e_start, int e_local, int* __restrict__ sorted,
                  int* __restrict__ pair_row, int* __restrict__ offsets, int* __restrict__ sorted_expert) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ int sh[];          // counts[e_local + 1]
   int* counts = sh;
   for (int i = threadIdx.x; i <= e_local; i += blockDim.x) counts[i] = 0;
@@ -313,6 +317,8 @@ expert_fc1_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, ExpertW w1
                   const int* __restrict__ sorted_expert, const int* __restrict__ offsets, int e_local, int topk,
                   __half* __restrict__ act, int H, int I, float limit, const int* __restrict__ direct_ids,
                   int e_start) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ uint4 xs[];
   const int row = blockIdx.y;
   int pair, e;
@@ -364,6 +370,8 @@ __global__ void __launch_bounds__(256)
 expert_fc2_kernel(const __half* __restrict__ act, ExpertW w2, const int* __restrict__ sorted_expert,
                   const int* __restrict__ offsets, int e_local, __nv_bfloat16* __restrict__ y, int H, int I,
                   const int* __restrict__ direct_ids, int e_start) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ uint4 xs[];
   const int row = blockIdx.y;
   int e;
@@ -410,7 +418,7 @@ STK_API int stk_router(const float* logits, long long ldl, const float* bias, co
                        int scoring, int renorm, float scaling, int* status, void* stream) {
   if (T <= 0) return 0;
   if (E > 512 || topk > 32) return -1;
-  router_kernel<<<(T + 7) / 8, 256, 0, (cudaStream_t)stream>>>(logits, ldl, bias, tid2eid, token_ids, vocab, ids,
+  launch_pdl(router_kernel, dim3((T + 7) / 8), dim3(256), 0, (cudaStream_t)stream, logits, ldl, bias, tid2eid, token_ids, vocab, ids,
                                                                weights, T, E, topk, scoring, renorm, scaling, status);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
@@ -429,7 +437,7 @@ STK_API int stk_moe_align(const int* ids, int n_pairs, int e_start, int e_local,
                                                              pair_row, sorted_expert);
     return cudaGetLastError() == cudaSuccess ? 0 : -4;
   }
-  moe_align_kernel<<<1, 1024, (e_local + 1) * sizeof(int), (cudaStream_t)stream>>>(ids, n_pairs, e_start, e_local,
+  launch_pdl(moe_align_kernel, dim3(1), dim3(1024), (e_local + 1) * sizeof(int), (cudaStream_t)stream, ids, n_pairs, e_start, e_local,
                                                                                    sorted, pair_row, offsets,
                                                                                    sorted_expert);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
@@ -447,7 +455,7 @@ STK_API int stk_moe_expert_fc1(const void* x, long long ldx, const void* w13, co
   const size_t smem = ((H + 1023) / 1024) * 2048;
   cudaStream_t st = (cudaStream_t)stream;
   const int iters = (H / 32 + 31) / 32;
-#define STK_FC1(I_) expert_fc1_kernel<I_><<<grid, 256, smem, st>>>((const __nv_bfloat16*)x, ldx, w, sorted, sorted_expert, offsets, e_local, topk, (__half*)act, H, I, limit, direct_ids, e_start)
+#define STK_FC1(I_) launch_pdl(expert_fc1_kernel<I_>, dim3(grid), dim3(256), smem, st, (const __nv_bfloat16*)x, ldx, w, sorted, sorted_expert, offsets, e_local, topk, (__half*)act, H, I, limit, direct_ids, e_start)
   if (iters <= 1) STK_FC1(1); else if (iters <= 2) STK_FC1(2); else if (iters <= 4) STK_FC1(4); else if (iters <= 8) STK_FC1(8); else STK_FC1(16);
 #undef STK_FC1
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
@@ -463,7 +471,7 @@ STK_API int stk_moe_expert_fc2(const void* act, const void* w2, const void* s2, 
   const size_t smem = ((I + 1023) / 1024) * 2048;
   cudaStream_t st = (cudaStream_t)stream;
   const int iters = (I / 32 + 31) / 32;
-#define STK_FC2(I_) expert_fc2_kernel<I_><<<grid, 256, smem, st>>>((const __half*)act, w, sorted_expert, offsets, e_local, (__nv_bfloat16*)y, H, I, direct_ids, e_start)
+#define STK_FC2(I_) launch_pdl(expert_fc2_kernel<I_>, dim3(grid), dim3(256), smem, st, (const __half*)act, w, sorted_expert, offsets, e_local, (__nv_bfloat16*)y, H, I, direct_ids, e_start)
   if (iters <= 1) STK_FC2(1); else if (iters <= 2) STK_FC2(2); else if (iters <= 4) STK_FC2(4); else if (iters <= 8) STK_FC2(8); else STK_FC2(16);
 #undef STK_FC2
   return cudaGetLastError() == cudaSuccess ? 0 : -4;

@@ -46,6 +46,8 @@ gumbel_argmax_partial_kernel(const T* __restrict__ logits, long long ld, const f
                              const int64_t* __restrict__ seed, const int64_t* __restrict__ pos,
                              const int* __restrict__ row_group, int pos_stride, float* __restrict__ part_val,
                              int* __restrict__ part_idx, float* __restrict__ processed, long long ldp, int V) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float sv[8];
   __shared__ int si[8];
   const int row = blockIdx.x;
@@ -85,6 +87,8 @@ gumbel_argmax_partial_kernel(const T* __restrict__ logits, long long ld, const f
 
 __global__ void gumbel_argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
                                            int chunks, int64_t* __restrict__ out, int rows) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= rows) return;
   float best = -INFINITY;
@@ -314,14 +318,14 @@ STK_API int stk_gumbel_argmax(const void* logits, long long ld, int logits_bf16,
   dim3 grid(rows, chunks);
   cudaStream_t st = (cudaStream_t)stream;
   if (logits_bf16)
-    gumbel_argmax_partial_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)logits, ld, temperature,
+    launch_pdl(gumbel_argmax_partial_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)logits, ld, temperature,
                                                                       seed, pos, row_group, pos_stride, part_val,
                                                                       part_idx, processed, ldp, V);
   else
-    gumbel_argmax_partial_kernel<float><<<grid, 256, 0, st>>>((const float*)logits, ld, temperature, seed, pos,
+    launch_pdl(gumbel_argmax_partial_kernel<float>, dim3(grid), dim3(256), 0, st, (const float*)logits, ld, temperature, seed, pos,
                                                               row_group, pos_stride, part_val, part_idx, processed,
                                                               ldp, V);
-  gumbel_argmax_final_kernel<<<(rows + 127) / 128, 128, 0, st>>>(part_val, part_idx, chunks, out, rows);
+  launch_pdl(gumbel_argmax_final_kernel, dim3((rows + 127) / 128), dim3(128), 0, st, part_val, part_idx, chunks, out, rows);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

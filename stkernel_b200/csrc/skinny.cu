@@ -100,6 +100,22 @@ skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const f
   const int grp = group_rows > 0 ? (blockIdx.x * 8 * rows_per_warp) / group_rows : 0;
   __shared__ float s_xscale[kSkinnyMaxT];
   __shared__ float s_red[32];
+  // Ahead of the previous kernel's completion: pull this CTA's weight rows (immutable) towards L2, one request per
+  // 128-byte line, so that the row loop below starts on L2 hits while the activations are still being produced.
+  pdl_trigger();
+  {
+    const int pw = threadIdx.x >> 5, pl = threadIdx.x & 31;
+    const int pn0 = (blockIdx.x * 8 + pw) * rows_per_warp;
+    const int row_bytes = kFp8 ? K : 2 * K;
+    for (int pass = 0; pass < (kSwiglu ? 2 : 1); ++pass)
+      for (int r = 0; r < rows_per_warp; ++r) {
+        const int n = pn0 + r;
+        if (n >= N) break;
+        const uint8_t* wrow = W + static_cast<long long>(n + pass * N) * ldw_bytes;
+        for (int b = pl * 128; b < row_bytes; b += 32 * 128) prefetch_l2(wrow + b);
+      }
+  }
+  pdl_wait();
   skinny_fill_x<T, kFp8>(reinterpret_cast<__half*>(xs4), x + static_cast<long long>(grp) * K, ldx, K, iters16, s_xscale, s_red, t_valid);
   __syncthreads();
   float xsc[T];
@@ -244,9 +260,8 @@ STK_API int stk_skinny_linear(const void* W, long long ldw, int is_fp8, const fl
       cudaFuncSetAttribute(skinny_linear_kernel<T_, F_, I_, S_>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); \
       configured = true;                                                                                               \
     }                                                                                                                  \
-    skinny_linear_kernel<T_, F_, I_, S_><<<grid, 256, smem, st>>>((const uint8_t*)W, ldw_bytes, w_scale, w_scale_ld,       \
-                                                              (const __nv_bfloat16*)x, ldx, out, ldo, N, K, out_fp32,  \
-                                                              rpw, group_rows, limit, T);                              \
+    launch_pdl(skinny_linear_kernel<T_, F_, I_, S_>, dim3(grid), dim3(256), smem, st, (const uint8_t*)W, ldw_bytes,     \
+               w_scale, w_scale_ld, (const __nv_bfloat16*)x, ldx, out, ldo, N, K, out_fp32, rpw, group_rows, limit, T); \
   }
 #define STK_SK2(T_, F_)                                                                                 \
   {                                                                                                     \
