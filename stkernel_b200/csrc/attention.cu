@@ -64,8 +64,8 @@ __device__ __forceinline__ void load_row_bf16(const MlaCache& c, int slot, __nv_
 template <int NH>
 __global__ void __launch_bounds__(256)
 sparse_mla_split_kernel(MlaArgs a) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   extern __shared__ uint8_t smraw[];
   const int D = a.D;
   const int DP = D + 2;                       // padded row (bank-conflict-free column reads)
@@ -197,8 +197,8 @@ __global__ void sparse_mla_combine_kernel(const float* __restrict__ partial, con
                                           __nv_bfloat16* __restrict__ out, long long ldo, int nh, int D, int n_splits,
                                           const int64_t* __restrict__ positions, const float* __restrict__ inv_freq,
                                           int R) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x, h = blockIdx.y;
   const float* base = partial + (static_cast<long long>(t) * n_splits * nh + h) * (D + 2);
   const long long sstride = static_cast<long long>(nh) * (D + 2);

@@ -144,8 +144,8 @@ __device__ __forceinline__ void bfly_reduce_store(float (&v)[NH], float* out, in
 template <int NH>
 __global__ void __launch_bounds__(kThreads, 1)
 sparse_mla_tc_kernel(const MlaTcArgs a) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   constexpr int kTmemCols = (5 * NH <= 128) ? 128 : (5 * NH <= 256) ? 256 : 512;
   constexpr int kQBytes = kPanels * NH * 128;
   constexpr int kPBytes = 2 * NH * 128;

@@ -36,12 +36,13 @@ constexpr uint32_t kSpinBudget = 20u * 1000u * 1000u;   // try_wait polls, ~ a s
 
 // ---- programmatic dependent launch -------------------------------------------
 // The decode step is a chain of short kernels.  Each one is launched with the programmatic-serialization attribute:
-// its CTAs may become resident while the previous kernel is still running.  A kernel first calls pdl_trigger() (so
-// that its own successor may do the same), touches only immutable data (weight prefetches into L2), and then calls
-// pdl_wait(), which returns once every earlier kernel of the stream has completed and its writes are visible.
+// its CTAs may become resident while the previous kernel is still running.  A kernel first touches only immutable
+// data (weight prefetches towards L2), then calls pdl_wait(), which returns once every earlier kernel of the stream
+// has completed and its writes are visible, and then pdl_trigger(), which lets its own successor become resident and
+// prefetch while this kernel computes (a lookahead of one kernel: triggering ahead of the wait lets the whole chain
+// pile up and prefetch more than L2 holds, which measured slower).
 // Rules: every thread of every such kernel reaches pdl_wait() before its first access to anything another kernel
-// writes, and before any early return; nothing written by another kernel is touched ahead of it.  Launched without
-// the attribute both calls are no-ops.
+// writes, and before any early return.  Launched without the attribute both calls are no-ops.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }

@@ -14,8 +14,8 @@ namespace stk {
 __global__ void embed_hc_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict__ embed,
                                 __nv_bfloat16* __restrict__ out, int H, int hc, int vocab, int vocab_start,
                                 int vocab_end, int* status) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   const long long id = ids[t];
   const bool in_vocab = id >= 0 && id < vocab;
@@ -41,8 +41,8 @@ struct NormJob {
 };
 
 __global__ void rmsnorm_kernel(NormJob j0, NormJob j1, float eps) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   extern __shared__ float sbuf[];     // H floats + 32
   const NormJob& j = blockIdx.y == 0 ? j0 : j1;
   const int t = blockIdx.x;
@@ -93,8 +93,8 @@ __global__ void rmsnorm_kernel(NormJob j0, NormJob j1, float eps) {
 // x bf16 [T, K] -> fp8 [T, K] + scales [K/128, ld] (scale = amax/448); one warp per group.
 __global__ void quant_fp8_group_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ q,
                                        long long ldq, float* __restrict__ scales, int scale_ld, int T, int K) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int groups = (K + 127) / 128;
@@ -123,8 +123,8 @@ __global__ void quant_fp8_group_kernel(const __nv_bfloat16* __restrict__ x, long
 __global__ void swiglu_clamp_kernel(const __nv_bfloat16* __restrict__ gu, long long ldg, __nv_bfloat16* __restrict__ act,
                                     long long lda, int I, float limit, uint8_t* q_out, long long ldq, float* q_scale,
                                     int q_scale_ld) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   for (int g = warp; g * 128 < I; g += nw) {
@@ -167,8 +167,8 @@ __global__ void swiglu_clamp_kernel(const __nv_bfloat16* __restrict__ gu, long l
 __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ w,
                                    const int* __restrict__ pair_row, const __nv_bfloat16* __restrict__ shared,
                                    __nv_bfloat16* __restrict__ out, int H, int topk) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 2;
   if (i >= H) return;

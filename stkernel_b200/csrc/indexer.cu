@@ -23,8 +23,8 @@ indexer_scores_kernel(const void* __restrict__ q, const float* __restrict__ w, I
                       const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_req,
                       const int* __restrict__ n_valid, float* __restrict__ scores, long long ld_scores, int ih,
                       int q_fp8) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   extern __shared__ float sm[];     // ih * DI floats + ih weights
   float* qs = sm;
   float* ws = sm + ih * DI;
@@ -96,8 +96,8 @@ template <int PER>
 __global__ void __launch_bounds__(1024)
 topk_rows_reg_kernel(const float* __restrict__ scores, long long ld, const int* __restrict__ n_valid,
                      int* __restrict__ out, int k, int out_ld) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   __shared__ int whist[32][256];
   __shared__ int hist[256];
   __shared__ uint32_t s_prefix;
@@ -218,8 +218,8 @@ topk_rows_reg_kernel(const float* __restrict__ scores, long long ld, const int* 
 __global__ void __launch_bounds__(1024)
 topk_rows_kernel(const float* __restrict__ scores, long long ld, const int* __restrict__ n_valid,
                  int* __restrict__ out, int k, int out_ld) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   __shared__ int hist[256];
   __shared__ uint32_t s_prefix;
   __shared__ int s_remaining;
@@ -312,8 +312,8 @@ __global__ void topk_to_slots_kernel(const int* __restrict__ topk, int k, int to
                                      const int* __restrict__ block_table, int bt_stride,
                                      const int* __restrict__ tok_req, int* __restrict__ slots, int slots_ld,
                                      int* __restrict__ lens, int max_rows, int* status) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   __shared__ int cnt;
   if (threadIdx.x == 0) cnt = 0;

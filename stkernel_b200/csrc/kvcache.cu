@@ -62,8 +62,8 @@ __device__ __forceinline__ void q_norm_rope_body(int block, __nv_bfloat16* __res
 __global__ void q_norm_rope_kernel(__nv_bfloat16* __restrict__ q, long long ldt, const int64_t* __restrict__ positions,
                                    const float* __restrict__ inv_freq, int T, int nh, int D, int R, float eps,
                                    int do_norm, int inverse) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   q_norm_rope_body(blockIdx.x, q, ldt, positions, inv_freq, T, nh, D, R, eps, do_norm, inverse);
 }
 
@@ -142,8 +142,8 @@ __global__ void kv_rope_quant_insert_kernel(const __nv_bfloat16* __restrict__ kv
                                             const int64_t* __restrict__ positions, const int64_t* __restrict__ slots,
                                             const float* __restrict__ inv_freq, CacheGeom cache, int T, int D, int R,
                                             long long num_slots, int* status) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   extern __shared__ float sm[];
   kv_rope_quant_insert_body(blockIdx.x, sm, kv, ldk, positions, slots, inv_freq, cache, T, D, R, num_slots, status);
 }
@@ -156,8 +156,8 @@ q_rope_kv_insert_kernel(__nv_bfloat16* __restrict__ q, long long ldt, int nh, fl
                         const __nv_bfloat16* __restrict__ kv, long long ldk, const int64_t* __restrict__ positions,
                         const int64_t* __restrict__ slots, const float* __restrict__ inv_freq, CacheGeom cache, int T,
                         int D, int R, long long num_slots, int* status) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   extern __shared__ float sm[];
   if (static_cast<int>(blockIdx.x) < q_blocks) {
     q_norm_rope_body(blockIdx.x, q, ldt, positions, inv_freq, T, nh, D, R, eps, 1, 0);
@@ -230,8 +230,8 @@ __device__ __forceinline__ const float* compress_src_row(const CompressArgs& a, 
 // One CTA per token; only the token that closes a window does work.
 __global__ void __launch_bounds__(128)
 compress_windows_kernel(CompressArgs a) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   extern __shared__ float sm[];    // D floats + 32
   const int t = blockIdx.x;
   const long long pos = a.positions[t];
@@ -321,8 +321,8 @@ compress_windows_kernel(CompressArgs a) {
 
 // Keep the raw rows of the last `ring` positions of each request (runs after compress_windows).
 __global__ void compress_save_state_kernel(CompressArgs a, const int* __restrict__ tok_last_pos) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   const long long pos = a.positions[t];
   if (pos < 0 || pos + a.ring <= tok_last_pos[t]) return;
@@ -338,8 +338,8 @@ __global__ void indexer_q_prep_kernel(const __nv_bfloat16* __restrict__ q, long 
                                       const int64_t* __restrict__ positions, const float* __restrict__ inv_freq,
                                       void* __restrict__ q_out, float* __restrict__ w_out, int T, int ih, int d, int R,
                                       int quantize) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int wp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (wp >= T * ih) return;

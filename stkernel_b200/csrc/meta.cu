@@ -14,8 +14,8 @@ namespace stk {
 __global__ void swa_indices_kernel(const int64_t* __restrict__ positions, const int* __restrict__ tok_req,
                                    const int* __restrict__ block_table, int bt_stride, int* __restrict__ slots,
                                    int ld, int* __restrict__ lens, int window) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   const long long pos = positions[t];
   const int req = tok_req[t];
@@ -43,8 +43,8 @@ __global__ void swa_indices_noncausal_kernel(const int* __restrict__ tok_req, co
                                              const int* __restrict__ seq_len, const int* __restrict__ block_table,
                                              int bt_stride, int* __restrict__ slots, int ld, int* __restrict__ lens,
                                              int window) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   const int req = tok_req[t];
   int n = 0;
@@ -69,8 +69,8 @@ __global__ void swa_indices_noncausal_kernel(const int* __restrict__ tok_req, co
 
 __global__ void compressed_valid_kernel(const int64_t* __restrict__ positions, int* __restrict__ n_valid, int T,
                                         int ratio) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= T) return;
   const long long pos = positions[t];
@@ -80,8 +80,8 @@ __global__ void compressed_valid_kernel(const int64_t* __restrict__ positions, i
 __global__ void c128_indices_kernel(const int64_t* __restrict__ positions, const int* __restrict__ tok_req,
                                     const int* __restrict__ block_table, int bt_stride, int* __restrict__ slots,
                                     int ld, int* __restrict__ lens, int ratio, int cap) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   const long long pos = positions[t];
   const int req = tok_req[t];
@@ -107,8 +107,8 @@ __global__ void token_maps_kernel(const int* __restrict__ query_start, const int
                                   int64_t* __restrict__ positions, int* __restrict__ first_pos,
                                   int* __restrict__ last_pos, const int* __restrict__ block_table, int bt_stride,
                                   int64_t* __restrict__ slot_mapping, int T_padded) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= T_padded) return;
   int r = -1;

@@ -237,8 +237,8 @@ template <int HCM>
 __global__ void __launch_bounds__(256)
 mhc_post_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                 const float* __restrict__ post, const float* __restrict__ comb, __nv_bfloat16* __restrict__ out, int H) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   __shared__ float sp[HCM], sc[HCM * HCM];
   if (threadIdx.x < HCM) sp[threadIdx.x] = post[t * HCM + threadIdx.x];
@@ -378,7 +378,6 @@ mhc_cluster_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   const int HC = H * hc;
   const bool fused = fz.fa != nullptr;
   // ahead of the previous kernel's completion: this CTA's slice of the (immutable) mix weights goes towards L2
-  pdl_trigger();
   {
     const int pslice = ((HC / kClusterSize) + 1) & ~1;
     const int pk0 = crank * pslice, pk1 = min(HC, pk0 + pslice);
@@ -388,6 +387,7 @@ mhc_cluster_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
     }
   }
   pdl_wait();
+  pdl_trigger();
   if (fused) {
     if (threadIdx.x < hc) s_po[threadIdx.x] = fz.post_old[t * hc + threadIdx.x];
     if (threadIdx.x < hc * hc) s_co[threadIdx.x] = fz.comb_old[t * hc * hc + threadIdx.x];

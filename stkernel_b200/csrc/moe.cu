@@ -25,8 +25,8 @@ __global__ void router_kernel(const float* __restrict__ logits, long long ldl, c
                               const int* __restrict__ tid2eid, const int64_t* __restrict__ token_ids, int vocab,
                               int* __restrict__ ids, float* __restrict__ weights, int T, int E, int topk, int scoring,
                               int renorm, float scaling, int* status) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (t >= T) return;
@@ -103,8 +103,8 @@ __global__ void router_kernel(const float* __restrict__ logits, long long ldl, c
 __global__ void __launch_bounds__(1024)
 moe_align_kernel(const int* __restrict__ ids, int n_pairs, int e_start, int e_local, int* __restrict__ sorted,
                  int* __restrict__ pair_row, int* __restrict__ offsets, int* __restrict__ sorted_expert) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   extern __shared__ int sh[];          // counts[e_local + 1]
   int* counts = sh;
   for (int i = threadIdx.x; i <= e_local; i += blockDim.x) counts[i] = 0;
@@ -317,8 +317,8 @@ expert_fc1_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, ExpertW w1
                   const int* __restrict__ sorted_expert, const int* __restrict__ offsets, int e_local, int topk,
                   __half* __restrict__ act, int H, int I, float limit, const int* __restrict__ direct_ids,
                   int e_start) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   extern __shared__ uint4 xs[];
   const int row = blockIdx.y;
   int pair, e;
@@ -370,8 +370,8 @@ __global__ void __launch_bounds__(256)
 expert_fc2_kernel(const __half* __restrict__ act, ExpertW w2, const int* __restrict__ sorted_expert,
                   const int* __restrict__ offsets, int e_local, __nv_bfloat16* __restrict__ y, int H, int I,
                   const int* __restrict__ direct_ids, int e_start) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   extern __shared__ uint4 xs[];
   const int row = blockIdx.y;
   int e;

@@ -46,8 +46,8 @@ gumbel_argmax_partial_kernel(const T* __restrict__ logits, long long ld, const f
                              const int64_t* __restrict__ seed, const int64_t* __restrict__ pos,
                              const int* __restrict__ row_group, int pos_stride, float* __restrict__ part_val,
                              int* __restrict__ part_idx, float* __restrict__ processed, long long ldp, int V) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   __shared__ float sv[8];
   __shared__ int si[8];
   const int row = blockIdx.x;
@@ -87,8 +87,8 @@ gumbel_argmax_partial_kernel(const T* __restrict__ logits, long long ld, const f
 
 __global__ void gumbel_argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
                                            int chunks, int64_t* __restrict__ out, int rows) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   const int row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= rows) return;
   float best = -INFINITY;

@@ -102,7 +102,6 @@ skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const f
   __shared__ float s_red[32];
   // Ahead of the previous kernel's completion: pull this CTA's weight rows (immutable) towards L2, one request per
   // 128-byte line, so that the row loop below starts on L2 hits while the activations are still being produced.
-  pdl_trigger();
   {
     const int pw = threadIdx.x >> 5, pl = threadIdx.x & 31;
     const int pn0 = (blockIdx.x * 8 + pw) * rows_per_warp;
@@ -116,6 +115,7 @@ skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const f
       }
   }
   pdl_wait();
+  pdl_trigger();
   skinny_fill_x<T, kFp8>(reinterpret_cast<__half*>(xs4), x + static_cast<long long>(grp) * K, ldx, K, iters16, s_xscale, s_red, t_valid);
   __syncthreads();
   float xsc[T];

@@ -100,6 +100,7 @@ class LayerWeights:
     w_oa: List[LinearWeight]
     w_ob: LinearWeight
     sink: torch.Tensor
+    sink_full: Optional[torch.Tensor] = None      # all heads' sinks (token-parallel attention under TP)
     w_oa_grouped: Optional[LinearWeight] = None   # the same groups stacked [G_l*o_lora, hpg*D] for one launch
     w_side: Optional[LinearWeight] = None  # bf16 [2cD (+ ih + 4di), H]: compressor | weights_proj | indexer compressor
     ape: Optional[torch.Tensor] = None
@@ -162,7 +163,8 @@ def build_layer(cfg: ModelConfig, src: WeightSource, prefix: str, li: int, devic
         attn_norm=g(f"{prefix}.attn_norm.weight", (H,)).to(BF16), ffn_norm=g(f"{prefix}.ffn_norm.weight", (H,)).to(BF16),
         w_qa_kv=w_qa_kv, q_norm=g(f"{a}.q_norm.weight", (cfg.q_lora_rank,)).to(BF16),
         kv_norm=g(f"{a}.kv_norm.weight", (D,)).to(BF16), w_qb=mk(wqb), w_oa=w_oa, w_oa_grouped=w_oa_grouped, w_ob=mk(wob.contiguous()),
-        sink=g(f"{a}.attn_sink", (nh,)).to(F32)[h0:h0 + nh_l].contiguous())
+        sink=g(f"{a}.attn_sink", (nh,)).to(F32)[h0:h0 + nh_l].contiguous(),
+        sink_full=g(f"{a}.attn_sink", (nh,)).to(F32).contiguous() if tp_size > 1 else None)
     if ratio:
         c = compressor_slots(ratio)
         side = [g(f"{a}.compressor.wkv.weight", (c * D, H)), g(f"{a}.compressor.wgate.weight", (c * D, H))]
@@ -272,6 +274,11 @@ class DSV4Model:
         # Decode-sized steps are a chain of launches that each fill a fraction of the GPU: independent branches of a
         # sub-block (compressor state update and KV insert beside the q / indexer chain, the shared expert beside the
         # router) run on a second stream, also inside captured graphs, so the chain gets shorter.
+        # Token-parallel sparse attention: every rank holds the whole latent KV cache, and gathering a token's
+        # top-k rows costs the same for 8 heads as for 64, so with heads split over the ranks the gather work is
+        # replicated.  Large steps instead exchange q (all-to-all: heads -> tokens), attend with all heads for 1/tp of
+        # the tokens, and exchange the output back (tokens -> heads).
+        self.mla_tp_min_rows = int(os.environ.get("STK_MLA_TP_MIN_ROWS", "1024"))
         self.fork_max_t = int(os.environ.get("STK_FORK_MAX_T", "64")) if dev.type == "cuda" else 0
         self.side_stream = torch.cuda.Stream(dev) if self.fork_max_t > 0 else None
 
@@ -390,8 +397,12 @@ class DSV4Model:
             if fork:
                 torch.cuda.current_stream().wait_event(ev_done)
         with span("sparse_mla", T):
-            o = A.sparse_mla(q, self.kv.swa_cache[li], meta.swa_slots, meta.swa_lens, comp_cache, topk_slots, topk_lens,
-                             lw.sink, D ** -0.5, inv_rope=(meta.positions, self.inv))
+            if (self.tp_size > 1 and self.comm is not None and lw.sink_full is not None and self.mla_tp_min_rows > 0
+                    and T >= self.mla_tp_min_rows):
+                o = self._mla_token_parallel(li, lw, q, meta, comp_cache, topk_slots, topk_lens)
+            else:
+                o = A.sparse_mla(q, self.kv.swa_cache[li], meta.swa_slots, meta.swa_lens, comp_cache, topk_slots,
+                                 topk_lens, lw.sink, D ** -0.5, inv_rope=(meta.positions, self.inv))
         # grouped low-rank output projection, then the row-parallel wo_b (+ all-reduce)
         G_l = len(lw.w_oa)
         hpg = cfg.num_attention_heads // cfg.o_groups
@@ -406,6 +417,29 @@ class DSV4Model:
             ar = self._gemm_ar_ctx(T, cfg.hidden_size)
             out = Fn.linear(z, lw.w_ob, tag="ob", ar_ctx=ar)
             return out if ar is not None else self._all_reduce(out)
+
+    def _mla_token_parallel(self, li: int, lw: LayerWeights, q: torch.Tensor, meta: StepMeta, comp_cache, topk_slots,
+                            topk_lens) -> torch.Tensor:
+        """q [T, nh_local, D] -> o [T, nh_local, D], computed as all heads of this rank's share of the tokens."""
+        tp, r = self.tp_size, self.tp_rank
+        T, nh_l, D = q.shape
+        share = -(-T // tp)
+        sizes = [max(0, min(T, (s + 1) * share) - min(T, s * share)) for s in range(tp)]
+        a0, mine = min(T, r * share), sizes[r]
+        # heads -> tokens: block s of the result holds head block s of my tokens
+        recv = self.comm.all_to_all_dim0(q, sizes, [mine] * tp)
+        if mine > 0:
+            q_seq = recv.view(tp, mine, nh_l, D).permute(1, 0, 2, 3).reshape(mine, tp * nh_l, D)
+            sl = slice(a0, a0 + mine)
+            o_seq = A.sparse_mla(q_seq, self.kv.swa_cache[li], meta.swa_slots[sl], meta.swa_lens[sl], comp_cache,
+                                 topk_slots[sl] if topk_slots is not None else None,
+                                 topk_lens[sl] if topk_lens is not None else None, lw.sink_full, D ** -0.5,
+                                 inv_rope=(meta.positions[sl], self.inv))
+            send = o_seq.view(mine, tp, nh_l, D).permute(1, 0, 2, 3).reshape(tp * mine, nh_l, D)
+        else:
+            send = q.new_zeros(0, nh_l, D)
+        # tokens -> heads: block s of the result holds my head block of rank s's tokens
+        return self.comm.all_to_all_dim0(send, [mine] * tp, sizes)
 
     # ---- MoE sub-block ----------------------------------------------------------
     def moe(self, lw: LayerWeights, y: torch.Tensor, yq, meta: StepMeta) -> torch.Tensor:

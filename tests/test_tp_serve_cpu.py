@@ -43,9 +43,10 @@ def _wait_up(port, proc, timeout=180):
 
 
 def _launch(world, port, extra=()):
-    # a tiny threshold so that the prompt's prefill step takes the sequence-parallel indexer path at world 2
+    # tiny thresholds so that the prompt's prefill step takes the sequence-parallel indexer path and the
+    # token-parallel attention path (q / output all-to-all) at world 2
     env = dict(os.environ, PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2", STK_CPU_ACT_FP32="1",
-               STK_INDEXER_SP_MIN_ROWS="4")
+               STK_INDEXER_SP_MIN_ROWS="4", STK_MLA_TP_MIN_ROWS="4")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(_free_port()), "-m", "stkernel_b200.serve.tp_worker", "--tiny", "--port", str(port),
            "--tensor-parallel-size", str(world), "--max-model-len", "512", "--max-num-seqs", "4",
