@@ -79,7 +79,7 @@ class QuantAct:
 
 
 SKINNY_MAX_T = 4          # above four tokens the tcgen05 GEMM with split-K is faster (measured at six)
-MHC_CLUSTER_MAX_T = int(_os.environ.get("STK_MHC_CLUSTER_MAX_T", "16"))
+MHC_CLUSTER_MAX_T = int(_os.environ.get("STK_MHC_CLUSTER_MAX_T", "64"))
 
 
 def _skinny_rows(t: int) -> int:
