@@ -30,6 +30,12 @@ struct MlaTcArgs {
   const int* swa_slots; int swa_ld; const int* swa_lens;
   const int* topk_slots; int topk_ld; const int* topk_lens;   // may be null
   float* partial;              // [T, n_splits, nh, 514]
+  // Direct output (n_splits == 1 only, out != nullptr): the CTA merges the sink, normalises, applies the inverse
+  // RoPE to the rope dims and writes bf16 [T, nh, 512] itself; no partial is written and no combine pass runs.
+  __nv_bfloat16* out; long long ldo;
+  const float* sink;           // [nh] or null
+  const int64_t* positions;    // [T] or null (no inverse RoPE)
+  const float* inv_freq;       // [32]
   int T, nh, n_splits, rows_per_split;
   float scale;
   int* status;
@@ -173,6 +179,12 @@ sparse_mla_tc_kernel(const MlaTcArgs a) {
   float* prow = a.partial + (static_cast<long long>(t) * a.n_splits + sp) * a.nh * (kD + 2);
 
   if (threadIdx.x == 0) STK_TRACE(0);
+  if (n_blocks == 0 && a.out != nullptr) {
+    // no keys at all: only the sink takes probability mass, the output is zero
+    __nv_bfloat16* orow = a.out + static_cast<long long>(t) * a.ldo;
+    for (int i = threadIdx.x; i < a.nh * kD; i += blockDim.x) orow[i] = __float2bfloat16(0.f);
+    return;
+  }
   if (n_blocks == 0) {
     for (int i = threadIdx.x; i < a.nh * (kD + 2); i += blockDim.x) {
       const int d = i % (kD + 2);
@@ -372,7 +384,52 @@ sparse_mla_tc_kernel(const MlaTcArgs a) {
     if (ok) ok = mbar_wait(&bars->pv_done, (n_blocks - 1) & 1, a.status, 611);
     if (threadIdx.x == 32) STK_TRACE(5);
     tc_fence_after();
-    if (ok) {
+    if (ok && a.out != nullptr) {
+      // direct output: per-head factor exp(m - M) / (exp(sink - M) + l * exp(m - M)) with M = max(sink, m)
+      named_bar_sync(2, kSoftmaxWarps * 32);
+      if (own < NH) {
+        const float m_nat = m_run[own] * 0.6931471805599453f;
+        const float sk = (a.sink != nullptr && own < a.nh) ? a.sink[own] : -INFINITY;
+        const float M = fmaxf(sk, m_nat);
+        float f = 0.f;
+        if (m_nat != -INFINITY) {
+          const float w = __expf(m_nat - M);
+          const float denom = (sk != -INFINITY ? __expf(sk - M) : 0.f) + l_run[own] * w;
+          f = denom > 0.f ? w / denom : 0.f;
+        }
+        alpha_s[own] = f;
+      }
+      named_bar_sync(2, kSoftmaxWarps * 32);
+      __nv_bfloat16* orow = a.out + static_cast<long long>(t) * a.ldo;
+      const float pos = a.positions != nullptr ? static_cast<float>(a.positions[t]) : 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int d = j * 128 + row;
+        const bool rot = a.positions != nullptr && j == 3 && q4 >= 2;      // d >= 448: warp-uniform
+        float sn = 0.f, cs = 1.f;
+        if (rot) sincosf(pos * a.inv_freq[(d - kNope) >> 1], &sn, &cs);
+#pragma unroll
+        for (int c = 0; c < NH; c += 16) {
+          uint32_t r16[16];
+          tmem_ld_32x16(tmem_o + j * NH + c + lane_addr, r16);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            if (c + i < a.nh) {
+              float v = __uint_as_float(r16[i]) * alpha_s[c + i];
+              if (rot) {
+                // the pair (even d, d + 1) sits in neighbouring lanes; values are rounded to bf16 before the rotation,
+                // as the separate combine pass does
+                v = __bfloat162float(__float2bfloat16(v));
+                const float p = __shfl_xor_sync(0xffffffffu, v, 1);
+                v = (d & 1) ? (-p * sn + v * cs) : (v * cs + p * sn);
+              }
+              orow[static_cast<long long>(c + i) * kD + d] = __float2bfloat16(v);
+            }
+          }
+        }
+      }
+    } else if (ok) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
 #pragma unroll
@@ -498,16 +555,15 @@ static int launch_mla_tc(const MlaTcArgs& a, cudaStream_t st) {
 
 using namespace stk;
 
-// Same contract as stk_sparse_mla (partials + combine), restricted to fp8_ds_mla rows with D = 512,
-// R = 64 and at most 64 local heads.  Returns -20 for shapes it does not cover.
-STK_API int stk_sparse_mla_tc(const void* q, long long ldt, const void* swa_cache, long long swa_stride,
-                              const void* comp_cache, long long comp_stride, const int* swa_slots, int swa_ld,
-                              const int* swa_lens, const int* topk_slots, int topk_ld, const int* topk_lens,
-                              float* workspace, int n_splits, int T, int nh, int D, int R, int max_rows, float scale,
-                              int* status, void* trace, void* stream) {
+static int mla_tc_run(const void* q, long long ldt, const void* swa_cache, long long swa_stride, const void* comp_cache,
+                      long long comp_stride, const int* swa_slots, int swa_ld, const int* swa_lens, const int* topk_slots,
+                      int topk_ld, const int* topk_lens, float* workspace, int n_splits, int T, int nh, int D, int R,
+                      int max_rows, float scale, void* out, long long ldo, const float* sink, const int64_t* positions,
+                      const float* inv_freq, int* status, void* trace, void* stream) {
   if (T <= 0) return 0;
   if (D != kD || R != kR || nh > 64 || nh < 1) return -20;
   if ((reinterpret_cast<uintptr_t>(q) & 15) || (ldt % 8)) return -21;
+  if (out != nullptr && n_splits != 1) return -22;
   MlaTcArgs a;
   a.q = (const __nv_bfloat16*)q; a.ldt = ldt;
   a.swa_base = (const uint8_t*)swa_cache; a.swa_stride = swa_stride;
@@ -515,6 +571,7 @@ STK_API int stk_sparse_mla_tc(const void* q, long long ldt, const void* swa_cach
   a.swa_slots = swa_slots; a.swa_ld = swa_ld; a.swa_lens = swa_lens;
   a.topk_slots = topk_slots; a.topk_ld = topk_ld; a.topk_lens = topk_lens;
   a.partial = workspace; a.T = T; a.nh = nh; a.n_splits = n_splits;
+  a.out = (__nv_bfloat16*)out; a.ldo = ldo; a.sink = sink; a.positions = positions; a.inv_freq = inv_freq;
   const int rps = (max_rows + n_splits - 1) / n_splits;
   a.rows_per_split = ((rps + kRows - 1) / kRows) * kRows;
   a.scale = scale; a.status = status; a.trace = (unsigned long long*)trace;
@@ -522,4 +579,30 @@ STK_API int stk_sparse_mla_tc(const void* q, long long ldt, const void* swa_cach
   if (nh <= 16) return launch_mla_tc<16>(a, st);
   if (nh <= 32) return launch_mla_tc<32>(a, st);
   return launch_mla_tc<64>(a, st);
+}
+
+// Same contract as stk_sparse_mla (partials + combine), restricted to fp8_ds_mla rows with D = 512,
+// R = 64 and at most 64 local heads.  Returns -20 for shapes it does not cover.
+STK_API int stk_sparse_mla_tc(const void* q, long long ldt, const void* swa_cache, long long swa_stride,
+                              const void* comp_cache, long long comp_stride, const int* swa_slots, int swa_ld,
+                              const int* swa_lens, const int* topk_slots, int topk_ld, const int* topk_lens,
+                              float* workspace, int n_splits, int T, int nh, int D, int R, int max_rows, float scale,
+                              int* status, void* trace, void* stream) {
+  return mla_tc_run(q, ldt, swa_cache, swa_stride, comp_cache, comp_stride, swa_slots, swa_ld, swa_lens, topk_slots,
+                    topk_ld, topk_lens, workspace, n_splits, T, nh, D, R, max_rows, scale, nullptr, 0, nullptr, nullptr,
+                    nullptr, status, trace, stream);
+}
+
+// One CTA per token over its whole row list, final output written by the kernel (sink merged, normalised, inverse
+// RoPE on the rope dims when positions != null): for steps with enough tokens to fill the GPU without row splits.
+STK_API int stk_sparse_mla_tc_out(const void* q, long long ldt, const void* swa_cache, long long swa_stride,
+                                  const void* comp_cache, long long comp_stride, const int* swa_slots, int swa_ld,
+                                  const int* swa_lens, const int* topk_slots, int topk_ld, const int* topk_lens, int T,
+                                  int nh, int D, int R, int max_rows, float scale, void* out, long long ldo,
+                                  const float* sink, const int64_t* positions, const float* inv_freq, int* status,
+                                  void* stream) {
+  if (out == nullptr) return -23;
+  return mla_tc_run(q, ldt, swa_cache, swa_stride, comp_cache, comp_stride, swa_slots, swa_ld, swa_lens, topk_slots,
+                    topk_ld, topk_lens, nullptr, 1, T, nh, D, R, max_rows, scale, out, ldo, sink, positions, inv_freq,
+                    status, nullptr, stream);
 }

@@ -277,8 +277,10 @@ class DSV4Model:
         # Token-parallel sparse attention: every rank holds the whole latent KV cache, and gathering a token's
         # top-k rows costs the same for 8 heads as for 64, so with heads split over the ranks the gather work is
         # replicated.  Large steps instead exchange q (all-to-all: heads -> tokens), attend with all heads for 1/tp of
-        # the tokens, and exchange the output back (tokens -> heads).
-        self.mla_tp_min_rows = int(os.environ.get("STK_MLA_TP_MIN_ROWS", "1024"))
+        # the tokens, and exchange the output back (tokens -> heads).  Off by default (0): measured on 2 GPUs the
+        # tensor-core kernel's time follows heads x tokens (its softmax warps, not the gather, set the pace), so the
+        # exchange buys nothing there; the knob stays for caches whose gather dominates.
+        self.mla_tp_min_rows = int(os.environ.get("STK_MLA_TP_MIN_ROWS", "0"))
         self.fork_max_t = int(os.environ.get("STK_FORK_MAX_T", "64")) if dev.type == "cuda" else 0
         self.side_stream = torch.cuda.Stream(dev) if self.fork_max_t > 0 else None
 

@@ -17,6 +17,7 @@ I32 = torch.int32
 # The tcgen05 sparse-MLA kernel serves fp8_ds_mla rows of the production shape; other shapes (and
 # this switch set to False, for A/B checks) use the split-row CUDA-core kernel.
 USE_TENSOR_CORE_MLA = True
+MLA_DIRECT_OUT = True     # single-split steps: final rows written by the attention kernel itself
 # optional int64[8] device tensor receiving stage timestamps (ns) of CTA (0, 0) of the tcgen05 kernel
 MLA_TRACE = None
 
@@ -244,6 +245,16 @@ def sparse_mla(q: torch.Tensor, swa_cache: PagedCache, swa_slots: torch.Tensor, 
         # tcgen05 kernel: one 64-row key block per CTA while the SMs are not full (a block is a serial chain of
         # gather -> QK^T -> softmax -> PV, so at decode sizes more, shorter CTAs finish sooner)
         n_splits = max(1, min((max_rows + 63) // 64, (2 * _lib.sm_count()) // max(t, 1)))
+        if n_splits == 1 and MLA_DIRECT_OUT:
+            # enough tokens to fill the GPU: the kernel writes the final rows itself (no fp32 partials, no combine pass)
+            out = torch.empty(t, nh, d, dtype=BF16, device=q.device)
+            _lib.call("stk_sparse_mla_tc_out", q, q.stride(0), swa_cache.buf, swa_cache.page_stride, cc.buf, cc.page_stride,
+                      swa_slots, swa_slots.stride(0), swa_lens, topk_slots,
+                      topk_slots.stride(0) if topk_slots is not None else 0, topk_lens, t, nh, d, swa_cache.rope_dim,
+                      max_rows, float(scale), out, out.stride(0), sink,
+                      inv_rope[0] if inv_rope is not None else None, inv_rope[1] if inv_rope is not None else None,
+                      _lib.status_buffer(), _lib.stream())
+            return out
         ws = scratch("mla.partial", (t * n_splits * nh * (d + 2),), F32, q.device)
         out = torch.empty(t, nh, d, dtype=BF16, device=q.device)
         _lib.call("stk_sparse_mla_tc", q, q.stride(0), swa_cache.buf, swa_cache.page_stride, cc.buf, cc.page_stride,

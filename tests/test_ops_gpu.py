@@ -307,6 +307,43 @@ def test_sparse_mla_matches_reference(nh, D, R_, fp8):
     assert rel_err(out2, ref2) < 1e-2
 
 
+@pytest.mark.parametrize("nh", [64, 8])
+def test_sparse_mla_direct_output_matches_split_path(nh):
+    """Steps with many tokens take the single-split kernel that writes the final rows itself (sink merge, normalisation,
+    inverse RoPE in its epilogue); compare with the fp32 reference and with the partial + combine path."""
+    torch.manual_seed(9)
+    D, R_, T, W, K = 512, 64, 320, 128, 256
+    n_pages = 24
+    rows = torch.randn(n_pages * 64, D)
+    ccpu = C.PagedCache.allocate(n_pages, D, R_, True, "latent", "cpu")
+    ccpu.write_rows_cpu(torch.arange(n_pages * 64), rows)
+    cg = C.PagedCache(ccpu.buf.to(dev()), D, R_, True, "latent")
+    q = torch.randn(T, nh, D, device=dev()).to(BF16)
+    swa_slots = torch.randint(0, n_pages * 64, (T, W), dtype=torch.int32, device=dev())
+    swa_lens = torch.randint(0, W + 1, (T,), dtype=torch.int32, device=dev())
+    topk_slots = torch.randint(0, n_pages * 64, (T, K), dtype=torch.int32, device=dev())
+    topk_slots[0, 3] = -1
+    topk_lens = torch.randint(0, K + 1, (T,), dtype=torch.int32, device=dev())
+    swa_lens[1] = 0
+    topk_lens[1] = 0                      # a token without any key: only the sink has mass, output zero
+    sink = torch.randn(nh, device=dev())
+    pos = torch.randint(0, 50000, (T,), device=dev(), dtype=torch.int64)
+    inv = Fn.inv_freq(R_, 10000.0, dev())
+    assert A.MLA_DIRECT_OUT
+    out = A.sparse_mla(q, cg, swa_slots, swa_lens, cg, topk_slots, topk_lens, sink, D ** -0.5, inv_rope=(pos, inv))
+    A.MLA_DIRECT_OUT = False
+    try:
+        split = A.sparse_mla(q, cg, swa_slots, swa_lens, cg, topk_slots, topk_lens, sink, D ** -0.5, inv_rope=(pos, inv))
+    finally:
+        A.MLA_DIRECT_OUT = True
+    assert rel_err(out, split) < 4e-3
+    assert float(out[1].float().abs().max()) == 0.0
+    sub = slice(0, 6)
+    ref = A.sparse_mla(q[sub].cpu(), ccpu, swa_slots[sub].cpu(), swa_lens[sub].cpu(), ccpu, topk_slots[sub].cpu(),
+                       topk_lens[sub].cpu(), sink.cpu(), D ** -0.5, inv_rope=(pos[sub].cpu(), inv.cpu()))
+    assert rel_err(out[sub], ref) < 1.2e-2
+
+
 @pytest.mark.parametrize("scoring", ["sigmoid", "sqrtsoftplus"])
 def test_router(scoring):
     T, E, k = 33, 256, 6
