@@ -100,49 +100,61 @@ __global__ void router_kernel(const float* __restrict__ logits, long long ldl, c
 // ---- pair sort by expert ------------------------------------------------------------
 // Single CTA.  sorted[q] = pair index, pair_row[p] = q (or -1 when the expert is not local),
 // offsets[e] = first row of local expert e, offsets[E_local] = total rows.
+// The pair list is staged in shared memory; a pair's row is its expert's offset plus the number of earlier pairs of
+// the same expert (stable order, so results do not depend on thread scheduling), counted by a broadcast scan.
 __global__ void __launch_bounds__(1024)
 moe_align_kernel(const int* __restrict__ ids, int n_pairs, int e_start, int e_local, int* __restrict__ sorted,
                  int* __restrict__ pair_row, int* __restrict__ offsets, int* __restrict__ sorted_expert) {
   pdl_wait();
   pdl_trigger();
-  extern __shared__ int sh[];          // counts[e_local + 1]
+  extern __shared__ int sh[];          // counts[e_local + 1] | local expert of every pair (or -1)
   int* counts = sh;
+  int* ids_s = sh + e_local + 1;
   for (int i = threadIdx.x; i <= e_local; i += blockDim.x) counts[i] = 0;
   __syncthreads();
   for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
-    const int e = ids[p] - e_start;
-    if (e >= 0 && e < e_local) atomicAdd(&counts[e], 1);
+    int e = ids[p] - e_start;
+    if (e < 0 || e >= e_local) e = -1;
+    ids_s[p] = e;
+    if (e >= 0) atomicAdd(&counts[e], 1);
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < 32) {
+    // exclusive scan of the expert counts by one warp
     int run = 0;
-    for (int e = 0; e < e_local; ++e) {
-      const int c = counts[e];
-      counts[e] = run;
-      offsets[e] = run;
-      run += c;
+    for (int e0 = 0; e0 < e_local; e0 += 32) {
+      const int e = e0 + threadIdx.x;
+      const int c = e < e_local ? counts[e] : 0;
+      int incl = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (static_cast<int>(threadIdx.x) >= o) incl += v;
+      }
+      if (e < e_local) {
+        counts[e] = run + incl - c;
+        offsets[e] = run + incl - c;
+      }
+      run += __shfl_sync(0xffffffffu, incl, 31);
     }
-    counts[e_local] = run;
-    offsets[e_local] = run;
+    if (threadIdx.x == 0) {
+      counts[e_local] = run;
+      offsets[e_local] = run;
+    }
   }
   __syncthreads();
-  // stable placement: one thread per expert walks the pair list in order
-  for (int e = threadIdx.x; e < e_local; e += blockDim.x) {
-    int pos = counts[e];
-    const int end = (e + 1 <= e_local) ? counts[e + 1] : pos;
-    if (pos == end) continue;
-    for (int p = 0; p < n_pairs && pos < end; ++p) {
-      if (ids[p] - e_start == e) {
-        sorted[pos] = p;
-        sorted_expert[pos] = e;
-        pair_row[p] = pos;
-        ++pos;
-      }
-    }
-  }
   for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
-    const int e = ids[p] - e_start;
-    if (e < 0 || e >= e_local) pair_row[p] = -1;
+    const int e = ids_s[p];
+    if (e < 0) {
+      pair_row[p] = -1;
+      continue;
+    }
+    int rank = 0;
+    for (int q = 0; q < p; ++q) rank += (ids_s[q] == e) ? 1 : 0;
+    const int pos = counts[e] + rank;
+    sorted[pos] = p;
+    sorted_expert[pos] = e;
+    pair_row[p] = pos;
   }
 }
 
@@ -437,7 +449,7 @@ STK_API int stk_moe_align(const int* ids, int n_pairs, int e_start, int e_local,
                                                              pair_row, sorted_expert);
     return cudaGetLastError() == cudaSuccess ? 0 : -4;
   }
-  launch_pdl(moe_align_kernel, dim3(1), dim3(1024), (e_local + 1) * sizeof(int), (cudaStream_t)stream, ids, n_pairs, e_start, e_local,
+  launch_pdl(moe_align_kernel, dim3(1), dim3(1024), (e_local + 1 + n_pairs) * sizeof(int), (cudaStream_t)stream, ids, n_pairs, e_start, e_local,
                                                                                    sorted, pair_row, offsets,
                                                                                    sorted_expert);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;

@@ -270,7 +270,7 @@ class DSV4Model:
         # `_indexer_sp_owned_ranges` in the reference; here every row of a step is split evenly, which is exact
         # because scoring and top-k are independent per row).
         self.indexer_sp = tp_size > 1 and comm is not None
-        self.indexer_sp_min_rows = int(os.environ.get("STK_INDEXER_SP_MIN_ROWS", "256"))
+        self.indexer_sp_min_rows = int(os.environ.get("STK_INDEXER_SP_MIN_ROWS", "8"))
         # Decode-sized steps are a chain of launches that each fill a fraction of the GPU: independent branches of a
         # sub-block (compressor state update and KV insert beside the q / indexer chain, the shared expert beside the
         # router) run on a second stream, also inside captured graphs, so the chain gets shorter.
