@@ -80,7 +80,7 @@ def main() -> None:
     ap.add_argument("--top", type=int, default=30)
     ap.add_argument("--out", default="")
     a = ap.parse_args()
-    from ..config import EngineConfig, SchedulerConfig, flash_config
+    from ..config import EngineConfig, ParallelConfig, SchedulerConfig, flash_config
     from ..models.dsv4 import RandomSource, build_model_weights
     from ..runtime.engine import Engine, SamplingParams
     from .decode_bench import add_synthetic_requests, fill_caches_synthetic
@@ -97,7 +97,8 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=dev)
         comm = Communicator(device=dev, use_symm=True)
     cfg = flash_config(num_layers=a.layers)
-    ec = EngineConfig(model=cfg, sched=SchedulerConfig(max_model_len=a.ctx + 8192, max_num_seqs=max(a.conc, 2),
+    ec = EngineConfig(model=cfg, parallel=ParallelConfig(tp_size=world, ep_size=world, fused_collectives=True),
+                      sched=SchedulerConfig(max_model_len=a.ctx + 8192, max_num_seqs=max(a.conc, 2),
                                                        max_num_batched_tokens=a.chunk,
                                                        graph_cap=64 if a.graphs else 0)).validate()
     eng = Engine(ec, build_model_weights(cfg, RandomSource(0), dev, rank, world, head_fp8=True), dev, comm, rank,

@@ -144,6 +144,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
+  // Launched with programmatic serialization (plain GEMMs only): barriers, TMEM and descriptors are set up and the
+  // first weight tiles of this CTA are on their way to L2 while the previous kernel finishes; activations, split-K
+  // counters and epochs are touched only after the wait.
+  if (warp == 0 && lane == 0 && !a.token_major && static_cast<int>(blockIdx.x) < a.splits * a.tiles_t * a.tiles_n) {
+    const int u = blockIdx.x;
+    const int tn = u % a.tiles_n;
+    const int sp = u / (a.tiles_n * a.tiles_t);
+    const int kbs = (a.k_blocks + a.splits - 1) / a.splits;
+    const int kb0 = sp * kbs;
+    const int kb1 = min(a.k_blocks, min(kb0 + kbs, kb0 + 8));
+    for (int kb = kb0; kb < kb1; ++kb) tma_prefetch_2d(&tmW, kb * (kFp8 ? 128 : 64), tn * 128);
+  }
+  pdl_wait();
+  pdl_trigger();
   uint32_t ar_epoch = 0;
   if (a.ar_enabled) ar_epoch = *epoch_ptr(a.ar, kArKind, 0) + 1;   // bumped only after every CTA has finished
 
@@ -588,7 +602,11 @@ static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmA
       return -3;
     configured = true;
   }
-  gemm_kernel<BT, kFp8><<<grid, kFp8 ? 320 : 192, smem, st>>>(tw, tx, a);
+  if (a.ar_enabled || a.gate_enabled) {
+    gemm_kernel<BT, kFp8><<<grid, kFp8 ? 320 : 192, smem, st>>>(tw, tx, a);      // waits on peers: plain launch
+  } else {
+    launch_pdl(gemm_kernel<BT, kFp8>, dim3(grid), dim3(kFp8 ? 320 : 192), smem, st, tw, tx, a);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
