@@ -234,6 +234,55 @@ def _fill_indexer_cache(S, d, fp8):
     return k, C.PagedCache(cache.buf.to(dev()), d, 64, fp8, "indexer"), cache
 
 
+@pytest.mark.parametrize("T", [3, 131, 300])
+def test_indexer_scores_tensor_core_matches_cuda_core(T):
+    """tcgen05 scorer (K block stationary, q tiles by TMA, head sum in the TMEM lane) against the CUDA-core scorer and
+    the CPU reference: two requests with scattered pages, causal n_valid, a padded token (request -1)."""
+    torch.manual_seed(17)
+    ih, d, S = 64, 128, 1000
+    n_pages = 2 * ((S + 63) // 64) + 3
+    cache = C.PagedCache.allocate(n_pages, d, 64, True, "indexer", "cpu")
+    perm = torch.randperm(n_pages - 1)[:2 * ((S + 63) // 64)] + 1
+    bt_cpu = perm.view(2, -1).to(torch.int32)
+    for req in range(2):
+        k = torch.randn(S, d)
+        slots = bt_cpu[req].long()[torch.arange(S) // 64] * 64 + torch.arange(S) % 64
+        cache.write_rows_cpu(slots, k)
+    gcache = C.PagedCache(cache.buf.to(dev()), d, 64, True, "indexer")
+    bt = bt_cpu.to(dev()).contiguous()
+    q = torch.randn(T, ih, d, device=dev()).to(BF16)
+    w = torch.rand(T, ih, device=dev())
+    split = T // 3                                          # request 0: first third, request 1: the rest
+    tok_req = torch.cat([torch.zeros(split, dtype=torch.int32), torch.ones(T - split, dtype=torch.int32)]).to(dev())
+    pos = torch.cat([torch.arange(split) + 900, torch.arange(T - split) * 9 + 5]).to(dev())
+    tok_req[-1] = -1
+    inv = Fn.inv_freq(64, 10000.0, dev())
+    qq, wf = C.indexer_q_prep(q, w, pos, inv, 64, True)
+    nv = A.compressed_valid(pos, 4)
+    nv[-1] = 0
+    assert int(nv.max()) <= S
+    assert A.USE_TENSOR_CORE_INDEXER
+    tc = A.indexer_scores(qq, wf, gcache, bt, tok_req, nv, S, tag="idx_tc_test").clone()
+    A.USE_TENSOR_CORE_INDEXER = False
+    try:
+        cc = A.indexer_scores(qq, wf, gcache, bt, tok_req, nv, S, tag="idx_cc_test").clone()
+    finally:
+        A.USE_TENSOR_CORE_INDEXER = True
+    checked = 0
+    for i in range(T):
+        n = int(nv[i])
+        if n:
+            assert rel_err(tc[i, :n], cc[i, :n]) < 1e-3, i
+            checked += 1
+    assert checked >= T // 2
+    sub = [0, max(0, split - 1), min(T - 2, split)]
+    ref = A.indexer_scores(qq[sub].cpu(), wf[sub].cpu(), cache, bt_cpu, tok_req[sub].cpu(), nv[sub].cpu(), S)
+    for j, i in enumerate(sub):
+        n = int(nv[i])
+        if n:
+            assert rel_err(tc[i, :n], ref[j, :n]) < 2e-3
+
+
 @pytest.mark.parametrize("fp8", [True, False])
 def test_indexer_scores_and_topk(fp8):
     torch.manual_seed(5)
