@@ -591,6 +591,20 @@ int make_tmap_2d(CUtensorMap* tm, const void* base, int elem_bytes, long long ro
   return r == CUDA_SUCCESS ? 0 : -2;
 }
 
+// Paged uint8 tensor [pages][rows_per_page][128 B] with `page_stride` bytes between pages; box = one page's rows.
+int make_tmap_pages(CUtensorMap* tm, const void* base, long long pages, int rows_per_page, long long page_stride) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return -1;
+  cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(rows_per_page), static_cast<cuuint64_t>(pages)};
+  cuuint64_t strides[2] = {128, static_cast<cuuint64_t>(page_stride)};
+  cuuint32_t box[3] = {128, static_cast<cuuint32_t>(rows_per_page), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -2;
+}
+
 template <int BT, bool kFp8>
 static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmArgs& a, int grid, cudaStream_t st) {
   using Cfg = GemmCfg<BT>;

@@ -4,7 +4,7 @@
 //
 // One CTA owns a block of 128 cache rows of one request and a chunk of tokens.  The block's K rows (two 64-row pages,
 // each a contiguous [64 x 128 B] region of the paged cache) are brought into shared memory once by TMA as the
-// M = 128 operand; the q rows of one or two tokens ([64 heads x 128 B] each, contiguous) stream through a two-stage
+// M = 128 operand (a 3-D tensor map [page][row][128 B] over the cache, one box per page); the q rows of one or two tokens ([64 heads x 128 B] each, contiguous) stream through a two-stage
 // ring as the N operand.  tcgen05.mma kind::f8f6f4 writes D[row, (token, head)] into a double-buffered TMEM
 // accumulator, so each epilogue thread owns one cache row and finds all heads of a token in its own TMEM lane:
 // ReLU, the head weights and the sum over heads are thread-local, and a warp stores 32 consecutive scores of a
@@ -19,6 +19,7 @@ namespace stk {
 
 int make_tmap_2d(CUtensorMap* tm, const void* base, int elem_bytes, long long rows, long long cols, long long ld,
                  int box_rows);
+int make_tmap_pages(CUtensorMap* tm, const void* base, long long pages, int rows_per_page, long long page_stride);
 
 struct IdxTcArgs {
   const float* w;              // [T, 64] folded head weights
@@ -44,7 +45,6 @@ struct IdxTcBarriers {
 constexpr int kIdxHeads = 64;
 constexpr int kIdxRowBytes = 128;          // 128 fp8 values
 constexpr int kIdxPageRows = 64;
-constexpr int kIdxPageLines = 66;          // a page is 66 lines of 128 B: 64 data rows + 64 fp32 scales
 
 __device__ __forceinline__ int idx_page(const IdxTcArgs& a, int req, int page_idx) {
   int p = page_idx < a.bt_stride ? a.block_table[static_cast<long long>(req) * a.bt_stride + page_idx] : 0;
@@ -134,8 +134,8 @@ indexer_scores_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
               ++nchg;
             }
             mbar_expect_tx(&bars->a_full, kABytes);
-            tma_load_2d(smem_a, &tmK, &bars->a_full, 0, idx_page(a, req, 2 * rb) * kIdxPageLines);
-            tma_load_2d(smem_a + kABytes / 2, &tmK, &bars->a_full, 0, idx_page(a, req, 2 * rb + 1) * kIdxPageLines);
+            tma_load_3d(smem_a, &tmK, &bars->a_full, 0, 0, idx_page(a, req, 2 * rb));
+            tma_load_3d(smem_a + kABytes / 2, &tmK, &bars->a_full, 0, 0, idx_page(a, req, 2 * rb + 1));
             a_pending = true;
             cur = req;
           }
@@ -258,15 +258,13 @@ STK_API int stk_indexer_scores_tc(const void* q, const float* w, const void* kca
                                   void* stream) {
   if (T <= 0 || max_rows <= 0) return 0;
   if (ih != kIdxHeads || di != kIdxRowBytes) return -20;
-  if (page_stride != kIdxPageLines * kIdxRowBytes || n_pages <= 0) return -20;
+  if (page_stride < kIdxPageRows * (kIdxRowBytes + 4) || page_stride % 16 || n_pages <= 0) return -20;
   if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(kcache) & 15) ||
       (reinterpret_cast<uintptr_t>(w) & 15))
     return -21;
   const int tpt = T >= 128 ? 2 : 1;
   CUtensorMap tk, tq;
-  if (make_tmap_2d(&tk, kcache, 1, static_cast<long long>(n_pages) * kIdxPageLines, kIdxRowBytes, kIdxRowBytes,
-                   kIdxPageRows) != 0)
-    return -13;
+  if (make_tmap_pages(&tk, kcache, n_pages, kIdxPageRows, page_stride) != 0) return -13;
   if (make_tmap_2d(&tq, q, 1, static_cast<long long>(T) * kIdxHeads, kIdxRowBytes, kIdxRowBytes, kIdxHeads * tpt) != 0)
     return -14;
   IdxTcArgs a;

@@ -18,6 +18,7 @@ I32 = torch.int32
 # this switch set to False, for A/B checks) use the split-row CUDA-core kernel.
 USE_TENSOR_CORE_MLA = True
 USE_TENSOR_CORE_INDEXER = True
+tc_indexer_calls = 0     # launches of the tcgen05 scorer (tests check that the path they mean to cover ran)
 MLA_DIRECT_OUT = True     # single-split steps: final rows written by the attention kernel itself
 # optional int64[8] device tensor receiving stage timestamps (ns) of CTA (0, 0) of the tcgen05 kernel
 MLA_TRACE = None
@@ -167,8 +168,10 @@ def indexer_scores(q: torch.Tensor, w: torch.Tensor, kcache: PagedCache, block_t
         return scores
     scores = scratch(f"{tag}.scores", (t, ld), F32, q.device)
     if (USE_TENSOR_CORE_INDEXER and q.dtype != BF16 and kcache.fp8 and ih == 64 and d == 128 and q.is_contiguous()
-            and kcache.page_stride == 66 * 128):
+            and kcache.page_stride % 16 == 0):
         # tcgen05 scorer: K block stationary in shared memory, q tiles streamed by TMA, one cache row per epilogue thread
+        global tc_indexer_calls
+        tc_indexer_calls += 1
         _lib.call("stk_indexer_scores_tc", q, w, kcache.buf, kcache.page_stride, kcache.num_pages, block_table,
                   block_table.stride(0), tok_req, n_valid, scores, ld, t, max_rows, ih, d, _lib.status_buffer(),
                   _lib.stream())

@@ -262,7 +262,9 @@ def test_indexer_scores_tensor_core_matches_cuda_core(T):
     nv[-1] = 0
     assert int(nv.max()) <= S
     assert A.USE_TENSOR_CORE_INDEXER
+    before = A.tc_indexer_calls
     tc = A.indexer_scores(qq, wf, gcache, bt, tok_req, nv, S, tag="idx_tc_test").clone()
+    assert A.tc_indexer_calls == before + 1
     A.USE_TENSOR_CORE_INDEXER = False
     try:
         cc = A.indexer_scores(qq, wf, gcache, bt, tok_req, nv, S, tag="idx_cc_test").clone()
