@@ -102,19 +102,39 @@ __global__ void quant_fp8_group_kernel(const __nv_bfloat16* __restrict__ x, long
   const int t = warp / groups, g = warp % groups;
   float v[4];
   float amax = 0.f;
+  const int i0 = g * 128 + lane * 4;
+  // four values per lane: one 8-byte load and one 4-byte store when the rows allow it
+  const bool vec = (i0 + 3 < K) && ((ldx & 3) == 0) && ((ldq & 3) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(x) & 7) == 0) && ((reinterpret_cast<uintptr_t>(q) & 3) == 0);
+  if (vec) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(x + t * ldx + i0);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
 #pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const int i = g * 128 + lane * 4 + k;
-    v[k] = i < K ? bf16_to_f(x[t * ldx + i]) : 0.f;
-    amax = fmaxf(amax, fabsf(v[k]));
+    for (int k = 0; k < 4; ++k) amax = fmaxf(amax, fabsf(v[k]));
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int i = i0 + k;
+      v[k] = i < K ? bf16_to_f(x[t * ldx + i]) : 0.f;
+      amax = fmaxf(amax, fabsf(v[k]));
+    }
   }
   amax = warp_max(amax);
   const float scale = fmaxf(amax, 1e-10f) * (1.f / 448.f);
   const float inv = 1.f / scale;
+  if (vec) {
+    uint32_t packed = 0;
 #pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const int i = g * 128 + lane * 4 + k;
-    if (i < K) q[t * ldq + i] = f_to_fp8(v[k] * inv);
+    for (int k = 0; k < 4; ++k) packed |= static_cast<uint32_t>(f_to_fp8(v[k] * inv)) << (8 * k);
+    *reinterpret_cast<uint32_t*>(q + t * ldq + i0) = packed;
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int i = i0 + k;
+      if (i < K) q[t * ldq + i] = f_to_fp8(v[k] * inv);
+    }
   }
   if (lane == 0) scales[static_cast<long long>(g) * scale_ld + t] = scale;
 }
