@@ -3,6 +3,7 @@ than the 126 MB L2 so that every call streams its operands from HBM as it does i
 
     python -m stkernel_b200.bench.op_bench --op mhc_fused --T 1
     python -m stkernel_b200.bench.op_bench --op mhc --T 1 --iters 3 --sets 3      # a small case for a profiler
+    python -m stkernel_b200.bench.op_bench --op indexer_tc --T 4096 --H 8192 --iters 20   # --H = compressed rows
 """
 from __future__ import annotations
 
@@ -28,7 +29,45 @@ def _mhc_sets(n_sets: int, h: int, hc: int, dev):
     return out
 
 
+def run_indexer(t: int, rows: int, iters: int, tensor_core: bool) -> dict:
+    """Prefill-shaped indexer scoring: t consecutive tokens of one request whose last token sees `rows` compressed rows
+    (ratio 4), 64 heads x 128 dims fp8, against the paged fp8 indexer cache."""
+    from ..ops import attention as A
+    from ..ops import cache as C
+    dev = torch.device("cuda:0")
+    ih, d = 64, 128
+    n_pages = (rows + 63) // 64 + 1
+    cache = C.PagedCache.allocate(n_pages, d, 64, True, "indexer", dev)
+    cache.buf[:, :64 * d] = torch.randint(0, 120, (n_pages, 64 * d), dtype=torch.uint8, device=dev)
+    cache.buf[:, 64 * d:64 * d + 256] = torch.full((n_pages, 64), 0.01, device=dev).view(torch.uint8).view(n_pages, 256)
+    bt = torch.arange(n_pages, dtype=torch.int32, device=dev)[None].contiguous()
+    q = torch.randn(t, ih, d, device=dev).to(BF16)
+    w = torch.rand(t, ih, device=dev)
+    pos = (torch.arange(t, device=dev) + (rows * 4 - t)).clamp_(min=0)
+    inv = Fn.inv_freq(64, 10000.0, dev)
+    qq, wf = C.indexer_q_prep(q, w, pos, inv, 64, True)
+    tok_req = torch.zeros(t, dtype=torch.int32, device=dev)
+    nv = A.compressed_valid(pos, 4)
+    A.USE_TENSOR_CORE_INDEXER = tensor_core
+    for _ in range(3):
+        A.indexer_scores(qq, wf, cache, bt, tok_req, nv, rows)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        A.indexer_scores(qq, wf, cache, bt, tok_req, nv, rows)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / iters
+    pairs = float(nv.sum())
+    flops = pairs * ih * d * 2
+    return {"op": "indexer_tc" if tensor_core else "indexer_cuda_core", "T": t, "rows": rows, "iters": iters,
+            "us_per_call": us, "token_row_pairs": pairs, "tflops": flops / us * 1e-6}
+
+
 def run(op: str, t: int, h: int, iters: int, n_sets: int, graph: bool = True) -> dict:
+    if op in ("indexer_tc", "indexer_cc"):
+        return run_indexer(t, h, iters, op == "indexer_tc")
     dev = torch.device("cuda:0")
     hc = 4
     sets = _mhc_sets(n_sets, h, hc, dev)
