@@ -79,12 +79,17 @@ def main() -> None:
     ap.add_argument("--graphs", type=int, default=1)
     ap.add_argument("--top", type=int, default=30)
     ap.add_argument("--out", default="")
+    ap.add_argument("--pdl", type=int, default=0,
+                    help="keep programmatic dependent launch on: a kernel's recorded time then includes its wait for "
+                         "the previous kernel, so per-kernel figures overlap (off by default for the table)")
     a = ap.parse_args()
     from ..config import EngineConfig, ParallelConfig, SchedulerConfig, flash_config
     from ..models.dsv4 import RandomSource, build_model_weights
     from ..runtime.engine import Engine, SamplingParams
     from .decode_bench import add_synthetic_requests, fill_caches_synthetic
 
+    from ..ops import _lib
+    _lib.call("stk_set_pdl", a.pdl)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))

@@ -60,7 +60,11 @@ __global__ void router_kernel(const float* __restrict__ logits, long long ldl, c
         if (lane == 0) set_status(status, kBadIndex, t);
         e = 0;
       }
-      const float s = __shfl_sync(0xffffffffu, sc[e >> 5], e & 31);
+      // static indexing only (a dynamic index would push sc[] and sel[] to local memory for the whole kernel)
+      float pick = 0.f;
+#pragma unroll
+      for (int i = 0; i < kPer; ++i) pick = (i == (e >> 5)) ? sc[i] : pick;
+      const float s = __shfl_sync(0xffffffffu, pick, e & 31);
       wsum += s;
       if (lane == j) { my_w = s; my_id = e; }
     }

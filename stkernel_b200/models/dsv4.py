@@ -271,16 +271,19 @@ class DSV4Model:
         # because scoring and top-k are independent per row).
         self.indexer_sp = tp_size > 1 and comm is not None
         self.indexer_sp_min_rows = int(os.environ.get("STK_INDEXER_SP_MIN_ROWS", "8"))
-        # Decode-sized steps are a chain of launches that each fill a fraction of the GPU: independent branches of a
-        # sub-block (compressor state update and KV insert beside the q / indexer chain, the shared expert beside the
-        # router) run on a second stream, also inside captured graphs, so the chain gets shorter.
         # Token-parallel sparse attention: every rank holds the whole latent KV cache, and gathering a token's
         # top-k rows costs the same for 8 heads as for 64, so with heads split over the ranks the gather work is
         # replicated.  Large steps instead exchange q (all-to-all: heads -> tokens), attend with all heads for 1/tp of
-        # the tokens, and exchange the output back (tokens -> heads).  Off by default (0): measured on 2 GPUs the
-        # tensor-core kernel's time follows heads x tokens (its softmax warps, not the gather, set the pace), so the
-        # exchange buys nothing there; the knob stays for caches whose gather dominates.
-        self.mla_tp_min_rows = int(os.environ.get("STK_MLA_TP_MIN_ROWS", "0"))
+        # the tokens, and exchange the output back (tokens -> heads).  Measured: with 32 heads per rank (2 GPUs) the
+        # tensor-core kernel's time follows heads x tokens (its softmax warps set the pace) and the exchange buys
+        # nothing; with 8 heads per rank (8 GPUs) a 4096-token chunk costs 2.06 ms against 2.93 ms for all 64 heads on
+        # one GPU, i.e. the gather dominates and 1/8 of the tokens with all heads is ~5x less work.  Default: on for
+        # steps of >= 1024 tokens when a rank holds at most 16 heads.
+        nh_local = cfg.num_attention_heads // max(1, tp_size)
+        self.mla_tp_min_rows = int(os.environ.get("STK_MLA_TP_MIN_ROWS", "1024" if nh_local <= 16 else "0"))
+        # Decode-sized steps are a chain of launches that each fill a fraction of the GPU: independent branches of a
+        # sub-block (compressor state update and KV insert beside the q / indexer chain, the shared expert beside the
+        # router) run on a second stream, also inside captured graphs, so the chain gets shorter.
         self.fork_max_t = int(os.environ.get("STK_FORK_MAX_T", "64")) if dev.type == "cuda" else 0
         self.side_stream = torch.cuda.Stream(dev) if self.fork_max_t > 0 else None
 
