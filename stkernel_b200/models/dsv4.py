@@ -265,6 +265,7 @@ class DSV4Model:
         self.topk_buffer: Optional[torch.Tensor] = None     # IndexCache: shared by consecutive C4A layers
         self.aux_layers: Tuple[int, ...] = ()
         self.aux_out: List[torch.Tensor] = []
+        self.stats = {"sp_steps": 0, "mla_token_parallel_calls": 0}     # which large-step paths ran (tests, debugging)
         # Sequence-parallel indexer: with TP the indexer weights are replicated, so each rank scores only its
         # share of a large step's rows and the top-k rows are all-gathered (overlay/attention.py
         # `_indexer_sp_owned_ranges` in the reference; here every row of a step is split evenly, which is exact
@@ -279,6 +280,11 @@ class DSV4Model:
         # nothing; with 8 heads per rank (8 GPUs) a 4096-token chunk costs 2.06 ms against 2.93 ms for all 64 heads on
         # one GPU, i.e. the gather dominates and 1/8 of the tokens with all heads is ~5x less work.  Default: on for
         # steps of >= 1024 tokens when a rank holds at most 16 heads.
+        # Sequence-parallel residual for large steps: the hyper-connection streams [T, hc, H] (and with them the mHC
+        # mixing, norms and residual adds, which are per token) live on 1/tp of the tokens per rank; a sub-block's
+        # input is all-gathered and its row-parallel output reduce-scattered (together the volume of the all-reduce
+        # they replace), so that work is no longer repeated on every rank.
+        self.sp_min_rows = int(os.environ.get("STK_SEQ_PARALLEL_MIN_ROWS", "1024")) if (tp_size > 1 and comm is not None) else 0
         nh_local = cfg.num_attention_heads // max(1, tp_size)
         self.mla_tp_min_rows = int(os.environ.get("STK_MLA_TP_MIN_ROWS", "1024" if nh_local <= 16 else "0"))
         # Decode-sized steps are a chain of launches that each fill a fraction of the GPU: independent branches of a
@@ -302,7 +308,10 @@ class DSV4Model:
         return self.comm.symm.gemm_ctx(t, n)
 
     # ---- attention sub-block ---------------------------------------------------
-    def attention(self, li: int, lw: LayerWeights, y: torch.Tensor, yq, meta: StepMeta, causal_meta=None) -> torch.Tensor:
+    def attention(self, li: int, lw: LayerWeights, y: torch.Tensor, yq, meta: StepMeta, causal_meta=None,
+                  scatter: bool = False) -> torch.Tensor:
+        """scatter: return this rank's 1/tp of the token rows of the reduced output (reduce-scatter) instead of all
+        rows (all-reduce)."""
         cfg = self.cfg
         T = y.shape[0]
         D, Rd = cfg.head_dim, cfg.qk_rope_head_dim
@@ -419,6 +428,8 @@ class DSV4Model:
             for gi, wg in enumerate(lw.w_oa):
                 Fn.linear(og[:, gi], wg, out=z[:, gi * cfg.o_lora_rank:(gi + 1) * cfg.o_lora_rank], tag=f"oa")
         with span("o_proj_b+allreduce", T):
+            if scatter:
+                return self.comm.reduce_scatter_dim0(Fn.linear(z, lw.w_ob, tag="ob"))
             ar = self._gemm_ar_ctx(T, cfg.hidden_size)
             out = Fn.linear(z, lw.w_ob, tag="ob", ar_ctx=ar)
             return out if ar is not None else self._all_reduce(out)
@@ -427,6 +438,7 @@ class DSV4Model:
                             topk_lens) -> torch.Tensor:
         """q [T, nh_local, D] -> o [T, nh_local, D], computed as all heads of this rank's share of the tokens."""
         tp, r = self.tp_size, self.tp_rank
+        self.stats["mla_token_parallel_calls"] += 1
         T, nh_l, D = q.shape
         share = -(-T // tp)
         sizes = [max(0, min(T, (s + 1) * share) - min(T, s * share)) for s in range(tp)]
@@ -447,7 +459,7 @@ class DSV4Model:
         return self.comm.all_to_all_dim0(send, [mine] * tp, sizes)
 
     # ---- MoE sub-block ----------------------------------------------------------
-    def moe(self, lw: LayerWeights, y: torch.Tensor, yq, meta: StepMeta) -> torch.Tensor:
+    def moe(self, lw: LayerWeights, y: torch.Tensor, yq, meta: StepMeta, scatter: bool = False) -> torch.Tensor:
         cfg = self.cfg
         T = y.shape[0]
         fork = self.side_stream is not None and 0 < T <= self.fork_max_t and lw.w_sh13 is not None
@@ -466,7 +478,7 @@ class DSV4Model:
             shared = self._shared_expert(lw, y, yq)
         out = M.moe_experts(y, ids, wts, lw.experts, cfg.swiglu_limit, shared, cfg.n_routed_experts,
                             shared_ready=ev_sh if fork else None)
-        return self._all_reduce(out)
+        return self.comm.reduce_scatter_dim0(out) if scatter else self._all_reduce(out)
 
     def _shared_expert(self, lw: LayerWeights, y: torch.Tensor, yq) -> Optional[torch.Tensor]:
         cfg = self.cfg
@@ -481,26 +493,31 @@ class DSV4Model:
             return Fn.linear(aq, lw.w_sh2, tag="sh2")
         return Fn.linear(Fn.swiglu_clamp(gu, cfg.swiglu_limit), lw.w_sh2, tag="sh2")
 
-    def layer(self, li: int, lw: LayerWeights, X: torch.Tensor, meta: StepMeta, pend=None, defer: bool = False):
+    def layer(self, li: int, lw: LayerWeights, X: torch.Tensor, meta: StepMeta, pend=None, defer: bool = False,
+              sp: bool = False):
         """One decoder layer.  `pend` = (sub-block output, streams, post, comb) left unmixed by the previous layer: its
         post-mix runs inside this layer's first pre-mix.  With `defer` the layer returns such a tuple instead of the
-        mixed streams."""
+        mixed streams.  With `sp` X holds this rank's 1/tp of the token rows (sequence-parallel residual)."""
         cfg = self.cfg
         n = X.shape[0]
-        want_q = lw.w_qa_kv.is_fp8 and Fn.wants_quant_act(n, X.device)
+        want_q = not sp and lw.w_qa_kv.is_fp8 and Fn.wants_quant_act(n, X.device)
         hc_args = (cfg.rms_norm_eps, cfg.hc_eps, cfg.hc_sinkhorn_iters)
         if pend is None:
             r = Fn.mhc_pre(X, *lw.hc_attn, lw.attn_norm, *hc_args, quant=want_q, tag="mhc_a")
         else:
             X, r = Fn.mhc_post_pre(*pend, *lw.hc_attn, lw.attn_norm, *hc_args, quant=want_q, tag="mhc_a")
         y, post, comb = r[0], r[1], r[2]
+        if sp:
+            y = self.comm.all_gather_dim0(y)
         with span("attention", n):
-            a = self.attention(li, lw, y, r[3] if want_q else None, meta)
-        want_q = lw.w_sh13 is not None and lw.w_sh13.is_fp8 and Fn.wants_quant_act(n, X.device)
+            a = self.attention(li, lw, y, r[3] if want_q else None, meta, scatter=sp)
+        want_q = not sp and lw.w_sh13 is not None and lw.w_sh13.is_fp8 and Fn.wants_quant_act(n, X.device)
         X, r = Fn.mhc_post_pre(a, X, post, comb, *lw.hc_ffn, lw.ffn_norm, *hc_args, quant=want_q, tag="mhc_f")
         y, post, comb = r[0], r[1], r[2]
+        if sp:
+            y = self.comm.all_gather_dim0(y)
         with span("moe", n):
-            f = self.moe(lw, y, r[3] if want_q else None, meta)
+            f = self.moe(lw, y, r[3] if want_q else None, meta, scatter=sp)
         if defer:
             return f, X, post, comb
         return Fn.mhc_post(f, X, post, comb)
@@ -509,19 +526,28 @@ class DSV4Model:
     def forward_hidden(self, meta: StepMeta) -> torch.Tensor:
         """-> final residual streams [T, hc, H]."""
         cfg = self.cfg
-        X = Fn.embed_hc(meta.token_ids, self.w.embed, cfg.hc_mult, cfg.vocab_size)
+        T = meta.token_ids.shape[0]
+        sp = (self.sp_min_rows > 0 and T >= self.sp_min_rows and T % self.tp_size == 0 and not self.aux_layers)
+        ids = meta.token_ids
+        if sp:
+            self.stats["sp_steps"] += 1
+            share = T // self.tp_size
+            ids = ids[self.tp_rank * share:(self.tp_rank + 1) * share]
+        X = Fn.embed_hc(ids, self.w.embed, cfg.hc_mult, cfg.vocab_size)
         self.aux_out = []
         pend = None
         last = len(self.w.layers) - 1
         for li, lw in enumerate(self.w.layers):
             defer = li != last and li not in self.aux_layers
-            out = self.layer(li, lw, X, meta, pend, defer)
+            out = self.layer(li, lw, X, meta, pend, defer, sp)
             if defer:
                 pend, X = out, out[1]
             else:
                 pend, X = None, out
             if li in self.aux_layers:
                 self.aux_out.append(X.float().mean(1).to(X.dtype))
+        if sp:
+            X = self.comm.all_gather_dim0(X)
         return X
 
     def head_hidden(self, X: torch.Tensor) -> torch.Tensor:

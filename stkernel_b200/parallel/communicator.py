@@ -78,7 +78,13 @@ class Communicator:
         if self.world_size == 1:
             return x
         assert x.shape[0] % self.world_size == 0
-        out = torch.empty(x.shape[0] // self.world_size, *x.shape[1:], dtype=x.dtype, device=x.device)
+        n = x.shape[0] // self.world_size
+        if not x.is_cuda:
+            # gloo has no reduce-scatter: sum everywhere, keep this rank's rows
+            y = x.contiguous().clone()
+            dist.all_reduce(y, group=self.group)
+            return y[self.rank * n:(self.rank + 1) * n].contiguous()
+        out = torch.empty(n, *x.shape[1:], dtype=x.dtype, device=x.device)
         dist.reduce_scatter_tensor(out, x.contiguous(), group=self.group)
         return out
 

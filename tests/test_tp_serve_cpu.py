@@ -44,9 +44,11 @@ def _wait_up(port, proc, timeout=180):
 
 def _launch(world, port, extra=()):
     # tiny thresholds so that the prompt's prefill step takes the sequence-parallel indexer path and the
-    # token-parallel attention path (q / output all-to-all) at world 2
+    # token-parallel attention path (q / output all-to-all) at world 2, and (for a prompt of even length) the
+    # sequence-parallel residual (all-gather / reduce-scatter around each sub-block)
     env = dict(os.environ, PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2", STK_CPU_ACT_FP32="1",
-               STK_INDEXER_SP_MIN_ROWS="4", STK_MLA_TP_MIN_ROWS="4")
+               STK_INDEXER_SP_MIN_ROWS="4", STK_MLA_TP_MIN_ROWS="4",
+               STK_SEQ_PARALLEL_MIN_ROWS="4")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(_free_port()), "-m", "stkernel_b200.serve.tp_worker", "--tiny", "--port", str(port),
            "--tensor-parallel-size", str(world), "--max-model-len", "512", "--max-num-seqs", "4",
@@ -80,7 +82,9 @@ def test_tp2_lockstep_serving_matches_tp1():
             chat = _post(port, "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4,
                                                         "temperature": 0.7, "seed": 3, "ignore_eos": True})
             assert chat["usage"]["completion_tokens"] == 4
-            outs[world] = r1["choices"][0]["text"]
+            # one character more: of the two prompt lengths one is even, which the sequence-parallel residual needs
+            r3 = _post(port, "/v1/completions", dict(body, prompt="!" + body["prompt"][::-1]))
+            outs[world] = (r1["choices"][0]["text"], r3["choices"][0]["text"])
         finally:
             _stop(proc)
     # the same weights split over two ranks give the same greedy text (fp32 activations on CPU)
