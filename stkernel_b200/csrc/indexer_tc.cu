@@ -212,19 +212,26 @@ indexer_scores_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
           const int tj = t + j;
           const float4* wj = reinterpret_cast<const float4*>(a.w + static_cast<long long>(tj) * kIdxHeads);
           float acc = 0.f;
+          // all 64 head columns of this token are requested before the single wait
+          uint32_t v0[32], v1[32];
+          tmem_ld_32x32(tmem_base + lane_addr + ab * N + j * kIdxHeads, v0);
+          tmem_ld_32x32(tmem_base + lane_addr + ab * N + j * kIdxHeads + 32, v1);
+          tmem_ld_wait();
 #pragma unroll
-          for (int c = 0; c < kIdxHeads; c += 16) {
-            uint32_t v[16];
-            tmem_ld_32x16(tmem_base + lane_addr + ab * N + j * kIdxHeads + c, v);
-            tmem_ld_wait();
+          for (int i = 0; i < 32; i += 4) {
+            const float4 w4 = __ldg(wj + (i >> 2));
+            acc = fmaf(w4.x, fmaxf(__uint_as_float(v0[i]), 0.f), acc);
+            acc = fmaf(w4.y, fmaxf(__uint_as_float(v0[i + 1]), 0.f), acc);
+            acc = fmaf(w4.z, fmaxf(__uint_as_float(v0[i + 2]), 0.f), acc);
+            acc = fmaf(w4.w, fmaxf(__uint_as_float(v0[i + 3]), 0.f), acc);
+          }
 #pragma unroll
-            for (int i = 0; i < 16; i += 4) {
-              const float4 w4 = __ldg(wj + ((c + i) >> 2));
-              acc = fmaf(w4.x, fmaxf(__uint_as_float(v[i]), 0.f), acc);
-              acc = fmaf(w4.y, fmaxf(__uint_as_float(v[i + 1]), 0.f), acc);
-              acc = fmaf(w4.z, fmaxf(__uint_as_float(v[i + 2]), 0.f), acc);
-              acc = fmaf(w4.w, fmaxf(__uint_as_float(v[i + 3]), 0.f), acc);
-            }
+          for (int i = 0; i < 32; i += 4) {
+            const float4 w4 = __ldg(wj + 8 + (i >> 2));
+            acc = fmaf(w4.x, fmaxf(__uint_as_float(v1[i]), 0.f), acc);
+            acc = fmaf(w4.y, fmaxf(__uint_as_float(v1[i + 1]), 0.f), acc);
+            acc = fmaf(w4.z, fmaxf(__uint_as_float(v1[i + 2]), 0.f), acc);
+            acc = fmaf(w4.w, fmaxf(__uint_as_float(v1[i + 3]), 0.f), acc);
           }
           if (r < a.n_valid[tj]) a.scores[static_cast<long long>(tj) * a.ld_scores + r] = acc * kscale;
         }
