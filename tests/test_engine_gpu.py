@@ -67,21 +67,26 @@ def test_graph_replay_matches_eager_and_is_deterministic():
 
 def test_stream_fork_and_dependent_launch_do_not_change_tokens():
     """The second-stream fork of the decode sub-blocks and programmatic dependent launch only reorder independent work:
-    sampled tokens equal those of the plain single-stream chain, eagerly and under graph replay."""
+    sampled tokens equal those of the plain single-stream chain — compared eagerly and, separately, under graph replay
+    (graph buckets pad the batch, which changes split counts and with them summation order, so eager and replayed runs
+    are not compared with each other here)."""
     cfg = flash_config(num_layers=4, n_routed_experts=16, vocab_size=4096)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=torch.Generator().manual_seed(n)).tolist() for n in (300, 41)]
-    outs = []
-    for fork, pdl, cap in ((0, 0, 0), (64, 1, 0), (64, 1, 4), (0, 1, 4)):
-        _lib.call("stk_set_pdl", pdl)
-        try:
-            eng = make_engine(cfg, RandomSource(3), graph_cap=cap, ctx=2048, chunk=512)
-            eng.model.fork_max_t = fork
-            outs.append(eng.generate(prompts, SamplingParams(temperature=0.8, seed=11, max_tokens=12)))
-            torch.cuda.synchronize()
-            _lib.check_status()
-        finally:
-            _lib.call("stk_set_pdl", 1)
-    assert outs[0] == outs[1] == outs[2] == outs[3]
+    for cap in (0, 4):
+        outs = {}
+        for fork, pdl in ((0, 0), (64, 0), (0, 1), (64, 1)):
+            _lib.call("stk_set_pdl", pdl)
+            try:
+                eng = make_engine(cfg, RandomSource(3), graph_cap=cap, ctx=2048, chunk=512)
+                eng.model.fork_max_t = fork
+                outs[(fork, pdl)] = eng.generate(prompts, SamplingParams(temperature=0.8, seed=11, max_tokens=12))
+                torch.cuda.synchronize()
+                _lib.check_status()
+            finally:
+                _lib.call("stk_set_pdl", 1)
+        base = outs[(0, 0)]
+        for k, v in outs.items():
+            assert v == base, (cap, k)
 
 
 def test_flash_shaped_layer_runs():
