@@ -11,6 +11,7 @@
 //
 // Takes the place of the reference's flashinfer_trtllm_batch_decode_sparse_mla_dsv4 call
 // (overlay/flashinfer_sparse.py:387-400,528-541).
+#define STK_PDL_CLASS 128      // bit of this file's kernels in the PDL mask (STK_PDL, stk_set_pdl_mask)
 #include "common.cuh"
 
 namespace stk {

@@ -18,6 +18,7 @@
 //
 // Replaces the reference's FlashInfer sparse-MLA decode/prefill kernels
 // (overlay/flashinfer_sparse.py:323-541).
+#define STK_PDL_CLASS 128      // bit of this file's kernels in the PDL mask (STK_PDL, stk_set_pdl_mask)
 #include "common.cuh"
 
 namespace stk {

@@ -273,7 +273,10 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 }  // namespace stk
 
 // ---- host: kernel launch with the programmatic-serialization attribute ---------
-extern "C" int stk_pdl_enabled();
+extern "C" int stk_pdl_enabled();      // bit mask: which files' kernels launch with the attribute
+#ifndef STK_PDL_CLASS
+#define STK_PDL_CLASS 1
+#endif
 
 namespace stk {
 template <typename... KArgs, typename... Args>
@@ -287,7 +290,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
-  cfg.numAttrs = stk_pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = (stk_pdl_enabled() & STK_PDL_CLASS) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 }  // namespace stk

@@ -6,6 +6,7 @@
 // per_token_group_quant "armada" and SiluAndMulWithClamp (MEASUREMENTS.md:544-546).
 #include <stdlib.h>
 
+#define STK_PDL_CLASS 1      // bit of this file's kernels in the PDL mask (STK_PDL, stk_set_pdl_mask)
 #include "common.cuh"
 
 namespace stk {
@@ -234,12 +235,17 @@ static int g_pdl = -1;
 STK_API int stk_pdl_enabled() {
   if (g_pdl < 0) {
     const char* e = getenv("STK_PDL");
-    g_pdl = (e != nullptr && e[0] == '0') ? 0 : 1;
+    g_pdl = e != nullptr ? atoi(e) : 0xffff;      // STK_PDL=0: off; STK_PDL=<mask>: only those files' kernels
+    if (e != nullptr && g_pdl == 1) g_pdl = 0xffff;
   }
   return g_pdl;
 }
+STK_API int stk_set_pdl_mask(int mask) {
+  g_pdl = mask;
+  return 0;
+}
 STK_API int stk_set_pdl(int on) {
-  g_pdl = on ? 1 : 0;
+  g_pdl = on ? 0xffff : 0;
   return 0;
 }
 

@@ -17,6 +17,7 @@
 // probes/oproj_prof.py:65-71) and its bf16 cuBLAS projections.
 #include <string.h>
 
+#define STK_PDL_CLASS 8      // bit of this file's kernels in the PDL mask (STK_PDL, stk_set_pdl_mask)
 #include "common.cuh"
 #include "stk_c_api.h"
 #include "symm.cuh"

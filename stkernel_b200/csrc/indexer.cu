@@ -6,6 +6,7 @@
 // persistent_topk: probes/sai_probe.py:2316-2337,2535-2595).  This file holds the exact
 // CUDA-core scorer used for decode-sized batches and as the numerics check of the
 // tensor-core scorer, and the top-k kernel shared by both.
+#define STK_PDL_CLASS 64      // bit of this file's kernels in the PDL mask (STK_PDL, stk_set_pdl_mask)
 #include "common.cuh"
 
 namespace stk {

@@ -13,6 +13,7 @@
 //
 // Tokens are walked as tiles of up to TPT consecutive tokens of the same request; when the request changes inside a
 // chunk the K block is reloaded (the MMA thread signals when the old block is no longer read).  Every wait is bounded.
+#define STK_PDL_CLASS 16      // bit of this file's kernels in the PDL mask (STK_PDL, stk_set_pdl_mask)
 #include "common.cuh"
 
 namespace stk {

@@ -13,6 +13,7 @@
 // rope bf16, and 8 scale bytes stored after the 64 data rows of the page:
 //   page = [64 x data_bytes][64 x 8 scale bytes][padding to page_stride].
 // Offsets use 64-bit arithmetic (caches exceed 2^31 bytes).
+#define STK_PDL_CLASS 32      // bit of this file's kernels in the PDL mask (STK_PDL, stk_set_pdl_mask)
 #include "common.cuh"
 
 namespace stk {

@@ -7,6 +7,7 @@
 //   compressed_valid       n_valid[t] = (pos+1) / ratio   (causal bound of overlay/indexer.py:948-1020)
 //   c128_indices           the most recent `cap` complete ratio-128 windows as slots
 //   token_maps             tok_req / first / last positions from per-request query ranges
+#define STK_PDL_CLASS 512      // bit of this file's kernels in the PDL mask (STK_PDL, stk_set_pdl_mask)
 #include "common.cuh"
 
 namespace stk {

@@ -9,6 +9,7 @@
 // and its post mix (overlay/nvidia_model.py:1779-1785).  For large token counts the dot
 // products can instead come from the tcgen05 GEMM (fn kept as a bf16 copy); `mhc_finalize`
 // then takes them as a single pre-reduced split.
+#define STK_PDL_CLASS 4      // bit of this file's kernels in the PDL mask (STK_PDL, stk_set_pdl_mask)
 #include "common.cuh"
 
 namespace stk {
@@ -688,7 +689,7 @@ static int mhc_cluster_launch(const void* x, const float* fn, const float* base,
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = stk_pdl_enabled() ? 2 : 1;
+  cfg.numAttrs = (stk_pdl_enabled() & STK_PDL_CLASS) ? 2 : 1;
   const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
   const __nv_bfloat16* nw = (const __nv_bfloat16*)norm_w;
   __nv_bfloat16* yp = (__nv_bfloat16*)y;

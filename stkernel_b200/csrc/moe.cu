@@ -15,6 +15,7 @@
 // Prefill-sized batches use the tcgen05 grouped GEMM instead.
 #include <cuda_fp4.h>
 
+#define STK_PDL_CLASS 1024      // bit of this file's kernels in the PDL mask (STK_PDL, stk_set_pdl_mask)
 #include "common.cuh"
 
 namespace stk {

@@ -9,6 +9,7 @@
 //   markov_topk_bias  DSpark first-order Markov head on the base-logit top-k:
 //                     out[idx] = base[idx] + W2[idx] . embed, -inf elsewhere
 //                     (overlay/dspark_v2.py:184-236).
+#define STK_PDL_CLASS 256      // bit of this file's kernels in the PDL mask (STK_PDL, stk_set_pdl_mask)
 #include "common.cuh"
 
 namespace stk {

@@ -8,6 +8,7 @@
 //
 // FP8 weights carry 128x128 block scales (applied per 16-value chunk); activations are used
 // unquantised, which is at least as accurate as the quantised tensor-core path.
+#define STK_PDL_CLASS 2      // bit of this file's kernels in the PDL mask (STK_PDL, stk_set_pdl_mask)
 #include "common.cuh"
 
 namespace stk {
