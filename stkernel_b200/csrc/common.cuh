@@ -274,11 +274,24 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 
 // ---- host: kernel launch with the programmatic-serialization attribute ---------
 extern "C" int stk_pdl_enabled();      // bit mask: which files' kernels launch with the attribute
+extern "C" int stk_pdl_eager();        // 1: also outside stream capture (experiments only, see pdl_use)
 #ifndef STK_PDL_CLASS
 #define STK_PDL_CLASS 1
 #endif
 
 namespace stk {
+// The attribute is used only while the stream is being captured into a CUDA graph.  There every edge from a copy or
+// memset node to a kernel node is a full dependency by construction.  In eager stream order a kernel that follows a
+// cudaMemcpyAsync (step inputs, torch copies, weight uploads) was observed to produce different results with the
+// attribute set (weights quantised right after their upload differed), so eager launches stay plain.
+inline bool pdl_use(cudaStream_t st, int cls) {
+  if (!(stk_pdl_enabled() & cls)) return false;
+  if (stk_pdl_eager()) return true;
+  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &cs) != cudaSuccess) return false;
+  return cs == cudaStreamCaptureStatusActive;
+}
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
@@ -290,7 +303,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
-  cfg.numAttrs = (stk_pdl_enabled() & STK_PDL_CLASS) ? 1 : 0;
+  cfg.numAttrs = pdl_use(st, STK_PDL_CLASS) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 }  // namespace stk

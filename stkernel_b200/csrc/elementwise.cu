@@ -240,6 +240,14 @@ STK_API int stk_pdl_enabled() {
   }
   return g_pdl;
 }
+STK_API int stk_pdl_eager() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("STK_PDL_EAGER");
+    v = (e != nullptr && e[0] == '1') ? 1 : 0;
+  }
+  return v;
+}
 STK_API int stk_set_pdl_mask(int mask) {
   g_pdl = mask;
   return 0;

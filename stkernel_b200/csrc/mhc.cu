@@ -689,7 +689,7 @@ static int mhc_cluster_launch(const void* x, const float* fn, const float* base,
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = (stk_pdl_enabled() & STK_PDL_CLASS) ? 2 : 1;
+  cfg.numAttrs = pdl_use((cudaStream_t)stream, STK_PDL_CLASS) ? 2 : 1;
   const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
   const __nv_bfloat16* nw = (const __nv_bfloat16*)norm_w;
   __nv_bfloat16* yp = (__nv_bfloat16*)y;
