@@ -280,10 +280,10 @@ extern "C" int stk_pdl_eager();        // 1: also outside stream capture (experi
 #endif
 
 namespace stk {
-// The attribute is used only while the stream is being captured into a CUDA graph.  There every edge from a copy or
-// memset node to a kernel node is a full dependency by construction.  In eager stream order a kernel that follows a
-// cudaMemcpyAsync (step inputs, torch copies, weight uploads) was observed to produce different results with the
-// attribute set (weights quantised right after their upload differed), so eager launches stay plain.
+// The attribute is used only while the stream is being captured into a CUDA graph: that is where the launch-bound
+// decode chain runs, and there every edge from a copy or memset node to a kernel node is a full dependency by
+// construction.  Eager launches (prefill, weight preparation, tests) follow torch copies and uploads in plain stream
+// order and stay plain; STK_PDL_EAGER=1 lifts that for experiments.
 inline bool pdl_use(cudaStream_t st, int cls) {
   if (!(stk_pdl_enabled() & cls)) return false;
   if (stk_pdl_eager()) return true;

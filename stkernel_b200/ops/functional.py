@@ -23,6 +23,7 @@ F32 = torch.float32
 FP8 = torch.float8_e4m3fn
 
 import os as _os
+import weakref
 
 # STK_CPU_ACT_FP32=1: fp32 activations on the CPU path (exact comparisons across TP degrees)
 _CPU_ACT = [torch.float32 if _os.environ.get("STK_CPU_ACT_FP32") == "1" else torch.bfloat16]
@@ -280,15 +281,19 @@ _MHC_WCAT: dict = {}
 def _mhc_wcat(fn: torch.Tensor, n_mix: int) -> torch.Tensor:
     """[128, hc*H] bf16: rows [0, n_mix) the bf16 rounding of fn, rows [32, 32 + n_mix) the bf16 rounding of the
     remainder, zeros elsewhere (a full 128-row weight tile).  Built once per weight tensor."""
-    key = (fn.data_ptr(), fn.shape)
-    w = _MHC_WCAT.get(key)
-    if w is None:
-        hi = fn.to(BF16)
-        lo = (fn - hi.to(F32)).to(BF16)
-        w = torch.zeros(128, fn.shape[1], dtype=BF16, device=fn.device)
-        w[:n_mix] = hi
-        w[32:32 + n_mix] = lo
-        _MHC_WCAT[key] = w
+    # keyed by the tensor object, not its address: a freed weight's address is reused by the allocator
+    ent = _MHC_WCAT.get(id(fn))
+    if ent is not None and ent[0]() is fn and ent[2] == fn._version:
+        return ent[1]
+    hi = fn.to(BF16)
+    lo = (fn - hi.to(F32)).to(BF16)
+    w = torch.zeros(128, fn.shape[1], dtype=BF16, device=fn.device)
+    w[:n_mix] = hi
+    w[32:32 + n_mix] = lo
+    if len(_MHC_WCAT) > 4096:
+        for k in [k for k, v in _MHC_WCAT.items() if v[0]() is None]:
+            del _MHC_WCAT[k]
+    _MHC_WCAT[id(fn)] = (weakref.ref(fn), w, fn._version)
     return w
 
 

@@ -265,3 +265,19 @@ def test_span_recorder_accounting():
     with r.span("cpu-only", 1):                                 # no CUDA here: passes through without recording
         pass
     assert ("decode", "cpu-only") not in r.totals
+
+
+def test_mhc_split_weight_cache_follows_the_tensor_not_its_address():
+    """The bf16 hi/lo split of an mHC mix matrix is cached per weight tensor; a new tensor that the allocator places at a
+    freed tensor's address must get its own split."""
+    import torch
+    from stkernel_b200.ops import functional as Fn
+    seen = []
+    for seed in range(6):
+        fn = torch.randn(24, 256, generator=torch.Generator().manual_seed(seed)) * 0.02
+        w = Fn._mhc_wcat(fn, 24)
+        assert torch.equal(w[:24].float() + w[32:56].float(), (fn.to(torch.bfloat16).float() + (fn - fn.to(torch.bfloat16).float()).to(torch.bfloat16).float()))
+        assert Fn._mhc_wcat(fn, 24) is w                     # second call: cached
+        seen.append(fn.data_ptr())
+        del fn, w
+    # (the CPU allocator usually hands the same block out again: the case the cache has to survive)
