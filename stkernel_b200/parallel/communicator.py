@@ -39,6 +39,23 @@ class Communicator:
                 self.symm = None
                 self.disabled_reason = f"{type(e).__name__}: {e}"
 
+        if self.device.type == "cuda" and self.world_size > 1:
+            self._warm_up_nccl()
+
+    def _warm_up_nccl(self) -> None:
+        """NCCL sets up its point-to-point and ring connections at the first use of each collective kind (seconds for
+        all-to-all on 8 GPUs): pay that at start-up, not inside the first large prefill step."""
+        w = self.world_size
+        x = torch.zeros(w * 8, dtype=torch.bfloat16, device=self.device)
+        out = torch.empty_like(x)
+        dist.all_to_all_single(out, x, group=self.group)
+        big = torch.empty(w * x.numel(), dtype=x.dtype, device=self.device)
+        dist.all_gather_into_tensor(big, x, group=self.group)
+        small = torch.empty(x.numel() // w, dtype=x.dtype, device=self.device)
+        dist.reduce_scatter_tensor(small, x, group=self.group)
+        dist.all_reduce(x, group=self.group)
+        torch.cuda.synchronize(self.device)
+
     # ---- collectives -------------------------------------------------------------
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         if self.world_size == 1:
