@@ -97,24 +97,6 @@ mhc_finalize_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict
   const long long HC = static_cast<long long>(hc) * H;
   const __nv_bfloat16* xt = x + t * HC;
 
-  // The streams of this token are requested before the serial mix/Sinkhorn prologue (one warp), so that their DRAM
-  // latency overlaps it: up to two 8-element chunks per thread and stream, held in registers.
-  constexpr int kPreChunks = 2;
-  const bool pref = hc <= 4 && (H & 7) == 0 && H <= 8 * kPreChunks * static_cast<int>(blockDim.x) &&
-                    (reinterpret_cast<uintptr_t>(x) & 15) == 0;
-  uint4 xr[kPreChunks][4];
-  if (pref) {
-#pragma unroll
-    for (int u = 0; u < kPreChunks; ++u) {
-      const int c = threadIdx.x + u * blockDim.x;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        xr[u][j] = make_uint4(0, 0, 0, 0);
-        if (j < hc && c * 8 < H) xr[u][j] = __ldg(reinterpret_cast<const uint4*>(xt + static_cast<long long>(j) * H + c * 8));
-      }
-    }
-  }
-
   float ssq = 0.f;
   if (!sumsq_in_partial) {
     for (int k = threadIdx.x * 2; k < HC; k += blockDim.x * 2) {
@@ -194,37 +176,6 @@ mhc_finalize_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict
 
   // weighted stream sum (rounded to bf16 like the layer input the norm sees)
   float ss = 0.f;
-  if (pref) {
-#pragma unroll
-    for (int u = 0; u < kPreChunks; ++u) {
-      const int c = threadIdx.x + u * blockDim.x;
-      if (c * 8 < H) {
-        float acc[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (j < hc) {
-            const float pj = pre[j];
-            const uint32_t wds[4] = {xr[u][j].x, xr[u][j].y, xr[u][j].z, xr[u][j].w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&wds[e]);
-              acc[2 * e] = fmaf(pj, __low2float(v), acc[2 * e]);
-              acc[2 * e + 1] = fmaf(pj, __high2float(v), acc[2 * e + 1]);
-            }
-          }
-        }
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          float a0 = acc[e];
-          if (mode == 0) a0 = bf16_to_f(__float2bfloat16(a0));
-          ybuf[c * 8 + e] = a0;
-          ss = fmaf(a0, a0, ss);
-        }
-      }
-    }
-  } else {
   for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
     float a0 = 0.f, a1 = 0.f;
     for (int j = 0; j < hc; ++j) {
@@ -240,8 +191,6 @@ mhc_finalize_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict
     ybuf[i + 1] = a1;
     ss = fmaf(a0, a0, fmaf(a1, a1, ss));
   }
-  }
-  if (pref) __syncthreads();            // ybuf is read below in a different thread layout
   float r = 1.f;
   if (mode == 0 && norm_w != nullptr) {
     ss = block_sum(ss, red);
