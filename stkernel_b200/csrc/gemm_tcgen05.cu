@@ -59,6 +59,9 @@ struct GemmArgs {
   // rescale is a single multiplier per thread instead of one per accumulator column.  T/N/tiles_* then describe the
   // swapped problem (a.N = tokens, a.T = weight rows); out is still [tokens, ldo].
   int token_major;
+  // Whether the split-K reduction may write `out` with 16-byte (fp32) / 4-byte (bf16) vector stores: the host sets
+  // it from the alignment of `out` and `ldo`; otherwise the reduction writes element by element.
+  int out_vec_ok;
 };
 
 constexpr int kArKind = 3;
@@ -490,7 +493,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
             const int nthr2 = kEpiWarps * 32;
             const int rows_valid = min(BT, a.T - tt * BT);
             const int cols_valid = min(128, a.N - tn * 128);
-            const bool vec_ok = (cols_valid == 128) && ((a.N & 3) == 0);
+            const bool vec_ok = (cols_valid == 128) && ((a.N & 3) == 0) && (a.out_vec_ok || a.ar_enabled);
             if (vec_ok) {
               for (int v = et2; v < rows_valid * 32; v += nthr2) {
                 const int r = v >> 5, c4 = (v & 31) * 4;
@@ -709,6 +712,10 @@ static int gemm_launch(const void* W, long long ldw, const void* X, long long ld
   a.workspace = workspace; a.counters = counters; a.status = status;
   a.group_tiles = groups > 1 ? (N / groups) / 128 : 0;
   a.group_k_elems = K;
+  {
+    const uintptr_t o = reinterpret_cast<uintptr_t>(out);
+    a.out_vec_ok = out_fp32 ? ((o & 15) == 0 && (ldo & 3) == 0) : ((o & 3) == 0 && (ldo & 1) == 0);
+  }
   a.ar_enabled = 0;
   memset(&a.ar, 0, sizeof(a.ar));
   if (ar_ctx != nullptr) {
@@ -784,9 +791,7 @@ static void* g_noalloc_ptr[kMaxDevices] = {};
 
 STK_API long long stk_gemm_noalloc_max_workspace_bytes() { return kNoAllocWorkspaceBytes; }
 
-STK_API int stk_gemm_noalloc(const void* W, long long ldw, const void* X, long long ldx, void* out, long long ldo,
-                             int T, int N, int K, int is_fp8, int out_fp32, const float* w_scale, int w_scale_ld,
-                             const float* x_scale, int x_scale_ld, int splits, int* status, int sm_count, void* stream) {
+static int noalloc_resolve(unsigned char** base) {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -30;
   if (g_noalloc_ptr[dev] == nullptr) {
@@ -796,6 +801,27 @@ STK_API int stk_gemm_noalloc(const void* W, long long ldw, const void* X, long l
     if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) return -31;
     g_noalloc_ptr[dev] = p;
   }
+  *base = static_cast<unsigned char*>(g_noalloc_ptr[dev]);
+  return 0;
+}
+
+// Zeroes the built-in tile counters on `stream` (a memset node, no allocation).  Needed only after a call whose
+// status word came back non-zero: a split that gave up a wait never counted itself in, so its tile's counter is
+// left between 1 and splits-1 and the next split-K call on that tile would reduce too early.
+STK_API int stk_gemm_noalloc_reset(void* stream) {
+  unsigned char* base = nullptr;
+  const int rc = noalloc_resolve(&base);
+  if (rc != 0) return rc;
+  return cudaMemsetAsync(base + kNoAllocWorkspaceBytes, 0, kNoAllocCounters * 4, reinterpret_cast<cudaStream_t>(stream)) ==
+                 cudaSuccess ? 0 : -34;
+}
+
+STK_API int stk_gemm_noalloc(const void* W, long long ldw, const void* X, long long ldx, void* out, long long ldo,
+                             int T, int N, int K, int is_fp8, int out_fp32, const float* w_scale, int w_scale_ld,
+                             const float* x_scale, int x_scale_ld, int splits, int* status, int sm_count, void* stream) {
+  unsigned char* base = nullptr;
+  const int rc = noalloc_resolve(&base);
+  if (rc != 0) return rc;
   if (splits < 1) splits = 1;
   const int bt = stk_gemm_pick_bt(T, is_fp8);
   const long long tiles = static_cast<long long>((N + 127) / 128) * ((T + bt - 1) / bt);
@@ -803,7 +829,6 @@ STK_API int stk_gemm_noalloc(const void* W, long long ldw, const void* X, long l
     if (static_cast<long long>(splits) * T * N * 4 > kNoAllocWorkspaceBytes) return -32;   // beyond the built-in scratch
     if (tiles > kNoAllocCounters) return -33;
   }
-  unsigned char* base = static_cast<unsigned char*>(g_noalloc_ptr[dev]);
   float* workspace = reinterpret_cast<float*>(base);
   int* counters = reinterpret_cast<int*>(base + kNoAllocWorkspaceBytes);
   return stk_gemm(W, ldw, X, ldx, out, ldo, T, N, K, is_fp8, out_fp32, w_scale, w_scale_ld, x_scale, x_scale_ld, splits,

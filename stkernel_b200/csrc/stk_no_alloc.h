@@ -24,8 +24,18 @@
 //     them on one stream.  The counters are zero between calls: the kernel resets each one as its
 //     tile completes; the workspace keeps the previous call's partials and is fully overwritten
 //     before it is read.
+//   * After a call that left a non-zero code in `status` (a wait inside the kernel ran out), the
+//     counters may be left non-zero and nothing outside the library can reach them: enqueue
+//     stk_gemm_noalloc_reset(stream) before the next split-K call.
+//   * `out` may have any alignment and row stride: the split-K reduction uses vector stores only when
+//     `out` is 16-byte aligned with ldo % 4 == 0 (fp32) or 4-byte aligned with an even ldo (bf16), and
+//     element stores otherwise.
+//   * The array's device address is cached per device ordinal for the primary context (the one the
+//     CUDA runtime uses); a host that drives several contexts on one device must make the primary
+//     context current for these calls.
 //   * Return value: 0 on launch, negative on rejected arguments (same codes as stk_gemm, plus
-//     -30 no current device, -31 symbol lookup failed, -32 workspace too small, -33 too many tiles).
+//     -30 no current device, -31 symbol lookup failed, -32 workspace too small, -33 too many tiles,
+//     -34 reset could not be enqueued).
 #pragma once
 #ifdef __cplusplus
 extern "C" {
@@ -36,6 +46,9 @@ long long stk_gemm_noalloc_max_workspace_bytes(void);
 int stk_gemm_noalloc(const void* W, long long ldw, const void* X, long long ldx, void* out, long long ldo, int T, int N,
                      int K, int is_fp8, int out_fp32, const float* w_scale, int w_scale_ld, const float* x_scale,
                      int x_scale_ld, int splits, int* status, int sm_count, void* stream);
+
+// Zeroes the built-in tile counters on `stream`; allocates nothing.  See the rule on non-zero status above.
+int stk_gemm_noalloc_reset(void* stream);
 
 #ifdef __cplusplus
 }

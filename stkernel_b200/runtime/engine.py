@@ -24,6 +24,17 @@ from .kv import KVManager, OutOfPages, size_pools
 from .metrics import Metrics
 
 
+class DeviceStatusError(RuntimeError):
+    """A kernel of the step recorded a non-zero status (a bounded wait ran out, or an index was out of range)."""
+
+    NAMES = {1: "mbarrier wait timed out", 2: "peer flag wait timed out", 3: "index out of range",
+             4: "local flag wait timed out"}
+
+    def __init__(self, code: int, detail: int):
+        super().__init__(f"device status {code} ({self.NAMES.get(code, '?')}), detail {detail}")
+        self.code, self.detail = code, detail
+
+
 @dataclass
 class SamplingParams:
     temperature: float = 0.0
@@ -254,6 +265,7 @@ class Engine:
         self.use_graphs = self.device.type == "cuda" and sc.graph_cap > 0
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
+        self._h_status: Optional[torch.Tensor] = None
 
     # ---- public API ------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
@@ -291,6 +303,42 @@ class Engine:
         while self.has_work():
             self.step()
         return [self.requests[i].output for i in ids]
+
+    # ---- device status ---------------------------------------------------------------
+    def _queue_status_read(self) -> None:
+        """Queue the copy of the kernels' status word behind the step, next to the sampled tokens: the host reads
+        both after the one synchronisation the step already has."""
+        if self.device.type != "cuda":
+            return
+        from ..ops import _lib
+        if self._h_status is None:
+            self._h_status = torch.zeros(2, dtype=torch.int32, pin_memory=True)
+        self._h_status.copy_(_lib.status_buffer(), non_blocking=True)
+
+    def _read_status(self) -> Tuple[int, int]:
+        """(code, detail) of the step just synchronised; (0, 0) = every bounded wait and index check passed."""
+        if self._h_status is None:
+            return 0, 0
+        return int(self._h_status[0]), int(self._h_status[1])
+
+    def _check_device_status(self) -> None:
+        """A kernel that gave up a bounded wait (peer flag, mbarrier) or met an out-of-range index skipped its work,
+        so this step's tokens are not to be trusted: count it, switch the symmetric-memory collectives off for good
+        (later all-reduces take the NCCL path, as overlay/dsv4_oneshot_shim.py:153-162 does after a failed
+        heartbeat) and fail the step.  Under lock-step tensor-parallel serving the raising rank ends the job
+        (`serve/tp_worker.py`), which the supervisor restarts."""
+        code, detail = self._read_status()
+        if code == 0:
+            return
+        self.metrics.device_status_errors += 1
+        if self.device.type == "cuda":
+            from ..ops import _lib
+            _lib.status_buffer().zero_()
+        comm = self.model.comm
+        symm = getattr(comm, "symm", None) if comm is not None else None
+        if symm is not None:
+            symm.disable(f"device status {code} (detail {detail}) in step {self.metrics.steps_total}")
+        raise DeviceStatusError(code, detail)
 
     # ---- one step -----------------------------------------------------------------
     def _stage(self, seqs: List[ScheduledSeq]) -> Tuple[int, int, int]:
@@ -347,11 +395,15 @@ class Engine:
         swa_slots, swa_lens = A.swa_indices(positions, tok_req, self.kv.swa.table_dev, cfg.sliding_window)
         return StepMeta(b.d_tokens[:t_pad], tok_req, positions, first, last, sm, swa_slots, swa_lens, max_comp_rows)
 
-    def _run_model(self, t_pad: int, n_req: int, ns: int, max_comp_rows: int) -> torch.Tensor:
-        """-> sampled tokens [ns] (device)."""
+    def _run_model(self, t_pad: int, n_req: int, ns: int, max_comp_rows: int, identity_rows: bool = False) -> torch.Tensor:
+        """-> sampled tokens [ns] (device).
+
+        identity_rows: token i is the sampling row of request i (a pure-decode step).  The staged row list is then
+        not read at all: a padded decode bucket has more rows than the step uploaded, and the entries past them still
+        hold an earlier (possibly much larger) step's row numbers."""
         b = self.buf
         meta = self._build_meta(t_pad, n_req, max_comp_rows)
-        logits = self.model.forward(meta, b.d_logit_rows[:ns])
+        logits = self.model.forward(meta, None if identity_rows else b.d_logit_rows[:ns])
         toks, _ = S.gumbel_argmax(logits, b.d_temp[:ns], b.d_seed[:ns], b.d_pos[:ns])
         return toks
 
@@ -387,11 +439,13 @@ class Engine:
         elif toks_dev is not None:
             if self.device.type == "cuda":
                 self.buf.h_out[:ns].copy_(toks_dev[:ns], non_blocking=True)
+                self._queue_status_read()
                 torch.cuda.current_stream().synchronize()
                 new_tokens = self.buf.h_out[:ns].tolist()
             else:
                 new_tokens = toks_dev[:ns].tolist()
-            self.d2h_bytes_last = ns * 8
+            self.d2h_bytes_last = ns * 8 + 8
+            self._check_device_status()
         k = 0
         now = time.time()
         for s in seqs:
@@ -511,11 +565,13 @@ class Engine:
             n_out = packed.numel()
             if self.device.type == "cuda":
                 self.buf.h_out[:n_out].copy_(packed, non_blocking=True)
+                self._queue_status_read()
                 torch.cuda.current_stream().synchronize()
                 res = self.buf.h_out[:n_out].tolist()
             else:
                 res = packed.tolist()
-            self.d2h_bytes_last = n_out * 8
+            self.d2h_bytes_last = n_out * 8 + 8
+            self._check_device_status()
             acc_h = res[:nb]
             ver_h = res[nb:nb + nb * (n_spec + 1)]
             dr_h = res[nb + nb * (n_spec + 1):]
@@ -604,14 +660,14 @@ class DecodeGraph:
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             for _ in range(2):
-                self.out = eng._run_model(bucket, bucket, bucket, rows_bucket)
+                self.out = eng._run_model(bucket, bucket, bucket, rows_bucket, identity_rows=True)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         from ..ops import _lib
         before = _lib.launch_count
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
-            self.out = eng._run_model(bucket, bucket, bucket, rows_bucket)
+            self.out = eng._run_model(bucket, bucket, bucket, rows_bucket, identity_rows=True)
         self.launches_per_replay = _lib.launch_count - before
 
     def replay(self) -> torch.Tensor:

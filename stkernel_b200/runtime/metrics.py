@@ -20,6 +20,7 @@ class Metrics:
     spec_num_accepted_tokens: int = 0
     spec_accepted_per_pos: List[int] = field(default_factory=list)
     prefix_cache_resets: int = 0
+    device_status_errors: int = 0
 
     def record_spec(self, n_draft: int, n_accepted: int) -> None:
         """One verified draft of n_draft tokens of which the first n_accepted were accepted."""
@@ -44,6 +45,7 @@ class Metrics:
             ("vllm:spec_decode_num_accepted_tokens_total", "counter", self.spec_num_accepted_tokens),
             ("stk:engine_steps_total", "counter", self.steps_total),
             ("stk:prefix_cache_resets_total", "counter", self.prefix_cache_resets),
+            ("stk:device_status_errors_total", "counter", self.device_status_errors),
         ]
         out = []
         for name, kind, val in rows:

@@ -5,10 +5,13 @@ after computing them: the compressed pages (ratio-4 latent + indexer-K), the sli
 last `window` tokens, and a copy of the compressors' ring rows (the raw rows a window that straddles the cut
 still needs).  A new request whose prompt starts with a cached chain adopts those pages (they are
 reference-counted, never copied) and starts its prefill at the cut.  `block` is 256 tokens, so that the cut
-falls on a page boundary of every group (64 sliding-window rows, 64 x 4 compressed rows); models with
-ratio-128 layers are not cached (their compressed rows share pages across cuts).
+falls on a page boundary of the sliding-window and ratio-4 groups (64 rows, 64 x 4 tokens) and on a window
+boundary of the ratio-128 compressor.  A ratio-128 page spans 8192 tokens, so a cut usually falls inside one:
+the full pages before it are shared like the others, and the rows of the partial page are copied into the entry
+and, on adoption, into a fresh page of the adopting request (at most 63 rows per ratio-128 layer).
 
-Entries are dropped least-recently-used when a pool runs low, and all at once by `reset()` — the
+Entries are dropped least-recently-used when a pool runs low, longest prefixes of a chain first (an entry is
+only reachable through its ancestors, so every touch of an entry also refreshes them), and all at once by `reset()` — the
 `/reset_prefix_cache` endpoint the reference's supervisor calls daily when idle
 (launchers/dsv4-tp4-supervisor.sh:117-132).  The reference relies on its engine's prefix cache for
 multi-turn chat; this is the equivalent for the hybrid cache layout (overlay/attention.py:743-759 lists the
@@ -38,6 +41,8 @@ class Entry:
     swa_pages: List[int]
     comp_state: Dict[int, torch.Tensor] = field(default_factory=dict)     # layer -> ring rows
     idx_state: Dict[int, torch.Tensor] = field(default_factory=dict)
+    c128_pages: List[int] = field(default_factory=list)                   # full ratio-128 pages (shared)
+    c128_tail: Dict[int, torch.Tensor] = field(default_factory=dict)      # layer -> bytes of the partial page
 
 
 def chain_hashes(tokens: Sequence[int], block: int = BLOCK, limit: Optional[int] = None) -> List[bytes]:
@@ -60,7 +65,8 @@ class PrefixCache:
         self.max_entries = max_entries
         self.entries: "OrderedDict[bytes, Entry]" = OrderedDict()
         cfg = kv.cfg
-        self.enabled = not any(cfg.layer_kind(l) == "c128a" for l in kv.layers) and block % (4 * PAGE) == 0
+        self.c128_layers = [l for l in kv.layers if cfg.layer_kind(l) == "c128a"]
+        self.enabled = block % (4 * PAGE) == 0 and block % 128 == 0
         self.window_pages = (cfg.sliding_window + PAGE - 1) // PAGE
         self.hits = 0
         self.hit_tokens = 0
@@ -73,13 +79,22 @@ class PrefixCache:
             return 0, None
         self.queries += 1
         best: Optional[Entry] = None
+        hit: List[bytes] = []
         for h in chain_hashes(prompt, self.block, limit=len(prompt) - 1):
             e = self.entries.get(h)
             if e is None:
                 break
             best = e
-            self.entries.move_to_end(h)
+            hit.append(h)
+        self._touch(hit)
         return (best.pos, best) if best is not None else (0, None)
+
+    def _touch(self, chain: Sequence[bytes]) -> None:
+        """Refresh a chain so that its longest prefix is the oldest of it and its root the newest: eviction then
+        takes leaves first and never strands an entry behind a missing ancestor."""
+        for h in reversed(chain):
+            if h in self.entries:
+                self.entries.move_to_end(h)
 
     def adopt(self, row: int, e: Entry) -> None:
         """Give request row `row` the cached state (pages shared, ring rows copied)."""
@@ -90,6 +105,15 @@ class PrefixCache:
             kv.comp_state[li][row].copy_(st)
         for li, st in e.idx_state.items():
             kv.idx_state[li][row].copy_(st)
+        if self.c128_layers:
+            if e.c128_pages:
+                kv.c128.adopt(row, 0, e.c128_pages)
+            if e.c128_tail:
+                lp = len(e.c128_pages)
+                kv.c128.ensure(row, lp, lp)                        # a page of its own for the rows past the shared ones
+                pg = int(kv.c128.table_np[row][lp])
+                for li, tail in e.c128_tail.items():
+                    kv.comp_cache[li].buf[pg].copy_(tail)
         self.hits += 1
         self.hit_tokens += e.pos
 
@@ -102,7 +126,7 @@ class PrefixCache:
         hashes = chain_hashes(prompt, self.block, limit=pos)
         key = hashes[-1]
         if key in self.entries:
-            self.entries.move_to_end(key)
+            self._touch(hashes)
             return False
         kv = self.kv
         n_c4_pages = (pos // 4) // PAGE
@@ -118,7 +142,19 @@ class PrefixCache:
             e.comp_state[li] = st[row].clone()
         for li, st in kv.idx_state.items():
             e.idx_state[li] = st[row].clone()
+        if self.c128_layers:
+            rows = pos // 128
+            full, part = rows // PAGE, rows % PAGE
+            if full > kv.c128.hi[row] or (part and full >= kv.c128.hi[row]):
+                self._drop(e)
+                return False
+            e.c128_pages = kv.c128.share(row, 0, full - 1) if full else []
+            if part:
+                pg = int(kv.c128.table_np[row][full])
+                for li in self.c128_layers:
+                    e.c128_tail[li] = kv.comp_cache[li].buf[pg].clone()
         self.entries[key] = e
+        self._touch(hashes)
         return True
 
     # ---- eviction ------------------------------------------------------------------------------
@@ -127,6 +163,8 @@ class PrefixCache:
             self.kv.c4.unref(pg)
         for pg in e.swa_pages:
             self.kv.swa.unref(pg)
+        for pg in e.c128_pages:
+            self.kv.c128.unref(pg)
 
     def evict_one(self) -> bool:
         if not self.entries:

@@ -99,3 +99,75 @@ def test_quantised_storage_matches_quant_aware_oracle():
     lg = eng.model.forward(eng._build_meta(t, n, 16))
     ref = oracle.logits(p)
     close(lg, ref, tol=1e-2)
+
+
+def test_padded_decode_bucket_ignores_stale_sample_rows():
+    """A decode bucket wider than the step (3 requests in a 4-row bucket) must not read the staged row list: the
+    entries past the uploaded ones still hold the row numbers of an earlier, larger step (here a 4-prompt prefill
+    whose last sampling row is far beyond the bucket)."""
+    torch.manual_seed(3)
+    cfg = tiny_config()
+    w = init_random_weights(cfg, seed=0)
+    eng = make_engine(cfg, w)
+    lens = (40, 33, 21, 50)
+    ids = [eng.add_request(torch.randint(0, cfg.vocab_size, (n,)).tolist(),
+                           SamplingParams(max_tokens=1 if i == 3 else 4)) for i, n in enumerate(lens)]
+    eng.step()                                    # one mixed step: all four prompts prefill and sample
+    assert eng.requests[ids[3]].finished
+    stale = eng.buf.d_logit_rows[:4].tolist()
+    assert max(stale) >= 4                        # what a 4-row decode graph would have indexed with
+    seqs = eng.sched.schedule()
+    assert len(seqs) == 3 and all(s.n == 1 for s in seqs)
+    t, n_req, ns = eng._stage(seqs)
+    eng._upload(t, n_req, ns)
+    eng.buf.d_qstart[n_req + 1:5].fill_(n_req)    # the padding rule of `_decode_graph`
+    ref = eng._run_model(t, n_req, ns, 16)
+    eng.buf.d_logit_rows.fill_(10 ** 6)           # poison: any read of it would raise on this path
+    got = eng._run_model(4, 4, 4, 16, identity_rows=True)
+    assert got[:3].tolist() == ref.tolist()
+
+
+def test_nonzero_device_status_fails_step_and_disables_symmetric_path():
+    """Host-side injection: the status word the engine reads after a step says a peer-flag wait ran out.  The step
+    must raise, be counted, and switch the symmetric collectives off so that later all-reduces take the library path."""
+    from stkernel_b200.runtime.engine import DeviceStatusError
+
+    class FakeSymm:
+        enabled = True
+        reason = None
+
+        def eligible(self, x):
+            return self.enabled
+
+        def all_reduce(self, x):
+            return x if self.enabled else None
+
+        def disable(self, reason):
+            self.enabled, self.reason = False, reason
+
+    class FakeComm:
+        def __init__(self):
+            self.symm, self.world_size, self.library_calls = FakeSymm(), 2, 0
+
+        def all_reduce(self, x):
+            if self.symm.eligible(x) and self.symm.all_reduce(x) is not None:
+                return x
+            self.library_calls += 1
+            return x
+
+    torch.manual_seed(4)
+    cfg = tiny_config()
+    eng = make_engine(cfg, init_random_weights(cfg, seed=0))
+    eng.model.comm = FakeComm()
+    eng.add_request(torch.randint(0, cfg.vocab_size, (12,)).tolist(), SamplingParams(max_tokens=4))
+    eng.step()
+    assert eng.metrics.device_status_errors == 0
+    eng._read_status = lambda: (2, 5)
+    with pytest.raises(DeviceStatusError) as ei:
+        eng.step()
+    assert ei.value.code == 2 and ei.value.detail == 5
+    assert eng.metrics.device_status_errors == 1
+    assert eng.model.comm.symm.enabled is False and "device status 2" in eng.model.comm.symm.reason
+    eng.model.comm.all_reduce(torch.zeros(4))
+    assert eng.model.comm.library_calls == 1
+    assert "stk:device_status_errors_total" in eng.metrics.render()

@@ -106,3 +106,59 @@ def test_http_reset_endpoint_drops_entries():
         assert eng.prefix_cache.hits == 1 and u["prompt_tokens"] == 300
         assert c.post("/reset_prefix_cache").json()["reset"] is True
         assert len(eng.prefix_cache.entries) == 0
+
+
+def test_eviction_takes_the_longest_prefix_first_and_strands_nothing():
+    """After any eviction every remaining entry must still be reachable through `match` (an entry is found only by
+    walking its chain from the root), whatever order chains were offered and matched in."""
+    cfg = tiny_config()
+    g = torch.Generator().manual_seed(2)
+    long_prompt = torch.randint(0, cfg.vocab_size, (4 * BLOCK + 3,), generator=g).tolist()
+    other = long_prompt[:BLOCK] + torch.randint(0, cfg.vocab_size, (2 * BLOCK + 3,), generator=g).tolist()
+    sp = SamplingParams(temperature=0.0, max_tokens=1)
+    eng2 = _engine(init_random_weights(cfg, seed=0), cfg, caching=True, chunk=256)
+    pc = eng2.prefix_cache
+    eng2.generate([long_prompt], sp)            # boundaries 256 .. 1024
+    eng2.generate([other], sp)                  # shares the first block, adds two entries of its own
+    assert len(pc.entries) == 6
+    pc.match(long_prompt)                       # a lookup must not make the root the oldest entry
+
+    def reachable():
+        seen = set()
+        for p in (long_prompt, other):
+            for h in chain_hashes(p, pc.block, limit=len(p) - 1):
+                if h not in pc.entries:
+                    break
+                seen.add(h)
+        return seen
+
+    while pc.entries:
+        assert reachable() == set(pc.entries.keys())
+        pc.evict_one()
+    assert eng2.kv.swa.pages_in_use == 0 and eng2.kv.c4.pages_in_use == 0
+
+
+def test_prefix_cache_with_ratio_128_layers_copies_the_partial_page():
+    """A model with a ratio-128 layer (the production layer mix): the cut at 256 tokens falls inside a ratio-128 page,
+    whose two rows travel with the entry; the adopting request produces the text of a cold engine."""
+    torch.manual_seed(0)
+    cfg = tiny_config(num_hidden_layers=3, compress_ratios=(4, 128, 0))
+    w = init_random_weights(cfg, seed=0)
+    g = torch.Generator().manual_seed(11)
+    common = torch.randint(0, cfg.vocab_size, (BLOCK + 150,), generator=g).tolist()
+    p1 = common + torch.randint(0, cfg.vocab_size, (20,), generator=g).tolist()
+    p2 = common + torch.randint(0, cfg.vocab_size, (140,), generator=g).tolist()     # crosses the next ratio-128 window
+    sp = SamplingParams(temperature=0.7, seed=5, max_tokens=8)
+    cold = _engine(w, cfg, caching=False)
+    ref = [cold.generate([p], sp)[0] for p in (p1, p2)]
+    warm = _engine(w, cfg, caching=True)
+    assert warm.prefix_cache is not None and warm.prefix_cache.c128_layers == [1]
+    out1 = warm.generate([p1], sp)[0]
+    e = next(iter(warm.prefix_cache.entries.values()))
+    assert e.pos == BLOCK and e.c128_pages == [] and list(e.c128_tail) == [1]
+    before = warm.metrics.prompt_tokens_total
+    out2 = warm.generate([p2], sp)[0]
+    assert warm.prefix_cache.hits == 1 and warm.metrics.prompt_tokens_total - before == len(p2) - BLOCK
+    assert [out1, out2] == ref
+    warm.reset_prefix_cache()
+    assert warm.kv.c128.pages_in_use == 0 and all(r == 0 for r in warm.kv.c128.ref)
