@@ -82,6 +82,14 @@ def main() -> None:
     ap.add_argument("--pdl", type=int, default=0,
                     help="keep programmatic dependent launch on: a kernel's recorded time then includes its wait for "
                          "the previous kernel, so per-kernel figures overlap (off by default for the table)")
+    ap.add_argument("--time-steps", type=int, default=0,
+                    help="first time this many steps by CUDA events without the profiler and print us/step")
+    ap.add_argument("--timeline", default="", help="also write the last step's launches in start order "
+                                                   "(start offset, duration, gap to the previous end, stream, name) to this file")
+    ap.add_argument("--shard-of", type=int, default=1,
+                    help="single process only: build rank 0's weight shard of a tensor/expert-parallel group of this "
+                         "size and run it alone, without collectives (the sums are incomplete, so the values mean "
+                         "nothing; the kernels, their shapes and their times are those of one rank of that group)")
     a = ap.parse_args()
     from ..config import EngineConfig, ParallelConfig, SchedulerConfig, flash_config
     from ..models.dsv4 import RandomSource, build_model_weights
@@ -106,11 +114,15 @@ def main() -> None:
                       sched=SchedulerConfig(max_model_len=a.ctx + 8192, max_num_seqs=max(a.conc, 2),
                                                        max_num_batched_tokens=a.chunk,
                                                        graph_cap=64 if a.graphs else 0)).validate()
-    eng = Engine(ec, build_model_weights(cfg, RandomSource(0), dev, rank, world, head_fp8=True), dev, comm, rank,
+    shard = a.shard_of if world == 1 else 1
+    if shard > 1:
+        ec = EngineConfig(model=cfg, parallel=ParallelConfig(tp_size=shard, ep_size=shard, fused_collectives=True),
+                          sched=ec.sched).validate()
+    eng = Engine(ec, build_model_weights(cfg, RandomSource(0), dev, rank, max(world, shard), head_fp8=True), dev, comm, rank,
                  max_context=a.ctx + 8192)
     fill_caches_synthetic(eng)
     if a.mode == "decode":
-        add_synthetic_requests(eng, a.conc, a.ctx, a.steps + 8, cfg.vocab_size, 3)
+        add_synthetic_requests(eng, a.conc, a.ctx, a.steps + 3 * a.time_steps + 8, cfg.vocab_size, 3)
     else:
         g = torch.Generator().manual_seed(0)
         eng.add_request(torch.randint(0, cfg.vocab_size, (a.chunk * (a.steps + 2),), generator=g).tolist(),
@@ -118,6 +130,19 @@ def main() -> None:
     for _ in range(2):
         eng.step()
     torch.cuda.synchronize()
+    timed_us = None
+    if a.time_steps > 0:
+        # the same steps without the profiler, by CUDA events (tokens forced, so no host read-back between steps)
+        g2 = torch.Generator().manual_seed(5)
+        forced = [torch.randint(0, cfg.vocab_size, (max(a.conc, 1),), generator=g2).tolist() for _ in range(a.time_steps)]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for rep in range(2):
+            e0.record()
+            for i in range(a.time_steps):
+                eng.step(forced[i] if a.mode == "decode" else None)
+            e1.record()
+            torch.cuda.synchronize()
+            timed_us = e0.elapsed_time(e1) * 1e3 / a.time_steps
     with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CUDA]) as prof:
         for _ in range(a.steps):
             eng.step()
@@ -125,7 +150,9 @@ def main() -> None:
     path = os.path.join(tempfile.gettempdir(), f"stk_trace_{rank}.json")
     prof.export_chrome_trace(path)
     s = summarise_trace(path, a.steps)
-    lines = [f"mode={a.mode} conc={a.conc} ctx={a.ctx} layers={a.layers} graphs={a.graphs} steps={a.steps} gpus={world}",
+    lines = [f"mode={a.mode} conc={a.conc} ctx={a.ctx} layers={a.layers} graphs={a.graphs} steps={a.steps} gpus={world}"
+             + (f" shard-of={shard}" if shard > 1 else "")
+             + (f"  [{timed_us:.1f} us/step by CUDA events over {a.time_steps} steps, no profiler, pdl={a.pdl}]" if timed_us else ""),
              f"busy {s['busy_us'] / a.steps:.1f} us/step, span {s['span_us'] / a.steps:.1f} us/step, "
              f"idle {100 * (1 - s['busy_us'] / max(s['span_us'], 1e-9)):.1f} %"]
     for b, v in sorted(s["buckets"].items(), key=lambda x: -x[1]):
@@ -134,6 +161,17 @@ def main() -> None:
     for n, d in rows:
         lines.append(f"  {sum(d) / a.steps:9.1f} us/step {len(d) // a.steps:4d}x/step avg {sum(d) / len(d):7.1f} us  {n[:70]}")
     text = "\n".join(lines)
+    if a.timeline and rank == 0:
+        ev = [e for e in json.load(open(path))["traceEvents"]
+              if e.get("cat") in ("kernel", "gpu_memcpy", "gpu_memset") and "dur" in e]
+        ev.sort(key=lambda e: e["ts"])
+        per_step = len(ev) // a.steps
+        last = ev[len(ev) - per_step:]
+        t0, prev_end, tl = last[0]["ts"], last[0]["ts"], []
+        for e in last:
+            tl.append(f"{e['ts'] - t0:9.1f} {e['dur']:7.1f} {e['ts'] - prev_end:7.1f}  s{e.get('args', {}).get('stream', '?')}  {e['name'][:90]}")
+            prev_end = max(prev_end, e["ts"] + e["dur"])
+        open(a.timeline, "w").write("# start_us dur_us gap_us stream name\n" + "\n".join(tl) + "\n")
     if rank == 0:
         print(text, flush=True)
         if a.out:

@@ -7,7 +7,10 @@
 #include <stdlib.h>
 
 #define STK_PDL_CLASS 1      // bit of this file's kernels in the PDL mask (STK_PDL, stk_set_pdl_mask)
+#include <string.h>
+
 #include "common.cuh"
+#include "symm.cuh"
 
 namespace stk {
 
@@ -185,13 +188,20 @@ __global__ void swiglu_clamp_kernel(const __nv_bfloat16* __restrict__ gu, long l
 }
 
 // out[t, :] = sum_j w[t, j] * y[pair(t, j), :] (+ shared[t, :]); fixed j order => deterministic.
+// use_ll: this rank's sum is a partial over the expert-parallel ranks; instead of `out` it goes into every rank's
+// all-reduce slot (symm.cuh, LLAr) and the consumer kernel adds the ranks.
 __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ w,
                                    const int* __restrict__ pair_row, const __nv_bfloat16* __restrict__ shared,
-                                   __nv_bfloat16* __restrict__ out, int H, int topk) {
+                                   __nv_bfloat16* __restrict__ out, int H, int topk, int use_ll, const LLAr ll) {
   pdl_wait();
   pdl_trigger();
   const int t = blockIdx.x;
   const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 2;
+  uint32_t epoch = 0;
+  if (use_ll) {
+    epoch = ll_push_epoch(ll);
+    if (threadIdx.x == 0) ll_push_done(ll, epoch);      // counters[1] is read by the next kernel only
+  }
   if (i >= H) return;
   constexpr int kMaxK = 16;
   int rows[kMaxK];
@@ -221,6 +231,12 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const fl
     const __nv_bfloat162 s = *reinterpret_cast<const __nv_bfloat162*>(shared + static_cast<long long>(t) * H + i);
     a0 += __low2float(s);
     a1 += __high2float(s);
+  }
+  if (use_ll) {
+    const uint32_t d = pack_bf16x2(a0, a1);
+    const long long word = (static_cast<long long>(t) * H + i) >> 1;
+    for (int p = 0; p < ll.world; ++p) ll_store(ll, epoch, (ll.rank + p) % ll.world, word, d);
+    return;
   }
   *reinterpret_cast<__nv_bfloat162*>(out + static_cast<long long>(t) * H + i) = __floats2bfloat162_rn(a0, a1);
 }
@@ -336,11 +352,18 @@ STK_API int stk_swiglu_clamp(const void* gu, long long ldg, void* act, long long
 }
 
 STK_API int stk_moe_combine(const void* y, const float* w, const int* pair_row, const void* shared, void* out, int T,
-                            int H, int topk, void* stream) {
+                            int H, int topk, const void* ll_ctx, void* stream) {
   if (T <= 0) return 0;
   if (H % 2 || topk > 16) return -1;
+  LLAr ll;
+  memset(&ll, 0, sizeof(ll));
+  if (ll_ctx != nullptr) {
+    memcpy(&ll, ll_ctx, sizeof(ll));
+    if (static_cast<long long>(T) * H / 2 > ll.words) return -2;
+  }
   dim3 grid(T, (H / 2 + 127) / 128);
   launch_pdl(moe_combine_kernel, dim3(grid), dim3(128), 0, (cudaStream_t)stream, (const __nv_bfloat16*)y, w, pair_row,
-                                                          (const __nv_bfloat16*)shared, (__nv_bfloat16*)out, H, topk);
+                                                          (const __nv_bfloat16*)shared, (__nv_bfloat16*)out, H, topk,
+                                                          ll_ctx != nullptr ? 1 : 0, ll);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }

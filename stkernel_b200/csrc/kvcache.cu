@@ -106,12 +106,15 @@ __device__ __forceinline__ void write_latent_row(const CacheGeom& c, long long s
     *reinterpret_cast<__nv_bfloat162*>(rdst + i) = __floats2bfloat162_rn(vals[nope + i], vals[nope + i + 1]);
 }
 
-// kv [T, D] bf16 (already normed).  One warp per token; slot -1 = padding (skipped).
+// kv [T, D] bf16.  One warp per token; slot -1 = padding (skipped).  With norm_w the row is RMS-normalised here
+// (weight norm_w, rounded to bf16 as a separate norm kernel would store it) instead of arriving normalised.
 __device__ __forceinline__ void kv_rope_quant_insert_body(int block, float* sm, const __nv_bfloat16* __restrict__ kv,
                                                           long long ldk, const int64_t* __restrict__ positions,
                                                           const int64_t* __restrict__ slots,
                                                           const float* __restrict__ inv_freq, const CacheGeom& cache,
-                                                          int T, int D, int R, long long num_slots, int* status) {
+                                                          int T, int D, int R, long long num_slots, int* status,
+                                                          const __nv_bfloat16* __restrict__ norm_w = nullptr,
+                                                          float norm_eps = 0.f) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = block * (blockDim.x >> 5) + warp;
   if (t >= T) return;
@@ -124,9 +127,23 @@ __device__ __forceinline__ void kv_rope_quant_insert_body(int block, float* sm, 
   float* vals = sm + warp * D;
   const float pos = static_cast<float>(positions[t]);
   const int nope = D - R;
+  float nr = 1.f;
+  if (norm_w != nullptr) {
+    float ss = 0.f;
+    for (int i = lane * 2; i < D; i += 64) {
+      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(kv + t * ldk + i);
+      ss = fmaf(__low2float(v), __low2float(v), fmaf(__high2float(v), __high2float(v), ss));
+    }
+    nr = rsqrtf(warp_sum(ss) / D + norm_eps);
+  }
   for (int i = lane * 2; i < D; i += 64) {
     const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(kv + t * ldk + i);
     float a = __low2float(v), b = __high2float(v);
+    if (norm_w != nullptr) {
+      const __nv_bfloat162 w = *reinterpret_cast<const __nv_bfloat162*>(norm_w + i);
+      a = bf16_to_f(__float2bfloat16(a * nr * __low2float(w)));
+      b = bf16_to_f(__float2bfloat16(b * nr * __high2float(w)));
+    }
     if (i >= nope) {
       rope_pair(a, b, pos, inv_freq[(i - nope) >> 1], false);
       a = bf16_to_f(__float2bfloat16(a));
@@ -156,7 +173,7 @@ __global__ void __launch_bounds__(256)
 q_rope_kv_insert_kernel(__nv_bfloat16* __restrict__ q, long long ldt, int nh, float eps, int q_blocks,
                         const __nv_bfloat16* __restrict__ kv, long long ldk, const int64_t* __restrict__ positions,
                         const int64_t* __restrict__ slots, const float* __restrict__ inv_freq, CacheGeom cache, int T,
-                        int D, int R, long long num_slots, int* status) {
+                        int D, int R, long long num_slots, int* status, const __nv_bfloat16* __restrict__ kv_norm_w) {
   pdl_wait();
   pdl_trigger();
   extern __shared__ float sm[];
@@ -164,7 +181,7 @@ q_rope_kv_insert_kernel(__nv_bfloat16* __restrict__ q, long long ldt, int nh, fl
     q_norm_rope_body(blockIdx.x, q, ldt, positions, inv_freq, T, nh, D, R, eps, 1, 0);
   } else {
     kv_rope_quant_insert_body(blockIdx.x - q_blocks, sm, kv, ldk, positions, slots, inv_freq, cache, T, D, R, num_slots,
-                              status);
+                              status, kv_norm_w, eps);
   }
 }
 
@@ -411,15 +428,18 @@ STK_API int stk_kv_rope_quant_insert(const void* kv, long long ldk, const int64_
 STK_API int stk_q_rope_kv_insert(void* q, long long ldt, int nh, float eps, const void* kv, long long ldk,
                                  const int64_t* positions, const int64_t* slots, const float* inv_freq, void* cache,
                                  long long page_stride, int data_bytes, int fp8, long long num_slots, int T, int D, int R,
-                                 int* status, void* stream) {
+                                 const void* kv_norm_w, int* status, void* stream) {
+  // kv_norm_w != nullptr: kv arrives un-normalised and is RMS-normalised (same eps) inside the insert.
+  // q == nullptr (nh = 0): only the latent rows are written (the attention kernel norms and rotates q itself).
   if (T <= 0) return 0;
   if (D % 2 || R % 2 || (fp8 && ((D - R) % 64 || (D - R) / 64 > 8))) return -1;
   CacheGeom g{(uint8_t*)cache, page_stride, data_bytes, fp8};
+  if (q == nullptr) nh = 0;
   const int q_blocks = static_cast<int>((static_cast<long long>(T) * nh + 7) / 8);
   const int kv_blocks = (T + 7) / 8;
   launch_pdl(q_rope_kv_insert_kernel, dim3(q_blocks + kv_blocks), dim3(256), 8 * D * sizeof(float), (cudaStream_t)stream, 
       (__nv_bfloat16*)q, ldt, nh, eps, q_blocks, (const __nv_bfloat16*)kv, ldk, positions, slots, inv_freq, g, T, D, R,
-      num_slots, status);
+      num_slots, status, (const __nv_bfloat16*)kv_norm_w);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

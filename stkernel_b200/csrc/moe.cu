@@ -17,11 +17,12 @@
 
 #define STK_PDL_CLASS 1024      // bit of this file's kernels in the PDL mask (STK_PDL, stk_set_pdl_mask)
 #include "common.cuh"
+#include "router.cuh"
 
 namespace stk {
 
 // ---- router ------------------------------------------------------------------------
-// One warp per token, E <= 512.
+// One warp per token, E <= 512 (the selection itself lives in router.cuh, shared with the gate projection's epilogue).
 __global__ void router_kernel(const float* __restrict__ logits, long long ldl, const float* __restrict__ bias,
                               const int* __restrict__ tid2eid, const int64_t* __restrict__ token_ids, int vocab,
                               int* __restrict__ ids, float* __restrict__ weights, int T, int E, int topk, int scoring,
@@ -29,77 +30,9 @@ __global__ void router_kernel(const float* __restrict__ logits, long long ldl, c
   pdl_wait();
   pdl_trigger();
   const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
   if (t >= T) return;
-  constexpr int kPer = 16;
-  float sc[kPer], sel[kPer];
-#pragma unroll
-  for (int i = 0; i < kPer; ++i) {
-    const int e = i * 32 + lane;
-    if (e < E) {
-      const float x = logits[t * ldl + e];
-      float s;
-      if (scoring == 0) s = 1.f / (1.f + __expf(-x));
-      else s = sqrtf(x > 20.f ? x : log1pf(__expf(x)));
-      sc[i] = s;
-      sel[i] = s + (bias ? bias[e] : 0.f);
-    } else {
-      sc[i] = 0.f;
-      sel[i] = -INFINITY;
-    }
-  }
-  float wsum = 0.f;
-  float my_w = 0.f;      // lane j keeps the j-th selected weight
-  int my_id = -1;
-  if (tid2eid != nullptr) {
-    const long long tok = token_ids[t];
-    const bool ok = tok >= 0 && tok < vocab;
-    if (!ok && lane == 0) set_status(status, kBadIndex, t);
-    for (int j = 0; j < topk; ++j) {
-      int e = ok ? tid2eid[tok * topk + j] : 0;
-      if (e < 0 || e >= E) {
-        if (lane == 0) set_status(status, kBadIndex, t);
-        e = 0;
-      }
-      // static indexing only (a dynamic index would push sc[] and sel[] to local memory for the whole kernel)
-      float pick = 0.f;
-#pragma unroll
-      for (int i = 0; i < kPer; ++i) pick = (i == (e >> 5)) ? sc[i] : pick;
-      const float s = __shfl_sync(0xffffffffu, pick, e & 31);
-      wsum += s;
-      if (lane == j) { my_w = s; my_id = e; }
-    }
-  } else {
-    for (int j = 0; j < topk; ++j) {
-      float best = -INFINITY;
-      int best_e = 0x7fffffff;
-#pragma unroll
-      for (int i = 0; i < kPer; ++i) {
-        const int e = i * 32 + lane;
-        if (sel[i] > best) { best = sel[i]; best_e = e; }
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-        if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
-      }
-      float s = 0.f;
-#pragma unroll
-      for (int i = 0; i < kPer; ++i) {
-        if (i * 32 + lane == best_e) { s = sc[i]; sel[i] = -INFINITY; }
-      }
-      s = __shfl_sync(0xffffffffu, s, best_e & 31);
-      wsum += s;
-      if (lane == j) { my_w = s; my_id = best_e; }
-    }
-  }
-  if (lane < topk) {
-    float w = my_w;
-    if (renorm) w = w / fmaxf(wsum, 1e-20f);
-    ids[t * topk + lane] = my_id;
-    weights[t * topk + lane] = w * scaling;
-  }
+  RouterArgs r{bias, tid2eid, token_ids, vocab, ids, weights, E, topk, scoring, renorm, scaling, status};
+  route_token(r, logits + t * ldl, t, threadIdx.x & 31);
 }
 
 // ---- pair sort by expert ------------------------------------------------------------
@@ -340,25 +273,27 @@ expert_fc1_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, ExpertW w1
   const int row = blockIdx.y;
   int pair, e;
   if (direct_ids != nullptr) {
-    // direct mode (a handful of pairs): row = pair index, no sort; non-local experts are skipped
+    // direct mode (a handful of pairs): row = pair index, no sort; non-local experts are skipped.  The token of a pair
+    // does not depend on the routing, so the activation row is staged while the expert id is still on its way.
     pair = row;
-    e = direct_ids[row] - e_start;
+    const int e_raw = __ldg(direct_ids + row);
+    fill_xs(reinterpret_cast<__half*>(xs), x + (pair / topk) * ldx, H);
+    e = e_raw - e_start;
     if (e < 0 || e >= e_local) return;
   } else {
     if (row >= offsets[e_local]) return;
     pair = sorted[row];
     e = sorted_expert[row];
+    fill_xs(reinterpret_cast<__half*>(xs), x + (pair / topk) * ldx, H);
   }
-  const int t = pair / topk;
-  fill_xs(reinterpret_cast<__half*>(xs), x + t * ldx, H);
-  __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_chunks = H / 32;
   const float gs = w13.gscale[e];
   const long long wstride = static_cast<long long>(H) / 2, sstride = static_cast<long long>(H) / 16;
   const uint8_t* wbase = w13.w + static_cast<long long>(e) * 2 * I * wstride;
   const uint8_t* sbase = w13.s + static_cast<long long>(e) * 2 * I * sstride;
-  // the four weight rows of this warp (gate and up of two outputs) are all loaded before any arithmetic
+  // the four weight rows of this warp (gate and up of two outputs) are all requested before the barrier that
+  // publishes the staged activations, and before any arithmetic
   Fp4Row<ITERS> rg[2], ru[2];
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
@@ -366,6 +301,7 @@ expert_fc1_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, ExpertW w1
     fp4_row_load<ITERS>(rg[j], wbase + i * wstride, sbase + i * sstride, n_chunks, lane);
     fp4_row_load<ITERS>(ru[j], wbase + (I + i) * wstride, sbase + (I + i) * sstride, n_chunks, lane);
   }
+  __syncthreads();
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
     const int i = blockIdx.x * 16 + warp * 2 + j;
@@ -393,7 +329,9 @@ expert_fc2_kernel(const __half* __restrict__ act, ExpertW w2, const int* __restr
   const int row = blockIdx.y;
   int e;
   if (direct_ids != nullptr) {
-    e = direct_ids[row] - e_start;
+    const int e_raw = __ldg(direct_ids + row);
+    fill_xs(reinterpret_cast<__half*>(xs), act + static_cast<long long>(row) * I, I);   // staged while the id is in flight
+    e = e_raw - e_start;
     if (e < 0 || e >= e_local) {
       // not a local expert: this pair contributes nothing on this rank
       for (int n = blockIdx.x * 32 + threadIdx.x; n < min(H, blockIdx.x * 32 + 32); n += blockDim.x)
@@ -403,9 +341,8 @@ expert_fc2_kernel(const __half* __restrict__ act, ExpertW w2, const int* __restr
   } else {
     if (row >= offsets[e_local]) return;
     e = sorted_expert[row];
+    fill_xs(reinterpret_cast<__half*>(xs), act + static_cast<long long>(row) * I, I);
   }
-  fill_xs(reinterpret_cast<__half*>(xs), act + static_cast<long long>(row) * I, I);
-  __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_chunks = I / 32;
   const float gs = w2.gscale[e];
@@ -418,6 +355,7 @@ expert_fc2_kernel(const __half* __restrict__ act, ExpertW w2, const int* __restr
     const int n = min(blockIdx.x * 32 + warp * 4 + j, H - 1);
     fp4_row_load<ITERS>(rw[j], wbase + n * wstride, sbase + n * sstride, n_chunks, lane);
   }
+  __syncthreads();
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int n = blockIdx.x * 32 + warp * 4 + j;

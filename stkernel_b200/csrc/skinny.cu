@@ -8,12 +8,33 @@
 //
 // FP8 weights carry 128x128 block scales (applied per 16-value chunk); activations are used
 // unquantised, which is at least as accurate as the quantised tensor-core path.
+//
+// Three optional fusions take neighbouring launches of the decode chain into this kernel:
+//   * prologue RMSNorm: the activation row is normalised (weight, eps; rounded to bf16 like a separate norm kernel's
+//     output) while it is staged into shared memory -- every CTA redoes the few-KB reduction, no CTA waits for another;
+//   * folded all-reduce (row-parallel layers): the output words go straight into every rank's receive slot
+//     (symm.cuh, LLAr) instead of to `out`; the consumer kernel adds the ranks;
+//   * router epilogue (gate projection): the CTA that finishes last selects the experts of every token.
 #define STK_PDL_CLASS 2      // bit of this file's kernels in the PDL mask (STK_PDL, stk_set_pdl_mask)
+#include <string.h>
+
 #include "common.cuh"
+#include "router.cuh"
+#include "symm.cuh"
 
 namespace stk {
 
 constexpr int kSkinnyMaxT = 8;
+
+struct SkinnyExtra {
+  const __nv_bfloat16* norm_w;   // prologue RMSNorm weight [K] (nullptr: off)
+  float norm_eps;
+  int use_ll;                    // push the result into the slots of `ll` instead of writing `out`
+  LLAr ll;
+  int route;                     // run the router over `out` (fp32 logits [T, N]) in the last CTA
+  int* route_counter;            // zero on entry, zero again on exit
+  RouterArgs router;
+};
 
 // x: [T, K] bf16 -> xs: half, permuted: chunk c = lane + 32*k holds values [16c, 16c+16) as two uint4
 // at index ((t * kIters + k) * 2 + i) * 32 + lane.
@@ -22,15 +43,46 @@ constexpr int kSkinnyMaxT = 8;
 // 28672: the packed fp16 partial sums of the fp8 path cannot overflow.
 template <int T, bool kPrescale>
 __device__ __forceinline__ void skinny_fill_x(__half* xs, const __nv_bfloat16* x, long long ldx, int K, int iters,
-                                              float* xscale, float* red, int t_valid) {
+                                              float* xscale, float* red, int t_valid,
+                                              const __nv_bfloat16* norm_w = nullptr, float norm_eps = 0.f) {
   // eight consecutive values = one 16-byte load, one conversion, one 16-byte store
   uint4* xs4 = reinterpret_cast<uint4*>(xs);
   const int k8n = K >> 3;
   const bool aligned = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((ldx & 7) == 0);
   float mul[T];
+  float nr[T];             // prologue RMSNorm: 1/rms of each row
 #pragma unroll
-  for (int t = 0; t < T; ++t) mul[t] = 1.f;
-  if constexpr (kPrescale) {
+  for (int t = 0; t < T; ++t) { mul[t] = 1.f; nr[t] = 1.f; }
+  if (norm_w != nullptr) {
+    // one pass over the row for both reductions: sum x^2 (the norm) and max |x * w| (the fp8 pre-scale bound: the
+    // normalised row is x * w times one scalar)
+#pragma unroll
+    for (int t = 0; t < T; ++t) {
+      float ss = 0.f, am = 0.f;
+      if (t < t_valid)
+        for (int k = threadIdx.x; k < K; k += blockDim.x) {
+          const float v = bf16_to_f(x[t * ldx + k]);
+          ss = fmaf(v, v, ss);
+          if constexpr (kPrescale) am = fmaxf(am, fabsf(v * bf16_to_f(norm_w[k])));
+        }
+      ss = warp_sum(ss);
+      am = warp_max(am);
+      __syncthreads();
+      if ((threadIdx.x & 31) == 0) { red[threadIdx.x >> 5] = ss; red[16 + (threadIdx.x >> 5)] = am; }
+      __syncthreads();
+      float s2 = 0.f, a2 = 0.f;
+      for (int w = 0; w < static_cast<int>(blockDim.x >> 5); ++w) { s2 += red[w]; a2 = fmaxf(a2, red[16 + w]); }
+      nr[t] = rsqrtf(s2 / static_cast<float>(K) + norm_eps);
+      if constexpr (kPrescale) {
+        const float amax = a2 * nr[t] * 1.01f;          // the rounding of each normalised value to bf16 stays inside
+        int e = 0;
+        if (amax > 8.f) e = static_cast<int>(ceilf(log2f(amax * 0.125f)));
+        if (threadIdx.x == 0) xscale[t] = exp2f(static_cast<float>(e));
+        mul[t] = exp2f(static_cast<float>(-e));
+      }
+    }
+    __syncthreads();
+  } else if constexpr (kPrescale) {
 #pragma unroll
     for (int t = 0; t < T; ++t) {
       float amax = 0.f;
@@ -75,6 +127,10 @@ __device__ __forceinline__ void skinny_fill_x(__half* xs, const __nv_bfloat16* x
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         float2 f = __bfloat1622float2(b[j]);
+        if (norm_w != nullptr) {
+          const float2 w = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(norm_w + k8 * 8 + 2 * j));
+          f = __bfloat1622float2(__floats2bfloat162_rn(f.x * nr[t] * w.x, f.y * nr[t] * w.y));
+        }
         if constexpr (kPrescale) { f.x *= mul[t]; f.y *= mul[t]; }
         oh[j] = __float22half2_rn(f);
       }
@@ -92,7 +148,8 @@ template <int T, bool kFp8, int ITERS, bool kSwiglu>
 __global__ void __launch_bounds__(256)
 skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const float* __restrict__ w_scale,
                      int w_scale_ld, const __nv_bfloat16* __restrict__ x, long long ldx, void* __restrict__ out,
-                     long long ldo, int N, int K, int out_fp32, int rows_per_warp, int group_rows, float limit, int t_valid) {
+                     long long ldo, int N, int K, int out_fp32, int rows_per_warp, int group_rows, float limit, int t_valid,
+                     const SkinnyExtra ex) {
   extern __shared__ uint4 xs4[];
   constexpr int kVals = kFp8 ? 16 : 8;                  // values per 16-byte weight chunk
   const int n_chunks = K / kVals;
@@ -115,15 +172,40 @@ skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const f
         for (int b = pl * 128; b < row_bytes; b += 32 * 128) prefetch_l2(wrow + b);
       }
   }
+  // ... and this warp's first row goes all the way into registers: weights are immutable, so the loads may be in
+  // flight while the previous kernel finishes; the row loop then starts without a memory round trip.
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = (blockIdx.x * 8 + warp) * rows_per_warp;
+  uint4 wv[ITERS];
+  float sc[ITERS];
+  auto load_row = [&](int wn) {
+    const uint4* wrow = reinterpret_cast<const uint4*>(W + wn * ldw_bytes);
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int c = it * 32 + lane;
+      wv[it] = make_uint4(0, 0, 0, 0);
+      sc[it] = 0.f;
+      if (c < n_chunks) {
+        wv[it] = __ldg(wrow + c);
+        if constexpr (kFp8) sc[it] = __ldg(w_scale + (wn >> 7) * w_scale_ld + (c >> 3));
+      }
+    }
+  };
+  constexpr bool kPreload = ITERS <= 8;
+  if (kPreload && n0 < N) load_row(n0);
   pdl_wait();
   pdl_trigger();
-  skinny_fill_x<T, kFp8>(reinterpret_cast<__half*>(xs4), x + static_cast<long long>(grp) * K, ldx, K, iters16, s_xscale, s_red, t_valid);
+  uint32_t ll_epoch = 0;
+  if (ex.use_ll) ll_epoch = ll_push_epoch(ex.ll);
+  skinny_fill_x<T, kFp8>(reinterpret_cast<__half*>(xs4), x + static_cast<long long>(grp) * K, ldx, K, iters16, s_xscale, s_red,
+                         t_valid, ex.norm_w, ex.norm_eps);
   __syncthreads();
   float xsc[T];
 #pragma unroll
   for (int t = 0; t < T; ++t) xsc[t] = kFp8 ? s_xscale[t] : 1.f;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = (blockIdx.x * 8 + warp) * rows_per_warp;
+  float prev[T];           // folded all-reduce: the even row's results wait for the odd row to share a word
+#pragma unroll
+  for (int t = 0; t < T; ++t) prev[t] = 0.f;
   for (int r = 0; r < rows_per_warp; ++r) {
     const int n = n0 + r;
     if (n >= N) break;
@@ -131,19 +213,7 @@ skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const f
 #pragma unroll
     for (int pass = 0; pass < (kSwiglu ? 2 : 1); ++pass) {
       const int wn = n + pass * N;                       // weight row (and scale row) of this pass
-      const uint4* wrow = reinterpret_cast<const uint4*>(W + wn * ldw_bytes);
-      uint4 wv[ITERS];
-      float sc[ITERS];
-#pragma unroll
-      for (int it = 0; it < ITERS; ++it) {
-        const int c = it * 32 + lane;
-        wv[it] = make_uint4(0, 0, 0, 0);
-        sc[it] = 0.f;
-        if (c < n_chunks) {
-          wv[it] = __ldg(wrow + c);
-          if constexpr (kFp8) sc[it] = __ldg(w_scale + (wn >> 7) * w_scale_ld + (c >> 3));
-        }
-      }
+      if (!(kPreload && r == 0 && pass == 0)) load_row(wn);
       float acc[T];
 #pragma unroll
       for (int t = 0; t < T; ++t) acc[t] = 0.f;
@@ -217,10 +287,35 @@ skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const f
         }
         v = g / (1.f + __expf(-g)) * u;
       }
-      if (lane == 0 && t < t_valid) {
+      if (ex.use_ll) {
+        // every lane holds the sums; rows n-1 and n share a word, lane p stores it to rank (rank + p) % world
+        if ((n & 1) == 0 && n + 1 < N) {
+          prev[t] = v;
+        } else if (t < t_valid && lane < ex.ll.world) {
+          const uint32_t d = (n & 1) ? pack_bf16x2(prev[t], v) : pack_bf16x2(v, 0.f);
+          ll_store(ex.ll, ll_epoch, (ex.ll.rank + lane) % ex.ll.world, (static_cast<long long>(t) * N + (n & ~1)) >> 1, d);
+        }
+      } else if (lane == 0 && t < t_valid) {
         if (out_fp32) reinterpret_cast<float*>(out)[t * ldo + n] = v;
         else reinterpret_cast<__nv_bfloat16*>(out)[t * ldo + n] = __float2bfloat16(v);
       }
+    }
+  }
+  if (ex.use_ll && threadIdx.x == 0) ll_push_done(ex.ll, ll_epoch);
+  if (ex.route) {
+    // the CTA that finishes last has every logit in reach: it routes the tokens, one warp each
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int done = atomicAdd(ex.route_counter, 1);
+      s_last = done == static_cast<int>(gridDim.x) - 1;
+      if (s_last) *ex.route_counter = 0;
+    }
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      for (int t = warp; t < t_valid; t += 8) route_token<true>(ex.router, reinterpret_cast<const float*>(out) + t * ldo, t, lane);
     }
   }
 }
@@ -229,10 +324,11 @@ skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const f
 
 using namespace stk;
 
-// T <= 4.  K must be a multiple of 16 (fp8) / 8 (bf16); rows 16-byte aligned.
-STK_API int stk_skinny_linear(const void* W, long long ldw, int is_fp8, const float* w_scale, int w_scale_ld,
-                              const void* x, long long ldx, void* out, long long ldo, int T, int N, int K,
-                              int out_fp32, int sm_count, int groups, int swiglu, float limit, void* stream) {
+// T <= 8.  K must be a multiple of 16 (fp8) / 8 (bf16); rows 16-byte aligned.
+static int skinny_launch(const void* W, long long ldw, int is_fp8, const float* w_scale, int w_scale_ld,
+                         const void* x, long long ldx, void* out, long long ldo, int T, int N, int K,
+                         int out_fp32, int sm_count, int groups, int swiglu, float limit, const SkinnyExtra& ex,
+                         void* stream) {
   if (T <= 0 || N <= 0) return 0;
   if (T > kSkinnyMaxT || K % 16 || K > 16384) return -1;
   const long long ldw_bytes = ldw * (is_fp8 ? 1 : 2);
@@ -242,8 +338,11 @@ STK_API int stk_skinny_linear(const void* W, long long ldw, int is_fp8, const fl
   const size_t smem = static_cast<size_t>(t_inst) * iters16 * 2 * 32 * 16;
   if (smem > 160 * 1024) return -6;
   // about four CTAs per SM; each warp takes `rpw` consecutive rows
-  int rpw = 1;
+  int rpw = ex.use_ll ? 2 : 1;                                      // the folded all-reduce packs two adjacent rows per word
   while ((N + 8 * rpw - 1) / (8 * rpw) > sm_count * 3 && rpw < 16) rpw *= 2;
+  if ((ex.use_ll || ex.norm_w != nullptr || ex.route) && (groups > 1 || swiglu)) return -7;
+  if (ex.use_ll && ((N & 1) || static_cast<long long>(T) * N / 2 > ex.ll.words)) return -8;
+  if (ex.route && (!out_fp32 || N > 512 || N != ex.router.E || ex.route_counter == nullptr)) return -9;
   int group_rows = 0;
   if (groups > 1) {
     group_rows = N / groups;
@@ -262,7 +361,7 @@ STK_API int stk_skinny_linear(const void* W, long long ldw, int is_fp8, const fl
       configured = true;                                                                                               \
     }                                                                                                                  \
     launch_pdl(skinny_linear_kernel<T_, F_, I_, S_>, dim3(grid), dim3(256), smem, st, (const uint8_t*)W, ldw_bytes,     \
-               w_scale, w_scale_ld, (const __nv_bfloat16*)x, ldx, out, ldo, N, K, out_fp32, rpw, group_rows, limit, T); \
+               w_scale, w_scale_ld, (const __nv_bfloat16*)x, ldx, out, ldo, N, K, out_fp32, rpw, group_rows, limit, T, ex); \
   }
 #define STK_SK2(T_, F_)                                                                                 \
   {                                                                                                     \
@@ -289,4 +388,42 @@ STK_API int stk_skinny_linear(const void* W, long long ldw, int is_fp8, const fl
 #undef STK_SK2
 #undef STK_SK3
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+STK_API int stk_skinny_linear(const void* W, long long ldw, int is_fp8, const float* w_scale, int w_scale_ld,
+                              const void* x, long long ldx, void* out, long long ldo, int T, int N, int K,
+                              int out_fp32, int sm_count, int groups, int swiglu, float limit, void* stream) {
+  SkinnyExtra ex;
+  memset(&ex, 0, sizeof(ex));
+  return skinny_launch(W, ldw, is_fp8, w_scale, w_scale_ld, x, ldx, out, ldo, T, N, K, out_fp32, sm_count, groups, swiglu,
+                       limit, ex, stream);
+}
+
+// The same projection with its neighbours fused in (see the head of this file):
+//   norm_w != nullptr   x is RMS-normalised (norm_w, norm_eps) on the way in;
+//   ll_ctx != nullptr   the bf16 result goes into every rank's all-reduce slot (N even) and `out` is not written;
+//   route != 0          `out` is fp32 gate logits [T, N = E]; the last CTA writes the experts and weights of every token
+//                       (route_counter: one zero-initialised int that the kernel leaves at zero).
+STK_API int stk_skinny_linear_fused(const void* W, long long ldw, int is_fp8, const float* w_scale, int w_scale_ld,
+                                    const void* x, long long ldx, void* out, long long ldo, int T, int N, int K,
+                                    int out_fp32, int sm_count, const void* norm_w, float norm_eps, const void* ll_ctx,
+                                    int route, int* route_counter, const float* bias, const int* tid2eid,
+                                    const int64_t* token_ids, int vocab, int* ids, float* weights, int topk, int scoring,
+                                    int renorm, float scaling, int* status, void* stream) {
+  SkinnyExtra ex;
+  memset(&ex, 0, sizeof(ex));
+  ex.norm_w = (const __nv_bfloat16*)norm_w;
+  ex.norm_eps = norm_eps;
+  if (ll_ctx != nullptr) {
+    memcpy(&ex.ll, ll_ctx, sizeof(ex.ll));
+    ex.use_ll = 1;
+  }
+  if (route) {
+    if (topk > 32) return -9;
+    ex.route = 1;
+    ex.route_counter = route_counter;
+    ex.router = RouterArgs{bias, tid2eid, token_ids, vocab, ids, weights, N, topk, scoring, renorm, scaling, status};
+  }
+  return skinny_launch(W, ldw, is_fp8, w_scale, w_scale_ld, x, ldx, out, ldo, T, N, K, out_fp32, sm_count, 1, 0, 0.f, ex,
+                       stream);
 }

@@ -65,4 +65,67 @@ __device__ __forceinline__ uint4 pack_bf16x8(const float (&acc)[8]) {
   return o;
 }
 
+// ---- all-reduce folded into its producer and its consumer ------------------------------------------------
+// For decode-sized activations the sum over ranks needs no kernel of its own.  The kernel that produces a
+// row-parallel partial result stores it straight into every rank's receive slot, and the kernel that consumes the
+// sum reads the `world` slots and adds them in a fixed order.  Each 8-byte word carries two bf16 values and the
+// 32-bit epoch of the exchange, written with one store, so the payload is its own flag: no fence, no separate flag
+// store, no wait kernel.  Slots are double-buffered by epoch parity; a word whose epoch is not the expected one has
+// simply not arrived yet (the previous use of the slot left epoch - 2).
+//
+// Epochs are device-resident so that captured graphs replay: the producer reads counters[0] (the epoch the last
+// consumer finished) and stamps counters[0] + 1; before it exits it writes that value to counters[1], which the
+// consumer reads; before the consumer exits it writes the value back to counters[0].  Every CTA writes the same
+// value, so no CTA has to be elected; a kernel never writes the word it reads.  Producer and consumer must be
+// ordered on one stream (with programmatic dependent launch: read the counter after pdl_wait()).
+//
+// Safety of slot reuse: a rank starts exchange e + 2 only after its own consumer of e + 1 finished, which needed
+// every peer's words of e + 1, which every peer wrote only after its consumer of e had finished reading.
+struct LLAr {
+  uint2* slots[kMaxRanks];   // each rank's receive region as mapped here: [2 parities][world sources][words]
+  uint32_t* counters;        // local, two words (see above)
+  long long words;           // capacity per (parity, source) in 8-byte words
+  int rank, world;
+  uint32_t spin_budget;      // polls before a consumer gives up on a word
+};
+
+__device__ __forceinline__ uint32_t ll_push_epoch(const LLAr& l) { return __ldcg(l.counters) + 1; }
+__device__ __forceinline__ void ll_push_done(const LLAr& l, uint32_t e) { l.counters[1] = e; }
+__device__ __forceinline__ uint32_t ll_read_epoch(const LLAr& l) { return __ldcg(l.counters + 1); }
+__device__ __forceinline__ void ll_read_done(const LLAr& l, uint32_t e) { l.counters[0] = e; }
+
+// Store one word (two bf16 values packed in `data`) into slot [parity(e)][my rank] of rank `peer`.
+__device__ __forceinline__ void ll_store(const LLAr& l, uint32_t e, int peer, long long word, uint32_t data) {
+  uint2* dst = l.slots[peer] + (static_cast<long long>(e & 1) * l.world + l.rank) * l.words + word;
+  // one 64-bit scalar store: single-copy atomic, so a reader sees the payload and its epoch together
+  const unsigned long long v = static_cast<unsigned long long>(data) | (static_cast<unsigned long long>(e) << 32);
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint2 ll_load(const uint2* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return make_uint2(static_cast<uint32_t>(v), static_cast<uint32_t>(v >> 32));
+}
+// Word `word` of source rank `src` for exchange e, polled until its epoch matches.  On expiry records a status and
+// returns false with data = 0 (the caller carries on with zeros: wrong numbers, no hang).
+__device__ __forceinline__ bool ll_wait_word(const LLAr& l, uint32_t e, int src, long long word, uint32_t& data,
+                                             int* status) {
+  const uint2* p = l.slots[l.rank] + (static_cast<long long>(e & 1) * l.world + src) * l.words + word;
+  for (uint32_t i = 0; i < l.spin_budget; ++i) {
+    const uint2 v = ll_load(p);
+    if (v.y == e) { data = v.x; return true; }
+    if (i > 128) __nanosleep(20);
+  }
+  data = 0;
+  set_status(status, kTimeoutPeerFlag, 300 + src);
+  return false;
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ float2 unpack_bf16x2(uint32_t v) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v));
+}
+
 }  // namespace stk

@@ -22,6 +22,7 @@ from typing import Callable, Dict, List, Optional, Tuple
 
 SAMPLER = "stkernel_b200/csrc/sampler.cu"
 MOE = "stkernel_b200/csrc/moe.cu"
+ROUTER = "stkernel_b200/csrc/router.cuh"      # the selection code shared by the router kernel and the gate epilogue
 ELEMENTWISE = "stkernel_b200/csrc/elementwise.cu"
 KVCACHE = "stkernel_b200/csrc/kvcache.cu"
 ATTENTION = "stkernel_b200/csrc/attention_tc.cu"
@@ -58,8 +59,8 @@ def _embed(text: str) -> Tuple[bool, str]:
 
 
 def _hash_moe(text: str) -> Tuple[bool, str]:
-    tok = _count(text, r"tok\s*>=\s*0\s*&&\s*tok\s*<\s*vocab\b")
-    eid = _count(text, r"e\s*<\s*0\s*\|\|\s*e\s*>=\s*E\b")
+    tok = _count(text, r"tok\s*>=\s*0\s*&&\s*tok\s*<\s*(r\.)?vocab\b")
+    eid = _count(text, r"e\s*<\s*0\s*\|\|\s*e\s*>=\s*(r\.)?E\b")
     return tok >= 1 and eid >= 1, f"hash-table token guard: {tok}/1, table-entry expert guard: {eid}/1"
 
 
@@ -82,7 +83,7 @@ def _attn_slots(text: str) -> Tuple[bool, str]:
 RULES: Tuple[Tuple[str, str, Checker], ...] = (
     ("sampler.gumbel_argmax", SAMPLER, _sampler),
     ("embed.token_id", ELEMENTWISE, _embed),
-    ("hash_moe.token_table", MOE, _hash_moe),
+    ("hash_moe.token_table", ROUTER, _hash_moe),
     ("expert_map.kernels", MOE, _expert_map),
     ("kv_cache.slot", KVCACHE, _kv_slots),
     ("sparse_mla.gather", ATTENTION, _attn_slots),
@@ -130,7 +131,8 @@ def self_test() -> int:
         SAMPLER: "const int v0 = blockIdx.y * chunk, v1 = min(V, v0 + chunk);\nfor (int v = v0 + threadIdx.x; v < v1; v += 1) {}\n"
                  "out[row] = best_i == 0x7fffffff ? 0 : best_i;",
         ELEMENTWISE: "const bool in_vocab = id >= 0 && id < vocab; if (!in_vocab) set_status(status, kBadIndex, t);",
-        MOE: "const bool ok = tok >= 0 && tok < vocab; if (e < 0 || e >= E) {}\n" + "if (e < 0 || e >= e_local) return;\n" * 4,
+        ROUTER: "const bool ok = tok >= 0 && tok < r.vocab; if (e < 0 || e >= r.E) {}\n",
+        MOE: "if (e < 0 || e >= e_local) return;\n" * 4,
         KVCACHE: "if (slot < 0) return; if (slot >= num_slots) {}",
         ATTENTION: "valid = slot >= 0; if (slot < 0) {}",
     }
@@ -140,7 +142,7 @@ def self_test() -> int:
         print("self-test: guarded sources did not PASS", [x for x in r if x.status != "PASS"])
         return 1
     broken = dict(src)
-    broken[MOE] = {"path": MOE, "text": good[MOE].replace("tok >= 0 && ", "")}
+    broken[ROUTER] = {"path": ROUTER, "text": good[ROUTER].replace("tok >= 0 && ", "")}
     r = evaluate(broken)
     bad = [x.name for x in r if x.status == "FAIL"]
     if exit_code(r) != 1 or bad != ["hash_moe.token_table"]:

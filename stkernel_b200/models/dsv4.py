@@ -292,12 +292,33 @@ class DSV4Model:
         # router) run on a second stream, also inside captured graphs, so the chain gets shorter.
         self.fork_max_t = int(os.environ.get("STK_FORK_MAX_T", "64")) if dev.type == "cuda" else 0
         self.side_stream = torch.cuda.Stream(dev) if self.fork_max_t > 0 else None
+        self.kv_stream = torch.cuda.Stream(dev) if self.fork_max_t > 0 else None     # latent-row insert, beside wq_b
+        # Decode-sized steps fold neighbouring launches into the weight-streaming projections (q/kv norms into the
+        # consumers, the router into the gate projection) and, under tensor parallelism, the two all-reduces of a layer
+        # into the kernels on either side of them (`_ll`).  STK_DECODE_FUSE=0 restores the separate launches;
+        # STK_LL_LOOPBACK=1 runs the folded all-reduce protocol on a single GPU (one rank, nothing to add).
+        self.decode_fuse = dev.type == "cuda" and os.environ.get("STK_DECODE_FUSE", "1") == "1"
+        self._ll_loop = None
+        if dev.type == "cuda" and tp_size == 1 and os.environ.get("STK_LL_LOOPBACK", "0") == "1":
+            from ..parallel.symm import LLExchange
+            self._ll_loop = LLExchange.loopback(dev, 64 * cfg.hidden_size // 2)
 
     # ---- collectives ----------------------------------------------------------
     def _all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         if self.tp_size == 1 or self.comm is None:
             return x
         return self.comm.all_reduce(x)
+
+    def _ll(self, t: int, h: int):
+        """The folded all-reduce for a decode-sized [t, h] row-parallel output, or None (then the output is reduced by
+        the GEMM epilogue / the all-reduce kernels)."""
+        if not self.decode_fuse or t > Fn.SKINNY_MAX_T:
+            return None
+        if self._ll_loop is not None:
+            return self._ll_loop if self._ll_loop.fits(t, h) else None
+        if self.tp_size == 1 or self.comm is None or getattr(self.comm, "symm", None) is None or not self.comm.fuse_gemm:
+            return None
+        return self.comm.symm.ll_exchange(t, h)
 
     def _gemm_ar_ctx(self, t: int, n: int):
         """Symmetric context when the row-parallel GEMM can all-reduce in its own epilogue."""
@@ -320,19 +341,44 @@ class DSV4Model:
         fork = bool(lw.ratio) and self.side_stream is not None and 0 < T <= self.fork_max_t
         ev_in = torch.cuda.current_stream().record_event() if fork else None
         qkv = Fn.linear(yq if yq is not None else y, lw.w_qa_kv, tag="qa_kv")
+        can_fork = self.side_stream is not None and 0 < T <= self.fork_max_t
+        ev_qkv = torch.cuda.current_stream().record_event() if can_fork else None
         use_q = lw.w_qb.is_fp8 and Fn.wants_quant_act(T, y.device)
-        res = Fn.rms_norm_pair(qkv[:, :ql], lw.q_norm, qkv[:, ql:], lw.kv_norm, cfg.rms_norm_eps, quant0=use_q, tag="qr")
-        qr, kvn = res[0], res[1]
-        qb = Fn.linear(res[2] if use_q else qr, lw.w_qb, tag="qb")
+        fuse_norms = self.decode_fuse and T <= Fn.SKINNY_MAX_T and not use_q
+        if fuse_norms:
+            # no norm launch: the q_lora row is normalised inside the wq_b projection, the kv row inside the cache insert
+            kvn, kv_norm_w = qkv[:, ql:], lw.kv_norm
+            qb = Fn.linear(qkv[:, :ql], lw.w_qb, tag="qb", norm=(lw.q_norm, cfg.rms_norm_eps))
+        else:
+            res = Fn.rms_norm_pair(qkv[:, :ql], lw.q_norm, qkv[:, ql:], lw.kv_norm, cfg.rms_norm_eps, quant0=use_q, tag="qr")
+            qr, kvn, kv_norm_w = res[0], res[1], None
+            qb = Fn.linear(res[2] if use_q else qr, lw.w_qb, tag="qb")
+
+        # decode-sized steps: the attention kernel norms and rotates q as it loads it, so only the latent row is written
+        q_in_mla = (fuse_norms and A.USE_DECODE_MLA and T <= A.MLA_DECODE_MAX_T and nh_l % 8 == 0 and D == 512
+                    and Rd == 64 and self.kv.swa_cache[li].fp8)
 
         def kv_insert():
-            return C.q_rope_kv_insert(qb[:, :nh_l * D].view(T, nh_l, D), kvn, meta.positions, meta.swa_slot_mapping,
-                                      self.inv, self.kv.swa_cache[li], cfg.rms_norm_eps)
+            qv = qb[:, :nh_l * D].view(T, nh_l, D)
+            if q_in_mla:
+                C.q_rope_kv_insert(None, kvn, meta.positions, meta.swa_slot_mapping, self.inv, self.kv.swa_cache[li],
+                                   cfg.rms_norm_eps, kv_norm_w=kv_norm_w)
+                return qv
+            return C.q_rope_kv_insert(qv, kvn, meta.positions, meta.swa_slot_mapping,
+                                      self.inv, self.kv.swa_cache[li], cfg.rms_norm_eps, kv_norm_w=kv_norm_w)
 
         topk_slots = topk_lens = None
         comp_cache = None
+        ev_done = None
         if not lw.ratio:
-            q = kv_insert()
+            if q_in_mla and can_fork:
+                # the latent row needs only the kv half of the projection: it is written beside the wq_b projection
+                with side_branch(self.kv_stream, "kv"):
+                    self.kv_stream.wait_event(ev_qkv)
+                    q = kv_insert()
+                    ev_done = self.kv_stream.record_event()
+            else:
+                q = kv_insert()
         else:
             c = compressor_slots(lw.ratio)
             ncomp = 2 * c * D
@@ -351,7 +397,8 @@ class DSV4Model:
                                    meta.tok_req, meta.first_pos, meta.last_pos, self.kv.idx_state[li],
                                    grp.table_dev, self.kv.idx_cache[li], lw.ratio, 2, cfg.rms_norm_eps)
 
-            ev_side = ev_idx = ev_done = None
+            ev_side = ev_idx = ev_kv = None
+            early_slots = None
             if fork:
                 # side stream: side projection -> indexer-key compressor -> KV compressor -> q rope + SWA insert;
                 # this stream keeps the q / indexer scoring chain and waits where it needs the other's results
@@ -359,15 +406,28 @@ class DSV4Model:
                 ev_qb = main.record_event()
                 with side_branch(sd):
                     sd.wait_event(ev_in)       # y is ready: the branch starts beside the qa/kv projection
+                    if lw.kind == "c4a" and not computes and self.topk_buffer is not None and self.topk_buffer.shape[0] >= T:
+                        # a layer that reuses the shared top-k rows only translates them to its own cache's slots:
+                        # nothing of this layer is needed for that
+                        early_slots = A.topk_to_slots(self.topk_buffer[:T], grp.table_dev, meta.tok_req,
+                                                      grp.max_pages_per_req * C.PAGE, tag=f"topk")
                     side = Fn.linear(y, lw.w_side, out_dtype=F32, tag="side")
                     ev_side = sd.record_event()
                     if computes:
                         compress_idx(side)
                         ev_idx = sd.record_event()
                     compress_main(side)
-                    sd.wait_event(ev_qb)
-                    q = kv_insert()
+                    if not q_in_mla:
+                        sd.wait_event(ev_qb)
+                        q = kv_insert()
                     ev_done = sd.record_event()
+                if q_in_mla:
+                    # the latent row needs only the kv half of the first projection: its own branch, beside wq_b and
+                    # not queued behind the compressors
+                    with side_branch(self.kv_stream, "kv"):
+                        self.kv_stream.wait_event(ev_qkv)
+                        q = kv_insert()
+                        ev_kv = self.kv_stream.record_event()
             else:
                 q = kv_insert()
                 side = Fn.linear(y, lw.w_side, out_dtype=F32, tag="side")
@@ -403,20 +463,26 @@ class DSV4Model:
                         scores = A.indexer_scores(qq, wf, self.kv.idx_cache[li], grp.table_dev, meta.tok_req, nv,
                                                   max(meta.max_comp_rows, 1))
                         A.topk_rows(scores, nv, K, out=self.topk_buffer)
-                topk_slots, topk_lens = A.topk_to_slots(self.topk_buffer[:T], grp.table_dev, meta.tok_req,
-                                                        grp.max_pages_per_req * C.PAGE, tag=f"topk")
+                if early_slots is not None:
+                    topk_slots, topk_lens = early_slots
+                else:
+                    topk_slots, topk_lens = A.topk_to_slots(self.topk_buffer[:T], grp.table_dev, meta.tok_req,
+                                                            grp.max_pages_per_req * C.PAGE, tag=f"topk")
             else:
                 topk_slots, topk_lens = A.c128_indices(meta.positions, meta.tok_req, grp.table_dev, lw.ratio,
                                                        cfg.index_topk)
-            if fork:
-                torch.cuda.current_stream().wait_event(ev_done)
+        if ev_done is not None:
+            torch.cuda.current_stream().wait_event(ev_done)
+        if lw.ratio and ev_kv is not None:
+            torch.cuda.current_stream().wait_event(ev_kv)
         with span("sparse_mla", T):
             if (self.tp_size > 1 and self.comm is not None and lw.sink_full is not None and self.mla_tp_min_rows > 0
                     and T >= self.mla_tp_min_rows):
                 o = self._mla_token_parallel(li, lw, q, meta, comp_cache, topk_slots, topk_lens)
             else:
                 o = A.sparse_mla(q, self.kv.swa_cache[li], meta.swa_slots, meta.swa_lens, comp_cache, topk_slots,
-                                 topk_lens, lw.sink, D ** -0.5, inv_rope=(meta.positions, self.inv))
+                                 topk_lens, lw.sink, D ** -0.5, inv_rope=(meta.positions, self.inv),
+                                 q_prep=(meta.positions, self.inv, cfg.rms_norm_eps) if q_in_mla else None)
         # grouped low-rank output projection, then the row-parallel wo_b (+ all-reduce)
         G_l = len(lw.w_oa)
         hpg = cfg.num_attention_heads // cfg.o_groups
@@ -430,6 +496,9 @@ class DSV4Model:
         with span("o_proj_b+allreduce", T):
             if scatter:
                 return self.comm.reduce_scatter_dim0(Fn.linear(z, lw.w_ob, tag="ob"))
+            ll = self._ll(T, cfg.hidden_size)
+            if ll is not None:
+                return Fn.linear(z, lw.w_ob, tag="ob", ll=ll)          # an LLPending: the next mHC kernel adds the ranks
             ar = self._gemm_ar_ctx(T, cfg.hidden_size)
             out = Fn.linear(z, lw.w_ob, tag="ob", ar_ctx=ar)
             return out if ar is not None else self._all_reduce(out)
@@ -471,13 +540,22 @@ class DSV4Model:
                 sd.wait_event(ev_in)
                 shared = self._shared_expert(lw, y, yq)
                 ev_sh = sd.record_event()
-        logits = Fn.linear(y, lw.w_gate, out_dtype=F32, tag="gate")
-        ids, wts = M.router(logits, lw.gate_bias, cfg.num_experts_per_tok, cfg.scoring_func, cfg.norm_topk_prob,
-                            cfg.routed_scaling_factor, lw.tid2eid, meta.token_ids)
+        routed = None
+        if self.decode_fuse and T <= Fn.SKINNY_MAX_T:
+            routed = Fn.gate_route(y, lw.w_gate, lw.gate_bias, cfg.num_experts_per_tok, cfg.scoring_func, cfg.norm_topk_prob,
+                                   cfg.routed_scaling_factor, lw.tid2eid, meta.token_ids)
+        if routed is None:
+            logits = Fn.linear(y, lw.w_gate, out_dtype=F32, tag="gate")
+            routed = M.router(logits, lw.gate_bias, cfg.num_experts_per_tok, cfg.scoring_func, cfg.norm_topk_prob,
+                              cfg.routed_scaling_factor, lw.tid2eid, meta.token_ids)
+        ids, wts = routed
         if not fork:
             shared = self._shared_expert(lw, y, yq)
+        ll = None if scatter or not (y.is_cuda and lw.experts.is_fp4) else self._ll(T, cfg.hidden_size)
         out = M.moe_experts(y, ids, wts, lw.experts, cfg.swiglu_limit, shared, cfg.n_routed_experts,
-                            shared_ready=ev_sh if fork else None)
+                            shared_ready=ev_sh if fork else None, ll=ll)
+        if ll is not None:
+            return out                                                  # an LLPending
         return self.comm.reduce_scatter_dim0(out) if scatter else self._all_reduce(out)
 
     def _shared_expert(self, lw: LayerWeights, y: torch.Tensor, yq) -> Optional[torch.Tensor]:

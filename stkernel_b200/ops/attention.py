@@ -222,16 +222,46 @@ def topk_to_slots(topk: torch.Tensor, block_table: torch.Tensor, tok_req: torch.
 
 
 # ---- attention ------------------------------------------------------------------------
+USE_DECODE_MLA = True          # register-resident kernel for decode-sized steps (False: always the tensor-core kernel)
+MLA_DECODE_MAX_T = 8
+
+
 def sparse_mla(q: torch.Tensor, swa_cache: PagedCache, swa_slots: torch.Tensor, swa_lens: torch.Tensor,
                comp_cache: Optional[PagedCache], topk_slots: Optional[torch.Tensor], topk_lens: Optional[torch.Tensor],
-               sink: torch.Tensor, scale: float, inv_rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
-               ) -> torch.Tensor:
+               sink: torch.Tensor, scale: float, inv_rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+               q_prep: Optional[Tuple[torch.Tensor, torch.Tensor, float]] = None) -> torch.Tensor:
     """q [T, nh, D] bf16 -> out [T, nh, D] bf16 attending to the SWA rows then the top-k rows.
 
     Only the first swa_lens[t] / topk_lens[t] entries of each list are read; -1 entries inside that
     range are masked.  inv_rope = (positions, inv_freq): also apply the inverse RoPE to the output's
-    rope dims (fused into the split-merge kernel on the tensor-core path)."""
+    rope dims (fused into the split-merge kernel on the tensor-core path).
+    q_prep = (positions, inv_freq, eps): q is the raw projection output; its per-head weightless RMSNorm and RoPE are
+    applied here (inside the decode kernel when it serves the step, else by the stand-alone op first)."""
     t, nh, d = q.shape
+    decode_kernel = (q.is_cuda and USE_DECODE_MLA and t <= MLA_DECODE_MAX_T and swa_cache.fp8 and d == 512
+                     and swa_cache.rope_dim == 64 and nh % 8 == 0 and q.stride(0) % 8 == 0 and q.stride(1) == d
+                     and (comp_cache is None or comp_cache.fp8)
+                     and swa_slots.shape[1] + (topk_slots.shape[1] if topk_slots is not None else 0) <= 4096)
+    if q_prep is not None and not decode_kernel:
+        from .functional import q_norm_rope
+        q = q_norm_rope(q, q_prep[0], q_prep[1], swa_cache.rope_dim, q_prep[2])
+    if decode_kernel:
+        max_rows = swa_slots.shape[1] + (topk_slots.shape[1] if topk_slots is not None else 0)
+        S = _lib.query("stk_mla_decode_splits", t, nh, max_rows, _lib.sm_count())
+        assert S > 0
+        ws = scratch("mla.dpartial", (t * S * nh * 516,), F32, q.device)
+        out = torch.empty(t, nh, d, dtype=BF16, device=q.device)
+        pos = q_prep[0] if q_prep is not None else (inv_rope[0] if inv_rope is not None else None)
+        inv = q_prep[1] if q_prep is not None else (inv_rope[1] if inv_rope is not None else None)
+        _lib.call("stk_sparse_mla_decode", q, q.stride(0), swa_cache.buf, swa_cache.page_stride, swa_cache.num_slots,
+                  comp_cache.buf if comp_cache is not None else None,
+                  comp_cache.page_stride if comp_cache is not None else 0,
+                  comp_cache.num_slots if comp_cache is not None else 0, swa_slots, swa_slots.stride(0), swa_slots.shape[1],
+                  swa_lens, topk_slots, topk_slots.stride(0) if topk_slots is not None else 0,
+                  topk_slots.shape[1] if topk_slots is not None else 0, topk_lens, sink, out, out.stride(0), ws,
+                  S, t, nh, float(scale), 1 if q_prep is not None else 0, float(q_prep[2]) if q_prep is not None else 0.0,
+                  pos, inv, 1 if inv_rope is not None else 0, _lib.status_buffer(), _lib.stream())
+        return out
     if not q.is_cuda:
         out = torch.zeros(t, nh, d, dtype=F32)
         for i in range(t):

@@ -155,18 +155,25 @@ def kv_rope_quant_insert(kv: torch.Tensor, positions: torch.Tensor, slots: torch
               cache.data_bytes, 1 if cache.fp8 else 0, cache.num_slots, t, d, rd, _lib.status_buffer(), _lib.stream())
 
 
-def q_rope_kv_insert(q: torch.Tensor, kv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, inv: torch.Tensor,
-                     cache: PagedCache, eps: float) -> torch.Tensor:
+def q_rope_kv_insert(q: Optional[torch.Tensor], kv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
+                     inv: torch.Tensor, cache: PagedCache, eps: float, kv_norm_w: Optional[torch.Tensor] = None
+                     ) -> Optional[torch.Tensor]:
     """One launch: per-head weightless RMSNorm + RoPE of q [T, nh, D] (in place) and RoPE + quantise +
-    insert of the latent rows kv [T, D]."""
-    if not q.is_cuda:
-        from .functional import q_norm_rope
+    insert of the latent rows kv [T, D].
+
+    kv_norm_w: kv arrives un-normalised and its RMSNorm (this weight, same eps) happens inside the insert.
+    q None: only the latent rows are written (the decode attention kernel norms and rotates q itself)."""
+    if not kv.is_cuda:
+        from .functional import cpu_act_dtype, q_norm_rope
+        if kv_norm_w is not None:
+            kv = R.rms_norm(kv, kv_norm_w, eps).to(cpu_act_dtype())
         kv_rope_quant_insert(kv, positions, slots, inv, cache)
-        return q_norm_rope(q, positions, inv, cache.rope_dim, eps)
-    t, nh, d = q.shape
-    _lib.call("stk_q_rope_kv_insert", q, q.stride(0), nh, eps, kv, kv.stride(0), positions, slots, inv, cache.buf,
-              cache.page_stride, cache.data_bytes, 1 if cache.fp8 else 0, cache.num_slots, t, d, cache.rope_dim,
-              _lib.status_buffer(), _lib.stream())
+        return q_norm_rope(q, positions, inv, cache.rope_dim, eps) if q is not None else None
+    t, d = kv.shape
+    nh = q.shape[1] if q is not None else 0
+    _lib.call("stk_q_rope_kv_insert", q, q.stride(0) if q is not None else 0, nh, eps, kv, kv.stride(0), positions, slots,
+              inv, cache.buf, cache.page_stride, cache.data_bytes, 1 if cache.fp8 else 0, cache.num_slots, t, d,
+              cache.rope_dim, kv_norm_w, _lib.status_buffer(), _lib.stream())
     return q
 
 

@@ -79,6 +79,35 @@ class QuantAct:
     scale: torch.Tensor
 
 
+@dataclass
+class LLPending:
+    """A [T, H] bf16 activation that exists only as per-rank partial sums in the receive slots of a folded all-reduce
+    (`parallel.symm.LLExchange`): the producer kernel pushed them, the consumer kernel (`mhc_post_pre`, or `ll_reduce`)
+    adds the ranks.  Exactly one consumer must follow each producer on the same stream."""
+    ex: "object"
+    t: int
+    h: int
+    device: torch.device
+
+    @property
+    def shape(self):
+        return (self.t, self.h)
+
+
+def ll_push(x: torch.Tensor, ex) -> LLPending:
+    """Producer on its own: push a finished [T, H] bf16 tensor into every rank's slot."""
+    t, h = x.shape
+    _lib.call("stk_ll_push", ex.ctx, x, x.stride(0), t, h, _lib.stream())
+    return LLPending(ex, t, h, x.device)
+
+
+def ll_reduce(p: LLPending) -> torch.Tensor:
+    """Consumer on its own: the sum over ranks as a plain bf16 tensor."""
+    out = torch.empty(p.t, p.h, dtype=BF16, device=p.device)
+    _lib.call("stk_ll_reduce", p.ex.ctx, out, out.stride(0), p.t, p.h, _lib.status_buffer(), _lib.stream())
+    return out
+
+
 SKINNY_MAX_T = 4          # above four tokens the tcgen05 GEMM with split-K is faster (measured at six)
 MHC_CLUSTER_MAX_T = int(_os.environ.get("STK_MHC_CLUSTER_MAX_T", "64"))
 
@@ -112,8 +141,14 @@ def quant_act(x: torch.Tensor, tag: str = "act") -> QuantAct:
     return QuantAct(q.view(FP8), s)
 
 
+def _skinny_ok(x, t: int, k: int, is_fp8: bool) -> bool:
+    # a lane holds at most 32 16-byte chunks of a weight row: K <= 16384 for fp8, K <= 8192 for bf16
+    return (isinstance(x, torch.Tensor) and x.is_cuda and t <= SKINNY_MAX_T and x.dtype == BF16 and k % 16 == 0
+            and k <= (16384 if is_fp8 else 8192) and _skinny_rows(t) * k * 2 <= 160 * 1024)
+
+
 def linear(x, lw: LinearWeight, out: Optional[torch.Tensor] = None, out_dtype=BF16, tag: str = "lin",
-           splits: Optional[int] = None, groups: int = 1, ar_ctx=None) -> torch.Tensor:
+           splits: Optional[int] = None, groups: int = 1, ar_ctx=None, norm=None, ll=None):
     """out[T, N] = x[T, K] @ W[N, K]^T.  x: bf16 tensor or a QuantAct (required format for fp8 weights
     is produced on the fly when a bf16 tensor is given).
 
@@ -121,7 +156,25 @@ def linear(x, lw: LinearWeight, out: Optional[torch.Tensor] = None, out_dtype=BF
     epilogue (row-parallel layers).  The output must be contiguous.
 
     groups > 1: block-diagonal product.  W is [N, K] with N/groups rows per group, x is [T, groups*K];
-    output columns of group g use x[:, g*K:(g+1)*K]."""
+    output columns of group g use x[:, g*K:(g+1)*K].
+
+    norm = (weight, eps): x is RMS-normalised first (inside the weight-streaming kernel for decode-sized batches).
+    ll: an `LLExchange`; the bf16 result is a per-rank partial sum that goes into the folded all-reduce and an
+    `LLPending` is returned instead of a tensor (row-parallel layers at decode sizes)."""
+    if (norm is not None or ll is not None) and not isinstance(x, QuantAct) and x.is_cuda:
+        t0, (n0, k0) = x.shape[0], lw.w.shape
+        if groups == 1 and ar_ctx is None and out_dtype == BF16 and _skinny_ok(x, t0, k0, lw.is_fp8) and (ll is None or n0 % 2 == 0):
+            o = out if out is not None else (None if ll is not None else torch.empty(t0, n0, dtype=BF16, device=x.device))
+            _lib.call("stk_skinny_linear_fused", lw.w, lw.w.stride(0), 1 if lw.is_fp8 else 0, lw.scale,
+                      lw.scale.stride(0) if lw.is_fp8 else 0, x, x.stride(0), o, o.stride(0) if o is not None else 0, t0, n0, k0,
+                      0, _lib.sm_count(), norm[0] if norm is not None else None, float(norm[1]) if norm is not None else 0.0,
+                      ll.ctx if ll is not None else None, 0, None, None, None, None, 0, None, None, 0, 0, 0, 0.0,
+                      _lib.status_buffer(), _lib.stream())
+            return LLPending(ll, t0, n0, x.device) if ll is not None else o
+    if norm is not None:
+        x = rms_norm(x, norm[0], norm[1])
+    if ll is not None:
+        return ll_push(linear(x, lw, out, out_dtype, tag, splits, groups, ar_ctx), ll)
     if isinstance(x, QuantAct):
         xa, dev, t = x, x.q.device, x.q.shape[0]
     else:
@@ -154,9 +207,7 @@ def linear(x, lw: LinearWeight, out: Optional[torch.Tensor] = None, out_dtype=BF
         return y
     if out is None:
         out = torch.empty(t, n, dtype=out_dtype, device=dev)
-    # a lane holds at most 32 16-byte chunks of a weight row: K <= 16384 for fp8, K <= 8192 for bf16
-    if (xa is None and t <= SKINNY_MAX_T and ar_ctx is None and x.dtype == BF16 and k % 16 == 0
-            and k <= (16384 if lw.is_fp8 else 8192) and _skinny_rows(t) * k * 2 <= 160 * 1024):
+    if xa is None and ar_ctx is None and _skinny_ok(x, t, k, lw.is_fp8):
         # one to four tokens: weight-streaming kernel, activations unquantised
         _lib.call("stk_skinny_linear", lw.w, lw.w.stride(0), 1 if lw.is_fp8 else 0, lw.scale,
                   lw.scale.stride(0) if lw.is_fp8 else 0, x, x.stride(0), out, out.stride(0), t, n, k,
@@ -181,6 +232,33 @@ def linear(x, lw: LinearWeight, out: Optional[torch.Tensor] = None, out_dtype=BF
               _lib.status_buffer(), sms, groups, ctypes.addressof(ar_ctx) if ar_ctx is not None else None,
               _lib.stream())
     return out
+
+
+_route_counters: dict = {}
+
+
+def gate_route(x: torch.Tensor, w_gate: LinearWeight, bias, top_k: int, scoring: str, renorm: bool, scaling: float,
+               tid2eid=None, token_ids=None):
+    """Router gate projection and expert selection in one launch for decode-sized batches (the CTA that finishes the
+    projection last routes the tokens); returns (ids i32 [T, k], weights f32 [T, k]) or None when that kernel does
+    not apply (the caller then runs the projection and the router separately)."""
+    t, k = x.shape
+    e = w_gate.w.shape[0]
+    if not _skinny_ok(x, t, k, w_gate.is_fp8) or e > 512 or top_k > 32:
+        return None
+    dev = x.device
+    cnt = _route_counters.get(dev.index)
+    if cnt is None:
+        cnt = _route_counters[dev.index] = torch.zeros(1, dtype=torch.int32, device=dev)
+    logits = scratch("gate.logits", (t, e), F32, dev)
+    ids = torch.empty(t, top_k, dtype=torch.int32, device=dev)
+    wts = torch.empty(t, top_k, dtype=F32, device=dev)
+    vocab = tid2eid.shape[0] if tid2eid is not None else 0
+    _lib.call("stk_skinny_linear_fused", w_gate.w, w_gate.w.stride(0), 1 if w_gate.is_fp8 else 0, w_gate.scale,
+              w_gate.scale.stride(0) if w_gate.is_fp8 else 0, x, x.stride(0), logits, logits.stride(0), t, e, k, 1,
+              _lib.sm_count(), None, 0.0, None, 1, cnt, bias, tid2eid, token_ids, vocab, ids, wts, top_k,
+              0 if scoring == "sigmoid" else 1, 1 if renorm else 0, float(scaling), _lib.status_buffer(), _lib.stream())
+    return ids, wts
 
 
 def linear_swiglu(x: torch.Tensor, lw13: LinearWeight, limit: float) -> Optional[torch.Tensor]:
@@ -309,6 +387,13 @@ def mhc_pre(residual: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale:
         return res + (quant_act(y),) if quant else res
     dev = residual.device
     n_mix = (2 + hc) * hc
+    if t <= MHC_CLUSTER_MAX_T and hc == 4 and h % 32 == 0 and h <= 4096:
+        y = torch.empty(t, h, dtype=BF16, device=dev)
+        post = torch.empty(t, hc, dtype=F32, device=dev)
+        comb = torch.empty(t, hc * hc, dtype=F32, device=dev)
+        _lib.call("stk_mhc_decode", residual, None, None, None, None, None, fn, base, scale, norm_w, post, comb, y, t, h,
+                  rms_eps, hc_eps, iters, 2.0, None, _lib.status_buffer(), _lib.stream())
+        return (y, post, comb, quant_act(y, tag + ".q")) if quant else (y, post, comb)
     if t <= MHC_CLUSTER_MAX_T and n_mix in (24, 8) and h <= 16384:
         # decode-sized batch: one launch, an 8-CTA cluster per token (DSMEM reductions); a quantised copy of the
         # few output rows, when the consumer wants one, is a second tiny launch
@@ -348,8 +433,10 @@ def mhc_pre(residual: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale:
     return (y, post, comb, QuantAct(q.view(FP8), s)) if quant else (y, post, comb)
 
 
-def mhc_post(x: torch.Tensor, residual: torch.Tensor, post: torch.Tensor, comb: torch.Tensor) -> torch.Tensor:
+def mhc_post(x, residual: torch.Tensor, post: torch.Tensor, comb: torch.Tensor) -> torch.Tensor:
     t, hc, h = residual.shape
+    if isinstance(x, LLPending):
+        x = ll_reduce(x)
     if not residual.is_cuda:
         return R.mhc_post(x, residual, post, comb.reshape(t, hc, hc)).to(cpu_act_dtype())
     out = torch.empty_like(residual)
@@ -365,6 +452,20 @@ def mhc_post_pre(x: torch.Tensor, residual: torch.Tensor, post_old: torch.Tensor
     streams and never re-read); otherwise the two ops run back to back."""
     t, hc, h = residual.shape
     n_mix = (2 + hc) * hc
+    if residual.is_cuda and t <= MHC_CLUSTER_MAX_T and hc == 4 and h % 32 == 0 and h <= 4096:
+        dev = residual.device
+        new_res = torch.empty_like(residual)
+        y = torch.empty(t, h, dtype=BF16, device=dev)
+        post = torch.empty(t, hc, dtype=F32, device=dev)
+        comb = torch.empty(t, hc * hc, dtype=F32, device=dev)
+        pend = isinstance(x, LLPending)
+        _lib.call("stk_mhc_decode", None, None if pend else x, residual, post_old, comb_old, new_res, fn, base, scale, norm_w,
+                  post, comb, y, t, h, rms_eps, hc_eps, iters, 2.0, x.ex.ctx if pend else None, _lib.status_buffer(),
+                  _lib.stream())
+        r = (y, post, comb, quant_act(y, tag + ".q")) if quant else (y, post, comb)
+        return new_res, r
+    if isinstance(x, LLPending):
+        x = ll_reduce(x)
     if (residual.is_cuda and t <= MHC_CLUSTER_MAX_T and n_mix == 24 and h <= 16384 and h % 32 == 0):
         dev = residual.device
         new_res = torch.empty_like(residual)

@@ -87,9 +87,11 @@ def router(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, scori
 
 
 def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, ew: ExpertWeights, limit: float,
-                shared: Optional[torch.Tensor] = None, total_experts: int = 0, shared_ready=None) -> torch.Tensor:
+                shared: Optional[torch.Tensor] = None, total_experts: int = 0, shared_ready=None, ll=None):
     """x [T, H] bf16 -> sum_k w_k * expert_k(x) (+ shared) as bf16 [T, H]; experts that are not local add nothing.
-    shared_ready: CUDA event after which `shared` (computed on another stream) may be read."""
+    shared_ready: CUDA event after which `shared` (computed on another stream) may be read.
+    ll: an `LLExchange`; this rank's sum is pushed into the folded all-reduce by the combine kernel and an
+    `LLPending` is returned (GPU, NVFP4 experts only)."""
     t, h = x.shape
     k = ids.shape[1]
     if not x.is_cuda or not ew.is_fp4:
@@ -135,8 +137,12 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, ew: E
                       ew.num_local, k, act, n_pairs, h, inter, float(limit), None, 0, st)
             _lib.call("stk_moe_expert_fc2", act, ew.w2, ew.s2, ew.g2, sorted_e, offsets, ew.num_local, y, n_pairs, h,
                       inter, None, 0, st)
-    out = torch.empty(t, h, dtype=BF16, device=dev)
     if shared_ready is not None:
         torch.cuda.current_stream().wait_event(shared_ready)
-    _lib.call("stk_moe_combine", y, weights, pair_row, shared, out, t, h, k, st)
+    if ll is not None:
+        from .functional import LLPending
+        _lib.call("stk_moe_combine", y, weights, pair_row, shared, None, t, h, k, ll.ctx, st)
+        return LLPending(ll, t, h, dev)
+    out = torch.empty(t, h, dtype=BF16, device=dev)
+    _lib.call("stk_moe_combine", y, weights, pair_row, shared, out, t, h, k, None, st)
     return out

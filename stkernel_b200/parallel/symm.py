@@ -19,7 +19,38 @@ from ..ops import _lib
 _MB = 1 << 20
 
 
-def region_layout(world: int, oneshot_bytes: int, twoshot_bytes: int, gemm_bytes: int = 2 * _MB) -> dict:
+class LLExchange:
+    """Receive slots + epoch counters of the all-reduce that is folded into its producer and consumer kernels
+    (csrc/symm.cuh, `LLAr`): a row-parallel layer's kernel stores its partial result into every rank's slot, the
+    next kernel adds the ranks.  `ctx` is the descriptor the kernels take by value.
+
+    `words` = capacity per source rank in 8-byte words (two bf16 values each): rows x hidden / 2."""
+
+    def __init__(self, bases: List[int], counters: torch.Tensor, words: int, rank: int, world: int,
+                 spin_budget: int = 2_000_000, keep=None):
+        L = _lib.lib()
+        self.ctx = (ctypes.c_ubyte * L.stk_ll_ctx_size())()
+        arr = (ctypes.c_longlong * world)(*bases)
+        rc = L.stk_ll_ctx_fill(self.ctx, arr, ctypes.c_void_p(counters.data_ptr()), words, rank, world, spin_budget)
+        if rc != 0:
+            raise RuntimeError(f"folded all-reduce context rejected ({rc})")
+        self.words, self.rank, self.world = words, rank, world
+        self.counters = counters
+        self._keep = keep
+
+    @staticmethod
+    def loopback(device, words: int) -> "LLExchange":
+        """A one-rank exchange over local memory: the same kernels and protocol with nothing to add (tests, and the
+        single-GPU stand-in for one rank of a group)."""
+        buf = torch.zeros(2 * words, dtype=torch.int64, device=device)
+        return LLExchange([buf.data_ptr()], torch.zeros(2, dtype=torch.int32, device=device), words, 0, 1, keep=buf)
+
+    def fits(self, t: int, h: int) -> bool:
+        return h % 2 == 0 and t * h // 2 <= self.words
+
+
+def region_layout(world: int, oneshot_bytes: int, twoshot_bytes: int, gemm_bytes: int = 2 * _MB,
+                  ll_words: int = 0) -> dict:
     """Byte offsets of the symmetric region (identical on every rank)."""
     off = 0
     lay = {}
@@ -40,6 +71,10 @@ def region_layout(world: int, oneshot_bytes: int, twoshot_bytes: int, gemm_bytes
     lay["off_gemm"] = off
     lay["gemm_bytes"] = gemm_bytes
     off += 2 * world * gemm_bytes
+    off = (off + 255) // 256 * 256
+    lay["off_ll"] = off
+    lay["ll_words"] = ll_words
+    off += 2 * world * ll_words * 8
     lay["off_user"] = (off + 255) // 256 * 256
     lay["oneshot_bytes"] = oneshot_bytes
     lay["twoshot_bytes"] = twoshot_bytes
@@ -88,13 +123,15 @@ class SymmetricAllReduce:
     ONESHOT_BLOCKS = 8
     TWOSHOT_BLOCKS = 128
 
+    LL_ROWS, LL_HIDDEN = 64, 8192            # the folded all-reduce holds up to 64 rows of 8192 values per rank
+
     def __init__(self, comm, max_bytes: int = 64 * _MB, oneshot_bytes: int = 2 * _MB, spin_budget: int = 4_000_000,
                  user_bytes: int = 0):
         self.comm = comm
         self.world = comm.world_size
         if self.world > 8:
             raise RuntimeError("symmetric all-reduce supports at most 8 ranks")
-        self.layout = region_layout(self.world, oneshot_bytes, max_bytes)
+        self.layout = region_layout(self.world, oneshot_bytes, max_bytes, ll_words=self.LL_ROWS * self.LL_HIDDEN // 2)
         self.heap = SymmetricHeap(comm, self.layout["off_user"] + user_bytes)
         L = _lib.lib()
         self.ctx = (ctypes.c_ubyte * L.stk_symm_ctx_size())()
@@ -110,6 +147,9 @@ class SymmetricAllReduce:
         self.enabled = True
         self.ag_capacity = (user_bytes // 2) // 256 * 256        # two gathered-activation buffers, used alternately
         self._ag_calls = 0
+        self.ll_counters = torch.zeros(2, dtype=torch.int32, device=comm.device)
+        self.ll = LLExchange([b + lay["off_ll"] for b in self.heap.bases], self.ll_counters, lay["ll_words"], comm.rank,
+                             self.world, spin_budget=spin_budget)
         comm.barrier()
 
     def eligible(self, x: torch.Tensor) -> bool:
@@ -195,6 +235,12 @@ class SymmetricAllReduce:
         _lib.call("stk_gemm_gated", weight, k, _ct.c_void_p(self.heap.local + off), k, out, out.stride(0), t, n, k, 0, 0,
                   None, 0, None, 0, st, _lib.sm_count(), self.ctx, rows, _lib.stream())
         return out
+
+    def ll_exchange(self, t: int, h: int) -> Optional[LLExchange]:
+        """The folded all-reduce for a [t, h] activation, or None when this path is off or the slots are too small."""
+        if not self.enabled or not self.ll.fits(t, h):
+            return None
+        return self.ll
 
     def disable(self, reason: str) -> None:
         self.enabled = False

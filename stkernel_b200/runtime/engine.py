@@ -266,6 +266,10 @@ class Engine:
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
         self._h_status: Optional[torch.Tensor] = None
+        # Optional host hook (request, device-drafted tokens) -> tokens to verify next step: benchmarks replace the
+        # drafter's proposals by a replayed sequence to exercise the accept path at a chosen acceptance rate (the
+        # draft block still runs on the device, so the step cost is the real one).
+        self.draft_override = None
 
     # ---- public API ------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None) -> int:
@@ -598,6 +602,8 @@ class Engine:
                     break
             r.num_computed = base + a + 1
             r.drafts = dr_h[si * n_spec:(si + 1) * n_spec]
+            if self.draft_override is not None and not r.finished:
+                r.drafts = list(self.draft_override(r, r.drafts))[:n_spec]
             si += 1
         self._offer_prefixes(seqs)
         self.metrics.num_requests_running = self.sched.num_running
@@ -624,6 +630,19 @@ class Engine:
         return g
 
 
+_CAPTURE_STREAMS: Dict[int, "torch.cuda.Stream"] = {}
+
+
+def _capture_stream(device) -> "torch.cuda.Stream":
+    """The stream decode steps are captured on: high priority, so that in the replayed graph the kernels of the
+    step's critical chain are scheduled ahead of the side branches (which the model runs on a default-priority
+    stream) whenever both have thread blocks waiting for an SM."""
+    idx = torch.device(device).index or 0
+    if idx not in _CAPTURE_STREAMS:
+        _CAPTURE_STREAMS[idx] = torch.cuda.Stream(device, priority=-1)
+    return _CAPTURE_STREAMS[idx]
+
+
 class SpecGraph:
     """A captured speculative pure-decode step: every request verifies 1 + N rows and drafts its next block."""
 
@@ -638,7 +657,7 @@ class SpecGraph:
         torch.cuda.synchronize()
         before = _lib.launch_count
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        with torch.cuda.graph(self.graph, stream=_capture_stream(eng.device)):
             self.out = eng._spec_device(t, n_req, ns, nb, rows_bucket)
         self.launches_per_replay = _lib.launch_count - before
 
@@ -666,7 +685,7 @@ class DecodeGraph:
         from ..ops import _lib
         before = _lib.launch_count
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        with torch.cuda.graph(self.graph, stream=_capture_stream(eng.device)):
             self.out = eng._run_model(bucket, bucket, bucket, rows_bucket, identity_rows=True)
         self.launches_per_replay = _lib.launch_count - before
 

@@ -85,7 +85,7 @@ def kernel_self_check(device="cuda:0") -> Dict[str, float]:
 
     torch.cuda.synchronize(dev)
     _lib.check_status()
-    limits = {"gemm_bf16_t64": 1e-2, "skinny_bf16_t1": 1e-2, "gemm_fp8_t64": 2e-3, "mhc_pre_y": 5e-3, "mhc_pre_comb": 2e-3,
+    limits = {"gemm_bf16_t64": 1e-2, "skinny_bf16_t1": 1e-2, "gemm_fp8_t64": 6e-3, "mhc_pre_y": 5e-3, "mhc_pre_comb": 2e-3,
               "mhc_post": 5e-3, "sparse_mla": 1e-2, "moe_nvfp4": 1.5e-2}
     bad = {n: e for n, e in res.items() if not e <= limits[n]}
     assert not bad, f"kernel self-check failed: {bad}"
