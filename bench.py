@@ -39,7 +39,8 @@ def reference_arm(args) -> None:
     # inside a Docker image; it has no setup.py/pyproject and cannot be installed or run here.
     print(json.dumps({"impl": "reference", "unavailable":
                       "reference is not installable (no setup.py/pyproject; it is an overlay on a closed "
-                      "vLLM Docker image whose engine and kernels are not in the source tree)"}))
+                      "vLLM Docker image whose engine and kernels are not in the source tree); its four "
+                      "self-contained Triton kernels are timed against ours by `python -m stkernel_b200.bench.ref_ops`"}))
 
 
 class ClockSampler:

@@ -126,7 +126,12 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=200)
     ap.add_argument("--sets", type=int, default=100)
     ap.add_argument("--no-graph", action="store_true")
-    a = ap.parse_args()
+    ap.add_argument("--impl", default="ours", help="'reference': time the reference's own shipped Triton kernels against "
+                                                   "this library's kernels for the same ops (see bench/ref_ops.py)")
+    a, rest = ap.parse_known_args()
+    if a.impl == "reference":
+        from .ref_ops import main as ref_main
+        raise SystemExit(ref_main(rest))
     print(json.dumps(run(a.op, a.T, a.H, a.iters, a.sets, not a.no_graph)))
 
 

@@ -183,6 +183,8 @@ class ParallelConfig:
     indexer_sp: bool = True      # sequence-parallel indexer scoring for prefill chunks
     indexer_sp_min_rows: int = 256
     fused_collectives: bool = True   # False => NCCL-after-GEMM baseline paths
+    eplb_redundant: int = 0          # spare physical expert slots per layer for replicas of hot experts (EPLB)
+    eplb_record: bool = False        # count routed tokens per logical expert and layer (input of a rebalance)
     use_multimem: bool = False       # NVLS multimem loads/stores in the all-reduce
 
     def validate(self) -> None:
@@ -191,6 +193,8 @@ class ParallelConfig:
                 raise ConfigError(f"{name} must be >= 1")
         if self.ep_size not in (1, self.tp_size):
             raise ConfigError("ep_size must be 1 or equal tp_size")
+        if self.eplb_redundant < 0 or self.eplb_redundant % self.tp_size:
+            raise ConfigError("eplb_redundant must be a non-negative multiple of tp_size")
 
 
 @dataclass(frozen=True)

@@ -53,6 +53,15 @@ struct MdArgs {
   int prep_q;                  // 1: q arrives raw: per-head weightless RMSNorm + RoPE here
   long long swa_slots_n, comp_slots_n;   // extents for the index guard
   int* status;
+  // Insert of the step's own latent rows (pure decode: every request contributes one token, so no token of the step
+  // attends to another token's new row): the warp that meets the token's own slot in the window list builds the cached
+  // row from the raw kv projection itself -- RMSNorm, RoPE, UE8M0 block quantisation, exactly as the stand-alone insert
+  // -- writes it to the cache and attends to it from registers.  No insert launch in front of the attention.
+  const __nv_bfloat16* kv_new;     // [T, 512] raw kv rows, or nullptr
+  long long kv_ld;
+  const __nv_bfloat16* kv_norm_w;  // [512]
+  const int64_t* cur_slot;         // [T] slot of each token's own row in the window cache (-1: none)
+  uint8_t* swa_write;              // the window cache, writable
 };
 
 __device__ __forceinline__ __half2 h2_from_raw(__half2_raw r) { return *reinterpret_cast<__half2*>(&r); }
@@ -140,6 +149,8 @@ mla_decode_split_kernel(const MdArgs a) {
   uint32_t rraw[kMdBatch];
   uint32_t sbyte[kMdBatch];
   bool valid[kMdBatch];
+  const long long own_slot = a.kv_new != nullptr ? __ldg(a.cur_slot + t) : -1;
+  int own_j = -1;
 #pragma unroll
   for (int j = 0; j < kMdBatch; ++j) {
     const int v = v0 + j;
@@ -153,7 +164,9 @@ mla_decode_split_kernel(const MdArgs a) {
     kraw[j] = make_uint4(0, 0, 0, 0);
     rraw[j] = 0;
     sbyte[j] = 127;
-    if (valid[j]) {
+    if (valid[j] && in_swa[j] && own_slot >= 0 && static_cast<long long>(slot[j]) == own_slot) {
+      own_j = j;                          // built below, once, outside this unrolled loop
+    } else if (valid[j]) {
       const MdCache& c = in_swa[j] ? a.swa : a.comp;
       const uint8_t* page = c.base + static_cast<long long>(slot[j] >> 6) * c.page_stride;
       const uint8_t* drow = page + static_cast<long long>(slot[j] & 63) * kMdRowData;
@@ -163,6 +176,80 @@ mla_decode_split_kernel(const MdArgs a) {
       }
       rraw[j] = __ldg(reinterpret_cast<const uint32_t*>(drow + kMdNope + lane * 4));
     }
+  }
+  if (own_j >= 0) {
+    uint4 own_k;
+    uint32_t own_r, own_sb = 127;
+      // ---- this token's own row: built here, stored, used from registers ----
+      const __nv_bfloat16* src = a.kv_new + t * a.kv_ld;
+      float f[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) f[i] = 0.f;
+      float wn[16];
+      if (lane < 28) {
+        const uint4 x0 = *reinterpret_cast<const uint4*>(src + lane * 16), x1 = *reinterpret_cast<const uint4*>(src + lane * 16 + 8);
+        const uint4 w0 = __ldg(reinterpret_cast<const uint4*>(a.kv_norm_w + lane * 16));
+        const uint4 w1 = __ldg(reinterpret_cast<const uint4*>(a.kv_norm_w + lane * 16 + 8));
+        const uint32_t xw[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+        const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float2 p = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&xw[i]));
+          const float2 q2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ww[i]));
+          f[2 * i] = p.x; f[2 * i + 1] = p.y;
+          wn[2 * i] = q2.x; wn[2 * i + 1] = q2.y;
+        }
+      }
+      float2 rp = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + kMdNope + 2 * lane));
+      const float2 rw = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(a.kv_norm_w + kMdNope + 2 * lane));
+      float ss = fmaf(rp.x, rp.x, rp.y * rp.y);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) ss = fmaf(f[i], f[i], ss);
+      const float nr = rsqrtf(warp_sum(ss) / static_cast<float>(kMdD) + a.eps);
+      float amax = 0.f;
+      if (lane < 28) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          f[i] = bf16_to_f(__float2bfloat16(f[i] * nr * wn[i]));
+          amax = fmaxf(amax, fabsf(f[i]));
+        }
+      }
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));       // a quantisation block = 64 dims = 4 lanes
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      uint8_t sb;
+      const float sc = ue8m0_scale(amax, &sb);
+      const float inv_sc = 1.f / sc;
+      uint32_t codes[4] = {0, 0, 0, 0};
+      if (lane < 28) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) codes[i >> 2] |= static_cast<uint32_t>(f_to_fp8(f[i] * inv_sc)) << (8 * (i & 3));
+        own_sb = sb;
+      }
+      own_k = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+      {
+        // RoPE of the pair at the token's position (rounded to bf16 after the norm and again after the rotation, as the
+        // separate norm and insert kernels store them)
+        const float x = bf16_to_f(__float2bfloat16(rp.x * nr * rw.x)), y = bf16_to_f(__float2bfloat16(rp.y * nr * rw.y));
+        float sn2, cs2;
+        sincosf(static_cast<float>(__ldg(a.positions + t)) * __ldg(a.inv_freq + lane), &sn2, &cs2);
+        own_r = pack2(x * cs2 - y * sn2, x * sn2 + y * cs2);
+      }
+      // one CTA per token stores the row (every head block and split that meets the slot computes the same bytes)
+      if (hb == 0) {
+        uint8_t* page = a.swa_write + static_cast<long long>(own_slot >> 6) * a.swa.page_stride;
+        uint8_t* drow = page + static_cast<long long>(own_slot & 63) * kMdRowData;
+        uint8_t* srow = page + 64LL * kMdRowData + (own_slot & 63) * 8;
+        if (lane < 28) {
+          *reinterpret_cast<uint4*>(drow + lane * 16) = own_k;
+          if ((lane & 3) == 0) srow[lane >> 2] = sb;
+        } else if (lane == 28) {
+          srow[7] = 0;
+        }
+        *reinterpret_cast<uint32_t*>(drow + kMdNope + lane * 4) = own_r;
+      }
+#pragma unroll
+    for (int j = 0; j < kMdBatch; ++j)
+      if (j == own_j) { kraw[j] = own_k; rraw[j] = own_r; sbyte[j] = own_sb; }
   }
   // a CTA none of whose 32 rows exists only marks its partials empty
   const bool cta_any = (s * 32 < n_swa) || (s * 32 + 32 > W && s * 32 < W + n_top);
@@ -333,13 +420,23 @@ mla_decode_merge_kernel(const float* __restrict__ partial, const float* __restri
   for (int s = 0; s < S; ++s) M = fmaxf(M, s_m[s]);
   float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
   float den = 0.f;
-  for (int s = sg; s < S; s += 4) {
-    const float m = s_m[s];
-    if (m != -INFINITY) {
-      const float w = __expf(m - M);
-      den = fmaf(w, s_l[s], den);
-      const float4 v = *reinterpret_cast<const float4*>(base + s * sstride + d);
-      o.x = fmaf(v.x, w, o.x); o.y = fmaf(v.y, w, o.y); o.z = fmaf(v.z, w, o.z); o.w = fmaf(v.w, w, o.w);
+  // this thread's splits are sg, sg + 4, ...: eight rows are requested before the first is used
+  for (int s0 = sg; s0 < S; s0 += 32) {
+    float w[8];
+    float4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int s = s0 + 4 * u;
+      const float m = s < S ? s_m[s] : -INFINITY;
+      w[u] = (m == -INFINITY) ? 0.f : __expf(m - M);
+      v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (w[u] != 0.f) v[u] = *reinterpret_cast<const float4*>(base + s * sstride + d);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int s = s0 + 4 * u;
+      if (w[u] != 0.f) den = fmaf(w[u], s_l[s], den);
+      o.x = fmaf(v[u].x, w[u], o.x); o.y = fmaf(v[u].y, w[u], o.y); o.z = fmaf(v[u].z, w[u], o.z); o.w = fmaf(v[u].w, w[u], o.w);
     }
   }
   *reinterpret_cast<float4*>(&s_o[sg][d]) = o;
@@ -389,7 +486,10 @@ STK_API int stk_sparse_mla_decode(const void* q, long long ldt, const void* swa_
                                   const int* topk_slots, int topk_ld, int topk_rows, const int* topk_lens, const float* sink, void* out,
                                   long long ldo, float* workspace, int S, int T, int nh, float scale, int prep_q,
                                   float eps, const int64_t* positions, const float* inv_freq, int out_inv_rope,
+                                  const void* kv_new, long long kv_ld, const void* kv_norm_w, const int64_t* cur_slot,
                                   int* status, void* stream) {
+  // kv_new != nullptr (pure decode steps only): the kernel also builds and inserts each token's own latent row from
+  // the raw kv projection (RMSNorm with kv_norm_w and eps, RoPE, UE8M0 quantisation) at cur_slot[t] of the window cache.
   if (T <= 0) return 0;
   if (nh % kMdHeads || S != (swa_rows + (topk_slots ? topk_rows : 0) + 31) / 32 || S > kMdMaxS || (ldt % 8) || (reinterpret_cast<uintptr_t>(q) & 15) || (ldo % 4) ||
       (reinterpret_cast<uintptr_t>(workspace) & 15) || (reinterpret_cast<uintptr_t>(out) & 7))
@@ -407,6 +507,14 @@ STK_API int stk_sparse_mla_decode(const void* q, long long ldt, const void* swa_
   a.partial = workspace; a.nh = nh; a.S = S; a.scale = scale; a.eps = eps; a.prep_q = prep_q;
   a.swa_slots_n = swa_slots_n; a.comp_slots_n = comp_cache ? comp_slots_n : swa_slots_n;
   a.status = status;
+  if (kv_new != nullptr) {
+    if (kv_norm_w == nullptr || cur_slot == nullptr || positions == nullptr || inv_freq == nullptr || (kv_ld % 8) ||
+        (reinterpret_cast<uintptr_t>(kv_new) & 15) || (reinterpret_cast<uintptr_t>(kv_norm_w) & 15))
+      return -5;
+    a.kv_new = (const __nv_bfloat16*)kv_new; a.kv_ld = kv_ld; a.kv_norm_w = (const __nv_bfloat16*)kv_norm_w;
+    a.cur_slot = cur_slot;
+    a.swa_write = (uint8_t*)const_cast<void*>(swa_cache);
+  }
   const size_t smem = 16 * 4 * kMdP * sizeof(float);
   static bool configured = false;
   if (!configured) {

@@ -9,8 +9,17 @@
 //   markov_topk_bias  DSpark first-order Markov head on the base-logit top-k:
 //                     out[idx] = base[idx] + W2[idx] . embed, -inf elsewhere
 //                     (overlay/dspark_v2.py:184-236).
+//   sample_threshold  per-row logit threshold of top-k and/or top-p (nucleus) truncation; the arg-max kernel then
+//                     skips logits below it, so truncated sampling keeps the same (seed, position, vocab id) noise
+//                     and drafts stay coupled with their verification.
+//   argmax_exchange   tensor-parallel LM head without gathering logits: every rank takes the noisy arg-max of its own
+//                     vocabulary shard (noise keyed by the global vocab id), pushes (value, id, status) to all ranks
+//                     and picks the winner of the `world` candidates -- 24 bytes per row and rank over NVLink.
 #define STK_PDL_CLASS 256      // bit of this file's kernels in the PDL mask (STK_PDL, stk_set_pdl_mask)
+#include <string.h>
+
 #include "common.cuh"
+#include "symm.cuh"
 
 namespace stk {
 
@@ -34,6 +43,11 @@ __device__ __forceinline__ float gumbel_from_key(uint32_t key, uint32_t v) {
   return -logf(-logf(u));
 }
 
+__device__ __forceinline__ uint32_t ordered_key_f(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
 template <typename T> __device__ __forceinline__ float ld_logit(const T* p, long long i);
 template <> __device__ __forceinline__ float ld_logit<float>(const float* p, long long i) { return p[i]; }
 template <> __device__ __forceinline__ float ld_logit<__nv_bfloat16>(const __nv_bfloat16* p, long long i) {
@@ -46,7 +60,10 @@ __global__ void __launch_bounds__(256)
 gumbel_argmax_partial_kernel(const T* __restrict__ logits, long long ld, const float* __restrict__ temperature,
                              const int64_t* __restrict__ seed, const int64_t* __restrict__ pos,
                              const int* __restrict__ row_group, int pos_stride, float* __restrict__ part_val,
-                             int* __restrict__ part_idx, float* __restrict__ processed, long long ldp, int V) {
+                             int* __restrict__ part_idx, float* __restrict__ processed, long long ldp, int V,
+                             int v_offset, const uint32_t* __restrict__ thr_keys) {
+  // v_offset: global vocabulary id of column 0 (vocabulary-sharded logits): noise and the reported id use global ids.
+  // thr_keys: per-row ordered key below which a logit is outside the top-k / top-p set (nullptr: no truncation).
   pdl_wait();
   pdl_trigger();
   __shared__ float sv[8];
@@ -63,11 +80,15 @@ gumbel_argmax_partial_kernel(const T* __restrict__ logits, long long ld, const f
   const int v0 = blockIdx.y * chunk, v1 = min(V, v0 + chunk);
   float best = -INFINITY;
   int best_i = 0x7fffffff;
+  const uint32_t thr = thr_keys ? thr_keys[row] : 0u;
   for (int v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
-    const float l = ld_logit<T>(logits, row * ld + v) * inv_t;
+    const float raw = ld_logit<T>(logits, row * ld + v);
+    float l = raw * inv_t;
+    if (thr_keys != nullptr && ordered_key_f(raw) < thr) l = -INFINITY;
     if (processed) processed[row * ldp + v] = l;
-    const float x = greedy ? l : l + gumbel_from_key(key, static_cast<uint32_t>(v));
-    if (x > best || (x == best && v < best_i)) { best = x; best_i = v; }
+    const int gv = v + v_offset;
+    const float x = greedy ? l : l + gumbel_from_key(key, static_cast<uint32_t>(gv));
+    if (x > best || (x == best && gv < best_i)) { best = x; best_i = gv; }
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
@@ -100,6 +121,156 @@ __global__ void gumbel_argmax_final_kernel(const float* __restrict__ part_val, c
     if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
   }
   out[row] = best_i == 0x7fffffff ? 0 : best_i;
+}
+
+// ---- top-k / top-p threshold ------------------------------------------------------------------------------------
+// One CTA of 1024 threads per row.  Works on the ordered keys of the raw logits (truncation does not depend on the
+// temperature's sign, and the mass of top-p is taken at the row's temperature as the samplers of the reference's engine
+// do: softmax(logits / T)).  Radix select, 8 bits per pass:
+//   top-k: walk the histogram of counts from the top until k entries are covered -> key of the k-th largest logit;
+//   top-p: among the survivors of top-k, walk the histogram of probability mass until p of the total is covered.
+// Ties at the threshold are kept (the set may be slightly larger than k / the minimal nucleus, never smaller).
+// thr_out[row] = max(key_k, key_p): a logit is inside the set iff its key >= thr_out[row].
+template <typename T>
+__global__ void __launch_bounds__(1024)
+sample_threshold_kernel(const T* __restrict__ logits, long long ld, const float* __restrict__ temperature,
+                        const int* __restrict__ row_group, const int* __restrict__ top_k,
+                        const float* __restrict__ top_p, uint32_t* __restrict__ thr_out, int V) {
+  __shared__ int hist[256];
+  __shared__ float mass[256];
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_rem;
+  __shared__ float s_mrem;
+  __shared__ float s_red[32];
+  pdl_wait();
+  pdl_trigger();
+  const int row = blockIdx.x;
+  const int g = row_group ? row_group[row] : row;
+  const T* lrow = logits + row * ld;
+  const int k = top_k ? top_k[g] : 0;
+  const float p = top_p ? top_p[g] : 1.f;
+  const float temp = temperature[g];
+  uint32_t key_k = 0u;
+  if (k > 0 && k < V) {
+    if (threadIdx.x == 0) { s_prefix = 0; s_rem = k; }
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+      __syncthreads();
+      const uint32_t prefix = s_prefix;
+      const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+      for (int v = threadIdx.x; v < V; v += blockDim.x) {
+        const uint32_t key = ordered_key_f(ld_logit<T>(lrow, v));
+        if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 0xff], 1);
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        int rem = s_rem, b = 255;
+        for (; b > 0; --b) {
+          if (hist[b] >= rem) break;
+          rem -= hist[b];
+        }
+        s_prefix = prefix | (static_cast<uint32_t>(b) << shift);
+        s_rem = rem;
+      }
+      __syncthreads();
+    }
+    key_k = s_prefix;
+  }
+  uint32_t key_p = 0u;
+  if (p < 1.f && temp > 0.f) {
+    const float inv_t = 1.f / temp;
+    // row maximum and the total mass of the top-k survivors
+    float mx = -INFINITY;
+    for (int v = threadIdx.x; v < V; v += blockDim.x) mx = fmaxf(mx, ld_logit<T>(lrow, v));
+    mx = block_max(mx, s_red);
+    __syncthreads();
+    float z = 0.f;
+    for (int v = threadIdx.x; v < V; v += blockDim.x) {
+      const float l = ld_logit<T>(lrow, v);
+      if (ordered_key_f(l) >= key_k) z += __expf((l - mx) * inv_t);
+    }
+    z = block_sum(z, s_red);
+    __syncthreads();
+    if (threadIdx.x == 0) { s_prefix = 0; s_mrem = p * z; }
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      for (int i = threadIdx.x; i < 256; i += blockDim.x) mass[i] = 0.f;
+      __syncthreads();
+      const uint32_t prefix = s_prefix;
+      const uint32_t mask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+      for (int v = threadIdx.x; v < V; v += blockDim.x) {
+        const float l = ld_logit<T>(lrow, v);
+        const uint32_t key = ordered_key_f(l);
+        if (key >= key_k && (key & mask) == prefix) atomicAdd(&mass[(key >> shift) & 0xff], __expf((l - mx) * inv_t));
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float rem = s_mrem;
+        int b = 255;
+        for (; b > 0; --b) {
+          if (mass[b] >= rem) break;
+          rem -= mass[b];
+        }
+        s_prefix = prefix | (static_cast<uint32_t>(b) << shift);
+        s_mrem = rem;
+      }
+      __syncthreads();
+    }
+    key_p = s_prefix;
+  }
+  if (threadIdx.x == 0) thr_out[row] = key_k > key_p ? key_k : key_p;
+}
+
+// ---- arg-max across vocabulary shards ---------------------------------------------------------------------------
+// One CTA, thread = row.  Reduces this rank's chunk candidates, pushes (value, global id, status word) into every
+// rank's slot of the folded all-reduce exchange (three words per row), waits (bounded) for all ranks and keeps the
+// largest value (ties: lowest id) -- the same token on every rank.  agreed_status = the largest status code any rank
+// reported, so that every rank learns of a failed wait or a bad index on any of them with the step's tokens.
+__global__ void __launch_bounds__(256)
+argmax_exchange_kernel(const LLAr ll, const float* __restrict__ part_val, const int* __restrict__ part_idx, int chunks,
+                       int64_t* __restrict__ out, int rows, const int* __restrict__ status_in, int* __restrict__ agreed_status,
+                       int* status) {
+  pdl_wait();
+  pdl_trigger();
+  const uint32_t e = ll_push_epoch(ll);
+  const int row = threadIdx.x;
+  if (row < rows) {
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int c = 0; c < chunks; ++c) {
+      const float v = part_val[row * chunks + c];
+      const int i = part_idx[row * chunks + c];
+      if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+    }
+    const uint32_t st = status_in ? static_cast<uint32_t>(status_in[0]) : 0u;
+    for (int p = 0; p < ll.world; ++p) {
+      const int peer = (ll.rank + p) % ll.world;
+      ll_store(ll, e, peer, 3LL * row, __float_as_uint(best));
+      ll_store(ll, e, peer, 3LL * row + 1, static_cast<uint32_t>(best_i));
+      ll_store(ll, e, peer, 3LL * row + 2, st);
+    }
+    float win = -INFINITY;
+    int win_i = 0x7fffffff;
+    uint32_t worst = 0;
+    for (int r = 0; r < ll.world; ++r) {
+      uint32_t dv, di, ds;
+      ll_wait_word(ll, e, r, 3LL * row, dv, status);
+      ll_wait_word(ll, e, r, 3LL * row + 1, di, status);
+      ll_wait_word(ll, e, r, 3LL * row + 2, ds, status);
+      const float v = __uint_as_float(dv);
+      const int i = static_cast<int>(di);
+      if (v > win || (v == win && i < win_i)) { win = v; win_i = i; }
+      worst = ds > worst ? ds : worst;
+    }
+    out[row] = win_i == 0x7fffffff ? 0 : win_i;
+    if (row == 0 && agreed_status != nullptr) agreed_status[0] = static_cast<int>(worst);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ll_push_done(ll, e);
+    ll_read_done(ll, e);
+  }
 }
 
 // verifier [B, N+1], draft [B, N] -> n_acc [B], emitted [B, N+1] (-1 past the first mismatch)
@@ -311,22 +482,47 @@ markov_chain_kernel(const int* __restrict__ cand_idx, const float* __restrict__ 
 using namespace stk;
 
 // part_val/part_idx: scratch of rows*chunks entries each.  row_group may be null (row == request).
+// top_k (int per request, <= 0: off) / top_p (float per request, >= 1: off) / thr_scratch (uint32 per row): all three
+// nullptr for untruncated sampling.  v_offset: global vocabulary id of logits column 0.  ll_ctx != nullptr: the logits
+// are one rank's vocabulary shard; the winner is agreed on across the ranks of the exchange (at most 256 rows, no
+// truncation) and agreed_status receives the largest status code of any rank (status_in = this rank's status word).
 STK_API int stk_gumbel_argmax(const void* logits, long long ld, int logits_bf16, const float* temperature,
                               const int64_t* seed, const int64_t* pos, const int* row_group, int pos_stride,
                               float* part_val, int* part_idx, int chunks, int64_t* out, float* processed,
-                              long long ldp, int rows, int V, void* stream) {
+                              long long ldp, int rows, int V, const int* top_k, const float* top_p,
+                              void* thr_scratch, int v_offset, const void* ll_ctx, const int* status_in,
+                              int* agreed_status, int* status, void* stream) {
   if (rows <= 0) return 0;
   dim3 grid(rows, chunks);
   cudaStream_t st = (cudaStream_t)stream;
+  uint32_t* thr = nullptr;
+  if (top_k != nullptr || top_p != nullptr) {
+    if (thr_scratch == nullptr || ll_ctx != nullptr) return -1;
+    thr = reinterpret_cast<uint32_t*>(thr_scratch);
+    if (logits_bf16)
+      launch_pdl(sample_threshold_kernel<__nv_bfloat16>, dim3(rows), dim3(1024), 0, st, (const __nv_bfloat16*)logits, ld,
+                 temperature, row_group, top_k, top_p, thr, V);
+    else
+      launch_pdl(sample_threshold_kernel<float>, dim3(rows), dim3(1024), 0, st, (const float*)logits, ld, temperature,
+                 row_group, top_k, top_p, thr, V);
+  }
   if (logits_bf16)
     launch_pdl(gumbel_argmax_partial_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)logits, ld, temperature,
                                                                       seed, pos, row_group, pos_stride, part_val,
-                                                                      part_idx, processed, ldp, V);
+                                                                      part_idx, processed, ldp, V, v_offset, (const uint32_t*)thr);
   else
     launch_pdl(gumbel_argmax_partial_kernel<float>, dim3(grid), dim3(256), 0, st, (const float*)logits, ld, temperature, seed, pos,
                                                               row_group, pos_stride, part_val, part_idx, processed,
-                                                              ldp, V);
-  launch_pdl(gumbel_argmax_final_kernel, dim3((rows + 127) / 128), dim3(128), 0, st, part_val, part_idx, chunks, out, rows);
+                                                              ldp, V, v_offset, (const uint32_t*)thr);
+  if (ll_ctx != nullptr) {
+    LLAr ll;
+    memcpy(&ll, ll_ctx, sizeof(ll));
+    if (rows > 256 || 3LL * rows > ll.words) return -2;
+    launch_pdl(argmax_exchange_kernel, dim3(1), dim3(256), 0, st, ll, (const float*)part_val, (const int*)part_idx, chunks, out,
+               rows, status_in, agreed_status, status);
+  } else {
+    launch_pdl(gumbel_argmax_final_kernel, dim3((rows + 127) / 128), dim3(128), 0, st, part_val, part_idx, chunks, out, rows);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

@@ -252,6 +252,76 @@ STK_API int stk_symm_ag_push(const void* ctx, const void* shard, long long shard
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
+// ---- peer-memory datapath probe -----------------------------------------------------------------------------------
+// What the link rooflines divide by is measured, not assumed (the counterpart of the reference's probes/uma_datapath.cu:
+// "which buffer types work, at what bandwidth, at what small-message latency").
+//   peer_copy_kernel   16-byte loads from `src`, 16-byte stores to `dst`; either side may be a peer's region.  Block
+//                      b of a multi-peer launch serves peer b % n_peers, so one launch drives all links at once.
+//   peer_pingpong      `rounds` flag round trips between ranks `a` and `b` inside one kernel on each side (bounded
+//                      waits): device time / rounds = the 8-byte store -> remote poll -> store back -> poll latency.
+namespace stk {
+struct PeerCopyJob {
+  uint4* dst[kMaxRanks];
+  const uint4* src[kMaxRanks];
+  int n_peers;
+  long long n_vec;          // per peer
+};
+
+__global__ void __launch_bounds__(512)
+peer_copy_kernel(PeerCopyJob j) {
+  const int p = blockIdx.x % j.n_peers;
+  const int bpp = gridDim.x / j.n_peers;                 // blocks per peer
+  const int bi = blockIdx.x / j.n_peers;
+  if (bi >= bpp) return;
+  uint4* dst = j.dst[p];
+  const uint4* src = j.src[p];
+  for (long long i = static_cast<long long>(bi) * blockDim.x + threadIdx.x; i < j.n_vec; i += static_cast<long long>(bpp) * blockDim.x)
+    dst[i] = src[i];
+}
+
+__global__ void peer_pingpong_kernel(uint32_t* my_flag, uint32_t* peer_flag, int initiator, int rounds, uint32_t base,
+                                     uint32_t budget, int* status) {
+  if (threadIdx.x != 0) return;
+  for (int r = 1; r <= rounds; ++r) {
+    const uint32_t e = base + static_cast<uint32_t>(r);
+    if (initiator) {
+      st_release_sys(peer_flag, e);
+      if (!wait_flag(my_flag, e, budget, status, 900)) return;
+    } else {
+      if (!wait_flag(my_flag, e, budget, status, 901)) return;
+      st_release_sys(peer_flag, e);
+    }
+  }
+}
+
+}  // namespace stk
+using namespace stk;
+
+// dsts/srcs: n_peers device addresses each (this process's mappings); bytes per peer, a multiple of 16.
+STK_API int stk_peer_copy(const long long* dsts, const long long* srcs, int n_peers, long long bytes, int blocks_per_peer,
+                          void* stream) {
+  if (n_peers < 1 || n_peers > kMaxRanks || bytes <= 0 || bytes % 16 || blocks_per_peer < 1) return -1;
+  PeerCopyJob j;
+  memset(&j, 0, sizeof(j));
+  for (int i = 0; i < n_peers; ++i) {
+    if ((dsts[i] & 15) || (srcs[i] & 15)) return -2;
+    j.dst[i] = reinterpret_cast<uint4*>(dsts[i]);
+    j.src[i] = reinterpret_cast<const uint4*>(srcs[i]);
+  }
+  j.n_peers = n_peers;
+  j.n_vec = bytes / 16;
+  peer_copy_kernel<<<blocks_per_peer * n_peers, 512, 0, (cudaStream_t)stream>>>(j);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+STK_API int stk_peer_pingpong(void* my_flag, void* peer_flag, int initiator, int rounds, int base, int budget, int* status,
+                              void* stream) {
+  if (rounds < 1 || my_flag == nullptr || peer_flag == nullptr) return -1;
+  peer_pingpong_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((uint32_t*)my_flag, (uint32_t*)peer_flag, initiator, rounds,
+                                                         (uint32_t)base, (uint32_t)budget, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
 STK_API int stk_flag_timeout_probe(const void* flag, int epoch, int budget, int* status, void* stream) {
   flag_timeout_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((const uint32_t*)flag, (uint32_t)epoch, (uint32_t)budget,
                                                                 status);

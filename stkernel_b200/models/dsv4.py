@@ -27,6 +27,7 @@ from ..ops import moe as M
 from ..utils.spans import span
 from ..ops.functional import LinearWeight
 from ..ops.scratch import side_branch
+from ..runtime.planning import sp_gather_sizes, split_indexer_prefill_chunks
 from .dsv4_oracle import index_cache_computes
 from .weights import compressor_slots
 
@@ -113,14 +114,42 @@ class LayerWeights:
     w_sh13: Optional[LinearWeight] = None
     w_sh2: Optional[LinearWeight] = None
     experts: Optional[M.ExpertWeights] = None
+    index: int = -1                        # layer number (load recording)
+    eplb: Optional[Tuple[torch.Tensor, torch.Tensor]] = None   # (logical -> physical table, replica counts); None = identity
 
 
 def _get(src: WeightSource, name: str, shape, device) -> torch.Tensor:
     return src.get(name, tuple(shape), device)
 
 
+def build_experts(cfg: ModelConfig, src: WeightSource, prefix: str, device, tp_rank: int, tp_size: int,
+                  placement=None) -> Tuple[M.ExpertWeights, Optional[Tuple[torch.Tensor, torch.Tensor]]]:
+    """This rank's routed experts of one layer.  Without a placement rank r holds the logical experts
+    [r*E/tp, (r+1)*E/tp); with one (parallel/eplb.py) it holds the logical experts of its physical slots, and the
+    second result maps router ids to slot ids."""
+    f = f"{prefix}.ffn"
+    E, I, H = cfg.n_routed_experts, cfg.moe_intermediate_size, cfg.hidden_size
+    if placement is None or placement.is_identity:
+        e_l = E // tp_size
+        logical = list(range(tp_rank * e_l, (tp_rank + 1) * e_l))
+        start, tables = tp_rank * e_l, None
+    else:
+        logical = placement.local_logical(tp_rank)
+        start, tables = tp_rank * placement.slots_per_rank, placement.tables(device)
+    g = lambda n, s: _get(src, n, s, device)
+    packs = []
+    for e in logical:
+        w13 = torch.cat([g(f"{f}.experts.{e}.w1.weight", (I, H)), g(f"{f}.experts.{e}.w3.weight", (I, H))], 0)
+        w2 = g(f"{f}.experts.{e}.w2.weight", (H, I))
+        packs.append(M.ExpertWeights.from_master(w13[None], w2[None], cfg.expert_dtype, device, 0))
+    cat = lambda xs: torch.cat(xs, 0).contiguous() if xs[0] is not None else None
+    ew = M.ExpertWeights(cat([p.w13 for p in packs]), cat([p.w2 for p in packs]), cat([p.s13 for p in packs]),
+                         cat([p.s2 for p in packs]), cat([p.g13 for p in packs]), cat([p.g2 for p in packs]), start)
+    return ew, tables
+
+
 def build_layer(cfg: ModelConfig, src: WeightSource, prefix: str, li: int, device, tp_rank: int, tp_size: int,
-                kind: Optional[str] = None) -> LayerWeights:
+                kind: Optional[str] = None, placement=None) -> LayerWeights:
     H, D, Rd, nh, hc = cfg.hidden_size, cfg.head_dim, cfg.qk_rope_head_dim, cfg.num_attention_heads, cfg.hc_mult
     dd = cfg.dense_dtype
     kind = kind or cfg.layer_kind(li)
@@ -194,17 +223,8 @@ def build_layer(cfg: ModelConfig, src: WeightSource, prefix: str, li: int, devic
         w3 = g(f"{f}.shared_experts.w3.weight", (Is, H))[r0:r0 + isl]
         lw.w_sh13 = mk(torch.cat([w1, w3], 0))
         lw.w_sh2 = mk(g(f"{f}.shared_experts.w2.weight", (H, Is))[:, r0:r0 + isl].contiguous())
-    e_l = E // tp_size
-    e0 = tp_rank * e_l
-    w13s, w2s = [], []
-    packs = []
-    for e in range(e0, e0 + e_l):
-        w13 = torch.cat([g(f"{f}.experts.{e}.w1.weight", (I, H)), g(f"{f}.experts.{e}.w3.weight", (I, H))], 0)
-        w2 = g(f"{f}.experts.{e}.w2.weight", (H, I))
-        packs.append(M.ExpertWeights.from_master(w13[None], w2[None], cfg.expert_dtype, device, 0))
-    cat = lambda xs: torch.cat(xs, 0).contiguous() if xs[0] is not None else None
-    lw.experts = M.ExpertWeights(cat([p.w13 for p in packs]), cat([p.w2 for p in packs]), cat([p.s13 for p in packs]),
-                                 cat([p.s2 for p in packs]), cat([p.g13 for p in packs]), cat([p.g2 for p in packs]), e0)
+    lw.experts, lw.eplb = build_experts(cfg, src, prefix, device, tp_rank, tp_size, placement)
+    lw.index = li
     return lw
 
 
@@ -219,14 +239,17 @@ class ModelWeights:
 
 
 def build_model_weights(cfg: ModelConfig, src: WeightSource, device, tp_rank: int = 0, tp_size: int = 1,
-                        head_fp8: bool = False) -> ModelWeights:
+                        head_fp8: bool = False, placements=None) -> ModelWeights:
+    """placements: optional list of per-layer expert placements (parallel/eplb.py), None entries = identity."""
     H, V, hc = cfg.hidden_size, cfg.vocab_size, cfg.hc_mult
     g = lambda n, s: _get(src, n, s, device)
     vl = (V + tp_size - 1) // tp_size
     v0 = tp_rank * vl
     head = g("head.weight", (V, H))[v0:min(V, v0 + vl)]
     head_w = LinearWeight.from_master(head, "fp8", device) if head_fp8 else LinearWeight(head.to(BF16).contiguous())
-    layers = [build_layer(cfg, src, f"layers.{li}", li, device, tp_rank, tp_size) for li in range(cfg.num_hidden_layers)]
+    layers = [build_layer(cfg, src, f"layers.{li}", li, device, tp_rank, tp_size,
+                          placement=placements[li] if placements is not None else None)
+              for li in range(cfg.num_hidden_layers)]
     return ModelWeights(
         embed=g("embed.weight", (V, H)).to(BF16).contiguous(), head=head_w, norm=g("norm.weight", (H,)).to(BF16),
         hc_head=(g("hc_head_fn", (hc, hc * H)).to(F32).contiguous(), g("hc_head_base", (hc,)).to(F32),
@@ -250,6 +273,7 @@ class StepMeta:
     swa_lens: torch.Tensor         # [T] int32
     max_comp_rows: int             # upper bound of compressed rows any request holds (c4 group)
     max_c128_rows: int = 0
+    pure_decode: bool = False      # every request contributes exactly one token (no token attends to another new row)
 
 
 class DSV4Model:
@@ -266,12 +290,15 @@ class DSV4Model:
         self.aux_layers: Tuple[int, ...] = ()
         self.aux_out: List[torch.Tensor] = []
         self.stats = {"sp_steps": 0, "mla_token_parallel_calls": 0}     # which large-step paths ran (tests, debugging)
+        self.load_recorder = None           # parallel.eplb.LoadRecorder when expert load is being recorded
         # Sequence-parallel indexer: with TP the indexer weights are replicated, so each rank scores only its
         # share of a large step's rows and the top-k rows are all-gathered (overlay/attention.py
         # `_indexer_sp_owned_ranges` in the reference; here every row of a step is split evenly, which is exact
         # because scoring and top-k are independent per row).
         self.indexer_sp = tp_size > 1 and comm is not None
         self.indexer_sp_min_rows = int(os.environ.get("STK_INDEXER_SP_MIN_ROWS", "8"))
+        # fp32 indexer scores of one scoring call stay below this many bytes (query sub-chunks at long contexts)
+        self.indexer_logits_bytes = int(os.environ.get("STK_INDEXER_MAX_LOGITS_MB", "512")) << 20
         # Token-parallel sparse attention: every rank holds the whole latent KV cache, and gathering a token's
         # top-k rows costs the same for 8 heads as for 64, so with heads split over the ranks the gather work is
         # replicated.  Large steps instead exchange q (all-to-all: heads -> tokens), attend with all heads for 1/tp of
@@ -320,6 +347,15 @@ class DSV4Model:
             return None
         return self.comm.symm.ll_exchange(t, h)
 
+    def _ll_any(self, words: int):
+        """The folded exchange for `words` 8-byte words regardless of the step size, or None."""
+        if not self.decode_fuse:
+            return None
+        if self.tp_size == 1 or self.comm is None or getattr(self.comm, "symm", None) is None or not self.comm.fuse_gemm:
+            return None
+        sy = self.comm.symm
+        return sy.ll if (sy.enabled and words <= sy.ll.words) else None
+
     def _gemm_ar_ctx(self, t: int, n: int):
         """Symmetric context when the row-parallel GEMM can all-reduce in its own epilogue."""
         if self.tp_size == 1 or self.comm is None or getattr(self.comm, "symm", None) is None or not self.device.type == "cuda":
@@ -358,8 +394,13 @@ class DSV4Model:
         q_in_mla = (fuse_norms and A.USE_DECODE_MLA and T <= A.MLA_DECODE_MAX_T and nh_l % 8 == 0 and D == 512
                     and Rd == 64 and self.kv.swa_cache[li].fp8)
 
+        # ... and on pure-decode steps it also builds and inserts the token's own latent row: no insert launch at all
+        kv_in_mla = q_in_mla and meta.pure_decode and meta.swa_slot_mapping.dtype == torch.int64
+
         def kv_insert():
             qv = qb[:, :nh_l * D].view(T, nh_l, D)
+            if kv_in_mla:
+                return qv
             if q_in_mla:
                 C.q_rope_kv_insert(None, kvn, meta.positions, meta.swa_slot_mapping, self.inv, self.kv.swa_cache[li],
                                    cfg.rms_norm_eps, kv_norm_w=kv_norm_w)
@@ -371,7 +412,9 @@ class DSV4Model:
         comp_cache = None
         ev_done = None
         if not lw.ratio:
-            if q_in_mla and can_fork:
+            if kv_in_mla:
+                q = kv_insert()
+            elif q_in_mla and can_fork:
                 # the latent row needs only the kv half of the projection: it is written beside the wq_b projection
                 with side_branch(self.kv_stream, "kv"):
                     self.kv_stream.wait_event(ev_qkv)
@@ -421,7 +464,9 @@ class DSV4Model:
                         sd.wait_event(ev_qb)
                         q = kv_insert()
                     ev_done = sd.record_event()
-                if q_in_mla:
+                if kv_in_mla:
+                    q = kv_insert()
+                elif q_in_mla:
                     # the latent row needs only the kv half of the first projection: its own branch, beside wq_b and
                     # not queued behind the compressors
                     with side_branch(self.kv_stream, "kv"):
@@ -449,20 +494,28 @@ class DSV4Model:
                     else:
                         compress_idx(side)
                     nv = A.compressed_valid(meta.positions, lw.ratio)
+                    n_rows = max(meta.max_comp_rows, 1)
+
+                    def score_topk(a0: int, a1: int, out: torch.Tensor) -> None:
+                        """Rows [a0, a1) of the step -> their top-k ids in out[: a1 - a0], in query sub-chunks that
+                        keep the fp32 score matrix inside the logits budget (overlay/indexer.py:92-143,301-319: here
+                        the scorer reads the paged K rows in place, so only the logits budget applies)."""
+                        for _, qs in split_indexer_prefill_chunks([n_rows], [a1 - a0], 1 << 62, self.indexer_logits_bytes):
+                            b0, b1 = a0 + qs.start, a0 + qs.stop
+                            sc = A.indexer_scores(qq[b0:b1], wf[b0:b1], self.kv.idx_cache[li], grp.table_dev,
+                                                  meta.tok_req[b0:b1], nv[b0:b1], n_rows)
+                            A.topk_rows(sc, nv[b0:b1], K, out=out[qs.start:qs.stop])
+
                     if self.indexer_sp and T >= self.indexer_sp_min_rows * self.tp_size:
-                        shard = -(-T // self.tp_size)
-                        a0 = min(T, self.tp_rank * shard)
-                        a1 = min(T, a0 + shard)
+                        sizes = sp_gather_sizes((0, T), self.tp_size)           # ceil split, the last ranks may be short
+                        shard = sizes[0]
+                        a0 = sum(sizes[:self.tp_rank])
                         part = torch.full((shard, K), -1, dtype=torch.int32, device=y.device)
-                        if a1 > a0:
-                            sc = A.indexer_scores(qq[a0:a1], wf[a0:a1], self.kv.idx_cache[li], grp.table_dev,
-                                                  meta.tok_req[a0:a1], nv[a0:a1], max(meta.max_comp_rows, 1))
-                            A.topk_rows(sc, nv[a0:a1], K, out=part)
+                        if sizes[self.tp_rank] > 0:
+                            score_topk(a0, a0 + sizes[self.tp_rank], part)
                         self.topk_buffer[:T] = self.comm.all_gather_dim0(part)[:T]
                     else:
-                        scores = A.indexer_scores(qq, wf, self.kv.idx_cache[li], grp.table_dev, meta.tok_req, nv,
-                                                  max(meta.max_comp_rows, 1))
-                        A.topk_rows(scores, nv, K, out=self.topk_buffer)
+                        score_topk(0, T, self.topk_buffer)
                 if early_slots is not None:
                     topk_slots, topk_lens = early_slots
                 else:
@@ -482,7 +535,8 @@ class DSV4Model:
             else:
                 o = A.sparse_mla(q, self.kv.swa_cache[li], meta.swa_slots, meta.swa_lens, comp_cache, topk_slots,
                                  topk_lens, lw.sink, D ** -0.5, inv_rope=(meta.positions, self.inv),
-                                 q_prep=(meta.positions, self.inv, cfg.rms_norm_eps) if q_in_mla else None)
+                                 q_prep=(meta.positions, self.inv, cfg.rms_norm_eps) if q_in_mla else None,
+                                 kv_insert=(kvn, kv_norm_w, meta.swa_slot_mapping) if kv_in_mla else None)
         # grouped low-rank output projection, then the row-parallel wo_b (+ all-reduce)
         G_l = len(lw.w_oa)
         hpg = cfg.num_attention_heads // cfg.o_groups
@@ -549,6 +603,11 @@ class DSV4Model:
             routed = M.router(logits, lw.gate_bias, cfg.num_experts_per_tok, cfg.scoring_func, cfg.norm_topk_prob,
                               cfg.routed_scaling_factor, lw.tid2eid, meta.token_ids)
         ids, wts = routed
+        if self.load_recorder is not None and lw.index >= 0:
+            self.load_recorder.record(lw.index, ids)                   # logical ids: what a rebalance needs
+        if lw.eplb is not None:
+            from ..parallel.eplb import to_physical
+            ids = to_physical(ids, *lw.eplb)                           # one replica per pair, round-robin by token
         if not fork:
             shared = self._shared_expert(lw, y, yq)
         ll = None if scatter or not (y.is_cuda and lw.experts.is_fp4) else self._ll(T, cfg.hidden_size)
@@ -639,6 +698,32 @@ class DSV4Model:
         if self.tp_size > 1 and self.comm is not None:
             lg = self.comm.all_gather_last_dim(lg)[:, :self.cfg.vocab_size]
         return lg
+
+    def sample(self, h: torch.Tensor, temp: torch.Tensor, seed: torch.Tensor, pos: torch.Tensor,
+               top_k: Optional[torch.Tensor] = None, top_p: Optional[torch.Tensor] = None,
+               agreed_status: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Head hidden states [n, H] -> sampled tokens [n] (seeded Gumbel arg-max).  Under tensor parallelism the
+        logits stay sharded: every rank takes the noisy arg-max of its vocabulary shard and the ranks exchange one
+        candidate per row (no logits all-gather); truncated sampling (top-k / top-p) needs the whole row and gathers."""
+        from ..ops import sampling as S
+        n = h.shape[0]
+        ll = None
+        if self.tp_size > 1 and top_k is None and top_p is None and h.is_cuda and n <= 256:
+            ll = self._ll_any(3 * n)
+        if ll is not None:
+            lg = Fn.linear(h, self.w.head, tag="head")
+            toks, _ = S.gumbel_argmax(lg, temp, seed, pos, vocab_start=self.w.vocab_start, ll=ll, agreed_status=agreed_status)
+            return toks
+        toks, _ = S.gumbel_argmax(self.compute_logits(h), temp, seed, pos, top_k=top_k, top_p=top_p)
+        return toks
+
+    def forward_sample(self, meta: StepMeta, logit_rows: Optional[torch.Tensor], temp, seed, pos, top_k=None, top_p=None,
+                       agreed_status=None) -> torch.Tensor:
+        """Sampled tokens for the selected token rows (all rows when logit_rows is None)."""
+        X = self.forward_hidden(meta)
+        if logit_rows is not None:
+            X = X.index_select(0, logit_rows)
+        return self.sample(self.head_hidden(X), temp, seed, pos, top_k, top_p, agreed_status)
 
     def forward(self, meta: StepMeta, logit_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Logits for the selected token rows (all rows when logit_rows is None)."""

@@ -229,14 +229,18 @@ MLA_DECODE_MAX_T = 8
 def sparse_mla(q: torch.Tensor, swa_cache: PagedCache, swa_slots: torch.Tensor, swa_lens: torch.Tensor,
                comp_cache: Optional[PagedCache], topk_slots: Optional[torch.Tensor], topk_lens: Optional[torch.Tensor],
                sink: torch.Tensor, scale: float, inv_rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
-               q_prep: Optional[Tuple[torch.Tensor, torch.Tensor, float]] = None) -> torch.Tensor:
+               q_prep: Optional[Tuple[torch.Tensor, torch.Tensor, float]] = None,
+               kv_insert: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
     """q [T, nh, D] bf16 -> out [T, nh, D] bf16 attending to the SWA rows then the top-k rows.
 
     Only the first swa_lens[t] / topk_lens[t] entries of each list are read; -1 entries inside that
     range are masked.  inv_rope = (positions, inv_freq): also apply the inverse RoPE to the output's
     rope dims (fused into the split-merge kernel on the tensor-core path).
     q_prep = (positions, inv_freq, eps): q is the raw projection output; its per-head weightless RMSNorm and RoPE are
-    applied here (inside the decode kernel when it serves the step, else by the stand-alone op first)."""
+    applied here (inside the decode kernel when it serves the step, else by the stand-alone op first).
+    kv_insert = (raw kv [T, D], kv norm weight [D], slots int64 [T]): pure-decode steps only (one token per request) and
+    only together with q_prep on the decode kernel -- the kernel builds each token's own latent row (norm, RoPE,
+    quantise), writes it into the window cache at its slot and attends to it, so no insert launch precedes it."""
     t, nh, d = q.shape
     decode_kernel = (q.is_cuda and USE_DECODE_MLA and t <= MLA_DECODE_MAX_T and swa_cache.fp8 and d == 512
                      and swa_cache.rope_dim == 64 and nh % 8 == 0 and q.stride(0) % 8 == 0 and q.stride(1) == d
@@ -245,6 +249,8 @@ def sparse_mla(q: torch.Tensor, swa_cache: PagedCache, swa_slots: torch.Tensor, 
     if q_prep is not None and not decode_kernel:
         from .functional import q_norm_rope
         q = q_norm_rope(q, q_prep[0], q_prep[1], swa_cache.rope_dim, q_prep[2])
+    if kv_insert is not None and not (decode_kernel and q_prep is not None):
+        raise ValueError("kv_insert needs the decode attention kernel with q_prep")
     if decode_kernel:
         max_rows = swa_slots.shape[1] + (topk_slots.shape[1] if topk_slots is not None else 0)
         S = _lib.query("stk_mla_decode_splits", t, nh, max_rows, _lib.sm_count())
@@ -260,7 +266,10 @@ def sparse_mla(q: torch.Tensor, swa_cache: PagedCache, swa_slots: torch.Tensor, 
                   swa_lens, topk_slots, topk_slots.stride(0) if topk_slots is not None else 0,
                   topk_slots.shape[1] if topk_slots is not None else 0, topk_lens, sink, out, out.stride(0), ws,
                   S, t, nh, float(scale), 1 if q_prep is not None else 0, float(q_prep[2]) if q_prep is not None else 0.0,
-                  pos, inv, 1 if inv_rope is not None else 0, _lib.status_buffer(), _lib.stream())
+                  pos, inv, 1 if inv_rope is not None else 0,
+                  kv_insert[0] if kv_insert is not None else None, kv_insert[0].stride(0) if kv_insert is not None else 0,
+                  kv_insert[1] if kv_insert is not None else None, kv_insert[2] if kv_insert is not None else None,
+                  _lib.status_buffer(), _lib.stream())
         return out
     if not q.is_cuda:
         out = torch.zeros(t, nh, d, dtype=F32)

@@ -446,13 +446,41 @@ def gumbel_noise(seed: torch.Tensor, pos: torch.Tensor, vocab: int) -> torch.Ten
     return -torch.log(-torch.log(u))
 
 
-def gumbel_sample(logits: torch.Tensor, temperature: torch.Tensor, seed: torch.Tensor, pos: torch.Tensor
+def truncation_mask(logits: torch.Tensor, temperature: torch.Tensor, top_k: Optional[torch.Tensor],
+                    top_p: Optional[torch.Tensor]) -> torch.Tensor:
+    """[B, V] bool: inside the top-k set and the top-p nucleus (of the top-k survivors, at temperature T); ties at
+    either threshold are kept."""
+    lf = logits.to(F32)
+    b, v = lf.shape
+    keep = torch.ones(b, v, dtype=torch.bool, device=lf.device)
+    for i in range(b):
+        row = lf[i]
+        k = int(top_k[i]) if top_k is not None else 0
+        if 0 < k < v:
+            keep[i] &= row >= torch.topk(row, k).values[-1]
+        p = float(top_p[i]) if top_p is not None else 1.0
+        t = float(temperature[i])
+        if p < 1.0 and t > 0:
+            masked = torch.where(keep[i], row, torch.full_like(row, float("-inf")))
+            pr = torch.softmax(masked / t, -1)
+            srt, _ = torch.sort(pr, descending=True)
+            cum = torch.cumsum(srt, 0)
+            j = int((cum >= p).nonzero()[0]) if bool((cum >= p).any()) else v - 1
+            keep[i] &= pr >= srt[j]
+    return keep
+
+
+def gumbel_sample(logits: torch.Tensor, temperature: torch.Tensor, seed: torch.Tensor, pos: torch.Tensor,
+                  top_k: Optional[torch.Tensor] = None, top_p: Optional[torch.Tensor] = None
                   ) -> Tuple[torch.Tensor, torch.Tensor]:
-    """-> (token [B] int64, processed logits [B, V] = logits/T).  temperature 0 => greedy."""
+    """-> (token [B] int64, processed logits [B, V] = logits/T, -inf outside the top-k / top-p set).
+    temperature 0 => greedy."""
     lf = logits.to(F32)
     t = temperature.to(F32)[:, None]
     greedy = t <= 0
     proc = lf / torch.where(greedy, torch.ones_like(t), t)
+    if top_k is not None or top_p is not None:
+        proc = torch.where(truncation_mask(lf, temperature.to(F32), top_k, top_p), proc, torch.full_like(proc, float("-inf")))
     noisy = torch.where(greedy, proc, proc + gumbel_noise(seed, pos, lf.shape[-1]))
     return noisy.argmax(-1), proc
 

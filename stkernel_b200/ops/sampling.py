@@ -14,18 +14,28 @@ F32 = torch.float32
 
 
 def gumbel_argmax(logits: torch.Tensor, temperature: torch.Tensor, seed: torch.Tensor, pos: torch.Tensor,
-                  rows_per_request: int = 1, want_processed: bool = False
-                  ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+                  rows_per_request: int = 1, want_processed: bool = False, top_k: Optional[torch.Tensor] = None,
+                  top_p: Optional[torch.Tensor] = None, vocab_start: int = 0, ll=None,
+                  agreed_status: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """logits [B*n, V]; row r belongs to request r // n and samples position pos[req] + r % n.
 
     token = argmax(logits/T + g(seed, position, v)); T <= 0 is greedy.  Returns int64 tokens [B*n]
-    and (optionally) the processed logits logits/T as fp32."""
+    and (optionally) the processed logits logits/T as fp32 (-inf outside the truncated set).
+
+    top_k (int32 per request, <= 0 off) / top_p (float per request, >= 1 off): the arg-max runs over the k largest
+    logits and/or the smallest set whose probability at temperature T reaches p (ties at the threshold stay in);
+    the noise stays a function of (seed, position, vocab id), so truncated drafts and verifications stay coupled.
+
+    vocab_start / ll: `logits` is one tensor-parallel rank's vocabulary shard starting at that id; the ranks of the
+    exchange `ll` agree on the winner without gathering logits (GPU only, no truncation); `agreed_status` (int32 [1])
+    receives the largest kernel status code of any rank."""
     rows, v = logits.shape
     n = rows_per_request
     if not logits.is_cuda:
         req = torch.arange(rows) // n
         p = pos[req] + torch.arange(rows) % n
-        tok, proc = R.gumbel_sample(logits, temperature[req], seed[req], p)
+        tok, proc = R.gumbel_sample(logits, temperature[req], seed[req], p,
+                                    top_k[req] if top_k is not None else None, top_p[req] if top_p is not None else None)
         return tok, (proc if want_processed else None)
     dev = logits.device
     chunks = 32 if v >= 32768 else 4
@@ -37,8 +47,12 @@ def gumbel_argmax(logits: torch.Tensor, temperature: torch.Tensor, seed: torch.T
     if n > 1:
         group = scratch("samp.group", (rows,), torch.int32, dev)
         group.copy_(torch.arange(rows, device=dev, dtype=torch.int32) // n)
+    trunc = top_k is not None or top_p is not None
+    thr = scratch("samp.thr", (rows,), torch.int32, dev) if trunc else None
     _lib.call("stk_gumbel_argmax", logits, logits.stride(0), 1 if logits.dtype == BF16 else 0, temperature, seed, pos,
-              group, n if n > 1 else 0, pv, pi, chunks, out, proc, v, rows, v, _lib.stream())
+              group, n if n > 1 else 0, pv, pi, chunks, out, proc, v, rows, v, top_k, top_p, thr, int(vocab_start),
+              ll.ctx if ll is not None else None, _lib.status_buffer() if ll is not None else None, agreed_status,
+              _lib.status_buffer(), _lib.stream())
     return out, proc
 
 

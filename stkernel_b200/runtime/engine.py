@@ -43,6 +43,12 @@ class SamplingParams:
     min_tokens: int = 0
     ignore_eos: bool = False
     eos_token_id: Optional[int] = None
+    top_k: int = 0                  # <= 0: off
+    top_p: float = 1.0              # >= 1: off
+
+    @property
+    def truncates(self) -> bool:
+        return self.top_k > 0 or self.top_p < 1.0
 
 
 @dataclass
@@ -179,6 +185,9 @@ class HostStage:
         self.h_temp = mk(ms, torch.float32)
         self.h_seed = mk(ms, torch.int64)
         self.h_pos = mk(ms, torch.int64)
+        self.h_topk = mk(ms, torch.int32)
+        self.h_topp = mk(ms, torch.float32)
+        self.n_topk, self.n_topp = self.h_topk.numpy(), self.h_topp.numpy()
         self.n_tokens, self.n_qstart, self.n_rows, self.n_start = (self.h_tokens.numpy(), self.h_qstart.numpy(),
                                                                    self.h_rows.numpy(), self.h_start.numpy())
         self.n_logit_rows, self.n_temp, self.n_seed, self.n_pos = (self.h_logit_rows.numpy(), self.h_temp.numpy(),
@@ -198,6 +207,8 @@ class StepBuffers:
         dv = lambda x: torch.zeros_like(x, device=device)
         self.d_tokens, self.d_qstart, self.d_rows, self.d_start = dv(h.h_tokens), dv(h.h_qstart), dv(h.h_rows), dv(h.h_start)
         self.d_logit_rows, self.d_temp, self.d_seed, self.d_pos = dv(h.h_logit_rows), dv(h.h_temp), dv(h.h_seed), dv(h.h_pos)
+        self.d_topk, self.d_topp = dv(h.h_topk), dv(h.h_topp)
+        self.truncating = False         # whether any sampling row of the staged step asks for top-k / top-p
         self.h_out = torch.zeros(3 * (max_samples or max_reqs) + max_reqs, dtype=torch.int64, pin_memory=pin)
         self.cuda = pin
 
@@ -258,6 +269,10 @@ class Engine:
             self.model.aux_layers = tuple(cfg.model.dspark_target_layer_ids)
             self.drafter = DSparkDrafter(cfg.model, cfg.spec, draft_weights, self.kv, comm, tp_rank, cfg.parallel.tp_size,
                                          mask_token_id)
+        self.weight_source = None            # set by the caller when experts are to be re-placed at run time
+        if cfg.parallel.eplb_record or cfg.parallel.eplb_redundant > 0:
+            from ..parallel.eplb import LoadRecorder
+            self.model.load_recorder = LoadRecorder(cfg.model.num_hidden_layers, cfg.model.n_routed_experts, self.device)
         self.metrics = Metrics()
         self._next_id = 0
         self.requests: Dict[int, Request] = {}
@@ -265,7 +280,9 @@ class Engine:
         self.use_graphs = self.device.type == "cuda" and sc.graph_cap > 0
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
+        self._placements: Dict[int, object] = {}
         self._h_status: Optional[torch.Tensor] = None
+        self._d_agreed: Optional[torch.Tensor] = None
         # Optional host hook (request, device-drafted tokens) -> tokens to verify next step: benchmarks replace the
         # drafter's proposals by a replayed sequence to exercise the accept path at a chosen acceptance rate (the
         # draft block still runs on the device, so the step cost is the real one).
@@ -309,6 +326,15 @@ class Engine:
         return [self.requests[i].output for i in ids]
 
     # ---- device status ---------------------------------------------------------------
+    def _agreed_status(self) -> Optional[torch.Tensor]:
+        """Under tensor parallelism the sampling exchange carries every rank's status word; the largest lands here, so
+        that all ranks fail the same step when any of them saw a wait run out."""
+        if self.device.type != "cuda" or self.cfg.parallel.tp_size == 1:
+            return None
+        if self._d_agreed is None:
+            self._d_agreed = torch.zeros(2, dtype=torch.int32, device=self.device)
+        return self._d_agreed
+
     def _queue_status_read(self) -> None:
         """Queue the copy of the kernels' status word behind the step, next to the sampled tokens: the host reads
         both after the one synchronisation the step already has."""
@@ -316,14 +342,19 @@ class Engine:
             return
         from ..ops import _lib
         if self._h_status is None:
-            self._h_status = torch.zeros(2, dtype=torch.int32, pin_memory=True)
-        self._h_status.copy_(_lib.status_buffer(), non_blocking=True)
+            self._h_status = torch.zeros(4, dtype=torch.int32, pin_memory=True)
+        self._h_status[:2].copy_(_lib.status_buffer(), non_blocking=True)
+        if self._d_agreed is not None:
+            self._h_status[2:].copy_(self._d_agreed, non_blocking=True)
 
     def _read_status(self) -> Tuple[int, int]:
         """(code, detail) of the step just synchronised; (0, 0) = every bounded wait and index check passed."""
         if self._h_status is None:
             return 0, 0
-        return int(self._h_status[0]), int(self._h_status[1])
+        code, detail = int(self._h_status[0]), int(self._h_status[1])
+        if code == 0 and int(self._h_status[2]) != 0:
+            return int(self._h_status[2]), -1          # another rank's code: no detail of our own
+        return code, detail
 
     def _check_device_status(self) -> None:
         """A kernel that gave up a bounded wait (peer flag, mbarrier) or met an out-of-range index skipped its work,
@@ -350,6 +381,7 @@ class Engine:
         b = self.buf.next_stage()
         t = 0
         ns = 0
+        trunc = False
         for i, s in enumerate(seqs):
             r = s.req
             self.kv.prepare(r.row, s.start, s.n + self.spec_lookahead)
@@ -367,8 +399,12 @@ class Engine:
                     b.n_temp[ns] = r.params.temperature
                     b.n_seed[ns] = r.params.seed
                     b.n_pos[ns] = s.start + j + 1    # position of the token being sampled
+                    b.n_topk[ns] = r.params.top_k
+                    b.n_topp[ns] = r.params.top_p
+                    trunc = trunc or r.params.truncates
                     ns += 1
         b.n_qstart[len(seqs)] = t
+        self.buf.truncating = trunc
         return t, len(seqs), ns
 
     def _upload(self, t: int, n: int, ns: int) -> None:
@@ -384,6 +420,9 @@ class Engine:
             d.d_temp[:ns].copy_(b.h_temp[:ns], non_blocking=nb)
             d.d_seed[:ns].copy_(b.h_seed[:ns], non_blocking=nb)
             d.d_pos[:ns].copy_(b.h_pos[:ns], non_blocking=nb)
+            if d.truncating:
+                d.d_topk[:ns].copy_(b.h_topk[:ns], non_blocking=nb)
+                d.d_topp[:ns].copy_(b.h_topp[:ns], non_blocking=nb)
         self.kv.sync(d.parity)
         if d.cuda:
             if b.event is None:
@@ -391,13 +430,14 @@ class Engine:
             b.event.record()
         self.h2d_bytes_last = d.h2d_bytes(t, n)
 
-    def _build_meta(self, t_pad: int, n_req: int, max_comp_rows: int) -> StepMeta:
+    def _build_meta(self, t_pad: int, n_req: int, max_comp_rows: int, pure_decode: bool = False) -> StepMeta:
         b = self.buf
         cfg = self.cfg.model
         tok_req, positions, first, last, sm = A.token_maps(b.d_qstart, b.d_rows, b.d_start, n_req, t_pad,
                                                            self.kv.swa.table_dev)
         swa_slots, swa_lens = A.swa_indices(positions, tok_req, self.kv.swa.table_dev, cfg.sliding_window)
-        return StepMeta(b.d_tokens[:t_pad], tok_req, positions, first, last, sm, swa_slots, swa_lens, max_comp_rows)
+        return StepMeta(b.d_tokens[:t_pad], tok_req, positions, first, last, sm, swa_slots, swa_lens, max_comp_rows,
+                        pure_decode=pure_decode)
 
     def _run_model(self, t_pad: int, n_req: int, ns: int, max_comp_rows: int, identity_rows: bool = False) -> torch.Tensor:
         """-> sampled tokens [ns] (device).
@@ -406,10 +446,11 @@ class Engine:
         not read at all: a padded decode bucket has more rows than the step uploaded, and the entries past them still
         hold an earlier (possibly much larger) step's row numbers."""
         b = self.buf
-        meta = self._build_meta(t_pad, n_req, max_comp_rows)
-        logits = self.model.forward(meta, None if identity_rows else b.d_logit_rows[:ns])
-        toks, _ = S.gumbel_argmax(logits, b.d_temp[:ns], b.d_seed[:ns], b.d_pos[:ns])
-        return toks
+        meta = self._build_meta(t_pad, n_req, max_comp_rows, pure_decode=identity_rows)
+        trunc = b.truncating and not identity_rows
+        return self.model.forward_sample(meta, None if identity_rows else b.d_logit_rows[:ns], b.d_temp[:ns], b.d_seed[:ns],
+                                         b.d_pos[:ns], b.d_topk[:ns] if trunc else None, b.d_topp[:ns] if trunc else None,
+                                         self._agreed_status())
 
     def step(self, forced: Optional[Sequence[int]] = None) -> List[Tuple[int, int]]:
         """Run one scheduler step.  Returns [(req_id, new_token)] for requests that produced a token.
@@ -431,7 +472,7 @@ class Engine:
             meta = self._build_meta(t, n_req, max_comp_rows)
             self.model.forward_hidden(meta)
             toks_dev = None
-        elif self.use_graphs and pure_decode and n_req <= self.cfg.sched.graph_cap:
+        elif self.use_graphs and pure_decode and n_req <= self.cfg.sched.graph_cap and not self.buf.truncating:
             toks_dev = self._decode_graph(n_req, max_comp_rows).replay()
         else:
             toks_dev = self._run_model(t, n_req, ns, max_comp_rows)
@@ -488,6 +529,40 @@ class Engine:
             if s.start < len(s.req.prompt) and end <= len(s.req.prompt) and end % pc.block == 0 and not s.req.finished:
                 pc.offer(s.req.row, s.req.prompt, end)
 
+    # ---- expert load balancing ---------------------------------------------------------------
+    def expert_load(self):
+        """Tokens routed to every logical expert of every layer since the last call ([layers, experts], CPU)."""
+        rec = self.model.load_recorder
+        if rec is None:
+            raise RuntimeError("expert load is not being recorded (ParallelConfig.eplb_record / eplb_redundant)")
+        return rec.take()
+
+    def rebalance_experts(self, load=None) -> List[float]:
+        """Between steps: recompute every layer's expert placement from the recorded (or given) load and rebuild that
+        layer's experts from `weight_source`.  All ranks must call it with the same load (the recorded counts are
+        identical on every rank: routing is replicated).  Returns the per-layer ratio of the most loaded rank's
+        expected tokens after / before; captured decode graphs are dropped (the expert tensors changed)."""
+        from ..models.dsv4 import build_experts
+        from ..parallel.eplb import Placement, rank_loads, rebalance
+        if self.weight_source is None:
+            raise RuntimeError("rebalance_experts needs Engine.weight_source")
+        if load is None:
+            load = self.expert_load()
+        par, mc = self.cfg.parallel, self.cfg.model
+        gains = []
+        for li, lw in enumerate(self.model.w.layers):
+            row = [float(x) for x in load[li]]
+            old = self._placements.get(li) or Placement(mc.n_routed_experts, par.tp_size, list(range(mc.n_routed_experts)))
+            new = rebalance(row, par.eplb_redundant, par.tp_size)
+            before, after = max(rank_loads(old, row)), max(rank_loads(new, row))
+            gains.append(after / before if before > 0 else 1.0)
+            if new.phys_to_logical != old.phys_to_logical:
+                lw.experts, lw.eplb = build_experts(mc, self.weight_source, f"layers.{li}", self.device, self.model.tp_rank,
+                                                    par.tp_size, new)
+                self._placements[li] = new
+        self._graphs.clear()
+        return gains
+
     def reset_prefix_cache(self) -> int:
         return self.prefix_cache.reset() if self.prefix_cache is not None else 0
 
@@ -515,8 +590,10 @@ class Engine:
         if nb == 0:
             return None
         b = self.buf
-        logits = self.model.compute_logits(self.model.head_hidden(X.index_select(0, b.d_logit_rows[:ns])))
-        toks, _ = S.gumbel_argmax(logits, b.d_temp[:ns], b.d_seed[:ns], b.d_pos[:ns])
+        trunc = b.truncating
+        toks = self.model.sample(self.model.head_hidden(X.index_select(0, b.d_logit_rows[:ns])), b.d_temp[:ns], b.d_seed[:ns],
+                                 b.d_pos[:ns], b.d_topk[:ns] if trunc else None, b.d_topp[:ns] if trunc else None,
+                                 self._agreed_status())
         hd, td = self.d_spec_host[:nb], self.d_spec_temp[:nb]
         idx = (hd[:, 0:1] + self._spec_cols[None, :]).clamp_(max=ns - 1)
         ver = toks[idx]
@@ -555,7 +632,7 @@ class Engine:
             self.d_spec_host[:nb].copy_(host[:nb], non_blocking=True)
             self.d_spec_temp[:nb].copy_(temps[:nb], non_blocking=True)
         full = nb == len(seqs) and all(s.n_sample == 1 + n_spec for s in seqs)
-        if self.use_graphs and full and t <= self.cfg.sched.graph_cap:
+        if self.use_graphs and full and t <= self.cfg.sched.graph_cap and not self.buf.truncating:
             rows_bucket = ((max_comp_rows + 64) // 2048 + 1) * 2048
             key = ("spec", n_req, rows_bucket)
             g = self._graphs.get(key)

@@ -26,7 +26,7 @@ import uuid
 from dataclasses import dataclass, field
 from typing import Any, AsyncIterator, Dict, List, Optional, Sequence, Tuple
 
-from fastapi import FastAPI, Request
+from fastapi import FastAPI, HTTPException, Request
 from fastapi.responses import JSONResponse, PlainTextResponse, StreamingResponse
 
 from ..runtime.engine import Engine, SamplingParams
@@ -260,16 +260,50 @@ def _usage(n_prompt: int, n_out: int) -> Dict[str, int]:
     return {"prompt_tokens": n_prompt, "completion_tokens": n_out, "total_tokens": n_prompt + n_out}
 
 
+def attach_response_format(messages: List[Dict[str, Any]], rf: Optional[Dict[str, Any]]) -> List[Dict[str, Any]]:
+    """OpenAI `response_format` -> the schema block of the leading system message, which the chat encoding renders
+    (overlay/tok_deepseek_v4_encoding.py:258-436 takes it from the message): `json_schema` passes its schema,
+    `json_object` asks for any JSON object, `text` (or nothing) leaves the prompt alone.  The output is steered by the
+    prompt, as in the reference's serving surface; it is not grammar-constrained."""
+    if not rf or rf.get("type") in (None, "text"):
+        return list(messages)
+    kind = rf.get("type")
+    if kind == "json_object":
+        schema: Any = {"type": "object"}
+    elif kind == "json_schema":
+        js = rf.get("json_schema") or {}
+        schema = js.get("schema", js)
+        if not isinstance(schema, dict) or not schema:
+            raise HTTPException(status_code=400, detail="response_format.json_schema.schema must be a non-empty object")
+    else:
+        raise HTTPException(status_code=400, detail=f"unsupported response_format type {kind!r}")
+    msgs = list(messages)
+    if msgs and msgs[0].get("role") == "system":
+        msgs[0] = {**msgs[0], "response_format": schema}
+    else:
+        msgs.insert(0, {"role": "system", "content": "", "response_format": schema})
+    return msgs
+
+
 def sampling_from_request(body: Dict[str, Any], eos_id: Optional[int], max_model_len: int, n_prompt: int,
                           default_max: int = 512, default_temperature: float = 1.0) -> SamplingParams:
     max_tokens = body.get("max_completion_tokens") or body.get("max_tokens") or default_max
     max_tokens = max(1, min(int(max_tokens), max_model_len - n_prompt))
     seed = body.get("seed")
     temp = body.get("temperature")
+    top_p = body.get("top_p")
+    top_k = body.get("top_k")
+    top_p = 1.0 if top_p is None else float(top_p)
+    top_k = 0 if top_k is None else int(top_k)
+    if not (0.0 < top_p <= 1.0):
+        raise HTTPException(status_code=400, detail="top_p must be in (0, 1]")
+    if top_k < -1:
+        raise HTTPException(status_code=400, detail="top_k must be -1 (off), 0 (off) or positive")
     return SamplingParams(temperature=float(default_temperature if temp is None else temp),
                           seed=int(seed) if seed is not None else uuid.uuid4().int & 0x7FFFFFFF,
                           max_tokens=max_tokens, min_tokens=int(body.get("min_tokens", 0) or 0),
-                          ignore_eos=bool(body.get("ignore_eos", False)), eos_token_id=eos_id)
+                          ignore_eos=bool(body.get("ignore_eos", False)), eos_token_id=eos_id,
+                          top_k=max(top_k, 0), top_p=top_p)
 
 
 def anthropic_to_chat(body: Dict[str, Any]) -> Tuple[List[Dict[str, Any]], Optional[List[Dict[str, Any]]]]:
@@ -375,7 +409,8 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
         if thinking:
             kwargs.setdefault("thinking", True)
         tools = body.get("tools") if body.get("tool_choice") != "none" else None
-        ids = tokenizer.apply_chat_template(body["messages"], tools=tools, **kwargs)
+        msgs = attach_response_format(body["messages"], body.get("response_format"))
+        ids = tokenizer.apply_chat_template(msgs, tools=tools, **kwargs)
         return ids, thinking, tools
 
     @app.post("/v1/chat/completions")

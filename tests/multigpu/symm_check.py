@@ -43,6 +43,31 @@ def timed(fn, iters=20, warm=3):
     return t.item()
 
 
+def measured_peer_store_bps(comm) -> float:
+    """Bytes per second of 16-byte stores from this rank into the next rank's symmetric region (64 MiB, best of 5),
+    minimum over ranks: the measured link figure the rooflines below divide by."""
+    import ctypes
+    L = _lib.lib()
+    n = 64 << 20
+    src = torch.empty(n, dtype=torch.uint8, device="cuda")
+    heap = comm.symm.heap
+    peer = (comm.rank + 1) % comm.world_size
+    dst = heap.bases[peer] + comm.symm.layout["off_ag"]          # the two-shot all-gather buffer: >= 64 MiB, idle here
+    one = lambda xs: (ctypes.c_longlong * 1)(*xs)
+    best = float("inf")
+    for _ in range(6):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        assert L.stk_peer_copy(one([dst]), one([src.data_ptr()]), 1, n, 64, _lib.stream()) == 0
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) * 1e-3)
+    dist.barrier()
+    t = torch.tensor([n / best], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return float(t.item())
+
+
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -52,6 +77,8 @@ def main():
     out = {"world": world, "symm": comm.symm is not None, "disabled_reason": comm.disabled_reason, "allreduce": [], "gemm_ar": [],
            "ag_gemm": []}
     assert comm.symm is not None, comm.disabled_reason
+    link_bps = measured_peer_store_bps(comm)
+    out["peer_store_gbs_measured"] = link_bps * 1e-9
     g = torch.Generator(device=dev).manual_seed(100 + rank)
     for numel in (4096, 6 * 4096, 64 * 4096, 256 * 4096, 4096 * 4096):
         x = torch.randn(numel, device=dev, generator=g).to(torch.bfloat16)
@@ -66,7 +93,13 @@ def main():
         buf = x.clone()
         ours = timed(lambda: comm.all_reduce(buf))
         nccl = timed(lambda: dist.all_reduce(buf))
-        out["allreduce"].append({"bytes": numel * 2, "ours_us": ours, "nccl_us": nccl, "rel_err": err})
+        nb = numel * 2
+        # bytes this rank sends: one-shot pushes the whole buffer to every peer, two-shot 2 x (world-1)/world of it
+        sent = nb * (world - 1) if nb <= comm.symm.oneshot_max else 2 * nb * (world - 1) // world
+        roof = sent / link_bps * 1e6
+        out["allreduce"].append({"bytes": nb, "ours_us": ours, "nccl_us": nccl, "rel_err": err, "nvlink_bytes_sent": sent,
+                                 "achieved_nvlink_gbs": sent / ours * 1e-3, "frac_of_measured_link": roof / ours,
+                                 "frac_of_900gbs": sent / 900e9 * 1e6 / ours})
     # ---- GEMM fused with the all-reduce (row-parallel layer) ----
     K_total, N = 8192, 4096
     k = K_total // world
@@ -137,9 +170,11 @@ def main():
             torch.matmul(full, w.t())
         flops = 2.0 * T * n_loc * K
         nvl = rows * K * 2 * (world - 1)         # bytes this rank receives
-        roof = max(flops / 1613.6e12, nvl / 770e9) * 1e6
+        roof = max(flops / 1613.6e12, nvl / link_bps) * 1e6
+        roof900 = max(flops / 1613.6e12, nvl / 900e9) * 1e6
         out["ag_gemm"].append({"T": T, "fused_us": fused, "nccl_ag_then_own_gemm_us": timed(base_own),
                                "nccl_ag_then_cublas_us": timed(base_torch), "roofline_us": roof, "frac_of_roofline": roof / fused,
+                               "frac_of_roofline_at_900gbs": roof900 / fused, "achieved_nvlink_gbs": nvl / fused * 1e-3,
                                "rel_err": err})
     if rank == 0:
         print("SYMM_OK " + json.dumps(out), flush=True)

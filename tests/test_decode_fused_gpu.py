@@ -188,13 +188,15 @@ def test_engine_with_folded_allreduce_and_fused_launches_matches_unfused(monkeyp
         monkeypatch.setenv("STK_DECODE_FUSE", "1" if mode == "fused" else "0")
         monkeypatch.setenv("STK_LL_LOOPBACK", "1" if mode == "fused" else "0")
         eng = Engine(ec, weights, dev(), max_context=1024)
-        outs[mode] = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12))
+        # sampled, not greedy: random-init logits are nearly flat, so a greedy arg-max hangs on 1e-3 differences while
+        # the seeded Gumbel noise separates the candidates by O(1)
+        outs[mode] = eng.generate(prompts, SamplingParams(temperature=1.0, seed=11, max_tokens=12))
         torch.cuda.synchronize()
         _lib.check_status()
         if mode == "fused":
             assert eng.model._ll_loop is not None and eng.model._ll_loop.counters[0].item() > 0
     agree = sum(a == b for x, y in zip(outs["fused"], outs["unfused"]) for a, b in zip(x, y))
-    assert agree >= 20, outs            # greedy text may part ways late through bf16 ties; it must not early
+    assert agree >= 22, outs            # the same noise picks the same tokens unless two candidates are within bf16 noise
 
 
 @pytest.mark.parametrize("nh", [8, 16, 64])
@@ -237,4 +239,46 @@ def test_decode_attention_kernel_matches_reference(nh, T):
         A.USE_DECODE_MLA = True
     assert rel_err(out, tc) < 1.2e-2
     torch.cuda.synchronize()
+    _lib.check_status()
+
+
+@pytest.mark.parametrize("nh", [8, 64])
+def test_decode_attention_inserts_the_tokens_own_row(nh):
+    """Pure-decode step: the attention kernel builds, stores and attends to each token's own latent row.  The cache
+    bytes must equal the stand-alone insert's, and the output the attention over that cache."""
+    from stkernel_b200.ops import attention as A
+    torch.manual_seed(50 + nh)
+    D, Rd, W, K, n_pages, T = 512, 64, 128, 512, 40, 3
+    base = C.PagedCache.allocate(n_pages, D, Rd, True, "latent", "cpu")
+    base.write_rows_cpu(torch.arange(n_pages * 64), torch.randn(n_pages * 64, D))
+    inv = Fn.inv_freq(Rd, 10000.0, dev())
+    pos = torch.tensor([4000, 130, 77], dtype=torch.int64, device=dev())
+    q_raw = (torch.randn(T, nh, D, device=dev()) * 2.0).to(BF16)
+    kv_raw = (torch.randn(T, D, device=dev()) * 1.5).to(BF16)
+    kv_w = (1 + 0.1 * torch.randn(D, device=dev())).to(BF16)
+    swa = torch.randperm(n_pages * 64)[:T * W].view(T, W).to(torch.int32).to(dev())
+    swa_l = torch.tensor([W, W, 78], dtype=torch.int32, device=dev())
+    own = torch.stack([swa[i, int(swa_l[i]) - 1] for i in range(T)]).to(torch.int64)      # last window entry = own slot
+    tk = torch.randint(0, n_pages * 64, (T, K), dtype=torch.int32, device=dev())
+    tk_l = torch.tensor([K, 40, 0], dtype=torch.int32, device=dev())
+    sink = torch.randn(nh, device=dev())
+    scale = D ** -0.5
+    # separate launches: insert, then attention
+    c_ref = C.PagedCache(base.buf.to(dev()), D, Rd, True, "latent")
+    C.q_rope_kv_insert(None, kv_raw, pos, own, inv, c_ref, 1e-6, kv_norm_w=kv_w)
+    ref = A.sparse_mla(q_raw.clone(), c_ref, swa, swa_l, c_ref, tk, tk_l, sink, scale, inv_rope=(pos, inv), q_prep=(pos, inv, 1e-6))
+    # one launch
+    c_new = C.PagedCache(base.buf.to(dev()), D, Rd, True, "latent")
+    out = A.sparse_mla(q_raw.clone(), c_new, swa, swa_l, c_new, tk, tk_l, sink, scale, inv_rope=(pos, inv), q_prep=(pos, inv, 1e-6),
+                       kv_insert=(kv_raw, kv_w, own))
+    torch.cuda.synchronize()
+    assert torch.equal(c_new.buf, c_ref.buf)
+    assert rel_err(out, ref) < 2e-3
+    # a token without a slot (padding row) inserts nothing
+    c_pad = C.PagedCache(base.buf.to(dev()), D, Rd, True, "latent")
+    none = torch.full((T,), -1, dtype=torch.int64, device=dev())
+    A.sparse_mla(q_raw.clone(), c_pad, swa, swa_l, c_pad, tk, tk_l, sink, scale, inv_rope=(pos, inv), q_prep=(pos, inv, 1e-6),
+                 kv_insert=(kv_raw, kv_w, none))
+    torch.cuda.synchronize()
+    assert torch.equal(c_pad.buf.cpu(), base.buf)
     _lib.check_status()

@@ -171,3 +171,26 @@ def test_nonzero_device_status_fails_step_and_disables_symmetric_path():
     eng.model.comm.all_reduce(torch.zeros(4))
     assert eng.model.comm.library_calls == 1
     assert "stk:device_status_errors_total" in eng.metrics.render()
+
+
+def test_indexer_scoring_in_query_subchunks_under_a_logits_budget():
+    """With a logits budget of a few hundred bytes the indexer scores a prefill chunk a handful of query rows at a
+    time; the selected rows, hence the text, must not change."""
+    torch.manual_seed(5)
+    cfg = tiny_config()
+    w = init_random_weights(cfg, seed=0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,)).tolist() for n in (90, 41)]
+    sp = SamplingParams(temperature=0.0, max_tokens=6)
+    ref = make_engine(cfg, w).generate(prompts, sp)
+    eng = make_engine(cfg, w)
+    eng.model.indexer_logits_bytes = 256
+    calls = []
+    from stkernel_b200.ops import attention as A
+    orig = A.indexer_scores
+    try:
+        A.indexer_scores = lambda q, *a, **k: (calls.append(q.shape[0]), orig(q, *a, **k))[1]
+        out = eng.generate(prompts, sp)
+    finally:
+        A.indexer_scores = orig
+    assert out == ref
+    assert len(calls) > 20 and max(calls) * 4 * 22 <= 256 + 4 * 22          # rows x compressed rows x 4 bytes within budget

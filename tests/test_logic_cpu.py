@@ -281,3 +281,13 @@ def test_mhc_split_weight_cache_follows_the_tensor_not_its_address():
         seen.append(fn.data_ptr())
         del fn, w
     # (the CPU allocator usually hands the same block out again: the case the cache has to survive)
+
+
+def test_c_api_header_is_generated_from_the_sources():
+    """`stk_c_api.h` lists every exported entry point and is regenerated whenever a signature changes."""
+    from stkernel_b200.csrc import gen_c_api
+    from stkernel_b200.ops import _lib
+    text = gen_c_api.HEADER.read_text()
+    assert text == gen_c_api.render(), "run `python -m stkernel_b200.csrc.gen_c_api`"
+    for name in _lib._parse_signatures():
+        assert f" {name}(" in text

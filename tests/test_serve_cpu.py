@@ -419,3 +419,56 @@ def test_stop_string_ends_stream_early(tool_client):
     body = {"messages": [{"role": "user", "content": "x"}], "max_tokens": 2000, "stop": ["check"], "chat_template_kwargs": {"thinking": True}}
     r = tool_client.post("/v1/chat/completions", json=body).json()
     assert r["choices"][0]["message"]["content"] == "Let me " and r["choices"][0]["finish_reason"] == "stop"
+
+
+def test_top_p_top_k_and_response_format_reach_the_engine_and_the_prompt():
+    """`top_p` / `top_k` become sampling parameters (bad values are refused), `response_format` lands in the system
+    block of the rendered prompt."""
+    from stkernel_b200.serve.api_server import attach_response_format, sampling_from_request
+    p = sampling_from_request({"top_p": 0.9, "top_k": 40, "temperature": 0.7, "seed": 1}, 1, 4096, 10)
+    assert p.top_p == 0.9 and p.top_k == 40 and p.truncates
+    p = sampling_from_request({"top_k": -1, "seed": 1}, 1, 4096, 10)
+    assert p.top_k == 0 and p.top_p == 1.0 and not p.truncates
+    with pytest.raises(Exception):
+        sampling_from_request({"top_p": 0.0}, 1, 4096, 10)
+    msgs = [{"role": "user", "content": "give me json"}]
+    assert attach_response_format(msgs, None) == msgs and attach_response_format(msgs, {"type": "text"}) == msgs
+    out = attach_response_format(msgs, {"type": "json_object"})
+    assert out[0]["role"] == "system" and out[0]["response_format"] == {"type": "object"} and out[1:] == msgs
+    schema = {"type": "object", "properties": {"a": {"type": "integer"}}, "required": ["a"]}
+    sys_first = [{"role": "system", "content": "be brief"}] + msgs
+    out = attach_response_format(sys_first, {"type": "json_schema", "json_schema": {"name": "x", "schema": schema}})
+    assert out[0]["content"] == "be brief" and out[0]["response_format"] == schema
+    from stkernel_b200.serve.tokenizer import render_chat
+    text = render_chat(out)
+    assert '"required"' in text and "be brief" in text
+    with pytest.raises(Exception):
+        attach_response_format(msgs, {"type": "grammar"})
+
+
+def test_truncated_sampling_matches_the_definition_on_cpu():
+    """top-k / top-p on the reference path: the sampled token always lies in the truncated set, greedy is unchanged,
+    and k = 1 equals the arg-max whatever the noise."""
+    import torch
+    from stkernel_b200.ops import reference as R
+    from stkernel_b200.ops import sampling as S
+    torch.manual_seed(0)
+    B, V = 6, 500
+    logits = torch.randn(B, V) * 3
+    temp = torch.full((B,), 0.8)
+    seed = torch.arange(B, dtype=torch.int64)
+    pos = torch.arange(B, dtype=torch.int64) + 5
+    k = torch.tensor([1, 5, 0, 50, 0, 3], dtype=torch.int32)
+    p = torch.tensor([1.0, 1.0, 0.5, 0.9, 0.05, 0.7])
+    tok, proc = S.gumbel_argmax(logits, temp, seed, pos, want_processed=True, top_k=k, top_p=p)
+    keep = R.truncation_mask(logits, temp, k, p)
+    assert all(bool(keep[i, tok[i]]) for i in range(B))
+    assert tok[0] == logits[0].argmax()
+    assert int(keep[1].sum()) == 5 and int(keep[5].sum()) <= 3
+    pr = torch.softmax(logits[2] / 0.8, -1)
+    assert pr[keep[2]].sum() >= 0.5 and pr[keep[2]].sum() - pr[keep[2]].min() < 0.5      # minimal nucleus
+    assert torch.isinf(proc[~keep]).all() and torch.isfinite(proc[keep]).all()
+    # untruncated call is unchanged by the new arguments
+    t0, _ = S.gumbel_argmax(logits, temp, seed, pos)
+    t1, _ = S.gumbel_argmax(logits, temp, seed, pos, top_k=torch.zeros(B, dtype=torch.int32), top_p=torch.ones(B))
+    assert torch.equal(t0, t1)
