@@ -71,13 +71,23 @@ __device__ __forceinline__ void route_token_impl(const RouterArgs& r, const floa
     }
   } else {
     for (int j = 0; j < r.topk; ++j) {
-      float best = -INFINITY;
-      int best_e = 0x7fffffff;
+      // lane-local best as a tree over the kPer candidates (a serial scan is kPer dependent compare/selects;
+      // one warp runs this code alone, so its time is the depth of the dependency chain, not the instruction count)
+      float bv[kPer];
+      int be[kPer];
 #pragma unroll
-      for (int i = 0; i < kPer; ++i) {
-        const int e = i * 32 + lane;
-        if (sel[i] > best) { best = sel[i]; best_e = e; }
+      for (int i = 0; i < kPer; ++i) { bv[i] = sel[i]; be[i] = i * 32 + lane; }
+#pragma unroll
+      for (int w = kPer / 2; w > 0; w >>= 1) {
+#pragma unroll
+        for (int i = 0; i < w; ++i) {
+          const bool take = bv[i + w] > bv[i];          // equal values keep the lower expert id (i < i + w)
+          bv[i] = take ? bv[i + w] : bv[i];
+          be[i] = take ? be[i + w] : be[i];
+        }
       }
+      const float best = bv[0];
+      int best_e = best == -INFINITY ? 0x7fffffff : be[0];
       // warp-wide arg-max in two hardware reductions: the largest key, then the lowest expert id among its holders
       const uint32_t key = ordered_key(best);
       const uint32_t kmax = __reduce_max_sync(0xffffffffu, key);

@@ -31,6 +31,8 @@ struct SkinnyExtra {
   float norm_eps;
   int use_ll;                    // push the result into the slots of `ll` instead of writing `out`
   LLAr ll;
+  int k_split;                   // 1, or 2: two CTAs per row block each take half of K and add into a zeroed fp32 `out`
+                                 // (two addends commute, so the result does not depend on arrival order)
   int route;                     // run the router over `out` (fp32 logits [T, N]) in the last CTA
   int* route_counter;            // zero on entry, zero again on exit
   RouterArgs router;
@@ -155,14 +157,18 @@ skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const f
   const int n_chunks = K / kVals;
   const int iters16 = ((K / 16) + 31) / 32;             // x layout is always in 16-value chunks
   // grouped (block-diagonal) mode: all rows of this CTA belong to one group, whose activations start at g*K
-  const int grp = group_rows > 0 ? (blockIdx.x * 8 * rows_per_warp) / group_rows : 0;
+  const int ksp = ex.k_split > 1 ? ex.k_split : 1;
+  const int rblk = static_cast<int>(blockIdx.x) / ksp, kh = static_cast<int>(blockIdx.x) % ksp;
+  const int c_per = (n_chunks + ksp - 1) / ksp;
+  const int c_lo = kh * c_per, c_hi = min(n_chunks, c_lo + c_per);        // this CTA's 16-byte chunks of every row
+  const int grp = group_rows > 0 ? (rblk * 8 * rows_per_warp) / group_rows : 0;
   __shared__ float s_xscale[kSkinnyMaxT];
   __shared__ float s_red[32];
   // Ahead of the previous kernel's completion: pull this CTA's weight rows (immutable) towards L2, one request per
   // 128-byte line, so that the row loop below starts on L2 hits while the activations are still being produced.
   {
     const int pw = threadIdx.x >> 5, pl = threadIdx.x & 31;
-    const int pn0 = (blockIdx.x * 8 + pw) * rows_per_warp;
+    const int pn0 = (rblk * 8 + pw) * rows_per_warp;
     const int row_bytes = kFp8 ? K : 2 * K;
     for (int pass = 0; pass < (kSwiglu ? 2 : 1); ++pass)
       for (int r = 0; r < rows_per_warp; ++r) {
@@ -175,17 +181,17 @@ skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const f
   // ... and this warp's first row goes all the way into registers: weights are immutable, so the loads may be in
   // flight while the previous kernel finishes; the row loop then starts without a memory round trip.
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = (blockIdx.x * 8 + warp) * rows_per_warp;
+  const int n0 = (rblk * 8 + warp) * rows_per_warp;
   uint4 wv[ITERS];
   float sc[ITERS];
   auto load_row = [&](int wn) {
     const uint4* wrow = reinterpret_cast<const uint4*>(W + wn * ldw_bytes);
 #pragma unroll
     for (int it = 0; it < ITERS; ++it) {
-      const int c = it * 32 + lane;
+      const int c = c_lo + it * 32 + lane;
       wv[it] = make_uint4(0, 0, 0, 0);
       sc[it] = 0.f;
-      if (c < n_chunks) {
+      if (c < c_hi) {
         wv[it] = __ldg(wrow + c);
         if constexpr (kFp8) sc[it] = __ldg(w_scale + (wn >> 7) * w_scale_ld + (c >> 3));
       }
@@ -219,8 +225,8 @@ skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const f
       for (int t = 0; t < T; ++t) acc[t] = 0.f;
 #pragma unroll
       for (int it = 0; it < ITERS; ++it) {
-        const int c = it * 32 + lane;
-        if (c < n_chunks) {
+        const int c = c_lo + it * 32 + lane;
+        if (c < c_hi) {
           const uint32_t ww[4] = {wv[it].x, wv[it].y, wv[it].z, wv[it].w};
           if constexpr (kFp8) {
             // Sixteen raw e4m3 codes -> eight half2; the eight products per token are summed in packed fp16 (activations
@@ -235,8 +241,8 @@ skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const f
             }
 #pragma unroll
             for (int t = 0; t < T; ++t) {
-              const uint4 xa = xs4[((t * iters16 + it) * 2 + 0) * 32 + lane];
-              const uint4 xb = xs4[((t * iters16 + it) * 2 + 1) * 32 + lane];
+              const uint4 xa = xs4[((t * iters16 + (c >> 5)) * 2 + 0) * 32 + (c & 31)];
+              const uint4 xb = xs4[((t * iters16 + (c >> 5)) * 2 + 1) * 32 + (c & 31)];
               const __half2* ha = reinterpret_cast<const __half2*>(&xa);
               const __half2* hb = reinterpret_cast<const __half2*>(&xb);
               __half2 p = __hmul2(w2[0], ha[0]);
@@ -296,7 +302,8 @@ skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const f
           ll_store(ex.ll, ll_epoch, (ex.ll.rank + lane) % ex.ll.world, (static_cast<long long>(t) * N + (n & ~1)) >> 1, d);
         }
       } else if (lane == 0 && t < t_valid) {
-        if (out_fp32) reinterpret_cast<float*>(out)[t * ldo + n] = v;
+        if (ksp > 1) atomicAdd(reinterpret_cast<float*>(out) + t * ldo + n, v);
+        else if (out_fp32) reinterpret_cast<float*>(out)[t * ldo + n] = v;
         else reinterpret_cast<__nv_bfloat16*>(out)[t * ldo + n] = __float2bfloat16(v);
       }
     }
@@ -316,6 +323,11 @@ skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const f
     if (s_last) {
       __threadfence();
       for (int t = warp; t < t_valid; t += 8) route_token<true>(ex.router, reinterpret_cast<const float*>(out) + t * ldo, t, lane);
+      if (ksp > 1) {
+        // the halves add into `out`: leave it zero for the next call
+        __syncthreads();
+        for (int i = threadIdx.x; i < t_valid * N; i += blockDim.x) reinterpret_cast<float*>(out)[(i / N) * ldo + i % N] = 0.f;
+      }
     }
   }
 }
@@ -349,10 +361,12 @@ static int skinny_launch(const void* W, long long ldw, int is_fp8, const float* 
     while (rpw > 1 && group_rows % (8 * rpw)) rpw /= 2;
     if (group_rows % (8 * rpw)) return -3;
   }
-  const int grid = (N + 8 * rpw - 1) / (8 * rpw);
-  cudaStream_t st = (cudaStream_t)stream;
+  const int ksp = ex.k_split > 1 ? 2 : 1;
   const int n_chunks = K / (is_fp8 ? 16 : 8);
-  const int iters = (n_chunks + 31) / 32;
+  if (ksp > 1 && (!out_fp32 || !ex.route || (n_chunks / 2) % 32 || groups > 1 || swiglu)) return -10;
+  const int grid = ((N + 8 * rpw - 1) / (8 * rpw)) * ksp;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int iters = ((n_chunks + ksp - 1) / ksp + 31) / 32;
 #define STK_SK3(T_, F_, I_, S_)                                                                                           \
   {                                                                                                                    \
     static bool configured = false;                                                                                    \
@@ -403,7 +417,9 @@ STK_API int stk_skinny_linear(const void* W, long long ldw, int is_fp8, const fl
 //   norm_w != nullptr   x is RMS-normalised (norm_w, norm_eps) on the way in;
 //   ll_ctx != nullptr   the bf16 result goes into every rank's all-reduce slot (N even) and `out` is not written;
 //   route != 0          `out` is fp32 gate logits [T, N = E]; the last CTA writes the experts and weights of every token
-//                       (route_counter: one zero-initialised int that the kernel leaves at zero).
+//                       (route_counter: one zero-initialised int that the kernel leaves at zero).  route == 2: K is
+//                       split over two CTAs per row block that add into `out`, which must be zero on entry and is
+//                       left zero (the logits are consumed by the routing inside the kernel).
 STK_API int stk_skinny_linear_fused(const void* W, long long ldw, int is_fp8, const float* w_scale, int w_scale_ld,
                                     const void* x, long long ldx, void* out, long long ldo, int T, int N, int K,
                                     int out_fp32, int sm_count, const void* norm_w, float norm_eps, const void* ll_ctx,
@@ -420,6 +436,9 @@ STK_API int stk_skinny_linear_fused(const void* W, long long ldw, int is_fp8, co
   }
   if (route) {
     if (topk > 32) return -9;
+    // a narrow projection (a few hundred rows) leaves most SMs idle: two CTAs per row block, half of K each
+    const int n_chunks = K / (is_fp8 ? 16 : 8);
+    ex.k_split = (route == 2 && (n_chunks / 2) % 32 == 0) ? 2 : 1;
     ex.route = 1;
     ex.route_counter = route_counter;
     ex.router = RouterArgs{bias, tid2eid, token_ids, vocab, ids, weights, N, topk, scoring, renorm, scaling, status};

@@ -250,13 +250,13 @@ def gate_route(x: torch.Tensor, w_gate: LinearWeight, bias, top_k: int, scoring:
     cnt = _route_counters.get(dev.index)
     if cnt is None:
         cnt = _route_counters[dev.index] = torch.zeros(1, dtype=torch.int32, device=dev)
-    logits = scratch("gate.logits", (t, e), F32, dev)
+    logits = scratch("gate.logits", (t, e), F32, dev, zero=True)      # zero on entry, left zero by the kernel
     ids = torch.empty(t, top_k, dtype=torch.int32, device=dev)
     wts = torch.empty(t, top_k, dtype=F32, device=dev)
     vocab = tid2eid.shape[0] if tid2eid is not None else 0
     _lib.call("stk_skinny_linear_fused", w_gate.w, w_gate.w.stride(0), 1 if w_gate.is_fp8 else 0, w_gate.scale,
               w_gate.scale.stride(0) if w_gate.is_fp8 else 0, x, x.stride(0), logits, logits.stride(0), t, e, k, 1,
-              _lib.sm_count(), None, 0.0, None, 1, cnt, bias, tid2eid, token_ids, vocab, ids, wts, top_k,
+              _lib.sm_count(), None, 0.0, None, 2, cnt, bias, tid2eid, token_ids, vocab, ids, wts, top_k,
               0 if scoring == "sigmoid" else 1, 1 if renorm else 0, float(scaling), _lib.status_buffer(), _lib.stream())
     return ids, wts
 

@@ -34,3 +34,12 @@ def test_expert_parallel_moe_over_peer_memory():
            "--tokens", "1,16", "--check-tokens", "48"]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
     assert "EP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_folded_allreduce_sharded_argmax_and_engine_across_ranks():
+    """Producer/consumer all-reduce, vocabulary-sharded arg-max and a tensor-parallel engine with every decode fusion
+    on, against library collectives.  NVLS off: a rank that fails must not leave multicast bindings behind."""
+    r = _torchrun(os.path.join(ROOT, "tests", "multigpu", "ll_check.py"), 2, 29533, timeout=420,
+                  extra_env={"NCCL_NVLS_ENABLE": "0"})
+    assert "LL_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
