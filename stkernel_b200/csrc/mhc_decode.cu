@@ -55,6 +55,7 @@ struct MhcDecodeArgs {
   float post_mult;
   int use_ll;                     // fused mode: fa is the sum of the ranks' slots of `ll`
   LLAr ll;
+  int stage_fn;                   // copy this thread's mix weights into (dynamic) shared memory ahead of the wait
   int* status;
 };
 
@@ -80,9 +81,23 @@ mhc_decode_kernel(const MhcDecodeArgs a) {
   __shared__ float s_r;
   __shared__ __align__(16) float s_fa[4][512];                      // per-thread-group partial sums of the ranks' slots
 
+  extern __shared__ __align__(16) float4 s_fn[];                    // [24][512] when stage_fn, else empty
+
   cluster_arrive();                                   // phase 0: "this CTA runs" (its shared memory may be written)
-  // ahead of the previous kernel's completion: this CTA's columns of the (immutable) mix weights go towards L2
-  if (cols * 4 >= 128) {
+  // Ahead of the previous kernel's completion: this thread's 24 x 16 bytes of the (immutable) mix weights.  Few tokens:
+  // asynchronous copies into shared memory, so that the dot products below start without a memory round trip (196 KB
+  // per CTA, one CTA per SM).  Many tokens: a prefetch towards L2 only, which keeps several CTAs resident per SM.
+  if (a.stage_fn) {
+    if (active) {
+      const float* fbase = a.fn + static_cast<long long>(j) * H + h;
+#pragma unroll
+      for (int m = 0; m < kDcMix; ++m) {
+        const uint32_t dst = smem_u32(&s_fn[m * kDcThreads + threadIdx.x]);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(fbase + static_cast<long long>(m) * HC) : "memory");
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  } else if (cols * 4 >= 128) {
     const int lines = cols * 4 / 128;
     for (int idx = threadIdx.x; idx < kDcMix * 4 * lines; idx += kDcThreads) {
       const int row = idx / lines, ln = idx % lines;          // row = m * 4 + stream
@@ -190,10 +205,19 @@ mhc_decode_kernel(const MhcDecodeArgs a) {
 #pragma unroll
     for (int c = 0; c < 4; ++c) mine[c] = j == 0 ? xs[0][c] : j == 1 ? xs[1][c] : j == 2 ? xs[2][c] : xs[3][c];
     const float* fbase = a.fn + static_cast<long long>(j) * H + h;
+    if (a.stage_fn) {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");      // this thread reads only what it copied itself
 #pragma unroll
-    for (int m = 0; m < kDcMix; ++m) {
-      const float4 f = __ldg(reinterpret_cast<const float4*>(fbase + static_cast<long long>(m) * HC));
-      acc[m] = fmaf(mine[0], f.x, fmaf(mine[1], f.y, fmaf(mine[2], f.z, mine[3] * f.w)));
+      for (int m = 0; m < kDcMix; ++m) {
+        const float4 f = s_fn[m * kDcThreads + threadIdx.x];
+        acc[m] = fmaf(mine[0], f.x, fmaf(mine[1], f.y, fmaf(mine[2], f.z, mine[3] * f.w)));
+      }
+    } else {
+#pragma unroll
+      for (int m = 0; m < kDcMix; ++m) {
+        const float4 f = __ldg(reinterpret_cast<const float4*>(fbase + static_cast<long long>(m) * HC));
+        acc[m] = fmaf(mine[0], f.x, fmaf(mine[1], f.y, fmaf(mine[2], f.z, mine[3] * f.w)));
+      }
     }
 #pragma unroll
     for (int k = 0; k < 4; ++k)
@@ -404,10 +428,18 @@ STK_API int stk_mhc_decode(const void* x, const void* fa, const void* res_old, c
       return -2;
     }
   }
+  // few tokens: one CTA per SM anyway, so each stages its mix weights in shared memory ahead of its predecessor's end
+  constexpr int kStageBytes = kDcMix * kDcThreads * 16;
+  static int stage_ok = 0;             // 0 unknown, 1 yes, -1 no
+  if (stage_ok == 0) {
+    stage_ok = cudaFuncSetAttribute(mhc_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes) == cudaSuccess ? 1 : -1;
+    if (stage_ok < 0) cudaGetLastError();
+  }
+  a.stage_fn = (stage_ok > 0 && T <= 16) ? 1 : 0;          // 16 clusters of 8 = 128 CTAs: at most one per SM
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(T * kDcCluster);
   cfg.blockDim = dim3(kDcThreads);
-  cfg.dynamicSmemBytes = 0;
+  cfg.dynamicSmemBytes = a.stage_fn ? kStageBytes : 0;
   cfg.stream = (cudaStream_t)stream;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;

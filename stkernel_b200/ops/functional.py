@@ -237,6 +237,17 @@ def linear(x, lw: LinearWeight, out: Optional[torch.Tensor] = None, out_dtype=BF
 _route_counters: dict = {}
 
 
+GATE_CLUSTER = _os.environ.get("STK_GATE_CLUSTER", "1") != "0"
+_gate_cluster_state: dict = {}
+
+
+def _gate_cluster_ok() -> bool:
+    d = torch.cuda.current_device()
+    if d not in _gate_cluster_state:
+        _gate_cluster_state[d] = _lib.query("stk_gate_route_cluster_ok") == 1
+    return _gate_cluster_state[d]
+
+
 def gate_route(x: torch.Tensor, w_gate: LinearWeight, bias, top_k: int, scoring: str, renorm: bool, scaling: float,
                tid2eid=None, token_ids=None):
     """Router gate projection and expert selection in one launch for decode-sized batches (the CTA that finishes the
@@ -247,13 +258,21 @@ def gate_route(x: torch.Tensor, w_gate: LinearWeight, bias, top_k: int, scoring:
     if not _skinny_ok(x, t, k, w_gate.is_fp8) or e > 512 or top_k > 32:
         return None
     dev = x.device
+    ids = torch.empty(t, top_k, dtype=torch.int32, device=dev)
+    wts = torch.empty(t, top_k, dtype=F32, device=dev)
+    vocab = tid2eid.shape[0] if tid2eid is not None else 0
+    w = w_gate.w
+    if (GATE_CLUSTER and not w_gate.is_fp8 and w.dtype == BF16 and k <= 4096 and k % 8 == 0 and w.stride(0) % 8 == 0
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and _gate_cluster_ok()):
+        # one 16-CTA cluster: the logits meet in distributed shared memory instead of global memory
+        _lib.call("stk_gate_route_cluster", w, w.stride(0), x, x.stride(0), t, e, k, bias, tid2eid, token_ids, vocab, ids,
+                  wts, top_k, 0 if scoring == "sigmoid" else 1, 1 if renorm else 0, float(scaling), _lib.status_buffer(),
+                  _lib.stream())
+        return ids, wts
     cnt = _route_counters.get(dev.index)
     if cnt is None:
         cnt = _route_counters[dev.index] = torch.zeros(1, dtype=torch.int32, device=dev)
     logits = scratch("gate.logits", (t, e), F32, dev, zero=True)      # zero on entry, left zero by the kernel
-    ids = torch.empty(t, top_k, dtype=torch.int32, device=dev)
-    wts = torch.empty(t, top_k, dtype=F32, device=dev)
-    vocab = tid2eid.shape[0] if tid2eid is not None else 0
     _lib.call("stk_skinny_linear_fused", w_gate.w, w_gate.w.stride(0), 1 if w_gate.is_fp8 else 0, w_gate.scale,
               w_gate.scale.stride(0) if w_gate.is_fp8 else 0, x, x.stride(0), logits, logits.stride(0), t, e, k, 1,
               _lib.sm_count(), None, 0.0, None, 2, cnt, bias, tid2eid, token_ids, vocab, ids, wts, top_k,
