@@ -371,6 +371,14 @@ def run_spec_phase(n_gpus: int, rank: int, dev, comm, fused: bool, layers: int, 
         row["spec_ms_per_step"] = rs["dev_ms"]
         row["random_drafter_accepted_per_step"] = (eng.metrics.spec_num_accepted_tokens - m0[1]) / max(drafts, 1)
         row["break_even_accepted_tokens"] = rs["dev_ms"] / rp["dev_ms"] - 1.0
+        # keep decoding (untimed) until the recorded text is long enough for a replay whose mean acceptance is not noise:
+        # 48 drafted steps per request at C=1, 16 at C=16
+        want_rep = 48 if conc == 1 else 16
+        need = (want_rep + warmup + 2) * (n_spec + 1)
+        guard = 0
+        while min(len(r.output) for r in eng.requests.values()) < need and guard < 2 * need:
+            eng.step()
+            guard += 1
         recorded = {r.params.seed: list(r.output) for r in eng.requests.values()}
         del eng
         torch.cuda.empty_cache()

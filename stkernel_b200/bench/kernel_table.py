@@ -90,8 +90,10 @@ def main() -> None:
                     help="single process only: build rank 0's weight shard of a tensor/expert-parallel group of this "
                          "size and run it alone, without collectives (the sums are incomplete, so the values mean "
                          "nothing; the kernels, their shapes and their times are those of one rank of that group)")
+    ap.add_argument("--spec", type=int, default=0, help="decode mode: DSpark speculative steps with this many draft tokens "
+                                                        "(3 draft layers; every step verifies conc * (spec + 1) rows)")
     a = ap.parse_args()
-    from ..config import EngineConfig, ParallelConfig, SchedulerConfig, flash_config
+    from ..config import EngineConfig, ParallelConfig, SchedulerConfig, SpecConfig, flash_config
     from ..models.dsv4 import RandomSource, build_model_weights
     from ..runtime.engine import Engine, SamplingParams
     from .decode_bench import add_synthetic_requests, fill_caches_synthetic
@@ -109,20 +111,30 @@ def main() -> None:
         from ..parallel.communicator import Communicator
         dist.init_process_group("nccl", device_id=dev)
         comm = Communicator(device=dev, use_symm=True)
-    cfg = flash_config(num_layers=a.layers)
-    ec = EngineConfig(model=cfg, parallel=ParallelConfig(tp_size=world, ep_size=world, fused_collectives=True),
-                      sched=SchedulerConfig(max_model_len=a.ctx + 8192, max_num_seqs=max(a.conc, 2),
-                                                       max_num_batched_tokens=a.chunk,
-                                                       graph_cap=64 if a.graphs else 0)).validate()
+    spec_on = a.spec > 0 and a.mode == "decode"
+    if spec_on:
+        cfg = flash_config(num_layers=a.layers, n_mtp_layers=3,
+                           dspark_target_layer_ids=(a.layers // 4, a.layers // 2, a.layers - 1))
+    else:
+        cfg = flash_config(num_layers=a.layers)
     shard = a.shard_of if world == 1 else 1
-    if shard > 1:
-        ec = EngineConfig(model=cfg, parallel=ParallelConfig(tp_size=shard, ep_size=shard, fused_collectives=True),
-                          sched=ec.sched).validate()
-    eng = Engine(ec, build_model_weights(cfg, RandomSource(0), dev, rank, max(world, shard), head_fp8=True), dev, comm, rank,
-                 max_context=a.ctx + 8192)
+    group = max(world, shard)
+    spec_cfg = SpecConfig(method="dspark", num_speculative_tokens=a.spec, markov_topk=512, temperature=0.6) if spec_on else SpecConfig()
+    ec = EngineConfig(model=cfg, parallel=ParallelConfig(tp_size=group, ep_size=group, fused_collectives=True),
+                      sched=SchedulerConfig(max_model_len=a.ctx + 8192, max_num_seqs=max(a.conc, 2),
+                                            max_num_batched_tokens=a.chunk, graph_cap=256 if a.graphs else 0),
+                      spec=spec_cfg).validate()
+    src = RandomSource(0)
+    weights = build_model_weights(cfg, src, dev, rank, group, head_fp8=True)
+    draft = None
+    if spec_on:
+        from ..spec.dspark import build_draft_weights
+        draft = build_draft_weights(cfg, src, weights, dev, rank, group)
+    eng = Engine(ec, weights, dev, comm, rank, max_context=a.ctx + 8192, draft_weights=draft)
     fill_caches_synthetic(eng)
     if a.mode == "decode":
-        add_synthetic_requests(eng, a.conc, a.ctx, a.steps + 3 * a.time_steps + 8, cfg.vocab_size, 3)
+        add_synthetic_requests(eng, a.conc, a.ctx, (a.steps + 3 * a.time_steps + 8) * (a.spec + 1), cfg.vocab_size, 3,
+                               0.6 if spec_on else 0.0)
     else:
         g = torch.Generator().manual_seed(0)
         eng.add_request(torch.randint(0, cfg.vocab_size, (a.chunk * (a.steps + 2),), generator=g).tolist(),
@@ -139,7 +151,7 @@ def main() -> None:
         for rep in range(2):
             e0.record()
             for i in range(a.time_steps):
-                eng.step(forced[i] if a.mode == "decode" else None)
+                eng.step(forced[i] if a.mode == "decode" and not spec_on else None)
             e1.record()
             torch.cuda.synchronize()
             timed_us = e0.elapsed_time(e1) * 1e3 / a.time_steps

@@ -18,7 +18,7 @@ from typing import Dict, List
 
 import torch
 
-from ..config import EngineConfig, SchedulerConfig, SpecConfig, flash_config
+from ..config import EngineConfig, ParallelConfig, SchedulerConfig, SpecConfig, flash_config
 from ..models.dsv4 import RandomSource, build_model_weights
 from ..ops import _lib
 from ..runtime.engine import Engine, SamplingParams
@@ -26,17 +26,20 @@ from ..spec.dspark import build_draft_weights
 from .decode_bench import add_synthetic_requests, fill_caches_synthetic
 
 
-def run(layers: int, ctx: int, conc: int, steps: int, n_spec: int, temperature: float, spec: bool) -> Dict:
+def run(layers: int, ctx: int, conc: int, steps: int, n_spec: int, temperature: float, spec: bool, shard_of: int = 1) -> Dict:
     dev = torch.device("cuda:0")
     n_mtp = 3 if spec else 0
     cfg = flash_config(layers, n_mtp_layers=n_mtp,
                        dspark_target_layer_ids=(layers // 4, layers // 2, layers - 1) if spec else ())
     sc = SchedulerConfig(max_model_len=ctx + 4096, max_num_seqs=max(conc, 2), max_num_batched_tokens=4096, graph_cap=256)
-    ec = EngineConfig(model=cfg, sched=sc, spec=SpecConfig(method="dspark" if spec else "none", num_speculative_tokens=n_spec,
+    par = ParallelConfig(tp_size=shard_of, ep_size=shard_of, fused_collectives=True) if shard_of > 1 else ParallelConfig()
+    ec = EngineConfig(model=cfg, parallel=par, sched=sc, spec=SpecConfig(method="dspark" if spec else "none", num_speculative_tokens=n_spec,
                                                             markov_topk=512, temperature=temperature)).validate()
     src = RandomSource(0)
-    w = build_model_weights(cfg, src, dev, head_fp8=True)
-    dw = build_draft_weights(cfg, src, w, dev) if spec else None
+    # shard_of > 1: rank 0's shard of a tensor/expert-parallel group of that size run alone, without collectives (the
+    # values mean nothing; kernels, shapes and times are those of one rank of the group)
+    w = build_model_weights(cfg, src, dev, 0, shard_of, head_fp8=True)
+    dw = build_draft_weights(cfg, src, w, dev, 0, shard_of) if spec else None
     eng = Engine(ec, w, dev, max_context=ctx + 4096, draft_weights=dw)
     fill_caches_synthetic(eng)
     ids = add_synthetic_requests(eng, conc, ctx, steps * (n_spec + 1) + 64, cfg.vocab_size, 7)
@@ -61,7 +64,7 @@ def run(layers: int, ctx: int, conc: int, steps: int, n_spec: int, temperature: 
     drafts = eng.metrics.spec_num_drafts - m0[1]
     acc = eng.metrics.spec_num_accepted_tokens - m0[2]
     per_pos = [a - (m0[3][i] if i < len(m0[3]) else 0) for i, a in enumerate(eng.metrics.spec_accepted_per_pos)]
-    return {"spec": spec, "conc": conc, "ctx": ctx, "layers": layers, "steps": steps, "ms_per_step_device": e0.elapsed_time(e1) / steps,
+    return {"spec": spec, "shard_of": shard_of, "conc": conc, "ctx": ctx, "layers": layers, "steps": steps, "ms_per_step_device": e0.elapsed_time(e1) / steps,
             "ms_per_step_wall": 1e3 * wall / steps, "tokens": toks, "tok_s": toks / wall,
             "accepted_per_step": acc / drafts if drafts else 0.0,
             "per_position_acceptance": [round(a / drafts, 4) for a in per_pos] if drafts else []}
@@ -76,11 +79,12 @@ def main() -> None:
     ap.add_argument("--spec-tokens", type=int, default=5)
     ap.add_argument("--temperature", type=float, default=0.6)
     ap.add_argument("--out", default="")
+    ap.add_argument("--shard-of", type=int, default=1, help="time rank 0's shard of a group of this size, alone")
     a = ap.parse_args()
     rows: List[Dict] = []
     for c in [int(x) for x in a.conc.split(",")]:
         for spec in (False, True):
-            r = run(a.layers, a.ctx, c, a.steps, a.spec_tokens, a.temperature, spec)
+            r = run(a.layers, a.ctx, c, a.steps, a.spec_tokens, a.temperature, spec, a.shard_of)
             rows.append(r)
             print(json.dumps(r), flush=True)
             torch.cuda.empty_cache()

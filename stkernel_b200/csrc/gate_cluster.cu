@@ -27,7 +27,7 @@ namespace {
 constexpr int kGcCluster = 16;      // CTAs per cluster (above the portable 8: the kernel opts in)
 constexpr int kGcWarps = 16;        // warps per CTA
 constexpr int kGcIters = 16;        // 16-byte chunks per lane per row: K <= 16 * 32 * 8 = 4096
-constexpr int kGcMaxT = 4;
+constexpr int kGcMaxT = 8;
 constexpr int kGcMaxE = 512;
 
 struct GateClusterArgs {
@@ -143,7 +143,7 @@ bool gate_cluster_launchable() {
 STK_API int stk_gate_route_cluster_ok() { return gate_cluster_launchable() ? 1 : 0; }
 
 // x [T, K] bf16 (row stride ldx elements, 16-byte aligned rows), W [E, K] bf16; writes ids [T, topk] and weights [T, topk].
-// Returns -1 when the shape is outside this kernel (T > 4, K > 4096 or not a multiple of 8, E > 512, topk > 32, rows not
+// Returns -1 when the shape is outside this kernel (T > 8, K > 4096 or not a multiple of 8, E > 512, topk > 32, rows not
 // 16-byte aligned); the caller then uses the grid-wide path.
 STK_API int stk_gate_route_cluster(const void* W, long long ldw, const void* x, long long ldx, int T, int E, int K,
                                    const float* bias, const int* tid2eid, const int64_t* token_ids, int vocab, int* ids,

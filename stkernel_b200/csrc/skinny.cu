@@ -16,6 +16,7 @@
 //     (symm.cuh, LLAr) instead of to `out`; the consumer kernel adds the ranks;
 //   * router epilogue (gate projection): the CTA that finishes last selects the experts of every token.
 #define STK_PDL_CLASS 2      // bit of this file's kernels in the PDL mask (STK_PDL, stk_set_pdl_mask)
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -334,9 +335,21 @@ skinny_linear_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const f
 
 }  // namespace stk
 
+#include "skinny_mma.cuh"
+
 using namespace stk;
 
 // T <= 8.  K must be a multiple of 16 (fp8) / 8 (bf16); rows 16-byte aligned.
+// STK_SKINNY_MMA=0 keeps five to eight tokens on the CUDA-core kernel (A/B runs)
+static bool stk_skinny_mma_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("STK_SKINNY_MMA");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
 static int skinny_launch(const void* W, long long ldw, int is_fp8, const float* w_scale, int w_scale_ld,
                          const void* x, long long ldx, void* out, long long ldo, int T, int N, int K,
                          int out_fp32, int sm_count, int groups, int swiglu, float limit, const SkinnyExtra& ex,
@@ -345,6 +358,10 @@ static int skinny_launch(const void* W, long long ldw, int is_fp8, const float* 
   if (T > kSkinnyMaxT || K % 16 || K > 16384) return -1;
   const long long ldw_bytes = ldw * (is_fp8 ? 1 : 2);
   if (ldw_bytes % 16 || (reinterpret_cast<uintptr_t>(W) & 15)) return -2;
+  // five to eight tokens: the eight-token warp-level tensor-core stream (skinny_mma.cuh)
+  if (T > 4 && !ex.route && stk_skinny_mma_enabled())
+    return skinny_mma_launch(W, ldw_bytes, is_fp8, w_scale, w_scale_ld, x, ldx, out, ldo, T, N, K, out_fp32, groups, swiglu,
+                             limit, ex, (cudaStream_t)stream);
   const int iters16 = ((K / 16) + 31) / 32;
   const int t_inst = T <= 4 ? T : (T <= 6 ? 6 : 8);                // template instance that serves this batch
   const size_t smem = static_cast<size_t>(t_inst) * iters16 * 2 * 32 * 16;

@@ -108,7 +108,8 @@ def ll_reduce(p: LLPending) -> torch.Tensor:
     return out
 
 
-SKINNY_MAX_T = 4          # above four tokens the tcgen05 GEMM with split-K is faster (measured at six)
+# largest batch served by the weight-streaming kernels (at most 8, the largest instance of the kernel)
+SKINNY_MAX_T = min(8, int(_os.environ.get("STK_SKINNY_MAX_T", "4")))
 MHC_CLUSTER_MAX_T = int(_os.environ.get("STK_MHC_CLUSTER_MAX_T", "64"))
 
 
@@ -141,10 +142,16 @@ def quant_act(x: torch.Tensor, tag: str = "act") -> QuantAct:
     return QuantAct(q.view(FP8), s)
 
 
-def _skinny_ok(x, t: int, k: int, is_fp8: bool) -> bool:
+def _skinny_ok(x, t: int, k: int, is_fp8: bool, n: Optional[int] = None) -> bool:
+    if not (isinstance(x, torch.Tensor) and x.is_cuda and t <= SKINNY_MAX_T and x.dtype == BF16):
+        return False
+    if t > 4:
+        # five to eight tokens: the warp-level tensor-core stream (16 weight rows per CTA, 128-value scale groups,
+        # eight activation rows in shared memory)
+        return (k % 128 == 0 and (n is None or n % 16 == 0) and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+                and 8 * ((k if is_fp8 else 2 * k) + 64) + 8 * (k // 128) * 4 + 4096 <= 200 * 1024)
     # a lane holds at most 32 16-byte chunks of a weight row: K <= 16384 for fp8, K <= 8192 for bf16
-    return (isinstance(x, torch.Tensor) and x.is_cuda and t <= SKINNY_MAX_T and x.dtype == BF16 and k % 16 == 0
-            and k <= (16384 if is_fp8 else 8192) and _skinny_rows(t) * k * 2 <= 160 * 1024)
+    return k % 16 == 0 and k <= (16384 if is_fp8 else 8192) and _skinny_rows(t) * k * 2 <= 160 * 1024
 
 
 def linear(x, lw: LinearWeight, out: Optional[torch.Tensor] = None, out_dtype=BF16, tag: str = "lin",
@@ -163,7 +170,7 @@ def linear(x, lw: LinearWeight, out: Optional[torch.Tensor] = None, out_dtype=BF
     `LLPending` is returned instead of a tensor (row-parallel layers at decode sizes)."""
     if (norm is not None or ll is not None) and not isinstance(x, QuantAct) and x.is_cuda:
         t0, (n0, k0) = x.shape[0], lw.w.shape
-        if groups == 1 and ar_ctx is None and out_dtype == BF16 and _skinny_ok(x, t0, k0, lw.is_fp8) and (ll is None or n0 % 2 == 0):
+        if groups == 1 and ar_ctx is None and out_dtype == BF16 and _skinny_ok(x, t0, k0, lw.is_fp8, n0 // max(groups, 1)) and (ll is None or n0 % 2 == 0):
             o = out if out is not None else (None if ll is not None else torch.empty(t0, n0, dtype=BF16, device=x.device))
             _lib.call("stk_skinny_linear_fused", lw.w, lw.w.stride(0), 1 if lw.is_fp8 else 0, lw.scale,
                       lw.scale.stride(0) if lw.is_fp8 else 0, x, x.stride(0), o, o.stride(0) if o is not None else 0, t0, n0, k0,
@@ -207,7 +214,7 @@ def linear(x, lw: LinearWeight, out: Optional[torch.Tensor] = None, out_dtype=BF
         return y
     if out is None:
         out = torch.empty(t, n, dtype=out_dtype, device=dev)
-    if xa is None and ar_ctx is None and _skinny_ok(x, t, k, lw.is_fp8):
+    if xa is None and ar_ctx is None and _skinny_ok(x, t, k, lw.is_fp8, n // max(groups, 1)):
         # one to four tokens: weight-streaming kernel, activations unquantised
         _lib.call("stk_skinny_linear", lw.w, lw.w.stride(0), 1 if lw.is_fp8 else 0, lw.scale,
                   lw.scale.stride(0) if lw.is_fp8 else 0, x, x.stride(0), out, out.stride(0), t, n, k,
@@ -288,6 +295,8 @@ def linear_swiglu(x: torch.Tensor, lw13: LinearWeight, limit: float) -> Optional
     if not x.is_cuda or t > SKINNY_MAX_T or x.dtype != BF16 or k % 16 or k > 8192 or n2 % 2 or _skinny_rows(t) * k * 2 > 160 * 1024:
         return None
     i = n2 // 2
+    if t > 4 and not _skinny_ok(x, t, k, lw13.is_fp8, i):
+        return None
     if lw13.is_fp8 and i % 128:
         return None
     out = torch.empty(t, i, dtype=BF16, device=x.device)

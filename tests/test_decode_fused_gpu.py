@@ -96,6 +96,38 @@ def test_router_inside_the_gate_projection(scoring, T, path, monkeypatch):
     _lib.check_status()
 
 
+@pytest.mark.parametrize("T", [6, 8])
+def test_fused_launches_at_verify_batch_sizes(T, monkeypatch):
+    """Speculative verification runs 6 rows per request: with the weight-streaming limit raised to 8 tokens the norm
+    prologue, the folded all-reduce push and the cluster gate serve those steps too."""
+    monkeypatch.setattr(Fn, "SKINNY_MAX_T", 8)
+    ex = _exchange()
+    torch.manual_seed(50 + T)
+    K, N = 1536, 4096
+    x = torch.randn(T, K, device=dev()).to(BF16) * 2.0
+    nw = (1 + 0.1 * torch.randn(K, device=dev())).to(BF16)
+    for dtype in ("bf16", "fp8"):
+        lw = Fn.LinearWeight.from_master(torch.randn(N, K, device=dev()) * 0.05, dtype, dev())
+        xn = R.rms_norm(x, nw, 1e-6).to(BF16)
+        if dtype == "fp8":            # above four tokens the activations are quantised per 128 values, as in the GEMM path
+            xn = R.dequant_fp8_group128_act(*R.quant_fp8_group128_act(xn))
+        exact = xn.float() @ lw.dequant().t()
+        for rep in range(3):
+            p = Fn.linear(x, lw, norm=(nw, 1e-6), ll=ex)
+            assert isinstance(p, Fn.LLPending)
+            got = Fn.ll_reduce(p)
+        assert rel_err(got, exact) < 1e-2
+    H, E, k = 4096, 256, 6
+    xg = torch.randn(T, H, device=dev()).to(BF16)
+    wg = Fn.LinearWeight((torch.randn(E, H, device=dev()) * 0.02).to(BF16))
+    bias = torch.rand(E, device=dev()) * 0.2 - 0.1
+    ids, wts = Fn.gate_route(xg, wg, bias, k, "sqrtsoftplus", True, 2.5)
+    rid, rw = M.router(xg.float() @ wg.w.float().t(), bias, k, "sqrtsoftplus", True, 2.5)
+    assert torch.equal(ids, rid) and torch.allclose(wts, rw, rtol=1e-4, atol=1e-6)
+    torch.cuda.synchronize()
+    _lib.check_status()
+
+
 @pytest.mark.parametrize("T,H", [(1, 4096), (4, 4096), (3, 1024)])
 def test_folded_allreduce_push_and_reduce_roundtrip(T, H):
     ex = _exchange()

@@ -2,6 +2,7 @@
 import pytest
 import torch
 
+from stkernel_b200.ops import _lib
 from stkernel_b200.ops import attention as A
 from stkernel_b200.ops import cache as C
 from stkernel_b200.ops import functional as Fn
@@ -553,6 +554,60 @@ def test_skinny_swiglu(dtype):
     gu = x.float() @ lw.dequant().t()
     ref = R.swiglu_clamp(gu[:, :I], gu[:, I:], 10.0)
     assert rel_err(act, ref) < 1e-2
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp8"])
+@pytest.mark.parametrize("T", [5, 6, 8])
+@pytest.mark.parametrize("N,K", [(2048, 4096), (16160, 1536), (4096, 8192), (176, 256), (576, 4096)])
+def test_skinny_mma_linear_five_to_eight_tokens(dtype, T, N, K, monkeypatch):
+    """Five to eight tokens: the warp-level tensor-core stream (fp8 activations quantised per 128 values inside the
+    kernel, exactly like the GEMM path)."""
+    monkeypatch.setattr(Fn, "SKINNY_MAX_T", 8)
+    torch.manual_seed(T + N)
+    buf = torch.randn(T, K + 256, device=dev()).to(BF16) * 2.0        # a strided view
+    x = buf[:, :K]
+    w = torch.randn(N, K, device=dev()) * 0.05
+    lw = Fn.LinearWeight.from_master(w, dtype, dev())
+    before = _lib.launch_count
+    out = Fn.linear(x, lw, out_dtype=F32)
+    assert _lib.launch_count == before + 1          # one kernel: no separate quantisation, no split-K reduction
+    if dtype == "fp8":
+        xq, xs = R.quant_fp8_group128_act(x.contiguous())
+        ref = R.dequant_fp8_group128_act(xq, xs) @ lw.dequant().t()
+    else:
+        ref = x.float() @ lw.dequant().t()
+    assert rel_err(out, ref) < 2e-3
+    assert rel_err(Fn.linear(x, lw), ref) < 1e-2
+    torch.cuda.synchronize()
+    _lib.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp8"])
+def test_skinny_mma_grouped_and_swiglu(dtype, monkeypatch):
+    monkeypatch.setattr(Fn, "SKINNY_MAX_T", 8)
+    torch.manual_seed(9)
+    G, Ng, K, T = 8, 1024, 512, 6
+    x = torch.randn(T, G * K, device=dev()).to(BF16)
+    lw = Fn.LinearWeight.from_master(torch.randn(G * Ng, K, device=dev()) * 0.05, dtype, dev())
+    out = Fn.linear(x, lw, out_dtype=F32, groups=G)
+    wd = lw.dequant().view(G, Ng, K)
+    if dtype == "fp8":
+        xf = torch.cat([R.dequant_fp8_group128_act(*R.quant_fp8_group128_act(x[:, g * K:(g + 1) * K].contiguous()))
+                        for g in range(G)], 1)
+    else:
+        xf = x.float()
+    ref = torch.einsum("tgk,gnk->tgn", xf.view(T, G, K), wd).reshape(T, G * Ng)
+    assert rel_err(out, ref) < 2e-3
+    I, K2 = 2048, 4096
+    x2 = torch.randn(T, K2, device=dev()).to(BF16)
+    lw2 = Fn.LinearWeight.from_master(torch.randn(2 * I, K2, device=dev()) * 0.03, dtype, dev())
+    act = Fn.linear_swiglu(x2, lw2, 10.0)
+    assert act is not None
+    x2f = R.dequant_fp8_group128_act(*R.quant_fp8_group128_act(x2)) if dtype == "fp8" else x2.float()
+    gu = x2f @ lw2.dequant().t()
+    assert rel_err(act, R.swiglu_clamp(gu[:, :I], gu[:, I:], 10.0)) < 1e-2
+    torch.cuda.synchronize()
+    _lib.check_status()
 
 
 @pytest.mark.parametrize("T,E,k", [(64, 16, 6), (700, 16, 6), (300, 32, 2), (2048, 8, 2)])
