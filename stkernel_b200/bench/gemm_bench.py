@@ -2,7 +2,7 @@
 against torch.matmul (cuBLAS), timed as CUDA-graph replays with operands larger than L2 rotated
 between calls.
 
-    python -m stkernel_b200.bench.gemm_bench [--out FILE]
+    python -m stkernel_b200.bench.gemm_bench [--out FILE] [--shapes 4096x4096x8192] [--dtypes bf16] [--no-cublas]
 """
 from __future__ import annotations
 
@@ -48,13 +48,18 @@ def graph_time(fns, iters: int = 10) -> float:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default="")
+    ap.add_argument("--shapes", default="", help="TxNxK[,TxNxK...] instead of the default list")
+    ap.add_argument("--dtypes", default="bf16,fp8")
+    ap.add_argument("--no-cublas", action="store_true", help="time only this library's kernel (profiler captures)")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
     peaks = load_peaks()
     rows = []
     shapes = [(1, 2048, 4096), (1, 40960, 1536), (1, 4096, 8192), (8, 4096, 8192), (64, 4096, 8192), (64, 40960, 1536),
               (256, 4096, 8192), (4096, 4096, 8192), (4096, 8192, 8192), (8192, 8192, 8192)]
-    for dtype in ("bf16", "fp8"):
+    if a.shapes:
+        shapes = [tuple(int(v) for v in sh.split("x")) for sh in a.shapes.split(",")]
+    for dtype in a.dtypes.split(","):
         for (T, N, K) in shapes:
             wbytes = N * K * (1 if dtype == "fp8" else 2)
             copies = max(2, min(8, (256 << 20) // wbytes + 1))
@@ -63,7 +68,7 @@ def main() -> None:
             xq = Fn.quant_act(x, "bench") if dtype == "fp8" else x
             outs = [torch.empty(T, N, dtype=torch.bfloat16, device=dev) for _ in range(copies)]
             ours = graph_time([lambda w=w, o=o: Fn.linear(xq, w, out=o) for w, o in zip(ws, outs)])
-            if dtype == "bf16":
+            if dtype == "bf16" and not a.no_cublas:
                 base = graph_time([lambda w=w, o=o: torch.matmul(x, w.w.t(), out=o) for w, o in zip(ws, outs)])
             else:
                 base = None

@@ -64,6 +64,16 @@ __global__ void __launch_bounds__(kGcWarps * 32, 1) gate_route_cluster_kernel(Ga
   }
   pdl_trigger();
   pdl_wait();
+  // the tokens: one burst of 16-byte asynchronous copies into shared memory (one memory round trip for any T)
+  extern __shared__ __align__(16) uint8_t s_x[];                        // [T][K] bf16
+  for (int q = threadIdx.x; q < a.T * n_chunks; q += blockDim.x) {
+    const int t = q / n_chunks, kc = q - t * n_chunks;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(s_x + (static_cast<size_t>(t) * n_chunks + kc) * 16)),
+                 "l"(a.x + static_cast<long long>(t) * a.ldx + kc * 8) : "memory");
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
   float* dst = cluster.map_shared_rank(&s_logits[0][0], 0);
   for (int e = e0, first = 1; e < min(a.E, (crank + 1) * rows_per_cta); e += kGcWarps, first = 0) {
     if (!first) {
@@ -75,21 +85,15 @@ __global__ void __launch_bounds__(kGcWarps * 32, 1) gate_route_cluster_kernel(Ga
       }
     }
     for (int t = 0; t < a.T; ++t) {
-      const uint4* xrow = reinterpret_cast<const uint4*>(a.x + static_cast<long long>(t) * a.ldx);
-      // the token in two batches of eight 16-byte loads per lane (registers: the weight row stays resident)
+      const uint4* xrow = reinterpret_cast<const uint4*>(s_x) + static_cast<size_t>(t) * n_chunks;
       float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint4 xv[kGcIters / 2];
-#pragma unroll
-        for (int i = 0; i < kGcIters / 2; ++i) {
-          const int c = (half * (kGcIters / 2) + i) * 32 + lane;
-          xv[i] = c < n_chunks ? __ldcg(xrow + c) : make_uint4(0, 0, 0, 0);
-        }
-#pragma unroll
-        for (int i = 0; i < kGcIters / 2; ++i) {
-          const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv[half * (kGcIters / 2) + i]);
-          const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv[i]);
+      for (int it = 0; it < kGcIters; ++it) {
+        const int c = it * 32 + lane;
+        if (c < n_chunks) {
+          const uint4 xv = xrow[c];
+          const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv[it]);
+          const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const float2 wf = __bfloat1622float2(wp[j]), xf = __bfloat1622float2(xp[j]);
@@ -119,9 +123,15 @@ bool gate_cluster_launchable() {
     cudaGetLastError();
     return false;
   }
+  if (cudaFuncSetAttribute(gate_route_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           kGcMaxT * kGcIters * 32 * 16) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(kGcCluster);
   cfg.blockDim = dim3(kGcWarps * 32);
+  cfg.dynamicSmemBytes = kGcMaxT * kGcIters * 32 * 16;       // the largest case: 8 tokens x 4096 values
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = kGcCluster;
@@ -163,7 +173,7 @@ STK_API int stk_gate_route_cluster(const void* W, long long ldw, const void* x, 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(kGcCluster);
   cfg.blockDim = dim3(kGcWarps * 32);
-  cfg.dynamicSmemBytes = 0;
+  cfg.dynamicSmemBytes = static_cast<size_t>(T) * K * 2;
   cfg.stream = (cudaStream_t)stream;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;

@@ -273,13 +273,13 @@ expert_fc1_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, ExpertW w1
   const int row = blockIdx.y;
   int pair, e;
   if (direct_ids != nullptr) {
-    // direct mode (a handful of pairs): row = pair index, no sort; non-local experts are skipped.  The token of a pair
-    // does not depend on the routing, so the activation row is staged while the expert id is still on its way.
+    // direct mode (a handful of pairs): row = pair index, no sort; non-local experts are skipped.
+    // Under expert parallelism most pairs belong to other ranks: their CTAs leave as soon as the id has arrived, before
+    // any staging (they would otherwise hold an SM slot for a full activation copy each).
     pair = row;
-    const int e_raw = __ldg(direct_ids + row);
-    fill_xs(reinterpret_cast<__half*>(xs), x + (pair / topk) * ldx, H);
-    e = e_raw - e_start;
+    e = __ldg(direct_ids + row) - e_start;
     if (e < 0 || e >= e_local) return;
+    fill_xs(reinterpret_cast<__half*>(xs), x + (pair / topk) * ldx, H);
   } else {
     if (row >= offsets[e_local]) return;
     pair = sorted[row];
@@ -329,15 +329,14 @@ expert_fc2_kernel(const __half* __restrict__ act, ExpertW w2, const int* __restr
   const int row = blockIdx.y;
   int e;
   if (direct_ids != nullptr) {
-    const int e_raw = __ldg(direct_ids + row);
-    fill_xs(reinterpret_cast<__half*>(xs), act + static_cast<long long>(row) * I, I);   // staged while the id is in flight
-    e = e_raw - e_start;
+    e = __ldg(direct_ids + row) - e_start;
     if (e < 0 || e >= e_local) {
       // not a local expert: this pair contributes nothing on this rank
       for (int n = blockIdx.x * 32 + threadIdx.x; n < min(H, blockIdx.x * 32 + 32); n += blockDim.x)
         y[static_cast<long long>(row) * H + n] = __float2bfloat16(0.f);
       return;
     }
+    fill_xs(reinterpret_cast<__half*>(xs), act + static_cast<long long>(row) * I, I);
   } else {
     if (row >= offsets[e_local]) return;
     e = sorted_expert[row];

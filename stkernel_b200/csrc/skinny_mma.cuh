@@ -45,7 +45,8 @@ __device__ __forceinline__ void mma_bf16_16x8x16(float (&d)[4], uint32_t a0, uin
 }
 
 // Shared-memory layout (dynamic): activation rows [8][row_bytes + 64] (the pad spreads the eight rows over the banks),
-// then fp8 only: x scales [8][K / 128] floats, then the cross-warp reduction buffer [8 warps][16][8] floats.
+// then fp8 only: x scales [8][K / 128] floats, then the cross-warp reduction buffer [8 warps][16][8] floats, then the
+// staging area of the prologue (fp8: the raw bf16 rows [T][2K]; with the fused norm: its weights [2K bytes]).
 template <bool kFp8, bool kSwiglu>
 __global__ void __launch_bounds__(kSmWarps * 32, 2)
 skinny_mma_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const float* __restrict__ w_scale, int w_scale_ld,
@@ -91,41 +92,54 @@ skinny_mma_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const floa
   if (ex.use_ll) ll_epoch = ll_push_epoch(ex.ll);
 
   // ---- prologue: x -> shared memory (RMSNorm, quantisation, zero rows beyond the batch) ----
-  // x is T x (K / 8) chunks of eight bf16 (16 bytes); thread `tid` takes chunks tid, tid + 256, ...  Loads go out in
-  // batches of eight per thread before anything depends on them: the prologue costs a few memory round trips, not one
-  // per chunk.  Sixteen consecutive chunks = one 128-value quantisation group = one half-warp.
+  // Every global byte the prologue needs (the T activation rows and, with the fused norm, its weight vector) is
+  // requested at once with 16-byte asynchronous copies into shared memory: one memory round trip, whatever T and K.
+  // x is T x (K / 8) chunks of eight bf16; thread `tid` takes chunks tid, tid + 256, ...; sixteen consecutive chunks =
+  // one 128-value quantisation group = one half-warp.
   const int cpt = K >> 3;                              // chunks per token
   const int n_chunks = T * cpt;
-  constexpr int kPb = 4;
+  uint8_t* stage = reinterpret_cast<uint8_t*>(red + kSmWarps * kSmRows * kSmTokens);     // fp8: raw bf16 rows [T][2K]
+  uint8_t* raw = kFp8 ? stage : xs;
+  const int raw_stride = kFp8 ? 2 * K : xstride;
+  uint8_t* nw_s = stage + (kFp8 ? T * 2 * K : 0);                                         // norm weights [2K bytes]
+  for (int q = threadIdx.x; q < n_chunks; q += blockDim.x) {
+    const int t = q / cpt, kc = q - t * cpt;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(raw + t * raw_stride + kc * 16)),
+                 "l"(xg + t * ldx + kc * 8) : "memory");
+  }
+  if (ex.norm_w != nullptr)
+    for (int kc = threadIdx.x; kc < cpt; kc += blockDim.x)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(nw_s + kc * 16)), "l"(ex.norm_w + kc * 8)
+                   : "memory");
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  // token slots beyond the batch: zeros (their results are never stored)
+  {
+    const int row16 = row_bytes >> 4;
+    for (int idx = threadIdx.x; idx < (kSmTokens - T) * row16; idx += blockDim.x) {
+      const int t = T + idx / row16, k16 = idx % row16;
+      *reinterpret_cast<uint4*>(xs + t * xstride + k16 * 16) = make_uint4(0, 0, 0, 0);
+    }
+    if constexpr (kFp8)
+      for (int idx = threadIdx.x; idx < (kSmTokens - T) * kgroups; idx += blockDim.x) xsc[T * kgroups + idx] = 0.f;
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
   if (ex.norm_w != nullptr) {
     float ss[kSmTokens];
 #pragma unroll
     for (int t = 0; t < kSmTokens; ++t) ss[t] = 0.f;
-    for (int q0 = threadIdx.x; q0 < n_chunks; q0 += kPb * blockDim.x) {
-      uint4 raw[kPb];
+    for (int q = threadIdx.x; q < n_chunks; q += blockDim.x) {
+      const int t = q / cpt, kc = q - t * cpt;
+      const uint4 v4 = *reinterpret_cast<const uint4*>(raw + t * raw_stride + kc * 16);
+      const uint32_t* rp = reinterpret_cast<const uint32_t*>(&v4);
+      float part = 0.f;
 #pragma unroll
-      for (int i = 0; i < kPb; ++i) {
-        const int q = q0 + i * blockDim.x;
-        raw[i] = make_uint4(0, 0, 0, 0);
-        if (q < n_chunks) {
-          const int t = q / cpt, kc = q - t * cpt;
-          raw[i] = *reinterpret_cast<const uint4*>(xg + t * ldx + kc * 8);
-        }
+      for (int j = 0; j < 4; ++j) {
+        const float2 v = unpack_bf16x2(rp[j]);
+        part = fmaf(v.x, v.x, fmaf(v.y, v.y, part));
       }
 #pragma unroll
-      for (int i = 0; i < kPb; ++i) {
-        const int q = q0 + i * blockDim.x;
-        const int t = q < n_chunks ? q / cpt : 0;
-        const uint32_t* rp = reinterpret_cast<const uint32_t*>(&raw[i]);
-        float part = 0.f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 v = unpack_bf16x2(rp[j]);
-          part = fmaf(v.x, v.x, fmaf(v.y, v.y, part));
-        }
-#pragma unroll
-        for (int tt = 0; tt < kSmTokens; ++tt) ss[tt] += (tt == t) ? part : 0.f;
-      }
+      for (int tt = 0; tt < kSmTokens; ++tt) ss[tt] += (tt == t) ? part : 0.f;
     }
 #pragma unroll
     for (int t = 0; t < kSmTokens; ++t) {
@@ -140,27 +154,17 @@ skinny_mma_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const floa
     }
     __syncthreads();
   }
-  for (int q0 = threadIdx.x; q0 < n_chunks; q0 += kPb * blockDim.x) {
-    uint4 raw[kPb], nwv[kPb];
-#pragma unroll
-    for (int i = 0; i < kPb; ++i) {
-      const int q = q0 + i * blockDim.x;
-      raw[i] = make_uint4(0, 0, 0, 0);
-      nwv[i] = make_uint4(0, 0, 0, 0);
-      if (q < n_chunks) {
-        const int t = q / cpt, kc = q - t * cpt;
-        raw[i] = *reinterpret_cast<const uint4*>(xg + t * ldx + kc * 8);
-        if (ex.norm_w != nullptr) nwv[i] = __ldg(reinterpret_cast<const uint4*>(ex.norm_w + kc * 8));
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < kPb; ++i) {
-      const int q = q0 + i * blockDim.x;
-      const bool ok = q < n_chunks;                   // uniform over a half-warp (16 | cpt, 16 | blockDim)
+  if (kFp8 || ex.norm_w != nullptr) {
+    // n_chunks is a multiple of 16: a half-warp is either all inside or all outside
+    for (int q0 = warp * 32; q0 < n_chunks; q0 += blockDim.x) {        // whole warps: the shuffles below are full-warp
+      const int q = q0 + lane;
+      const bool ok = q < n_chunks;
       const int t = ok ? q / cpt : 0, kc = ok ? q - t * cpt : 0;
-      uint32_t* rp = reinterpret_cast<uint32_t*>(&raw[i]);
+      uint4 v4 = *reinterpret_cast<const uint4*>(raw + t * raw_stride + kc * 16);
+      uint32_t* rp = reinterpret_cast<uint32_t*>(&v4);
       if (ex.norm_w != nullptr) {
-        const uint32_t* wp = reinterpret_cast<const uint32_t*>(&nwv[i]);
+        const uint4 w4 = *reinterpret_cast<const uint4*>(nw_s + kc * 16);
+        const uint32_t* wp = reinterpret_cast<const uint32_t*>(&w4);
         const float nr = s_nr[t];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -179,6 +183,7 @@ skinny_mma_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const floa
         float amax = 0.f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+        // the sixteen lanes of a half-warp hold one group; the other half reduces its own
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
         const float scale = fmaxf(amax, 1e-10f) * (1.f / 448.f);
@@ -194,19 +199,9 @@ skinny_mma_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const floa
           if ((lane & 15) == 0) xsc[t * kgroups + (kc >> 4)] = scale;
         }
       } else {
-        if (ok) *reinterpret_cast<uint4*>(xs + t * xstride + kc * 16) = raw[i];
+        if (ok) *reinterpret_cast<uint4*>(xs + t * xstride + kc * 16) = v4;
       }
     }
-  }
-  // token slots beyond the batch: zeros (their results are never stored)
-  {
-    const int row16 = row_bytes >> 4;
-    for (int idx = threadIdx.x; idx < (kSmTokens - T) * row16; idx += blockDim.x) {
-      const int t = T + idx / row16, k16 = idx % row16;
-      *reinterpret_cast<uint4*>(xs + t * xstride + k16 * 16) = make_uint4(0, 0, 0, 0);
-    }
-    if constexpr (kFp8)
-      for (int idx = threadIdx.x; idx < (kSmTokens - T) * kgroups; idx += blockDim.x) xsc[T * kgroups + idx] = 0.f;
   }
   __syncthreads();
 
@@ -305,8 +300,10 @@ static int skinny_mma_launch(const void* W, long long ldw_bytes, int is_fp8, con
     // a CTA's 16 rows always share one 128-row scale block (16 divides 128); nothing to check
   }
   const int row_bytes = is_fp8 ? K : 2 * K;
+  // activation rows + x scales + reduction buffer + staging (raw bf16 rows for the fp8 path, norm weights)
   const size_t smem = static_cast<size_t>(kSmTokens) * (row_bytes + 64) + (is_fp8 ? kSmTokens * (K / 128) * 4 : 0) +
-                      kSmWarps * kSmRows * kSmTokens * 4;
+                      kSmWarps * kSmRows * kSmTokens * 4 + (is_fp8 ? static_cast<size_t>(T) * 2 * K : 0) +
+                      (ex.norm_w != nullptr ? 2 * K : 0);
   if (smem > 200 * 1024) return -24;
   const int grid = N / kSmRows;
 #define STK_SMMA(F_, S_)                                                                                              \

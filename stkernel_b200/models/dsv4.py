@@ -8,7 +8,8 @@ Parallel layout (one rank per GPU, `tp` ranks):
   * replicated: embedding, mHC parameters, fused wq_a|wkv, compressors, indexer, router gate
   * column-parallel: wq_b (heads), wo_a (o-groups), shared-expert w1|w3, LM head (vocab)
   * row-parallel + all-reduce: wo_b, shared-expert w2
-  * routed experts: expert-parallel (E/tp experts per rank), summed by the same all-reduce
+  * routed experts: expert-parallel (E/tp experts per rank), summed by the same all-reduce; decode-sized steps use a
+    second copy cut along the intermediate dimension (1/tp of every expert per rank: balanced whatever the routing)
 """
 from __future__ import annotations
 
@@ -114,6 +115,7 @@ class LayerWeights:
     w_sh13: Optional[LinearWeight] = None
     w_sh2: Optional[LinearWeight] = None
     experts: Optional[M.ExpertWeights] = None
+    experts_tp: Optional[M.ExpertWeights] = None          # all experts, 1/tp of each one's intermediate rows (decode steps)
     index: int = -1                        # layer number (load recording)
     eplb: Optional[Tuple[torch.Tensor, torch.Tensor]] = None   # (logical -> physical table, replica counts); None = identity
 
@@ -146,6 +148,36 @@ def build_experts(cfg: ModelConfig, src: WeightSource, prefix: str, device, tp_r
     ew = M.ExpertWeights(cat([p.w13 for p in packs]), cat([p.w2 for p in packs]), cat([p.s13 for p in packs]),
                          cat([p.s2 for p in packs]), cat([p.g13 for p in packs]), cat([p.g2 for p in packs]), start)
     return ew, tables
+
+
+def build_experts_sliced(cfg: ModelConfig, src: WeightSource, prefix: str, device, tp_rank: int,
+                         tp_size: int) -> M.ExpertWeights:
+    """Every routed expert of one layer, cut along its intermediate dimension: rank r holds rows [r*I/tp, (r+1)*I/tp) of
+    w1 / w3 and the matching columns of w2.  A decode step touches only top-k experts per token; with whole experts
+    per rank the step waits for the rank that happens to hold most of them, with slices every rank streams the same
+    bytes (1/tp of each selected expert) and the partial sums meet in the all-reduce that follows anyway."""
+    f = f"{prefix}.ffn"
+    E, I, H = cfg.n_routed_experts, cfg.moe_intermediate_size, cfg.hidden_size
+    il = I // tp_size
+    r0 = tp_rank * il
+    g = lambda n, s: _get(src, n, s, device)
+    packs = []
+    for e in range(E):
+        w13 = torch.cat([g(f"{f}.experts.{e}.w1.weight", (I, H))[r0:r0 + il], g(f"{f}.experts.{e}.w3.weight", (I, H))[r0:r0 + il]], 0)
+        w2 = g(f"{f}.experts.{e}.w2.weight", (H, I))[:, r0:r0 + il].contiguous()
+        packs.append(M.ExpertWeights.from_master(w13[None], w2[None], cfg.expert_dtype, device, 0))
+    cat = lambda xs: torch.cat(xs, 0).contiguous() if xs[0] is not None else None
+    return M.ExpertWeights(cat([p.w13 for p in packs]), cat([p.w2 for p in packs]), cat([p.s13 for p in packs]),
+                           cat([p.s2 for p in packs]), cat([p.g13 for p in packs]), cat([p.g2 for p in packs]), 0)
+
+
+def decode_expert_slices_wanted(cfg: ModelConfig, tp_size: int, device) -> bool:
+    """Whether a second, sliced copy of the routed experts is kept for decode-sized steps (GPU, tensor parallel, NVFP4
+    experts whose slices keep whole 32-value blocks; STK_MOE_DECODE_SLICED=0 switches it off)."""
+    import os
+    if os.environ.get("STK_MOE_DECODE_SLICED", "1") == "0" or tp_size <= 1 or torch.device(device).type != "cuda":
+        return False
+    return cfg.expert_dtype == "nvfp4" and cfg.moe_intermediate_size % (32 * tp_size) == 0
 
 
 def build_layer(cfg: ModelConfig, src: WeightSource, prefix: str, li: int, device, tp_rank: int, tp_size: int,
@@ -224,6 +256,8 @@ def build_layer(cfg: ModelConfig, src: WeightSource, prefix: str, li: int, devic
         lw.w_sh13 = mk(torch.cat([w1, w3], 0))
         lw.w_sh2 = mk(g(f"{f}.shared_experts.w2.weight", (H, Is))[:, r0:r0 + isl].contiguous())
     lw.experts, lw.eplb = build_experts(cfg, src, prefix, device, tp_rank, tp_size, placement)
+    if decode_expert_slices_wanted(cfg, tp_size, device):
+        lw.experts_tp = build_experts_sliced(cfg, src, prefix, device, tp_rank, tp_size)
     lw.index = li
     return lw
 
@@ -605,13 +639,18 @@ class DSV4Model:
         ids, wts = routed
         if self.load_recorder is not None and lw.index >= 0:
             self.load_recorder.record(lw.index, ids)                   # logical ids: what a rebalance needs
-        if lw.eplb is not None:
+        # decode-sized steps: every rank computes its slice of every selected expert (balanced by construction);
+        # larger steps: whole experts per rank
+        experts = lw.experts
+        if lw.experts_tp is not None and not scatter and T * ids.shape[1] <= M.DIRECT_MAX_PAIRS:
+            experts = lw.experts_tp
+        elif lw.eplb is not None:
             from ..parallel.eplb import to_physical
             ids = to_physical(ids, *lw.eplb)                           # one replica per pair, round-robin by token
         if not fork:
             shared = self._shared_expert(lw, y, yq)
-        ll = None if scatter or not (y.is_cuda and lw.experts.is_fp4) else self._ll(T, cfg.hidden_size)
-        out = M.moe_experts(y, ids, wts, lw.experts, cfg.swiglu_limit, shared, cfg.n_routed_experts,
+        ll = None if scatter or not (y.is_cuda and experts.is_fp4) else self._ll(T, cfg.hidden_size)
+        out = M.moe_experts(y, ids, wts, experts, cfg.swiglu_limit, shared, cfg.n_routed_experts,
                             shared_ready=ev_sh if fork else None, ll=ll)
         if ll is not None:
             return out                                                  # an LLPending

@@ -108,8 +108,9 @@ def ll_reduce(p: LLPending) -> torch.Tensor:
     return out
 
 
-# largest batch served by the weight-streaming kernels (at most 8, the largest instance of the kernel)
-SKINNY_MAX_T = min(8, int(_os.environ.get("STK_SKINNY_MAX_T", "4")))
+# largest batch served by the weight-streaming kernels: CUDA-core dot products up to four tokens, the eight-token
+# warp-level tensor-core stream above (speculative verification rows, small decode batches)
+SKINNY_MAX_T = min(8, int(_os.environ.get("STK_SKINNY_MAX_T", "8")))
 MHC_CLUSTER_MAX_T = int(_os.environ.get("STK_MHC_CLUSTER_MAX_T", "64"))
 
 
@@ -149,7 +150,8 @@ def _skinny_ok(x, t: int, k: int, is_fp8: bool, n: Optional[int] = None) -> bool
         # five to eight tokens: the warp-level tensor-core stream (16 weight rows per CTA, 128-value scale groups,
         # eight activation rows in shared memory)
         return (k % 128 == 0 and (n is None or n % 16 == 0) and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
-                and 8 * ((k if is_fp8 else 2 * k) + 64) + 8 * (k // 128) * 4 + 4096 <= 200 * 1024)
+                and 8 * ((k if is_fp8 else 2 * k) + 64) + 8 * (k // 128) * 4 + 4096 + (2 * k * t if is_fp8 else 0) + 2 * k
+                <= 200 * 1024)
     # a lane holds at most 32 16-byte chunks of a weight row: K <= 16384 for fp8, K <= 8192 for bf16
     return k % 16 == 0 and k <= (16384 if is_fp8 else 8192) and _skinny_rows(t) * k * 2 <= 160 * 1024
 

@@ -86,7 +86,7 @@ def main():
     # ---- projection -> mHC post/pre ----
     hdim, k = 4096, 2048 // world * world
     kl = k // world
-    for t in (1, 3):
+    for t in (1, 3, 6):
         gw = torch.Generator(device=dev).manual_seed(11 + rank)
         x = torch.randn(t, kl, device=dev, generator=gw).to(BF16)
         lw = Fn.LinearWeight.from_master(torch.randn(hdim, kl, device=dev, generator=gw) * 0.05, "fp8", dev)
@@ -124,6 +124,11 @@ def main():
     from stkernel_b200.runtime.engine import Engine, SamplingParams
     cfg = flash_config(num_layers=3, n_routed_experts=16, vocab_size=4096)
     weights = build_model_weights(cfg, RandomSource(0), dev, rank, world, head_fp8=True)
+    assert weights.layers[0].experts_tp is not None          # decode steps use the sliced copy of the experts ...
+    os.environ["STK_MOE_DECODE_SLICED"] = "0"
+    weights_ep = build_model_weights(cfg, RandomSource(0), dev, rank, world, head_fp8=True)
+    del os.environ["STK_MOE_DECODE_SLICED"]
+    assert weights_ep.layers[0].experts_tp is None           # ... the comparison engine whole experts per rank
     gp = torch.Generator().manual_seed(3)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=gp).tolist() for n in (300, 17)]
     toks = {}
@@ -133,7 +138,7 @@ def main():
         ec = EngineConfig(model=cfg, parallel=ParallelConfig(tp_size=world, ep_size=world, fused_collectives=mode == "fused"),
                           sched=SchedulerConfig(max_model_len=1024, max_num_seqs=4, max_num_batched_tokens=256,
                                                 graph_cap=4)).validate()
-        eng = Engine(ec, weights, dev, c, rank, max_context=1024)
+        eng = Engine(ec, weights if mode == "fused" else weights_ep, dev, c, rank, max_context=1024)
         toks[mode] = eng.generate(prompts, SamplingParams(temperature=1.0, seed=11, max_tokens=12))
         torch.cuda.synchronize()
         _lib.check_status()

@@ -55,7 +55,7 @@ def test_gemm_fp8_block(T, N, K):
     lw = Fn.LinearWeight.from_master(w, "fp8", dev())
     xq, xs = R.quant_fp8_group128_act(x)
     ref = R.dequant_fp8_group128_act(xq, xs) @ lw.dequant().t()
-    if T <= Fn.SKINNY_MAX_T:          # the weight-streaming kernel keeps the activations unquantised
+    if T <= 4:                        # the CUDA-core weight-streaming kernel keeps the activations unquantised
         ref = x.float() @ lw.dequant().t()
     out = Fn.linear(x, lw, out_dtype=F32)
     assert rel_err(out, ref) < 2e-3
@@ -436,6 +436,34 @@ def test_moe_experts_nvfp4(T, H, I, E):
     assert rel_err(out_hi, ref_hi) < 1.5e-2
 
 
+def test_moe_experts_sliced_along_the_intermediate_dimension():
+    """Decode steps under tensor parallelism: every rank holds 1/tp of every expert's intermediate rows; the ranks'
+    partial results add up to the whole experts' output."""
+    torch.manual_seed(12)
+    T, H, I, E, k, tp = 2, 4096, 2048, 16, 6, 8
+    w13 = torch.randn(E, 2 * I, H) * 0.02
+    w2 = torch.randn(E, H, I) * 0.02
+    x = torch.randn(T, H, device=dev()).to(BF16)
+    ids, w = M.router(torch.randn(T, E, device=dev()), None, k, "sigmoid", True, 1.0)
+    il = I // tp
+    total = torch.zeros(T, H)
+    ref = torch.zeros(T, H)
+    for r in range(tp):
+        sl = slice(r * il, (r + 1) * il)
+        w13_r = torch.cat([w13[:, :I][:, sl], w13[:, I:][:, sl]], 1).contiguous()
+        w2_r = w2[:, :, sl].contiguous()
+        ew = M.ExpertWeights.from_master(w13_r, w2_r, "nvfp4", dev())
+        out = M.moe_experts(x, ids, w, ew, 10.0, None, E)
+        d13, d2 = ew.dequant()
+        ref += R.moe_experts(x, ids, w, d13, d2, 10.0).float().cpu()
+        total += out.float().cpu()
+    assert rel_err(total, ref) < 1.5e-2
+    full = R.moe_experts(x, ids, w, w13.to(dev()), w2.to(dev()), 10.0).float().cpu()
+    assert rel_err(total, full) < 0.15          # NVFP4 quantisation of the weights
+    torch.cuda.synchronize()
+    _lib.check_status()
+
+
 def test_gumbel_argmax_and_coupling():
     B, N, V = 3, 5, 129280
     logits = torch.randn(B * (N + 1), V, device=dev())
@@ -500,7 +528,7 @@ def test_gemm_grouped_block_diagonal(dtype, T):
     out = Fn.linear(x, stacked, out_dtype=F32, groups=G)
     for g in range(G):
         xg = x[:, g * K:(g + 1) * K]
-        if dtype == "fp8" and T > Fn.SKINNY_MAX_T:
+        if dtype == "fp8" and T > 4:
             xq, xs = R.quant_fp8_group128_act(xg)
             ref = R.dequant_fp8_group128_act(xq, xs) @ lws[g].dequant().t()
         else:
@@ -570,7 +598,8 @@ def test_skinny_mma_linear_five_to_eight_tokens(dtype, T, N, K, monkeypatch):
     lw = Fn.LinearWeight.from_master(w, dtype, dev())
     before = _lib.launch_count
     out = Fn.linear(x, lw, out_dtype=F32)
-    assert _lib.launch_count == before + 1          # one kernel: no separate quantisation, no split-K reduction
+    if Fn._skinny_ok(x, T, K, dtype == "fp8", N):   # (the largest fp8 case at 8 tokens exceeds the staging area)
+        assert _lib.launch_count == before + 1      # one kernel: no separate quantisation, no split-K reduction
     if dtype == "fp8":
         xq, xs = R.quant_fp8_group128_act(x.contiguous())
         ref = R.dequant_fp8_group128_act(xq, xs) @ lw.dequant().t()
