@@ -18,6 +18,8 @@
 #include <string.h>
 
 #define STK_PDL_CLASS 8      // bit of this file's kernels in the PDL mask (STK_PDL, stk_set_pdl_mask)
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "stk_c_api.h"
 #include "symm.cuh"
@@ -559,6 +561,166 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
 }
 
 // ---------------------------------------------------------------------------------
+// Wide tile for large bf16 problems: one CTA owns 256 weight rows x 256 tokens.
+//
+// Measured on the 128 x 256 tile above (4096 x 4096 x 8192, ncu): tensor pipe 31 % active, no unit saturated; the
+// kernel is paced by operand delivery (48 KB per 512 tensor-core cycles per SM, 7.9 TB/s out of L2 over all SMs), and
+// adding L2 prefetch requests made it slower -- it is the L2 -> SM path that is short, not DRAM.  Two 128-row MMAs that
+// share one 256-token operand stage need 64 KB per 1024 cycles: two thirds of the traffic per FLOP.  The two
+// accumulators take all 512 TMEM columns, so the epilogue of a tile is not overlapped with the next tile's MMAs; with
+// eight epilogue warps it is a few per cent of a tile for K >= 2048.
+// ---------------------------------------------------------------------------------
+struct WideArgs {
+  int T, N, k_blocks, tiles_n, tiles_t;
+  void* out;
+  long long ldo;
+  int out_fp32;
+  int* status;
+};
+
+constexpr int kWideStages = 3;
+constexpr int kWideStageBytes = 2 * 128 * 128 + 256 * 128;       // two weight tiles + one token tile = 64 KB
+
+__global__ void __launch_bounds__(320, 1)
+gemm_wide_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const WideArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  GemmBarriers* bars = reinterpret_cast<GemmBarriers*>(smem + kWideStages * kWideStageBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kWideStages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    mbar_init(&bars->tmem_full[0], 1);
+    mbar_init(&bars->tmem_empty[0], 8);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  pdl_wait();
+  pdl_trigger();
+  const int units = a.tiles_n * a.tiles_t;
+  constexpr uint32_t kIdesc = umma_idesc(1u, 1u, 128, 256);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0, issued = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+        const int tn = u % a.tiles_n, tt = u / a.tiles_n;
+        for (int kb = 0; kb < a.k_blocks; ++kb) {
+          if (!mbar_wait(&bars->empty[stage], phase ^ 1, a.status, 100 + stage)) { ok = false; break; }
+          mbar_expect_tx(&bars->full[stage], kWideStageBytes);
+          uint8_t* st = smem + stage * kWideStageBytes;
+          tma_load_2d(st, &tmW, &bars->full[stage], kb * 64, tn * 256);
+          tma_load_2d(st + 128 * 128, &tmW, &bars->full[stage], kb * 64, tn * 256 + 128);
+          tma_load_2d(st + 2 * 128 * 128, &tmX, &bars->full[stage], kb * 64, tt * 256);
+          ++issued;
+          if (++stage == kWideStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // drain: wait (bounded) until every load issued to the ring has landed
+        const int pending = issued < kWideStages ? issued : kWideStages;
+        int s = stage;
+        uint32_t ph = phase;
+        for (int i = 0; i < pending; ++i) {
+          if (--s < 0) { s = kWideStages - 1; ph ^= 1; }
+          mbar_wait(&bars->full[s], ph, nullptr, 0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0, aphase = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+        if (!mbar_wait(&bars->tmem_empty[0], aphase ^ 1, a.status, 200)) { ok = false; break; }
+        tc_fence_after();
+        for (int kb = 0; kb < a.k_blocks; ++kb) {
+          if (!mbar_wait(&bars->full[stage], phase, a.status, 300 + stage)) { ok = false; break; }
+          tc_fence_after();
+          const uint8_t* st = smem + stage * kWideStageBytes;
+          const uint64_t a0 = umma_desc_sw128(smem_u32(st));
+          const uint64_t a1 = umma_desc_sw128(smem_u32(st + 128 * 128));
+          const uint64_t bd = umma_desc_sw128(smem_u32(st + 2 * 128 * 128));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+            umma_f16(tmem_base, a0 + 2 * k, bd + 2 * k, kIdesc, acc);
+            umma_f16(tmem_base + 256, a1 + 2 * k, bd + 2 * k, kIdesc, acc);
+          }
+          umma_commit(&bars->empty[stage]);
+          if (++stage == kWideStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&bars->tmem_full[0]);
+        aphase ^= 1;
+      }
+    }
+  } else {
+    // eight epilogue warps: lane quarter q = warp % 4 (the TMEM lanes a warp may read), column half h
+    const int e = warp - 2;
+    const int q = warp & 3, h = e >> 2;
+    uint32_t aphase = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+      const int tn = u % a.tiles_n, tt = u / a.tiles_n;
+      if (!mbar_wait(&bars->tmem_full[0], aphase, a.status, 400)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int m = 0; m < 2; ++m) {
+        const int n = tn * 256 + m * 128 + q * 32 + lane;
+        const bool n_ok = n < a.N;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          const int col = h * 128 + c * 32;
+          tmem_ld_32x32(tmem_base + m * 256 + col + (static_cast<uint32_t>(q * 32) << 16), r);
+          tmem_ld_wait();
+          const int t0 = tt * 256 + col;
+          if (n_ok) {
+            if (a.out_fp32) {
+              float* o = reinterpret_cast<float*>(a.out);
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (t0 + j < a.T) o[static_cast<long long>(t0 + j) * a.ldo + n] = __uint_as_float(r[j]);
+            } else {
+              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out);
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (t0 + j < a.T) o[static_cast<long long>(t0 + j) * a.ldo + n] = __float2bfloat16(__uint_as_float(r[j]));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->tmem_empty[0]);
+      aphase ^= 1;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -655,6 +817,16 @@ STK_API long long stk_gemm_workspace_bytes(int T, int N, int splits) {
   return splits > 1 ? static_cast<long long>(splits) * T * N * 4 : 0;
 }
 
+// STK_GEMM_WIDE=0 keeps large bf16 problems on the 128 x 256 tile (A/B runs)
+static bool gemm_wide_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("STK_GEMM_WIDE");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
 static int gemm_launch(const void* W, long long ldw, const void* X, long long ldx, void* out, long long ldo, int T, int N,
                        int K, int is_fp8, int out_fp32, const float* w_scale, int w_scale_ld, const float* x_scale,
                        int x_scale_ld, int splits, float* workspace, int* counters, int* status, int sm_count,
@@ -688,6 +860,28 @@ static int gemm_launch(const void* W, long long ldw, const void* X, long long ld
     const int units = a.tiles_n * a.tiles_t;
     const int grid = units < sm_count ? units : sm_count;
     return launch_gemm<128, true>(ta, tb, a, grid, reinterpret_cast<cudaStream_t>(stream));
+  }
+  if (!is_fp8 && groups == 1 && ar_ctx == nullptr && gate_ctx == nullptr && splits <= 1 && bt_override == 0 && T >= 512 &&
+      N >= 512 && gemm_wide_enabled()) {
+    CUtensorMap tw2, tx2;
+    if (make_tmap_2d(&tw2, W, 2, N, K, ldw, 128) != 0) return -13;
+    if (make_tmap_2d(&tx2, X, 2, T, K, ldx, 256) != 0) return -14;
+    WideArgs wa;
+    wa.T = T; wa.N = N;
+    wa.k_blocks = (K * 2 + 127) / 128;
+    wa.tiles_n = (N + 255) / 256;
+    wa.tiles_t = (T + 255) / 256;
+    wa.out = out; wa.ldo = ldo; wa.out_fp32 = out_fp32; wa.status = status;
+    const int wunits = wa.tiles_n * wa.tiles_t;
+    const int wgrid = wunits < sm_count ? wunits : sm_count;
+    const int wsmem = kWideStages * kWideStageBytes + 256 + 1024;
+    static bool wide_configured = false;
+    if (!wide_configured) {
+      if (cudaFuncSetAttribute(gemm_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, wsmem) != cudaSuccess) return -3;
+      wide_configured = true;
+    }
+    launch_pdl(gemm_wide_kernel, dim3(wgrid), dim3(320), wsmem, reinterpret_cast<cudaStream_t>(stream), tw2, tx2, wa);
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
   }
   int bt = stk_gemm_pick_bt(T, is_fp8);
   if (bt_override == 16 || bt_override == 32 || bt_override == 64 || bt_override == 128) bt = bt_override;

@@ -189,34 +189,36 @@ __device__ __forceinline__ void fp4_row_load(Fp4Row<ITERS>& r, const uint8_t* __
   }
 }
 
+// One 32-value chunk: 16 bytes of e2m1 pairs, two e4m3 block scales, activations at (iteration k, lane) of `xs`.
+__device__ __forceinline__ float fp4_chunk_dot(const uint4& wv, uint32_t sc, const uint4* __restrict__ xs, int k, int lane) {
+  const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
+  float part[2];
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    __half2 hs = __floats2half2_rn(0.f, 0.f);
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const uint4 xv = xs[(k * 4 + g * 2 + q) * 32 + lane];
+      const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+      const uint32_t w = words[g * 2 + q];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const __half2_raw hr = __nv_cvt_fp4x2_to_halfraw2(static_cast<__nv_fp4x2_storage_t>((w >> (8 * b)) & 0xff), __NV_E2M1);
+        hs = __hfma2(*reinterpret_cast<const __half2*>(&hr), *reinterpret_cast<const __half2*>(&xw[b]), hs);
+      }
+    }
+    part[g] = __low2float(hs) + __high2float(hs);
+  }
+  return fmaf(part[0], fp8_to_f(sc & 0xff), part[1] * fp8_to_f((sc >> 8) & 0xff));
+}
+
 template <int ITERS>
 __device__ __forceinline__ float fp4_row_dot(const Fp4Row<ITERS>& r, const uint4* __restrict__ xs, int n_chunks, int lane) {
   float acc = 0.f;
 #pragma unroll
   for (int k = 0; k < ITERS; ++k) {
     const int c = k * 32 + lane;
-    if (c < n_chunks) {
-      const uint32_t words[4] = {r.w[k].x, r.w[k].y, r.w[k].z, r.w[k].w};
-      float part[2];
-#pragma unroll
-      for (int g = 0; g < 2; ++g) {
-        __half2 hs = __floats2half2_rn(0.f, 0.f);
-#pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          const uint4 xv = xs[(k * 4 + g * 2 + q) * 32 + lane];
-          const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
-          const uint32_t w = words[g * 2 + q];
-#pragma unroll
-          for (int b = 0; b < 4; ++b) {
-            const __half2_raw hr = __nv_cvt_fp4x2_to_halfraw2(static_cast<__nv_fp4x2_storage_t>((w >> (8 * b)) & 0xff), __NV_E2M1);
-            hs = __hfma2(*reinterpret_cast<const __half2*>(&hr), *reinterpret_cast<const __half2*>(&xw[b]), hs);
-          }
-        }
-        part[g] = __low2float(hs) + __high2float(hs);
-      }
-      acc = fmaf(part[0], fp8_to_f(r.s[k] & 0xff), acc);
-      acc = fmaf(part[1], fp8_to_f((r.s[k] >> 8) & 0xff), acc);
-    }
+    if (c < n_chunks) acc += fp4_chunk_dot(r.w[k], r.s[k], xs, k, lane);
   }
   return warp_sum(acc);
 }
@@ -314,6 +316,52 @@ expert_fc1_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, ExpertW w1
       }
       act[static_cast<long long>(row) * I + i] = __float2half(g / (1.f + __expf(-g)) * u);
     }
+  }
+}
+
+// FC2 for narrow experts (I <= 512: the slices of tensor-parallel decode): a row is L = I / 32 chunks, so L lanes per
+// row and 32 / L rows per warp pass; four passes per warp, 8 warps: 128 * (8 / L) ... rows per CTA = 8 * (32 / L) * 4.
+// Direct mode only (row = pair index).  grid (ceil(H / rows_per_cta), n_pairs).
+template <int L>
+__global__ void __launch_bounds__(256)
+expert_fc2_narrow_kernel(const __half* __restrict__ act, ExpertW w2, int e_local, __nv_bfloat16* __restrict__ y, int H, int I,
+                         const int* __restrict__ direct_ids, int e_start) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ uint4 xs[];
+  constexpr int R = 32 / L, kJ = 4;
+  constexpr int kRowsPerCta = 8 * R * kJ;
+  const int row = blockIdx.y;
+  const int e = __ldg(direct_ids + row) - e_start;
+  if (e < 0 || e >= e_local) {
+    for (int n = blockIdx.x * kRowsPerCta + threadIdx.x; n < min(H, (static_cast<int>(blockIdx.x) + 1) * kRowsPerCta); n += blockDim.x)
+      y[static_cast<long long>(row) * H + n] = __float2bfloat16(0.f);
+    return;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane / L, cl = lane % L;
+  const float gs = w2.gscale[e];
+  const long long wstride = static_cast<long long>(I) / 2, sstride = static_cast<long long>(I) / 16;
+  const uint8_t* wbase = w2.w + static_cast<long long>(e) * H * wstride;
+  const uint8_t* sbase = w2.s + static_cast<long long>(e) * H * sstride;
+  const int n0 = blockIdx.x * kRowsPerCta + warp * R * kJ;
+  uint4 wv[kJ];
+  uint32_t sc[kJ];
+#pragma unroll
+  for (int j = 0; j < kJ; ++j) {
+    const int n = min(n0 + j * R + sub, H - 1);
+    wv[j] = __ldg(reinterpret_cast<const uint4*>(wbase + n * wstride) + cl);
+    sc[j] = __ldg(reinterpret_cast<const uint16_t*>(sbase + n * sstride) + cl);
+  }
+  fill_xs(reinterpret_cast<__half*>(xs), act + static_cast<long long>(row) * I, I);
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < kJ; ++j) {
+    float v = fp4_chunk_dot(wv[j], sc[j], xs, 0, cl);
+#pragma unroll
+    for (int o = L / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int n = n0 + j * R + sub;
+    if (cl == 0 && n < H) y[static_cast<long long>(row) * H + n] = __float2bfloat16(v * gs);
   }
 }
 
@@ -421,9 +469,19 @@ STK_API int stk_moe_expert_fc2(const void* act, const void* w2, const void* s2, 
   if (max_rows <= 0) return 0;
   if (I % 32 || I > 16384) return -1;
   ExpertW w{(const uint8_t*)w2, (const uint8_t*)s2, g2};
-  dim3 grid((H + 31) / 32, max_rows);
   const size_t smem = ((I + 1023) / 1024) * 2048;
   cudaStream_t st = (cudaStream_t)stream;
+  if (direct_ids != nullptr && I <= 512 && (I & (I - 1)) == 0) {
+    // narrow experts: several rows per warp pass
+    const int L = I / 32;
+#define STK_FC2N(L_)                                                                                              \
+  launch_pdl(expert_fc2_narrow_kernel<L_>, dim3((H + 8 * (32 / L_) * 4 - 1) / (8 * (32 / L_) * 4), max_rows), dim3(256), smem, st, \
+             (const __half*)act, w, e_local, (__nv_bfloat16*)y, H, I, direct_ids, e_start)
+    if (L == 1) STK_FC2N(1); else if (L == 2) STK_FC2N(2); else if (L == 4) STK_FC2N(4); else if (L == 8) STK_FC2N(8); else STK_FC2N(16);
+#undef STK_FC2N
+    return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  }
+  dim3 grid((H + 31) / 32, max_rows);
   const int iters = (I / 32 + 31) / 32;
 #define STK_FC2(I_) launch_pdl(expert_fc2_kernel<I_>, dim3(grid), dim3(256), smem, st, (const __half*)act, w, sorted_expert, offsets, e_local, (__nv_bfloat16*)y, H, I, direct_ids, e_start)
   if (iters <= 1) STK_FC2(1); else if (iters <= 2) STK_FC2(2); else if (iters <= 4) STK_FC2(4); else if (iters <= 8) STK_FC2(8); else STK_FC2(16);

@@ -72,6 +72,7 @@ class Communicator:
         """[T, n] per rank -> [T, n * world] (rank-major along the last dim)."""
         if self.world_size == 1:
             return x
+        self.calls["nccl"] += 1
         parts = torch.empty(self.world_size * x.shape[0], x.shape[1], dtype=x.dtype, device=x.device)
         dist.all_gather_into_tensor(parts, x.contiguous(), group=self.group)
         return parts.view(self.world_size, x.shape[0], x.shape[1]).permute(1, 0, 2).reshape(x.shape[0], -1)
@@ -79,6 +80,7 @@ class Communicator:
     def all_gather_dim0(self, x: torch.Tensor) -> torch.Tensor:
         if self.world_size == 1:
             return x
+        self.calls["nccl"] += 1
         out = torch.empty(self.world_size * x.shape[0], *x.shape[1:], dtype=x.dtype, device=x.device)
         dist.all_gather_into_tensor(out, x.contiguous(), group=self.group)
         return out
@@ -87,6 +89,7 @@ class Communicator:
         """Ragged all-gather along dim 0 (`sizes[r]` rows from rank r)."""
         if self.world_size == 1:
             return x
+        self.calls["nccl"] += 1
         outs = [torch.empty(s, *x.shape[1:], dtype=x.dtype, device=x.device) for s in sizes]
         dist.all_gather(outs, x.contiguous(), group=self.group)
         return torch.cat(outs, 0)
@@ -94,6 +97,7 @@ class Communicator:
     def reduce_scatter_dim0(self, x: torch.Tensor) -> torch.Tensor:
         if self.world_size == 1:
             return x
+        self.calls["nccl"] += 1
         assert x.shape[0] % self.world_size == 0
         n = x.shape[0] // self.world_size
         if not x.is_cuda:
@@ -108,6 +112,7 @@ class Communicator:
     def reduce_scatterv_dim0(self, x: torch.Tensor, sizes: Sequence[int]) -> torch.Tensor:
         if self.world_size == 1:
             return x
+        self.calls["nccl"] += 1
         chunks = list(torch.split(x.contiguous(), list(sizes), 0))
         out = torch.empty_like(chunks[self.rank])
         dist.reduce_scatter(out, chunks, group=self.group)
@@ -127,6 +132,7 @@ class Communicator:
 
     def all_to_all_dim0(self, x: torch.Tensor, in_sizes: Sequence[int], out_sizes: Sequence[int]) -> torch.Tensor:
         """Expert-parallel dispatch/combine baseline: ragged all-to-all along dim 0."""
+        self.calls["nccl"] += 1
         out = torch.empty(sum(out_sizes), *x.shape[1:], dtype=x.dtype, device=x.device)
         dist.all_to_all_single(out, x.contiguous(), list(out_sizes), list(in_sizes), group=self.group)
         return out
