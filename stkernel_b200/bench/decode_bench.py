@@ -310,21 +310,39 @@ class ReplayDrafter:
     """Stands in for a trained drafter when the weights are random: proposes the tokens the same engine emitted in an
     earlier pass over the same request (same seeds, same kernels, hence the same text), corrupting position j with
     the probability that gives the published cumulative acceptance.  Only the proposals are replaced on the host;
-    the draft block still runs on the device every step."""
+    the draft block still runs on the device every step.
+
+    The replayed text is only a valid oracle while this pass still emits it: an accepted draft row is computed beside
+    other rows than in the recording pass, and one rounding-level flip of a sampled token changes everything after it.
+    The drafter therefore checks, at every call, that the request's output is still a prefix of the recording, and
+    counts steps and emitted tokens only while it is (`steps_in_sync`, `tokens_in_sync`)."""
 
     def __init__(self, recorded: Dict[int, List[int]], vocab: int, acceptance=REFERENCE_ACCEPTANCE, seed: int = 0):
         self.rec, self.vocab = recorded, vocab
         self.cond = [acceptance[0]] + [acceptance[j] / acceptance[j - 1] for j in range(1, len(acceptance))]
         self.rng = random.Random(seed)
+        self.in_sync: Dict[int, bool] = {}
+        self.last_len: Dict[int, int] = {}
+        self.steps_in_sync = 0
+        self.tokens_in_sync = 0
+        self.counting = False
 
     def __call__(self, req: Request, device_drafts: List[int]) -> List[int]:
-        rec = self.rec.get(req.params.seed)
+        key = req.params.seed
+        rec = self.rec.get(key)
         have = len(req.output)
+        ok = rec is not None and self.in_sync.get(key, True) and have + len(device_drafts) < len(rec) \
+            and list(req.output) == rec[:have]
+        if self.counting and key in self.last_len and self.in_sync.get(key, True):
+            # the step that just ended was drafted from a valid oracle
+            self.steps_in_sync += 1
+            self.tokens_in_sync += have - self.last_len[key]
+        self.in_sync[key] = ok
+        self.last_len[key] = have
+        if not ok:
+            return list(device_drafts)
         out = []
         for j in range(len(device_drafts)):
-            if rec is None or have + j >= len(rec):
-                out.append(device_drafts[j])
-                continue
             tok = rec[have + j]
             c = self.cond[min(j, len(self.cond) - 1)]
             out.append(tok if self.rng.random() < c else (tok + 1) % self.vocab)
@@ -388,6 +406,7 @@ def run_spec_phase(n_gpus: int, rank: int, dev, comm, fused: bool, layers: int, 
         n_rep = max(8, min(len(v) for v in recorded.values()) // (n_spec + 1) - warmup - 2)
         for _ in range(warmup):
             eng.step()
+        eng.draft_override.counting = True
         g0 = eng.metrics.generation_tokens_total
         m0 = (eng.metrics.spec_num_drafts, eng.metrics.spec_num_accepted_tokens, list(eng.metrics.spec_accepted_per_pos))
         _sync(n_gpus)
@@ -402,12 +421,21 @@ def run_spec_phase(n_gpus: int, rank: int, dev, comm, fused: bool, layers: int, 
         toks = eng.metrics.generation_tokens_total - g0
         drafts = eng.metrics.spec_num_drafts - m0[0]
         per = [a - (m0[2][i] if i < len(m0[2]) else 0) for i, a in enumerate(eng.metrics.spec_accepted_per_pos)]
+        rd = eng.draft_override
         row["replay_steps"] = n_rep
         row["replay_ms_per_step"] = _max_over_ranks(e0.elapsed_time(e1) / n_rep, n_gpus, dev)
-        row["replay_accepted_per_step"] = (eng.metrics.spec_num_accepted_tokens - m0[1]) / max(drafts, 1)
-        row["replay_per_position_acceptance"] = [round(a / max(drafts, 1), 4) for a in per]
-        row["replay_tok_s"] = toks / wall
-        row["replay_speedup_vs_plain"] = (toks / wall) / row["plain_tok_s"]
+        row["replay_wall_ms_per_step"] = wall * 1e3 / n_rep
+        row["replay_accepted_per_step_all_steps"] = (eng.metrics.spec_num_accepted_tokens - m0[1]) / max(drafts, 1)
+        row["replay_per_position_acceptance_all_steps"] = [round(a / max(drafts, 1), 4) for a in per]
+        # steps drafted from a valid oracle (the request still emitted the recorded text): the acceptance of those
+        # steps is the reference's profile; a step costs the same whatever it accepts, so tokens/s over those steps
+        # is tokens per step / measured time per step
+        row["replay_request_steps_in_sync"] = rd.steps_in_sync
+        row["replay_tokens_per_step_in_sync"] = rd.tokens_in_sync / max(rd.steps_in_sync, 1)
+        tps = conc * row["replay_tokens_per_step_in_sync"] / (row["replay_wall_ms_per_step"] * 1e-3)
+        row["replay_tok_s"] = tps
+        row["replay_tok_s_all_steps"] = toks / wall
+        row["replay_speedup_vs_plain"] = tps / row["plain_tok_s"]
         _lib.check_status()
         del eng
         torch.cuda.empty_cache()

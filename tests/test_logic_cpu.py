@@ -291,3 +291,24 @@ def test_c_api_header_is_generated_from_the_sources():
     assert text == gen_c_api.render(), "run `python -m stkernel_b200.csrc.gen_c_api`"
     for name in _lib._parse_signatures():
         assert f" {name}(" in text
+
+
+def test_replay_drafter_counts_only_steps_drafted_from_a_valid_oracle():
+    """The bench's stand-in drafter replays a recorded text; once the request emits something else the recording is no
+    oracle any more, and neither its steps nor its tokens may enter the acceptance figures."""
+    from types import SimpleNamespace
+    from stkernel_b200.bench.decode_bench import ReplayDrafter
+    rec = {7: list(range(100, 160))}
+    d = ReplayDrafter(rec, vocab=1000, acceptance=(1.0, 1.0, 1.0), seed=0)
+    d.counting = True
+    req = SimpleNamespace(params=SimpleNamespace(seed=7), output=[])
+    assert d(req, [1, 2, 3]) == [100, 101, 102]                 # acceptance 1.0: the recorded continuation
+    req.output = [100, 101, 102, 103]                           # three accepted + the bonus token
+    assert d(req, [1, 2, 3]) == [104, 105, 106]
+    assert (d.steps_in_sync, d.tokens_in_sync) == (1, 4)
+    req.output = req.output + [104, 999]                        # the engine emitted a token the recording does not have
+    assert d(req, [1, 2, 3]) == [1, 2, 3]                       # out of sync: the device drafts go through
+    assert (d.steps_in_sync, d.tokens_in_sync) == (2, 6)        # the step that just ended was still drafted validly
+    req.output = req.output + [5]
+    d(req, [1, 2, 3])
+    assert (d.steps_in_sync, d.tokens_in_sync) == (2, 6)        # steps after the divergence are not counted
