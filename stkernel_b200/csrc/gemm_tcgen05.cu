@@ -561,14 +561,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
 }
 
 // ---------------------------------------------------------------------------------
-// Wide tile for large bf16 problems: one CTA owns 256 weight rows x 256 tokens.
+// Wide tile for large bf16 problems: one CTA owns 256 tokens x 256 weight rows (token-major: TMEM lanes are tokens,
+// so an epilogue thread writes 64 contiguous bytes of its token's output row per chunk).
 //
 // Measured on the 128 x 256 tile above (4096 x 4096 x 8192, ncu): tensor pipe 31 % active, no unit saturated; the
 // kernel is paced by operand delivery (48 KB per 512 tensor-core cycles per SM, 7.9 TB/s out of L2 over all SMs), and
-// adding L2 prefetch requests made it slower -- it is the L2 -> SM path that is short, not DRAM.  Two 128-row MMAs that
-// share one 256-token operand stage need 64 KB per 1024 cycles: two thirds of the traffic per FLOP.  The two
-// accumulators take all 512 TMEM columns, so the epilogue of a tile is not overlapped with the next tile's MMAs; with
-// eight epilogue warps it is a few per cent of a tile for K >= 2048.
+// adding L2 prefetch requests made it slower -- it is the L2 -> SM path that is short, not DRAM.  Two 128-token MMAs that
+// share one 256-row weight stage need 64 KB per 1024 cycles: two thirds of the traffic per FLOP, and the three-stage
+// ring covers 3072 tensor-core cycles instead of 2048.  The two accumulators take all 512 TMEM columns, so the
+// epilogue of a tile is not overlapped with the next tile's MMAs; eight epilogue warps with 16-byte stores keep it short.
 // ---------------------------------------------------------------------------------
 struct WideArgs {
   int T, N, k_blocks, tiles_n, tiles_t;
@@ -624,9 +625,10 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
           if (!mbar_wait(&bars->empty[stage], phase ^ 1, a.status, 100 + stage)) { ok = false; break; }
           mbar_expect_tx(&bars->full[stage], kWideStageBytes);
           uint8_t* st = smem + stage * kWideStageBytes;
-          tma_load_2d(st, &tmW, &bars->full[stage], kb * 64, tn * 256);
-          tma_load_2d(st + 128 * 128, &tmW, &bars->full[stage], kb * 64, tn * 256 + 128);
-          tma_load_2d(st + 2 * 128 * 128, &tmX, &bars->full[stage], kb * 64, tt * 256);
+          // token-major: the two A operands are 128-token tiles (TMEM lanes = tokens), B is the 256-row weight tile
+          tma_load_2d(st, &tmX, &bars->full[stage], kb * 64, tt * 256);
+          tma_load_2d(st + 128 * 128, &tmX, &bars->full[stage], kb * 64, tt * 256 + 128);
+          tma_load_2d(st + 2 * 128 * 128, &tmW, &bars->full[stage], kb * 64, tn * 256);
           ++issued;
           if (++stage == kWideStages) { stage = 0; phase ^= 1; }
         }
@@ -680,28 +682,41 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       const int tn = u % a.tiles_n, tt = u / a.tiles_n;
       if (!mbar_wait(&bars->tmem_full[0], aphase, a.status, 400)) { ok = false; break; }
       tc_fence_after();
+      // a thread owns one token row and, per chunk, 32 consecutive output features: 64 contiguous bytes of bf16
+      const bool vec_ok = !a.out_fp32 && (a.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.out) & 15) == 0);
 #pragma unroll
       for (int m = 0; m < 2; ++m) {
-        const int n = tn * 256 + m * 128 + q * 32 + lane;
-        const bool n_ok = n < a.N;
+        const int t = tt * 256 + m * 128 + q * 32 + lane;
+        const bool t_ok = t < a.T;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
           const int col = h * 128 + c * 32;
           tmem_ld_32x32(tmem_base + m * 256 + col + (static_cast<uint32_t>(q * 32) << 16), r);
           tmem_ld_wait();
-          const int t0 = tt * 256 + col;
-          if (n_ok) {
-            if (a.out_fp32) {
-              float* o = reinterpret_cast<float*>(a.out);
+          const int n0 = tn * 256 + col;
+          if (t_ok) {
+            if (vec_ok && n0 + 32 <= a.N) {
+              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out) + static_cast<long long>(t) * a.ldo + n0;
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 ov;
+                __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  oh[i] = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * i]), __uint_as_float(r[j + 2 * i + 1]));
+                *reinterpret_cast<uint4*>(o + j) = ov;
+              }
+            } else if (a.out_fp32) {
+              float* o = reinterpret_cast<float*>(a.out) + static_cast<long long>(t) * a.ldo + n0;
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (t0 + j < a.T) o[static_cast<long long>(t0 + j) * a.ldo + n] = __uint_as_float(r[j]);
+                if (n0 + j < a.N) o[j] = __uint_as_float(r[j]);
             } else {
-              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out);
+              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(a.out) + static_cast<long long>(t) * a.ldo + n0;
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (t0 + j < a.T) o[static_cast<long long>(t0 + j) * a.ldo + n] = __float2bfloat16(__uint_as_float(r[j]));
+                if (n0 + j < a.N) o[j] = __float2bfloat16(__uint_as_float(r[j]));
             }
           }
         }
@@ -864,8 +879,8 @@ static int gemm_launch(const void* W, long long ldw, const void* X, long long ld
   if (!is_fp8 && groups == 1 && ar_ctx == nullptr && gate_ctx == nullptr && splits <= 1 && bt_override == 0 && T >= 512 &&
       N >= 512 && gemm_wide_enabled()) {
     CUtensorMap tw2, tx2;
-    if (make_tmap_2d(&tw2, W, 2, N, K, ldw, 128) != 0) return -13;
-    if (make_tmap_2d(&tx2, X, 2, T, K, ldx, 256) != 0) return -14;
+    if (make_tmap_2d(&tw2, W, 2, N, K, ldw, 256) != 0) return -13;       // B operand: 256 weight rows
+    if (make_tmap_2d(&tx2, X, 2, T, K, ldx, 128) != 0) return -14;       // A operands: 128 tokens each
     WideArgs wa;
     wa.T = T; wa.N = N;
     wa.k_blocks = (K * 2 + 127) / 128;

@@ -355,7 +355,8 @@ static int skinny_launch(const void* W, long long ldw, int is_fp8, const float* 
                          int out_fp32, int sm_count, int groups, int swiglu, float limit, const SkinnyExtra& ex,
                          void* stream) {
   if (T <= 0 || N <= 0) return 0;
-  if (T > kSkinnyMaxT || K % 16 || K > 16384) return -1;
+  if (T > kSkinnyMaxT && !(T <= kSkinnyMmaMaxTokens && !ex.route && stk_skinny_mma_enabled())) return -1;
+  if (K % 16 || K > 16384) return -1;
   const long long ldw_bytes = ldw * (is_fp8 ? 1 : 2);
   if (ldw_bytes % 16 || (reinterpret_cast<uintptr_t>(W) & 15)) return -2;
   // five to eight tokens: the eight-token warp-level tensor-core stream (skinny_mma.cuh)

@@ -27,6 +27,8 @@ constexpr int kSmTokens = 8;          // token slots (the mma's N); rows beyond 
 constexpr int kSmRows = 16;           // weight rows per CTA (the mma's M)
 constexpr int kSmWarps = 8;
 constexpr int kSmBatch = 8;           // 64-byte blocks per warp whose loads are in flight together
+constexpr int kSkinnyMmaMaxTokens = 64;
+constexpr long long kSkinnyMmaNarrowBytes = 8ll << 20;
 
 __device__ __forceinline__ void mma_e4m3_16x8x32(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                  uint32_t b0, uint32_t b1) {
@@ -51,7 +53,7 @@ template <bool kFp8, bool kSwiglu>
 __global__ void __launch_bounds__(kSmWarps * 32, 2)
 skinny_mma_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const float* __restrict__ w_scale, int w_scale_ld,
                   const __nv_bfloat16* __restrict__ x, long long ldx, void* __restrict__ out, long long ldo, int N, int K,
-                  int out_fp32, int group_rows, float limit, int T, const SkinnyExtra ex) {
+                  int out_fp32, int group_rows, float limit, int T_all, const SkinnyExtra ex) {
   extern __shared__ __align__(16) uint8_t sm_raw[];
   const int row_bytes = kFp8 ? K : 2 * K;
   const int xstride = row_bytes + 64;
@@ -67,7 +69,10 @@ skinny_mma_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const floa
   const int n0 = blockIdx.x * kSmRows;
   const int nblk = row_bytes >> 6;
   const int grp = group_rows > 0 ? n0 / group_rows : 0;
-  const __nv_bfloat16* xg = x + static_cast<long long>(grp) * K;
+  // more than eight tokens (narrow weights only, see the launcher): blockIdx.y picks a group of eight
+  const int t_base = blockIdx.y * kSmTokens;
+  const int T = min(kSmTokens, T_all - t_base);
+  const __nv_bfloat16* xg = x + static_cast<long long>(grp) * K + static_cast<long long>(t_base) * ldx;
 
   uint4 a_lo[kSmBatch], a_hi[kSmBatch];
   float wsc[kSmBatch];
@@ -272,14 +277,15 @@ skinny_mma_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const floa
       const int ne = n0 + 2 * rp;
       if (t < T && ne + 1 < N) {
         const uint32_t d = pack_bf16x2(red[(2 * rp) * kSmTokens + t], red[(2 * rp + 1) * kSmTokens + t]);
-        const long long word = (static_cast<long long>(t) * N + ne) >> 1;
+        const long long word = (static_cast<long long>(t_base + t) * N + ne) >> 1;
         for (int p = 0; p < ex.ll.world; ++p) ll_store(ex.ll, ll_epoch, (ex.ll.rank + p) % ex.ll.world, word, d);
       }
     }
     if (threadIdx.x == 0) ll_push_done(ex.ll, ll_epoch);
   } else if (threadIdx.x < kSmRows * kSmTokens && t_out < T && n < N) {
-    if (out_fp32) reinterpret_cast<float*>(out)[t_out * ldo + n] = v;
-    else reinterpret_cast<__nv_bfloat16*>(out)[t_out * ldo + n] = __float2bfloat16(v);
+    const long long o = static_cast<long long>(t_base + t_out) * ldo + n;
+    if (out_fp32) reinterpret_cast<float*>(out)[o] = v;
+    else reinterpret_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16(v);
   }
 }
 
@@ -287,7 +293,12 @@ skinny_mma_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const floa
 static int skinny_mma_launch(const void* W, long long ldw_bytes, int is_fp8, const float* w_scale, int w_scale_ld,
                              const void* x, long long ldx, void* out, long long ldo, int T, int N, int K, int out_fp32,
                              int groups, int swiglu, float limit, const SkinnyExtra& ex, cudaStream_t st) {
-  if (T < 1 || T > kSmTokens || N % kSmRows || K % 128) return -20;
+  // up to 8 tokens for any weight; up to 64 for narrow bf16 weights (<= 8 MB: router gate, side projections), where the
+  // matrix stays in L2 while each group of eight tokens streams it again and a tensor-core tile would be mostly
+  // padding (fp8 weights would re-quantise the activations in every CTA: measured slower than the tcgen05 tile)
+  const long long w_bytes = static_cast<long long>(N) * (swiglu ? 2 : 1) * K * (is_fp8 ? 1 : 2);
+  if (T < 1 || N % kSmRows || K % 128) return -20;
+  if (T > kSmTokens && (is_fp8 || T > kSkinnyMmaMaxTokens || w_bytes > kSkinnyMmaNarrowBytes)) return -20;
   if ((ldx & 7) || (reinterpret_cast<uintptr_t>(x) & 15)) return -21;       // 16-byte loads of the activation rows
   if (ex.route || ex.k_split > 1) return -22;
   if (ex.norm_w != nullptr && (reinterpret_cast<uintptr_t>(ex.norm_w) & 15)) return -21;
@@ -302,10 +313,10 @@ static int skinny_mma_launch(const void* W, long long ldw_bytes, int is_fp8, con
   const int row_bytes = is_fp8 ? K : 2 * K;
   // activation rows + x scales + reduction buffer + staging (raw bf16 rows for the fp8 path, norm weights)
   const size_t smem = static_cast<size_t>(kSmTokens) * (row_bytes + 64) + (is_fp8 ? kSmTokens * (K / 128) * 4 : 0) +
-                      kSmWarps * kSmRows * kSmTokens * 4 + (is_fp8 ? static_cast<size_t>(T) * 2 * K : 0) +
+                      kSmWarps * kSmRows * kSmTokens * 4 + (is_fp8 ? static_cast<size_t>(T < kSmTokens ? T : kSmTokens) * 2 * K : 0) +
                       (ex.norm_w != nullptr ? 2 * K : 0);
   if (smem > 200 * 1024) return -24;
-  const int grid = N / kSmRows;
+  const dim3 grid(N / kSmRows, (T + kSmTokens - 1) / kSmTokens);
 #define STK_SMMA(F_, S_)                                                                                              \
   {                                                                                                                   \
     static bool configured = false;                                                                                   \
@@ -313,7 +324,7 @@ static int skinny_mma_launch(const void* W, long long ldw_bytes, int is_fp8, con
       cudaFuncSetAttribute(skinny_mma_kernel<F_, S_>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);       \
       configured = true;                                                                                              \
     }                                                                                                                 \
-    launch_pdl(skinny_mma_kernel<F_, S_>, dim3(grid), dim3(kSmWarps * 32), smem, st, (const uint8_t*)W, ldw_bytes,    \
+    launch_pdl(skinny_mma_kernel<F_, S_>, grid, dim3(kSmWarps * 32), smem, st, (const uint8_t*)W, ldw_bytes,    \
                w_scale, w_scale_ld, (const __nv_bfloat16*)x, ldx, out, ldo, N, K, out_fp32, group_rows, limit, T, ex); \
   }
   if (is_fp8) {

@@ -143,14 +143,25 @@ def quant_act(x: torch.Tensor, tag: str = "act") -> QuantAct:
     return QuantAct(q.view(FP8), s)
 
 
-def _skinny_ok(x, t: int, k: int, is_fp8: bool, n: Optional[int] = None) -> bool:
-    if not (isinstance(x, torch.Tensor) and x.is_cuda and t <= SKINNY_MAX_T and x.dtype == BF16):
+SKINNY_NARROW_BYTES = 8 << 20        # bf16 weights this small stay in L2 while groups of eight tokens stream them again
+SKINNY_NARROW_MAX_T = 64
+
+
+def _skinny_ok(x, t: int, k: int, is_fp8: bool, n: Optional[int] = None, rows: Optional[int] = None) -> bool:
+    """Whether the weight-streaming kernels serve x[t, k] @ W[n, k]^T.  `rows`: weight rows actually streamed (2n for the
+    fused SwiGLU pair, n * groups for a block-diagonal weight)."""
+    if not (isinstance(x, torch.Tensor) and x.is_cuda and x.dtype == BF16):
         return False
+    if t > SKINNY_MAX_T:
+        # narrow bf16 weights (router gate, side projections): up to 64 tokens in groups of eight
+        if not (SKINNY_MAX_T >= 8 and not is_fp8 and t <= SKINNY_NARROW_MAX_T and n is not None
+                and (rows or n) * k * 2 <= SKINNY_NARROW_BYTES):
+            return False
     if t > 4:
         # five to eight tokens: the warp-level tensor-core stream (16 weight rows per CTA, 128-value scale groups,
         # eight activation rows in shared memory)
         return (k % 128 == 0 and (n is None or n % 16 == 0) and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
-                and 8 * ((k if is_fp8 else 2 * k) + 64) + 8 * (k // 128) * 4 + 4096 + (2 * k * t if is_fp8 else 0) + 2 * k
+                and 8 * ((k if is_fp8 else 2 * k) + 64) + 8 * (k // 128) * 4 + 4096 + (2 * k * min(t, 8) if is_fp8 else 0) + 2 * k
                 <= 200 * 1024)
     # a lane holds at most 32 16-byte chunks of a weight row: K <= 16384 for fp8, K <= 8192 for bf16
     return k % 16 == 0 and k <= (16384 if is_fp8 else 8192) and _skinny_rows(t) * k * 2 <= 160 * 1024
@@ -172,7 +183,7 @@ def linear(x, lw: LinearWeight, out: Optional[torch.Tensor] = None, out_dtype=BF
     `LLPending` is returned instead of a tensor (row-parallel layers at decode sizes)."""
     if (norm is not None or ll is not None) and not isinstance(x, QuantAct) and x.is_cuda:
         t0, (n0, k0) = x.shape[0], lw.w.shape
-        if groups == 1 and ar_ctx is None and out_dtype == BF16 and _skinny_ok(x, t0, k0, lw.is_fp8, n0 // max(groups, 1)) and (ll is None or n0 % 2 == 0):
+        if groups == 1 and ar_ctx is None and out_dtype == BF16 and _skinny_ok(x, t0, k0, lw.is_fp8, n0 // max(groups, 1), n0) and (ll is None or n0 % 2 == 0):
             o = out if out is not None else (None if ll is not None else torch.empty(t0, n0, dtype=BF16, device=x.device))
             _lib.call("stk_skinny_linear_fused", lw.w, lw.w.stride(0), 1 if lw.is_fp8 else 0, lw.scale,
                       lw.scale.stride(0) if lw.is_fp8 else 0, x, x.stride(0), o, o.stride(0) if o is not None else 0, t0, n0, k0,
@@ -216,7 +227,7 @@ def linear(x, lw: LinearWeight, out: Optional[torch.Tensor] = None, out_dtype=BF
         return y
     if out is None:
         out = torch.empty(t, n, dtype=out_dtype, device=dev)
-    if xa is None and ar_ctx is None and _skinny_ok(x, t, k, lw.is_fp8, n // max(groups, 1)):
+    if xa is None and ar_ctx is None and _skinny_ok(x, t, k, lw.is_fp8, n // max(groups, 1), n):
         # one to four tokens: weight-streaming kernel, activations unquantised
         _lib.call("stk_skinny_linear", lw.w, lw.w.stride(0), 1 if lw.is_fp8 else 0, lw.scale,
                   lw.scale.stride(0) if lw.is_fp8 else 0, x, x.stride(0), out, out.stride(0), t, n, k,
@@ -297,7 +308,7 @@ def linear_swiglu(x: torch.Tensor, lw13: LinearWeight, limit: float) -> Optional
     if not x.is_cuda or t > SKINNY_MAX_T or x.dtype != BF16 or k % 16 or k > 8192 or n2 % 2 or _skinny_rows(t) * k * 2 > 160 * 1024:
         return None
     i = n2 // 2
-    if t > 4 and not _skinny_ok(x, t, k, lw13.is_fp8, i):
+    if t > 4 and not _skinny_ok(x, t, k, lw13.is_fp8, i, n2):
         return None
     if lw13.is_fp8 and i % 128:
         return None

@@ -628,6 +628,33 @@ def test_skinny_mma_linear_five_to_eight_tokens(dtype, T, N, K, monkeypatch):
     _lib.check_status()
 
 
+@pytest.mark.parametrize("T", [9, 16, 33, 64])
+@pytest.mark.parametrize("N,K", [(256, 4096), (576, 4096), (1024, 1536)])
+def test_skinny_mma_narrow_weights_up_to_64_tokens(T, N, K):
+    """Router gate / side projections at decode batch sizes: the bf16 weight (<= 8 MB) is streamed once per group of
+    eight tokens instead of through a mostly empty tensor-core tile with split-K."""
+    torch.manual_seed(T * 7 + N)
+    x = torch.randn(T, K, device=dev()).to(BF16)
+    lw = Fn.LinearWeight((torch.randn(N, K, device=dev()) * 0.05).to(BF16))
+    assert Fn._skinny_ok(x, T, K, False, N, N)
+    before = _lib.launch_count
+    out = Fn.linear(x, lw, out_dtype=F32)
+    assert _lib.launch_count == before + 1
+    ref = x.float() @ lw.dequant().t()
+    assert rel_err(out, ref) < 2e-3
+    assert (out - ref).abs().max().item() < 0.02 * ref.abs().max().item()
+    nw = (1 + 0.1 * torch.randn(K, device=dev())).to(BF16)
+    xn = R.rms_norm(x, nw, 1e-6).to(BF16)
+    assert rel_err(Fn.linear(x, lw, norm=(nw, 1e-6)), xn.float() @ lw.dequant().t()) < 1e-2
+    # fp8 weights at these batch sizes stay on the tensor-core tile
+    lw8 = Fn.LinearWeight.from_master(torch.randn(N, K, device=dev()) * 0.05, "fp8", dev())
+    assert not Fn._skinny_ok(x, T, K, True, N, N)
+    ref8 = R.dequant_fp8_group128_act(*R.quant_fp8_group128_act(x)) @ lw8.dequant().t()
+    assert rel_err(Fn.linear(x, lw8, out_dtype=F32), ref8) < 2e-3
+    torch.cuda.synchronize()
+    _lib.check_status()
+
+
 @pytest.mark.parametrize("dtype", ["bf16", "fp8"])
 def test_skinny_mma_grouped_and_swiglu(dtype, monkeypatch):
     monkeypatch.setattr(Fn, "SKINNY_MAX_T", 8)
