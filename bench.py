@@ -140,7 +140,10 @@ def main() -> None:
             "per_layer_us": res["decode_c1_ms"] * 1e3 / res["layers"],
             "layer_tok_s": res["decode_c1_tok_s"] * res["layers"],
             "spread": {"ms_per_step_min": res["decode_c1_repeats"]["dev_ms_min"],
-                       "ms_per_step_max": res["decode_c1_repeats"]["dev_ms_max"]},
+                       "ms_per_step_max": res["decode_c1_repeats"]["dev_ms_max"],
+                       # the same K steps as seen by the fastest and the slowest rank (median repeat): rank skew
+                       "ms_per_step_fastest_rank": res["decode_c1_repeats"]["dev_ms_fastest_rank"],
+                       "ms_per_step_slowest_rank": res["decode_c1_repeats"]["dev_ms_slowest_rank"]},
             "clocks": clocks.summary(),
             "e2e": {"value": res["e2e_tok_s"], "unit": "tok/s", "h2d_bytes_per_step": res["h2d_bytes"],
                     "d2h_bytes_per_step": res["d2h_bytes"], "ms_per_step": res["e2e_ms"],

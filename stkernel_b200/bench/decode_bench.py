@@ -119,7 +119,9 @@ def timed_steps(eng: Engine, steps: int, world: int, forced_vocab: int, n_rows: 
     wall = (time.perf_counter() - t0) * 1e3 / steps
     dev_ms = e0.elapsed_time(e1) / steps
     _sync(world)
-    return _max_over_ranks(dev_ms, world, eng.device), _max_over_ranks(wall, world, eng.device)
+    # third value: the fastest rank's device time (the ranks run the same step; the gap to the maximum is rank skew)
+    return (_max_over_ranks(dev_ms, world, eng.device), _max_over_ranks(wall, world, eng.device),
+            _min_over_ranks(dev_ms, world, eng.device))
 
 
 def timed_repeats(eng: Engine, steps: int, world: int, vocab: int, n_rows: int, host_roundtrip: bool,
@@ -127,13 +129,15 @@ def timed_repeats(eng: Engine, steps: int, world: int, vocab: int, n_rows: int, 
     """Repeats of exactly `steps` steps until the phase has run for `min_seconds` (at least 3, at most `max_repeats`;
     the count follows the first repeat's time, which every rank knows as the same max-over-ranks number)."""
     first = timed_steps(eng, steps, world, vocab, n_rows, host_roundtrip)
-    per = max(first) * steps / 1e3
+    per = max(first[0], first[1]) * steps / 1e3
     reps = int(min(max_repeats, max(3, -(-min_seconds // max(per, 1e-6)))))
     runs = [first] + [timed_steps(eng, steps, world, vocab, n_rows, host_roundtrip) for _ in range(reps - 1)]
     dev = sorted(r[0] for r in runs)
     wall = sorted(r[1] for r in runs)
+    mid = sorted(runs, key=lambda r: r[0])[len(runs) // 2]
     return {"dev_ms": dev[len(dev) // 2], "wall_ms": wall[len(wall) // 2], "repeats": len(runs),
-            "dev_ms_min": dev[0], "dev_ms_max": dev[-1], "wall_ms_min": wall[0], "wall_ms_max": wall[-1]}
+            "dev_ms_min": dev[0], "dev_ms_max": dev[-1], "wall_ms_min": wall[0], "wall_ms_max": wall[-1],
+            "dev_ms_fastest_rank": mid[2], "dev_ms_slowest_rank": mid[0]}
 
 
 def _engine(mcfg, n_gpus: int, rank: int, dev, comm, weights, fused: bool, max_ctx: int, max_seqs: int, graph_cap: int,

@@ -90,6 +90,7 @@ def main() -> None:
                     help="single process only: build rank 0's weight shard of a tensor/expert-parallel group of this "
                          "size and run it alone, without collectives (the sums are incomplete, so the values mean "
                          "nothing; the kernels, their shapes and their times are those of one rank of that group)")
+    ap.add_argument("--index-cache", type=int, default=1, help="0: every ratio-4 layer computes its own top-k (IndexCache off)")
     ap.add_argument("--spec", type=int, default=0, help="decode mode: DSpark speculative steps with this many draft tokens "
                                                         "(3 draft layers; every step verifies conc * (spec + 1) rows)")
     a = ap.parse_args()
@@ -113,10 +114,10 @@ def main() -> None:
         comm = Communicator(device=dev, use_symm=True)
     spec_on = a.spec > 0 and a.mode == "decode"
     if spec_on:
-        cfg = flash_config(num_layers=a.layers, n_mtp_layers=3,
+        cfg = flash_config(num_layers=a.layers, n_mtp_layers=3, use_index_cache=bool(a.index_cache),
                            dspark_target_layer_ids=(a.layers // 4, a.layers // 2, a.layers - 1))
     else:
-        cfg = flash_config(num_layers=a.layers)
+        cfg = flash_config(num_layers=a.layers, use_index_cache=bool(a.index_cache))
     shard = a.shard_of if world == 1 else 1
     group = max(world, shard)
     spec_cfg = SpecConfig(method="dspark", num_speculative_tokens=a.spec, markov_topk=512, temperature=0.6) if spec_on else SpecConfig()

@@ -497,27 +497,45 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUt
             const int cols_valid = min(128, a.N - tn * 128);
             const bool vec_ok = (cols_valid == 128) && ((a.N & 3) == 0) && (a.out_vec_ok || a.ar_enabled);
             if (vec_ok) {
-              for (int v = et2; v < rows_valid * 32; v += nthr2) {
-                const int r = v >> 5, c4 = (v & 31) * 4;
-                const int t = tt * BT + r;
-                float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+              // four output vectors per thread at a time, so that 4 x (unrolled splits) loads are in flight: one vector
+              // at a time left a reducing CTA at a few dozen GB/s
+              const int total = rows_valid * 32;
+              for (int v0 = et2; v0 < total; v0 += nthr2 * 4) {
+                float4 s4[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) s4[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
                 for (int p = 0; p < a.splits; ++p) {
-                  const float4 x = __ldcg(reinterpret_cast<const float4*>(
-                      &a.workspace[(static_cast<long long>(p) * a.T + t) * a.N + tn * 128 + c4]));
-                  s4.x += x.x; s4.y += x.y; s4.z += x.z; s4.w += x.w;
-                }
-                if (a.ar_enabled) {
-                  if constexpr (Cfg::kArTileBytes > 0) {
-                    __nv_bfloat162* d = reinterpret_cast<__nv_bfloat162*>(ar_tile + r * 128 + c4);
-                    d[0] = __floats2bfloat162_rn(s4.x, s4.y);
-                    d[1] = __floats2bfloat162_rn(s4.z, s4.w);
+#pragma unroll
+                  for (int u = 0; u < 4; ++u) {
+                    const int v = v0 + u * nthr2;
+                    if (v < total) {
+                      const int r = v >> 5, c4 = (v & 31) * 4;
+                      const float4 x = __ldcg(reinterpret_cast<const float4*>(
+                          &a.workspace[(static_cast<long long>(p) * a.T + tt * BT + r) * a.N + tn * 128 + c4]));
+                      s4[u].x += x.x; s4[u].y += x.y; s4[u].z += x.z; s4[u].w += x.w;
+                    }
                   }
-                } else if (a.out_fp32) {
-                  *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + t * a.ldo + tn * 128 + c4) = s4;
-                } else {
-                  __nv_bfloat162* d = reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(a.out) + t * a.ldo + tn * 128 + c4);
-                  d[0] = __floats2bfloat162_rn(s4.x, s4.y);
-                  d[1] = __floats2bfloat162_rn(s4.z, s4.w);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                  const int v = v0 + u * nthr2;
+                  if (v >= total) break;
+                  const int r = v >> 5, c4 = (v & 31) * 4;
+                  const int t = tt * BT + r;
+                  if (a.ar_enabled) {
+                    if constexpr (Cfg::kArTileBytes > 0) {
+                      __nv_bfloat162* d = reinterpret_cast<__nv_bfloat162*>(ar_tile + r * 128 + c4);
+                      d[0] = __floats2bfloat162_rn(s4[u].x, s4[u].y);
+                      d[1] = __floats2bfloat162_rn(s4[u].z, s4[u].w);
+                    }
+                  } else if (a.out_fp32) {
+                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + t * a.ldo + tn * 128 + c4) = s4[u];
+                  } else {
+                    __nv_bfloat162* d = reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(a.out) + t * a.ldo + tn * 128 + c4);
+                    d[0] = __floats2bfloat162_rn(s4[u].x, s4[u].y);
+                    d[1] = __floats2bfloat162_rn(s4[u].z, s4[u].w);
+                  }
                 }
               }
             } else {
@@ -899,6 +917,12 @@ static int gemm_launch(const void* W, long long ldw, const void* X, long long ld
     return cudaGetLastError() == cudaSuccess ? 0 : -4;
   }
   int bt = stk_gemm_pick_bt(T, is_fp8);
+  if (!is_fp8 && T > 128 && groups == 1) {
+    // mid-size bf16 problems: split-K through the fp32 workspace costs more than it gains above 128 tokens
+    // (measured), so parallelism comes from narrower token tiles until about 0.7 x the SMs have a tile
+    const int wt = (N + 127) / 128;
+    while (bt > 64 && wt * ((T + bt - 1) / bt) * 10 < sm_count * 7) bt /= 2;
+  }
   if (bt_override == 16 || bt_override == 32 || bt_override == 64 || bt_override == 128) bt = bt_override;
   CUtensorMap tw, tx;
   if (make_tmap_2d(&tw, W, es, N, K, ldw, 128) != 0) return -13;

@@ -45,10 +45,12 @@ def test_tiny_logits_match_oracle(dense, kv):
     got = torch.cat([lg1, lg2]).float().cpu()
     ref = oracle.logits(p)
     rel = ((got - ref).norm() / ref.norm()).item()
-    assert rel < (0.08 if dense == "bf16" else 0.12), rel
-    # the argmax agrees on most positions
     agree = (got.argmax(-1) == ref.argmax(-1)).float().mean().item()
-    assert agree > 0.8, agree
+    print(f"oracle check {dense}/{kv}: rel {rel:.4f} argmax {agree:.3f}")
+    # measured on B200: bf16 1.2 % / 0.986, fp8 (weights, activations and KV all quantised; the oracle keeps the
+    # activations unquantised) 8.7 % / 0.87 over three layers of a 256-wide model with nearly flat random logits
+    assert rel < (0.02 if dense == "bf16" else 0.12), rel
+    assert agree > (0.95 if dense == "bf16" else 0.8), agree
 
 
 def test_graph_replay_matches_eager_and_is_deterministic():
@@ -152,3 +154,38 @@ def test_dspark_step_graph_replay_matches_eager():
         if cap:
             assert any(isinstance(k, tuple) and k[0] == "spec" for k in eng._graphs)
     assert outs[0] == outs[1]
+
+
+def test_dspark_text_does_not_depend_on_what_the_drafter_proposes():
+    """Losslessness on the GPU, with the kernels held fixed: two speculative engines that differ only in their proposals
+    (one never accepted, one replaying the other's text so that nearly every draft is accepted) emit the same text for
+    the same seeds.  Both run the same verify-row kernels, so this isolates the accept / rollback / context-insert
+    logic from the kernel-selection differences between 1-row and (1+N)-row steps."""
+    from stkernel_b200.bench.decode_bench import ReplayDrafter
+    from stkernel_b200.config import SpecConfig
+    from stkernel_b200.spec.dspark import build_draft_weights
+    cfg = tiny_config(dense_dtype="bf16", kv_cache_dtype="fp8_ds_mla", expert_dtype="nvfp4", n_mtp_layers=2,
+                      dspark_target_layer_ids=(0, 1), dspark_markov_rank=16)
+    w = init_random_weights(cfg, seed=5)
+    tw = build_model_weights(cfg, DictSource(w), "cuda:0")
+    dw = build_draft_weights(cfg, DictSource(w), tw, "cuda:0")
+    torch.manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,)).tolist() for n in (33, 90)]
+    sc = SchedulerConfig(max_model_len=512, max_num_seqs=4, max_num_batched_tokens=256, graph_cap=0)
+    ec = EngineConfig(model=cfg, sched=sc, spec=SpecConfig(method="dspark", num_speculative_tokens=3, markov_topk=8)).validate()
+
+    def run(override_factory):
+        eng = Engine(ec, tw, "cuda:0", max_context=512, draft_weights=dw)
+        eng.draft_override = override_factory()
+        ids = [eng.add_request(p, SamplingParams(temperature=0.7, seed=40 + i, max_tokens=24)) for i, p in enumerate(prompts)]
+        while eng.has_work():
+            eng.step()
+        torch.cuda.synchronize()
+        _lib.check_status()
+        return [list(eng.requests[i].output) for i in ids], eng.metrics
+
+    never, m0 = run(lambda: (lambda req, drafts: [(cfg.vocab_size - 1)] * len(drafts)))
+    recorded = {40 + i: t for i, t in enumerate(never)}
+    replay, m1 = run(lambda: ReplayDrafter(recorded, cfg.vocab_size, acceptance=(1.0, 1.0, 1.0)))
+    assert m1.spec_num_accepted_tokens > m0.spec_num_accepted_tokens + 10      # the second run really accepted drafts
+    assert replay == never

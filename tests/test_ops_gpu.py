@@ -553,7 +553,7 @@ def test_gemm_grouped_block_diagonal(dtype, T):
         assert rel_err(out[:, g * Ng:(g + 1) * Ng], ref) < 3e-3
 
 
-@pytest.mark.parametrize("T,N,K", [(64, 4096, 8192), (100, 384, 1024), (128, 4096, 2048)])
+@pytest.mark.parametrize("T,N,K", [(64, 4096, 8192), (100, 384, 1024), (128, 4096, 2048), (256, 4096, 8192), (300, 640, 2048)])
 def test_gemm_splitk_wide_tiles(T, N, K):
     torch.manual_seed(3)
     x = torch.randn(T, K, device=dev()).to(BF16)
