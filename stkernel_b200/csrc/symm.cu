@@ -138,6 +138,90 @@ twoshot_ar_kernel(SymmCtx c, const uint4* __restrict__ in, uint4* __restrict__ o
   if (threadIdx.x == 0) *ep = epoch;
 }
 
+// ---- reduce-scatter and all-gather along dim 0 (sequence-parallel prefill) ---------------------------------------
+// The two halves of the two-shot all-reduce as kernels of their own, over the same staging regions.  Because they
+// share those regions with the all-reduce (whose parity scheme assumes a pure sequence of all-reduces), each closes
+// the one window a neighbouring collective could reach: the reduce-scatter ends with a barrier (a rank reads its
+// staging area after the last flag exchange, so a faster rank's next push must wait), the all-gather starts with one
+// (a rank may still be copying a previous result out of the gather area).  A barrier is one flag exchange, about 5 us;
+// these kernels move tens of megabytes.
+constexpr int kRsKind = 5, kAgCollKind = 6, kBarKind = 7;
+constexpr int kAgBarBlock0 = 1024;            // barrier flags of the all-gather live beside those of the reduce-scatter
+
+__device__ __forceinline__ bool block_flag_exchange(const SymmCtx& c, int kind, int block, uint32_t epoch, int* ok_s,
+                                                    int* status, int detail) {
+  __syncthreads();
+  if (threadIdx.x < c.world) {
+    __threadfence_system();      // cumulative with the barrier: every thread's stores precede the flag
+    st_release_sys(flag_ptr(c, threadIdx.x, kind, block, c.rank), epoch);
+  }
+  __syncthreads();
+  if (threadIdx.x < c.world) {
+    if (!wait_flag(flag_ptr(c, c.rank, kind, block, threadIdx.x), epoch, c.spin_budget, status, detail + threadIdx.x)) *ok_s = 0;
+  }
+  __syncthreads();
+  return *ok_s != 0;
+}
+
+// in: [world * chunk_vecs] (chunk p is meant for rank p); out: [chunk_vecs] = sum over ranks of their chunk `rank`.
+__global__ void __launch_bounds__(512)
+symm_reduce_scatter_kernel(SymmCtx c, const uint4* __restrict__ in, uint4* __restrict__ out, long long chunk_vecs,
+                           int* status) {
+  __shared__ int ok_s;
+  const int b = blockIdx.x, nb = gridDim.x;
+  uint32_t* ep = epoch_ptr(c, kRsKind, b);
+  const uint32_t epoch = *ep + 1;
+  const int par = epoch & 1;
+  const long long per = (chunk_vecs + nb - 1) / nb;
+  const long long o0 = b * per, o1 = min(chunk_vecs, o0 + per);
+  if (threadIdx.x == 0) ok_s = 1;
+  for (int p = 0; p < c.world; ++p) {
+    const int peer = (c.rank + p) % c.world;
+    uint4* dst = reinterpret_cast<uint4*>(c.base[peer] + c.off_rs) + (static_cast<long long>(par) * c.world + c.rank) * chunk_vecs;
+    const uint4* src = in + static_cast<long long>(peer) * chunk_vecs;
+    for (long long i = o0 + threadIdx.x; i < o1; i += blockDim.x) dst[i] = __ldg(src + i);
+  }
+  if (block_flag_exchange(c, kRsKind, b, epoch, &ok_s, status, 700)) {
+    const uint4* slots = reinterpret_cast<const uint4*>(c.base[c.rank] + c.off_rs) + static_cast<long long>(par) * c.world * chunk_vecs;
+    for (long long i = o0 + threadIdx.x; i < o1; i += blockDim.x) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int r = 0; r < c.world; ++r) add_bf16x8(acc, __ldcg(slots + r * chunk_vecs + i));
+      out[i] = pack_bf16x8(acc);
+    }
+  }
+  block_flag_exchange(c, kBarKind, b, epoch, &ok_s, status, 720);      // nobody pushes again before everybody has read
+  if (threadIdx.x == 0) *ep = epoch;
+}
+
+// shard: [shard_vecs]; out: [world * shard_vecs], rank-major.
+__global__ void __launch_bounds__(512)
+symm_all_gather_kernel(SymmCtx c, const uint4* __restrict__ shard, uint4* __restrict__ out, long long shard_vecs,
+                       int* status) {
+  __shared__ int ok_s;
+  const int b = blockIdx.x, nb = gridDim.x;
+  uint32_t* ep = epoch_ptr(c, kAgCollKind, b);
+  const uint32_t epoch = *ep + 1;
+  const int par = epoch & 1;
+  const long long per = (shard_vecs + nb - 1) / nb;
+  const long long o0 = b * per, o1 = min(shard_vecs, o0 + per);
+  if (threadIdx.x == 0) ok_s = 1;
+  if (block_flag_exchange(c, kBarKind, kAgBarBlock0 + b, epoch, &ok_s, status, 740)) {      // everybody has left the previous collective
+    for (int p = 0; p < c.world; ++p) {
+      const int peer = (c.rank + p) % c.world;
+      uint4* dst = reinterpret_cast<uint4*>(c.base[peer] + c.off_ag + static_cast<long long>(par) * c.twoshot_bytes) +
+                   static_cast<long long>(c.rank) * shard_vecs;
+      for (long long i = o0 + threadIdx.x; i < o1; i += blockDim.x) dst[i] = __ldg(shard + i);
+    }
+    if (block_flag_exchange(c, kAgCollKind, b, epoch, &ok_s, status, 760)) {
+      const uint4* ag = reinterpret_cast<const uint4*>(c.base[c.rank] + c.off_ag + static_cast<long long>(par) * c.twoshot_bytes);
+      for (int r = 0; r < c.world; ++r)
+        for (long long i = o0 + threadIdx.x; i < o1; i += blockDim.x) out[r * shard_vecs + i] = __ldcg(ag + r * shard_vecs + i);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *ep = epoch;
+}
+
 // A wait that nothing satisfies, on a local flag: exercises the timeout path without any peer.
 __global__ void flag_timeout_probe_kernel(const uint32_t* flag, uint32_t epoch, uint32_t budget, int* status) {
   if (threadIdx.x == 0) {
@@ -208,6 +292,30 @@ STK_API int stk_twoshot_allreduce(const void* ctx, const void* in, void* out, lo
   const SymmCtx* c = reinterpret_cast<const SymmCtx*>(ctx);
   if (n_bytes % 16 || n_bytes > c->twoshot_bytes || nblocks < 1 || nblocks > kMaxArBlocks) return -1;
   twoshot_ar_kernel<<<nblocks, 512, 0, (cudaStream_t)stream>>>(*c, (const uint4*)in, (uint4*)out, n_bytes / 16, 1, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// out[chunk] = sum over ranks of in[rank * chunk ..]; total_bytes = world * chunk bytes <= the two-shot capacity.
+STK_API int stk_symm_reduce_scatter(const void* ctx, const void* in, void* out, long long total_bytes, int nblocks,
+                                    int* status, void* stream) {
+  const SymmCtx* c = reinterpret_cast<const SymmCtx*>(ctx);
+  if (total_bytes <= 0 || total_bytes % (16ll * c->world) || total_bytes > c->twoshot_bytes || nblocks < 1 ||
+      nblocks > kMaxArBlocks)
+    return -1;
+  symm_reduce_scatter_kernel<<<nblocks, 512, 0, (cudaStream_t)stream>>>(*c, (const uint4*)in, (uint4*)out,
+                                                                         total_bytes / c->world / 16, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// out[rank-major] = every rank's shard; world * shard_bytes <= the two-shot capacity.
+STK_API int stk_symm_all_gather(const void* ctx, const void* shard, void* out, long long shard_bytes, int nblocks,
+                                int* status, void* stream) {
+  const SymmCtx* c = reinterpret_cast<const SymmCtx*>(ctx);
+  if (shard_bytes <= 0 || shard_bytes % 16 || shard_bytes * c->world > c->twoshot_bytes || nblocks < 1 ||
+      nblocks > kMaxArBlocks)
+    return -1;
+  symm_all_gather_kernel<<<nblocks, 512, 0, (cudaStream_t)stream>>>(*c, (const uint4*)shard, (uint4*)out, shard_bytes / 16,
+                                                                     status);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 

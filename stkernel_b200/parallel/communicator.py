@@ -10,6 +10,8 @@ overlay/dsv4_oneshot_shim.py:136-162).
 """
 from __future__ import annotations
 
+import os
+
 from typing import List, Optional, Sequence
 
 import torch
@@ -30,6 +32,8 @@ class Communicator:
         self.fuse_gemm = fuse_gemm
         self.disabled_reason: Optional[str] = None
         self.calls = {"oneshot": 0, "twoshot": 0, "nccl": 0}
+        # sequence-parallel all-gather / reduce-scatter through this library's kernels (STK_OWN_GATHER_SCATTER=0: NCCL)
+        self.own_gather_scatter = os.environ.get("STK_OWN_GATHER_SCATTER", "1") != "0"
         if use_symm and self.device.type == "cuda" and self.world_size > 1:
             try:
                 from .symm import SymmetricAllReduce
@@ -80,6 +84,10 @@ class Communicator:
     def all_gather_dim0(self, x: torch.Tensor) -> torch.Tensor:
         if self.world_size == 1:
             return x
+        if self.symm is not None and x.is_cuda and self.own_gather_scatter:
+            out = self.symm.all_gather(x.contiguous())
+            if out is not None:
+                return out
         self.calls["nccl"] += 1
         out = torch.empty(self.world_size * x.shape[0], *x.shape[1:], dtype=x.dtype, device=x.device)
         dist.all_gather_into_tensor(out, x.contiguous(), group=self.group)
@@ -97,9 +105,13 @@ class Communicator:
     def reduce_scatter_dim0(self, x: torch.Tensor) -> torch.Tensor:
         if self.world_size == 1:
             return x
-        self.calls["nccl"] += 1
         assert x.shape[0] % self.world_size == 0
         n = x.shape[0] // self.world_size
+        if self.symm is not None and x.is_cuda and self.own_gather_scatter:
+            out = self.symm.reduce_scatter(x.contiguous())
+            if out is not None:
+                return out
+        self.calls["nccl"] += 1
         if not x.is_cuda:
             # gloo has no reduce-scatter: sum everywhere, keep this rank's rows
             y = x.contiguous().clone()

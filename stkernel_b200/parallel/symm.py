@@ -27,7 +27,7 @@ class LLExchange:
     `words` = capacity per source rank in 8-byte words (two bf16 values each): rows x hidden / 2."""
 
     def __init__(self, bases: List[int], counters: torch.Tensor, words: int, rank: int, world: int,
-                 spin_budget: int = 2_000_000, keep=None):
+                 spin_budget: int = 16_000_000, keep=None):
         L = _lib.lib()
         self.ctx = (ctypes.c_ubyte * L.stk_ll_ctx_size())()
         arr = (ctypes.c_longlong * world)(*bases)
@@ -125,7 +125,7 @@ class SymmetricAllReduce:
 
     LL_ROWS, LL_HIDDEN = 64, 8192            # the folded all-reduce holds up to 64 rows of 8192 values per rank
 
-    def __init__(self, comm, max_bytes: int = 64 * _MB, oneshot_bytes: int = 2 * _MB, spin_budget: int = 4_000_000,
+    def __init__(self, comm, max_bytes: int = 64 * _MB, oneshot_bytes: int = 2 * _MB, spin_budget: int = 16_000_000,
                  user_bytes: int = 0):
         self.comm = comm
         self.world = comm.world_size
@@ -177,6 +177,38 @@ class SymmetricAllReduce:
             raise _lib.KernelError(f"symmetric all-reduce launch returned {rc}")
         _lib.launch_count += 1
         return x
+
+    def reduce_scatter(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        """x [world * n, ...] bf16 -> this rank's [n, ...] summed over ranks (own kernel over the two-shot staging
+        area); None when this path does not apply."""
+        nbytes = x.numel() * x.element_size()
+        if (not self.enabled or x.dtype != torch.bfloat16 or not x.is_contiguous() or nbytes > self.twoshot_max
+                or x.data_ptr() % 16
+                or nbytes % (16 * self.world) or x.shape[0] % self.world):
+            return None
+        out = torch.empty(x.shape[0] // self.world, *x.shape[1:], dtype=x.dtype, device=x.device)
+        rc = _lib.lib().stk_symm_reduce_scatter(self.ctx, x.data_ptr(), out.data_ptr(), nbytes, self.TWOSHOT_BLOCKS,
+                                                 _lib.status_buffer().data_ptr(), _lib.stream())
+        if rc != 0:
+            raise _lib.KernelError(f"symmetric reduce-scatter launch returned {rc}")
+        _lib.launch_count += 1
+        self.comm.calls["own_rs"] = self.comm.calls.get("own_rs", 0) + 1
+        return out
+
+    def all_gather(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        """x [n, ...] -> [world * n, ...] rank-major (own kernel); None when this path does not apply."""
+        nbytes = x.numel() * x.element_size()
+        if (not self.enabled or not x.is_contiguous() or nbytes % 16 or nbytes * self.world > self.twoshot_max
+                or nbytes == 0 or x.data_ptr() % 16):
+            return None
+        out = torch.empty(self.world * x.shape[0], *x.shape[1:], dtype=x.dtype, device=x.device)
+        rc = _lib.lib().stk_symm_all_gather(self.ctx, x.data_ptr(), out.data_ptr(), nbytes, self.TWOSHOT_BLOCKS,
+                                             _lib.status_buffer().data_ptr(), _lib.stream())
+        if rc != 0:
+            raise _lib.KernelError(f"symmetric all-gather launch returned {rc}")
+        _lib.launch_count += 1
+        self.comm.calls["own_ag"] = self.comm.calls.get("own_ag", 0) + 1
+        return out
 
     def self_test(self) -> None:
         """Lock-step comparison with the library collective at a few sizes; raises on mismatch."""

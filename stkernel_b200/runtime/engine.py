@@ -720,6 +720,15 @@ def _capture_stream(device) -> "torch.cuda.Stream":
     return _CAPTURE_STREAMS[idx]
 
 
+def _after_capture_rendezvous(eng: "Engine") -> None:
+    """Capturing a step takes a rank-dependent amount of host time (hundreds of milliseconds for a deep model).  The
+    kernels of the first replay poll their peers with a bounded budget, so the ranks meet on the host before any of
+    them replays: a rank that is still capturing is not mistaken for a dead one."""
+    comm = eng.model.comm
+    if comm is not None and getattr(comm, "world_size", 1) > 1 and eng.device.type == "cuda":
+        comm.barrier()
+
+
 class SpecGraph:
     """A captured speculative pure-decode step: every request verifies 1 + N rows and drafts its next block."""
 
@@ -737,6 +746,7 @@ class SpecGraph:
         with torch.cuda.graph(self.graph, stream=_capture_stream(eng.device)):
             self.out = eng._spec_device(t, n_req, ns, nb, rows_bucket)
         self.launches_per_replay = _lib.launch_count - before
+        _after_capture_rendezvous(eng)
 
     def replay(self) -> torch.Tensor:
         from ..ops import _lib
@@ -765,6 +775,7 @@ class DecodeGraph:
         with torch.cuda.graph(self.graph, stream=_capture_stream(eng.device)):
             self.out = eng._run_model(bucket, bucket, bucket, rows_bucket, identity_rows=True)
         self.launches_per_replay = _lib.launch_count - before
+        _after_capture_rendezvous(eng)
 
     def replay(self) -> torch.Tensor:
         from ..ops import _lib

@@ -100,6 +100,36 @@ def main():
         out["allreduce"].append({"bytes": nb, "ours_us": ours, "nccl_us": nccl, "rel_err": err, "nvlink_bytes_sent": sent,
                                  "achieved_nvlink_gbs": sent / ours * 1e-3, "frac_of_measured_link": roof / ours,
                                  "frac_of_900gbs": sent / 900e9 * 1e6 / ours})
+    # ---- reduce-scatter / all-gather along dim 0 (sequence-parallel prefill), interleaved with all-reduces ----
+    out["rs_ag"] = []
+    for rows, hdim in ((world * 8, 4096), (1024, 4096), (4096, 4096)):
+        rows = rows // world * world
+        x = torch.randn(rows, hdim, device=dev, generator=g).to(torch.bfloat16)
+        ref_rs = torch.empty(rows // world, hdim, dtype=torch.float32, device=dev)
+        dist.reduce_scatter_tensor(ref_rs, x.float())
+        shard = x[: rows // world].contiguous()
+        ref_ag = torch.empty(rows, hdim, dtype=torch.bfloat16, device=dev)
+        dist.all_gather_into_tensor(ref_ag, shard)
+        for rep in range(3):                                   # back to back and around an all-reduce: the shared staging areas
+            got_rs = comm.symm.reduce_scatter(x)
+            comm.all_reduce(x.clone())
+            got_ag = comm.symm.all_gather(shard)
+            got_rs2 = comm.symm.reduce_scatter(x)
+            got_ag2 = comm.symm.all_gather(shard)
+            torch.cuda.synchronize()
+            _lib.check_status()
+            assert got_rs is not None and got_ag is not None
+            e = ((got_rs.float() - ref_rs).norm() / ref_rs.norm()).item()
+            assert e < 1e-2 and torch.equal(got_rs, got_rs2), ("reduce_scatter", rows, e)
+            assert torch.equal(got_ag, ref_ag) and torch.equal(got_ag2, ref_ag), ("all_gather", rows)
+        nb = rows * hdim * 2
+        o_rs = torch.empty(rows // world, hdim, dtype=torch.bfloat16, device=dev)
+        o_ag = torch.empty(rows, hdim, dtype=torch.bfloat16, device=dev)
+        out["rs_ag"].append({"bytes": nb, "own_reduce_scatter_us": timed(lambda: comm.symm.reduce_scatter(x)),
+                             "nccl_reduce_scatter_us": timed(lambda: dist.reduce_scatter_tensor(o_rs, x)),
+                             "own_all_gather_us": timed(lambda: comm.symm.all_gather(shard)),
+                             "nccl_all_gather_us": timed(lambda: dist.all_gather_into_tensor(o_ag, shard)),
+                             "rs_rel_err": e})
     # ---- GEMM fused with the all-reduce (row-parallel layer) ----
     K_total, N = 8192, 4096
     k = K_total // world
