@@ -993,9 +993,10 @@ STK_API int stk_gemm(const void* W, long long ldw, const void* X, long long ldx,
 // Plain GEMM with an explicit token-tile width (16/32/64/128): narrow weights with many tokens get their parallelism
 // from token tiles instead of split-K (e.g. the 24-row hyper-connection mix projection over [T, 16384]).
 STK_API int stk_gemm_tile(const void* W, long long ldw, const void* X, long long ldx, void* out, long long ldo, int T, int N,
-                          int K, int out_fp32, int bt, int* status, int sm_count, void* stream) {
-  return gemm_launch(W, ldw, X, ldx, out, ldo, T, N, K, 0, out_fp32, nullptr, 0, nullptr, 0, 1, nullptr, nullptr, status,
-                     sm_count, 1, nullptr, nullptr, 0, stream, bt);
+                          int K, int out_fp32, int bt, int splits, float* workspace, int* counters, int* status,
+                          int sm_count, void* stream) {
+  return gemm_launch(W, ldw, X, ldx, out, ldo, T, N, K, 0, out_fp32, nullptr, 0, nullptr, 0, splits < 1 ? 1 : splits,
+                     workspace, counters, status, sm_count, 1, nullptr, nullptr, 0, stream, bt);
 }
 
 // All-gather -> GEMM: X is the gathered [T, K] matrix inside this rank's symmetric region (filled by

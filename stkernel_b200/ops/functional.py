@@ -451,7 +451,14 @@ def mhc_pre(residual: torch.Tensor, fn: torch.Tensor, base: torch.Tensor, scale:
         wcat = _mhc_wcat(fn, n_mix)
         x2d = residual.view(t, hc * h)
         prod = scratch("mhc.gemm", (t, 128), F32, dev)
-        _lib.call("stk_gemm_tile", wcat, wcat.stride(0), x2d, x2d.stride(0), prod, 128, t, 128, hc * h, 1, 32,
+        # one weight tile: the parallelism is token tiles x K splits (a sequence-parallel rank holds a few hundred tokens)
+        tiles = (t + 31) // 32
+        splits = max(1, min(16, _lib.sm_count() // tiles, (hc * h) // 256))
+        ws = cnt = None
+        if splits > 1:
+            ws = scratch("mhc.gemm.splitk", (splits * t * 128,), F32, dev)
+            cnt = scratch("gemm.counters", (4096,), torch.int32, dev, zero=True)
+        _lib.call("stk_gemm_tile", wcat, wcat.stride(0), x2d, x2d.stride(0), prod, 128, t, 128, hc * h, 1, 32, splits, ws, cnt,
                   _lib.status_buffer(), _lib.sm_count(), _lib.stream())
         partial = scratch("mhc.partial", (t * (n_mix + 1),), F32, dev).view(t, n_mix + 1)
         torch.add(prod[:, :n_mix], prod[:, 32:32 + n_mix], out=partial[:, :n_mix])

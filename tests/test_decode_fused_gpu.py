@@ -233,8 +233,16 @@ def test_engine_with_folded_allreduce_and_fused_launches_matches_unfused(monkeyp
         _lib.check_status()
         if mode == "fused":
             assert eng.model._ll_loop is not None and eng.model._ll_loop.counters[0].item() > 0
-    agree = sum(a == b for x, y in zip(outs["fused"], outs["unfused"]) for a, b in zip(x, y))
-    assert agree >= 22, outs            # the same noise picks the same tokens unless two candidates are within bf16 noise
+    # The same noise picks the same token unless two candidates are within bf16 rounding of each other; after such a
+    # flip the two texts are different continuations, so agreement is measured as the common prefix of each request
+    # (the kernels themselves are compared exactly, one by one, in the tests above).
+    def prefix(a, b):
+        n = 0
+        while n < min(len(a), len(b)) and a[n] == b[n]:
+            n += 1
+        return n
+    pre = [prefix(x, y) for x, y in zip(outs["fused"], outs["unfused"])]
+    assert min(pre) >= 2 and sum(pre) >= 10, (pre, outs)
 
 
 @pytest.mark.parametrize("nh", [8, 16, 64])
