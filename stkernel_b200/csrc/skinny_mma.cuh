@@ -28,7 +28,7 @@ constexpr int kSmRows = 16;           // weight rows per CTA (the mma's M)
 constexpr int kSmWarps = 8;
 constexpr int kSmBatch = 8;           // 64-byte blocks per warp whose loads are in flight together
 constexpr int kSkinnyMmaMaxTokens = 64;
-constexpr long long kSkinnyMmaNarrowBytes = 8ll << 20;
+constexpr long long kSkinnyMmaNarrowBytes = 4ll << 20;
 
 __device__ __forceinline__ void mma_e4m3_16x8x32(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                  uint32_t b0, uint32_t b1) {
@@ -293,9 +293,11 @@ skinny_mma_kernel(const uint8_t* __restrict__ W, long long ldw_bytes, const floa
 static int skinny_mma_launch(const void* W, long long ldw_bytes, int is_fp8, const float* w_scale, int w_scale_ld,
                              const void* x, long long ldx, void* out, long long ldo, int T, int N, int K, int out_fp32,
                              int groups, int swiglu, float limit, const SkinnyExtra& ex, cudaStream_t st) {
-  // up to 8 tokens for any weight; up to 64 for narrow bf16 weights (<= 8 MB: router gate, side projections), where the
-  // matrix stays in L2 while each group of eight tokens streams it again and a tensor-core tile would be mostly
-  // padding (fp8 weights would re-quantise the activations in every CTA: measured slower than the tcgen05 tile)
+  // up to 8 tokens for any weight; up to 64 for narrow bf16 weights (<= 4 MB: the router gate), where the matrix stays
+  // in L2 while each group of eight tokens streams it again and a tensor-core tile would be mostly padding.  Not for
+  // fp8 weights (every CTA would re-quantise the activations: measured slower than the tcgen05 tile) and not for
+  // wider ones: their rows x token-groups grid fills every SM and, on the side stream, held back the persistent GEMMs
+  // of the main chain (measured on one GPU at 64 tokens: +12 us on each of 37 fp8 projections per step)
   const long long w_bytes = static_cast<long long>(N) * (swiglu ? 2 : 1) * K * (is_fp8 ? 1 : 2);
   if (T < 1 || N % kSmRows || K % 128) return -20;
   if (T > kSmTokens && (is_fp8 || T > kSkinnyMmaMaxTokens || w_bytes > kSkinnyMmaNarrowBytes)) return -20;

@@ -143,8 +143,11 @@ def quant_act(x: torch.Tensor, tag: str = "act") -> QuantAct:
     return QuantAct(q.view(FP8), s)
 
 
-SKINNY_NARROW_BYTES = 8 << 20        # bf16 weights this small stay in L2 while groups of eight tokens stream them again
+SKINNY_NARROW_BYTES = 4 << 20        # bf16 weights this small (the router gate) stay in L2 while groups of eight tokens stream them again
 SKINNY_NARROW_MAX_T = 64
+# Off by default: one rank's share of an 8-rank group gained 7 % per 64-token step with it (3507 -> 3277 us), the same
+# step of the unsharded 6-layer model on one GPU lost 7 % (10057 -> 10789 us) without any one kernel accounting for it.
+SKINNY_NARROW = _os.environ.get("STK_SKINNY_NARROW", "0") == "1"
 
 
 def _skinny_ok(x, t: int, k: int, is_fp8: bool, n: Optional[int] = None, rows: Optional[int] = None) -> bool:
@@ -154,7 +157,7 @@ def _skinny_ok(x, t: int, k: int, is_fp8: bool, n: Optional[int] = None, rows: O
         return False
     if t > SKINNY_MAX_T:
         # narrow bf16 weights (router gate, side projections): up to 64 tokens in groups of eight
-        if not (SKINNY_MAX_T >= 8 and not is_fp8 and t <= SKINNY_NARROW_MAX_T and n is not None
+        if not (SKINNY_NARROW and SKINNY_MAX_T >= 8 and not is_fp8 and t <= SKINNY_NARROW_MAX_T and n is not None
                 and (rows or n) * k * 2 <= SKINNY_NARROW_BYTES):
             return False
     if t > 4:

@@ -629,10 +629,11 @@ def test_skinny_mma_linear_five_to_eight_tokens(dtype, T, N, K, monkeypatch):
 
 
 @pytest.mark.parametrize("T", [9, 16, 33, 64])
-@pytest.mark.parametrize("N,K", [(256, 4096), (576, 4096), (1024, 1536)])
-def test_skinny_mma_narrow_weights_up_to_64_tokens(T, N, K):
-    """Router gate / side projections at decode batch sizes: the bf16 weight (<= 8 MB) is streamed once per group of
-    eight tokens instead of through a mostly empty tensor-core tile with split-K."""
+@pytest.mark.parametrize("N,K", [(256, 4096), (512, 4096), (1024, 1536)])
+def test_skinny_mma_narrow_weights_up_to_64_tokens(T, N, K, monkeypatch):
+    """The router gate at decode batch sizes: the bf16 weight (<= 4 MB) is streamed once per group of eight tokens
+    instead of through a mostly empty tensor-core tile with split-K (an option: STK_SKINNY_NARROW=1)."""
+    monkeypatch.setattr(Fn, "SKINNY_NARROW", True)
     torch.manual_seed(T * 7 + N)
     x = torch.randn(T, K, device=dev()).to(BF16)
     lw = Fn.LinearWeight((torch.randn(N, K, device=dev()) * 0.05).to(BF16))
