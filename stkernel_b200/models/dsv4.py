@@ -28,7 +28,7 @@ from ..ops import moe as M
 from ..utils.spans import span
 from ..ops.functional import LinearWeight
 from ..ops.scratch import side_branch
-from ..runtime.planning import sp_gather_sizes, split_indexer_prefill_chunks
+from ..runtime.planning import pp_layer_range, sp_gather_sizes, split_indexer_prefill_chunks
 from .dsv4_oracle import index_cache_computes
 from .weights import compressor_slots
 
@@ -270,11 +270,14 @@ class ModelWeights:
     hc_head: Tuple[torch.Tensor, torch.Tensor, torch.Tensor]
     layers: List[LayerWeights]
     vocab_start: int = 0
+    layer_offset: int = 0               # global index of layers[0] (a pipeline stage holds a contiguous range)
 
 
 def build_model_weights(cfg: ModelConfig, src: WeightSource, device, tp_rank: int = 0, tp_size: int = 1,
-                        head_fp8: bool = False, placements=None) -> ModelWeights:
-    """placements: optional list of per-layer expert placements (parallel/eplb.py), None entries = identity."""
+                        head_fp8: bool = False, placements=None, layer_range: Optional[Tuple[int, int]] = None) -> ModelWeights:
+    """placements: optional list of per-layer expert placements (parallel/eplb.py), None entries = identity.
+    layer_range: (lo, hi) of a pipeline stage; only those layers are built (embedding, head and final norm are small
+    next to them and are kept on every stage)."""
     H, V, hc = cfg.hidden_size, cfg.vocab_size, cfg.hc_mult
     g = lambda n, s: _get(src, n, s, device)
     vl = (V + tp_size - 1) // tp_size
@@ -283,12 +286,12 @@ def build_model_weights(cfg: ModelConfig, src: WeightSource, device, tp_rank: in
     head_w = LinearWeight.from_master(head, "fp8", device) if head_fp8 else LinearWeight(head.to(BF16).contiguous())
     layers = [build_layer(cfg, src, f"layers.{li}", li, device, tp_rank, tp_size,
                           placement=placements[li] if placements is not None else None)
-              for li in range(cfg.num_hidden_layers)]
+              for li in range(*(layer_range or (0, cfg.num_hidden_layers)))]
     return ModelWeights(
         embed=g("embed.weight", (V, H)).to(BF16).contiguous(), head=head_w, norm=g("norm.weight", (H,)).to(BF16),
         hc_head=(g("hc_head_fn", (hc, hc * H)).to(F32).contiguous(), g("hc_head_base", (hc,)).to(F32),
                  g("hc_head_scale", (1,)).to(F32)),
-        layers=layers, vocab_start=v0)
+        layers=layers, vocab_start=v0, layer_offset=layer_range[0] if layer_range else 0)
 
 
 # ----------------------------------------------------------------------------
@@ -321,6 +324,7 @@ class DSV4Model:
         self.device = dev
         self.inv = Fn.inv_freq(cfg.qk_rope_head_dim, cfg.rope_theta, dev)
         self.topk_buffer: Optional[torch.Tensor] = None     # IndexCache: shared by consecutive C4A layers
+        self.pipe = None                                     # parallel.pipeline.PipeStage when the model is one stage of several
         self.aux_layers: Tuple[int, ...] = ()
         self.aux_out: List[torch.Tensor] = []
         self.stats = {"sp_steps": 0, "mla_token_parallel_calls": 0}     # which large-step paths ran (tests, debugging)
@@ -709,11 +713,24 @@ class DSV4Model:
             self.stats["sp_steps"] += 1
             share = T // self.tp_size
             ids = ids[self.tp_rank * share:(self.tp_rank + 1) * share]
-        X = Fn.embed_hc(ids, self.w.embed, cfg.hc_mult, cfg.vocab_size)
+        pipe = self.pipe
+        lo = self.w.layer_offset
+        hi = lo + len(self.w.layers)
+        if pipe is None or pipe.first:
+            X = Fn.embed_hc(ids, self.w.embed, cfg.hc_mult, cfg.vocab_size)
+        else:
+            # the streams of this step from the previous stage (its share of the rows when the residual is sharded),
+            # and the shared top-k rows when this stage begins inside an IndexCache group
+            from ..parallel.pipeline import stage_starts_inside_index_group
+            X = pipe.recv_prev((ids.shape[0], cfg.hc_mult, cfg.hidden_size), Fn.cpu_act_dtype() if not ids.is_cuda else BF16,
+                               ids.device)
+            if stage_starts_inside_index_group(cfg, lo, hi):
+                self.topk_buffer = pipe.recv_prev((max(T, 16), cfg.index_topk), torch.int32, ids.device)
         self.aux_out = []
         pend = None
-        last = len(self.w.layers) - 1
-        for li, lw in enumerate(self.w.layers):
+        last = hi - 1
+        for idx, lw in enumerate(self.w.layers):
+            li = lo + idx
             defer = li != last and li not in self.aux_layers
             out = self.layer(li, lw, X, meta, pend, defer, sp)
             if defer:
@@ -722,6 +739,16 @@ class DSV4Model:
                 pend, X = None, out
             if li in self.aux_layers:
                 self.aux_out.append(X.float().mean(1).to(X.dtype))
+        if pipe is not None and not pipe.last:
+            from ..parallel.pipeline import stage_starts_inside_index_group
+            pipe.send_next(X)
+            nlo, nhi = pp_layer_range(cfg.num_hidden_layers, pipe.pp_size, pipe.pp_rank + 1)
+            if stage_starts_inside_index_group(cfg, nlo, nhi):
+                tb = self.topk_buffer
+                if tb is None or tb.shape[0] < max(T, 16):
+                    tb = torch.full((max(T, 16), cfg.index_topk), -1, dtype=torch.int32, device=X.device)
+                pipe.send_next(tb[:max(T, 16)])
+            return X
         if sp:
             X = self.comm.all_gather_dim0(X)
         return X
@@ -760,9 +787,15 @@ class DSV4Model:
                        agreed_status=None) -> torch.Tensor:
         """Sampled tokens for the selected token rows (all rows when logit_rows is None)."""
         X = self.forward_hidden(meta)
+        pipe = self.pipe
+        if pipe is not None and not pipe.last:
+            # an earlier stage: the step's tokens come back from the last one
+            n = logit_rows.shape[0] if logit_rows is not None else meta.token_ids.shape[0]
+            return pipe.broadcast_from_last(torch.zeros(n, dtype=torch.int64, device=meta.token_ids.device))
         if logit_rows is not None:
             X = X.index_select(0, logit_rows)
-        return self.sample(self.head_hidden(X), temp, seed, pos, top_k, top_p, agreed_status)
+        toks = self.sample(self.head_hidden(X), temp, seed, pos, top_k, top_p, agreed_status)
+        return pipe.broadcast_from_last(toks.contiguous()) if pipe is not None else toks
 
     def forward(self, meta: StepMeta, logit_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Logits for the selected token rows (all rows when logit_rows is None)."""

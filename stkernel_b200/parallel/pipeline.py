@@ -1,0 +1,80 @@
+"""Pipeline parallelism: the decoder cut into contiguous stages of layers, one stage per group of ranks.
+
+A stage receives the residual streams of a step from its predecessor, runs its layers over its own KV caches, and
+sends them on; the first stage embeds, the last one runs the head and samples, and the sampled tokens are broadcast
+back so that every stage's scheduler advances identically (lock-step scheduling, as under tensor parallelism).
+With tensor parallelism inside the stages, rank (pp_rank, tp_rank) talks to (pp_rank +- 1, tp_rank): global rank =
+pp_rank * tp_size + tp_rank.
+
+What crosses a stage boundary per step: the streams [T, hc, H] bf16 (the rank's 1/tp of the rows when the residual is
+sequence-parallel) and, when the next stage begins inside an IndexCache group, the shared top-k row list
+[T, index_topk] int32 of the group's computing layer.
+
+Counterpart of the reference's pipeline hooks (overlay/nvidia_model.py:1623-1648 make_empty_intermediate_tensors /
+PPMissingLayer, 1693-1711 stage-local layer ranges, 1823-1824 intermediate tensors in forward); the stage arithmetic is
+`runtime/planning.pp_layer_range`.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..runtime.planning import index_cache_pattern, pp_layer_range
+
+
+@dataclass
+class PipeStage:
+    pp_rank: int
+    pp_size: int
+    tp_rank: int = 0
+    tp_size: int = 1
+    group: Optional[dist.ProcessGroup] = None        # a group that contains every rank of the pipeline (default: world)
+
+    @property
+    def first(self) -> bool:
+        return self.pp_rank == 0
+
+    @property
+    def last(self) -> bool:
+        return self.pp_rank == self.pp_size - 1
+
+    def _global(self, pp_rank: int) -> int:
+        return pp_rank * self.tp_size + self.tp_rank
+
+    def layer_range(self, num_layers: int) -> Tuple[int, int]:
+        return pp_layer_range(num_layers, self.pp_size, self.pp_rank)
+
+    # ---- point to point ------------------------------------------------------------------------------------------
+    def send_next(self, t: torch.Tensor) -> None:
+        dist.send(t.contiguous(), dst=self._global(self.pp_rank + 1), group=self.group)
+
+    def recv_prev(self, shape, dtype, device) -> torch.Tensor:
+        t = torch.empty(shape, dtype=dtype, device=device)
+        dist.recv(t, src=self._global(self.pp_rank - 1), group=self.group)
+        return t
+
+    def broadcast_from_last(self, t: torch.Tensor) -> torch.Tensor:
+        """Every stage ends the step with the last stage's tensor (the sampled tokens)."""
+        # one broadcast per tensor-parallel column: the ranks with this tp_rank form the pipeline
+        src = self._global(self.pp_size - 1)
+        if self.tp_size == 1:
+            dist.broadcast(t, src=src, group=self.group)
+            return t
+        # with tensor parallelism the pipeline's ranks are a strided subset of the world: relay backwards stage by stage
+        if not self.last:
+            dist.recv(t, src=self._global(self.pp_rank + 1), group=self.group)
+        if not self.first:
+            dist.send(t, dst=self._global(self.pp_rank - 1), group=self.group)
+        return t
+
+
+def stage_starts_inside_index_group(cfg, lo: int, hi: int) -> bool:
+    """Whether the first ratio-4 layer of stage [lo, hi) reuses the top-k rows of a layer in an earlier stage."""
+    pat = index_cache_pattern(cfg.compress_ratios, cfg.num_hidden_layers, cfg.index_topk_freq if cfg.use_index_cache else 1)
+    for li in range(lo, hi):
+        if pat[li] is not None:
+            return pat[li] is False
+    return False

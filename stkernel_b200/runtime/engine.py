@@ -226,7 +226,10 @@ class StepBuffers:
 
 class Engine:
     def __init__(self, cfg: EngineConfig, weights: ModelWeights, device, comm=None, tp_rank: int = 0,
-                 max_context: Optional[int] = None, draft_weights=None, mask_token_id: int = 0):
+                 max_context: Optional[int] = None, draft_weights=None, mask_token_id: int = 0, pipe=None):
+        """pipe: a `parallel.pipeline.PipeStage` when this engine is one pipeline stage (its `weights` then hold the
+        stage's layers only, `build_model_weights(layer_range=pipe.layer_range(...))`).  Every stage runs the same
+        scheduler on the same requests; the last stage samples and the tokens are broadcast."""
         cfg.validate()
         self.cfg = cfg
         self.device = torch.device(device)
@@ -242,10 +245,23 @@ class Engine:
             raise ValueError("speculative decoding needs the draft weights")
         # a verify step touches N positions past the accepted prefix and the draft block N more
         self.spec_lookahead = 2 * n_spec + 1 if spec_on else 0
+        if pipe is not None:
+            if pipe.pp_size != cfg.parallel.pp_size:
+                raise ValueError("pipeline stage and ParallelConfig.pp_size disagree")
+            if spec_on:
+                raise ValueError("speculative decoding is not available across pipeline stages")
+            lo, hi = pipe.layer_range(cfg.model.num_hidden_layers)
+            if weights.layer_offset != lo or len(weights.layers) != hi - lo:
+                raise ValueError(f"stage {pipe.pp_rank} expects layers [{lo}, {hi}), the weights hold "
+                                 f"[{weights.layer_offset}, {weights.layer_offset + len(weights.layers)})")
+        elif cfg.parallel.pp_size > 1:
+            raise ValueError("ParallelConfig.pp_size > 1 needs a PipeStage")
+        stage_layers = list(range(*pipe.layer_range(cfg.model.num_hidden_layers))) if pipe is not None else None
         self.kv = KVManager(cfg.model, self.device, sc.max_num_seqs, ctx + 64, pools["swa_pages"] + (sc.max_num_seqs if spec_on else 0),
                             pools["c4_pages"], pools["c128_pages"] if has_c128 else 0, sc.max_num_batched_tokens,
-                            extra_swa_layers=cfg.model.n_mtp_layers if spec_on else 0, spec_tokens=n_spec)
+                            layers=stage_layers, extra_swa_layers=cfg.model.n_mtp_layers if spec_on else 0, spec_tokens=n_spec)
         self.model = DSV4Model(cfg.model, weights, self.kv, comm, tp_rank, cfg.parallel.tp_size)
+        self.model.pipe = pipe
         self.prefix_cache = None
         if cfg.cache.enable_prefix_caching:
             from .prefix_cache import PrefixCache
@@ -277,7 +293,8 @@ class Engine:
         self._next_id = 0
         self.requests: Dict[int, Request] = {}
         self._graphs: Dict[tuple, object] = {}
-        self.use_graphs = self.device.type == "cuda" and sc.graph_cap > 0
+        # a captured step cannot hold the stage-to-stage sends and receives: pipeline stages run eagerly
+        self.use_graphs = self.device.type == "cuda" and sc.graph_cap > 0 and pipe is None
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
         self._placements: Dict[int, object] = {}

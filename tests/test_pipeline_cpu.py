@@ -1,0 +1,103 @@
+"""Pipeline parallelism on CPU (gloo ranks): the decoder cut into 2 and 3 stages gives the same greedy tokens as one
+process, each stage holds only its own layers and KV caches, and a stage that begins inside an IndexCache group gets the
+shared top-k rows from its predecessor."""
+import json
+import os
+import socket
+
+import pytest
+import torch
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _run(rank, world, port, path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      STK_CPU_ACT_FP32="1", CUDA_VISIBLE_DEVICES="")
+    import torch.distributed as dist
+    from stkernel_b200.config import EngineConfig, ParallelConfig, SchedulerConfig, tiny_config
+    from stkernel_b200.models.dsv4 import DictSource, build_model_weights
+    from stkernel_b200.models.weights import init_random_weights
+    from stkernel_b200.parallel.pipeline import PipeStage, stage_starts_inside_index_group
+    from stkernel_b200.runtime.engine import Engine, SamplingParams
+    # five layers, ratio-4 layers at 0, 1, 3, 4 with IndexCache frequency 2: layers 1 and 4 reuse the rows of 0 and 3
+    cfg = tiny_config(dense_dtype="bf16", kv_cache_dtype="bf16", expert_dtype="bf16", num_hidden_layers=5,
+                      compress_ratios=(4, 4, 0, 4, 4), index_topk_freq=2)
+    w = init_random_weights(cfg, seed=2)
+    pipe = None
+    rng = None
+    if world > 1:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        pipe = PipeStage(pp_rank=rank, pp_size=world)
+        rng = pipe.layer_range(cfg.num_hidden_layers)
+    ec = EngineConfig(model=cfg, parallel=ParallelConfig(pp_size=world),
+                      sched=SchedulerConfig(max_model_len=256, max_num_seqs=2, max_num_batched_tokens=64,
+                                            graph_cap=0)).validate()
+    weights = build_model_weights(cfg, DictSource(w), "cpu", layer_range=rng)
+    eng = Engine(ec, weights, "cpu", max_context=256, pipe=pipe)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (70, 33)]
+    out = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=6))
+    info = {"out": out, "layers": [weights.layer_offset, weights.layer_offset + len(weights.layers)],
+            "kv_layers": sorted(eng.kv.swa_cache.keys()),
+            "starts_inside_group": stage_starts_inside_index_group(cfg, *rng) if rng else False}
+    json.dump(info, open(f"{path}.{rank}", "w"))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def _spawn(world, path):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    ps = [ctx.Process(target=_run, args=(r, world, port, path)) for r in range(world)]
+    for q in ps:
+        q.start()
+    for q in ps:
+        q.join(240)
+        assert q.exitcode == 0
+    return [json.load(open(f"{path}.{r}")) for r in range(world)]
+
+
+@pytest.mark.timeout(600)
+def test_pipeline_stages_match_single_process(tmp_path):
+    one = _spawn(1, str(tmp_path / "one"))[0]
+    assert one["layers"] == [0, 5]
+    for world in (2, 3):
+        stages = _spawn(world, str(tmp_path / f"pp{world}"))
+        # every stage ends each step with the last stage's tokens, and they are the single-process tokens
+        for st in stages:
+            assert st["out"] == one["out"], (world, st["layers"])
+        # contiguous cover, own KV only
+        assert stages[0]["layers"][0] == 0 and stages[-1]["layers"][1] == 5
+        for a, b in zip(stages, stages[1:]):
+            assert a["layers"][1] == b["layers"][0]
+        for st in stages:
+            assert st["kv_layers"] == list(range(*st["layers"]))
+    # the 3-stage cut is [0,2) [2,4) [4,5): the last stage starts at layer 4, which reuses layer 3's top-k rows
+    assert _spawn(3, str(tmp_path / "pp3b"))[2]["starts_inside_group"] is True
+
+
+def test_pipeline_stage_arithmetic_and_guards():
+    from stkernel_b200.config import EngineConfig, ParallelConfig, SchedulerConfig, tiny_config
+    from stkernel_b200.models.dsv4 import DictSource, build_model_weights
+    from stkernel_b200.models.weights import init_random_weights
+    from stkernel_b200.parallel.pipeline import PipeStage
+    from stkernel_b200.runtime.engine import Engine
+    cfg = tiny_config(dense_dtype="bf16", kv_cache_dtype="bf16", expert_dtype="bf16")
+    st = PipeStage(pp_rank=1, pp_size=2, tp_rank=1, tp_size=4)
+    assert st._global(0) == 1 and st._global(1) == 5 and st.last and not st.first
+    w = build_model_weights(cfg, DictSource(init_random_weights(cfg, seed=0)), "cpu")
+    ec = EngineConfig(model=cfg, parallel=ParallelConfig(pp_size=2),
+                      sched=SchedulerConfig(max_model_len=128, max_num_seqs=2, max_num_batched_tokens=64, graph_cap=0)).validate()
+    with pytest.raises(ValueError):
+        Engine(ec, w, "cpu", max_context=128)                                   # pp_size 2 without a stage
+    with pytest.raises(ValueError):
+        Engine(ec, w, "cpu", max_context=128, pipe=PipeStage(pp_rank=0, pp_size=2))   # the weights hold every layer
