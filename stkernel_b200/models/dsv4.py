@@ -20,9 +20,10 @@ from typing import Callable, Dict, List, Optional, Tuple
 
 import torch
 
-from ..config import ModelConfig
+from ..config import KV_SCALE_BYTES, ModelConfig
 from ..ops import attention as A
 from ..ops import cache as C
+from ..ops.cache import PAGE, PagedCache
 from ..ops import functional as Fn
 from ..ops import moe as M
 from ..utils.spans import span
@@ -327,7 +328,14 @@ class DSV4Model:
         self.pipe = None                                     # parallel.pipeline.PipeStage when the model is one stage of several
         self.aux_layers: Tuple[int, ...] = ()
         self.aux_out: List[torch.Tensor] = []
-        self.stats = {"sp_steps": 0, "mla_token_parallel_calls": 0}     # which large-step paths ran (tests, debugging)
+        self.stats = {"sp_steps": 0, "mla_token_parallel_calls": 0, "dcp_topk_merges": 0}     # which paths ran (tests)
+        # Decode context parallel (kv.dcp_size > 1): the ratio-4 caches hold every dcp_size-th page of each request.
+        # A layer that computes top-k rows scores its own keys and the ranks merge their candidates; the selected
+        # latent rows are then brought into a dense staging buffer on every rank (at most dcp_stage_bytes per call,
+        # larger steps go in token blocks) and the attention kernels read that buffer like any paged cache.
+        self._dcp_lt: Optional[torch.Tensor] = None
+        self._dcp_stages: Dict[tuple, PagedCache] = {}
+        self.dcp_stage_bytes = int(os.environ.get("STK_DCP_STAGE_MB", "64")) << 20
         self.load_recorder = None           # parallel.eplb.LoadRecorder when expert load is being recorded
         # Sequence-parallel indexer: with TP the indexer weights are replicated, so each rank scores only its
         # share of a large step's rows and the top-k rows are all-gathered (overlay/attention.py
@@ -466,6 +474,7 @@ class DSV4Model:
             grp = self.kv.c4 if lw.kind == "c4a" else self.kv.c128
             comp_cache = self.kv.comp_cache[li]
             computes = lw.kind == "c4a" and lw.computes_topk
+            dcp = lw.kind == "c4a" and self.kv.dcp_size > 1
             ih = cfg.index_n_heads
 
             def compress_main(side):
@@ -487,7 +496,8 @@ class DSV4Model:
                 ev_qb = main.record_event()
                 with side_branch(sd):
                     sd.wait_event(ev_in)       # y is ready: the branch starts beside the qa/kv projection
-                    if lw.kind == "c4a" and not computes and self.topk_buffer is not None and self.topk_buffer.shape[0] >= T:
+                    if (lw.kind == "c4a" and not computes and not dcp and self.topk_buffer is not None
+                            and self.topk_buffer.shape[0] >= T):
                         # a layer that reuses the shared top-k rows only translates them to its own cache's slots:
                         # nothing of this layer is needed for that
                         early_slots = A.topk_to_slots(self.topk_buffer[:T], grp.table_dev, meta.tok_req,
@@ -544,7 +554,9 @@ class DSV4Model:
                                                   meta.tok_req[b0:b1], nv[b0:b1], n_rows)
                             A.topk_rows(sc, nv[b0:b1], K, out=out[qs.start:qs.stop])
 
-                    if self.indexer_sp and T >= self.indexer_sp_min_rows * self.tp_size:
+                    if dcp:
+                        self._dcp_score_topk(li, qq, wf, nv, n_rows, grp, meta, K)
+                    elif self.indexer_sp and T >= self.indexer_sp_min_rows * self.tp_size:
                         sizes = sp_gather_sizes((0, T), self.tp_size)           # ceil split, the last ranks may be short
                         shard = sizes[0]
                         a0 = sum(sizes[:self.tp_rank])
@@ -554,7 +566,9 @@ class DSV4Model:
                         self.topk_buffer[:T] = self.comm.all_gather_dim0(part)[:T]
                     else:
                         score_topk(0, T, self.topk_buffer)
-                if early_slots is not None:
+                if dcp:
+                    topk_slots = topk_lens = None           # staged per token block below
+                elif early_slots is not None:
                     topk_slots, topk_lens = early_slots
                 else:
                     topk_slots, topk_lens = A.topk_to_slots(self.topk_buffer[:T], grp.table_dev, meta.tok_req,
@@ -567,7 +581,9 @@ class DSV4Model:
         if lw.ratio and ev_kv is not None:
             torch.cuda.current_stream().wait_event(ev_kv)
         with span("sparse_mla", T):
-            if (self.tp_size > 1 and self.comm is not None and lw.sink_full is not None and self.mla_tp_min_rows > 0
+            if lw.ratio and dcp:
+                o = self._dcp_sparse_mla(li, lw, q, meta, grp, q_in_mla, kv_in_mla, kvn, kv_norm_w)
+            elif (self.tp_size > 1 and self.comm is not None and lw.sink_full is not None and self.mla_tp_min_rows > 0
                     and T >= self.mla_tp_min_rows):
                 o = self._mla_token_parallel(li, lw, q, meta, comp_cache, topk_slots, topk_lens)
             else:
@@ -594,6 +610,105 @@ class DSV4Model:
             ar = self._gemm_ar_ctx(T, cfg.hidden_size)
             out = Fn.linear(z, lw.w_ob, tag="ob", ar_ctx=ar)
             return out if ar is not None else self._all_reduce(out)
+
+    # ---- decode context parallel: ratio-4 rows dealt page by page over the ranks -----------------------------------
+    def _dcp_local_table(self, grp) -> torch.Tensor:
+        if self._dcp_lt is None:
+            self._dcp_lt = grp.local_table()
+        return self._dcp_lt
+
+    def _dcp_score_topk(self, li: int, qq, wf, nv: torch.Tensor, n_rows: int, grp, meta: StepMeta, K: int) -> None:
+        """Every rank scores the indexer keys it stores, keeps its K best (score, global row) pairs per token, and
+        the ranks' lists are gathered and merged into the global top-k (overlay/ops_cache_utils.py:472-503,557-617
+        interleaved KV; probes/sai_probe.py:1065-1146 cross-rank candidate merge).  Writes self.topk_buffer[:T]."""
+        r, n = self.kv.dcp_rank, self.kv.dcp_size
+        T = qq.shape[0]
+        span_rows = PAGE * n
+        # rows of the first nv that live here: whole rounds of pages, plus this rank's part of the open round
+        nv_l = ((nv // span_rows) * PAGE + (nv % span_rows - r * PAGE).clamp(0, PAGE)).to(torch.int32)
+        rows_l = (n_rows // span_rows + 1) * PAGE
+        lt = self._dcp_local_table(grp)
+        cand = torch.empty(T, 2, K, dtype=torch.int32, device=qq.device)
+        ninf = float("-inf")
+        for _, qs in split_indexer_prefill_chunks([rows_l], [T], 1 << 62, self.indexer_logits_bytes):
+            b0, b1 = qs.start, qs.stop
+            sc = A.indexer_scores(qq[b0:b1], wf[b0:b1], self.kv.idx_cache[li], lt, meta.tok_req[b0:b1], nv_l[b0:b1], rows_l)
+            ids = A.topk_rows(sc, nv_l[b0:b1], K)
+            ok = ids >= 0
+            val = torch.gather(sc, 1, ids.clamp(min=0).long())
+            cand[b0:b1, 1] = torch.where(ok, val, torch.full_like(val, ninf)).contiguous().view(torch.int32)
+            gid = ((ids // PAGE) * n + r) * PAGE + ids % PAGE
+            cand[b0:b1, 0] = torch.where(ok, gid, torch.full_like(gid, -1))
+        allc = self.comm.all_gather_dim0(cand).view(n, T, 2, K)
+        gids = allc[:, :, 0].permute(1, 0, 2).reshape(T, n * K)
+        vals = allc[:, :, 1].permute(1, 0, 2).reshape(T, n * K).view(torch.float32)
+        # K best by (score descending, row ascending): two stable sorts, so equal scores resolve the same way on every
+        # rank and as on a rank that holds all rows
+        order = torch.sort(torch.where(gids >= 0, gids, torch.full_like(gids, 1 << 30)), dim=1, stable=True)[1]
+        gids, vals = torch.gather(gids, 1, order), torch.gather(vals, 1, order)
+        top, pos = torch.sort(vals, dim=1, descending=True, stable=True)
+        ids = torch.gather(gids, 1, pos[:, :K])
+        self.topk_buffer[:T] = torch.where(top[:, :K] > ninf, ids, torch.full_like(ids, -1))
+        self.stats["dcp_topk_merges"] += 1
+
+    def _dcp_stage(self, li: int, ids: torch.Tensor, tok_req: torch.Tensor, grp):
+        """ids [t, K] global ratio-4 row ids (-1 padded) -> (cache, slots, lens): a dense paged buffer that holds
+        row ids[i, j] at slot i * K + j.  Every rank fills in the rows it stores and the ranks' buffers are added
+        (one writer per row), so each selected row crosses the links once and attention reads local memory."""
+        r, n = self.kv.dcp_rank, self.kv.dcp_size
+        cache = self.kv.comp_cache[li]
+        t, K = ids.shape
+        db = cache.data_bytes
+        sb = KV_SCALE_BYTES if cache.fp8 else 0
+        ok = ids >= 0
+        idl = ids.clamp(min=0).long()
+        lp = idl // PAGE
+        mine = ok & (lp % n == r)
+        phys = grp.table_dev[tok_req.clamp(min=0).long()[:, None], lp].long()
+        phys = torch.where(mine, phys, torch.zeros_like(phys)).clamp(min=0)
+        rr = idl % PAGE
+        rows = t * K
+        pages = -(-rows // PAGE)
+        key = (pages, db, sb)
+        stage = self._dcp_stages.get(key)
+        if stage is None:
+            stage = self._dcp_stages[key] = PagedCache.allocate(pages, cache.dim, cache.rope_dim, cache.fp8, cache.kind,
+                                                                ids.device)
+        flat = torch.arange(rows, device=ids.device)
+        dst_pg, dst_r = flat // PAGE, flat % PAGE
+        m = mine.view(rows, 1)
+        for off, width in ((0, db), (PAGE * db, sb)):
+            if width == 0:
+                continue
+            src = cache.buf[:, off:off + PAGE * width].view(cache.num_pages, PAGE, width)[phys, rr].view(rows, width)
+            dst = stage.buf[:, off:off + PAGE * width].view(pages, PAGE, width)
+            dst[dst_pg, dst_r] = torch.where(m, src, torch.zeros_like(src))
+        self.comm.all_reduce(stage.buf.view(torch.int32))
+        slots = torch.where(ok, flat.view(t, K), torch.full_like(idl, -1)).to(torch.int32)
+        return stage, slots, ok.sum(1).to(torch.int32)
+
+    def _dcp_sparse_mla(self, li: int, lw: LayerWeights, q, meta: StepMeta, grp, q_in_mla: bool, kv_in_mla: bool, kvn,
+                        kv_norm_w) -> torch.Tensor:
+        cfg = self.cfg
+        T, D = q.shape[0], cfg.head_dim
+        K = cfg.index_topk
+        cache = self.kv.comp_cache[li]
+        row_bytes = cache.data_bytes + (KV_SCALE_BYTES if cache.fp8 else 0)
+        step = max(1, self.dcp_stage_bytes // (K * row_bytes))
+        if T <= step:
+            cc, ts, tl = self._dcp_stage(li, self.topk_buffer[:T], meta.tok_req, grp)
+            return A.sparse_mla(q, self.kv.swa_cache[li], meta.swa_slots, meta.swa_lens, cc, ts, tl, lw.sink, D ** -0.5,
+                                inv_rope=(meta.positions, self.inv),
+                                q_prep=(meta.positions, self.inv, cfg.rms_norm_eps) if q_in_mla else None,
+                                kv_insert=(kvn, kv_norm_w, meta.swa_slot_mapping) if kv_in_mla else None)
+        # a prefill chunk: token blocks small enough for the staging budget
+        o = torch.empty_like(q)
+        for a in range(0, T, step):
+            sl = slice(a, min(T, a + step))
+            cc, ts, tl = self._dcp_stage(li, self.topk_buffer[sl], meta.tok_req[sl], grp)
+            o[sl] = A.sparse_mla(q[sl], self.kv.swa_cache[li], meta.swa_slots[sl], meta.swa_lens[sl], cc, ts, tl, lw.sink,
+                                 D ** -0.5, inv_rope=(meta.positions[sl], self.inv))
+        return o
 
     def _mla_token_parallel(self, li: int, lw: LayerWeights, q: torch.Tensor, meta: StepMeta, comp_cache, topk_slots,
                             topk_lens) -> torch.Tensor:
@@ -707,6 +822,7 @@ class DSV4Model:
         """-> final residual streams [T, hc, H]."""
         cfg = self.cfg
         T = meta.token_ids.shape[0]
+        self._dcp_lt = None                  # the block tables may have changed since the last step
         sp = (self.sp_min_rows > 0 and T >= self.sp_min_rows and T % self.tp_size == 0 and not self.aux_layers)
         ids = meta.token_ids
         if sp:

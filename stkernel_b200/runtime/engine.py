@@ -235,7 +235,11 @@ class Engine:
         self.device = torch.device(device)
         sc = cfg.sched
         ctx = max_context or sc.max_model_len
-        pools = size_pools(cfg.model, sc.max_num_seqs, ctx, sc.max_num_batched_tokens)
+        # decode context parallel: the ranks of the tensor-parallel group each store 1/dcp of the ratio-4 caches
+        dcp = cfg.parallel.dcp_size
+        if dcp > 1 and (dcp != cfg.parallel.tp_size or comm is None):
+            raise ValueError("dcp_size must be 1 or tp_size (the context-parallel ranks are the tensor-parallel group)")
+        pools = size_pools(cfg.model, sc.max_num_seqs, ctx, sc.max_num_batched_tokens, dcp)
         if cfg.cache.num_pages is not None:
             pools["swa_pages"] = max(pools["swa_pages"], cfg.cache.num_pages)
         has_c128 = any(cfg.model.layer_kind(i) == "c128a" for i in range(cfg.model.num_hidden_layers))
@@ -259,7 +263,8 @@ class Engine:
         stage_layers = list(range(*pipe.layer_range(cfg.model.num_hidden_layers))) if pipe is not None else None
         self.kv = KVManager(cfg.model, self.device, sc.max_num_seqs, ctx + 64, pools["swa_pages"] + (sc.max_num_seqs if spec_on else 0),
                             pools["c4_pages"], pools["c128_pages"] if has_c128 else 0, sc.max_num_batched_tokens,
-                            layers=stage_layers, extra_swa_layers=cfg.model.n_mtp_layers if spec_on else 0, spec_tokens=n_spec)
+                            layers=stage_layers, extra_swa_layers=cfg.model.n_mtp_layers if spec_on else 0, spec_tokens=n_spec,
+                            dcp_rank=tp_rank if dcp > 1 else 0, dcp_size=dcp)
         self.model = DSV4Model(cfg.model, weights, self.kv, comm, tp_rank, cfg.parallel.tp_size)
         self.model.pipe = pipe
         self.prefix_cache = None
@@ -293,8 +298,9 @@ class Engine:
         self._next_id = 0
         self.requests: Dict[int, Request] = {}
         self._graphs: Dict[tuple, object] = {}
-        # a captured step cannot hold the stage-to-stage sends and receives: pipeline stages run eagerly
-        self.use_graphs = self.device.type == "cuda" and sc.graph_cap > 0 and pipe is None
+        # a captured step cannot hold the stage-to-stage sends and receives: pipeline stages run eagerly; so do steps
+        # under decode context parallelism (their staging buffers are allocated as block sizes first appear)
+        self.use_graphs = self.device.type == "cuda" and sc.graph_cap > 0 and pipe is None and dcp == 1
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
         self._placements: Dict[int, object] = {}

@@ -42,6 +42,11 @@ class GroupTable:
     max_pages_per_req: int
     device: torch.device
     rows_per_token: float            # 1 for swa, 1/ratio for compressed groups
+    # Decode context parallel: logical page lp of every request is stored by rank lp % dcp_size only.  The other
+    # ranks map it to one shared scratch page past the pool (`trash`), so kernels that write a compressed row through
+    # the table need no owner test, and nothing ever reads that page.
+    dcp_rank: int = 0
+    dcp_size: int = 1
     table_host: torch.Tensor = field(init=False)
     table_dev: torch.Tensor = field(init=False)
     free: List[int] = field(init=False)
@@ -68,6 +73,16 @@ class GroupTable:
         self.lo = [0] * self.max_requests
         self.hi = [0] * self.max_requests
         self.dirty_rows = set()
+        self.trash = self.num_pages if self.dcp_size > 1 else -2          # physical id of the scratch page
+
+    def owns(self, logical: int) -> bool:
+        return self.dcp_size == 1 or logical % self.dcp_size == self.dcp_rank
+
+    def local_table(self) -> torch.Tensor:
+        """[max_requests, ceil(max_pages / dcp)] block table over this rank's own pages only: column l is logical
+        page l * dcp_size + dcp_rank.  Row r of that local numbering is global row
+        ((r // PAGE) * dcp_size + dcp_rank) * PAGE + r % PAGE."""
+        return self.table_dev[:, self.dcp_rank::self.dcp_size].contiguous()
 
     def ensure(self, row: int, first_logical: int, last_logical: int) -> None:
         """Make logical pages [first, last] of request `row` resident (the resident set stays an interval)."""
@@ -81,6 +96,9 @@ class GroupTable:
         if first_logical < self.lo[row]:
             raise OutOfPages(f"{self.name}: page {first_logical} of row {row} was already released")
         for lp in range(start, last_logical + 1):
+            if not self.owns(lp):
+                t[lp] = self.trash
+                continue
             while not self.free and self.on_pressure is not None and self.on_pressure():
                 pass                                       # cached prefixes give pages back, oldest first
             if not self.free:
@@ -104,6 +122,8 @@ class GroupTable:
             self.dirty_rows.add(row)
 
     def unref(self, page: int) -> None:
+        if page == self.trash:
+            return
         self.ref[page] -= 1
         if self.ref[page] == 0:
             self.free.append(page)
@@ -115,7 +135,8 @@ class GroupTable:
         if any(pg < 0 for pg in pages):
             raise OutOfPages(f"{self.name}: cannot share a page that is not resident")
         for pg in pages:
-            self.ref[pg] += 1
+            if pg != self.trash:
+                self.ref[pg] += 1
         return pages
 
     def adopt(self, row: int, first_logical: int, pages: List[int]) -> None:
@@ -124,7 +145,8 @@ class GroupTable:
         t = self.table_np[row]
         for i, pg in enumerate(pages):
             t[first_logical + i] = pg
-            self.ref[pg] += 1
+            if pg != self.trash:
+                self.ref[pg] += 1
         self.lo[row], self.hi[row] = first_logical, first_logical + len(pages)
         self.dirty = True
         self.dirty_rows.add(row)
@@ -158,8 +180,12 @@ class KVManager:
 
     def __init__(self, cfg: ModelConfig, device, max_requests: int, max_model_len: int, swa_pages: int,
                  c4_pages: int, c128_pages: int = 0, max_chunk: int = 4096, layers: Optional[List[int]] = None,
-                 extra_swa_layers: int = 0, spec_tokens: int = 0):
+                 extra_swa_layers: int = 0, spec_tokens: int = 0, dcp_rank: int = 0, dcp_size: int = 1):
+        """dcp_size > 1: the ratio-4 caches (compressed latent rows and indexer keys, the part of the KV that grows
+        with the context) are dealt page by page over the ranks; `c4_pages` is then this rank's pool.  The
+        sliding-window and ratio-128 caches stay replicated (a window, and 1/32 of the ratio-4 rows)."""
         self.cfg = cfg
+        self.dcp_rank, self.dcp_size = dcp_rank, dcp_size
         self.device = torch.device(device)
         self.max_requests = max_requests
         fp8 = cfg.kv_cache_dtype == "fp8_ds_mla"
@@ -167,7 +193,8 @@ class KVManager:
         # the block table spans the whole context; SWA residency is bounded by window + chunk
         pages_ctx = (max_model_len + PAGE - 1) // PAGE + 1
         self.swa = GroupTable("swa", swa_pages, max_requests, pages_ctx, self.device, 1.0)
-        self.c4 = GroupTable("c4", max(c4_pages, 1), max_requests, (max_model_len // 4) // PAGE + 2, self.device, 0.25)
+        self.c4 = GroupTable("c4", max(c4_pages, 1), max_requests, (max_model_len // 4) // PAGE + 2, self.device, 0.25,
+                             dcp_rank, dcp_size)
         self.c128 = GroupTable("c128", max(c128_pages, 1), max_requests, (max_model_len // 128) // PAGE + 2,
                                self.device, 1 / 128)
         self.layers = layers if layers is not None else list(range(cfg.num_hidden_layers))
@@ -186,9 +213,9 @@ class KVManager:
             self.swa_cache[li] = PagedCache.allocate(swa_pages, D, Rd, fp8, "latent", self.device)
             kind = cfg.layer_kind(li) if li < cfg.num_hidden_layers else "swa"
             if kind == "c4a":
-                self.comp_cache[li] = PagedCache.allocate(self.c4.num_pages, D, Rd, fp8, "latent", self.device)
-                self.idx_cache[li] = PagedCache.allocate(self.c4.num_pages, cfg.index_head_dim, Rd, fp8, "indexer",
-                                                         self.device)
+                n4 = self.c4.num_pages + (1 if dcp_size > 1 else 0)          # + the scratch page
+                self.comp_cache[li] = PagedCache.allocate(n4, D, Rd, fp8, "latent", self.device)
+                self.idx_cache[li] = PagedCache.allocate(n4, cfg.index_head_dim, Rd, fp8, "indexer", self.device)
                 self.comp_state[li] = torch.zeros(max_requests, ring4, 2 * 2 * D, dtype=torch.float32, device=self.device)
                 self.idx_state[li] = torch.zeros(max_requests, ring4, 2 * 2 * cfg.index_head_dim, dtype=torch.float32,
                                                  device=self.device)
@@ -229,7 +256,8 @@ class KVManager:
 
     def admit_needs(self, n_tokens: int, context: int) -> Tuple[int, int]:
         """(sliding-window pages, ratio-4 pages) a new request of this size must find free."""
-        return (min(n_tokens, context) + self.cfg.sliding_window) // PAGE + 2, (context // 4) // PAGE + 1
+        c4 = (context // 4) // PAGE + 1
+        return (min(n_tokens, context) + self.cfg.sliding_window) // PAGE + 2, -(-c4 // self.dcp_size)
 
     def can_admit(self, n_tokens: int, context: int) -> bool:
         need_swa, need_c4 = self.admit_needs(n_tokens, context)
@@ -248,9 +276,10 @@ class KVManager:
         return n
 
 
-def size_pools(cfg: ModelConfig, max_requests: int, max_context: int, max_chunk: int) -> Dict[str, int]:
-    """Pages needed so that `max_requests` sequences of `max_context` tokens fit (no prefix sharing)."""
+def size_pools(cfg: ModelConfig, max_requests: int, max_context: int, max_chunk: int, dcp_size: int = 1) -> Dict[str, int]:
+    """Pages needed so that `max_requests` sequences of `max_context` tokens fit (no prefix sharing); with decode
+    context parallelism `c4_pages` is one rank's share (every dcp_size-th page of each request, rounded up)."""
     swa = max_requests * ((cfg.sliding_window + PAGE - 1) // PAGE + 2) + (max_chunk + PAGE - 1) // PAGE + 2
-    c4 = max_requests * ((max_context // 4 + PAGE - 1) // PAGE + 1)
+    c4 = max_requests * -(-((max_context // 4 + PAGE - 1) // PAGE + 1) // dcp_size)
     c128 = max_requests * ((max_context // 128 + PAGE - 1) // PAGE + 1)
     return {"swa_pages": swa, "c4_pages": c4, "c128_pages": c128}

@@ -131,6 +131,7 @@ def build_engine(a, rank: int, world: int, device) -> Tuple[Engine, Any]:
                                 dspark_target_layer_ids=(a.layers // 4, a.layers // 2, a.layers - 1) if n_mtp else ())
         src = RandomSource(0)
     ecfg = EngineConfig(model=mcfg, parallel=ParallelConfig(tp_size=world, ep_size=world,
+                                                            dcp_size=getattr(a, "decode_context_parallel_size", 1),
                                                             fused_collectives=os.environ.get("STK_FUSED_COLLECTIVES", "1") == "1"),
                         sched=SchedulerConfig(max_model_len=a.max_model_len, max_num_seqs=a.max_num_seqs,
                                               max_num_batched_tokens=a.max_num_batched_tokens, graph_cap=a.graph_cap),
@@ -161,6 +162,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--max-num-seqs", type=int, default=32)
     ap.add_argument("--max-num-batched-tokens", type=int, default=4096)
     ap.add_argument("--graph-cap", type=int, default=64)
+    ap.add_argument("--decode-context-parallel-size", type=int, default=1,
+                    help="1, or the tensor-parallel size: the ratio-4 KV caches are dealt page by page over the ranks")
     ap.add_argument("--kv-cache-dtype", default="fp8_ds_mla")
     ap.add_argument("--temperature", type=float, default=0.8)
     ap.add_argument("--speculative-config", default="")
