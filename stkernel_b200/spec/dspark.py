@@ -183,6 +183,7 @@ class _DraftKV:
     def __init__(self, kv, first_layer: int, n: int):
         self.swa_cache = {k: kv.swa_cache[first_layer + k] for k in range(n)}
         self.swa = kv.swa
+        self.dcp_rank, self.dcp_size = 0, 1
         self.comp_cache: Dict[int, Any] = {}
         self.idx_cache: Dict[int, Any] = {}
         self.comp_state: Dict[int, Any] = {}
