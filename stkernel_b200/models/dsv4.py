@@ -29,7 +29,8 @@ from ..ops import moe as M
 from ..utils.spans import span
 from ..ops.functional import LinearWeight
 from ..ops.scratch import side_branch
-from ..runtime.planning import pp_layer_range, sp_gather_sizes, split_indexer_prefill_chunks
+from ..runtime.planning import (dcp_global_row, dcp_local_rows, dcp_owner, pp_layer_range, sp_gather_sizes,
+                                split_indexer_prefill_chunks)
 from .dsv4_oracle import index_cache_computes
 from .weights import compressor_slots
 
@@ -623,10 +624,8 @@ class DSV4Model:
         interleaved KV; probes/sai_probe.py:1065-1146 cross-rank candidate merge).  Writes self.topk_buffer[:T]."""
         r, n = self.kv.dcp_rank, self.kv.dcp_size
         T = qq.shape[0]
-        span_rows = PAGE * n
-        # rows of the first nv that live here: whole rounds of pages, plus this rank's part of the open round
-        nv_l = ((nv // span_rows) * PAGE + (nv % span_rows - r * PAGE).clamp(0, PAGE)).to(torch.int32)
-        rows_l = (n_rows // span_rows + 1) * PAGE
+        nv_l = dcp_local_rows(nv, n, r, PAGE).to(torch.int32)           # rows of each token's first nv that live here
+        rows_l = (n_rows // (PAGE * n) + 1) * PAGE
         lt = self._dcp_local_table(grp)
         cand = torch.empty(T, 2, K, dtype=torch.int32, device=qq.device)
         ninf = float("-inf")
@@ -637,7 +636,7 @@ class DSV4Model:
             ok = ids >= 0
             val = torch.gather(sc, 1, ids.clamp(min=0).long())
             cand[b0:b1, 1] = torch.where(ok, val, torch.full_like(val, ninf)).contiguous().view(torch.int32)
-            gid = ((ids // PAGE) * n + r) * PAGE + ids % PAGE
+            gid = dcp_global_row(ids, n, r, PAGE)
             cand[b0:b1, 0] = torch.where(ok, gid, torch.full_like(gid, -1))
         allc = self.comm.all_gather_dim0(cand).view(n, T, 2, K)
         gids = allc[:, :, 0].permute(1, 0, 2).reshape(T, n * K)
@@ -663,7 +662,7 @@ class DSV4Model:
         ok = ids >= 0
         idl = ids.clamp(min=0).long()
         lp = idl // PAGE
-        mine = ok & (lp % n == r)
+        mine = ok & (dcp_owner(idl, n, PAGE) == r)
         phys = grp.table_dev[tok_req.clamp(min=0).long()[:, None], lp].long()
         phys = torch.where(mine, phys, torch.zeros_like(phys)).clamp(min=0)
         rr = idl % PAGE

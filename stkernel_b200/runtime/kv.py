@@ -27,6 +27,7 @@ import torch
 
 from ..config import ModelConfig
 from ..ops.cache import PAGE, PagedCache
+from .planning import dcp_owner
 
 
 class OutOfPages(RuntimeError):
@@ -76,7 +77,7 @@ class GroupTable:
         self.trash = self.num_pages if self.dcp_size > 1 else -2          # physical id of the scratch page
 
     def owns(self, logical: int) -> bool:
-        return self.dcp_size == 1 or logical % self.dcp_size == self.dcp_rank
+        return self.dcp_size == 1 or dcp_owner(logical * PAGE, self.dcp_size, PAGE) == self.dcp_rank
 
     def local_table(self) -> torch.Tensor:
         """[max_requests, ceil(max_pages / dcp)] block table over this rank's own pages only: column l is logical

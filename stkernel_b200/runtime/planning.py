@@ -94,26 +94,30 @@ def sp_gather_sizes(prefill_chunk: Range, tp_size: int) -> List[int]:
 # ---------------------------------------------------------------------------------------
 # decode context parallel
 # ---------------------------------------------------------------------------------------
-def dcp_owner(row: int, dcp_size: int, interleave: int = 1) -> int:
+def _clamp(x, lo: int, hi: int):
+    return x.clamp(lo, hi) if hasattr(x, "clamp") else max(lo, min(hi, x))
+
+
+# The four functions below take Python ints or integer tensors (the model calls them on whole steps at once).
+def dcp_owner(row, dcp_size: int, interleave: int = 1):
     """Rank that stores compressed-KV row `row` (rows dealt round-robin in groups of `interleave`)."""
     return (row // interleave) % dcp_size
 
 
-def dcp_local_rows(n_rows: int, dcp_size: int, rank: int, interleave: int = 1) -> int:
-    """How many of the first n_rows live on `rank`."""
-    full, rem = divmod(n_rows, interleave * dcp_size)
-    return full * interleave + max(0, min(interleave, rem - rank * interleave))
+def dcp_local_rows(n_rows, dcp_size: int, rank: int, interleave: int = 1):
+    """How many of the first n_rows live on `rank`: whole rounds, plus the rank's part of the open round."""
+    span = interleave * dcp_size
+    return (n_rows // span) * interleave + _clamp(n_rows % span - rank * interleave, 0, interleave)
 
 
-def dcp_local_index(row: int, dcp_size: int, interleave: int = 1) -> int:
+def dcp_local_index(row, dcp_size: int, interleave: int = 1):
     """Index of global row `row` inside its owner's local cache."""
     g = row // interleave
     return (g // dcp_size) * interleave + row % interleave
 
 
-def dcp_global_row(local: int, dcp_size: int, rank: int, interleave: int = 1) -> int:
-    g, r = divmod(local, interleave)
-    return (g * dcp_size + rank) * interleave + r
+def dcp_global_row(local, dcp_size: int, rank: int, interleave: int = 1):
+    return ((local // interleave) * dcp_size + rank) * interleave + local % interleave
 
 
 def merge_topk_candidates(per_rank: Sequence[Sequence[Tuple[float, int]]], k: int) -> List[int]:
