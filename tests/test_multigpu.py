@@ -43,3 +43,11 @@ def test_folded_allreduce_sharded_argmax_and_engine_across_ranks():
     r = _torchrun(os.path.join(ROOT, "tests", "multigpu", "ll_check.py"), 2, 29533, timeout=420,
                   extra_env={"NCCL_NVLS_ENABLE": "0"})
     assert "LL_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_decode_context_parallel_engine_across_ranks():
+    """The ratio-4 caches dealt page by page over two ranks against the same engine with replicated caches."""
+    r = _torchrun(os.path.join(ROOT, "tests", "multigpu", "dcp_check.py"), 2, 29534, timeout=420,
+                  extra_env={"NCCL_NVLS_ENABLE": "0"})
+    assert "DCP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
