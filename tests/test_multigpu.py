@@ -51,3 +51,11 @@ def test_decode_context_parallel_engine_across_ranks():
     r = _torchrun(os.path.join(ROOT, "tests", "multigpu", "dcp_check.py"), 2, 29534, timeout=420,
                   extra_env={"NCCL_NVLS_ENABLE": "0"})
     assert "DCP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_pipeline_stages_across_two_gpus():
+    """Two pipeline stages on two GPUs against the whole model on one."""
+    r = _torchrun(os.path.join(ROOT, "tests", "multigpu", "pp_check.py"), 2, 29535, timeout=420,
+                  extra_env={"NCCL_NVLS_ENABLE": "0"})
+    assert "PP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
