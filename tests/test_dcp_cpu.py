@@ -17,7 +17,7 @@ def _free_port():
     return p
 
 
-def _run(rank, world, port, path, kv_dtype, stage_mb):
+def _run(rank, world, port, path, kv_dtype, stage_mb, shared_prefix=False):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       STK_CPU_ACT_FP32="1", STK_DCP_STAGE_MB=stage_mb, CUDA_VISIBLE_DEVICES="")
     import torch.distributed as dist
@@ -41,24 +41,32 @@ def _run(rank, world, port, path, kv_dtype, stage_mb):
     g = torch.Generator().manual_seed(0)
     # 4 tokens per compressed row, 64 rows per page: 700 tokens reach the third page of the ratio-4 caches
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (700, 290)]
+    hits = None
+    if shared_prefix:
+        # a finished request leaves its first 512 tokens (two pages of compressed rows: one per rank) in the prefix
+        # cache; the next request starts from them
+        first = eng.generate([prompts[0][:600]], SamplingParams(temperature=0.0, max_tokens=3))
+        prompts = [prompts[0][:520] + prompts[1][:90]]
     rows = [eng.add_request(p, SamplingParams(temperature=0.0, max_tokens=5)) for p in prompts]
     peak = 0
     while eng.has_work():
         eng.step()
         peak = max(peak, eng.kv.c4.pages_in_use)
     out = [list(eng.requests[r].output) for r in rows]
-    json.dump({"out": out, "stats": eng.model.stats, "c4_peak": peak, "c4_pool": eng.kv.c4.num_pages},
+    if shared_prefix:
+        out = first + out
+    json.dump({"out": out, "prefix_hit_tokens": eng.prefix_cache.hit_tokens if eng.prefix_cache is not None else -1, "stats": eng.model.stats, "c4_peak": peak, "c4_pool": eng.kv.c4.num_pages},
               open(f"{path}.{rank}", "w"))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
 
 
-def _spawn(world, path, kv_dtype, stage_mb="64"):
+def _spawn(world, path, kv_dtype, stage_mb="64", shared_prefix=False):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     port = _free_port()
-    ps = [ctx.Process(target=_run, args=(r, world, port, path, kv_dtype, stage_mb)) for r in range(world)]
+    ps = [ctx.Process(target=_run, args=(r, world, port, path, kv_dtype, stage_mb, shared_prefix)) for r in range(world)]
     for q in ps:
         q.start()
     for q in ps:
@@ -89,6 +97,16 @@ def test_context_parallel_prefill_in_token_blocks(tmp_path):
     one = _spawn(1, str(tmp_path / "one"), "bf16")[0]
     two = _spawn(2, str(tmp_path / "two"), "bf16", stage_mb="0")
     assert two[0]["out"] == one["out"] and two[1]["out"] == one["out"]
+
+
+@pytest.mark.timeout(900)
+def test_context_parallel_with_a_cached_prefix(tmp_path):
+    one = _spawn(1, str(tmp_path / "one"), "bf16", shared_prefix=True)[0]
+    two = _spawn(2, str(tmp_path / "two"), "bf16", shared_prefix=True)
+    assert one["prefix_hit_tokens"] == 512
+    for r in two:
+        assert r["prefix_hit_tokens"] == 512
+        assert r["out"] == one["out"]
 
 
 def test_group_table_deals_pages_over_ranks():

@@ -53,6 +53,39 @@ def _run(rank, world, port, path):
         dist.destroy_process_group()
 
 
+def _run_pp_tp(rank, port, path):
+    """Four ranks: two pipeline stages of two tensor-parallel ranks each (global rank = pp_rank * 2 + tp_rank), with
+    the sequence-parallel residual on, so a stage boundary carries each rank's share of the token rows."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE="4",
+                      STK_CPU_ACT_FP32="1", STK_SEQ_PARALLEL_MIN_ROWS="4", CUDA_VISIBLE_DEVICES="")
+    import torch.distributed as dist
+    from stkernel_b200.config import EngineConfig, ParallelConfig, SchedulerConfig, tiny_config
+    from stkernel_b200.models.dsv4 import DictSource, build_model_weights
+    from stkernel_b200.models.weights import init_random_weights
+    from stkernel_b200.parallel.communicator import Communicator
+    from stkernel_b200.parallel.pipeline import PipeStage
+    from stkernel_b200.runtime.engine import Engine, SamplingParams
+    dist.init_process_group("gloo", rank=rank, world_size=4)
+    groups = [dist.new_group([0, 1]), dist.new_group([2, 3])]          # every rank creates every group
+    pp_rank, tp_rank = divmod(rank, 2)
+    comm = Communicator(group=groups[pp_rank], device="cpu", use_symm=False)
+    cfg = tiny_config(dense_dtype="bf16", kv_cache_dtype="bf16", expert_dtype="bf16", num_hidden_layers=5,
+                      compress_ratios=(4, 4, 0, 4, 4), index_topk_freq=2)
+    w = init_random_weights(cfg, seed=2)
+    pipe = PipeStage(pp_rank=pp_rank, pp_size=2, tp_rank=tp_rank, tp_size=2)
+    ec = EngineConfig(model=cfg, parallel=ParallelConfig(tp_size=2, ep_size=2, pp_size=2),
+                      sched=SchedulerConfig(max_model_len=256, max_num_seqs=2, max_num_batched_tokens=64,
+                                            graph_cap=0)).validate()
+    weights = build_model_weights(cfg, DictSource(w), "cpu", tp_rank, 2, layer_range=pipe.layer_range(cfg.num_hidden_layers))
+    eng = Engine(ec, weights, "cpu", comm, tp_rank, max_context=256, pipe=pipe)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (70, 33)]
+    out = eng.generate(prompts, SamplingParams(temperature=0.0, max_tokens=6))
+    json.dump({"out": out, "sp_steps": eng.model.stats["sp_steps"]}, open(f"{path}.{rank}", "w"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def _spawn(world, path):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
@@ -101,3 +134,22 @@ def test_pipeline_stage_arithmetic_and_guards():
         Engine(ec, w, "cpu", max_context=128)                                   # pp_size 2 without a stage
     with pytest.raises(ValueError):
         Engine(ec, w, "cpu", max_context=128, pipe=PipeStage(pp_rank=0, pp_size=2))   # the weights hold every layer
+
+
+@pytest.mark.timeout(600)
+def test_pipeline_stages_of_tensor_parallel_ranks(tmp_path):
+    import torch.multiprocessing as mp
+    one = _spawn(1, str(tmp_path / "one"))[0]
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    path = str(tmp_path / "pptp")
+    ps = [ctx.Process(target=_run_pp_tp, args=(r, port, path)) for r in range(4)]
+    for q in ps:
+        q.start()
+    for q in ps:
+        q.join(300)
+        assert q.exitcode == 0
+    got = [json.load(open(f"{path}.{r}")) for r in range(4)]
+    for g_ in got:
+        assert g_["out"] == one["out"]
+        assert g_["sp_steps"] >= 1
