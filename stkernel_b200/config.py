@@ -53,6 +53,10 @@ class ModelConfig:
     index_topk: int = 2048
     index_topk_freq: int = 4
     use_index_cache: bool = True
+    # Indexer operand format: "fp8" = e4m3 q with the scale folded into the head weights and e4m3 keys with one scale
+    # per row (when the KV cache is fp8_ds_mla, else bf16); "mxfp4" = e2m1 q and keys with one ue8m0 scale per 32
+    # values (overlay/ops_fused_indexer_q.py:175-282): half the indexer-K bytes.  Reference (CPU) path only.
+    indexer_dtype: str = "fp8"
     hc_mult: int = 4
     hc_sinkhorn_iters: int = 20
     hc_eps: float = 1e-6
@@ -140,6 +144,10 @@ class ModelConfig:
             raise ConfigError("index_topk_freq must be >= 1")
         if self.index_head_dim < self.qk_rope_head_dim:
             raise ConfigError("index_head_dim must be >= rope dim")
+        if self.indexer_dtype not in ("fp8", "mxfp4"):
+            raise ConfigError(f"unknown indexer_dtype {self.indexer_dtype!r}")
+        if self.indexer_dtype == "mxfp4" and (self.qk_rope_head_dim % 32 or (self.index_head_dim - self.qk_rope_head_dim) % 32):
+            raise ConfigError("mxfp4 indexer operands need the rope and non-rope parts of index_head_dim in blocks of 32")
 
 
 def alternating_ratios(n_layers: int, first: int = 4, second: int = 0) -> Tuple[int, ...]:

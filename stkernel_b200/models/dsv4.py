@@ -537,7 +537,7 @@ class DSV4Model:
                         torch.cuda.current_stream().wait_event(ev_side)
                     wi = side[:, ncomp:ncomp + ih]
                     quant = cfg.kv_cache_dtype == "fp8_ds_mla"
-                    qq, wf = C.indexer_q_prep(qi, wi, meta.positions, self.inv, Rd, quant)
+                    qq, wf = C.indexer_q_prep(qi, wi, meta.positions, self.inv, Rd, quant, fmt=cfg.indexer_dtype)
                     if fork:
                         torch.cuda.current_stream().wait_event(ev_idx)
                     else:

@@ -130,13 +130,18 @@ class OracleModel:
                     qi = self.dense_linear(qr, f"{i}.wq_b.weight").view(s, ih, di)
                     wi = y @ self.bf16_w(f"{i}.weights_proj.weight").t()
                     quant = cfg.kv_cache_dtype == "fp8_ds_mla"
-                    qq, wf = R.indexer_q_prepare(qi, wi, cos, sin, Rd, quantize=quant)
                     ki = self._compress(y, f"{i}.compressor", ratio, di, positions)
-                    if quant:
-                        kq, ks = R.indexer_k_quant(ki)
-                        scores = R.indexer_scores(qq, wf, kq.to(F32), ks)
+                    if cfg.indexer_dtype == "mxfp4":
+                        qp, qs, wf = R.indexer_q_prepare_mxfp4(qi, wi, cos, sin, Rd)
+                        kd = R.dequant_mxfp4(*R.quant_mxfp4(ki.to(F32)))
+                        scores = R.indexer_scores(R.dequant_mxfp4(qp, qs), wf, kd, None)
                     else:
-                        scores = R.indexer_scores(qq, wf, ki.to(torch.bfloat16).to(F32), None)
+                        qq, wf = R.indexer_q_prepare(qi, wi, cos, sin, Rd, quantize=quant)
+                        if quant:
+                            kq, ks = R.indexer_k_quant(ki)
+                            scores = R.indexer_scores(qq, wf, kq.to(F32), ks)
+                        else:
+                            scores = R.indexer_scores(qq, wf, ki.to(torch.bfloat16).to(F32), None)
                     topk = R.topk_rows(scores, n_valid, cfg.index_topk)
                     shared_topk["topk"] = topk
                 else:

@@ -157,6 +157,8 @@ def indexer_scores(q: torch.Tensor, w: torch.Tensor, kcache: PagedCache, block_t
     t, ih, d = q.shape
     ld = max(4, (max_rows + 3) // 4 * 4)
     if not q.is_cuda:
+        if hasattr(q, "dequant"):                # MXFP4 operand (ops.cache.Mxfp4Rows): both sides dequantise exactly
+            q = q.dequant()
         scores = torch.full((t, ld), float("-inf"), dtype=F32)
         for i in range(t):
             nv, req = int(n_valid[i]), int(tok_req[i])

@@ -43,6 +43,7 @@ class PagedCache:
     rope_dim: int
     fp8: bool
     kind: str                  # "latent" | "indexer"
+    fp4: bool = False          # indexer rows as MXFP4: dim/2 bytes of e2m1 pairs + dim/32 ue8m0 bytes (reference path only)
 
     @property
     def num_pages(self) -> int:
@@ -60,10 +61,15 @@ class PagedCache:
     def data_bytes(self) -> int:
         if self.kind == "latent":
             return (self.dim - self.rope_dim) + 2 * self.rope_dim if self.fp8 else 2 * self.dim
+        if self.fp4:
+            return self.dim // 2
         return self.dim if self.fp8 else 2 * self.dim
 
     @staticmethod
-    def page_bytes(dim: int, rope_dim: int, fp8: bool, kind: str) -> int:
+    def page_bytes(dim: int, rope_dim: int, fp8: bool, kind: str, fp4: bool = False) -> int:
+        if fp4:
+            assert kind == "indexer" and dim % 32 == 0
+            return _round_up(PAGE * (dim // 2 + dim // 32), 576)
         if kind == "latent":
             raw = PAGE * ((dim - rope_dim) + 2 * rope_dim + KV_SCALE_BYTES) if fp8 else PAGE * 2 * dim
         else:
@@ -71,9 +77,11 @@ class PagedCache:
         return _round_up(raw, 576)
 
     @staticmethod
-    def allocate(num_pages: int, dim: int, rope_dim: int, fp8: bool, kind: str, device) -> "PagedCache":
-        stride = PagedCache.page_bytes(dim, rope_dim, fp8, kind)
-        return PagedCache(torch.zeros(num_pages, stride, dtype=torch.uint8, device=device), dim, rope_dim, fp8, kind)
+    def allocate(num_pages: int, dim: int, rope_dim: int, fp8: bool, kind: str, device, fp4: bool = False) -> "PagedCache":
+        if fp4 and torch.device(device).type == "cuda":
+            raise NotImplementedError("MXFP4 indexer rows are served by the reference (CPU) path only; no GPU kernel reads them")
+        stride = PagedCache.page_bytes(dim, rope_dim, fp8, kind, fp4)
+        return PagedCache(torch.zeros(num_pages, stride, dtype=torch.uint8, device=device), dim, rope_dim, fp8, kind, fp4)
 
     # ---- CPU row access (reference path) ----------------------------------
     def write_rows_cpu(self, slots: torch.Tensor, rows: torch.Tensor) -> None:
@@ -98,7 +106,14 @@ class PagedCache:
                 for i in range(slots.numel()):
                     self.buf[page[i], r[i] * db:(r[i] + 1) * db] = data[i]
         else:
-            if self.fp8:
+            if self.fp4:
+                packed, sb = R.quant_mxfp4(rows.to(F32))
+                nsb = self.dim // 32
+                for i in range(slots.numel()):
+                    self.buf[page[i], r[i] * db:(r[i] + 1) * db] = packed[i]
+                    o = PAGE * db + r[i] * nsb
+                    self.buf[page[i], o:o + nsb] = sb[i]
+            elif self.fp8:
                 q, sc = R.indexer_k_quant(rows)
                 scb = sc.to(F32).contiguous().view(torch.uint8).view(-1, 4)
                 for i in range(slots.numel()):
@@ -114,7 +129,7 @@ class PagedCache:
         """-> (rows [n, dim] fp32 dequantised (indexer fp8: raw fp8 values), scales [n] for indexer fp8)."""
         n = slots.numel()
         out = torch.zeros(n, self.dim, dtype=F32)
-        scales = torch.ones(n, dtype=F32) if (self.kind == "indexer" and self.fp8) else None
+        scales = torch.ones(n, dtype=F32) if (self.kind == "indexer" and self.fp8 and not self.fp4) else None
         db = self.data_bytes
         for i in range(n):
             s = int(slots[i])
@@ -131,7 +146,11 @@ class PagedCache:
                 else:
                     out[i] = raw.view(BF16).to(F32)
             else:
-                if self.fp8:
+                if self.fp4:
+                    nsb = self.dim // 32
+                    o = PAGE * db + r * nsb
+                    out[i] = R.dequant_mxfp4(raw[None], self.buf[page, o:o + nsb][None])[0]
+                elif self.fp8:
                     out[i] = raw.view(FP8).to(F32)
                     o = PAGE * db + r * 4
                     scales[i] = self.buf[page, o:o + 4].view(F32)[0]
@@ -246,10 +265,42 @@ def compress_windows(kvs: torch.Tensor, ape: torch.Tensor, norm_w: torch.Tensor,
               ring, eps, _lib.status_buffer(), _lib.stream())
 
 
+@dataclass
+class Mxfp4Rows:
+    """An MXFP4 operand: packed e2m1 pairs [T, ..., d/2] and ue8m0 scale bytes [T, ..., d/32]; sliced by rows."""
+    packed: torch.Tensor
+    scales: torch.Tensor
+
+    def __getitem__(self, idx) -> "Mxfp4Rows":
+        return Mxfp4Rows(self.packed[idx], self.scales[idx])
+
+    @property
+    def shape(self):
+        return (*self.packed.shape[:-1], self.packed.shape[-1] * 2)
+
+    @property
+    def is_cuda(self) -> bool:
+        return self.packed.is_cuda
+
+    @property
+    def device(self):
+        return self.packed.device
+
+    def dequant(self) -> torch.Tensor:
+        return R.dequant_mxfp4(self.packed, self.scales)
+
+
 def indexer_q_prep(q: torch.Tensor, w: torch.Tensor, positions: torch.Tensor, inv: torch.Tensor, rope_dim: int,
-                   quantize: bool) -> Tuple[torch.Tensor, torch.Tensor]:
-    """q [T, ih, d] bf16, w [T, ih] fp32 -> (q operand: fp8 bytes or bf16 [T, ih, d], folded weights fp32)."""
+                   quantize: bool, fmt: str = "fp8"):
+    """q [T, ih, d] bf16, w [T, ih] fp32 -> (q operand: fp8 bytes or bf16 [T, ih, d], folded weights fp32).
+    fmt "mxfp4": the operand is an `Mxfp4Rows` and the weights carry no q scale (reference path only)."""
     t, ih, d = q.shape
+    if fmt == "mxfp4":
+        if q.is_cuda:
+            raise NotImplementedError("MXFP4 indexer operands are served by the reference (CPU) path only")
+        ang = positions.to(F32)[:, None] * inv[None, :]
+        packed, sb, wf = R.indexer_q_prepare_mxfp4(q, w, torch.cos(ang), torch.sin(ang), rope_dim)
+        return Mxfp4Rows(packed, sb), wf
     if not q.is_cuda:
         ang = positions.to(F32)[:, None] * inv[None, :]
         qq, wf = R.indexer_q_prepare(q, w, torch.cos(ang), torch.sin(ang), rope_dim, quantize)

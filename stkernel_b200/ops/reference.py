@@ -301,6 +301,21 @@ def indexer_q_prepare(q: torch.Tensor, weights: torch.Tensor, cos: torch.Tensor,
     return qq, weights.to(F32) * scale * fold
 
 
+def indexer_q_prepare_mxfp4(q: torch.Tensor, weights: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                            rope_dim: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """q [T, ih, d] (pre-rope), weights [T, ih] -> (packed e2m1 [T, ih, d/2], ue8m0 bytes [T, ih, d/32], weights).
+
+    RoPE on the last rope_dim dims, round to bf16, then one power-of-two scale per 32 values (the rope and non-rope
+    parts are whole blocks).  The block scales stay with q, so only d^-0.5 and ih^-0.5 fold into the head weights
+    (overlay/ops_fused_indexer_q.py:175-282)."""
+    t, ih, d = q.shape
+    qf = q.to(F32).clone()
+    qf[..., d - rope_dim:] = apply_rope_interleaved(qf[..., d - rope_dim:], cos, sin)
+    qf = qf.to(torch.bfloat16).to(F32)
+    packed, scales = quant_mxfp4(qf)
+    return packed, scales, weights.to(F32) * (d ** -0.5) * (ih ** -0.5)
+
+
 def indexer_scores(q: torch.Tensor, w: torch.Tensor, k: torch.Tensor, k_scale: Optional[torch.Tensor]) -> torch.Tensor:
     """score[t, s] = sum_h w[t,h] * relu(q[t,h] . k[s]) * k_scale[s]."""
     dots = torch.einsum("thd,sd->ths", q.to(F32), k.to(F32))

@@ -216,7 +216,8 @@ class KVManager:
             if kind == "c4a":
                 n4 = self.c4.num_pages + (1 if dcp_size > 1 else 0)          # + the scratch page
                 self.comp_cache[li] = PagedCache.allocate(n4, D, Rd, fp8, "latent", self.device)
-                self.idx_cache[li] = PagedCache.allocate(n4, cfg.index_head_dim, Rd, fp8, "indexer", self.device)
+                self.idx_cache[li] = PagedCache.allocate(n4, cfg.index_head_dim, Rd, fp8, "indexer", self.device,
+                                                         fp4=cfg.indexer_dtype == "mxfp4")
                 self.comp_state[li] = torch.zeros(max_requests, ring4, 2 * 2 * D, dtype=torch.float32, device=self.device)
                 self.idx_state[li] = torch.zeros(max_requests, ring4, 2 * 2 * cfg.index_head_dim, dtype=torch.float32,
                                                  device=self.device)
