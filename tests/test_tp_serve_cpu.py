@@ -70,9 +70,10 @@ def test_tp2_lockstep_serving_matches_tp1():
     body = {"prompt": "lockstep serving over two ranks, with a prompt long enough to fill compressed rows", "max_tokens": 8,
             "temperature": 0, "ignore_eos": True}
     outs = {}
-    for world in (1, 2):
+    # the third server also deals the ratio-4 KV pages over its two ranks (decode context parallelism)
+    for key, world, extra in ((1, 1, ()), (2, 2, ()), ("dcp", 2, ("--decode-context-parallel-size", "2"))):
         port = _free_port()
-        proc = _launch(world, port)
+        proc = _launch(world, port, extra)
         try:
             _wait_up(port, proc)
             r1 = _post(port, "/v1/completions", body)
@@ -84,11 +85,11 @@ def test_tp2_lockstep_serving_matches_tp1():
             assert chat["usage"]["completion_tokens"] == 4
             # one character more: of the two prompt lengths one is even, which the sequence-parallel residual needs
             r3 = _post(port, "/v1/completions", dict(body, prompt="!" + body["prompt"][::-1]))
-            outs[world] = (r1["choices"][0]["text"], r3["choices"][0]["text"])
+            outs[key] = (r1["choices"][0]["text"], r3["choices"][0]["text"])
         finally:
             _stop(proc)
     # the same weights split over two ranks give the same greedy text (fp32 activations on CPU)
-    assert outs[1] == outs[2]
+    assert outs[1] == outs[2] == outs["dcp"]
 
 
 def _follower_main(rank, port, result_path):
