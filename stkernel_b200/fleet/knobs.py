@@ -5,7 +5,7 @@ nothing.  The set mirrors the shell knobs of the reference launcher
 (launchers/start-hy4-tp4.sh:16-118: GPU_MEM, MAX_MODEL_LEN, MAX_NUM_SEQS, MAX_NUM_BATCHED, SPEC_TOKENS,
 FP8HEAD, MARKOV_TOPK, REFINE, MARKOV_SIDELOAD, and the env block :123-147), restated for one 8-GPU
 NVSwitch node: TP_SIZE picks the GPUs, ONESHOT arms the symmetric-memory all-reduce, FUSED the
-GEMM+collective kernels.
+GEMM+collective kernels, DCP deals the ratio-4 KV pages over the ranks (capacity for long contexts).
 """
 from __future__ import annotations
 
@@ -69,6 +69,7 @@ class Knobs:
     oneshot: int = 1
     fused: int = 1
     multimem: int = 0
+    dcp: int = 0                  # 1: ratio-4 KV pages dealt over the tensor-parallel ranks (decode context parallel)
     idx_freq: int = 4
     idx_sp: int = 1
     compressor_fp8: int = 1
@@ -143,6 +144,7 @@ def parse_knobs(env: Mapping[str, str]) -> Knobs:
     k.oneshot = _flag(env, "ONESHOT", "1")
     k.fused = _flag(env, "FUSED", "1")
     k.multimem = _flag(env, "MULTIMEM", "0")
+    k.dcp = _flag(env, "DCP", "0")
     k.idx_freq = _uint(env, "IDXFREQ", "4", 1, 64)
     k.idx_sp = _flag(env, "IDXSP", "1")
     k.compressor_fp8 = _flag(env, "COMPRESSOR_FP8", "1")
@@ -160,6 +162,12 @@ def parse_knobs(env: Mapping[str, str]) -> Knobs:
         raise KnobError("ABORT: REFINE=1 requires SPEC_TOKENS >= 2 (there are no noise slots to refine)")
     if k.fused == 1 and k.oneshot == 0 and k.tp_size > 1:
         raise KnobError("ABORT: FUSED=1 needs the symmetric-memory path (ONESHOT=1)")
+    if k.dcp == 1 and k.tp_size == 1:
+        raise KnobError("ABORT: DCP=1 deals the ratio-4 KV pages over the tensor-parallel ranks (TP_SIZE >= 2)")
+    if k.dcp == 1 and k.spec_tokens:
+        raise KnobError("ABORT: DCP=1 is not available with speculative decoding (SPEC_TOKENS=0)")
+    if k.dcp == 1:
+        k.warnings.append("DCP=1: steps run without CUDA graphs (a capacity setting for long contexts, not a speed-up)")
     if k.multimem == 1 and k.oneshot == 0:
         raise KnobError("ABORT: MULTIMEM=1 needs the symmetric-memory path (ONESHOT=1)")
     if k.max_num_batched < k.max_num_seqs * (1 + k.spec_tokens):

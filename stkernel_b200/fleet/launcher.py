@@ -66,6 +66,8 @@ def serve_command(k: Knobs, python: str = sys.executable) -> List[str]:
            "--max-model-len", str(k.max_model_len), "--max-num-seqs", str(k.max_num_seqs),
            "--max-num-batched-tokens", str(k.max_num_batched), "--graph-cap", str(k.graph_cap),
            "--kv-cache-dtype", "fp8_ds_mla", "--temperature", str(k.temperature)]
+    if k.dcp:
+        cmd += ["--decode-context-parallel-size", str(k.tp_size)]
     if k.spec_tokens:
         cmd += ["--speculative-config", json.dumps({"method": "dspark", "num_speculative_tokens": k.spec_tokens,
                                                    "draft_sample_method": "probabilistic", "markov_topk": k.markov_topk})]
