@@ -327,6 +327,7 @@ class DSV4Model:
         self.inv = Fn.inv_freq(cfg.qk_rope_head_dim, cfg.rope_theta, dev)
         self.topk_buffer: Optional[torch.Tensor] = None     # IndexCache: shared by consecutive C4A layers
         self.pipe = None                                     # parallel.pipeline.PipeStage when the model is one stage of several
+        self.pipe_defer = False                              # the engine exchanges a step's tokens when it finishes the step
         self.aux_layers: Tuple[int, ...] = ()
         self.aux_out: List[torch.Tensor] = []
         self.stats = {"sp_steps": 0, "mla_token_parallel_calls": 0, "dcp_topk_merges": 0}     # which paths ran (tests)
@@ -904,13 +905,17 @@ class DSV4Model:
         X = self.forward_hidden(meta)
         pipe = self.pipe
         if pipe is not None and not pipe.last:
-            # an earlier stage: the step's tokens come back from the last one
+            # an earlier stage: the step's tokens come back from the last one (now, or when the engine finishes the
+            # step if the exchange is deferred)
             n = logit_rows.shape[0] if logit_rows is not None else meta.token_ids.shape[0]
-            return pipe.broadcast_from_last(torch.zeros(n, dtype=torch.int64, device=meta.token_ids.device))
+            toks = torch.zeros(n, dtype=torch.int64, device=meta.token_ids.device)
+            return toks if self.pipe_defer else pipe.broadcast_from_last(toks)
         if logit_rows is not None:
             X = X.index_select(0, logit_rows)
         toks = self.sample(self.head_hidden(X), temp, seed, pos, top_k, top_p, agreed_status)
-        return pipe.broadcast_from_last(toks.contiguous()) if pipe is not None else toks
+        if pipe is None or self.pipe_defer:
+            return toks.contiguous() if pipe is not None else toks
+        return pipe.broadcast_from_last(toks.contiguous())
 
     def forward(self, meta: StepMeta, logit_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Logits for the selected token rows (all rows when logit_rows is None)."""

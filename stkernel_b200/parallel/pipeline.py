@@ -78,3 +78,62 @@ def stage_starts_inside_index_group(cfg, lo: int, hi: int) -> bool:
         if pat[li] is not None:
             return pat[li] is False
     return False
+
+
+class MicroBatchPipeline:
+    """Several engines of one stage taking turns, so that every stage has work while another engine's step is in flight.
+
+    The requests are dealt over `len(engines)` engines that share the stage's weights (each has its own scheduler and
+    its own share of the KV pools).  Tick t begins the step of engine t mod G (schedule, forward, send to the next
+    stage) and then finishes the step that engine (t + 1) mod G began G - 1 ticks ago (receive its tokens from the last
+    stage, update its requests): with G = number of stages, those tokens were produced one stage-time earlier, so in the
+    steady state no stage waits.  Every stage runs the same ticks in the same order, which keeps the sends, receives
+    and broadcasts of all stages matched.
+    """
+
+    def __init__(self, engines):
+        assert engines and all(e.model.pipe is not None for e in engines)
+        self.engines = list(engines)
+        for e in self.engines:
+            e.model.pipe_defer = True
+        self.tick = 0
+        self.overlapped_ticks = 0                          # ticks that finished one step while another was in flight
+        self.pending = [None] * len(self.engines)          # a begun, unfinished step per engine
+        self._next = 0
+        self._where = {}                                    # global request id -> (engine index, its request id)
+
+    def add_request(self, prompt, params=None) -> int:
+        gi = self._next
+        self._next += 1
+        ei = gi % len(self.engines)                         # the same on every stage
+        self._where[gi] = (ei, self.engines[ei].add_request(prompt, params))
+        return gi
+
+    def has_work(self) -> bool:
+        return any(p is not None for p in self.pending) or any(e.has_work() for e in self.engines)
+
+    def step(self):
+        """One tick.  Returns [(global request id, token)] of the step that finished in it."""
+        g = len(self.engines)
+        ei = self.tick % g
+        out = []
+        if self.pending[ei] is None and self.engines[ei].has_work():
+            self.pending[ei] = self.engines[ei].step_begin()
+        fi = (self.tick + 1) % g                            # begun G - 1 ticks ago (this tick's own step when G is 1)
+        if self.pending[fi] is not None:
+            ticket, self.pending[fi] = self.pending[fi], None
+            self.overlapped_ticks += any(p is not None for p in self.pending)
+            back = {rid: gid for gid, (e, rid) in self._where.items() if e == fi}
+            out = [(back[rid], tok) for rid, tok in self.engines[fi].step_finish(ticket)]
+        self.tick += 1
+        return out
+
+    def output(self, gid: int):
+        ei, rid = self._where[gid]
+        return self.engines[ei].requests[rid].output
+
+    def generate(self, prompts, params=None):
+        ids = [self.add_request(p, params) for p in prompts]
+        while self.has_work():
+            self.step()
+        return [self.output(i) for i in ids]

@@ -484,9 +484,16 @@ class Engine:
         device->host read, so consecutive steps queue on the device without a host round trip."""
         if self.drafter is not None:
             return self._step_spec()
+        ticket = self.step_begin()
+        return self.step_finish(ticket, forced) if ticket is not None else []
+
+    def step_begin(self):
+        """First half of a step: schedule, stage, upload and queue the model.  Returns a ticket for `step_finish`, or
+        None when nothing was scheduled.  A pipeline stage whose model defers the token exchange
+        (`parallel.pipeline.MicroBatchPipeline`) can begin another engine's step before this one is finished."""
         seqs = self.sched.schedule()
         if not seqs:
-            return []
+            return None
         t, n_req, ns = self._stage(seqs)
         self._upload(t, n_req, ns)
         max_end = max(s.start + s.n for s in seqs)
@@ -501,6 +508,14 @@ class Engine:
             toks_dev = self._decode_graph(n_req, max_comp_rows).replay()
         else:
             toks_dev = self._run_model(t, n_req, ns, max_comp_rows)
+        return seqs, ns, toks_dev
+
+    def step_finish(self, ticket, forced: Optional[Sequence[int]] = None) -> List[Tuple[int, int]]:
+        """Second half: read the sampled tokens (after the deferred exchange between pipeline stages, if any) and update
+        the requests."""
+        seqs, ns, toks_dev = ticket
+        if toks_dev is not None and self.model.pipe is not None and self.model.pipe_defer:
+            toks_dev = self.model.pipe.broadcast_from_last(toks_dev)
         out: List[Tuple[int, int]] = []
         new_tokens: List[int] = []
         if toks_dev is not None and forced is not None:

@@ -86,6 +86,39 @@ def _run_pp_tp(rank, port, path):
     dist.destroy_process_group()
 
 
+def _run_micro(rank, world, port, path):
+    """Two stages, each with two engines taking turns (micro-batches in flight)."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      STK_CPU_ACT_FP32="1", CUDA_VISIBLE_DEVICES="")
+    import torch.distributed as dist
+    from stkernel_b200.config import EngineConfig, ParallelConfig, SchedulerConfig, tiny_config
+    from stkernel_b200.models.dsv4 import DictSource, build_model_weights
+    from stkernel_b200.models.weights import init_random_weights
+    from stkernel_b200.parallel.pipeline import MicroBatchPipeline, PipeStage
+    from stkernel_b200.runtime.engine import Engine, SamplingParams
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg = tiny_config(dense_dtype="bf16", kv_cache_dtype="bf16", expert_dtype="bf16", num_hidden_layers=5,
+                      compress_ratios=(4, 4, 0, 4, 4), index_topk_freq=2)
+    w = init_random_weights(cfg, seed=2)
+    pipe = PipeStage(pp_rank=rank, pp_size=world)
+    ec = EngineConfig(model=cfg, parallel=ParallelConfig(pp_size=world),
+                      sched=SchedulerConfig(max_model_len=256, max_num_seqs=2, max_num_batched_tokens=64,
+                                            graph_cap=0)).validate()
+    weights = build_model_weights(cfg, DictSource(w), "cpu", layer_range=pipe.layer_range(cfg.num_hidden_layers))
+    mb = MicroBatchPipeline([Engine(ec, weights, "cpu", max_context=256, pipe=pipe) for _ in range(world)])
+    g = torch.Generator().manual_seed(0)
+    lens = (70, 33, 21, 90, 5)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+    # uneven lengths and token budgets: engines run out of work at different ticks
+    ids = [mb.add_request(p, SamplingParams(temperature=0.0, max_tokens=3 + 2 * i)) for i, p in enumerate(prompts)]
+    while mb.has_work():
+        mb.step()
+    json.dump({"out": [mb.output(i) for i in ids], "ticks": mb.tick, "overlapped": mb.overlapped_ticks},
+              open(f"{path}.{rank}", "w"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def _spawn(world, path):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
@@ -153,3 +186,42 @@ def test_pipeline_stages_of_tensor_parallel_ranks(tmp_path):
     for g_ in got:
         assert g_["out"] == one["out"]
         assert g_["sp_steps"] >= 1
+
+
+@pytest.mark.timeout(600)
+def test_micro_batches_in_flight_match_single_process(tmp_path):
+    """Five requests of uneven length over two stages with two engines each: the texts are those of one process that
+    runs each request alone, and most ticks have a step in flight while another begins."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    path = str(tmp_path / "mb")
+    ps = [ctx.Process(target=_run_micro, args=(r, 2, port, path)) for r in range(2)]
+    for q in ps:
+        q.start()
+    for q in ps:
+        q.join(400)
+        assert q.exitcode == 0
+    a, b = (json.load(open(f"{path}.{r}")) for r in range(2))
+    assert a == b
+    # reference: the whole model in this process, one request at a time
+    from stkernel_b200.config import EngineConfig, SchedulerConfig, tiny_config
+    from stkernel_b200.models.dsv4 import DictSource, build_model_weights
+    from stkernel_b200.models.weights import init_random_weights
+    from stkernel_b200.ops import functional as Fn
+    from stkernel_b200.runtime.engine import Engine, SamplingParams
+    Fn.set_cpu_act_dtype(torch.float32)
+    try:
+        cfg = tiny_config(dense_dtype="bf16", kv_cache_dtype="bf16", expert_dtype="bf16", num_hidden_layers=5,
+                          compress_ratios=(4, 4, 0, 4, 4), index_topk_freq=2)
+        w = init_random_weights(cfg, seed=2)
+        ec = EngineConfig(model=cfg, sched=SchedulerConfig(max_model_len=256, max_num_seqs=2, max_num_batched_tokens=64,
+                                                           graph_cap=0)).validate()
+        eng = Engine(ec, build_model_weights(cfg, DictSource(w), "cpu"), "cpu", max_context=256)
+        g = torch.Generator().manual_seed(0)
+        prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (70, 33, 21, 90, 5)]
+        want = [eng.generate([p], SamplingParams(temperature=0.0, max_tokens=3 + 2 * i))[0] for i, p in enumerate(prompts)]
+    finally:
+        Fn.set_cpu_act_dtype(torch.bfloat16)
+    assert a["out"] == want
+    assert a["overlapped"] >= a["ticks"] // 2
