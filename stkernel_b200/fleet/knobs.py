@@ -164,8 +164,6 @@ def parse_knobs(env: Mapping[str, str]) -> Knobs:
         raise KnobError("ABORT: FUSED=1 needs the symmetric-memory path (ONESHOT=1)")
     if k.dcp == 1 and k.tp_size == 1:
         raise KnobError("ABORT: DCP=1 deals the ratio-4 KV pages over the tensor-parallel ranks (TP_SIZE >= 2)")
-    if k.dcp == 1 and k.spec_tokens:
-        raise KnobError("ABORT: DCP=1 is not available with speculative decoding (SPEC_TOKENS=0)")
     if k.dcp == 1:
         k.warnings.append("DCP=1: steps run without CUDA graphs (a capacity setting for long contexts, not a speed-up)")
     if k.multimem == 1 and k.oneshot == 0:

@@ -239,8 +239,6 @@ class Engine:
         dcp = cfg.parallel.dcp_size
         if dcp > 1 and (dcp != cfg.parallel.tp_size or comm is None):
             raise ValueError("dcp_size must be 1 or tp_size (the context-parallel ranks are the tensor-parallel group)")
-        if dcp > 1 and cfg.spec.method == "dspark":
-            raise ValueError("speculative decoding is not available with decode context parallelism")
         pools = size_pools(cfg.model, sc.max_num_seqs, ctx, sc.max_num_batched_tokens, dcp)
         if cfg.cache.num_pages is not None:
             pools["swa_pages"] = max(pools["swa_pages"], cfg.cache.num_pages)

@@ -109,6 +109,61 @@ def test_context_parallel_with_a_cached_prefix(tmp_path):
         assert r["out"] == one["out"]
 
 
+def _run_spec(rank, world, port, path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      STK_CPU_ACT_FP32="1", CUDA_VISIBLE_DEVICES="")
+    import torch.distributed as dist
+    from stkernel_b200.config import EngineConfig, ParallelConfig, SchedulerConfig, SpecConfig, tiny_config
+    from stkernel_b200.models.dsv4 import DictSource, build_model_weights
+    from stkernel_b200.models.weights import init_random_weights
+    from stkernel_b200.runtime.engine import Engine, SamplingParams
+    from stkernel_b200.spec import dspark as DS
+    comm = None
+    if world > 1:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from stkernel_b200.parallel.communicator import Communicator
+        comm = Communicator(device="cpu", use_symm=False)
+    cfg = tiny_config(n_mtp_layers=2, dspark_target_layer_ids=(0, 1), dspark_markov_rank=16, dense_dtype="bf16",
+                      kv_cache_dtype="bf16", expert_dtype="bf16")
+    w = init_random_weights(cfg, seed=0)
+    tw = build_model_weights(cfg, DictSource(w), "cpu", rank, world)
+    # one rank: plain decoding; two ranks: speculative decoding over context-parallel caches
+    spec = SpecConfig(method="dspark", num_speculative_tokens=3, markov_topk=8) if world > 1 else SpecConfig()
+    dw = DS.build_draft_weights(cfg, DictSource(w), tw, "cpu", rank, world) if world > 1 else None
+    ec = EngineConfig(model=cfg, parallel=ParallelConfig(tp_size=world, ep_size=world, dcp_size=world), spec=spec,
+                      sched=SchedulerConfig(max_model_len=1024, max_num_seqs=4, max_num_batched_tokens=96,
+                                            graph_cap=0)).validate()
+    eng = Engine(ec, tw, "cpu", comm, rank, max_context=1024, draft_weights=dw)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (600, 150, 7)]
+    out = eng.generate(prompts, SamplingParams(temperature=0.8, seed=11, max_tokens=14))
+    json.dump({"out": out, "drafts": eng.metrics.spec_num_drafts}, open(f"{path}.{rank}", "w"))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(900)
+def test_speculative_decoding_over_context_parallel_caches(tmp_path):
+    """Verify rows, rollbacks of rejected rows and the draft layers with the ratio-4 pages dealt over two ranks: the
+    sampled text (fixed seeds) equals plain decoding on one rank."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    res = {}
+    for world in (1, 2):
+        port = _free_port()
+        path = str(tmp_path / f"w{world}")
+        ps = [ctx.Process(target=_run_spec, args=(r, world, port, path)) for r in range(world)]
+        for q in ps:
+            q.start()
+        for q in ps:
+            q.join(500)
+            assert q.exitcode == 0
+        res[world] = [json.load(open(f"{path}.{r}")) for r in range(world)]
+    assert res[2][0]["out"] == res[2][1]["out"] == res[1][0]["out"]
+    assert res[2][0]["drafts"] > 0 and res[1][0]["drafts"] == 0
+
+
 def test_group_table_deals_pages_over_ranks():
     from stkernel_b200.runtime.kv import GroupTable
     tabs = [GroupTable("c4", 4, 2, 10, torch.device("cpu"), 0.25, r, 3) for r in range(3)]

@@ -36,7 +36,6 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     ({"EFFORT": "extreme"}, "EFFORT must be one of"),
     ({"TEMP": "hot"}, "TEMP must be a number"),
     ({"DCP": "1", "TP_SIZE": "1", "SPEC_TOKENS": "0"}, "TP_SIZE >= 2"),
-    ({"DCP": "1"}, "not available with speculative decoding"),
 ])
 def test_launcher_fails_closed_with_exit_2(env, needle):
     """Run the real entry point in a child process: a bad knob ends it with exit code 2 and an ABORT
@@ -62,9 +61,9 @@ def test_good_knobs_dry_run_and_command():
     assert launcher.main(["--dry-run", "--no-attest"], env={"MODEL_PATH": "/models/x"}) == 0
     k2 = parse_knobs({"MAX_NUM_SEQS": "64", "MAX_NUM_BATCHED": "4096"})
     assert k2.warnings and "outside CUDA graphs" in k2.warnings[0]
-    k3 = parse_knobs({"DCP": "1", "SPEC_TOKENS": "0", "TP_SIZE": "4"})
+    k3 = parse_knobs({"DCP": "1", "TP_SIZE": "4"})
     c3 = launcher.serve_command(k3, python="python")
-    assert c3[c3.index("--decode-context-parallel-size") + 1] == "4" and "--speculative-config" not in c3
+    assert c3[c3.index("--decode-context-parallel-size") + 1] == "4" and "--speculative-config" in c3
     assert any("without CUDA graphs" in w for w in k3.warnings)
     assert "--decode-context-parallel-size" not in cmd
     assert "MODEL_PATH is not set" in launcher.preflight(parse_knobs({}), gpu_count=8)
