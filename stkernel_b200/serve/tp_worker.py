@@ -130,22 +130,40 @@ def build_engine(a, rank: int, world: int, device) -> Tuple[Engine, Any]:
             mcfg = flash_config(a.layers, n_mtp_layers=n_mtp,
                                 dspark_target_layer_ids=(a.layers // 4, a.layers // 2, a.layers - 1) if n_mtp else ())
         src = RandomSource(0)
-    ecfg = EngineConfig(model=mcfg, parallel=ParallelConfig(tp_size=world, ep_size=world,
+    # ranks are laid out stage-major: global rank = pp_rank * tp + tp_rank
+    pp = getattr(a, "pipeline_parallel_size", 1)
+    tp = world // pp
+    pp_rank, tp_rank = divmod(rank, tp)
+    ecfg = EngineConfig(model=mcfg, parallel=ParallelConfig(tp_size=tp, ep_size=tp, pp_size=pp,
                                                             dcp_size=getattr(a, "decode_context_parallel_size", 1),
                                                             fused_collectives=os.environ.get("STK_FUSED_COLLECTIVES", "1") == "1"),
                         sched=SchedulerConfig(max_model_len=a.max_model_len, max_num_seqs=a.max_num_seqs,
                                               max_num_batched_tokens=a.max_num_batched_tokens, graph_cap=a.graph_cap),
                         spec=spec_cfg).validate()
     comm = None
-    if world > 1:
+    pipe = None
+    layer_range = None
+    if pp > 1:
+        from ..parallel.pipeline import PipeStage
+        pipe = PipeStage(pp_rank=pp_rank, pp_size=pp, tp_rank=tp_rank, tp_size=tp)
+        layer_range = pipe.layer_range(mcfg.num_hidden_layers)
+    if tp > 1:
         from ..parallel.communicator import Communicator
-        comm = Communicator(device=device, use_symm=os.environ.get("STK_ONESHOT_AR", "1") == "1" and device.type == "cuda")
-    weights = build_model_weights(mcfg, src, device, rank, world, head_fp8=mcfg.dense_dtype == "fp8" and device.type == "cuda")
+        group = None
+        if pp > 1:
+            # one tensor-parallel group per stage; every rank creates every group.  The stages' groups use the library
+            # collectives (the symmetric-memory kernels are set up for one group spanning all ranks).
+            groups = [dist.new_group(list(range(s * tp, (s + 1) * tp))) for s in range(pp)]
+            group = groups[pp_rank]
+        comm = Communicator(group=group, device=device,
+                            use_symm=pp == 1 and os.environ.get("STK_ONESHOT_AR", "1") == "1" and device.type == "cuda")
+    weights = build_model_weights(mcfg, src, device, tp_rank, tp, head_fp8=mcfg.dense_dtype == "fp8" and device.type == "cuda",
+                                  layer_range=layer_range)
     draft = None
     if spec_cfg.method == "dspark":
         from ..spec.dspark import build_draft_weights
-        draft = build_draft_weights(mcfg, src, weights, device, rank, world)
-    eng = Engine(ecfg, weights, device, comm, rank, draft_weights=draft)
+        draft = build_draft_weights(mcfg, src, weights, device, tp_rank, tp)
+    eng = Engine(ecfg, weights, device, comm, tp_rank, draft_weights=draft, pipe=pipe)
     return eng, mcfg
 
 
@@ -162,6 +180,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--max-num-seqs", type=int, default=32)
     ap.add_argument("--max-num-batched-tokens", type=int, default=4096)
     ap.add_argument("--graph-cap", type=int, default=64)
+    ap.add_argument("--pipeline-parallel-size", type=int, default=1,
+                    help="contiguous stages of layers; WORLD_SIZE = pipeline x tensor parallel size (stage-major ranks)")
     ap.add_argument("--decode-context-parallel-size", type=int, default=1,
                     help="1, or the tensor-parallel size: the ratio-4 KV caches are dealt page by page over the ranks")
     ap.add_argument("--kv-cache-dtype", default="fp8_ds_mla")
@@ -177,8 +197,9 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    if a.tensor_parallel_size != world:
-        print(f"ABORT: --tensor-parallel-size {a.tensor_parallel_size} but WORLD_SIZE={world}", file=sys.stderr)
+    if a.tensor_parallel_size * a.pipeline_parallel_size != world:
+        print(f"ABORT: --tensor-parallel-size {a.tensor_parallel_size} x --pipeline-parallel-size "
+              f"{a.pipeline_parallel_size} but WORLD_SIZE={world}", file=sys.stderr)
         return 2
     use_cuda = torch.cuda.is_available()
     device = torch.device(f"cuda:{local}" if use_cuda else "cpu")

@@ -42,7 +42,7 @@ def _wait_up(port, proc, timeout=180):
     raise TimeoutError("server did not come up")
 
 
-def _launch(world, port, extra=()):
+def _launch(world, port, extra=(), tp=None):
     # tiny thresholds so that the prompt's prefill step takes the sequence-parallel indexer path and the
     # token-parallel attention path (q / output all-to-all) at world 2, and (for a prompt of even length) the
     # sequence-parallel residual (all-gather / reduce-scatter around each sub-block)
@@ -51,7 +51,7 @@ def _launch(world, port, extra=()):
                STK_SEQ_PARALLEL_MIN_ROWS="4")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(_free_port()), "-m", "stkernel_b200.serve.tp_worker", "--tiny", "--port", str(port),
-           "--tensor-parallel-size", str(world), "--max-model-len", "512", "--max-num-seqs", "4",
+           "--tensor-parallel-size", str(tp if tp is not None else world), "--max-model-len", "512", "--max-num-seqs", "4",
            "--max-num-batched-tokens", "128", "--graph-cap", "0", "--heartbeat-timeout", "20", *extra]
     return subprocess.Popen(cmd, env=env, cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, start_new_session=True)
 
@@ -70,10 +70,12 @@ def test_tp2_lockstep_serving_matches_tp1():
     body = {"prompt": "lockstep serving over two ranks, with a prompt long enough to fill compressed rows", "max_tokens": 8,
             "temperature": 0, "ignore_eos": True}
     outs = {}
-    # the third server also deals the ratio-4 KV pages over its two ranks (decode context parallelism)
-    for key, world, extra in ((1, 1, ()), (2, 2, ()), ("dcp", 2, ("--decode-context-parallel-size", "2"))):
+    # the third server also deals the ratio-4 KV pages over its two ranks (decode context parallelism); the fourth
+    # runs its two ranks as two pipeline stages of one layer each
+    for key, world, extra, tp in ((1, 1, (), None), (2, 2, (), None), ("dcp", 2, ("--decode-context-parallel-size", "2"), None),
+                                  ("pp", 2, ("--pipeline-parallel-size", "2"), 1)):
         port = _free_port()
-        proc = _launch(world, port, extra)
+        proc = _launch(world, port, extra, tp)
         try:
             _wait_up(port, proc)
             r1 = _post(port, "/v1/completions", body)
@@ -89,7 +91,7 @@ def test_tp2_lockstep_serving_matches_tp1():
         finally:
             _stop(proc)
     # the same weights split over two ranks give the same greedy text (fp32 activations on CPU)
-    assert outs[1] == outs[2] == outs["dcp"]
+    assert outs[1] == outs[2] == outs["dcp"] == outs["pp"]
 
 
 def _follower_main(rank, port, result_path):
