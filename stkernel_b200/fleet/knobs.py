@@ -69,6 +69,7 @@ class Knobs:
     oneshot: int = 1
     fused: int = 1
     multimem: int = 0
+    pp_size: int = 1              # pipeline stages; ranks = TP_SIZE x PP_SIZE
     dcp: int = 0                  # 1: ratio-4 KV pages dealt over the tensor-parallel ranks (decode context parallel)
     idx_freq: int = 4
     idx_sp: int = 1
@@ -145,6 +146,7 @@ def parse_knobs(env: Mapping[str, str]) -> Knobs:
     k.fused = _flag(env, "FUSED", "1")
     k.multimem = _flag(env, "MULTIMEM", "0")
     k.dcp = _flag(env, "DCP", "0")
+    k.pp_size = _uint(env, "PP_SIZE", "1", 1, 8)
     k.idx_freq = _uint(env, "IDXFREQ", "4", 1, 64)
     k.idx_sp = _flag(env, "IDXSP", "1")
     k.compressor_fp8 = _flag(env, "COMPRESSOR_FP8", "1")
@@ -162,6 +164,12 @@ def parse_knobs(env: Mapping[str, str]) -> Knobs:
         raise KnobError("ABORT: REFINE=1 requires SPEC_TOKENS >= 2 (there are no noise slots to refine)")
     if k.fused == 1 and k.oneshot == 0 and k.tp_size > 1:
         raise KnobError("ABORT: FUSED=1 needs the symmetric-memory path (ONESHOT=1)")
+    if k.tp_size * k.pp_size > 8:
+        raise KnobError(f"ABORT: TP_SIZE x PP_SIZE must fit one 8-GPU node (got {k.tp_size} x {k.pp_size})")
+    if k.pp_size > 1 and k.spec_tokens:
+        raise KnobError("ABORT: PP_SIZE > 1 is not available with speculative decoding (SPEC_TOKENS=0)")
+    if k.pp_size > 1:
+        k.warnings.append("PP_SIZE > 1: steps run without CUDA graphs and the stages' tensor-parallel groups use NCCL")
     if k.dcp == 1 and k.tp_size == 1:
         raise KnobError("ABORT: DCP=1 deals the ratio-4 KV pages over the tensor-parallel ranks (TP_SIZE >= 2)")
     if k.dcp == 1:

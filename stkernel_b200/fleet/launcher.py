@@ -52,13 +52,13 @@ def preflight(k: Knobs, gpu_count: Optional[int] = None) -> List[str]:
         problems.append(f"model config missing ({k.model_path}/config.json)")
     if k.markov_sideload and not os.path.isfile(k.markov_sideload):
         problems.append(f"MARKOV_SIDELOAD missing ({k.markov_sideload})")
-    if gpu_count is not None and gpu_count < k.tp_size:
-        problems.append(f"TP_SIZE={k.tp_size} but only {gpu_count} GPU(s) visible")
+    if gpu_count is not None and gpu_count < k.tp_size * k.pp_size:
+        problems.append(f"TP_SIZE={k.tp_size} x PP_SIZE={k.pp_size} but only {gpu_count} GPU(s) visible")
     return problems
 
 
 def serve_command(k: Knobs, python: str = sys.executable) -> List[str]:
-    cmd = [python, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={k.tp_size}",
+    cmd = [python, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={k.tp_size * k.pp_size}",
            "--master-addr", "127.0.0.1", "--master-port", "29400",
            "-m", "stkernel_b200.serve.tp_worker",
            "--model", k.model_path, "--served-model-name", k.served_name, "--port", str(k.port),
@@ -66,6 +66,8 @@ def serve_command(k: Knobs, python: str = sys.executable) -> List[str]:
            "--max-model-len", str(k.max_model_len), "--max-num-seqs", str(k.max_num_seqs),
            "--max-num-batched-tokens", str(k.max_num_batched), "--graph-cap", str(k.graph_cap),
            "--kv-cache-dtype", "fp8_ds_mla", "--temperature", str(k.temperature)]
+    if k.pp_size > 1:
+        cmd += ["--pipeline-parallel-size", str(k.pp_size)]
     if k.dcp:
         cmd += ["--decode-context-parallel-size", str(k.tp_size)]
     if k.spec_tokens:

@@ -36,6 +36,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     ({"EFFORT": "extreme"}, "EFFORT must be one of"),
     ({"TEMP": "hot"}, "TEMP must be a number"),
     ({"DCP": "1", "TP_SIZE": "1", "SPEC_TOKENS": "0"}, "TP_SIZE >= 2"),
+    ({"PP_SIZE": "2"}, "TP_SIZE x PP_SIZE must fit"),
+    ({"PP_SIZE": "2", "TP_SIZE": "4"}, "not available with speculative decoding"),
 ])
 def test_launcher_fails_closed_with_exit_2(env, needle):
     """Run the real entry point in a child process: a bad knob ends it with exit code 2 and an ABORT
@@ -65,7 +67,13 @@ def test_good_knobs_dry_run_and_command():
     c3 = launcher.serve_command(k3, python="python")
     assert c3[c3.index("--decode-context-parallel-size") + 1] == "4" and "--speculative-config" in c3
     assert any("without CUDA graphs" in w for w in k3.warnings)
-    assert "--decode-context-parallel-size" not in cmd
+    assert "--decode-context-parallel-size" not in cmd and "--pipeline-parallel-size" not in cmd
+    k4 = parse_knobs({"PP_SIZE": "2", "TP_SIZE": "4", "SPEC_TOKENS": "0"})
+    c4 = launcher.serve_command(k4, python="python")
+    assert "--nproc-per-node=8" in c4 and c4[c4.index("--pipeline-parallel-size") + 1] == "2"
+    assert c4[c4.index("--tensor-parallel-size") + 1] == "4"
+    assert any("only 4 GPU" in p for p in launcher.preflight(parse_knobs({"MODEL_PATH": "/models/x", "PP_SIZE": "2", "TP_SIZE": "4",
+                                                                          "SPEC_TOKENS": "0"}), gpu_count=4))
     assert "MODEL_PATH is not set" in launcher.preflight(parse_knobs({}), gpu_count=8)
     assert any("only 2 GPU" in p for p in launcher.preflight(parse_knobs({"MODEL_PATH": "/models/x"}), gpu_count=2))
 
