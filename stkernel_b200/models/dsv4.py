@@ -29,7 +29,7 @@ from ..ops import moe as M
 from ..utils.spans import span
 from ..ops.functional import LinearWeight
 from ..ops.scratch import side_branch
-from ..runtime.planning import (dcp_global_row, dcp_local_rows, dcp_owner, pp_layer_range, sp_gather_sizes,
+from ..runtime.planning import (dcp_global_row, dcp_local_index, dcp_local_rows, dcp_owner, pp_layer_range, sp_gather_sizes,
                                 split_indexer_prefill_chunks)
 from .dsv4_oracle import index_cache_computes
 from .weights import compressor_slots
@@ -313,6 +313,17 @@ class StepMeta:
     max_comp_rows: int             # upper bound of compressed rows any request holds (c4 group)
     max_c128_rows: int = 0
     pure_decode: bool = False      # every request contributes exactly one token (no token attends to another new row)
+
+
+def dcp_merge_candidates(gids: torch.Tensor, vals: torch.Tensor, k: int) -> torch.Tensor:
+    """gids [T, n] int32 global row ids (-1 = no candidate), vals [T, n] fp32 scores (-inf for no candidate) -> the k best
+    ids per row by (score descending, row ascending), -1 padded.  Two stable sorts, so equal scores resolve the same way
+    on every rank and as on a rank that holds all rows (`runtime.planning.merge_topk_candidates` states the same rule)."""
+    order = torch.sort(torch.where(gids >= 0, gids, torch.full_like(gids, 1 << 30)), dim=1, stable=True)[1]
+    gids, vals = torch.gather(gids, 1, order), torch.gather(vals, 1, order)
+    top, pos = torch.sort(vals, dim=1, descending=True, stable=True)
+    ids = torch.gather(gids, 1, pos[:, :k])
+    return torch.where(top[:, :k] > float("-inf"), ids, torch.full_like(ids, -1))
 
 
 class DSV4Model:
@@ -642,13 +653,7 @@ class DSV4Model:
         allc = self.comm.all_gather_dim0(cand).view(n, T, 2, K)
         gids = allc[:, :, 0].permute(1, 0, 2).reshape(T, n * K)
         vals = allc[:, :, 1].permute(1, 0, 2).reshape(T, n * K).view(torch.float32)
-        # K best by (score descending, row ascending): two stable sorts, so equal scores resolve the same way on every
-        # rank and as on a rank that holds all rows
-        order = torch.sort(torch.where(gids >= 0, gids, torch.full_like(gids, 1 << 30)), dim=1, stable=True)[1]
-        gids, vals = torch.gather(gids, 1, order), torch.gather(vals, 1, order)
-        top, pos = torch.sort(vals, dim=1, descending=True, stable=True)
-        ids = torch.gather(gids, 1, pos[:, :K])
-        self.topk_buffer[:T] = torch.where(top[:, :K] > ninf, ids, torch.full_like(ids, -1))
+        self.topk_buffer[:T] = dcp_merge_candidates(gids, vals, K)
         self.stats["dcp_topk_merges"] += 1
 
     def _dcp_stage(self, li: int, ids: torch.Tensor, tok_req: torch.Tensor, grp):
@@ -662,9 +667,9 @@ class DSV4Model:
         sb = KV_SCALE_BYTES if cache.fp8 else 0
         ok = ids >= 0
         idl = ids.clamp(min=0).long()
-        lp = idl // PAGE
         mine = ok & (dcp_owner(idl, n, PAGE) == r)
-        phys = grp.table_dev[tok_req.clamp(min=0).long()[:, None], lp].long()
+        # this rank's own numbering of its rows: page = local index // PAGE of the local block table
+        phys = self._dcp_local_table(grp)[tok_req.clamp(min=0).long()[:, None], dcp_local_index(idl, n, PAGE) // PAGE].long()
         phys = torch.where(mine, phys, torch.zeros_like(phys)).clamp(min=0)
         rr = idl % PAGE
         rows = t * K

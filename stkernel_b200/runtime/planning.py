@@ -4,13 +4,11 @@
   two budgets at once -- gathered-K workspace rows and the fp32 logits buffer -- sub-chunking a single
   oversized request along its queries (budget rule of overlay/indexer.py `split_indexer_prefill_chunks`,
   exercised by tests/test_logic.py:103-148 in the reference);
-* `indexer_sp_ranges`: which query rows of a mixed step a TP rank scores when indexer scoring is
-  sequence-parallel: decode rows and small chunks on every rank, large chunks ceil-split across ranks,
-  adjacent spans merged; a decode-only step is not split (overlay/attention.py
-  `_indexer_sp_owned_ranges`, tests/test_logic.py:154-216);
+* `sp_gather_sizes`: how a large step's rows are ceil-split over the TP ranks when indexer scoring is
+  sequence-parallel (the split rule of overlay/attention.py `_indexer_sp_owned_ranges`);
 * decode-context-parallel helpers: interleaved ownership of KV positions and the merge of per-rank
   top-k candidates into the global top-k (the DCP merge of probes/sai_probe.py:1872-2618);
-* pipeline stage layer ranges (overlay/nvidia_model.py:1623-1648), tile rounding, layer kinds.
+* pipeline stage layer ranges (overlay/nvidia_model.py:1623-1648) and the IndexCache compute/reuse pattern.
 """
 from __future__ import annotations
 
@@ -54,36 +52,6 @@ def split_indexer_prefill_chunks(seq_lens: Sequence[int], query_lens: Sequence[i
 # ---------------------------------------------------------------------------------------
 # sequence-parallel indexer scoring
 # ---------------------------------------------------------------------------------------
-def merge_ranges(ranges: Sequence[Range]) -> List[Range]:
-    out: List[Range] = []
-    for a, b in sorted(r for r in ranges if r[1] > r[0]):
-        if out and a <= out[-1][1]:
-            out[-1] = (out[-1][0], max(out[-1][1], b))
-        else:
-            out.append((a, b))
-    return out
-
-
-def indexer_sp_ranges(num_decode_tokens: int, prefill_chunks: Optional[Sequence[Range]], tp_size: int, rank: int,
-                      min_rows: int = 256) -> Optional[List[Range]]:
-    """Row ranges of the step's token dimension that `rank` scores; None = score everything (decode-only
-    step, or TP 1).  Every row is owned by at least one rank; rows of large chunks by exactly one."""
-    if tp_size <= 1 or not prefill_chunks:
-        return None
-    mine: List[Range] = []
-    if num_decode_tokens > 0:
-        mine.append((0, num_decode_tokens))
-    for a, b in prefill_chunks:
-        n = b - a
-        if n < min_rows:
-            mine.append((a, b))
-            continue
-        shard = -(-n // tp_size)
-        lo = min(b, a + rank * shard)
-        mine.append((lo, min(b, lo + shard)))
-    return merge_ranges(mine)
-
-
 def sp_gather_sizes(prefill_chunk: Range, tp_size: int) -> List[int]:
     """Rows each rank contributes for one large chunk (for the ragged all-gather of its top-k rows)."""
     a, b = prefill_chunk
@@ -121,14 +89,15 @@ def dcp_global_row(local, dcp_size: int, rank: int, interleave: int = 1):
 
 
 def merge_topk_candidates(per_rank: Sequence[Sequence[Tuple[float, int]]], k: int) -> List[int]:
-    """Global top-k row ids from each rank's local top-k (score, global row) lists; ties to the lower row."""
+    """Global top-k row ids from each rank's local top-k (score, global row) lists; ties to the lower row.
+    The plain statement of what `models.dsv4.dcp_merge_candidates` does on whole steps with tensor sorts."""
     allc = [c for lst in per_rank for c in lst]
     allc.sort(key=lambda c: (-c[0], c[1]))
     return [row for _, row in allc[:k]]
 
 
 # ---------------------------------------------------------------------------------------
-# pipeline stages, tiles, layer kinds
+# pipeline stages, IndexCache pattern
 # ---------------------------------------------------------------------------------------
 def pp_layer_range(num_layers: int, pp_size: int, rank: int) -> Range:
     """Contiguous layers of a stage; earlier stages take the remainder (the last stage also runs the head)."""
@@ -137,25 +106,13 @@ def pp_layer_range(num_layers: int, pp_size: int, rank: int) -> Range:
     return start, start + base + (1 if rank < rem else 0)
 
 
-def round_up_tile(n: int, tile: int) -> int:
-    return -(-n // tile) * tile
-
-
-def layer_kinds(compress_ratios: Sequence[int], num_layers: int) -> List[str]:
-    out = []
-    for i in range(num_layers):
-        r = compress_ratios[i] if i < len(compress_ratios) else 0
-        out.append("swa" if r <= 1 else "c4a" if r == 4 else "c128a" if r == 128 else f"ratio{r}")
-    return out
-
-
 def index_cache_pattern(compress_ratios: Sequence[int], num_layers: int, freq: int) -> List[Optional[bool]]:
     """Per layer: True = computes its own top-k (F), False = reuses the previous F layer's (S), None = no
     indexer.  Counted over C4A layers only; the first C4A layer always computes."""
     out: List[Optional[bool]] = []
     ordinal = 0
-    for k in layer_kinds(compress_ratios, num_layers):
-        if k != "c4a":
+    for i in range(num_layers):
+        if (compress_ratios[i] if i < len(compress_ratios) else 0) != 4:
             out.append(None)
             continue
         out.append(freq <= 1 or ordinal % freq == 0)

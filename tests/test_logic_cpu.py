@@ -52,26 +52,12 @@ def test_prefill_chunker_budgets():
 
 # ---- sequence-parallel indexer ranges --------------------------------------------------------------
 def test_indexer_sp_coverage():
-    tp, ndt = 4, 12
-    chunks = [(12, 140), (140, 4236), (4236, 4801)]
-    per_rank = [P.indexer_sp_ranges(ndt, chunks, tp, r) for r in range(tp)]
-    for rr in per_rank:
-        rows = set()
-        for a, b in rr:
-            assert b > a
-            rows.update(range(a, b))
-        assert set(range(0, ndt)) <= rows and set(range(12, 140)) <= rows            # replicated parts
-    assert per_rank[0] == [(0, 1164), (4236, 4378)]                                  # adjacent spans merged
-    assert len(per_rank[1]) == 3
-    for a, b in chunks[1:]:
+    tp = 4
+    for a, b in ((140, 4236), (4236, 4801), (0, 3), (7, 7)):
+        sizes = P.sp_gather_sizes((a, b), tp)
         n = b - a
-        owned = [{x for lo, hi in rr for x in range(lo, hi) if a <= x < b} for rr in per_rank]
-        assert set().union(*owned) == set(range(a, b)) and sum(len(s) for s in owned) == n
-        assert all(len(s) <= -(-n // tp) for s in owned)
-        assert P.sp_gather_sizes((a, b), tp) == [len(s) for s in owned]
-    assert P.indexer_sp_ranges(8, None, tp, 0) is None and P.indexer_sp_ranges(8, [], tp, 0) is None
-    assert P.indexer_sp_ranges(0, [(0, 4096)], 1, 0) is None
-    assert P.merge_ranges([(5, 9), (0, 3), (3, 5), (20, 20)]) == [(0, 9)]
+        assert sum(sizes) == n and len(sizes) == tp
+        assert all(x <= -(-n // tp) for x in sizes) and sizes == sorted(sizes, reverse=True)      # ceil split, short tail
 
 
 # ---- DCP / PP / helpers ---------------------------------------------------------------------------
@@ -93,15 +79,26 @@ def test_dcp_index_math_and_topk_merge():
         per_rank.append(sorted(mine, key=lambda c: -c[0])[:32])
     want = [i for _, i in sorted(((scores[i], i) for i in range(500)), key=lambda c: (-c[0], c[1]))[:32]]
     assert P.merge_topk_candidates(per_rank, 32) == want
+    # the model's tensor merge follows the same rule, ties included
+    from stkernel_b200.models.dsv4 import dcp_merge_candidates
+    tied = [round(x, 1) for x in scores]
+    per_rank = []
+    for r in range(4):
+        mine = sorted(((tied[i], i) for i in range(500) if P.dcp_owner(i, 4) == r), key=lambda c: (-c[0], c[1]))[:32]
+        per_rank.append(mine + [(float("-inf"), -1)] * 3)                            # short lists are padded
+    gids = torch.tensor([[i for lst in per_rank for _, i in lst]], dtype=torch.int32)
+    vals = torch.tensor([[v for lst in per_rank for v, _ in lst]], dtype=torch.float32)
+    want = P.merge_topk_candidates([[c for c in lst if c[1] >= 0] for lst in per_rank], 32)
+    assert dcp_merge_candidates(gids, vals, 32)[0].tolist() == want
+    few = dcp_merge_candidates(gids[:, :35], vals[:, :35], 34)[0].tolist()          # one rank's 32 candidates + padding
+    assert few[:32] == [i for _, i in per_rank[0][:32]] and few[32:] == [-1, -1]
 
 
-def test_pp_ranges_tiles_and_layer_kinds():
+def test_pp_ranges_and_index_cache_pattern():
     for n, pp in ((48, 4), (43, 4), (6, 8)):
         spans = [P.pp_layer_range(n, pp, r) for r in range(pp)]
         assert spans[0][0] == 0 and spans[-1][1] == n and all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
         assert max(b - a for a, b in spans) - min(b - a for a, b in spans) <= 1
-    assert P.round_up_tile(1, 128) == 128 and P.round_up_tile(128, 128) == 128 and P.round_up_tile(129, 128) == 256
-    assert P.layer_kinds((4, 0, 128, 1), 5) == ["c4a", "swa", "c128a", "swa", "swa"]
     ratios = (4, 0, 4, 4, 0, 4, 4, 4)
     pat = P.index_cache_pattern(ratios, 8, 3)
     assert pat == [True, None, False, False, None, True, False, False]
