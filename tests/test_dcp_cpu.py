@@ -39,8 +39,8 @@ def _run(rank, world, port, path, kv_dtype, stage_mb, shared_prefix=False):
                                             graph_cap=0)).validate()
     eng = Engine(ec, build_model_weights(cfg, DictSource(w), "cpu", rank, world), "cpu", comm, rank, max_context=1024)
     g = torch.Generator().manual_seed(0)
-    # 4 tokens per compressed row, 64 rows per page: 700 tokens reach the third page of the ratio-4 caches
-    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (700, 290)]
+    # 4 tokens per compressed row, 64 rows per page: 530 tokens reach the third page of the ratio-4 caches
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (530, 270)]
     hits = None
     if shared_prefix:
         # a finished request leaves its first 512 tokens (two pages of compressed rows: one per rank) in the prefix
@@ -79,24 +79,18 @@ def _spawn(world, path, kv_dtype, stage_mb="64", shared_prefix=False):
 @pytest.mark.parametrize("kv_dtype", ["bf16", "fp8_ds_mla"])
 def test_context_parallel_decode_matches_one_rank(tmp_path, kv_dtype):
     one = _spawn(1, str(tmp_path / "one"), kv_dtype)[0]
-    two = _spawn(2, str(tmp_path / "two"), kv_dtype)
+    # the bf16 run has a staging budget of zero megabytes, which forces one token per staging call (the block loop of
+    # large steps); the fp8 run stages a whole step at once
+    two = _spawn(2, str(tmp_path / "two"), kv_dtype, stage_mb="0" if kv_dtype == "bf16" else "64")
     assert one["stats"]["dcp_topk_merges"] == 0
     for r in two:
         assert r["out"] == one["out"]
         assert r["stats"]["dcp_topk_merges"] >= 1
-    # 700 + 290 tokens fill 3 + 2 pages of compressed rows: the single rank holds all 5, rank 0 pages 0 and 2 of the
+    # 530 + 270 tokens fill 3 + 2 pages of compressed rows: the single rank holds all 5, rank 0 pages 0 and 2 of the
     # first request and page 0 of the second, rank 1 the two pages numbered 1
     assert one["c4_peak"] == 5
     assert [r["c4_peak"] for r in two] == [3, 2]
     assert all(r["c4_pool"] < one["c4_pool"] for r in two)
-
-
-@pytest.mark.timeout(900)
-def test_context_parallel_prefill_in_token_blocks(tmp_path):
-    # a staging budget of zero megabytes forces one token per staging call: the block loop of large steps
-    one = _spawn(1, str(tmp_path / "one"), "bf16")[0]
-    two = _spawn(2, str(tmp_path / "two"), "bf16", stage_mb="0")
-    assert two[0]["out"] == one["out"] and two[1]["out"] == one["out"]
 
 
 @pytest.mark.timeout(900)
@@ -135,8 +129,8 @@ def _run_spec(rank, world, port, path):
                                             graph_cap=0)).validate()
     eng = Engine(ec, tw, "cpu", comm, rank, max_context=1024, draft_weights=dw)
     g = torch.Generator().manual_seed(0)
-    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (600, 150, 7)]
-    out = eng.generate(prompts, SamplingParams(temperature=0.8, seed=11, max_tokens=14))
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (300, 150, 7)]
+    out = eng.generate(prompts, SamplingParams(temperature=0.8, seed=11, max_tokens=10))
     json.dump({"out": out, "drafts": eng.metrics.spec_num_drafts}, open(f"{path}.{rank}", "w"))
     if world > 1:
         dist.barrier()
