@@ -212,6 +212,11 @@ class CacheConfig:
     gpu_memory_utilization: float = 0.60
     num_pages: Optional[int] = None  # explicit pool size (tests / bench)
     enable_prefix_caching: bool = True
+    # Context tokens the compressed-KV pools hold over all requests together.  None: room for max_num_seqs requests of
+    # max_model_len each (nothing ever waits for pages).  With `size_by_memory` the engine derives it on a GPU from
+    # gpu_memory_utilization x device memory minus what is allocated when it starts (the weights).
+    kv_pool_tokens: Optional[int] = None
+    size_by_memory: bool = False
 
     def validate(self) -> None:
         if self.page_tokens != 64:

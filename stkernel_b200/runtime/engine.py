@@ -20,7 +20,7 @@ from ..models.dsv4 import DSV4Model, ModelWeights, StepMeta
 from ..ops import attention as A
 from ..ops import sampling as S
 from ..ops.cache import PAGE
-from .kv import KVManager, OutOfPages, size_pools
+from .kv import KVManager, OutOfPages, kv_bytes_per_context_token, size_pools
 from .metrics import Metrics
 
 
@@ -137,11 +137,13 @@ class Scheduler:
                 if self.prefix_cache is None or not self.prefix_cache.entries:
                     break
                 # cached prefixes hold pages too: give them up, oldest first, before refusing a request
-                self.prefix_cache.make_room(*self.kv.admit_needs(min(budget, len(r.prompt)), ctx))
+                need_swa, need_c4 = self.kv.admit_needs(min(budget, len(r.prompt)), ctx)
+                self.prefix_cache.make_room(need_swa, need_c4 + self.kv.promised())
                 if not self.kv.can_admit(min(budget, len(r.prompt)), ctx):
                     break
             self.waiting.pop(0)
             r.row = self.kv.alloc_row()
+            self.kv.reserve(r.row, ctx)
             self.running.append(r)
             start = 0
             if self.prefix_cache is not None:
@@ -239,7 +241,14 @@ class Engine:
         dcp = cfg.parallel.dcp_size
         if dcp > 1 and (dcp != cfg.parallel.tp_size or comm is None):
             raise ValueError("dcp_size must be 1 or tp_size (the context-parallel ranks are the tensor-parallel group)")
-        pools = size_pools(cfg.model, sc.max_num_seqs, ctx, sc.max_num_batched_tokens, dcp)
+        pool_tokens = cfg.cache.kv_pool_tokens
+        if pool_tokens is None and cfg.cache.size_by_memory and self.device.type == "cuda":
+            free, total = torch.cuda.mem_get_info(self.device)
+            budget = cfg.cache.gpu_memory_utilization * total - (total - free)
+            lo_hi = pipe.layer_range(cfg.model.num_hidden_layers) if pipe is not None else (0, cfg.model.num_hidden_layers)
+            per_token = kv_bytes_per_context_token(cfg.model, list(range(*lo_hi)), dcp)
+            pool_tokens = max(ctx, int(budget / max(per_token, 1e-9)))
+        pools = size_pools(cfg.model, sc.max_num_seqs, ctx, sc.max_num_batched_tokens, dcp, pool_tokens)
         if cfg.cache.num_pages is not None:
             pools["swa_pages"] = max(pools["swa_pages"], cfg.cache.num_pages)
         has_c128 = any(cfg.model.layer_kind(i) == "c128a" for i in range(cfg.model.num_hidden_layers))
@@ -318,6 +327,8 @@ class Engine:
         req = Request(rid, list(prompt), params or SamplingParams())
         if len(req.prompt) + req.params.max_tokens > self.cfg.sched.max_model_len + 64:
             raise ValueError("request exceeds max_model_len")
+        if not self.kv.fits(min(len(req.prompt) + req.params.max_tokens, self.cfg.sched.max_model_len)):
+            raise ValueError("request needs more compressed-KV pages than the pool holds")
         self.requests[rid] = req
         self.sched.add(req)
         self.metrics.requests_total += 1

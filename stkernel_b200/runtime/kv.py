@@ -175,6 +175,12 @@ class GroupTable:
     def pages_in_use(self) -> int:
         return self.num_pages - len(self.free)
 
+    def held(self, row: int) -> int:
+        """Pool pages behind the resident logical pages of `row` (with context parallelism: this rank's only)."""
+        n, r = self.dcp_size, self.dcp_rank
+        below = lambda x: (x - r + n - 1) // n if x > r else 0         # logical pages < x that this rank stores
+        return below(self.hi[row]) - below(self.lo[row])
+
 
 class KVManager:
     """Owns the group tables, the per-layer cache tensors and the request-row allocator."""
@@ -225,6 +231,11 @@ class KVManager:
                 self.comp_cache[li] = PagedCache.allocate(self.c128.num_pages, D, Rd, fp8, "latent", self.device)
                 self.comp_state[li] = torch.zeros(max_requests, ring128, 2 * D, dtype=torch.float32, device=self.device)
         self.free_rows = list(range(max_requests - 1, -1, -1))
+        self.spec_tokens = spec_tokens
+        # ratio-4 pages promised to admitted requests for their whole context (allocated page by page as they grow):
+        # admission counts the part not yet allocated as taken, so a pool smaller than max_requests x max_model_len
+        # makes requests wait instead of running out of pages in the middle of a step
+        self.reserved: Dict[int, int] = {}
 
     # ---- request rows -------------------------------------------------------
     def alloc_row(self) -> int:
@@ -235,7 +246,16 @@ class KVManager:
     def free_row(self, row: int) -> None:
         for g in (self.swa, self.c4, self.c128):
             g.release_all(row)
+        self.reserved.pop(row, None)
         self.free_rows.append(row)
+
+    def reserve(self, row: int, context: int) -> None:
+        """Promise request `row` the ratio-4 pages of a context of `context` tokens."""
+        self.reserved[row] = self.admit_needs(0, context)[1]
+
+    def promised(self) -> int:
+        """Ratio-4 pages promised to running requests and not allocated yet."""
+        return sum(max(0, need - self.c4.held(row)) for row, need in self.reserved.items())
 
     # ---- per-step residency ---------------------------------------------------
     def prepare(self, row: int, start_pos: int, n_tokens: int, lookback: Optional[int] = None) -> None:
@@ -258,12 +278,17 @@ class KVManager:
 
     def admit_needs(self, n_tokens: int, context: int) -> Tuple[int, int]:
         """(sliding-window pages, ratio-4 pages) a new request of this size must find free."""
-        c4 = (context // 4) // PAGE + 1
+        c4 = ((context + (2 * self.spec_tokens + 1 if self.spec_tokens else 0)) // 4) // PAGE + 1
         return (min(n_tokens, context) + self.cfg.sliding_window) // PAGE + 2, -(-c4 // self.dcp_size)
+
+    def fits(self, context: int) -> bool:
+        """Whether a request of this context could ever be admitted (its ratio-4 pages fit the whole pool)."""
+        return self.admit_needs(0, context)[1] <= self.c4.num_pages
 
     def can_admit(self, n_tokens: int, context: int) -> bool:
         need_swa, need_c4 = self.admit_needs(n_tokens, context)
-        return bool(self.free_rows) and len(self.swa.free) >= need_swa and len(self.c4.free) >= need_c4
+        return (bool(self.free_rows) and len(self.swa.free) >= need_swa
+                and len(self.c4.free) - self.promised() >= need_c4)
 
     def sync(self, parity: int = 0) -> None:
         for g in (self.swa, self.c4, self.c128):
@@ -278,10 +303,33 @@ class KVManager:
         return n
 
 
-def size_pools(cfg: ModelConfig, max_requests: int, max_context: int, max_chunk: int, dcp_size: int = 1) -> Dict[str, int]:
+def size_pools(cfg: ModelConfig, max_requests: int, max_context: int, max_chunk: int, dcp_size: int = 1,
+               pool_tokens: Optional[int] = None) -> Dict[str, int]:
     """Pages needed so that `max_requests` sequences of `max_context` tokens fit (no prefix sharing); with decode
-    context parallelism `c4_pages` is one rank's share (every dcp_size-th page of each request, rounded up)."""
+    context parallelism `c4_pages` is one rank's share (every dcp_size-th page of each request, rounded up).
+    pool_tokens: cap the compressed pools at this many context tokens over all requests together (plus the partial
+    pages every request may leave open); admission then makes requests wait for room."""
     swa = max_requests * ((cfg.sliding_window + PAGE - 1) // PAGE + 2) + (max_chunk + PAGE - 1) // PAGE + 2
     c4 = max_requests * -(-((max_context // 4 + PAGE - 1) // PAGE + 1) // dcp_size)
     c128 = max_requests * ((max_context // 128 + PAGE - 1) // PAGE + 1)
+    if pool_tokens is not None:
+        c4 = min(c4, -(-(pool_tokens // 4) // (PAGE * dcp_size)) + max_requests)
+        c128 = min(c128, -(-(pool_tokens // 128) // PAGE) + 2 * max_requests + 1)
     return {"swa_pages": swa, "c4_pages": c4, "c128_pages": c128}
+
+
+def kv_bytes_per_context_token(cfg: ModelConfig, layers: Optional[List[int]] = None, dcp_size: int = 1) -> float:
+    """Bytes of compressed KV (latent + indexer-K rows of the ratio-4 layers, latent rows of the ratio-128 layers) that
+    one token of context costs a rank: the quantity that turns a memory budget into `pool_tokens`."""
+    fp8 = cfg.kv_cache_dtype == "fp8_ds_mla"
+    D, Rd, di = cfg.head_dim, cfg.qk_rope_head_dim, cfg.index_head_dim
+    latent = PagedCache.page_bytes(D, Rd, fp8, "latent") / PAGE
+    index = PagedCache.page_bytes(di, Rd, fp8, "indexer", fp4=cfg.indexer_dtype == "mxfp4") / PAGE
+    total = 0.0
+    for li in (layers if layers is not None else range(cfg.num_hidden_layers)):
+        kind = cfg.layer_kind(li)
+        if kind == "c4a":
+            total += (latent + index) / 4 / dcp_size
+        elif kind == "c128a":
+            total += latent / 128
+    return total

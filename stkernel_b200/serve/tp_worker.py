@@ -24,7 +24,7 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
-from ..config import EngineConfig, ParallelConfig, SchedulerConfig, SpecConfig, flash_config, tiny_config
+from ..config import CacheConfig, EngineConfig, ParallelConfig, SchedulerConfig, SpecConfig, flash_config, tiny_config
 from ..runtime.engine import Engine, SamplingParams
 from .api_server import AsyncEngine, create_app
 from .tokenizer import ByteTokenizer, ChatTokenizer, HFTokenizer
@@ -139,6 +139,7 @@ def build_engine(a, rank: int, world: int, device) -> Tuple[Engine, Any]:
                                                             fused_collectives=os.environ.get("STK_FUSED_COLLECTIVES", "1") == "1"),
                         sched=SchedulerConfig(max_model_len=a.max_model_len, max_num_seqs=a.max_num_seqs,
                                               max_num_batched_tokens=a.max_num_batched_tokens, graph_cap=a.graph_cap),
+                        cache=CacheConfig(gpu_memory_utilization=a.gpu_memory_utilization, size_by_memory=True),
                         spec=spec_cfg).validate()
     comm = None
     pipe = None
