@@ -18,6 +18,7 @@ never stalls a step.
 from __future__ import annotations
 
 import asyncio
+import dataclasses
 import json
 import queue
 import threading
@@ -260,6 +261,31 @@ def _usage(n_prompt: int, n_out: int) -> Dict[str, int]:
     return {"prompt_tokens": n_prompt, "completion_tokens": n_out, "total_tokens": n_prompt + n_out}
 
 
+def flatten_content_parts(messages: List[Dict[str, Any]]) -> List[Dict[str, Any]]:
+    """OpenAI content-part arrays (`"content": [{"type": "text", "text": ...}, ...]`) -> plain strings, text parts joined
+    by newlines; any other part type is a 400 (the model reads text only)."""
+    out = []
+    for m in messages:
+        c = m.get("content")
+        if isinstance(c, list):
+            texts = []
+            for part in c:
+                kind = part.get("type") if isinstance(part, dict) else None
+                if kind not in ("text", "input_text"):
+                    raise HTTPException(status_code=400, detail=f"unsupported content part type {kind!r}")
+                texts.append(part.get("text", ""))
+            m = {**m, "content": "\n".join(texts)}
+        out.append(m)
+    return out
+
+
+def choice_count(body: Dict[str, Any], limit: int = 16) -> int:
+    n = body.get("n", 1)
+    if not isinstance(n, int) or isinstance(n, bool) or not 1 <= n <= limit:
+        raise HTTPException(status_code=400, detail=f"n must be an integer in [1, {limit}]")
+    return n
+
+
 def attach_response_format(messages: List[Dict[str, Any]], rf: Optional[Dict[str, Any]]) -> List[Dict[str, Any]]:
     """OpenAI `response_format` -> the schema block of the leading system message, which the chat encoding renders
     (overlay/tok_deepseek_v4_encoding.py:258-436 takes it from the message): `json_schema` passes its schema,
@@ -409,7 +435,7 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
         if thinking:
             kwargs.setdefault("thinking", True)
         tools = body.get("tools") if body.get("tool_choice") != "none" else None
-        msgs = attach_response_format(body["messages"], body.get("response_format"))
+        msgs = attach_response_format(flatten_content_parts(body["messages"]), body.get("response_format"))
         ids = tokenizer.apply_chat_template(msgs, tools=tools, **kwargs)
         return ids, thinking, tools
 
@@ -418,6 +444,9 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
         try:
             body = await request.json()
             ids, thinking, tools = prepare_chat(body)
+            n_choices = choice_count(body)
+        except HTTPException as e:
+            return err(e.status_code, str(e.detail))
         except Exception as e:
             return err(400, f"{type(e).__name__}: {e}")
         if len(ids) >= max_len:
@@ -426,11 +455,13 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
         stop = body.get("stop") or []
         stop = [stop] if isinstance(stop, str) else list(stop)
         rid = f"chatcmpl-{uuid.uuid4().hex}"
-        pipe = OutputPipeline(tokenizer, thinking, tools, stop)
+        # one output pipeline (detokenizer, reasoning splitter, tool parser) and one seed per choice
+        pipes = [OutputPipeline(tokenizer, thinking, tools, stop) for _ in range(n_choices)]
+        seeds = [dataclasses.replace(params, seed=(params.seed + i) & 0x7FFFFFFF) for i in range(n_choices)]
         base = {"id": rid, "object": "chat.completion.chunk", "created": int(time.time()), "model": model_name}
         include_usage = bool((body.get("stream_options") or {}).get("include_usage"))
 
-        def finish(reason: Optional[str]) -> str:
+        def finish(pipe: OutputPipeline, reason: Optional[str]) -> str:
             if pipe.has_tool_calls:
                 return "tool_calls"
             return "stop" if (pipe.stopped or reason == "stop") else (reason or "stop")
@@ -438,53 +469,89 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
         if body.get("stream"):
             async def events():
                 n_out = 0
-                yield sse({**base, "choices": [{"index": 0, "delta": {"role": "assistant", "content": ""}, "finish_reason": None}]})
-                reason = None
-                async for ev in aeng.generate(ids, params):
-                    if ev.error:
-                        yield sse({"error": {"message": ev.error, "type": "internal_error"}})
-                        break
-                    n_out += len(ev.tokens)
-                    piece = pipe.push(ev.tokens, ev.finished, eos_id)
-                    delta: Dict[str, Any] = {}
-                    if piece.reasoning:
-                        delta["reasoning_content"] = piece.reasoning
-                    if piece.content:
-                        delta["content"] = piece.content
-                    if piece.tool_calls:
-                        delta["tool_calls"] = [t.to_openai() for t in piece.tool_calls]
-                    if delta:
-                        yield sse({**base, "choices": [{"index": 0, "delta": delta, "finish_reason": None}]})
-                    reason = ev.finish_reason
-                    if pipe.stopped or ev.finished:
-                        break
-                yield sse({**base, "choices": [{"index": 0, "delta": {}, "finish_reason": finish(reason)}]})
+                for i in range(n_choices):
+                    yield sse({**base, "choices": [{"index": i, "delta": {"role": "assistant", "content": ""}, "finish_reason": None}]})
+                merged: asyncio.Queue = asyncio.Queue()
+
+                async def pump(i: int):
+                    try:
+                        async for ev in aeng.generate(ids, seeds[i]):
+                            await merged.put((i, ev))
+                            if ev.error or ev.finished:
+                                return
+                    finally:
+                        await merged.put((i, None))
+
+                tasks = [asyncio.ensure_future(pump(i)) for i in range(n_choices)]
+                open_choices, done, reasons = n_choices, set(), [None] * n_choices
+                try:
+                    while open_choices:
+                        i, ev = await merged.get()
+                        if ev is None:
+                            open_choices -= 1
+                            if i not in done:
+                                done.add(i)
+                                yield sse({**base, "choices": [{"index": i, "delta": {}, "finish_reason": finish(pipes[i], reasons[i])}]})
+                            continue
+                        if i in done:
+                            continue
+                        if ev.error:
+                            yield sse({"error": {"message": ev.error, "type": "internal_error"}})
+                            done.add(i)
+                            continue
+                        n_out += len(ev.tokens)
+                        piece = pipes[i].push(ev.tokens, ev.finished, eos_id)
+                        delta: Dict[str, Any] = {}
+                        if piece.reasoning:
+                            delta["reasoning_content"] = piece.reasoning
+                        if piece.content:
+                            delta["content"] = piece.content
+                        if piece.tool_calls:
+                            delta["tool_calls"] = [t.to_openai() for t in piece.tool_calls]
+                        if delta:
+                            yield sse({**base, "choices": [{"index": i, "delta": delta, "finish_reason": None}]})
+                        reasons[i] = ev.finish_reason
+                        if pipes[i].stopped or ev.finished:
+                            done.add(i)
+                            yield sse({**base, "choices": [{"index": i, "delta": {}, "finish_reason": finish(pipes[i], reasons[i])}]})
+                            if not ev.finished:
+                                tasks[i].cancel()             # a stop string: the generator's exit aborts the request
+                finally:
+                    for t in tasks:
+                        t.cancel()
                 if include_usage:
                     yield sse({**base, "choices": [], "usage": _usage(len(ids), n_out)})
                 yield sse("[DONE]")
             return StreamingResponse(events(), media_type="text/event-stream")
 
-        reasoning, content, n_out, reason = "", "", 0, None
-        async for ev in aeng.generate(ids, params):
-            if ev.error:
-                return err(500, ev.error, "internal_error")
-            n_out += len(ev.tokens)
-            piece = pipe.push(ev.tokens, ev.finished, eos_id)
-            reasoning += piece.reasoning
-            content += piece.content
-            reason = ev.finish_reason
-            if pipe.stopped or ev.finished:
-                break
-        message: Dict[str, Any] = {"role": "assistant", "content": content or None}
-        if reasoning:
-            message["reasoning_content"] = reasoning
-        if pipe.has_tool_calls:
-            message["tool_calls"] = [{"id": c["id"], "type": "function",
-                                      "function": {"name": c["name"], "arguments": c["arguments"]}}
-                                     for c in pipe.tools.complete_calls]
+        async def collect(i: int):
+            pipe = pipes[i]
+            reasoning, content, n_out, reason = "", "", 0, None
+            async for ev in aeng.generate(ids, seeds[i]):
+                if ev.error:
+                    return ev.error
+                n_out += len(ev.tokens)
+                piece = pipe.push(ev.tokens, ev.finished, eos_id)
+                reasoning += piece.reasoning
+                content += piece.content
+                reason = ev.finish_reason
+                if pipe.stopped or ev.finished:
+                    break
+            message: Dict[str, Any] = {"role": "assistant", "content": content or None}
+            if reasoning:
+                message["reasoning_content"] = reasoning
+            if pipe.has_tool_calls:
+                message["tool_calls"] = [{"id": c["id"], "type": "function",
+                                          "function": {"name": c["name"], "arguments": c["arguments"]}}
+                                         for c in pipe.tools.complete_calls]
+            return {"index": i, "message": message, "finish_reason": finish(pipe, reason)}, n_out
+
+        results = await asyncio.gather(*(collect(i) for i in range(n_choices)))
+        for r in results:
+            if isinstance(r, str):
+                return err(500, r, "internal_error")
         return {"id": rid, "object": "chat.completion", "created": base["created"], "model": model_name,
-                "choices": [{"index": 0, "message": message, "finish_reason": finish(reason)}],
-                "usage": _usage(len(ids), n_out)}
+                "choices": [r[0] for r in results], "usage": _usage(len(ids), sum(r[1] for r in results))}
 
     # ---- raw completions ------------------------------------------------------------------
     @app.post("/v1/completions")

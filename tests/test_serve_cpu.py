@@ -257,6 +257,47 @@ def test_chat_stream_matches_nonstream(client):
     assert chunks[-2]["choices"][0]["finish_reason"] == "length"
 
 
+def test_several_choices_and_content_parts(client):
+    """`n` choices: one seed, detokenizer and parser per choice; streamed chunks carry the choice index and add up to
+    the whole answers.  Content-part arrays are read as their text."""
+    body = {"messages": [{"role": "user", "content": "pick"}], "max_tokens": 6, "temperature": 1.0, "seed": 5, "ignore_eos": True,
+            "n": 3}
+    r = client.post("/v1/chat/completions", json=body).json()
+    assert [c["index"] for c in r["choices"]] == [0, 1, 2] and r["usage"]["completion_tokens"] == 18
+    texts = [c["message"]["content"] or "" for c in r["choices"]]
+    assert len(set(texts)) > 1                                                     # different seeds, different samples
+    # choice i samples with seed + i: the first choice is the answer of the same request with n = 1
+    one = client.post("/v1/chat/completions", json={**body, "n": 1}).json()
+    assert one["choices"][0]["message"] == r["choices"][0]["message"]
+    shifted = client.post("/v1/chat/completions", json={**body, "n": 1, "seed": 7}).json()
+    assert shifted["choices"][0]["message"] == r["choices"][2]["message"]
+    with client.stream("POST", "/v1/chat/completions", json={**body, "stream": True, "stream_options": {"include_usage": True}}) as resp:
+        lines = _sse(resp)
+    assert lines[-1] == "[DONE]"
+    chunks = [json.loads(x) for x in lines[:-1]]
+    streamed = ["", "", ""]
+    finished = {}
+    for c in chunks:
+        for ch in c["choices"]:
+            streamed[ch["index"]] += ch["delta"].get("content", "")
+            if ch["finish_reason"]:
+                assert ch["index"] not in finished
+                finished[ch["index"]] = ch["finish_reason"]
+    assert streamed == texts and finished == {0: "length", 1: "length", 2: "length"}
+    assert chunks[-1]["usage"]["completion_tokens"] == 18
+    assert client.post("/v1/chat/completions", json={**body, "n": 0}).status_code == 400
+    assert client.post("/v1/chat/completions", json={**body, "n": 99}).status_code == 400
+    # content parts
+    parts = {"messages": [{"role": "user", "content": [{"type": "text", "text": "hello"}, {"type": "text", "text": "there"}]}],
+             "max_tokens": 4, "temperature": 0, "ignore_eos": True}
+    plain = {**parts, "messages": [{"role": "user", "content": "hello\nthere"}]}
+    a, b = client.post("/v1/chat/completions", json=parts).json(), client.post("/v1/chat/completions", json=plain).json()
+    assert a["choices"][0]["message"] == b["choices"][0]["message"] and a["usage"] == b["usage"]
+    bad = {**parts, "messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "x"}}]}]}
+    r = client.post("/v1/chat/completions", json=bad)
+    assert r.status_code == 400 and "image_url" in r.json()["error"]["message"]
+
+
 def test_thinking_mode_routes_to_reasoning(client):
     body = {"messages": [{"role": "user", "content": "think"}], "max_tokens": 5, "temperature": 0, "ignore_eos": True,
             "chat_template_kwargs": {"thinking": True}}
