@@ -6,9 +6,10 @@ health probe and prefix-cache reset; bench/bench-dec.py:60-119 `/metrics`; bench
 `/start_profile` + `/stop_profile`; bench/bench-ctx.py:28-82 streaming with usage):
 
     GET  /health, /v1/models, /metrics
-    POST /v1/chat/completions   (stream or not; stream_options.include_usage; tools; thinking kwargs)
+    POST /v1/chat/completions   (stream or not; stream_options.include_usage; tools; thinking kwargs; n choices)
     POST /v1/completions        (raw prompt or token ids)
     POST /v1/messages           (Anthropic wire: text / thinking / tool_use blocks, SSE events)
+    POST /v1/messages/count_tokens, /tokenize, /detokenize
     POST /start_profile, /stop_profile, /reset_prefix_cache
 
 `AsyncEngine` owns the engine on one worker thread (the thread that owns the CUDA context and
@@ -595,22 +596,57 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
         return {**base, "choices": [{"index": 0, "text": pipe.text, "finish_reason": "stop" if pipe.stopped else reason}],
                 "usage": _usage(len(ids), n_out)}
 
+    # ---- tokenizer routes -------------------------------------------------------------------
+    @app.post("/tokenize")
+    async def tokenize(request: Request):
+        """{"prompt": str} or {"messages": [...], "tools": [...]} -> the ids the matching completion route would run."""
+        try:
+            body = await request.json()
+            if "messages" in body:
+                ids, _, _ = prepare_chat(body)
+            else:
+                ids = tokenizer.encode(body["prompt"])
+        except HTTPException as e:
+            return err(e.status_code, str(e.detail))
+        except Exception as e:
+            return err(400, f"{type(e).__name__}: {e}")
+        return {"tokens": list(ids), "count": len(ids), "max_model_len": max_len}
+
+    @app.post("/detokenize")
+    async def detokenize(request: Request):
+        try:
+            body = await request.json()
+            return {"prompt": tokenizer.decode([int(t) for t in body["tokens"]])}
+        except Exception as e:
+            return err(400, f"{type(e).__name__}: {e}")
+
     # ---- Anthropic messages ---------------------------------------------------------------
+    def prepare_messages(body: Dict[str, Any]):
+        msgs, tools = anthropic_to_chat(body)
+        th = body.get("thinking") or {}
+        kwargs = dict(base_kwargs)
+        if th.get("type") == "enabled":
+            kwargs["thinking"] = True
+        elif th.get("type") == "disabled":
+            kwargs["thinking"] = False
+        thinking = thinking_enabled(kwargs, default_thinking)
+        if thinking:
+            kwargs.setdefault("thinking", True)
+        return tokenizer.apply_chat_template(msgs, tools=tools, **kwargs), thinking, tools
+
+    @app.post("/v1/messages/count_tokens")
+    async def count_tokens(request: Request):
+        try:
+            ids, _, _ = prepare_messages(await request.json())
+        except Exception as e:
+            return err(400, f"{type(e).__name__}: {e}")
+        return {"input_tokens": len(ids)}
+
     @app.post("/v1/messages")
     async def messages(request: Request):
         try:
             body = await request.json()
-            msgs, tools = anthropic_to_chat(body)
-            th = body.get("thinking") or {}
-            kwargs = dict(base_kwargs)
-            if th.get("type") == "enabled":
-                kwargs["thinking"] = True
-            elif th.get("type") == "disabled":
-                kwargs["thinking"] = False
-            thinking = thinking_enabled(kwargs, default_thinking)
-            if thinking:
-                kwargs.setdefault("thinking", True)
-            ids = tokenizer.apply_chat_template(msgs, tools=tools, **kwargs)
+            ids, thinking, tools = prepare_messages(body)
         except Exception as e:
             return err(400, f"{type(e).__name__}: {e}")
         if len(ids) >= max_len:

@@ -298,6 +298,21 @@ def test_several_choices_and_content_parts(client):
     assert r.status_code == 400 and "image_url" in r.json()["error"]["message"]
 
 
+def test_tokenizer_routes(client):
+    t = client.post("/tokenize", json={"prompt": "abc def"}).json()
+    assert t["count"] == len(t["tokens"]) > 0 and t["max_model_len"] == 512
+    assert client.post("/detokenize", json={"tokens": t["tokens"]}).json()["prompt"] == "abc def"
+    msgs = [{"role": "user", "content": "count me"}]
+    chat = client.post("/tokenize", json={"messages": msgs}).json()
+    run = client.post("/v1/chat/completions", json={"messages": msgs, "max_tokens": 1, "temperature": 0}).json()
+    assert chat["count"] == run["usage"]["prompt_tokens"]
+    n = client.post("/v1/messages/count_tokens", json={"messages": msgs, "system": "be brief"}).json()["input_tokens"]
+    m = client.post("/v1/messages", json={"messages": msgs, "system": "be brief", "max_tokens": 1}).json()
+    assert n == m["usage"]["input_tokens"]
+    assert client.post("/tokenize", json={}).status_code == 400
+    assert client.post("/detokenize", json={"tokens": "x"}).status_code == 400
+
+
 def test_thinking_mode_routes_to_reasoning(client):
     body = {"messages": [{"role": "user", "content": "think"}], "max_tokens": 5, "temperature": 0, "ignore_eos": True,
             "chat_template_kwargs": {"thinking": True}}
