@@ -53,7 +53,7 @@ def _run(rank, world, port, path):
         dist.destroy_process_group()
 
 
-def _run_pp_tp(rank, port, path):
+def _run_pp_tp(rank, port, path, dcp=1):
     """Four ranks: two pipeline stages of two tensor-parallel ranks each (global rank = pp_rank * 2 + tp_rank), with
     the sequence-parallel residual on, so a stage boundary carries each rank's share of the token rows."""
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE="4",
@@ -73,7 +73,7 @@ def _run_pp_tp(rank, port, path):
                       compress_ratios=(4, 4, 0, 4, 4), index_topk_freq=2)
     w = init_random_weights(cfg, seed=2)
     pipe = PipeStage(pp_rank=pp_rank, pp_size=2, tp_rank=tp_rank, tp_size=2)
-    ec = EngineConfig(model=cfg, parallel=ParallelConfig(tp_size=2, ep_size=2, pp_size=2),
+    ec = EngineConfig(model=cfg, parallel=ParallelConfig(tp_size=2, ep_size=2, pp_size=2, dcp_size=dcp),
                       sched=SchedulerConfig(max_model_len=256, max_num_seqs=2, max_num_batched_tokens=64,
                                             graph_cap=0)).validate()
     weights = build_model_weights(cfg, DictSource(w), "cpu", tp_rank, 2, layer_range=pipe.layer_range(cfg.num_hidden_layers))
@@ -170,13 +170,15 @@ def test_pipeline_stage_arithmetic_and_guards():
 
 
 @pytest.mark.timeout(600)
-def test_pipeline_stages_of_tensor_parallel_ranks(tmp_path):
+@pytest.mark.parametrize("dcp", [1, 2])
+def test_pipeline_stages_of_tensor_parallel_ranks(tmp_path, dcp):
+    """dcp 2: each stage's two ranks also deal the ratio-4 KV pages of the stage's layers between them."""
     import torch.multiprocessing as mp
     one = _spawn(1, str(tmp_path / "one"))[0]
     ctx = mp.get_context("spawn")
     port = _free_port()
     path = str(tmp_path / "pptp")
-    ps = [ctx.Process(target=_run_pp_tp, args=(r, port, path)) for r in range(4)]
+    ps = [ctx.Process(target=_run_pp_tp, args=(r, port, path, dcp)) for r in range(4)]
     for q in ps:
         q.start()
     for q in ps:
