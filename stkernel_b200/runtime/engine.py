@@ -248,6 +248,12 @@ class Engine:
             lo_hi = pipe.layer_range(cfg.model.num_hidden_layers) if pipe is not None else (0, cfg.model.num_hidden_layers)
             per_token = kv_bytes_per_context_token(cfg.model, list(range(*lo_hi)), dcp)
             pool_tokens = max(ctx, int(budget / max(per_token, 1e-9)))
+            if comm is not None or pipe is not None:
+                # every rank (and every stage) runs the same scheduler: they must agree on the pool, so take the smallest
+                import torch.distributed as dist
+                seen = [None] * dist.get_world_size()
+                dist.all_gather_object(seen, pool_tokens)
+                pool_tokens = min(seen)
         pools = size_pools(cfg.model, sc.max_num_seqs, ctx, sc.max_num_batched_tokens, dcp, pool_tokens)
         if cfg.cache.num_pages is not None:
             pools["swa_pages"] = max(pools["swa_pages"], cfg.cache.num_pages)
