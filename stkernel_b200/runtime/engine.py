@@ -20,7 +20,7 @@ from ..models.dsv4 import DSV4Model, ModelWeights, StepMeta
 from ..ops import attention as A
 from ..ops import sampling as S
 from ..ops.cache import PAGE
-from .kv import KVManager, OutOfPages, kv_bytes_per_context_token, size_pools
+from .kv import KVManager, OutOfPages, memory_pool_tokens, size_pools
 from .metrics import Metrics
 
 
@@ -244,10 +244,9 @@ class Engine:
         pool_tokens = cfg.cache.kv_pool_tokens
         if pool_tokens is None and cfg.cache.size_by_memory and self.device.type == "cuda":
             free, total = torch.cuda.mem_get_info(self.device)
-            budget = cfg.cache.gpu_memory_utilization * total - (total - free)
             lo_hi = pipe.layer_range(cfg.model.num_hidden_layers) if pipe is not None else (0, cfg.model.num_hidden_layers)
-            per_token = kv_bytes_per_context_token(cfg.model, list(range(*lo_hi)), dcp)
-            pool_tokens = max(ctx, int(budget / max(per_token, 1e-9)))
+            pool_tokens = memory_pool_tokens(cfg.model, cfg.cache.gpu_memory_utilization, free, total, ctx,
+                                             list(range(*lo_hi)), dcp)
             if comm is not None or pipe is not None:
                 # every rank (and every stage) runs the same scheduler: they must agree on the pool, so take the smallest
                 import torch.distributed as dist

@@ -333,3 +333,13 @@ def kv_bytes_per_context_token(cfg: ModelConfig, layers: Optional[List[int]] = N
         elif kind == "c128a":
             total += latent / 128
     return total
+
+
+def memory_pool_tokens(cfg: ModelConfig, utilization: float, free_bytes: int, total_bytes: int, min_tokens: int,
+                       layers: Optional[List[int]] = None, dcp_size: int = 1) -> int:
+    """Context tokens the compressed pools may hold when this process may use `utilization` of the device's memory:
+    that share minus what is taken already (the weights; other tenants of a shared GPU count too), divided by the
+    bytes one token costs, but never less than one request of `min_tokens` (launchers/start-hy4-tp4.sh:16-30 GPU_MEM)."""
+    budget = utilization * total_bytes - (total_bytes - free_bytes)
+    per_token = kv_bytes_per_context_token(cfg, layers, dcp_size)
+    return max(min_tokens, int(budget / max(per_token, 1e-9)))

@@ -9,7 +9,7 @@ from stkernel_b200.models.weights import init_random_weights
 from stkernel_b200.ops import functional as Fn
 from stkernel_b200.ops.cache import PAGE
 from stkernel_b200.runtime.engine import Engine, SamplingParams
-from stkernel_b200.runtime.kv import kv_bytes_per_context_token, size_pools
+from stkernel_b200.runtime.kv import kv_bytes_per_context_token, memory_pool_tokens, size_pools
 
 
 @pytest.fixture(autouse=True)
@@ -79,3 +79,18 @@ def test_bytes_per_context_token_and_pool_sizes():
     assert capped["c4_pages"] == -(-(2_800_000 // 4) // PAGE) + 32 < full["c4_pages"]
     assert capped["swa_pages"] == full["swa_pages"]
     assert size_pools(cfg, 32, 430000, 4096, dcp_size=8, pool_tokens=2_800_000)["c4_pages"] == -(-(2_800_000 // 4) // (PAGE * 8)) + 32
+
+
+def test_pool_tokens_from_a_memory_share():
+    from stkernel_b200.config import flash_config
+    cfg = flash_config(num_layers=48)
+    gb = 1 << 30
+    per = kv_bytes_per_context_token(cfg)
+    # 60 % of 180 GB with 25 GB taken by the weights: 83 GB of compressed KV
+    got = memory_pool_tokens(cfg, 0.60, free_bytes=155 * gb, total_bytes=180 * gb, min_tokens=32768)
+    assert abs(got - 83 * gb / per) / got < 1e-6 and got > 15_000_000
+    # the same share of a GPU that other tenants have filled: one request's worth, never less
+    assert memory_pool_tokens(cfg, 0.60, free_bytes=20 * gb, total_bytes=180 * gb, min_tokens=32768) == 32768
+    # context parallelism over 8 ranks: about 8 times the tokens in the same memory (the ratio-128 rows stay replicated)
+    wide = memory_pool_tokens(cfg, 0.60, 155 * gb, 180 * gb, 32768, dcp_size=8)
+    assert 7.0 < wide / got < 8.01
