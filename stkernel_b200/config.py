@@ -234,7 +234,10 @@ class SchedulerConfig:
     max_num_batched_tokens: int = 4096
     graph_cap: int = 256             # largest decode batch captured as a CUDA graph
     decode_first: bool = True
-    async_scheduling: bool = True
+    # Schedule and launch step k+1 before the tokens of step k are read: a decode row's input token is copied on the
+    # device from the previous step's samples, the host reads them while the next step runs, and a request that turns
+    # out to have ended (EOS) has one surplus row computed and dropped.  Off by default; not with speculative decoding.
+    async_scheduling: bool = False
 
     def validate(self) -> None:
         if self.max_num_seqs < 1 or self.max_num_batched_tokens < 1:

@@ -117,6 +117,8 @@ class Scheduler:
         for r in self.running:
             if r.finished or r.in_prefill:
                 continue
+            if len(r.output) >= r.params.max_tokens or r.total_len >= sc.max_model_len:
+                continue             # its last token is still in flight (asynchronous scheduling); nothing more to run
             if budget <= 0:
                 break
             k = min(len(r.drafts), budget - 1)
@@ -309,6 +311,11 @@ class Engine:
             from ..parallel.eplb import LoadRecorder
             self.model.load_recorder = LoadRecorder(cfg.model.num_hidden_layers, cfg.model.n_routed_experts, self.device)
         self.metrics = Metrics()
+        self.async_scheduling = sc.async_scheduling and not spec_on and pipe is None
+        self._inflight = None                # asynchronous scheduling: the step that is launched and not read yet
+        self._async_parity = 0
+        self._h_async = ([torch.zeros(sc.max_num_seqs * (1 + n_spec), dtype=torch.int64, pin_memory=True) for _ in range(2)]
+                         if self.async_scheduling and self.device.type == "cuda" else [])
         self._next_id = 0
         self.requests: Dict[int, Request] = {}
         self._graphs: Dict[tuple, object] = {}
@@ -340,7 +347,7 @@ class Engine:
         return rid
 
     def has_work(self) -> bool:
-        return bool(self.sched.waiting or self.sched.running)
+        return bool(self.sched.waiting or self.sched.running) or self._inflight is not None
 
     def abort(self, req_id: int) -> bool:
         """Drop a request between steps (client went away, stop string hit); frees its pages."""
@@ -498,10 +505,107 @@ class Engine:
         device->host read, so consecutive steps queue on the device without a host round trip."""
         if self.drafter is not None:
             return self._step_spec()
+        if self.async_scheduling:
+            if forced is not None:
+                raise ValueError("forced tokens need a step whose tokens are read before the next one is scheduled")
+            return self._step_async()
         ticket = self.step_begin()
         return self.step_finish(ticket, forced) if ticket is not None else []
 
-    def step_begin(self):
+    # ---- asynchronous scheduling ---------------------------------------------------------------------------------
+    PENDING = -1                      # placeholder in Request.output for a token that is sampled but not read yet
+
+    def _step_async(self) -> List[Tuple[int, int]]:
+        """Begin step k+1, then read step k.  Returns the tokens of step k."""
+        prev, self._inflight = self._inflight, None
+        if prev is not None:
+            # prefill spans that ended on a block boundary: their state is kept before the next step changes it
+            self._offer_prefixes(prev[0])
+
+        def feed(seqs: List[ScheduledSeq]) -> None:
+            # decode rows whose input token is still on the device: copy it from the previous step's samples
+            if prev is None or prev[2] is None:
+                return
+            where = {id(s.req): k for k, s in enumerate(x for x in prev[0] if x.samples)}
+            src: List[int] = []           # sample index in the previous step ...
+            dst: List[int] = []           # ... -> token row of the step being begun
+            t = 0
+            for s in seqs:
+                r = s.req
+                if s.n == 1 and r.output and r.output[-1] == self.PENDING and s.start == r.total_len - 1:
+                    src.append(where[id(r)])
+                    dst.append(t)
+                t += s.n
+            if src:
+                dev = self.device
+                self.buf.d_tokens.index_copy_(0, torch.tensor(dst, dtype=torch.int64, device=dev),
+                                              prev[2].index_select(0, torch.tensor(src, dtype=torch.int64, device=dev)))
+
+        nxt = self.step_begin(after_upload=feed)
+        if nxt is not None:
+            seqs, ns, toks_dev = nxt
+            host, ready = None, None
+            if toks_dev is not None and self.device.type == "cuda":
+                # start this step's device->host copy now, ahead of the kernels of the step after it
+                host = self._h_async[self._async_parity]
+                self._async_parity ^= 1
+                host[:ns].copy_(toks_dev[:ns], non_blocking=True)
+                self._queue_status_read()
+                ready = torch.cuda.Event()
+                ready.record()
+            nxt = (seqs, ns, toks_dev, host, ready)
+            # provisional bookkeeping, so that the step after this one can be scheduled before this one is read
+            for s in seqs:
+                s.req.num_computed = s.start + s.n
+                if s.samples:
+                    s.req.output.append(self.PENDING)
+        out = self._finish_async(prev) if prev is not None else []
+        self._inflight = nxt
+        return out
+
+    def _finish_async(self, ticket) -> List[Tuple[int, int]]:
+        seqs, ns, toks_dev, host, ready = ticket
+        new_tokens: List[int] = []
+        if toks_dev is not None:
+            if ready is not None:
+                ready.synchronize()                                # this step's copy only, not the step begun since
+                new_tokens = host[:ns].tolist()
+            else:
+                new_tokens = toks_dev[:ns].tolist()
+            self.d2h_bytes_last = ns * 8 + 8
+            self._check_device_status()
+        out: List[Tuple[int, int]] = []
+        k = 0
+        now = time.time()
+        for s in seqs:
+            r = s.req
+            if s.start < len(r.prompt):
+                self.metrics.prompt_tokens_total += s.n
+            if not s.samples:
+                continue
+            tok = new_tokens[k]
+            k += 1
+            if r.finished:
+                continue                                           # ended one step earlier (EOS) or aborted: a surplus row
+            n_out = s.start + s.n - len(r.prompt) + 1
+            r.output[n_out - 1] = tok                              # the placeholder of this step
+            if r.first_token_time is None:
+                r.first_token_time = now
+            self.metrics.generation_tokens_total += 1
+            out.append((r.req_id, tok))
+            p = r.params
+            hit_eos = (p.eos_token_id is not None and tok == p.eos_token_id and not p.ignore_eos and n_out >= p.min_tokens)
+            if n_out >= p.max_tokens or hit_eos or len(r.prompt) + n_out >= self.cfg.sched.max_model_len:
+                del r.output[n_out:]                               # the placeholder of the step in flight, if any
+                r.finish_reason = "stop" if hit_eos else "length"
+                self.sched.retire(r)
+                self.metrics.requests_finished += 1
+        self.metrics.num_requests_running = self.sched.num_running
+        self.metrics.num_requests_waiting = self.sched.num_waiting
+        self.metrics.steps_total += 1
+        return out
+
+    def step_begin(self, after_upload=None):
         """First half of a step: schedule, stage, upload and queue the model.  Returns a ticket for `step_finish`, or
         None when nothing was scheduled.  A pipeline stage whose model defers the token exchange
         (`parallel.pipeline.MicroBatchPipeline`) can begin another engine's step before this one is finished."""
@@ -510,6 +614,8 @@ class Engine:
             return None
         t, n_req, ns = self._stage(seqs)
         self._upload(t, n_req, ns)
+        if after_upload is not None:
+            after_upload(seqs)
         max_end = max(s.start + s.n for s in seqs)
         max_comp_rows = max(1, max_end // 4)
         pure_decode = all(s.n == 1 and s.samples for s in seqs)

@@ -138,7 +138,8 @@ def build_engine(a, rank: int, world: int, device) -> Tuple[Engine, Any]:
                                                             dcp_size=getattr(a, "decode_context_parallel_size", 1),
                                                             fused_collectives=os.environ.get("STK_FUSED_COLLECTIVES", "1") == "1"),
                         sched=SchedulerConfig(max_model_len=a.max_model_len, max_num_seqs=a.max_num_seqs,
-                                              max_num_batched_tokens=a.max_num_batched_tokens, graph_cap=a.graph_cap),
+                                              max_num_batched_tokens=a.max_num_batched_tokens, graph_cap=a.graph_cap,
+                                              async_scheduling=getattr(a, "async_scheduling", False)),
                         cache=CacheConfig(gpu_memory_utilization=a.gpu_memory_utilization, size_by_memory=True),
                         spec=spec_cfg).validate()
     comm = None
@@ -181,6 +182,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--max-num-seqs", type=int, default=32)
     ap.add_argument("--max-num-batched-tokens", type=int, default=4096)
     ap.add_argument("--graph-cap", type=int, default=64)
+    ap.add_argument("--async-scheduling", action="store_true",
+                    help="launch step k+1 before the tokens of step k are read (not with speculative decoding)")
     ap.add_argument("--pipeline-parallel-size", type=int, default=1,
                     help="contiguous stages of layers; WORLD_SIZE = pipeline x tensor parallel size (stage-major ranks)")
     ap.add_argument("--decode-context-parallel-size", type=int, default=1,
