@@ -70,6 +70,7 @@ class Knobs:
     fused: int = 1
     multimem: int = 0
     pp_size: int = 1              # pipeline stages; ranks = TP_SIZE x PP_SIZE
+    async_sched: int = 0          # 1: schedule and launch the next step before this step's tokens are read
     dcp: int = 0                  # 1: ratio-4 KV pages dealt over the tensor-parallel ranks (decode context parallel)
     idx_freq: int = 4
     idx_sp: int = 1
@@ -147,6 +148,7 @@ def parse_knobs(env: Mapping[str, str]) -> Knobs:
     k.multimem = _flag(env, "MULTIMEM", "0")
     k.dcp = _flag(env, "DCP", "0")
     k.pp_size = _uint(env, "PP_SIZE", "1", 1, 8)
+    k.async_sched = _flag(env, "ASYNC_SCHED", "0")
     k.idx_freq = _uint(env, "IDXFREQ", "4", 1, 64)
     k.idx_sp = _flag(env, "IDXSP", "1")
     k.compressor_fp8 = _flag(env, "COMPRESSOR_FP8", "1")
@@ -170,6 +172,9 @@ def parse_knobs(env: Mapping[str, str]) -> Knobs:
         raise KnobError("ABORT: PP_SIZE > 1 is not available with speculative decoding (SPEC_TOKENS=0)")
     if k.pp_size > 1:
         k.warnings.append("PP_SIZE > 1: steps run without CUDA graphs and the stages' tensor-parallel groups use NCCL")
+    if k.async_sched == 1 and (k.spec_tokens or k.pp_size > 1):
+        raise KnobError("ABORT: ASYNC_SCHED=1 is not available with speculative decoding or pipeline stages "
+                        "(SPEC_TOKENS=0, PP_SIZE=1)")
     if k.dcp == 1 and k.tp_size == 1:
         raise KnobError("ABORT: DCP=1 deals the ratio-4 KV pages over the tensor-parallel ranks (TP_SIZE >= 2)")
     if k.dcp == 1:

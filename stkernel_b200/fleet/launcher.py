@@ -68,6 +68,8 @@ def serve_command(k: Knobs, python: str = sys.executable) -> List[str]:
            "--kv-cache-dtype", "fp8_ds_mla", "--temperature", str(k.temperature)]
     if k.pp_size > 1:
         cmd += ["--pipeline-parallel-size", str(k.pp_size)]
+    if k.async_sched:
+        cmd += ["--async-scheduling"]
     if k.dcp:
         cmd += ["--decode-context-parallel-size", str(k.tp_size)]
     if k.spec_tokens:

@@ -37,6 +37,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     ({"TEMP": "hot"}, "TEMP must be a number"),
     ({"DCP": "1", "TP_SIZE": "1", "SPEC_TOKENS": "0"}, "TP_SIZE >= 2"),
     ({"PP_SIZE": "2"}, "TP_SIZE x PP_SIZE must fit"),
+    ({"ASYNC_SCHED": "1"}, "ASYNC_SCHED=1 is not available with speculative decoding"),
     ({"PP_SIZE": "2", "TP_SIZE": "4"}, "not available with speculative decoding"),
 ])
 def test_launcher_fails_closed_with_exit_2(env, needle):
@@ -68,6 +69,8 @@ def test_good_knobs_dry_run_and_command():
     assert c3[c3.index("--decode-context-parallel-size") + 1] == "4" and "--speculative-config" in c3
     assert any("without CUDA graphs" in w for w in k3.warnings)
     assert "--decode-context-parallel-size" not in cmd and "--pipeline-parallel-size" not in cmd
+    assert "--async-scheduling" in launcher.serve_command(parse_knobs({"ASYNC_SCHED": "1", "SPEC_TOKENS": "0"}), python="python")
+    assert "--async-scheduling" not in cmd
     k4 = parse_knobs({"PP_SIZE": "2", "TP_SIZE": "4", "SPEC_TOKENS": "0"})
     c4 = launcher.serve_command(k4, python="python")
     assert "--nproc-per-node=8" in c4 and c4[c4.index("--pipeline-parallel-size") + 1] == "2"
