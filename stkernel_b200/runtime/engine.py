@@ -591,6 +591,8 @@ class Engine:
             r.output[n_out - 1] = tok                              # the placeholder of this step
             if r.first_token_time is None:
                 r.first_token_time = now
+                self.metrics.ttft_sum += now - r.arrival
+                self.metrics.ttft_count += 1
             self.metrics.generation_tokens_total += 1
             out.append((r.req_id, tok))
             p = r.params
@@ -600,8 +602,7 @@ class Engine:
                 r.finish_reason = "stop" if hit_eos else "length"
                 self.sched.retire(r)
                 self.metrics.requests_finished += 1
-        self.metrics.num_requests_running = self.sched.num_running
-        self.metrics.num_requests_waiting = self.sched.num_waiting
+        self._refresh_gauges()
         self.metrics.steps_total += 1
         return out
 
@@ -664,6 +665,8 @@ class Engine:
                 r.output.append(tok)
                 if r.first_token_time is None:
                     r.first_token_time = now
+                    self.metrics.ttft_sum += now - r.arrival
+                    self.metrics.ttft_count += 1
                 self.metrics.generation_tokens_total += 1
                 out.append((r.req_id, tok))
                 p = r.params
@@ -674,10 +677,18 @@ class Engine:
                     self.sched.retire(r)
                     self.metrics.requests_finished += 1
         self._offer_prefixes(seqs)
-        self.metrics.num_requests_running = self.sched.num_running
-        self.metrics.num_requests_waiting = self.sched.num_waiting
+        self._refresh_gauges()
         self.metrics.steps_total += 1
         return out
+
+    def _refresh_gauges(self) -> None:
+        m = self.metrics
+        m.num_requests_running = self.sched.num_running
+        m.num_requests_waiting = self.sched.num_waiting
+        m.kv_cache_usage = self.kv.c4.pages_in_use / max(1, self.kv.c4.num_pages)
+        pc = self.prefix_cache
+        if pc is not None:
+            m.prefix_cache_queries, m.prefix_cache_hits, m.prefix_cache_hit_tokens = pc.queries, pc.hits, pc.hit_tokens
 
     def _offer_prefixes(self, seqs: List[ScheduledSeq]) -> None:
         """After a step: a prefill span that ended on a block boundary leaves its state to the prefix cache."""
@@ -833,6 +844,8 @@ class Engine:
                 r.output.append(tok)
                 if r.first_token_time is None:
                     r.first_token_time = now
+                    self.metrics.ttft_sum += now - r.arrival
+                    self.metrics.ttft_count += 1
                 self.metrics.generation_tokens_total += 1
                 out.append((r.req_id, tok))
                 if self._finish_if_done(r, tok):
@@ -843,8 +856,7 @@ class Engine:
                 r.drafts = list(self.draft_override(r, r.drafts))[:n_spec]
             si += 1
         self._offer_prefixes(seqs)
-        self.metrics.num_requests_running = self.sched.num_running
-        self.metrics.num_requests_waiting = self.sched.num_waiting
+        self._refresh_gauges()
         self.metrics.steps_total += 1
         return out
 

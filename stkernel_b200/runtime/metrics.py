@@ -21,6 +21,12 @@ class Metrics:
     spec_accepted_per_pos: List[int] = field(default_factory=list)
     prefix_cache_resets: int = 0
     device_status_errors: int = 0
+    kv_cache_usage: float = 0.0          # compressed-KV pool pages in use / pool size (the pool that grows with context)
+    prefix_cache_queries: int = 0
+    prefix_cache_hits: int = 0
+    prefix_cache_hit_tokens: int = 0
+    ttft_sum: float = 0.0                # time to first token over finished first tokens
+    ttft_count: int = 0
 
     def record_spec(self, n_draft: int, n_accepted: int) -> None:
         """One verified draft of n_draft tokens of which the first n_accepted were accepted."""
@@ -43,6 +49,12 @@ class Metrics:
             ("vllm:spec_decode_num_drafts_total", "counter", self.spec_num_drafts),
             ("vllm:spec_decode_num_draft_tokens_total", "counter", self.spec_num_draft_tokens),
             ("vllm:spec_decode_num_accepted_tokens_total", "counter", self.spec_num_accepted_tokens),
+            ("vllm:gpu_cache_usage_perc", "gauge", round(self.kv_cache_usage, 6)),
+            ("vllm:prefix_cache_queries_total", "counter", self.prefix_cache_queries),
+            ("vllm:prefix_cache_hits_total", "counter", self.prefix_cache_hits),
+            ("stk:prefix_cache_hit_tokens_total", "counter", self.prefix_cache_hit_tokens),
+            ("vllm:time_to_first_token_seconds_sum", "counter", round(self.ttft_sum, 6)),
+            ("vllm:time_to_first_token_seconds_count", "counter", self.ttft_count),
             ("stk:engine_steps_total", "counter", self.steps_total),
             ("stk:prefix_cache_resets_total", "counter", self.prefix_cache_resets),
             ("stk:device_status_errors_total", "counter", self.device_status_errors),

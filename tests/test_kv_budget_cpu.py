@@ -43,10 +43,13 @@ def test_requests_wait_for_pages_and_finish_with_the_same_text():
     while tight.has_work():
         tight.step()
         most_running = max(most_running, tight.sched.num_running)
+        assert 0.0 <= tight.metrics.kv_cache_usage <= 1.0
         waited = waited or (tight.sched.num_waiting > 0 and tight.sched.num_running < 4)
         assert len(tight.kv.c4.free) - tight.kv.promised() >= 0          # never promised more than the pool has
     assert [tight.requests[i].output for i in ids] == want
     assert waited and most_running < 5
+    m = tight.metrics
+    assert m.kv_cache_usage == 0.0 and m.ttft_count == 5 and m.ttft_sum > 0
     assert tight.kv.c4.pages_in_use == 0 and tight.kv.promised() == 0 and not tight.kv.reserved
 
 

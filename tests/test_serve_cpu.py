@@ -229,6 +229,9 @@ def test_models_health_metrics(client):
     assert m["data"][0]["id"] == "tiny-dsv4"
     text = client.get("/metrics").text
     assert "vllm:generation_tokens_total" in text and "vllm:num_requests_running" in text
+    for name in ("vllm:gpu_cache_usage_perc", "vllm:prefix_cache_queries_total", "vllm:prefix_cache_hits_total",
+                 "vllm:time_to_first_token_seconds_sum", "vllm:time_to_first_token_seconds_count"):
+        assert name in text
 
 
 def test_chat_completion_and_usage(client):
