@@ -212,7 +212,9 @@ class OutputPipeline:
     """tokens -> text -> (reasoning | content | tool-call deltas), with stop strings."""
 
     def __init__(self, tok: ChatTokenizer, thinking: bool, tools: Optional[list], stop: Sequence[str] = (),
-                 parse_tools: bool = True):
+                 parse_tools: bool = True, primed: str = ""):
+        """primed: text that the prompt already ends with as the beginning of the answer (a demanded tool call's
+        opening); the parsers see it in front of what the model generates."""
         self.detok = IncrementalDetokenizer(tok)
         self.split = ReasoningSplitter(thinking)
         self.tools = ToolCallParser(tools) if (tools and parse_tools) else None
@@ -220,6 +222,7 @@ class OutputPipeline:
         self.text = ""
         self.stopped = False
         self._pending = ""
+        self._primed = primed
 
     def _route(self, text: str, final: bool) -> Piece:
         r, c = self.split.push(text) if text else ("", "")
@@ -239,8 +242,8 @@ class OutputPipeline:
 
     def push(self, token_ids: Sequence[int], final: bool, eos_id: Optional[int] = None) -> Piece:
         ids = [t for t in token_ids if t != eos_id]
-        text = self._pending + self.detok.push(ids)
-        self._pending = ""
+        text = self._primed + self._pending + self.detok.push(ids)
+        self._pending = self._primed = ""
         if self.stop and text:
             hit = min((text.find(s) for s in self.stop if s in text), default=-1)
             if hit >= 0:
@@ -278,6 +281,29 @@ def flatten_content_parts(messages: List[Dict[str, Any]]) -> List[Dict[str, Any]
             m = {**m, "content": "\n".join(texts)}
         out.append(m)
     return out
+
+
+def forced_tool_prefix(tool_choice: Any, tools: Optional[List[Dict[str, Any]]]) -> Optional[str]:
+    """OpenAI `tool_choice` -> the text a demanded call starts with, or None when the model is free to choose
+    ("auto", "none", absent).  "required" opens the tool-call block and the first invoke's name attribute; a named
+    function also fixes the name.  (The reference leaves both unenforced: SERVING_SURFACE_AUDIT.md:80-95.)"""
+    from .encoding import DSML, TOOL_CALLS_BLOCK
+    if tool_choice in (None, "auto", "none"):
+        return None
+    name = None
+    if isinstance(tool_choice, dict):
+        name = (tool_choice.get("function") or {}).get("name") or tool_choice.get("name")
+        if not name:
+            raise HTTPException(status_code=400, detail="tool_choice names no function")
+    elif tool_choice not in ("required", "any"):
+        raise HTTPException(status_code=400, detail=f"unsupported tool_choice {tool_choice!r}")
+    known = [t.get("function", {}).get("name") for t in (tools or [])]
+    if not known:
+        raise HTTPException(status_code=400, detail="tool_choice demands a call but the request has no tools")
+    if name is not None and name not in known:
+        raise HTTPException(status_code=400, detail=f"tool_choice names {name!r}, which is not among the tools")
+    head = f'\n\n<{DSML}{TOOL_CALLS_BLOCK}>\n<{DSML}invoke name="'
+    return head + (f'{name}">\n' if name is not None else "")
 
 
 def choice_count(body: Dict[str, Any], limit: int = 16) -> int:
@@ -437,14 +463,20 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
             kwargs.setdefault("thinking", True)
         tools = body.get("tools") if body.get("tool_choice") != "none" else None
         msgs = attach_response_format(flatten_content_parts(body["messages"]), body.get("response_format"))
-        ids = tokenizer.apply_chat_template(msgs, tools=tools, **kwargs)
-        return ids, thinking, tools
+        forced = forced_tool_prefix(body.get("tool_choice"), tools)
+        if forced is None:
+            return tokenizer.apply_chat_template(msgs, tools=tools, **kwargs), thinking, tools, ""
+        # a call is demanded ("required", or a named function): the answer starts inside the tool-call block (and inside
+        # the named invoke), without a thinking section, and the model continues from there
+        kwargs["thinking"] = False
+        prompt = tokenizer.apply_chat_template(msgs, tools=tools, tokenize=False, **kwargs)
+        return tokenizer.encode(prompt + forced), False, tools, forced
 
     @app.post("/v1/chat/completions")
     async def chat(request: Request):
         try:
             body = await request.json()
-            ids, thinking, tools = prepare_chat(body)
+            ids, thinking, tools, forced = prepare_chat(body)
             n_choices = choice_count(body)
         except HTTPException as e:
             return err(e.status_code, str(e.detail))
@@ -457,7 +489,7 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
         stop = [stop] if isinstance(stop, str) else list(stop)
         rid = f"chatcmpl-{uuid.uuid4().hex}"
         # one output pipeline (detokenizer, reasoning splitter, tool parser) and one seed per choice
-        pipes = [OutputPipeline(tokenizer, thinking, tools, stop) for _ in range(n_choices)]
+        pipes = [OutputPipeline(tokenizer, thinking, tools, stop, primed=forced) for _ in range(n_choices)]
         seeds = [dataclasses.replace(params, seed=(params.seed + i) & 0x7FFFFFFF) for i in range(n_choices)]
         base = {"id": rid, "object": "chat.completion.chunk", "created": int(time.time()), "model": model_name}
         include_usage = bool((body.get("stream_options") or {}).get("include_usage"))
@@ -603,7 +635,7 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
         try:
             body = await request.json()
             if "messages" in body:
-                ids, _, _ = prepare_chat(body)
+                ids, _, _, _ = prepare_chat(body)
             else:
                 ids = tokenizer.encode(body["prompt"])
         except HTTPException as e:
@@ -632,12 +664,22 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
         thinking = thinking_enabled(kwargs, default_thinking)
         if thinking:
             kwargs.setdefault("thinking", True)
-        return tokenizer.apply_chat_template(msgs, tools=tools, **kwargs), thinking, tools
+        # Anthropic tool_choice: {"type": "auto" | "none" | "any" | "tool", "name": ...}
+        tc = body.get("tool_choice") or {}
+        kind = tc.get("type") if isinstance(tc, dict) else tc
+        if kind == "none":
+            tools = None
+        forced = forced_tool_prefix({"name": tc.get("name")} if kind == "tool" else ("required" if kind == "any" else None), tools)
+        if forced is None:
+            return tokenizer.apply_chat_template(msgs, tools=tools, **kwargs), thinking, tools, ""
+        kwargs["thinking"] = False
+        prompt = tokenizer.apply_chat_template(msgs, tools=tools, tokenize=False, **kwargs)
+        return tokenizer.encode(prompt + forced), False, tools, forced
 
     @app.post("/v1/messages/count_tokens")
     async def count_tokens(request: Request):
         try:
-            ids, _, _ = prepare_messages(await request.json())
+            ids, _, _, _ = prepare_messages(await request.json())
         except Exception as e:
             return err(400, f"{type(e).__name__}: {e}")
         return {"input_tokens": len(ids)}
@@ -646,13 +688,13 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
     async def messages(request: Request):
         try:
             body = await request.json()
-            ids, thinking, tools = prepare_messages(body)
+            ids, thinking, tools, forced = prepare_messages(body)
         except Exception as e:
             return err(400, f"{type(e).__name__}: {e}")
         if len(ids) >= max_len:
             return err(400, f"prompt has {len(ids)} tokens; the model's context is {max_len}")
         params = sampling_from_request(body, eos_id, max_len, len(ids), default_temperature=default_temperature)
-        pipe = OutputPipeline(tokenizer, thinking, tools, body.get("stop_sequences") or [])
+        pipe = OutputPipeline(tokenizer, thinking, tools, body.get("stop_sequences") or [], primed=forced)
         mid = f"msg_{uuid.uuid4().hex[:24]}"
 
         def stop_reason(reason):

@@ -367,11 +367,13 @@ class ScriptedEngine:
         import torch
         self.device = torch.device("cpu")
         self.requests, self._next, self._live = {}, 0, []
+        self.prompts = []
 
     def add_request(self, prompt, params):
         import types
         rid = self._next
         self._next += 1
+        self.prompts.append(list(prompt))
         self.requests[rid] = types.SimpleNamespace(req_id=rid, prompt=prompt, params=params, output=[], finished=False, finish_reason=None)
         self._live.append(rid)
         return rid
@@ -472,6 +474,49 @@ def test_anthropic_tool_use_blocks(tool_client):
     partial = "".join(e["delta"]["partial_json"] for e in events if e["type"] == "content_block_delta" and e["delta"]["type"] == "input_json_delta")
     assert json.loads(partial) == {"city": "서울", "days": 2}
     assert [e["delta"]["stop_reason"] for e in events if e["type"] == "message_delta"] == ["tool_use"]
+
+
+def test_demanded_tool_call_starts_inside_the_call():
+    """tool_choice "required" / a named function: the prompt ends with the opening of the call, the model continues it,
+    and the parsers see the opening in front of what was generated."""
+    from fastapi.testclient import TestClient
+    from stkernel_b200.serve.api_server import create_app, forced_tool_prefix
+    tok = ChatTokenizer(ByteTokenizer(1024))
+    whole = E.dsml_tool_calls([{"function": {"name": "get_weather", "arguments": json.dumps({"city": "Busan", "days": 1})}}])
+    named = forced_tool_prefix({"type": "function", "function": {"name": "get_weather"}}, TOOLS)
+    anyone = forced_tool_prefix("required", TOOLS)
+    assert whole.startswith(named) and named.startswith(anyone) and anyone.endswith('invoke name="')
+    assert forced_tool_prefix("auto", TOOLS) is None and forced_tool_prefix(None, TOOLS) is None
+    for choice, prefix in (({"type": "function", "function": {"name": "get_weather"}}, named), ("required", anyone)):
+        eng = ScriptedEngine(tok, whole[len(prefix):])            # the model writes the rest of the call
+        with TestClient(create_app(eng, tok, "scripted")) as c:
+            body = {"messages": [{"role": "user", "content": "2+2? no tools please"}], "tools": TOOLS, "max_tokens": 500,
+                    "tool_choice": choice, "chat_template_kwargs": {"thinking": True}}
+            r = c.post("/v1/chat/completions", json=body).json()
+            ch = r["choices"][0]
+            assert ch["finish_reason"] == "tool_calls" and not ch["message"].get("reasoning_content")
+            call = ch["message"]["tool_calls"][0]["function"]
+            assert call["name"] == "get_weather" and json.loads(call["arguments"]) == {"city": "Busan", "days": 1}
+            prompt = tok.decode(eng.prompts[0])
+            assert prompt.endswith(prefix) and E.THINK_OPEN not in prompt.split(prefix)[0][-20:]
+            with c.stream("POST", "/v1/chat/completions", json={**body, "stream": True}) as resp:
+                chunks = [json.loads(x) for x in _sse(resp)[:-1]]
+            names = [t["function"].get("name") for ck in chunks for ch2 in ck["choices"] for t in ch2["delta"].get("tool_calls", [])]
+            args = "".join(t["function"].get("arguments", "") for ck in chunks for ch2 in ck["choices"]
+                           for t in ch2["delta"].get("tool_calls", []))
+            assert "get_weather" in names and json.loads(args) == {"city": "Busan", "days": 1}
+            # Anthropic wire: {"type": "tool", "name": ...} / {"type": "any"}
+            a_choice = {"type": "tool", "name": "get_weather"} if isinstance(choice, dict) else {"type": "any"}
+            a_tools = [{"name": "get_weather", "description": "w", "input_schema": TOOLS[0]["function"]["parameters"]}]
+            m = c.post("/v1/messages", json={"messages": [{"role": "user", "content": "hi"}], "tools": a_tools, "max_tokens": 500,
+                                             "tool_choice": a_choice}).json()
+            use = [b for b in m["content"] if b["type"] == "tool_use"]
+            assert m["stop_reason"] == "tool_use" and use[0]["name"] == "get_weather" and use[0]["input"] == {"city": "Busan", "days": 1}
+    with TestClient(create_app(ScriptedEngine(tok, "x"), tok, "scripted")) as c:
+        base = {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 5}
+        assert c.post("/v1/chat/completions", json={**base, "tool_choice": "required"}).status_code == 400          # no tools
+        bad = {"type": "function", "function": {"name": "nope"}}
+        assert c.post("/v1/chat/completions", json={**base, "tools": TOOLS, "tool_choice": bad}).status_code == 400
 
 
 def test_stop_string_ends_stream_early(tool_client):
