@@ -80,6 +80,30 @@ def test_cached_prefix_state_is_taken_before_the_next_step_changes_it(model):
     assert outs[True][1] == cold
 
 
+def test_with_a_capped_pool_requests_wait_and_texts_match(model):
+    """Asynchronous scheduling over a compressed-KV pool that cannot hold every request at once."""
+    from stkernel_b200.config import CacheConfig
+    cfg, tw = model
+    torch.manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,)).tolist() for n in (300, 280, 270, 20, 290, 33)]
+    params = [SamplingParams(temperature=0.5, seed=i, max_tokens=4 + i) for i in range(6)]
+    outs = {}
+    for mode in (False, True):
+        ec = EngineConfig(model=cfg, cache=CacheConfig(kv_pool_tokens=700),
+                          sched=SchedulerConfig(max_model_len=1024, max_num_seqs=4, max_num_batched_tokens=96,
+                                                graph_cap=0, async_scheduling=mode)).validate()
+        eng = Engine(ec, tw, "cpu", max_context=1024)
+        ids = [eng.add_request(p, sp) for p, sp in zip(prompts, params)]
+        waited = False
+        while eng.has_work():
+            eng.step()
+            waited = waited or eng.sched.num_waiting > 0
+            assert len(eng.kv.c4.free) - eng.kv.promised() >= 0
+        assert waited and not eng.kv.reserved
+        outs[mode] = [eng.requests[i].output for i in ids]
+    assert outs[True] == outs[False]
+
+
 def test_abort_while_a_step_is_in_flight(model):
     cfg, _ = model
     torch.manual_seed(2)
