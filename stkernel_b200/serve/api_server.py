@@ -587,12 +587,54 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
                 "choices": [r[0] for r in results], "usage": _usage(len(ids), sum(r[1] for r in results))}
 
     # ---- raw completions ------------------------------------------------------------------
+    async def completions_batch(body: Dict[str, Any], prompts: List[Any], n_choices: int):
+        """Every prompt x n samples as one response: choice index = prompt index * n + sample index."""
+        all_ids = [list(p) if isinstance(p, list) else tokenizer.encode(p) for p in prompts]
+        for ids in all_ids:
+            if len(ids) >= max_len:
+                return err(400, f"prompt has {len(ids)} tokens; the model's context is {max_len}")
+        stop = [body["stop"]] if isinstance(body.get("stop"), str) else (body.get("stop") or [])
+
+        async def one(k: int):
+            ids = all_ids[k // n_choices]
+            params = sampling_from_request(body, eos_id, max_len, len(ids), default_temperature=default_temperature)
+            if body.get("seed") is not None:
+                params = dataclasses.replace(params, seed=(params.seed + k % n_choices) & 0x7FFFFFFF)
+            pipe = OutputPipeline(tokenizer, False, None, stop)
+            n_out, reason = 0, None
+            async for ev in aeng.generate(ids, params):
+                if ev.error:
+                    return ev.error
+                n_out += len(ev.tokens)
+                pipe.push(ev.tokens, ev.finished, eos_id)
+                reason = ev.finish_reason
+                if pipe.stopped or ev.finished:
+                    break
+            return {"index": k, "text": pipe.text, "finish_reason": "stop" if pipe.stopped else reason}, n_out
+
+        results = await asyncio.gather(*(one(k) for k in range(len(all_ids) * n_choices)))
+        for r in results:
+            if isinstance(r, str):
+                return err(500, r, "internal_error")
+        return {"id": f"cmpl-{uuid.uuid4().hex}", "object": "text_completion", "created": int(time.time()), "model": model_name,
+                "choices": [r[0] for r in results],
+                "usage": _usage(sum(len(i) for i in all_ids), sum(r[1] for r in results))}
+
     @app.post("/v1/completions")
     async def completions(request: Request):
         try:
             body = await request.json()
             prompt = body["prompt"]
+            n_choices = choice_count(body)
+            # a batch of prompts (strings or token lists) and / or several samples per prompt: answered whole
+            batch = isinstance(prompt, list) and bool(prompt) and not isinstance(prompt[0], int)
+            if batch or n_choices > 1:
+                if body.get("stream"):
+                    raise HTTPException(status_code=400, detail="streaming takes one prompt and n = 1")
+                return await completions_batch(body, list(prompt) if batch else [prompt], n_choices)
             ids = list(prompt) if isinstance(prompt, list) and prompt and isinstance(prompt[0], int) else tokenizer.encode(prompt)
+        except HTTPException as e:
+            return err(e.status_code, str(e.detail))
         except Exception as e:
             return err(400, f"{type(e).__name__}: {e}")
         if len(ids) >= max_len:

@@ -301,6 +301,19 @@ def test_several_choices_and_content_parts(client):
     assert r.status_code == 400 and "image_url" in r.json()["error"]["message"]
 
 
+def test_completions_batch_of_prompts_and_samples(client):
+    one = lambda p, seed: client.post("/v1/completions", json={"prompt": p, "max_tokens": 5, "temperature": 0.8, "seed": seed,
+                                                                "ignore_eos": True}).json()["choices"][0]["text"]
+    r = client.post("/v1/completions", json={"prompt": ["first prompt", "second"], "n": 2, "max_tokens": 5, "temperature": 0.8,
+                                             "seed": 3, "ignore_eos": True}).json()
+    assert [c["index"] for c in r["choices"]] == [0, 1, 2, 3] and r["usage"]["completion_tokens"] == 20
+    assert [c["text"] for c in r["choices"]] == [one("first prompt", 3), one("first prompt", 4), one("second", 3), one("second", 4)]
+    ids = client.post("/tokenize", json={"prompt": "second"}).json()["tokens"]
+    r2 = client.post("/v1/completions", json={"prompt": [ids], "max_tokens": 5, "temperature": 0.8, "seed": 3, "ignore_eos": True}).json()
+    assert r2["choices"][0]["text"] == r["choices"][2]["text"]
+    assert client.post("/v1/completions", json={"prompt": ["a", "b"], "stream": True}).status_code == 400
+
+
 def test_tokenizer_routes(client):
     t = client.post("/tokenize", json={"prompt": "abc def"}).json()
     assert t["count"] == len(t["tokens"]) > 0 and t["max_model_len"] == 512
