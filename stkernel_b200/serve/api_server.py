@@ -98,6 +98,21 @@ class AsyncEngine:
                 except Exception as e:
                     loop.call_soon_threadsafe(fut.set_exception, e)
 
+    def _publish(self, produced: Sequence[Tuple[int, int]]) -> None:
+        """One event per request and step: a speculative step yields several tokens for a request, and the finished flag
+        must arrive with the last of them, not the first."""
+        eng = self.engine
+        by_req: Dict[int, List[int]] = {}
+        for rid, tok in produced:
+            by_req.setdefault(rid, []).append(tok)
+        for rid, toks in by_req.items():
+            r = eng.requests.get(rid)
+            done = r is not None and r.finished
+            self._post(rid, TokenEvent(toks, done, r.finish_reason if done else None))
+            if done:
+                self._streams.pop(rid, None)
+                eng.release(rid)
+
     def _on_add(self, rid: int, prompt: List[int], params: SamplingParams) -> None:
         """Hook: a request entered the engine (multi-rank leaders mirror it to the followers)."""
 
@@ -120,13 +135,7 @@ class AsyncEngine:
                     eng.abort(rid)
                 self._streams.clear()
                 continue
-            for rid, tok in produced:
-                r = eng.requests.get(rid)
-                done = r is not None and r.finished
-                self._post(rid, TokenEvent([tok], done, r.finish_reason if done else None))
-                if done:
-                    self._streams.pop(rid, None)
-                    eng.release(rid)
+            self._publish(produced)
 
     # -- asyncio side ------------------------------------------------------------------------
     async def generate(self, prompt: Sequence[int], params: SamplingParams) -> AsyncIterator[TokenEvent]:

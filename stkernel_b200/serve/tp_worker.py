@@ -76,14 +76,7 @@ class LockstepLeader(AsyncEngine):
                 self.failed = f"{type(e).__name__}: {e}"
                 print(f"leader: step failed ({self.failed}); stopping", file=sys.stderr)
                 os._exit(4)
-            for rid, tok in produced:
-                r = eng.requests.get(rid)
-                done = r is not None and r.finished
-                from .api_server import TokenEvent
-                self._post(rid, TokenEvent([tok], done, r.finish_reason if done else None))
-                if done:
-                    self._streams.pop(rid, None)
-                    eng.release(rid)
+            self._publish(produced)
         self._broadcast([(EV_STOP, None)])
 
 

@@ -182,3 +182,33 @@ def test_rowwise_fp8_draft_head():
     assert F8.pick_head_impl(False, False) == "bf16"
     with pytest.raises(ValueError):
         F8.pick_head_impl(True, True)
+
+
+def test_http_server_delivers_every_token_of_a_request_that_ends_inside_a_speculative_step():
+    """A step that accepts several drafts yields several tokens for one request; the one that ends the request must not
+    cut the others off (the finished flag travels with the last token of the step)."""
+    from fastapi.testclient import TestClient
+    from stkernel_b200.serve.api_server import create_app
+    from stkernel_b200.serve.tokenizer import ByteTokenizer, ChatTokenizer
+    cfg, plain, spec = _engines()
+    tok = ChatTokenizer(ByteTokenizer(cfg.vocab_size))
+    prompt = tok.encode("hello there")
+    want = plain.generate([prompt], SamplingParams(temperature=0.0, max_tokens=14, ignore_eos=True))[0]
+
+    def oracle(req, drafted):                                   # a drafter that is always right: every draft is accepted
+        k = len(req.output)
+        return want[k:k + len(drafted)] if k + len(drafted) <= len(want) else drafted
+    spec.draft_override = oracle
+    import json
+    with TestClient(create_app(spec, tok, "tiny")) as c, TestClient(create_app(plain, tok, "tiny")) as ref:
+        for limit in range(9, 15):
+            body = {"prompt": prompt, "max_tokens": limit, "temperature": 0.0, "ignore_eos": True}
+            r, rr = c.post("/v1/completions", json=body).json(), ref.post("/v1/completions", json=body).json()
+            assert r["usage"]["completion_tokens"] == limit and r["choices"][0]["finish_reason"] == "length"
+            assert r["choices"][0]["text"] == rr["choices"][0]["text"]          # one token per step on the reference server
+            with c.stream("POST", "/v1/completions", json={**body, "stream": True}) as resp:
+                lines = [x[6:] for x in resp.iter_lines() if x.startswith("data: ")]
+            chunks = [json.loads(x) for x in lines[:-1]]
+            assert "".join(ch["choices"][0]["text"] for ch in chunks) == rr["choices"][0]["text"]
+            assert chunks[-1]["usage"]["completion_tokens"] == limit
+    assert spec.metrics.spec_num_accepted_tokens > 20           # steps did carry several tokens
