@@ -101,7 +101,8 @@ def follower_loop(engine: Engine, cpu_group, heartbeat_timeout: float = 120.0) -
         # The leader sends one message per step while it has work and empty heartbeats only while idle;
         # lockstep engines agree on `has_work`, so a message that finds work pending is a step.
         if engine.has_work():
-            engine.step()
+            for rid in {rid for rid, _ in engine.step()}:
+                engine.release(rid)                      # forgets the request once it has finished (a no-op before)
 
 
 def build_engine(a, rank: int, world: int, device) -> Tuple[Engine, Any]:
