@@ -132,6 +132,60 @@ class MicroBatchPipeline:
         ei, rid = self._where[gid]
         return self.engines[ei].requests[rid].output
 
+    # ---- the rest of the engine surface that the serving layer uses --------------------------------------------------
+    @property
+    def cfg(self):
+        return self.engines[0].cfg
+
+    @property
+    def device(self):
+        return self.engines[0].device
+
+    @property
+    def metrics(self):
+        """Counters summed over the engines (a fresh object: read it, do not write to it)."""
+        import dataclasses
+        from ..runtime.metrics import Metrics
+        total = Metrics()
+        for e in self.engines:
+            for f in dataclasses.fields(Metrics):
+                a, b = getattr(total, f.name), getattr(e.metrics, f.name)
+                if isinstance(b, list):
+                    setattr(total, f.name, [x + y for x, y in zip(a + [0] * (len(b) - len(a)), b + [0] * (len(a) - len(b)))])
+                elif f.name == "kv_cache_usage":
+                    setattr(total, f.name, max(a, b))
+                else:
+                    setattr(total, f.name, a + b)
+        return total
+
+    @property
+    def requests(self):
+        """global request id -> Request, for the requests that have not been released."""
+        out = {}
+        for gid, (ei, rid) in self._where.items():
+            r = self.engines[ei].requests.get(rid)
+            if r is not None:
+                out[gid] = r
+        return out
+
+    def abort(self, gid: int) -> bool:
+        if gid not in self._where:
+            return False
+        ei, rid = self._where[gid]
+        return self.engines[ei].abort(rid)
+
+    def release(self, gid: int) -> None:
+        if gid in self._where:
+            ei, rid = self._where[gid]
+            r = self.engines[ei].requests.get(rid)
+            if r is not None and r.finished:
+                self.engines[ei].release(rid)
+                del self._where[gid]
+
+    def reset_prefix_cache(self) -> int:
+        self.engines[0].metrics.prefix_cache_resets += 1
+        return sum(e.reset_prefix_cache() for e in self.engines)
+
     def generate(self, prompts, params=None):
         ids = [self.add_request(p, params) for p in prompts]
         while self.has_work():

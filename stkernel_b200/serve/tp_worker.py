@@ -15,6 +15,7 @@ Flag names follow the reference's serve script (launchers/start-hy4-tp4.sh:354-3
 from __future__ import annotations
 
 import argparse
+import dataclasses
 import json
 import os
 import sys
@@ -159,6 +160,13 @@ def build_engine(a, rank: int, world: int, device) -> Tuple[Engine, Any]:
     if spec_cfg.method == "dspark":
         from ..spec.dspark import build_draft_weights
         draft = build_draft_weights(mcfg, src, weights, device, tp_rank, tp)
+    micro = getattr(a, "pipeline_micro_batches", False)
+    if pipe is not None and micro:
+        # as many engines per stage as there are stages, taking turns: every stage has work while another micro-batch is
+        # in flight.  They share the weights; each gets its share of the sequence slots and of the KV pools.
+        from ..parallel.pipeline import MicroBatchPipeline
+        share = dataclasses.replace(ecfg, sched=dataclasses.replace(ecfg.sched, max_num_seqs=max(1, ecfg.sched.max_num_seqs // pp)))
+        return MicroBatchPipeline([Engine(share, weights, device, comm, tp_rank, pipe=pipe) for _ in range(pp)]), mcfg
     eng = Engine(ecfg, weights, device, comm, tp_rank, draft_weights=draft, pipe=pipe)
     return eng, mcfg
 
@@ -180,6 +188,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
                     help="launch step k+1 before the tokens of step k are read (not with speculative decoding)")
     ap.add_argument("--pipeline-parallel-size", type=int, default=1,
                     help="contiguous stages of layers; WORLD_SIZE = pipeline x tensor parallel size (stage-major ranks)")
+    ap.add_argument("--pipeline-micro-batches", action="store_true",
+                    help="with pipeline stages: one engine per stage and micro-batch, their steps interleaved")
     ap.add_argument("--decode-context-parallel-size", type=int, default=1,
                     help="1, or the tensor-parallel size: the ratio-4 KV caches are dealt page by page over the ranks")
     ap.add_argument("--kv-cache-dtype", default="fp8_ds_mla")

@@ -113,7 +113,15 @@ def _run_micro(rank, world, port, path):
     ids = [mb.add_request(p, SamplingParams(temperature=0.0, max_tokens=3 + 2 * i)) for i, p in enumerate(prompts)]
     while mb.has_work():
         mb.step()
-    json.dump({"out": [mb.output(i) for i in ids], "ticks": mb.tick, "overlapped": mb.overlapped_ticks},
+    outs = [list(mb.output(i)) for i in ids]
+    # the engine surface the serving layer uses: summed counters, request lookup, release
+    assert mb.metrics.generation_tokens_total == sum(len(o) for o in outs) and mb.metrics.requests_finished == len(ids)
+    assert sorted(mb.requests) == ids and all(mb.requests[i].finished for i in ids)
+    assert mb.abort(ids[0]) is False                    # finished already
+    for i in ids:
+        mb.release(i)
+    assert mb.requests == {} and not mb.has_work()
+    json.dump({"out": outs, "ticks": mb.tick, "overlapped": mb.overlapped_ticks},
               open(f"{path}.{rank}", "w"))
     dist.barrier()
     dist.destroy_process_group()

@@ -72,9 +72,11 @@ def test_tp2_lockstep_serving_matches_tp1():
     outs = {}
     # the third server also deals the ratio-4 KV pages over its two ranks (decode context parallelism); the fourth
     # runs its two ranks as two pipeline stages of one layer each; the fifth launches every step before the previous
-    # one's tokens are read (leader and follower must still take the same steps)
+    # one's tokens are read (leader and follower must still take the same steps); the sixth runs two engines per stage
+    # with their steps interleaved (micro-batches in flight)
     for key, world, extra, tp in ((1, 1, (), None), (2, 2, (), None), ("dcp", 2, ("--decode-context-parallel-size", "2"), None),
-                                  ("pp", 2, ("--pipeline-parallel-size", "2"), 1), ("async", 2, ("--async-scheduling",), None)):
+                                  ("pp", 2, ("--pipeline-parallel-size", "2"), 1), ("async", 2, ("--async-scheduling",), None),
+                                  ("ppmb", 2, ("--pipeline-parallel-size", "2", "--pipeline-micro-batches"), 1)):
         port = _free_port()
         proc = _launch(world, port, extra, tp)
         try:
@@ -92,7 +94,7 @@ def test_tp2_lockstep_serving_matches_tp1():
         finally:
             _stop(proc)
     # the same weights split over two ranks give the same greedy text (fp32 activations on CPU)
-    assert outs[1] == outs[2] == outs["dcp"] == outs["pp"] == outs["async"]
+    assert outs[1] == outs[2] == outs["dcp"] == outs["pp"] == outs["async"] == outs["ppmb"]
 
 
 def _follower_main(rank, port, result_path):
