@@ -67,7 +67,7 @@ def serve_command(k: Knobs, python: str = sys.executable) -> List[str]:
            "--max-num-batched-tokens", str(k.max_num_batched), "--graph-cap", str(k.graph_cap),
            "--kv-cache-dtype", "fp8_ds_mla", "--temperature", str(k.temperature)]
     if k.pp_size > 1:
-        cmd += ["--pipeline-parallel-size", str(k.pp_size)]
+        cmd += ["--pipeline-parallel-size", str(k.pp_size), "--pipeline-micro-batches"]
     if k.async_sched:
         cmd += ["--async-scheduling"]
     if k.dcp:

@@ -73,7 +73,7 @@ def test_good_knobs_dry_run_and_command():
     assert "--async-scheduling" not in cmd
     k4 = parse_knobs({"PP_SIZE": "2", "TP_SIZE": "4", "SPEC_TOKENS": "0"})
     c4 = launcher.serve_command(k4, python="python")
-    assert "--nproc-per-node=8" in c4 and c4[c4.index("--pipeline-parallel-size") + 1] == "2"
+    assert "--nproc-per-node=8" in c4 and c4[c4.index("--pipeline-parallel-size") + 1] == "2" and "--pipeline-micro-batches" in c4
     assert c4[c4.index("--tensor-parallel-size") + 1] == "4"
     assert any("only 4 GPU" in p for p in launcher.preflight(parse_knobs({"MODEL_PATH": "/models/x", "PP_SIZE": "2", "TP_SIZE": "4",
                                                                           "SPEC_TOKENS": "0"}), gpu_count=4))
