@@ -536,6 +536,19 @@ def test_stop_string_ends_stream_early(tool_client):
     body = {"messages": [{"role": "user", "content": "x"}], "max_tokens": 2000, "stop": ["check"], "chat_template_kwargs": {"thinking": True}}
     r = tool_client.post("/v1/chat/completions", json=body).json()
     assert r["choices"][0]["message"]["content"] == "Let me " and r["choices"][0]["finish_reason"] == "stop"
+    # streamed, two choices: each ends at its own stop string and the stream still closes with [DONE]
+    with tool_client.stream("POST", "/v1/chat/completions", json={**body, "n": 2, "stream": True,
+                                                                   "stream_options": {"include_usage": True}}) as resp:
+        lines = _sse(resp)
+    assert lines[-1] == "[DONE]"
+    chunks = [json.loads(x) for x in lines[:-1]]
+    text, fin = ["", ""], {}
+    for c in chunks:
+        for ch in c["choices"]:
+            text[ch["index"]] += ch["delta"].get("content", "")
+            if ch["finish_reason"]:
+                fin[ch["index"]] = ch["finish_reason"]
+    assert text == ["Let me ", "Let me "] and fin == {0: "stop", 1: "stop"}
 
 
 def test_top_p_top_k_and_response_format_reach_the_engine_and_the_prompt():
