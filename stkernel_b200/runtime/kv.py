@@ -205,6 +205,8 @@ class KVManager:
         self.c128 = GroupTable("c128", max(c128_pages, 1), max_requests, (max_model_len // 128) // PAGE + 2,
                                self.device, 1 / 128)
         self.layers = layers if layers is not None else list(range(cfg.num_hidden_layers))
+        self.model_has_c4 = any(cfg.layer_kind(l) == "c4a" for l in range(cfg.num_hidden_layers))
+        self.model_has_c128 = any(cfg.layer_kind(l) == "c128a" for l in range(cfg.num_hidden_layers))
         self.swa_cache: Dict[int, PagedCache] = {}
         self.comp_cache: Dict[int, PagedCache] = {}
         self.idx_cache: Dict[int, PagedCache] = {}
@@ -267,11 +269,13 @@ class KVManager:
         lo = max(0, start_pos - W + 1)
         self.swa.release_before(row, lo // PAGE)
         self.swa.ensure(row, lo // PAGE, (end - 1) // PAGE)
-        if any(cfg.layer_kind(l) == "c4a" for l in self.layers):
+        # by the kinds of the whole model, not of this pipeline stage's layers: every stage keeps the same tables, so
+        # their schedulers and prefix caches decide alike
+        if self.model_has_c4:
             n_rows = end // 4
             if n_rows > 0:
                 self.c4.ensure(row, 0, (n_rows - 1) // PAGE)
-        if any(cfg.layer_kind(l) == "c128a" for l in self.layers):
+        if self.model_has_c128:
             n_rows = end // 128
             if n_rows > 0:
                 self.c128.ensure(row, 0, (n_rows - 1) // PAGE)

@@ -43,6 +43,7 @@ class Entry:
     idx_state: Dict[int, torch.Tensor] = field(default_factory=dict)
     c128_pages: List[int] = field(default_factory=list)                   # full ratio-128 pages (shared)
     c128_tail: Dict[int, torch.Tensor] = field(default_factory=dict)      # layer -> bytes of the partial page
+    c128_part: bool = False                                               # rows past the shared pages exist
 
 
 def chain_hashes(tokens: Sequence[int], block: int = BLOCK, limit: Optional[int] = None) -> List[bytes]:
@@ -65,7 +66,9 @@ class PrefixCache:
         self.max_entries = max_entries
         self.entries: "OrderedDict[bytes, Entry]" = OrderedDict()
         cfg = kv.cfg
-        self.c128_layers = [l for l in kv.layers if cfg.layer_kind(l) == "c128a"]
+        self.c128_layers = [l for l in kv.layers if cfg.layer_kind(l) == "c128a"]     # this stage's: their bytes are copied
+        # decisions follow the whole model, so that every pipeline stage keeps and finds the same entries
+        self.has_c128 = kv.model_has_c128
         self.enabled = block % (4 * PAGE) == 0 and block % 128 == 0
         self.window_pages = (cfg.sliding_window + PAGE - 1) // PAGE
         self.hits = 0
@@ -105,10 +108,10 @@ class PrefixCache:
             kv.comp_state[li][row].copy_(st)
         for li, st in e.idx_state.items():
             kv.idx_state[li][row].copy_(st)
-        if self.c128_layers:
+        if self.has_c128:
             if e.c128_pages:
                 kv.c128.adopt(row, 0, e.c128_pages)
-            if e.c128_tail:
+            if e.c128_part:
                 lp = len(e.c128_pages)
                 kv.c128.ensure(row, lp, lp)                        # a page of its own for the rows past the shared ones
                 pg = int(kv.c128.table_np[row][lp])
@@ -142,13 +145,14 @@ class PrefixCache:
             e.comp_state[li] = st[row].clone()
         for li, st in kv.idx_state.items():
             e.idx_state[li] = st[row].clone()
-        if self.c128_layers:
+        if self.has_c128:
             rows = pos // 128
             full, part = rows // PAGE, rows % PAGE
             if full > kv.c128.hi[row] or (part and full >= kv.c128.hi[row]):
                 self._drop(e)
                 return False
             e.c128_pages = kv.c128.share(row, 0, full - 1) if full else []
+            e.c128_part = bool(part)
             if part:
                 pg = int(kv.c128.table_np[row][full])
                 for li in self.c128_layers:

@@ -127,6 +127,40 @@ def _run_micro(rank, world, port, path):
     dist.destroy_process_group()
 
 
+def _run_prefix(rank, world, port, path):
+    """Stages with different layer kinds (stage 0: ratio-4 + ratio-128 layers, stage 1: a sliding-window layer only) and
+    a request that starts from a cached prefix: every stage must keep and find the same entry."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      STK_CPU_ACT_FP32="1", CUDA_VISIBLE_DEVICES="")
+    import torch.distributed as dist
+    from stkernel_b200.config import EngineConfig, ParallelConfig, SchedulerConfig, tiny_config
+    from stkernel_b200.models.dsv4 import DictSource, build_model_weights
+    from stkernel_b200.models.weights import init_random_weights
+    from stkernel_b200.parallel.pipeline import PipeStage
+    from stkernel_b200.runtime.engine import Engine, SamplingParams
+    cfg = tiny_config(dense_dtype="bf16", kv_cache_dtype="bf16", expert_dtype="bf16", num_hidden_layers=3,
+                      compress_ratios=(4, 128, 0))
+    w = init_random_weights(cfg, seed=2)
+    pipe = rng = None
+    if world > 1:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        pipe = PipeStage(pp_rank=rank, pp_size=world)
+        rng = pipe.layer_range(cfg.num_hidden_layers)
+    ec = EngineConfig(model=cfg, parallel=ParallelConfig(pp_size=world),
+                      sched=SchedulerConfig(max_model_len=1024, max_num_seqs=2, max_num_batched_tokens=128,
+                                            graph_cap=0)).validate()
+    eng = Engine(ec, build_model_weights(cfg, DictSource(w), "cpu", layer_range=rng), "cpu", max_context=1024, pipe=pipe)
+    g = torch.Generator().manual_seed(0)
+    base = torch.randint(0, cfg.vocab_size, (600,), generator=g).tolist()
+    tail = torch.randint(0, cfg.vocab_size, (40,), generator=g).tolist()
+    sp = SamplingParams(temperature=0.0, max_tokens=4)
+    out = [eng.generate([base], sp), eng.generate([base[:520] + tail], sp)]
+    json.dump({"out": out, "hits": eng.prefix_cache.hit_tokens, "c4_pages": eng.kv.c4.pages_in_use}, open(f"{path}.{rank}", "w"))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def _spawn(world, path):
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
@@ -235,3 +269,22 @@ def test_micro_batches_in_flight_match_single_process(tmp_path):
         Fn.set_cpu_act_dtype(torch.bfloat16)
     assert a["out"] == want
     assert a["overlapped"] >= a["ticks"] // 2
+
+
+@pytest.mark.timeout(600)
+def test_cached_prefix_across_stages_with_different_layer_kinds(tmp_path):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    res = {}
+    for world in (1, 2):
+        port = _free_port()
+        path = str(tmp_path / f"pfx{world}")
+        ps = [ctx.Process(target=_run_prefix, args=(r, world, port, path)) for r in range(world)]
+        for q in ps:
+            q.start()
+        for q in ps:
+            q.join(300)
+            assert q.exitcode == 0
+        res[world] = [json.load(open(f"{path}.{r}")) for r in range(world)]
+    assert res[1][0]["hits"] == 512
+    assert res[2][0] == res[2][1] == res[1][0]          # texts, hit tokens and page accounting alike on every stage
