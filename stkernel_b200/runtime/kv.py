@@ -97,17 +97,17 @@ class GroupTable:
         if first_logical < self.lo[row]:
             raise OutOfPages(f"{self.name}: page {first_logical} of row {row} was already released")
         for lp in range(start, last_logical + 1):
-            if not self.owns(lp):
+            if self.owns(lp):
+                while not self.free and self.on_pressure is not None and self.on_pressure():
+                    pass                                   # cached prefixes give pages back, oldest first
+                if not self.free:
+                    # the pages taken so far stay with the row (the interval below covers them): nothing leaks
+                    raise OutOfPages(f"{self.name}: pool of {self.num_pages} pages exhausted")
+                t[lp] = self.free.pop()
+                self.ref[int(t[lp])] = 1
+            else:
                 t[lp] = self.trash
-                continue
-            while not self.free and self.on_pressure is not None and self.on_pressure():
-                pass                                       # cached prefixes give pages back, oldest first
-            if not self.free:
-                raise OutOfPages(f"{self.name}: pool of {self.num_pages} pages exhausted")
-            t[lp] = self.free.pop()
-            self.ref[int(t[lp])] = 1
-        if last_logical + 1 > self.hi[row]:
-            self.hi[row] = last_logical + 1
+            self.hi[row] = lp + 1
             self.dirty = True
             self.dirty_rows.add(row)
 
