@@ -602,3 +602,59 @@ def test_truncated_sampling_matches_the_definition_on_cpu():
     t0, _ = S.gumbel_argmax(logits, temp, seed, pos)
     t1, _ = S.gumbel_argmax(logits, temp, seed, pos, top_k=torch.zeros(B, dtype=torch.int32), top_p=torch.ones(B))
     assert torch.equal(t0, t1)
+
+
+from stkernel_b200.serve.api_server import OutputPipeline  # noqa: E402
+
+_PIPE_TOK = ChatTokenizer(ByteTokenizer(1024))
+PIPE_TOOLS = [{"type": "function", "function": {"name": "get_weather", "description": "w", "parameters": {
+                  "type": "object", "properties": {"city": {"type": "string"}, "days": {"type": "integer"}, "opts": {"type": "object"}}}}},
+              {"type": "function", "function": {"name": "f2", "description": "x", "parameters": {
+                  "type": "object", "properties": {"q": {"type": "string"}}}}}]
+
+
+# ---- randomised chunking of the whole output pipeline --------------------------------------------------------------
+def _pipe_run(text, thinking, stop, sizes):
+    ids = _PIPE_TOK.encode(text)
+    pipe = OutputPipeline(_PIPE_TOK, thinking, PIPE_TOOLS, stop)
+    r = c = ""; calls = {}
+    i = 0; k = 0
+    while i < len(ids) and not pipe.stopped:
+        n = sizes[k % len(sizes)]; k += 1
+        chunk = ids[i:i + n]; i += n
+        p = pipe.push(chunk, i >= len(ids), None)
+        r += p.reasoning; c += p.content
+        for t in p.tool_calls:
+            d = t.to_openai()
+            e = calls.setdefault(d["index"], {"name": "", "arguments": ""})
+            f = d.get("function", {})
+            if f.get("name"): e["name"] = f["name"]
+            e["arguments"] += f.get("arguments", "")
+    if i >= len(ids) and not pipe.stopped and k == 0:
+        pass
+    return r, c, calls, pipe.stopped
+
+
+def test_output_pipeline_is_independent_of_how_tokens_are_grouped():
+    """Detokenizer, stop strings, reasoning splitter and tool-call parser together: any grouping of the tokens into steps
+    gives the reasoning, content, tool calls and stop flag of pushing them all at once."""
+    import random
+    rng = random.Random(0)
+    for trial in range(150):
+        think = rng.random() < 0.5
+        parts = []
+        if think:
+            parts.append(rng.choice(["I think so.", "Let me <see> 한글 생각", "", "multi\nline\n\nthought"]) + E.THINK_CLOSE)
+        parts.append(rng.choice(["Answer: 42.", "한국어 답변 ✓ emoji 🙂", "", "text with < and <｜ partial", "stop here please"]))
+        if rng.random() < 0.6:
+            calls = [{"function": {"name": rng.choice(["get_weather", "f2"]),
+                                   "arguments": json.dumps(rng.choice([{"city": "서울", "days": 2}, {"q": "a<b>c"},
+                                                                       {"city": "x", "opts": {"a": [1, 2]}}, {}]))}}
+                     for _ in range(rng.randint(1, 3))]
+            parts.append(E.dsml_tool_calls(calls))
+        text = "".join(parts)
+        stop = rng.choice([[], [], ["please"], ["42"]])
+        whole = _pipe_run(text, think, stop, [10 ** 6])
+        for _ in range(3):
+            sizes = [rng.randint(1, 9) for _ in range(7)]
+            assert _pipe_run(text, think, stop, sizes) == whole, (text, stop, sizes)
