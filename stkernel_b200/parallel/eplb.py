@@ -73,26 +73,13 @@ def initial_placement(n_logical: int, n_redundant: int, ep_size: int) -> Placeme
     return rebalance([1.0] * n_logical, n_redundant, ep_size)
 
 
-def rebalance(load: Sequence[float], n_redundant: int, ep_size: int) -> Placement:
-    """Placement for the observed per-logical-expert load (tokens routed to it).
-
-    Replication: each spare slot goes to the expert whose load per replica is currently highest.  Packing: physical
-    slots sorted by their load share, each placed on the rank with the smallest total that still has a free slot and,
-    where possible, no replica of the same expert yet.  With no spares and uniform load this is the identity."""
+def _pack(load: Sequence[float], reps: Sequence[int], ep_size: int) -> List[int]:
+    """Physical slots (one per replica, load split evenly) onto ranks of equal slot count: heaviest first, each onto the
+    rank with the smallest total that still has a free slot and, where possible, no replica of the same expert yet."""
     n = len(load)
-    n_phys = n + n_redundant
-    if n_phys % ep_size:
-        raise ValueError("n_logical + n_redundant must be a multiple of the expert-parallel size")
-    load = [max(float(x), 0.0) for x in load]
-    reps = [1] * n
-    for _ in range(n_redundant):
-        e = max(range(n), key=lambda i: (load[i] / reps[i], -i))
-        reps[e] += 1
-    if n_redundant == 0 and len(set(load)) <= 1:
-        return Placement(n, ep_size, list(range(n)))
     items = [(load[e] / reps[e], e) for e in range(n) for _ in range(reps[e])]
     items.sort(key=lambda x: (-x[0], x[1]))
-    per = n_phys // ep_size
+    per = len(items) // ep_size
     rank_load = [0.0] * ep_size
     rank_slots: List[List[int]] = [[] for _ in range(ep_size)]
     for share, e in items:
@@ -101,8 +88,42 @@ def rebalance(load: Sequence[float], n_redundant: int, ep_size: int) -> Placemen
         r = min(fresh, key=lambda q: (rank_load[q], q))
         rank_slots[r].append(e)
         rank_load[r] += share
-    p2l = [e for r in range(ep_size) for e in sorted(rank_slots[r])]
-    out = Placement(n, ep_size, p2l)
+    return [e for r in range(ep_size) for e in sorted(rank_slots[r])]
+
+
+def _replicate(load: Sequence[float], n_redundant: int, ep_size: int) -> List[int]:
+    """Replica counts: each spare slot goes to the expert whose load per replica is currently highest, up to one replica
+    per rank (a second replica on a rank takes nothing off that rank); what is left over goes to the least loaded experts."""
+    n = len(load)
+    reps = [1] * n
+    for _ in range(n_redundant):
+        open_ = [i for i in range(n) if reps[i] < ep_size]
+        if open_:
+            e = max(open_, key=lambda i: (load[i] / reps[i], -i))
+        else:
+            # every expert is on every rank already: a further copy cannot help, so it goes where it disturbs least
+            e = min(range(n), key=lambda i: (load[i], reps[i], i))
+        reps[e] += 1
+    return reps
+
+
+def rebalance(load: Sequence[float], n_redundant: int, ep_size: int) -> Placement:
+    """Placement for the observed per-logical-expert load (tokens routed to it).
+
+    Replication and packing are greedy (`_replicate`, `_pack`); the result is compared with the placement that ignores
+    the load (uniform replication, same packing) and the one with the smaller busiest rank is returned, so a rebalance
+    never makes the busiest rank busier.  With no spares and uniform load this is the identity."""
+    n = len(load)
+    n_phys = n + n_redundant
+    if n_phys % ep_size:
+        raise ValueError("n_logical + n_redundant must be a multiple of the expert-parallel size")
+    load = [max(float(x), 0.0) for x in load]
+    if n_redundant == 0 and len(set(load)) <= 1:
+        return Placement(n, ep_size, list(range(n)))
+    flat = [1.0] * n
+    candidates = [Placement(n, ep_size, _pack(load, _replicate(load, n_redundant, ep_size), ep_size)),
+                  Placement(n, ep_size, _pack(flat, _replicate(flat, n_redundant, ep_size), ep_size))]
+    out = min(candidates, key=lambda p: max(rank_loads(p, load)))
     out.validate()
     return out
 

@@ -81,3 +81,32 @@ def test_engine_records_load_and_a_rebalanced_engine_emits_the_same_text():
     assert len(gains) == cfg.num_hidden_layers and all(g <= 1.0 + 1e-9 for g in gains)
     assert eng.model.w.layers[0].experts.num_local == 10 and eng.model.w.layers[0].eplb is not None
     assert eng.generate(prompts, sp) == ref
+
+
+def test_random_loads_keep_the_placement_valid_and_never_make_the_busiest_rank_busier():
+    import random
+    from stkernel_b200.parallel.eplb import initial_placement, rank_loads, rebalance, to_physical
+    rng = random.Random(0)
+    for _ in range(300):
+        ep = rng.choice([1, 2, 4, 8])
+        n_log = ep * rng.randint(1, 8)
+        red = ep * rng.randint(0, 3)
+        kind = rng.choice(["uniform", "zero", "skew", "one"])
+        load = {"uniform": [1.0] * n_log, "zero": [0.0] * n_log,
+                "skew": [rng.random() ** 4 * 100 for _ in range(n_log)],
+                "one": [100.0 if i == n_log // 2 else 0.0 for i in range(n_log)]}[kind]
+        p = rebalance(load, red, ep)
+        p.validate()
+        reps = p.replicas()
+        assert len(reps) == n_log and all(len(r) >= 1 for r in reps)
+        assert p.n_physical == n_log + red and sorted(x for r in reps for x in r) == list(range(p.n_physical))
+        if sum(load) > 0:
+            assert max(rank_loads(p, load)) <= max(rank_loads(initial_placement(n_log, red, ep), load)) * (1 + 1e-9)
+        if kind == "one" and red >= ep and ep > 1:
+            # the one busy expert has a replica on every rank and no more: the load is even
+            assert len(reps[n_log // 2]) >= ep and max(rank_loads(p, load)) == pytest.approx(100.0 / ep)
+        l2p, cnt = p.tables("cpu")
+        ids = torch.randint(0, n_log, (40, 3), dtype=torch.int32)
+        ph = to_physical(ids, l2p, cnt)
+        owner = {s: e for e, r in enumerate(reps) for s in r}
+        assert [owner[x] for x in ph.flatten().tolist()] == ids.flatten().tolist()
