@@ -6,6 +6,11 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
+# The CPU suite runs tiny models: intra-op parallelism over every core costs more in thread hand-offs than it saves, and
+# the multi-process tests share the cores between ranks.
+if not torch.cuda.is_available():
+    torch.set_num_threads(min(4, os.cpu_count() or 1))
+
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200)")

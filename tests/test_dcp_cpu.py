@@ -21,6 +21,7 @@ def _run(rank, world, port, path, kv_dtype, stage_mb, shared_prefix=False):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       STK_CPU_ACT_FP32="1", STK_DCP_STAGE_MB=stage_mb, CUDA_VISIBLE_DEVICES="")
     import torch.distributed as dist
+    torch.set_num_threads(2)                      # several ranks share the host: tiny tensors gain nothing from more
     from stkernel_b200.config import EngineConfig, ParallelConfig, SchedulerConfig, tiny_config
     from stkernel_b200.models.dsv4 import DictSource, build_model_weights
     from stkernel_b200.models.weights import init_random_weights
@@ -62,26 +63,31 @@ def _run(rank, world, port, path, kv_dtype, stage_mb, shared_prefix=False):
         dist.destroy_process_group()
 
 
-def _spawn(world, path, kv_dtype, stage_mb="64", shared_prefix=False):
+def _spawn_all(runs):
+    """runs: [(world, path, kv_dtype, stage_mb, shared_prefix)], started together; -> the ranks' results of each run."""
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
-    port = _free_port()
-    ps = [ctx.Process(target=_run, args=(r, world, port, path, kv_dtype, stage_mb, shared_prefix)) for r in range(world)]
-    for q in ps:
-        q.start()
-    for q in ps:
-        q.join(500)
-        assert q.exitcode == 0
-    return [json.load(open(f"{path}.{r}")) for r in range(world)]
+    procs = []
+    for world, path, kv_dtype, stage_mb, shared_prefix in runs:
+        port = _free_port()
+        procs.append([ctx.Process(target=_run, args=(r, world, port, path, kv_dtype, stage_mb, shared_prefix)) for r in range(world)])
+    for ps in procs:
+        for q in ps:
+            q.start()
+    for ps in procs:
+        for q in ps:
+            q.join(500)
+            assert q.exitcode == 0
+    return [[json.load(open(f"{run[1]}.{r}")) for r in range(run[0])] for run in runs]
 
 
 @pytest.mark.timeout(900)
 @pytest.mark.parametrize("kv_dtype", ["bf16", "fp8_ds_mla"])
 def test_context_parallel_decode_matches_one_rank(tmp_path, kv_dtype):
-    one = _spawn(1, str(tmp_path / "one"), kv_dtype)[0]
     # the bf16 run has a staging budget of zero megabytes, which forces one token per staging call (the block loop of
     # large steps); the fp8 run stages a whole step at once
-    two = _spawn(2, str(tmp_path / "two"), kv_dtype, stage_mb="0" if kv_dtype == "bf16" else "64")
+    (one,), two = _spawn_all([(1, str(tmp_path / "one"), kv_dtype, "64", False),
+                              (2, str(tmp_path / "two"), kv_dtype, "0" if kv_dtype == "bf16" else "64", False)])
     assert one["stats"]["dcp_topk_merges"] == 0
     for r in two:
         assert r["out"] == one["out"]
@@ -95,8 +101,7 @@ def test_context_parallel_decode_matches_one_rank(tmp_path, kv_dtype):
 
 @pytest.mark.timeout(900)
 def test_context_parallel_with_a_cached_prefix(tmp_path):
-    one = _spawn(1, str(tmp_path / "one"), "bf16", shared_prefix=True)[0]
-    two = _spawn(2, str(tmp_path / "two"), "bf16", shared_prefix=True)
+    (one,), two = _spawn_all([(1, str(tmp_path / "one"), "bf16", "64", True), (2, str(tmp_path / "two"), "bf16", "64", True)])
     assert one["prefix_hit_tokens"] == 512
     for r in two:
         assert r["prefix_hit_tokens"] == 512
@@ -107,6 +112,7 @@ def _run_spec(rank, world, port, path):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       STK_CPU_ACT_FP32="1", CUDA_VISIBLE_DEVICES="")
     import torch.distributed as dist
+    torch.set_num_threads(2)                      # several ranks share the host: tiny tensors gain nothing from more
     from stkernel_b200.config import EngineConfig, ParallelConfig, SchedulerConfig, SpecConfig, tiny_config
     from stkernel_b200.models.dsv4 import DictSource, build_model_weights
     from stkernel_b200.models.weights import init_random_weights
@@ -143,17 +149,17 @@ def test_speculative_decoding_over_context_parallel_caches(tmp_path):
     sampled text (fixed seeds) equals plain decoding on one rank."""
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
-    res = {}
+    res, procs = {}, {}
     for world in (1, 2):
         port = _free_port()
-        path = str(tmp_path / f"w{world}")
-        ps = [ctx.Process(target=_run_spec, args=(r, world, port, path)) for r in range(world)]
-        for q in ps:
+        procs[world] = [ctx.Process(target=_run_spec, args=(r, world, port, str(tmp_path / f"w{world}"))) for r in range(world)]
+        for q in procs[world]:
             q.start()
-        for q in ps:
+    for world in (1, 2):
+        for q in procs[world]:
             q.join(500)
             assert q.exitcode == 0
-        res[world] = [json.load(open(f"{path}.{r}")) for r in range(world)]
+        res[world] = [json.load(open(str(tmp_path / f"w{world}") + f".{r}")) for r in range(world)]
     assert res[2][0]["out"] == res[2][1]["out"] == res[1][0]["out"]
     assert res[2][0]["drafts"] > 0 and res[1][0]["drafts"] == 0
 

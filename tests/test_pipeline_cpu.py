@@ -21,6 +21,7 @@ def _run(rank, world, port, path):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       STK_CPU_ACT_FP32="1", CUDA_VISIBLE_DEVICES="")
     import torch.distributed as dist
+    torch.set_num_threads(2)                      # several ranks share the host: tiny tensors gain nothing from more
     from stkernel_b200.config import EngineConfig, ParallelConfig, SchedulerConfig, tiny_config
     from stkernel_b200.models.dsv4 import DictSource, build_model_weights
     from stkernel_b200.models.weights import init_random_weights
@@ -59,6 +60,7 @@ def _run_pp_tp(rank, port, path, dcp=1):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE="4",
                       STK_CPU_ACT_FP32="1", STK_SEQ_PARALLEL_MIN_ROWS="4", CUDA_VISIBLE_DEVICES="")
     import torch.distributed as dist
+    torch.set_num_threads(2)                      # several ranks share the host: tiny tensors gain nothing from more
     from stkernel_b200.config import EngineConfig, ParallelConfig, SchedulerConfig, tiny_config
     from stkernel_b200.models.dsv4 import DictSource, build_model_weights
     from stkernel_b200.models.weights import init_random_weights
@@ -91,6 +93,7 @@ def _run_micro(rank, world, port, path):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       STK_CPU_ACT_FP32="1", CUDA_VISIBLE_DEVICES="")
     import torch.distributed as dist
+    torch.set_num_threads(2)                      # several ranks share the host: tiny tensors gain nothing from more
     from stkernel_b200.config import EngineConfig, ParallelConfig, SchedulerConfig, tiny_config
     from stkernel_b200.models.dsv4 import DictSource, build_model_weights
     from stkernel_b200.models.weights import init_random_weights
@@ -133,6 +136,7 @@ def _run_prefix(rank, world, port, path):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       STK_CPU_ACT_FP32="1", CUDA_VISIBLE_DEVICES="")
     import torch.distributed as dist
+    torch.set_num_threads(2)                      # several ranks share the host: tiny tensors gain nothing from more
     from stkernel_b200.config import EngineConfig, ParallelConfig, SchedulerConfig, tiny_config
     from stkernel_b200.models.dsv4 import DictSource, build_model_weights
     from stkernel_b200.models.weights import init_random_weights
@@ -189,8 +193,9 @@ def test_pipeline_stages_match_single_process(tmp_path):
             assert a["layers"][1] == b["layers"][0]
         for st in stages:
             assert st["kv_layers"] == list(range(*st["layers"]))
-    # the 3-stage cut is [0,2) [2,4) [4,5): the last stage starts at layer 4, which reuses layer 3's top-k rows
-    assert _spawn(3, str(tmp_path / "pp3b"))[2]["starts_inside_group"] is True
+        # the 3-stage cut is [0,2) [2,4) [4,5): the last stage starts at layer 4, which reuses layer 3's top-k rows
+        if world == 3:
+            assert stages[2]["starts_inside_group"] is True
 
 
 def test_pipeline_stage_arithmetic_and_guards():

@@ -22,6 +22,7 @@ def _run(rank, world, port, path):
                       STK_CPU_ACT_FP32="1", STK_INDEXER_SP_MIN_ROWS="4", STK_MLA_TP_MIN_ROWS="4",
                       STK_SEQ_PARALLEL_MIN_ROWS="4", CUDA_VISIBLE_DEVICES="")
     import torch.distributed as dist
+    torch.set_num_threads(2)                      # several ranks share the host: tiny tensors gain nothing from more
     from stkernel_b200.config import EngineConfig, ParallelConfig, SchedulerConfig, tiny_config
     from stkernel_b200.models.dsv4 import DictSource, build_model_weights
     from stkernel_b200.models.weights import init_random_weights

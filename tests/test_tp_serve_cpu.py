@@ -73,13 +73,16 @@ def test_tp2_lockstep_serving_matches_tp1():
     # the third server also deals the ratio-4 KV pages over its two ranks (decode context parallelism); the fourth
     # runs its two ranks as two pipeline stages of one layer each; the fifth launches every step before the previous
     # one's tokens are read (leader and follower must still take the same steps); the sixth runs two engines per stage
-    # with their steps interleaved (micro-batches in flight)
-    for key, world, extra, tp in ((1, 1, (), None), (2, 2, (), None), ("dcp", 2, ("--decode-context-parallel-size", "2"), None),
-                                  ("pp", 2, ("--pipeline-parallel-size", "2"), 1), ("async", 2, ("--async-scheduling",), None),
-                                  ("ppmb", 2, ("--pipeline-parallel-size", "2", "--pipeline-micro-batches"), 1)):
-        port = _free_port()
-        proc = _launch(world, port, extra, tp)
-        try:
+    # with their steps interleaved (micro-batches in flight).  All six run side by side.
+    configs = ((1, 1, (), None), (2, 2, (), None), ("dcp", 2, ("--decode-context-parallel-size", "2"), None),
+               ("pp", 2, ("--pipeline-parallel-size", "2"), 1), ("async", 2, ("--async-scheduling",), None),
+               ("ppmb", 2, ("--pipeline-parallel-size", "2", "--pipeline-micro-batches"), 1))
+    servers = []
+    try:
+        for key, world, extra, tp in configs:
+            port = _free_port()
+            servers.append((key, port, _launch(world, port, extra, tp)))
+        for key, port, proc in servers:
             _wait_up(port, proc)
             r1 = _post(port, "/v1/completions", body)
             r2 = _post(port, "/v1/completions", body)
@@ -91,7 +94,8 @@ def test_tp2_lockstep_serving_matches_tp1():
             # one character more: of the two prompt lengths one is even, which the sequence-parallel residual needs
             r3 = _post(port, "/v1/completions", dict(body, prompt="!" + body["prompt"][::-1]))
             outs[key] = (r1["choices"][0]["text"], r3["choices"][0]["text"])
-        finally:
+    finally:
+        for _, _, proc in servers:
             _stop(proc)
     # the same weights split over two ranks give the same greedy text (fp32 activations on CPU)
     assert outs[1] == outs[2] == outs["dcp"] == outs["pp"] == outs["async"] == outs["ppmb"]
