@@ -830,32 +830,10 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
 
 
 def main(argv: Optional[Sequence[str]] = None) -> int:
-    """`python -m stkernel_b200.serve.api_server --layers N [--tokenizer DIR] [--port P]`: serve a
-    random-weight model of the flagship architecture (a checkpoint path goes through the launcher)."""
-    import argparse
-    import torch
-    import uvicorn
-    from ..config import flash_config, tiny_config, EngineConfig
-    from ..models.dsv4 import RandomSource, build_model_weights
-    from .tokenizer import ByteTokenizer, HFTokenizer
-
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--layers", type=int, default=2)
-    ap.add_argument("--tiny", action="store_true", help="CPU-sized architecture (tests, demos)")
-    ap.add_argument("--tokenizer", default=None)
-    ap.add_argument("--host", default="127.0.0.1")
-    ap.add_argument("--port", type=int, default=8000)
-    ap.add_argument("--served-model-name", default="deepseek-v4-flash")
-    ap.add_argument("--default-thinking", action="store_true")
-    a = ap.parse_args(argv)
-    device = torch.device("cuda:0" if torch.cuda.is_available() else "cpu")
-    mcfg = tiny_config() if a.tiny else flash_config(a.layers)
-    cfg = EngineConfig(model=mcfg)
-    weights = build_model_weights(mcfg, RandomSource(mcfg, seed=0), device)
-    eng = Engine(cfg, weights, device)
-    tok = ChatTokenizer(HFTokenizer(a.tokenizer) if a.tokenizer else ByteTokenizer(mcfg.vocab_size))
-    uvicorn.run(create_app(eng, tok, a.served_model_name, a.default_thinking), host=a.host, port=a.port, log_level="info")
-    return 0
+    """`python -m stkernel_b200.serve.api_server --layers N [--tiny] [--tokenizer DIR] [--port P] ...`: one process, one
+    device.  The flags are those of the multi-rank worker (`serve/tp_worker.py`), which this runs with a single rank."""
+    from .tp_worker import main as worker_main
+    return worker_main(argv)
 
 
 if __name__ == "__main__":

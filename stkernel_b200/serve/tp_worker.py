@@ -196,6 +196,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--temperature", type=float, default=0.8)
     ap.add_argument("--speculative-config", default="")
     ap.add_argument("--default-chat-template-kwargs", default="")
+    ap.add_argument("--default-thinking", action="store_true", help="requests think unless they say otherwise")
     ap.add_argument("--profiler-dir", default="/tmp/stk_profiles")
     ap.add_argument("--layers", type=int, default=2, help="random-weight mode: decoder layers")
     ap.add_argument("--tiny", action="store_true", help="random-weight mode: CPU-sized architecture")
@@ -224,7 +225,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     import uvicorn
     tok = ChatTokenizer(HFTokenizer(a.tokenizer or a.model) if (a.tokenizer or a.model) else ByteTokenizer(mcfg.vocab_size))
     kwargs = json.loads(a.default_chat_template_kwargs) if a.default_chat_template_kwargs else None
-    app = create_app(eng, tok, a.served_model_name, profile_dir=a.profiler_dir, default_chat_template_kwargs=kwargs,
+    app = create_app(eng, tok, a.served_model_name, default_thinking=a.default_thinking, profile_dir=a.profiler_dir,
+                     default_chat_template_kwargs=kwargs,
                      async_engine=LockstepLeader(eng, cpu_group) if world > 1 else None,
                      default_temperature=a.temperature)
     uvicorn.run(app, host=a.host, port=a.port, log_level="info")

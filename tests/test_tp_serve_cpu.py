@@ -101,6 +101,23 @@ def test_tp2_lockstep_serving_matches_tp1():
     assert outs[1] == outs[2] == outs["dcp"] == outs["pp"] == outs["async"] == outs["ppmb"]
 
 
+@pytest.mark.timeout(300)
+def test_single_process_entry_point_serves():
+    """`python -m stkernel_b200.serve.api_server`: the one-device command of the quick start."""
+    port = _free_port()
+    env = dict(os.environ, PYTHONPATH=ROOT, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2", STK_CPU_ACT_FP32="1")
+    cmd = [sys.executable, "-m", "stkernel_b200.serve.api_server", "--tiny", "--port", str(port), "--max-model-len", "512",
+           "--max-num-seqs", "2", "--max-num-batched-tokens", "128", "--graph-cap", "0", "--default-thinking"]
+    proc = subprocess.Popen(cmd, env=env, cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, start_new_session=True)
+    try:
+        _wait_up(port, proc)
+        r = _post(port, "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4,
+                                                 "temperature": 0, "ignore_eos": True})
+        assert r["usage"]["completion_tokens"] == 4 and r["choices"][0]["finish_reason"] == "length"
+    finally:
+        _stop(proc)
+
+
 def _follower_main(rank, port, result_path):
     import datetime
     import torch.distributed as dist
