@@ -120,3 +120,41 @@ def test_speculative_engine_with_partly_right_drafts_matches_requests_run_alone(
     assert [eng.requests[i].output for i in ids] == want
     m = eng.metrics
     assert 0 < m.spec_num_accepted_tokens < m.spec_num_draft_tokens
+
+
+@pytest.mark.parametrize("trial", [302, 308])
+def test_random_aborts_leave_the_other_requests_and_the_pools_intact(model, trial):
+    """Requests aborted at random moments (waiting, mid-prefill, decoding, with a step in flight): the others get the
+    text they get alone, and once everything has ended no page, row or promise is left behind."""
+    cfg, _ = model
+    rng = random.Random(trial)
+    g = torch.Generator().manual_seed(trial)
+    prompts = [torch.randint(0, cfg.vocab_size, (rng.choice([3, 40, 130, 257, 300]),), generator=g).tolist()
+               for _ in range(rng.randint(4, 8))]
+    params = [SamplingParams(temperature=0.0, max_tokens=rng.randint(2, 10)) for _ in prompts]
+    alone = _engine(model, 1, 4096, prefix=False)
+    want = [alone.generate([p], sp)[0] for p, sp in zip(prompts, params)]
+    eng = _engine(model, rng.choice([2, 3]), rng.choice([24, 64, 128]), async_on=rng.random() < 0.5,
+                  pool=rng.choice([None, 900]), prefix=rng.random() < 0.5)
+    ids, k, aborted = [], 0, set()
+    while k < len(prompts) or eng.has_work():
+        for _ in range(rng.randint(0, 2)):
+            if k < len(prompts):
+                ids.append(eng.add_request(prompts[k], params[k]))
+                k += 1
+        if ids and rng.random() < 0.25:
+            victim = rng.choice(ids)
+            if eng.abort(victim):
+                aborted.add(victim)
+                eng.release(victim)
+        if eng.has_work():
+            eng.step()
+    assert len(aborted) >= 2
+    for j, i in enumerate(ids):
+        if i not in aborted:
+            assert eng.requests[i].output == want[j]
+    if eng.prefix_cache is not None:
+        eng.prefix_cache.reset()
+    kv = eng.kv
+    assert (kv.c4.pages_in_use, kv.swa.pages_in_use, kv.c128.pages_in_use) == (0, 0, 0)
+    assert len(kv.free_rows) == eng.cfg.sched.max_num_seqs and kv.promised() == 0 and not kv.reserved
