@@ -339,6 +339,8 @@ class DSV4Model:
         self.topk_buffer: Optional[torch.Tensor] = None     # IndexCache: shared by consecutive C4A layers
         self.pipe = None                                     # parallel.pipeline.PipeStage when the model is one stage of several
         self.pipe_defer = False                              # the engine exchanges a step's tokens when it finishes the step
+        self.want_logprobs: Optional[int] = None             # set by the engine for a step that reports log-probabilities
+        self.last_logprobs = None                            # (sampled token's, top values, top ids) of that step
         self.aux_layers: Tuple[int, ...] = ()
         self.aux_out: List[torch.Tensor] = []
         self.stats = {"sp_steps": 0, "mla_token_parallel_calls": 0, "dcp_topk_merges": 0}     # which paths ran (tests)
@@ -894,6 +896,15 @@ class DSV4Model:
         candidate per row (no logits all-gather); truncated sampling (top-k / top-p) needs the whole row and gathers."""
         from ..ops import sampling as S
         n = h.shape[0]
+        if self.want_logprobs is not None:
+            # log-probabilities asked for: the whole rows are needed anyway (gathered across ranks); the token is the one
+            # the sharded arg-max would pick (same noise, same logits)
+            lg = self.compute_logits(h)
+            toks, _ = S.gumbel_argmax(lg, temp, seed, pos, top_k=top_k, top_p=top_p)
+            lp = torch.log_softmax(lg.float(), dim=-1)
+            top_lp, top_ids = lp.topk(max(1, min(self.want_logprobs, lp.shape[1])), dim=-1)
+            self.last_logprobs = (lp.gather(1, toks.view(-1, 1).long()).squeeze(1), top_lp, top_ids)
+            return toks
         ll = None
         if self.tp_size > 1 and top_k is None and top_p is None and h.is_cuda and n <= 256:
             ll = self._ll_any(3 * n)

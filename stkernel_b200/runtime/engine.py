@@ -45,6 +45,7 @@ class SamplingParams:
     eos_token_id: Optional[int] = None
     top_k: int = 0                  # <= 0: off
     top_p: float = 1.0              # >= 1: off
+    logprobs: Optional[int] = None  # report the sampled token's log-probability and this many most likely alternatives
 
     @property
     def truncates(self) -> bool:
@@ -64,6 +65,7 @@ class Request:
     first_token_time: Optional[float] = None
     finish_reason: Optional[str] = None   # "stop" (EOS), "length" (token or context limit), "abort"
     drafts: List[int] = field(default_factory=list)   # proposals awaiting verification (speculative decoding)
+    logprobs: List[Tuple[float, List[Tuple[int, float]]]] = field(default_factory=list)   # per output token, when asked for
 
     @property
     def tokens(self) -> List[int]:
@@ -339,12 +341,19 @@ class Engine:
         req = Request(rid, list(prompt), params or SamplingParams())
         if len(req.prompt) + req.params.max_tokens > self.cfg.sched.max_model_len + 64:
             raise ValueError("request exceeds max_model_len")
+        if req.params.logprobs is not None and not self.supports_logprobs:
+            raise ValueError("log-probabilities are not available with speculative decoding, asynchronous scheduling or "
+                             "pipeline stages")
         if not self.kv.fits(min(len(req.prompt) + req.params.max_tokens, self.cfg.sched.max_model_len)):
             raise ValueError("request needs more compressed-KV pages than the pool holds")
         self.requests[rid] = req
         self.sched.add(req)
         self.metrics.requests_total += 1
         return rid
+
+    @property
+    def supports_logprobs(self) -> bool:
+        return self.drafter is None and not self.async_scheduling and self.model.pipe is None
 
     def has_work(self) -> bool:
         return bool(self.sched.waiting or self.sched.running) or self._inflight is not None
@@ -620,11 +629,19 @@ class Engine:
         max_end = max(s.start + s.n for s in seqs)
         max_comp_rows = max(1, max_end // 4)
         pure_decode = all(s.n == 1 and s.samples for s in seqs)
+        want_lp = max((s.req.params.logprobs for s in seqs if s.samples and s.req.params.logprobs is not None), default=None)
         if ns == 0:
             # prefill chunk that samples nothing: run the body only
             meta = self._build_meta(t, n_req, max_comp_rows)
             self.model.forward_hidden(meta)
             toks_dev = None
+        elif want_lp is not None:
+            # a step that reports log-probabilities runs outside the captured graphs and gathers whole logit rows
+            self.model.want_logprobs, self.model.last_logprobs = want_lp, None
+            try:
+                toks_dev = self._run_model(t, n_req, ns, max_comp_rows)
+            finally:
+                self.model.want_logprobs = None
         elif self.use_graphs and pure_decode and n_req <= self.cfg.sched.graph_cap and not self.buf.truncating:
             toks_dev = self._decode_graph(n_req, max_comp_rows).replay()
         else:
@@ -652,6 +669,11 @@ class Engine:
                 new_tokens = toks_dev[:ns].tolist()
             self.d2h_bytes_last = ns * 8 + 8
             self._check_device_status()
+        lps = None
+        if toks_dev is not None and self.model.last_logprobs is not None:
+            tok_lp, top_lp, top_ids = (x[:ns].tolist() for x in self.model.last_logprobs)
+            self.model.last_logprobs = None
+            lps = list(zip(tok_lp, top_lp, top_ids))
         k = 0
         now = time.time()
         for s in seqs:
@@ -661,6 +683,9 @@ class Engine:
                 self.metrics.prompt_tokens_total += s.n
             if s.samples:
                 tok = new_tokens[k]
+                if lps is not None and r.params.logprobs is not None:
+                    lp, vals, ids_ = lps[k]
+                    r.logprobs.append((lp, list(zip(ids_, vals))[:r.params.logprobs]))
                 k += 1
                 r.output.append(tok)
                 if r.first_token_time is None:

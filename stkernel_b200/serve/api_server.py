@@ -46,6 +46,7 @@ class TokenEvent:
     finished: bool
     finish_reason: Optional[str] = None
     error: Optional[str] = None
+    logprobs: Optional[List[Any]] = None          # per token: (log-probability, [(id, log-probability), ...]) when asked for
 
 
 class AsyncEngine:
@@ -108,7 +109,10 @@ class AsyncEngine:
         for rid, toks in by_req.items():
             r = eng.requests.get(rid)
             done = r is not None and r.finished
-            self._post(rid, TokenEvent(toks, done, r.finish_reason if done else None))
+            lps = None
+            if r is not None and getattr(r.params, "logprobs", None) is not None:
+                lps = list(r.logprobs[-len(toks):])
+            self._post(rid, TokenEvent(toks, done, r.finish_reason if done else None, logprobs=lps))
             if done:
                 self._streams.pop(rid, None)
                 eng.release(rid)
@@ -315,6 +319,17 @@ def forced_tool_prefix(tool_choice: Any, tools: Optional[List[Dict[str, Any]]]) 
     return head + (f'{name}">\n' if name is not None else "")
 
 
+def logprob_entries(tokenizer, tokens: Sequence[int], lps: Optional[Sequence[Any]]) -> List[Dict[str, Any]]:
+    """OpenAI chat `logprobs.content` entries for the tokens of one event."""
+    def one(tid: int, lp: float) -> Dict[str, Any]:
+        text = tokenizer.decode([int(tid)])
+        return {"token": text, "logprob": float(lp), "bytes": list(text.encode("utf-8"))}
+    out = []
+    for tid, (lp, top) in zip(tokens, lps or []):
+        out.append({**one(tid, lp), "top_logprobs": [one(i, v) for i, v in top]})
+    return out
+
+
 def choice_count(body: Dict[str, Any], limit: int = 16) -> int:
     n = body.get("n", 1)
     if not isinstance(n, int) or isinstance(n, bool) or not 1 <= n <= limit:
@@ -361,7 +376,14 @@ def sampling_from_request(body: Dict[str, Any], eos_id: Optional[int], max_model
         raise HTTPException(status_code=400, detail="top_p must be in (0, 1]")
     if top_k < -1:
         raise HTTPException(status_code=400, detail="top_k must be -1 (off), 0 (off) or positive")
-    return SamplingParams(temperature=float(default_temperature if temp is None else temp),
+    want_lp = None
+    if body.get("logprobs") not in (None, False):
+        # chat: `logprobs: true` + `top_logprobs: n`; raw completions: `logprobs: n`
+        n_top = body.get("top_logprobs") if isinstance(body.get("logprobs"), bool) else body.get("logprobs")
+        want_lp = int(n_top or 0)
+        if not 0 <= want_lp <= 20:
+            raise HTTPException(status_code=400, detail="top_logprobs must be in [0, 20]")
+    return SamplingParams(logprobs=want_lp, temperature=float(default_temperature if temp is None else temp),
                           seed=int(seed) if seed is not None else uuid.uuid4().int & 0x7FFFFFFF,
                           max_tokens=max_tokens, min_tokens=int(body.get("min_tokens", 0) or 0),
                           ignore_eos=bool(body.get("ignore_eos", False)), eos_token_id=eos_id,
@@ -431,6 +453,12 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
     def err(status: int, msg: str, kind: str = "invalid_request_error"):
         return JSONResponse({"error": {"message": msg, "type": kind, "code": status}}, status_code=status)
 
+    def refuse_logprobs(params: SamplingParams):
+        if params.logprobs is not None and not getattr(engine, "supports_logprobs", False):
+            return err(400, "log-probabilities are not available on this server (speculative decoding, asynchronous "
+                            "scheduling or pipeline stages are on)")
+        return None
+
     def sse(obj: Any) -> str:
         return "data: " + (obj if isinstance(obj, str) else json.dumps(obj, ensure_ascii=False)) + "\n\n"
 
@@ -494,6 +522,8 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
         if len(ids) >= max_len:
             return err(400, f"prompt has {len(ids)} tokens; the model's context is {max_len}")
         params = sampling_from_request(body, eos_id, max_len, len(ids), default_temperature=default_temperature)
+        if refuse_logprobs(params) is not None:
+            return refuse_logprobs(params)
         stop = body.get("stop") or []
         stop = [stop] if isinstance(stop, str) else list(stop)
         rid = f"chatcmpl-{uuid.uuid4().hex}"
@@ -550,8 +580,12 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
                             delta["content"] = piece.content
                         if piece.tool_calls:
                             delta["tool_calls"] = [t.to_openai() for t in piece.tool_calls]
-                        if delta:
-                            yield sse({**base, "choices": [{"index": i, "delta": delta, "finish_reason": None}]})
+                        entries = logprob_entries(tokenizer, ev.tokens, ev.logprobs) if ev.logprobs else None
+                        if delta or entries:
+                            choice = {"index": i, "delta": delta, "finish_reason": None}
+                            if entries:
+                                choice["logprobs"] = {"content": entries}
+                            yield sse({**base, "choices": [choice]})
                         reasons[i] = ev.finish_reason
                         if pipes[i].stopped or ev.finished:
                             done.add(i)
@@ -569,10 +603,13 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
         async def collect(i: int):
             pipe = pipes[i]
             reasoning, content, n_out, reason = "", "", 0, None
+            entries: List[Dict[str, Any]] = []
             async for ev in aeng.generate(ids, seeds[i]):
                 if ev.error:
                     return ev.error
                 n_out += len(ev.tokens)
+                if ev.logprobs:
+                    entries += logprob_entries(tokenizer, ev.tokens, ev.logprobs)
                 piece = pipe.push(ev.tokens, ev.finished, eos_id)
                 reasoning += piece.reasoning
                 content += piece.content
@@ -586,7 +623,10 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
                 message["tool_calls"] = [{"id": c["id"], "type": "function",
                                           "function": {"name": c["name"], "arguments": c["arguments"]}}
                                          for c in pipe.tools.complete_calls]
-            return {"index": i, "message": message, "finish_reason": finish(pipe, reason)}, n_out
+            choice = {"index": i, "message": message, "finish_reason": finish(pipe, reason)}
+            if seeds[i].logprobs is not None:
+                choice["logprobs"] = {"content": entries}
+            return choice, n_out
 
         results = await asyncio.gather(*(collect(i) for i in range(n_choices)))
         for r in results:
@@ -649,6 +689,8 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
         if len(ids) >= max_len:
             return err(400, f"prompt has {len(ids)} tokens; the model's context is {max_len}")
         params = sampling_from_request(body, eos_id, max_len, len(ids), default_temperature=default_temperature)
+        if refuse_logprobs(params) is not None:
+            return refuse_logprobs(params)
         rid = f"cmpl-{uuid.uuid4().hex}"
         pipe = OutputPipeline(tokenizer, False, None, [body["stop"]] if isinstance(body.get("stop"), str) else (body.get("stop") or []))
         base = {"id": rid, "object": "text_completion", "created": int(time.time()), "model": model_name}
@@ -668,16 +710,23 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
                 yield sse("[DONE]")
             return StreamingResponse(events(), media_type="text/event-stream")
         n_out, reason = 0, None
+        legacy = {"tokens": [], "token_logprobs": [], "top_logprobs": []}
         async for ev in aeng.generate(ids, params):
             if ev.error:
                 return err(500, ev.error, "internal_error")
             n_out += len(ev.tokens)
+            for e in logprob_entries(tokenizer, ev.tokens, ev.logprobs) if ev.logprobs else ():
+                legacy["tokens"].append(e["token"])
+                legacy["token_logprobs"].append(e["logprob"])
+                legacy["top_logprobs"].append({t["token"]: t["logprob"] for t in e["top_logprobs"]})
             pipe.push(ev.tokens, ev.finished, eos_id)
             reason = ev.finish_reason
             if pipe.stopped or ev.finished:
                 break
-        return {**base, "choices": [{"index": 0, "text": pipe.text, "finish_reason": "stop" if pipe.stopped else reason}],
-                "usage": _usage(len(ids), n_out)}
+        choice = {"index": 0, "text": pipe.text, "finish_reason": "stop" if pipe.stopped else reason}
+        if params.logprobs is not None:
+            choice["logprobs"] = legacy
+        return {**base, "choices": [choice], "usage": _usage(len(ids), n_out)}
 
     # ---- tokenizer routes -------------------------------------------------------------------
     @app.post("/tokenize")

@@ -194,3 +194,29 @@ def test_indexer_scoring_in_query_subchunks_under_a_logits_budget():
         A.indexer_scores = orig
     assert out == ref
     assert len(calls) > 20 and max(calls) * 4 * 22 <= 256 + 4 * 22          # rows x compressed rows x 4 bytes within budget
+
+
+def test_log_probabilities_match_the_oracle_and_do_not_change_the_text():
+    torch.manual_seed(0)
+    cfg = tiny_config()
+    w = init_random_weights(cfg, seed=0)
+    eng = make_engine(cfg, w, chunk=48)
+    p = torch.randint(0, cfg.vocab_size, (30,)).tolist()
+    a = eng.add_request(p, SamplingParams(temperature=0.0, max_tokens=5, logprobs=3))
+    b = eng.add_request(p, SamplingParams(temperature=0.0, max_tokens=5))            # same batch, not asking
+    while eng.has_work():
+        eng.step()
+    ra, rb = eng.requests[a], eng.requests[b]
+    assert ra.output == rb.output and len(ra.logprobs) == 5 and rb.logprobs == []
+    _, logits = OracleModel(cfg, w).greedy_decode(torch.tensor(p), 5)
+    ref = torch.log_softmax(logits.float(), -1)
+    for i, (lp, top) in enumerate(ra.logprobs):
+        assert abs(lp - float(ref[i, ra.output[i]])) < 2e-3
+        assert len(top) == 3 and top[0][0] == ra.output[i]
+        assert [t for t, _ in top] == ref[i].topk(3).indices.tolist()
+    # sampled (temperature 1): the reported value is the model's log-probability of the token that was drawn
+    c = eng.add_request(p, SamplingParams(temperature=1.0, seed=5, max_tokens=4, logprobs=0))
+    while eng.has_work():
+        eng.step()
+    rc = eng.requests[c]
+    assert len(rc.logprobs) == 4 and all(top == [] and lp <= 0 for lp, top in rc.logprobs)

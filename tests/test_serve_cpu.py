@@ -314,6 +314,36 @@ def test_completions_batch_of_prompts_and_samples(client):
     assert client.post("/v1/completions", json={"prompt": ["a", "b"], "stream": True}).status_code == 400
 
 
+def test_log_probabilities(client):
+    import math
+    body = {"messages": [{"role": "user", "content": "hello"}], "max_tokens": 5, "temperature": 0, "ignore_eos": True,
+            "logprobs": True, "top_logprobs": 3}
+    r = client.post("/v1/chat/completions", json=body).json()
+    entries = r["choices"][0]["logprobs"]["content"]
+    assert len(entries) == 5
+    for e in entries:
+        assert e["logprob"] <= 0 and len(e["top_logprobs"]) == 3
+        # greedy: the sampled token is the most likely one, and the alternatives come in decreasing order
+        assert e["top_logprobs"][0]["logprob"] == pytest.approx(e["logprob"], abs=1e-5)
+        assert [t["logprob"] for t in e["top_logprobs"]] == sorted((t["logprob"] for t in e["top_logprobs"]), reverse=True)
+        assert e["bytes"] == list(e["token"].encode("utf-8"))
+    # the same answer as without them, and no key when they are not asked for
+    plain = client.post("/v1/chat/completions", json={k: v for k, v in body.items() if "logprobs" not in k}).json()
+    assert plain["choices"][0]["message"] == r["choices"][0]["message"] and "logprobs" not in plain["choices"][0]
+    # streamed: the chunks' entries add up to the same list
+    with client.stream("POST", "/v1/chat/completions", json={**body, "stream": True}) as resp:
+        chunks = [json.loads(x) for x in _sse(resp)[:-1]]
+    streamed = [e for c in chunks for ch in c["choices"] for e in (ch.get("logprobs") or {}).get("content", [])]
+    assert [(e["token"], round(e["logprob"], 5)) for e in streamed] == [(e["token"], round(e["logprob"], 5)) for e in entries]
+    # raw completions, legacy layout
+    raw = client.post("/v1/completions", json={"prompt": "hello", "max_tokens": 4, "temperature": 0, "ignore_eos": True,
+                                               "logprobs": 2}).json()["choices"][0]["logprobs"]
+    assert len(raw["tokens"]) == len(raw["token_logprobs"]) == len(raw["top_logprobs"]) == 4
+    assert all(len(d) <= 2 and max(d.values()) <= 0 for d in raw["top_logprobs"])
+    assert all(math.isfinite(x) for x in raw["token_logprobs"])
+    assert client.post("/v1/chat/completions", json={**body, "top_logprobs": 50}).status_code == 400
+
+
 def test_tokenizer_routes(client):
     t = client.post("/tokenize", json={"prompt": "abc def"}).json()
     assert t["count"] == len(t["tokens"]) > 0 and t["max_model_len"] == 512

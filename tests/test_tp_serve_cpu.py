@@ -7,6 +7,7 @@ import socket
 import subprocess
 import sys
 import time
+import urllib.error
 import urllib.request
 
 import pytest
@@ -78,6 +79,7 @@ def test_tp2_lockstep_serving_matches_tp1():
                ("pp", 2, ("--pipeline-parallel-size", "2"), 1), ("async", 2, ("--async-scheduling",), None),
                ("ppmb", 2, ("--pipeline-parallel-size", "2", "--pipeline-micro-batches"), 1))
     servers = []
+    lps = {}
     try:
         for key, world, extra, tp in configs:
             port = _free_port()
@@ -94,11 +96,28 @@ def test_tp2_lockstep_serving_matches_tp1():
             # one character more: of the two prompt lengths one is even, which the sequence-parallel residual needs
             r3 = _post(port, "/v1/completions", dict(body, prompt="!" + body["prompt"][::-1]))
             outs[key] = (r1["choices"][0]["text"], r3["choices"][0]["text"])
+            lp_body = {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4, "temperature": 0, "ignore_eos": True,
+                       "logprobs": True, "top_logprobs": 2}
+            if key in (1, 2, "dcp"):
+                lp = _post(port, "/v1/chat/completions", lp_body)["choices"][0]["logprobs"]["content"]
+                lps[key] = [(e["token"], e["logprob"]) for e in lp]
+            else:
+                # stages and the asynchronous scheduler do not report log-probabilities: a clear refusal
+                try:
+                    _post(port, "/v1/chat/completions", lp_body)
+                    refused = False
+                except urllib.error.HTTPError as e:
+                    refused = e.code == 400
+                assert refused
     finally:
         for _, _, proc in servers:
             _stop(proc)
     # the same weights split over two ranks give the same greedy text (fp32 activations on CPU)
     assert outs[1] == outs[2] == outs["dcp"] == outs["pp"] == outs["async"] == outs["ppmb"]
+    # log-probabilities over two ranks (logits gathered) are those of one rank
+    for key in (2, "dcp"):
+        assert [t for t, _ in lps[key]] == [t for t, _ in lps[1]]
+        assert all(abs(a - b) < 1e-3 for (_, a), (_, b) in zip(lps[key], lps[1]))
 
 
 @pytest.mark.timeout(300)
