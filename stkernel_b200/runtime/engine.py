@@ -318,6 +318,11 @@ class Engine:
         self._async_parity = 0
         self._h_async = ([torch.zeros(sc.max_num_seqs * (1 + n_spec), dtype=torch.int64, pin_memory=True) for _ in range(2)]
                          if self.async_scheduling and self.device.type == "cuda" else [])
+        self._feed_parity = 0
+        self._h_feed = ([torch.zeros(2, sc.max_num_seqs, dtype=torch.int64, pin_memory=True) for _ in range(2)]
+                        if self.async_scheduling and self.device.type == "cuda" else [])
+        self._d_feed = (torch.zeros(2, sc.max_num_seqs, dtype=torch.int64, device=self.device)
+                        if self.async_scheduling and self.device.type == "cuda" else None)
         self._next_id = 0
         self.requests: Dict[int, Request] = {}
         self._graphs: Dict[tuple, object] = {}
@@ -545,10 +550,22 @@ class Engine:
                     src.append(where[id(r)])
                     dst.append(t)
                 t += s.n
-            if src:
-                dev = self.device
-                self.buf.d_tokens.index_copy_(0, torch.tensor(dst, dtype=torch.int64, device=dev),
-                                              prev[2].index_select(0, torch.tensor(src, dtype=torch.int64, device=dev)))
+            if not src:
+                return
+            m = len(src)
+            if self.device.type == "cuda":
+                # the two index lists go up through pinned memory without blocking the host (a pageable copy would wait
+                # for the step that is running); the pinned pair alternates, as the copy of the step before may be queued
+                host = self._h_feed[self._feed_parity]
+                self._feed_parity ^= 1
+                host[0, :m] = torch.tensor(dst, dtype=torch.int64)
+                host[1, :m] = torch.tensor(src, dtype=torch.int64)
+                self._d_feed[0, :m].copy_(host[0, :m], non_blocking=True)        # contiguous rows: plain asynchronous copies
+                self._d_feed[1, :m].copy_(host[1, :m], non_blocking=True)
+                d_dst, d_src = self._d_feed[0, :m], self._d_feed[1, :m]
+            else:
+                d_dst, d_src = torch.tensor(dst, dtype=torch.int64), torch.tensor(src, dtype=torch.int64)
+            self.buf.d_tokens.index_copy_(0, d_dst, prev[2].index_select(0, d_src))
 
         nxt = self.step_begin(after_upload=feed)
         if nxt is not None:
