@@ -111,7 +111,7 @@ class AsyncEngine:
             done = r is not None and r.finished
             lps = None
             if r is not None and getattr(r.params, "logprobs", None) is not None:
-                lps = list(r.logprobs[-len(toks):])
+                lps = list(getattr(r, "logprobs", [])[-len(toks):])
             self._post(rid, TokenEvent(toks, done, r.finish_reason if done else None, logprobs=lps))
             if done:
                 self._streams.pop(rid, None)
@@ -132,14 +132,13 @@ class AsyncEngine:
                 self._wake.clear()
                 continue
             try:
-                produced = eng.step()
-            except Exception as e:                           # a failed step fails every open stream
+                self._publish(eng.step())
+            except Exception as e:                           # a failed step fails every open stream; the loop lives on
                 for rid in list(self._streams):
                     self._post(rid, TokenEvent([], True, "error", error=f"{type(e).__name__}: {e}"))
                     eng.abort(rid)
                 self._streams.clear()
                 continue
-            self._publish(produced)
 
     # -- asyncio side ------------------------------------------------------------------------
     async def generate(self, prompt: Sequence[int], params: SamplingParams) -> AsyncIterator[TokenEvent]:
@@ -330,6 +329,21 @@ def logprob_entries(tokenizer, tokens: Sequence[int], lps: Optional[Sequence[Any
     return out
 
 
+def parse_stop(value: Any) -> List[str]:
+    if value is None:
+        return []
+    if isinstance(value, str):
+        return [value] if value else []
+    if isinstance(value, list) and all(isinstance(x, str) for x in value):
+        return [x for x in value if x]
+    raise HTTPException(status_code=400, detail="stop must be a string or a list of strings")
+
+
+def want_usage(body: Dict[str, Any]) -> bool:
+    so = body.get("stream_options")
+    return isinstance(so, dict) and bool(so.get("include_usage"))
+
+
 def choice_count(body: Dict[str, Any], limit: int = 16) -> int:
     n = body.get("n", 1)
     if not isinstance(n, int) or isinstance(n, bool) or not 1 <= n <= limit:
@@ -364,6 +378,16 @@ def attach_response_format(messages: List[Dict[str, Any]], rf: Optional[Dict[str
 
 def sampling_from_request(body: Dict[str, Any], eos_id: Optional[int], max_model_len: int, n_prompt: int,
                           default_max: int = 512, default_temperature: float = 1.0) -> SamplingParams:
+    try:
+        return _sampling_from_request(body, eos_id, max_model_len, n_prompt, default_max, default_temperature)
+    except HTTPException:
+        raise
+    except (TypeError, ValueError, OverflowError) as e:
+        raise HTTPException(status_code=400, detail=f"bad sampling parameter: {type(e).__name__}: {e}") from None
+
+
+def _sampling_from_request(body: Dict[str, Any], eos_id: Optional[int], max_model_len: int, n_prompt: int,
+                           default_max: int, default_temperature: float) -> SamplingParams:
     max_tokens = body.get("max_completion_tokens") or body.get("max_tokens") or default_max
     max_tokens = max(1, min(int(max_tokens), max_model_len - n_prompt))
     seed = body.get("seed")
@@ -453,6 +477,10 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
     def err(status: int, msg: str, kind: str = "invalid_request_error"):
         return JSONResponse({"error": {"message": msg, "type": kind, "code": status}}, status_code=status)
 
+    @app.exception_handler(HTTPException)
+    async def http_error(request: Request, exc: HTTPException):
+        return err(exc.status_code, str(exc.detail))
+
     def refuse_logprobs(params: SamplingParams):
         if params.logprobs is not None and not getattr(engine, "supports_logprobs", False):
             return err(400, "log-probabilities are not available on this server (speculative decoding, asynchronous "
@@ -524,14 +552,13 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
         params = sampling_from_request(body, eos_id, max_len, len(ids), default_temperature=default_temperature)
         if refuse_logprobs(params) is not None:
             return refuse_logprobs(params)
-        stop = body.get("stop") or []
-        stop = [stop] if isinstance(stop, str) else list(stop)
+        stop = parse_stop(body.get("stop"))
         rid = f"chatcmpl-{uuid.uuid4().hex}"
         # one output pipeline (detokenizer, reasoning splitter, tool parser) and one seed per choice
         pipes = [OutputPipeline(tokenizer, thinking, tools, stop, primed=forced) for _ in range(n_choices)]
         seeds = [dataclasses.replace(params, seed=(params.seed + i) & 0x7FFFFFFF) for i in range(n_choices)]
         base = {"id": rid, "object": "chat.completion.chunk", "created": int(time.time()), "model": model_name}
-        include_usage = bool((body.get("stream_options") or {}).get("include_usage"))
+        include_usage = want_usage(body)
 
         def finish(pipe: OutputPipeline, reason: Optional[str]) -> str:
             if pipe.has_tool_calls:
@@ -642,7 +669,7 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
         for ids in all_ids:
             if len(ids) >= max_len:
                 return err(400, f"prompt has {len(ids)} tokens; the model's context is {max_len}")
-        stop = [body["stop"]] if isinstance(body.get("stop"), str) else (body.get("stop") or [])
+        stop = parse_stop(body.get("stop"))
 
         async def one(k: int):
             ids = all_ids[k // n_choices]
@@ -692,7 +719,7 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
         if refuse_logprobs(params) is not None:
             return refuse_logprobs(params)
         rid = f"cmpl-{uuid.uuid4().hex}"
-        pipe = OutputPipeline(tokenizer, False, None, [body["stop"]] if isinstance(body.get("stop"), str) else (body.get("stop") or []))
+        pipe = OutputPipeline(tokenizer, False, None, parse_stop(body.get("stop")))
         base = {"id": rid, "object": "text_completion", "created": int(time.time()), "model": model_name}
         if body.get("stream"):
             async def events():
@@ -794,7 +821,7 @@ def create_app(engine: Engine, tokenizer: ChatTokenizer, model_name: str = "deep
         if len(ids) >= max_len:
             return err(400, f"prompt has {len(ids)} tokens; the model's context is {max_len}")
         params = sampling_from_request(body, eos_id, max_len, len(ids), default_temperature=default_temperature)
-        pipe = OutputPipeline(tokenizer, thinking, tools, body.get("stop_sequences") or [], primed=forced)
+        pipe = OutputPipeline(tokenizer, thinking, tools, parse_stop(body.get("stop_sequences")), primed=forced)
         mid = f"msg_{uuid.uuid4().hex[:24]}"
 
         def stop_reason(reason):

@@ -68,7 +68,7 @@ class LockstepLeader(AsyncEngine):
             if not eng.has_work():
                 continue
             try:
-                produced = eng.step()
+                self._publish(eng.step())
             except Exception as e:                           # a failed step ends every open stream and the job:
                 from .api_server import TokenEvent          # the ranks can no longer be assumed to be in step
                 for rid in list(self._streams):
@@ -77,7 +77,6 @@ class LockstepLeader(AsyncEngine):
                 self.failed = f"{type(e).__name__}: {e}"
                 print(f"leader: step failed ({self.failed}); stopping", file=sys.stderr)
                 os._exit(4)
-            self._publish(produced)
         self._broadcast([(EV_STOP, None)])
 
 

@@ -688,3 +688,37 @@ def test_output_pipeline_is_independent_of_how_tokens_are_grouped():
         for _ in range(3):
             sizes = [rng.randint(1, 9) for _ in range(7)]
             assert _pipe_run(text, think, stop, sizes) == whole, (text, stop, sizes)
+
+
+def test_random_request_bodies_never_cause_a_server_error_or_stop_the_engine_thread():
+    """Wrongly typed and contradictory fields on every POST route: the answer is a 2xx or a 4xx, never a 5xx, and the
+    server still answers a well-formed request afterwards."""
+    import random
+    from fastapi.testclient import TestClient
+    from stkernel_b200.serve.api_server import create_app
+    tok = ChatTokenizer(ByteTokenizer(1024))
+    rng = random.Random(0)
+    vals = [None, True, False, 0, -1, 1, 3, 0.5, -0.5, "", "x", "auto", "none", "required", [], [1, 2], ["a"], {},
+            {"type": "json_object"}, {"type": "function", "function": {"name": "get_weather"}},
+            [{"role": "user", "content": "hi"}], [{"role": "user"}], [{"content": "x"}], [{"role": "tool", "content": "r"}],
+            [{"role": "assistant", "tool_calls": [{"function": {"name": "f", "arguments": "{"}}]}],
+            [{"role": "user", "content": [{"type": "text", "text": "a"}]}], TOOLS, [{"type": "function"}], "think",
+            {"thinking": True}, {"include_usage": True}]
+    keys = ["messages", "prompt", "max_tokens", "temperature", "top_p", "top_k", "n", "stream", "stop", "seed", "tools",
+            "tool_choice", "response_format", "logprobs", "top_logprobs", "chat_template_kwargs", "stream_options",
+            "min_tokens", "ignore_eos", "system", "thinking", "stop_sequences", "reasoning_effort", "max_completion_tokens",
+            "tokens"]
+    routes = ["/v1/chat/completions", "/v1/completions", "/v1/messages", "/tokenize", "/detokenize", "/v1/messages/count_tokens"]
+    with TestClient(create_app(ScriptedEngine(tok, "hello world"), tok, "scripted"), raise_server_exceptions=False) as c:
+        for _ in range(400):
+            body = {k: rng.choice(vals) for k in rng.sample(keys, rng.randint(0, 7))}
+            if rng.random() < 0.6:
+                body["messages"] = [{"role": "user", "content": "hi"}]
+            if rng.random() < 0.3:
+                body["prompt"] = "hello"
+            body.setdefault("max_tokens", 3)
+            path = rng.choice(routes)
+            r = c.post(path, json=body)
+            assert r.status_code < 500, (path, body, r.text[:200])
+        ok = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 3})
+        assert ok.status_code == 200 and ok.json()["usage"]["completion_tokens"] == 3
