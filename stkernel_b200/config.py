@@ -29,6 +29,27 @@ MXFP4_GROUP = 32             # elements per ue8m0 scale (MXFP4 checkpoint layout
 FP8_MAX = 448.0
 
 
+def _check_field_types(cfg) -> None:
+    """Every field holds a value of its declared kind (a `config.json` with a string where a number belongs must fail as
+    a configuration error that names the field, not as a TypeError somewhere in the arithmetic)."""
+    for f in dataclasses.fields(cfg):
+        v, d = getattr(cfg, f.name), f.default
+        if isinstance(d, bool):
+            ok = isinstance(v, bool)
+        elif isinstance(d, int):
+            ok = isinstance(v, int) and not isinstance(v, bool)
+        elif isinstance(d, float):
+            ok = isinstance(v, (int, float)) and not isinstance(v, bool) and v == v and abs(v) != float("inf")
+        elif isinstance(d, str):
+            ok = isinstance(v, str)
+        elif isinstance(d, tuple):
+            ok = isinstance(v, tuple) and all(isinstance(x, int) and not isinstance(x, bool) for x in v)
+        else:
+            ok = True
+        if not ok:
+            raise ConfigError(f"{f.name}: {v!r} is not a valid {type(d).__name__}")
+
+
 @dataclass(frozen=True)
 class ModelConfig:
     """Architecture of a DeepSeek-V4-style decoder.
@@ -115,6 +136,14 @@ class ModelConfig:
         return r if r > 1 else 0
 
     def validate(self) -> None:
+        _check_field_types(self)
+        for name in ("vocab_size", "hidden_size", "num_hidden_layers", "num_attention_heads", "head_dim", "q_lora_rank",
+                     "o_lora_rank", "o_groups", "index_n_heads", "index_head_dim", "index_topk", "hc_mult",
+                     "n_routed_experts", "num_experts_per_tok", "moe_intermediate_size", "sliding_window"):
+            if getattr(self, name) < 1:
+                raise ConfigError(f"{name} must be positive")
+        if self.qk_rope_head_dim < 0 or self.n_mtp_layers < 0 or self.n_shared_experts < 0 or self.num_hash_layers < 0:
+            raise ConfigError("qk_rope_head_dim, n_mtp_layers, n_shared_experts and num_hash_layers must not be negative")
         if self.head_dim <= self.qk_rope_head_dim:
             raise ConfigError("head_dim must exceed qk_rope_head_dim")
         if self.nope_dim % KV_QUANT_BLOCK:

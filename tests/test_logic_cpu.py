@@ -309,3 +309,28 @@ def test_replay_drafter_counts_only_steps_drafted_from_a_valid_oracle():
     req.output = req.output + [5]
     d(req, [1, 2, 3])
     assert (d.steps_in_sync, d.tokens_in_sync) == (2, 6)        # steps after the divergence are not counted
+
+
+def test_model_config_rejects_wrongly_typed_fields_as_configuration_errors():
+    """A `config.json` with a string where a number belongs (or a scalar where a list belongs) fails with a
+    configuration error that names the field; randomised over all fields."""
+    import dataclasses
+    from stkernel_b200.config import ConfigError, model_config_from_hf
+    base = {k: (list(v) if isinstance(v, tuple) else v) for k, v in dataclasses.asdict(tiny_config()).items()}
+    assert model_config_from_hf(base) == tiny_config()
+    for name, value in (("hidden_size", "4096"), ("compress_ratios", 4), ("norm_topk_prob", 1), ("rope_theta", "x"),
+                        ("scoring_func", 3), ("num_hidden_layers", 0), ("hc_eps", float("nan")), ("o_groups", True)):
+        with pytest.raises(ConfigError) as e:
+            model_config_from_hf({**base, name: value})
+        assert name in str(e.value)
+    rng = random.Random(0)
+    vals = [None, 0, -1, 2, 64, 0.5, "", "fp8", [], [4, 0], True, {}, 10 ** 9]
+    for _ in range(3000):
+        hf = dict(base)
+        for k in rng.sample(list(base), rng.randint(1, 4)):
+            hf[k] = rng.choice(vals)
+        try:
+            cfg = model_config_from_hf(hf)
+            [cfg.layer_kind(i) for i in range(cfg.num_hidden_layers)]
+        except ConfigError:
+            pass
