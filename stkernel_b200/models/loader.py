@@ -74,18 +74,32 @@ class SafetensorsIndex:
         return sorted(os.path.join(path, n) for n in os.listdir(path) if n.endswith(".safetensors"))
 
     def _read_header(self, file: str) -> None:
+        size = os.path.getsize(file)
         with open(file, "rb") as f:
-            (n,) = struct.unpack("<Q", f.read(8))
-            if n > 256 << 20:
-                raise ValueError(f"{file}: implausible header length {n}")
+            head = f.read(8)
+            if len(head) < 8:
+                raise ValueError(f"{file}: shorter than a safetensors header")
+            (n,) = struct.unpack("<Q", head)
+            if n > 256 << 20 or n > size - 8:
+                raise ValueError(f"{file}: implausible header length {n} (file of {size} bytes)")
             header = json.loads(f.read(n))
+        if not isinstance(header, dict):
+            raise ValueError(f"{file}: the header is not a JSON object")
         self._data0[file] = 8 + n
         for name, meta in header.items():
             if name == "__metadata__":
                 continue
+            # a damaged or truncated shard fails here, by tensor name, not later inside a view of too few bytes
+            if not (isinstance(meta, dict) and isinstance(meta.get("dtype"), str) and isinstance(meta.get("shape"), list)
+                    and isinstance(meta.get("data_offsets"), list) and len(meta["data_offsets"]) == 2
+                    and all(isinstance(x, int) and not isinstance(x, bool) and x >= 0
+                            for x in meta["shape"] + meta["data_offsets"])):
+                raise ValueError(f"{file}: malformed entry for tensor {name}")
             if meta["dtype"] not in _DTYPES:
                 raise ValueError(f"{file}: tensor {name} has unsupported dtype {meta['dtype']}")
             a, b = meta["data_offsets"]
+            if a > b or 8 + n + b > size:
+                raise ValueError(f"{file}: tensor {name} claims bytes [{a}, {b}) of a data region of {size - 8 - n}")
             self.tensors[name] = TensorInfo(file, meta["dtype"], tuple(meta["shape"]), a, b)
 
     def __contains__(self, name: str) -> bool:

@@ -105,3 +105,49 @@ def test_shard_plan_covers_and_partitions():
     assert L.plan_bytes(full, 8, 0) < 40e9 and L.plan_bytes(full, 1, 0) > 150e9
     with pytest.raises(ValueError):
         L.shard_plan(cfg, 3, 0)
+
+
+def test_damaged_shards_fail_as_value_errors_that_name_the_file(tmp_path):
+    """Truncated files, flipped header bytes, absurd header lengths and malformed tensor entries: a ValueError at index
+    time (or when the tensor is read), never another exception from deep inside a view."""
+    import json
+    import random
+    import struct
+    from stkernel_b200.models.loader import SafetensorsIndex, write_safetensors
+    good = tmp_path / "good"
+    good.mkdir()
+    write_safetensors(str(good / "model-00001-of-00001.safetensors"),
+                      {"a": torch.randn(4, 8), "b": torch.arange(10, dtype=torch.int32)})
+    raw = (good / "model-00001-of-00001.safetensors").read_bytes()
+    assert set(SafetensorsIndex(str(good)).keys()) == {"a", "b"}
+    rng = random.Random(0)
+    bad = tmp_path / "bad"
+    bad.mkdir()
+    refused = 0
+    for _ in range(300):
+        b = bytearray(raw)
+        op = rng.choice(["trunc", "flip", "hdrlen", "json"])
+        if op == "trunc":
+            b = b[:rng.randrange(len(b))]
+        elif op == "flip":
+            for _ in range(rng.randint(1, 5)):
+                b[rng.randrange(min(len(b), 200))] = rng.randrange(256)
+        elif op == "hdrlen":
+            b[:8] = struct.pack("<Q", rng.choice([0, 1, 7, 10 ** 6, 2 ** 63, len(b)]))
+        else:
+            n = struct.unpack("<Q", bytes(b[:8]))[0]
+            hdr = json.loads(bytes(b[8:8 + n]))
+            hdr[rng.choice(list(hdr))] = rng.choice([None, 1, {"dtype": "F32"},
+                                                     {"dtype": "XX", "shape": [1], "data_offsets": [0, 4]},
+                                                     {"dtype": "F32", "shape": [4, 8], "data_offsets": [0, 10 ** 9]},
+                                                     {"dtype": "F32", "shape": [-1], "data_offsets": [4, 0]}])
+            h = json.dumps(hdr).encode()
+            b = bytearray(struct.pack("<Q", len(h)) + h + bytes(b[8 + n:]))
+        (bad / "model-00001-of-00001.safetensors").write_bytes(bytes(b))
+        try:
+            idx = SafetensorsIndex(str(bad))
+            for name in list(idx.keys()):
+                idx.get(name)
+        except (ValueError, KeyError):
+            refused += 1
+    assert refused > 200
