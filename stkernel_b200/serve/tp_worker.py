@@ -42,7 +42,19 @@ class LockstepLeader(AsyncEngine):
         super().__init__(engine)
 
     def _broadcast(self, events: List[Tuple[int, Any]]) -> None:
-        dist.broadcast_object_list([events], src=0, group=self.cpu_group)
+        try:
+            dist.broadcast_object_list([events], src=0, group=self.cpu_group)
+        except RuntimeError as e:
+            # a follower is gone (or the group timed out): the ranks cannot be in step any more.  Every open stream gets
+            # an error and the process ends, so that the supervisor restarts the stack instead of probing a server that
+            # still answers /health with nothing behind it.
+            from .api_server import TokenEvent
+            for rid in list(self._streams):
+                self._post(rid, TokenEvent([], True, "error", error=f"control channel lost: {e}"))
+            self._streams.clear()
+            self.failed = f"control channel lost: {e}"
+            print(f"leader: {self.failed}; stopping", file=sys.stderr)
+            os._exit(3)
 
     def _on_add(self, rid: int, prompt: List[int], params: SamplingParams) -> None:
         self._mirror.append((EV_ADD, (list(prompt), dict(vars(params)))))

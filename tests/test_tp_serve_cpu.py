@@ -170,3 +170,37 @@ def test_follower_exits_when_leader_dies(tmp_path):
         assert not p.is_alive()
     out = json.load(open(res))
     assert out["rc"] == 3 and out["dt"] < 60
+
+
+def _leader_main(rank, port):
+    import datetime
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE="2")
+    dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=10))
+    if rank == 1:
+        # a follower that takes one heartbeat and then dies
+        box = [None]
+        dist.broadcast_object_list(box, src=0)
+        os._exit(0)
+    import types
+    from stkernel_b200.runtime.metrics import Metrics
+    from stkernel_b200.serve.tp_worker import LockstepLeader
+    idle = types.SimpleNamespace(has_work=lambda: False, requests={}, metrics=Metrics())
+    LockstepLeader(idle, dist.group.WORLD)            # its thread sends heartbeats; the second one finds nobody
+    time.sleep(60)
+    os._exit(0)                                       # not reached: the leader ends the process with code 3
+
+
+@pytest.mark.timeout(120)
+def test_leader_exits_when_a_follower_dies():
+    import torch.multiprocessing as mp
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    ps = [ctx.Process(target=_leader_main, args=(r, port)) for r in range(2)]
+    t0 = time.time()
+    for p in ps:
+        p.start()
+    for p in ps:
+        p.join(90)
+        assert not p.is_alive()
+    assert ps[0].exitcode == 3 and ps[1].exitcode == 0 and time.time() - t0 < 50
